@@ -1,0 +1,169 @@
+/*
+ * mlxs_moe.h: C ABI of the B200 routed-MoE layer (router -> dispatch -> grouped expert gate/up/down with in-register
+ * weight decode -> SwiGLU -> weighted combine), the drop-in for mlx-stream's routed-expert hot path.
+ *
+ * Conventions follow the reference's own native boundary (csrc/q3_lookahead4.h:44-98, csrc/mlx_alloc_shim.h:14-17,
+ * src/sdk_ext/expert/io.zig:62-69): every call returns an int (0 = ok, negative = a named refusal), the message of
+ * the last refusal on the calling thread is at mlxs_moe_last_error(), the caller compares mlxs_moe_abi() with the
+ * value it was built against and refuses a mismatch, buffers are caller-owned, there are no callbacks.
+ * One caller thread per handle (the reference's single inference thread, sdk/arch.zig:100-105).  All device work is
+ * queued on the stream the caller passes (a cudaStream_t as void*, NULL = the default stream).
+ * Pointers named *_dev are device pointers on the handle's device; *_host are host pointers.
+ * There is no CPU fallback: without a CUDA device every compute entry refuses with MLXS_E_CUDA.
+ */
+#ifndef MLXS_MOE_H
+#define MLXS_MOE_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MLXS_MOE_ABI 2026112501
+
+/* refusals (the names mirror the reference's refusal sets: src/sdk_ext/quant.zig:94-111, src/expert/bank.zig:79-101) */
+enum {
+    MLXS_OK = 0,
+    MLXS_E_ARG = -1,          /* null / out-of-range argument */
+    MLXS_E_CONFIG = -2,       /* a config field is not implemented (named in the message) */
+    MLXS_E_CUDA = -3,         /* a CUDA runtime call failed (message carries the CUDA error) */
+    MLXS_E_BANK = -4,         /* record bytes / geometry do not match the bank kind */
+    MLXS_E_NOT_LOADED = -5,   /* a routed expert (or the shared expert / router bias) was never loaded */
+    MLXS_E_TOO_MANY_TOKENS = -6,
+    MLXS_E_DEVICE_STATUS = -7, /* a kernel recorded an error word (bad id, bounded wait ran out) */
+    MLXS_E_MANIFEST = -8,     /* manifest field mismatch (named) */
+    MLXS_E_EP = -9            /* expert-parallel exchange not initialised / failed */
+};
+
+/* bank kinds: the record layouts are the reference's own.
+ *  EXL3_K3_MUL1: nine segments gate/up/down x {code I16 [in/16,out/16,48], rout F16 [out], rin F16 [in]}
+ *                (src/expert/bank.zig:116-141)
+ *  MXFP4:        six parts gate/up/down x {weight U32 [out,in/8], scales U8 E8M0 [out,in/32]}
+ *                (src/arch/mimo_v2/bank.zig:13-27, 341-345)
+ *  NVFP4:        nine parts gate/up/down x {weight U32 [out,in/8], scales U8 E4M3 [out,in/16], global F32}
+ *                (src/arch/glm5_next/bank.zig:5-13) */
+enum { MLXS_BANK_EXL3_K3_MUL1 = 0, MLXS_BANK_MXFP4 = 1, MLXS_BANK_NVFP4 = 2 };
+/* router scoring: sqrt(softplus) = DeepSeek-V4.1 (src/arch/deepseek_v41/graph.zig:2032-2051), sigmoid = MiMo / GLM
+ * (src/arch/mimo_v2/kernels/mimo_glue_top8.metal, src/arch/glm5_next/kernels/glm5n_glue_top8.metal); softmax has no
+ * counterpart in the reference (every arch refuses it) and is provided for the MiMo-shaped benchmark config. */
+enum { MLXS_SCORE_SQRTSOFTPLUS = 0, MLXS_SCORE_SIGMOID = 1, MLXS_SCORE_SOFTMAX = 2 };
+/* activation between gate/up and down (src/sdk_ext/quant.zig:54-61) */
+enum { MLXS_ACT_SWIGLU = 0, MLXS_ACT_SWIGLU_CLAMPED = 1 };
+/* combine arithmetic:
+ *  F32:   sum_k f32(row_k) w_k + shared in f32, one rounding to bf16 (src/arch/deepseek_v41/graph.zig:2182-2184)
+ *  CHAIN: rows stored bf16, each product rounded, folded k = 0..top_k-1, bf16 once, then a bf16 add of the shared row
+ *         (src/arch/mimo_v2/kernels/mimo_moe_combine.metal, src/arch/glm5_next/kernels/glm5n_moe_combine.metal) */
+enum { MLXS_COMBINE_F32 = 0, MLXS_COMBINE_CHAIN = 1 };
+
+typedef struct mlxs_moe mlxs_moe; /* opaque */
+
+typedef struct {
+    uint32_t struct_size; /* sizeof(mlxs_moe_config): the version gate of the struct */
+    uint32_t hidden, inter, n_experts, top_k, n_layers;
+    uint32_t bank_kind;
+    uint32_t act;
+    float act_limit; /* for MLXS_ACT_SWIGLU_CLAMPED */
+    uint32_t scoring;
+    uint32_t norm_topk;   /* weights / (sum + 1e-20) */
+    float routed_scale;   /* x routed_scaling_factor */
+    uint32_t shared_expert; /* 1: a bf16 dense shared expert is added (src/arch/deepseek_v41/graph.zig:2162-2172) */
+    uint32_t combine;
+    uint32_t max_tokens; /* largest T of one call (the reference's call bound is 16,384 rows: README.md:181-195) */
+    int32_t device;      /* CUDA ordinal */
+    uint32_t ep_world, ep_rank; /* expert parallel: this rank owns experts [rank E/world, (rank+1) E/world) */
+} mlxs_moe_config;
+
+typedef struct {
+    uint64_t route_calls, expert_calls, tokens, assignments;
+    uint64_t distinct_experts_last; /* distinct routed experts of the last call on this rank */
+    uint64_t weight_bytes_last;     /* algorithmic weight bytes of the last call: distinct x bytes per expert */
+    uint64_t a2a_bytes_sent, a2a_bytes_recv;
+    uint64_t resident_bytes;        /* HBM held by the handle */
+    uint32_t device_status;         /* sticky error word written by kernels (0 = none) */
+    uint32_t reserved;
+} mlxs_moe_stats;
+
+/* version gate and error text (csrc/q3_lookahead4.h:91, csrc/mlx_alloc_shim.h:14-17) */
+int32_t mlxs_moe_abi(void);
+const char *mlxs_moe_last_error(void);
+
+/* Module.init's quant accept: every field checked once, refusals by name (src/exl3/quant.zig:202-212,
+ * src/sdk_ext/quant.zig:94-111).  Allocates the resident bank and the workspaces for max_tokens. */
+int mlxs_moe_create(const mlxs_moe_config *cfg, mlxs_moe **out);
+void mlxs_moe_destroy(mlxs_moe *h);
+
+/* the bank kind's record size at the handle's dims (src/expert/bank.zig:116-141): logical bytes and the 4096-padded
+ * stride records have in an experts.bin */
+int mlxs_moe_record_bytes(const mlxs_moe *h, uint64_t *logical_bytes, uint64_t *record_stride);
+
+/* Replaces the expert source's fill of a slot row (src/sdk_ext/expert.zig:226-264; csrc/q3_lookahead4_exl3.c): one
+ * expert's record, in the reference's layout, becomes HBM resident.  `record` is a host pointer (on_device = 0) or a
+ * device pointer (1); nbytes >= logical bytes.  Experts outside this rank's shard are accepted and ignored. */
+int mlxs_moe_load_expert(mlxs_moe *h, uint32_t layer, uint32_t expert, const void *record, uint64_t nbytes,
+                         int on_device);
+/* Bank.open + stream fill (src/expert/bank.zig:208-324, src/arch/mimo_v2/bank.zig:172-260,
+ * src/arch/glm5_next/bank.zig:29-48): reads <dir>/expert-manifest*.json + experts.bin in the reference's formats,
+ * verifies geometry (and record sha256 when the manifest carries it) and loads this rank's experts. */
+int mlxs_moe_load_bank(mlxs_moe *h, const char *dir);
+
+/* the router's noaux_tc correction bias, f32 [n_experts] host, NULL = zeros (src/arch/deepseek_v41/graph.zig:2035) */
+int mlxs_moe_set_router_bias(mlxs_moe *h, uint32_t layer, const float *bias_host);
+/* the shared expert's bf16 linears: w1 (gate) [inter, hidden], w3 (up) [inter, hidden], w2 (down) [hidden, inter]
+ * (src/arch/deepseek_v41/graph.zig:2162-2172 sh_w1 / sh_w3 / sh_w2) */
+int mlxs_moe_set_shared(mlxs_moe *h, uint32_t layer, const void *w1, const void *w3, const void *w2, int on_device);
+
+/* Gate.__call__'s tail (src/arch/deepseek_v41/graph.zig:2041-2051, src/kernels/exl3/q3rc_router_tail.metal:12-40,
+ * src/arch/mimo_v2/kernels/mimo_glue_top8.metal): logits f32 [T, n_experts] -> ids i32 [T, top_k] in rank order
+ * (score + bias descending, ties to the lower index, NaN last), weights f32 [T, top_k]. */
+int mlxs_moe_route(mlxs_moe *h, uint32_t layer, const float *logits_dev, uint32_t T, int32_t *ids_dev,
+                   float *weights_dev, void *stream);
+/* Hook.routed (src/arch/deepseek_v41/experts.zig:1214-1223): x bf16 [T, hidden], ids [T, top_k] -> the unweighted
+ * expert outputs f32 [T, top_k, hidden] in router order. */
+int mlxs_moe_routed(mlxs_moe *h, uint32_t layer, const void *x_dev, const int32_t *ids_dev, uint32_t T,
+                    float *out_dev, void *stream);
+/* Source.forward + forwardShared (src/arch/glm5_next/experts.zig:566-595, 639-653): x bf16 [T, hidden], ids, weights
+ * -> y bf16 [T, hidden] (routed experts, weighted combine, + shared expert when configured). */
+int mlxs_moe_experts(mlxs_moe *h, uint32_t layer, const void *x_dev, const int32_t *ids_dev,
+                     const float *weights_dev, uint32_t T, void *y_dev, void *stream);
+/* Tr.moe (src/arch/deepseek_v41/graph.zig:2196-2240) from the router's logits on: route + experts in one call; the
+ * ids never visit the host (the reference's routing barrier, experts.zig:1576-1587, is gone). */
+int mlxs_moe_forward(mlxs_moe *h, uint32_t layer, const void *x_dev, const float *logits_dev, uint32_t T, void *y_dev,
+                     void *stream);
+/* the same through host buffers (what arch.step / arch.prefill's caller holds): copies x and logits in, runs,
+ * copies y out and synchronises the stream. */
+int mlxs_moe_forward_host(mlxs_moe *h, uint32_t layer, const void *x_host, const float *logits_host, uint32_t T,
+                          void *y_host, void *stream);
+
+/* quant seam, one projection without the rotations: z f32 [rows, out] = xh f32 [rows, in] . W_hat of
+ * (layer, expert, proj 0 gate / 1 up / 2 down) through the same in-register decode as the layer path.  One-hot rows
+ * give W_hat's rows bit for bit: the reference's decode_table self-check (src/exl3/selfcheck.zig:848-901). */
+int mlxs_moe_exl3_gemv(mlxs_moe *h, uint32_t layer, uint32_t expert, uint32_t proj, const float *xh_dev,
+                       uint32_t rows, float *z_dev, void *stream);
+
+int mlxs_moe_stats_get(mlxs_moe *h, mlxs_moe_stats *out);
+
+/* per-stage device timing with CUDA events on the caller's stream, off by default (the reference's comptime profile
+ * hooks and kernel bench: src/sdk_ext/profile.zig:1-60, src/arch/glm5_next/exl3_kbench.zig:1-23).  `read` synchronises
+ * the pending events, returns the sums since the last read and clears them. */
+enum { MLXS_STAGE_ROUTER = 0, MLXS_STAGE_DISPATCH, MLXS_STAGE_PREP, MLXS_STAGE_GATE_UP, MLXS_STAGE_DOWN,
+       MLXS_STAGE_SHARED, MLXS_STAGE_COMBINE, MLXS_STAGE_EXCHANGE, MLXS_STAGE_COUNT };
+typedef struct {
+    double ms[MLXS_STAGE_COUNT];
+    uint64_t launches[MLXS_STAGE_COUNT];
+} mlxs_moe_profile;
+int mlxs_moe_profile_enable(mlxs_moe *h, int on);
+int mlxs_moe_profile_read(mlxs_moe *h, mlxs_moe_profile *out);
+
+/* ---- expert parallel (no counterpart in the reference: it pages experts from SSD on one GPU; here they are HBM
+ * resident and sharded, with a dispatch and a combine all-to-all per layer) ---- */
+/* 128-byte NCCL unique id made on rank 0 and handed to every rank by the host */
+int mlxs_moe_ep_unique_id(void *id128_out);
+int mlxs_moe_ep_init(mlxs_moe *h, const void *id128);
+/* host-side plan of one exchange (pure function, also used by the CPU tests): for `n` assignments with expert ids
+ * `ids`, counts per destination rank */
+int mlxs_moe_ep_plan(const int32_t *ids, uint64_t n, uint32_t n_experts, uint32_t world, uint64_t *send_counts);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

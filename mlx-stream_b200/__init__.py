@@ -1,0 +1,182 @@
+"""Host-side Python view of libmlxs_moe.so (ctypes over the C ABI in include/mlxs_moe.h).
+
+The product is the shared library; this module only mirrors the reference's seam names so the parity tests and the
+benchmark read like the reference's own callers:
+  MoE.route    = Gate.__call__'s tail            (src/arch/deepseek_v41/graph.zig:2041-2051)
+  MoE.routed   = Hook.routed                     (src/arch/deepseek_v41/experts.zig:1214-1223)
+  MoE.experts  = Source.forward / forwardShared  (src/arch/glm5_next/experts.zig:566-595, 639-653)
+  MoE.forward  = Tr.moe from the logits on       (src/arch/deepseek_v41/graph.zig:2196-2240)
+Pointers are plain integers (device or host addresses); nothing here touches torch.  There is no CPU fallback: if
+the library is missing or the machine has no CUDA device the calls raise.
+"""
+import ctypes as C
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+LIB_PATH = HERE / "libmlxs_moe.so"
+ABI = 2026112501
+
+BANK_EXL3_K3_MUL1, BANK_MXFP4, BANK_NVFP4 = 0, 1, 2
+SCORE_SQRTSOFTPLUS, SCORE_SIGMOID, SCORE_SOFTMAX = 0, 1, 2
+ACT_SWIGLU, ACT_SWIGLU_CLAMPED = 0, 1
+COMBINE_F32, COMBINE_CHAIN = 0, 1
+
+EXPORTS = [
+    "mlxs_moe_abi", "mlxs_moe_last_error", "mlxs_moe_create", "mlxs_moe_destroy", "mlxs_moe_record_bytes",
+    "mlxs_moe_load_expert", "mlxs_moe_load_bank", "mlxs_moe_set_router_bias", "mlxs_moe_set_shared", "mlxs_moe_route",
+    "mlxs_moe_routed", "mlxs_moe_experts", "mlxs_moe_forward", "mlxs_moe_forward_host", "mlxs_moe_exl3_gemv",
+    "mlxs_moe_stats_get", "mlxs_moe_profile_enable", "mlxs_moe_profile_read", "mlxs_moe_ep_unique_id", "mlxs_moe_ep_init", "mlxs_moe_ep_plan",
+]
+
+
+class Config(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("hidden", C.c_uint32), ("inter", C.c_uint32), ("n_experts", C.c_uint32),
+                ("top_k", C.c_uint32), ("n_layers", C.c_uint32), ("bank_kind", C.c_uint32), ("act", C.c_uint32),
+                ("act_limit", C.c_float), ("scoring", C.c_uint32), ("norm_topk", C.c_uint32),
+                ("routed_scale", C.c_float), ("shared_expert", C.c_uint32), ("combine", C.c_uint32),
+                ("max_tokens", C.c_uint32), ("device", C.c_int32), ("ep_world", C.c_uint32), ("ep_rank", C.c_uint32)]
+
+
+class Stats(C.Structure):
+    _fields_ = [("route_calls", C.c_uint64), ("expert_calls", C.c_uint64), ("tokens", C.c_uint64),
+                ("assignments", C.c_uint64), ("distinct_experts_last", C.c_uint64), ("weight_bytes_last", C.c_uint64),
+                ("a2a_bytes_sent", C.c_uint64), ("a2a_bytes_recv", C.c_uint64), ("resident_bytes", C.c_uint64),
+                ("device_status", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+STAGES = ["router", "dispatch", "prep", "gate_up", "down", "shared", "combine", "exchange"]
+
+
+class Profile(C.Structure):
+    _fields_ = [("ms", C.c_double * 8), ("launches", C.c_uint64 * 8)]
+
+
+class MlxsError(RuntimeError):
+    def __init__(self, rc, msg):
+        super().__init__(f"mlxs_moe rc={rc}: {msg}")
+        self.rc = rc
+        self.msg = msg
+
+
+_lib = None
+
+
+def lib():
+    """The loaded library.  Raises if it has not been built (python mlx-stream_b200/build.py)."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise FileNotFoundError(f"{LIB_PATH} is missing: run `python mlx-stream_b200/build.py` (needs nvcc)")
+        L = C.CDLL(str(LIB_PATH))
+        L.mlxs_moe_abi.restype = C.c_int32
+        L.mlxs_moe_last_error.restype = C.c_char_p
+        L.mlxs_moe_create.argtypes = [C.POINTER(Config), C.POINTER(C.c_void_p)]
+        L.mlxs_moe_destroy.argtypes = [C.c_void_p]
+        L.mlxs_moe_destroy.restype = None
+        L.mlxs_moe_record_bytes.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
+        L.mlxs_moe_load_expert.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint64, C.c_int]
+        L.mlxs_moe_load_bank.argtypes = [C.c_void_p, C.c_char_p]
+        L.mlxs_moe_set_router_bias.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p]
+        L.mlxs_moe_set_shared.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
+        L.mlxs_moe_route.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.mlxs_moe_routed.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
+        L.mlxs_moe_experts.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32,
+                                       C.c_void_p, C.c_void_p]
+        L.mlxs_moe_forward.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
+        L.mlxs_moe_forward_host.argtypes = L.mlxs_moe_forward.argtypes
+        L.mlxs_moe_exl3_gemv.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32,
+                                         C.c_void_p, C.c_void_p]
+        L.mlxs_moe_stats_get.argtypes = [C.c_void_p, C.POINTER(Stats)]
+        L.mlxs_moe_profile_enable.argtypes = [C.c_void_p, C.c_int]
+        L.mlxs_moe_profile_read.argtypes = [C.c_void_p, C.POINTER(Profile)]
+        L.mlxs_moe_ep_unique_id.argtypes = [C.c_void_p]
+        L.mlxs_moe_ep_init.argtypes = [C.c_void_p, C.c_void_p]
+        L.mlxs_moe_ep_plan.argtypes = [C.c_void_p, C.c_uint64, C.c_uint32, C.c_uint32, C.c_void_p]
+        if L.mlxs_moe_abi() != ABI:
+            raise RuntimeError(f"libmlxs_moe.so ABI {L.mlxs_moe_abi()} != binding ABI {ABI}")
+        _lib = L
+    return _lib
+
+
+def last_error():
+    return lib().mlxs_moe_last_error().decode()
+
+
+def _check(rc):
+    if rc != 0:
+        raise MlxsError(rc, last_error())
+
+
+def make_config(hidden, inter, n_experts, top_k, n_layers=1, bank_kind=BANK_EXL3_K3_MUL1, act=ACT_SWIGLU_CLAMPED,
+                act_limit=10.0, scoring=SCORE_SQRTSOFTPLUS, norm_topk=True, routed_scale=1.0, shared_expert=False,
+                combine=COMBINE_F32, max_tokens=64, device=0, ep_world=1, ep_rank=0):
+    return Config(C.sizeof(Config), hidden, inter, n_experts, top_k, n_layers, bank_kind, act, act_limit, scoring,
+                  int(norm_topk), routed_scale, int(shared_expert), combine, max_tokens, device, ep_world, ep_rank)
+
+
+class MoE:
+    """One handle = one rank's routed-MoE layers (weights resident in HBM)."""
+
+    def __init__(self, cfg: Config):
+        self.cfg = cfg
+        self._h = C.c_void_p()
+        _check(lib().mlxs_moe_create(C.byref(cfg), C.byref(self._h)))
+
+    def close(self):
+        if self._h:
+            lib().mlxs_moe_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def record_bytes(self):
+        a, b = C.c_uint64(), C.c_uint64()
+        _check(lib().mlxs_moe_record_bytes(self._h, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
+    def load_expert(self, layer, expert, record_ptr, nbytes, on_device=False):
+        _check(lib().mlxs_moe_load_expert(self._h, layer, expert, record_ptr, nbytes, int(on_device)))
+
+    def load_bank(self, directory):
+        _check(lib().mlxs_moe_load_bank(self._h, str(directory).encode()))
+
+    def set_router_bias(self, layer, bias_host_ptr):
+        _check(lib().mlxs_moe_set_router_bias(self._h, layer, bias_host_ptr))
+
+    def set_shared(self, layer, w1, w3, w2, on_device=False):
+        _check(lib().mlxs_moe_set_shared(self._h, layer, w1, w3, w2, int(on_device)))
+
+    def route(self, layer, logits, T, ids, weights, stream=None):
+        _check(lib().mlxs_moe_route(self._h, layer, logits, T, ids, weights, stream))
+
+    def routed(self, layer, x, ids, T, out, stream=None):
+        _check(lib().mlxs_moe_routed(self._h, layer, x, ids, T, out, stream))
+
+    def experts(self, layer, x, ids, weights, T, y, stream=None):
+        _check(lib().mlxs_moe_experts(self._h, layer, x, ids, weights, T, y, stream))
+
+    def forward(self, layer, x, logits, T, y, stream=None):
+        _check(lib().mlxs_moe_forward(self._h, layer, x, logits, T, y, stream))
+
+    def forward_host(self, layer, x_host, logits_host, T, y_host, stream=None):
+        _check(lib().mlxs_moe_forward_host(self._h, layer, x_host, logits_host, T, y_host, stream))
+
+    def exl3_gemv(self, layer, expert, proj, xh, rows, z, stream=None):
+        _check(lib().mlxs_moe_exl3_gemv(self._h, layer, expert, proj, xh, rows, z, stream))
+
+    def profile_enable(self, on=True):
+        _check(lib().mlxs_moe_profile_enable(self._h, int(on)))
+
+    def profile_read(self):
+        p = Profile()
+        _check(lib().mlxs_moe_profile_read(self._h, C.byref(p)))
+        return {STAGES[i]: (p.ms[i], p.launches[i]) for i in range(8)}
+
+    def stats(self):
+        s = Stats()
+        _check(lib().mlxs_moe_stats_get(self._h, C.byref(s)))
+        return s

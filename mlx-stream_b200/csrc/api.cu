@@ -1,0 +1,485 @@
+// The C ABI (include/mlxs_moe.h): handle, resident bank, workspaces, and the per-call kernel sequence.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/mlxs_moe.h"
+#include "common.cuh"
+#include "kernels.h"
+
+using namespace mlxs;
+
+static thread_local std::string g_err;
+
+static int fail(int rc, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_err = buf;
+    return rc;
+}
+#define CU(call)                                                                                          \
+    do {                                                                                                  \
+        cudaError_t e__ = (call);                                                                         \
+        if (e__ != cudaSuccess) return fail(MLXS_E_CUDA, "%s: %s", #call, cudaGetErrorString(e__));     \
+    } while (0)
+
+struct LayerBank {
+    uint32_t* gu_code = nullptr;
+    uint32_t* d_code = nullptr;
+    __half* scales = nullptr;
+    uint8_t* loaded_dev = nullptr;  // [E] 1 = resident on this rank
+    std::vector<uint8_t> loaded;
+    float* bias = nullptr;          // [E] or null
+    __nv_bfloat16 *sh_w1 = nullptr, *sh_w3 = nullptr, *sh_w2 = nullptr;
+};
+
+struct mlxs_moe {
+    mlxs_moe_config cfg{};
+    int sm_count = 0;
+    uint32_t e_local = 0, e_first = 0;
+    uint64_t logical_bytes = 0, record_stride = 0;
+    std::vector<LayerBank> layers;
+    std::vector<void*> allocs;
+    uint64_t resident = 0;
+    // workspaces
+    int32_t* ids_ws = nullptr;
+    float* w_ws = nullptr;
+    DispatchTables tabs{};
+    uint32_t* xa_gu = nullptr;
+    uint32_t* xa_d = nullptr;
+    float* ro = nullptr;
+    __nv_bfloat16* sh_h = nullptr;
+    float* sh_out = nullptr;
+    uint32_t* status = nullptr;
+    uint8_t* staging = nullptr;
+    void *x_io = nullptr, *y_io = nullptr;
+    float* logits_io = nullptr;
+    mlxs_moe_stats stats{};
+    // per-stage timing (off by default)
+    bool prof_on = false;
+    struct Span { int stage; cudaEvent_t a, b; };
+    std::vector<Span> spans;
+    std::vector<cudaEvent_t> ev_pool;
+    mlxs_moe_profile prof{};
+    cudaEvent_t ev_get() {
+        if (!ev_pool.empty()) { cudaEvent_t e = ev_pool.back(); ev_pool.pop_back(); return e; }
+        cudaEvent_t e = nullptr;
+        cudaEventCreate(&e);
+        return e;
+    }
+
+    template <class T>
+    int alloc(T** p, size_t n_bytes) {
+        void* q = nullptr;
+        cudaError_t e = cudaMalloc(&q, n_bytes ? n_bytes : 16);
+        if (e != cudaSuccess) return fail(MLXS_E_CUDA, "cudaMalloc(%zu): %s", n_bytes, cudaGetErrorString(e));
+        allocs.push_back(q);
+        resident += n_bytes;
+        *p = static_cast<T*>(q);
+        return 0;
+    }
+};
+
+extern "C" int32_t mlxs_moe_abi(void) { return MLXS_MOE_ABI; }
+extern "C" const char* mlxs_moe_last_error(void) { return g_err.c_str(); }
+
+static uint64_t exl3_logical(uint64_t H, uint64_t I) { return 3 * ((H / 16) * (I / 16) * 96) + 6 * H + 6 * I; }
+static uint64_t mxfp4_logical(uint64_t H, uint64_t I) { return 3 * (H * I / 2 + H * I / 32); }
+static uint64_t nvfp4_logical(uint64_t H, uint64_t I) { return 3 * (H * I / 2 + H * I / 16 + 4); }
+
+extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
+    if (!c || !out) return fail(MLXS_E_ARG, "create: null argument");
+    *out = nullptr;
+    if (c->struct_size != sizeof(mlxs_moe_config))
+        return fail(MLXS_E_CONFIG, "create: struct_size %u, this library has %zu", c->struct_size, sizeof(mlxs_moe_config));
+    // refusals by name, once, at construction (src/exl3/quant.zig:202-212; src/sdk_ext/quant.zig:94-111)
+    if (c->hidden == 0 || c->hidden % 128) return fail(MLXS_E_CONFIG, "create: hidden %u is not a multiple of 128", c->hidden);
+    if (c->inter == 0 || c->inter % 128) return fail(MLXS_E_CONFIG, "create: inter %u is not a multiple of 128", c->inter);
+    if (c->n_experts == 0 || c->n_experts > 1024) return fail(MLXS_E_CONFIG, "create: n_experts %u outside 1..1024", c->n_experts);
+    if (c->top_k == 0 || c->top_k > 64 || c->top_k > c->n_experts)
+        return fail(MLXS_E_CONFIG, "create: top_k %u outside 1..min(64, n_experts)", c->top_k);
+    if (c->n_layers == 0) return fail(MLXS_E_CONFIG, "create: n_layers is 0");
+    if (c->bank_kind > MLXS_BANK_NVFP4) return fail(MLXS_E_CONFIG, "create: bank_kind %u unknown", c->bank_kind);
+    if (c->act > MLXS_ACT_SWIGLU_CLAMPED) return fail(MLXS_E_CONFIG, "create: act %u unknown (ActivationUnsupported)", c->act);
+    if (c->act == MLXS_ACT_SWIGLU_CLAMPED && !(c->act_limit > 0.f))
+        return fail(MLXS_E_CONFIG, "create: act_limit must be > 0 for the clamped SwiGLU");
+    if (c->scoring > MLXS_SCORE_SOFTMAX) return fail(MLXS_E_CONFIG, "create: scoring %u unknown", c->scoring);
+    if (c->combine > MLXS_COMBINE_CHAIN) return fail(MLXS_E_CONFIG, "create: combine %u unknown", c->combine);
+    if (c->max_tokens == 0 || c->max_tokens > 65536) return fail(MLXS_E_CONFIG, "create: max_tokens %u outside 1..65536", c->max_tokens);
+    if (c->ep_world == 0 || c->ep_rank >= c->ep_world || c->n_experts % c->ep_world)
+        return fail(MLXS_E_CONFIG, "create: ep_world %u / ep_rank %u do not shard %u experts", c->ep_world, c->ep_rank, c->n_experts);
+    if (c->bank_kind == MLXS_BANK_EXL3_K3_MUL1 && c->combine != MLXS_COMBINE_F32)
+        return fail(MLXS_E_CONFIG, "create: the EXL3 bank's routed rows are f32; combine must be MLXS_COMBINE_F32");
+    int ndev = 0;
+    cudaError_t ce = cudaGetDeviceCount(&ndev);
+    if (ce != cudaSuccess || ndev == 0)
+        return fail(MLXS_E_CUDA, "create: no CUDA device (%s); this library has no CPU path", cudaGetErrorString(ce));
+    if (c->device < 0 || c->device >= ndev) return fail(MLXS_E_ARG, "create: device %d of %d", c->device, ndev);
+    CU(cudaSetDevice(c->device));
+    cudaDeviceProp prop;
+    CU(cudaGetDeviceProperties(&prop, c->device));
+    if (prop.major != 10) return fail(MLXS_E_CUDA, "create: device is sm_%d%d; the kernels are built for sm_100a only", prop.major, prop.minor);
+
+    mlxs_moe* h = new (std::nothrow) mlxs_moe();
+    if (!h) return fail(MLXS_E_ARG, "create: out of host memory");
+    h->cfg = *c;
+    h->sm_count = prop.multiProcessorCount;
+    h->e_local = c->n_experts / c->ep_world;
+    h->e_first = c->ep_rank * h->e_local;
+    const uint64_t H = c->hidden, I = c->inter;
+    h->logical_bytes = c->bank_kind == MLXS_BANK_EXL3_K3_MUL1 ? exl3_logical(H, I)
+                       : c->bank_kind == MLXS_BANK_MXFP4      ? mxfp4_logical(H, I)
+                                                              : nvfp4_logical(H, I);
+    h->record_stride = (h->logical_bytes + 4095) / 4096 * 4096;
+    h->layers.resize(c->n_layers);
+    int rc = 0;
+    auto bail = [&](int r) { mlxs_moe_destroy(h); return r; };
+    const Exl3Dims d{c->hidden, c->inter};
+    for (auto& L : h->layers) {
+        L.loaded.assign(c->n_experts, 0);
+        if ((rc = h->alloc(&L.loaded_dev, c->n_experts))) return bail(rc);
+        cudaMemset(L.loaded_dev, 0, c->n_experts);
+        if (c->bank_kind == MLXS_BANK_EXL3_K3_MUL1) {
+            if ((rc = h->alloc(&L.gu_code, (size_t)h->e_local * 2 * exl3_code_words(d) * 4))) return bail(rc);
+            if ((rc = h->alloc(&L.d_code, (size_t)h->e_local * exl3_code_words(d) * 4))) return bail(rc);
+            if ((rc = h->alloc(&L.scales, (size_t)h->e_local * exl3_scales_per_expert(d) * 2))) return bail(rc);
+        }
+    }
+    const size_t T = c->max_tokens, A = T * c->top_k;
+    const uint32_t max_chunks = (uint32_t)(A / CHUNK_ROWS + (A < c->n_experts ? A : c->n_experts) + 1);
+    h->tabs.max_chunks = max_chunks;
+    if ((rc = h->alloc(&h->ids_ws, A * 4)) || (rc = h->alloc(&h->w_ws, A * 4)) || (rc = h->alloc(&h->tabs.header, 64)) ||
+        (rc = h->alloc(&h->tabs.offsets, (c->n_experts + 1) * 4)) || (rc = h->alloc(&h->tabs.order, A * 4)) ||
+        (rc = h->alloc(&h->tabs.chunk_expert, max_chunks * 4)) || (rc = h->alloc(&h->tabs.chunk_row0, max_chunks * 4)) ||
+        (rc = h->alloc(&h->tabs.chunk_rows, max_chunks * 4)) || (rc = h->alloc(&h->tabs.group_chunk0, max_chunks * 4)) ||
+        (rc = h->alloc(&h->tabs.group_mc, max_chunks * 4)) || (rc = h->alloc(&h->status, 16)) ||
+        (rc = h->alloc(&h->staging, h->record_stride)) || (rc = h->alloc(&h->x_io, T * H * 2)) ||
+        (rc = h->alloc(&h->y_io, T * H * 2)) || (rc = h->alloc(&h->logits_io, T * c->n_experts * 4)))
+        return bail(rc);
+    cudaMemset(h->status, 0, 16);
+    cudaMemset(h->tabs.header, 0, 64);
+    if (c->bank_kind == MLXS_BANK_EXL3_K3_MUL1) {
+        const size_t kmax = (H > I ? H : I) / 16;
+        if ((rc = h->alloc(&h->xa_gu, (size_t)max_chunks * 2 * kmax * 512)) ||
+            (rc = h->alloc(&h->xa_d, (size_t)max_chunks * kmax * 512)) || (rc = h->alloc(&h->ro, A * (H > I ? H : I) * 4)))
+            return bail(rc);
+    }
+    if (c->shared_expert) {
+        if ((rc = h->alloc(&h->sh_h, T * I * 2)) || (rc = h->alloc(&h->sh_out, T * H * 4))) return bail(rc);
+    }
+    if (cudaDeviceSynchronize() != cudaSuccess) return bail(fail(MLXS_E_CUDA, "create: device synchronize failed"));
+    *out = h;
+    return MLXS_OK;
+}
+
+extern "C" void mlxs_moe_destroy(mlxs_moe* h) {
+    if (!h) return;
+    cudaSetDevice(h->cfg.device);
+    cudaDeviceSynchronize();
+    for (void* p : h->allocs) cudaFree(p);
+    for (auto& s : h->spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
+    for (auto e : h->ev_pool) cudaEventDestroy(e);
+    delete h;
+}
+
+extern "C" int mlxs_moe_record_bytes(const mlxs_moe* h, uint64_t* logical_bytes, uint64_t* record_stride) {
+    if (!h) return fail(MLXS_E_ARG, "record_bytes: null handle");
+    if (logical_bytes) *logical_bytes = h->logical_bytes;
+    if (record_stride) *record_stride = h->record_stride;
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_load_expert(mlxs_moe* h, uint32_t layer, uint32_t expert, const void* record, uint64_t nbytes,
+                                    int on_device) {
+    if (!h || !record) return fail(MLXS_E_ARG, "load_expert: null argument");
+    if (layer >= h->cfg.n_layers) return fail(MLXS_E_ARG, "load_expert: layer %u of %u", layer, h->cfg.n_layers);
+    if (expert >= h->cfg.n_experts) return fail(MLXS_E_ARG, "load_expert: expert %u of %u", expert, h->cfg.n_experts);
+    if (nbytes < h->logical_bytes)
+        return fail(MLXS_E_BANK, "load_expert: record has %llu bytes, the bank kind's record is %llu (RecordGeometry)",
+                    (unsigned long long)nbytes, (unsigned long long)h->logical_bytes);
+    if (expert < h->e_first || expert >= h->e_first + h->e_local) return MLXS_OK;  // another rank's shard
+    CU(cudaSetDevice(h->cfg.device));
+    LayerBank& L = h->layers[layer];
+    const uint32_t le = expert - h->e_first;
+    const uint8_t* src = static_cast<const uint8_t*>(record);
+    if (!on_device) {
+        CU(cudaMemcpyAsync(h->staging, record, h->logical_bytes, cudaMemcpyHostToDevice, 0));
+        src = h->staging;
+    }
+    if (h->cfg.bank_kind == MLXS_BANK_EXL3_K3_MUL1) {
+        const Exl3Dims d{h->cfg.hidden, h->cfg.inter};
+        CU(launch_exl3_repack(src, d, L.gu_code + (size_t)le * 2 * exl3_code_words(d),
+                              L.d_code + (size_t)le * exl3_code_words(d), L.scales + (size_t)le * exl3_scales_per_expert(d), 0));
+    } else {
+        return fail(MLXS_E_CONFIG, "load_expert: bank kind %u has no resident layout yet", h->cfg.bank_kind);
+    }
+    const uint8_t one = 1;
+    CU(cudaMemcpyAsync(L.loaded_dev + expert, &one, 1, cudaMemcpyHostToDevice, 0));
+    CU(cudaStreamSynchronize(0));
+    L.loaded[expert] = 1;
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_load_bank(mlxs_moe* h, const char* dir) {
+    if (!h || !dir) return fail(MLXS_E_ARG, "load_bank: null argument");
+    return fail(MLXS_E_MANIFEST, "load_bank: manifest reader not built in this version");
+}
+
+extern "C" int mlxs_moe_set_router_bias(mlxs_moe* h, uint32_t layer, const float* bias_host) {
+    if (!h) return fail(MLXS_E_ARG, "set_router_bias: null handle");
+    if (layer >= h->cfg.n_layers) return fail(MLXS_E_ARG, "set_router_bias: layer %u of %u", layer, h->cfg.n_layers);
+    CU(cudaSetDevice(h->cfg.device));
+    LayerBank& L = h->layers[layer];
+    if (!bias_host) { L.bias = nullptr; return MLXS_OK; }
+    if (!L.bias) { int rc = h->alloc(&L.bias, h->cfg.n_experts * 4); if (rc) return rc; }
+    CU(cudaMemcpy(L.bias, bias_host, h->cfg.n_experts * 4, cudaMemcpyHostToDevice));
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_set_shared(mlxs_moe* h, uint32_t layer, const void* w1, const void* w3, const void* w2, int on_device) {
+    if (!h || !w1 || !w3 || !w2) return fail(MLXS_E_ARG, "set_shared: null argument");
+    if (layer >= h->cfg.n_layers) return fail(MLXS_E_ARG, "set_shared: layer %u of %u", layer, h->cfg.n_layers);
+    if (!h->cfg.shared_expert) return fail(MLXS_E_CONFIG, "set_shared: the handle was created without a shared expert");
+    CU(cudaSetDevice(h->cfg.device));
+    LayerBank& L = h->layers[layer];
+    const size_t n = (size_t)h->cfg.hidden * h->cfg.inter * 2;
+    int rc;
+    if (!L.sh_w1 && ((rc = h->alloc(&L.sh_w1, n)) || (rc = h->alloc(&L.sh_w3, n)) || (rc = h->alloc(&L.sh_w2, n)))) return rc;
+    const cudaMemcpyKind k = on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
+    CU(cudaMemcpy(L.sh_w1, w1, n, k));
+    CU(cudaMemcpy(L.sh_w3, w3, n, k));
+    CU(cudaMemcpy(L.sh_w2, w2, n, k));
+    return MLXS_OK;
+}
+
+// brackets one stage's launches with events when profiling is on
+struct StageTimer {
+    mlxs_moe* h; cudaStream_t st; cudaEvent_t a = nullptr, b = nullptr; int stage;
+    StageTimer(mlxs_moe* h_, int stage_, cudaStream_t st_) : h(h_), st(st_), stage(stage_) {
+        if (h->prof_on) { a = h->ev_get(); b = h->ev_get(); cudaEventRecord(a, st); }
+    }
+    ~StageTimer() {
+        if (a) { cudaEventRecord(b, st); h->spans.push_back({stage, a, b}); }
+    }
+};
+
+static int check_call(mlxs_moe* h, uint32_t layer, uint32_t T, const char* who) {
+    if (!h) return fail(MLXS_E_ARG, "%s: null handle", who);
+    if (layer >= h->cfg.n_layers) return fail(MLXS_E_ARG, "%s: layer %u of %u", who, layer, h->cfg.n_layers);
+    if (T > h->cfg.max_tokens) return fail(MLXS_E_TOO_MANY_TOKENS, "%s: %u tokens, the handle was created for %u", who, T, h->cfg.max_tokens);
+    cudaError_t e = cudaSetDevice(h->cfg.device);
+    if (e != cudaSuccess) return fail(MLXS_E_CUDA, "%s: cudaSetDevice: %s", who, cudaGetErrorString(e));
+    return 0;
+}
+
+extern "C" int mlxs_moe_route(mlxs_moe* h, uint32_t layer, const float* logits_dev, uint32_t T, int32_t* ids_dev,
+                              float* weights_dev, void* stream) {
+    int rc = check_call(h, layer, T, "route");
+    if (rc) return rc;
+    if (T && (!logits_dev || !ids_dev || !weights_dev)) return fail(MLXS_E_ARG, "route: null buffer");
+    const mlxs_moe_config& c = h->cfg;
+    StageTimer tm(h, MLXS_STAGE_ROUTER, (cudaStream_t)stream);
+    CU(launch_router(logits_dev, h->layers[layer].bias, (int)T, (int)c.n_experts, (int)c.top_k, (int)c.scoring,
+                     (int)c.norm_topk, c.routed_scale, ids_dev, weights_dev, (cudaStream_t)stream));
+    h->stats.route_calls += 1;
+    return MLXS_OK;
+}
+
+// dispatch + the bank's expert kernels -> ro (unweighted rows in assignment order)
+static int run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, uint32_t T, float* ro,
+                      cudaStream_t st) {
+    const mlxs_moe_config& c = h->cfg;
+    LayerBank& L = h->layers[layer];
+    const uint32_t A = T * c.top_k;
+    if (c.ep_world != 1) return fail(MLXS_E_EP, "experts: expert-parallel exchange is not initialised");
+    {
+        StageTimer tm(h, MLXS_STAGE_DISPATCH, st);
+        CU(launch_dispatch(ids_dev, A, c.n_experts, L.loaded_dev, h->tabs, h->status, st));
+    }
+    if (c.bank_kind == MLXS_BANK_EXL3_K3_MUL1) {
+        const Exl3Dims d{c.hidden, c.inter};
+        Exl3Layer EL{L.gu_code, L.d_code, L.scales};
+        {
+            StageTimer tm(h, MLXS_STAGE_PREP, st);
+            CU(launch_exl3_prep_in(static_cast<const __nv_bfloat16*>(x_dev), c.top_k, EL, d, h->tabs, h->xa_gu, st));
+        }
+        Exl3GemvArgs a{};
+        a.L = EL; a.d = d; a.t = h->tabs; a.xa_gu = h->xa_gu; a.xa_d = h->xa_d; a.ro = ro; a.ro_bf16 = 0;
+        a.limit = c.act == MLXS_ACT_SWIGLU_CLAMPED ? c.act_limit : 0.f;
+        a.status = h->status; a.sm_count = h->sm_count;
+        {
+            StageTimer tm(h, MLXS_STAGE_GATE_UP, st);
+            CU(launch_exl3_gate_up(a, st));
+        }
+        {
+            StageTimer tm(h, MLXS_STAGE_DOWN, st);
+            CU(launch_exl3_down(a, st));
+        }
+    } else {
+        return fail(MLXS_E_CONFIG, "experts: bank kind %u kernels are not built yet", c.bank_kind);
+    }
+    h->stats.expert_calls += 1;
+    h->stats.tokens += T;
+    h->stats.assignments += A;
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, uint32_t T,
+                               float* out_dev, void* stream) {
+    int rc = check_call(h, layer, T, "routed");
+    if (rc) return rc;
+    if (T == 0) return MLXS_OK;
+    if (!x_dev || !ids_dev || !out_dev) return fail(MLXS_E_ARG, "routed: null buffer");
+    return run_routed(h, layer, x_dev, ids_dev, T, out_dev, (cudaStream_t)stream);
+}
+
+extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev,
+                                const float* weights_dev, uint32_t T, void* y_dev, void* stream) {
+    int rc = check_call(h, layer, T, "experts");
+    if (rc) return rc;
+    if (T == 0) return MLXS_OK;
+    if (!x_dev || !ids_dev || !weights_dev || !y_dev) return fail(MLXS_E_ARG, "experts: null buffer");
+    const mlxs_moe_config& c = h->cfg;
+    LayerBank& L = h->layers[layer];
+    cudaStream_t st = (cudaStream_t)stream;
+    if (c.shared_expert && !L.sh_w1) return fail(MLXS_E_NOT_LOADED, "experts: layer %u has no shared expert weights", layer);
+    if ((rc = run_routed(h, layer, x_dev, ids_dev, T, h->ro, st))) return rc;
+    const float* shared = nullptr;
+    if (c.shared_expert) {
+        StageTimer tm(h, MLXS_STAGE_SHARED, st);
+        CU(launch_shared_expert(static_cast<const __nv_bfloat16*>(x_dev), L.sh_w1, L.sh_w3, L.sh_w2, T, c.hidden, c.inter,
+                                c.act == MLXS_ACT_SWIGLU_CLAMPED ? c.act_limit : 0.f, h->sh_h, h->sh_out, st));
+        shared = h->sh_out;
+    }
+    StageTimer tm(h, MLXS_STAGE_COMBINE, st);
+    CU(launch_combine(h->ro, 0, weights_dev, shared, T, c.top_k, c.hidden, c.combine == MLXS_COMBINE_CHAIN,
+                      static_cast<__nv_bfloat16*>(y_dev), st));
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_forward(mlxs_moe* h, uint32_t layer, const void* x_dev, const float* logits_dev, uint32_t T,
+                                void* y_dev, void* stream) {
+    int rc = mlxs_moe_route(h, layer, logits_dev, T, h ? h->ids_ws : nullptr, h ? h->w_ws : nullptr, stream);
+    if (rc) return rc;
+    return mlxs_moe_experts(h, layer, x_dev, h->ids_ws, h->w_ws, T, y_dev, stream);
+}
+
+static int read_status(mlxs_moe* h, cudaStream_t st) {
+    uint32_t s = 0;
+    CU(cudaMemcpyAsync(&s, h->status, 4, cudaMemcpyDeviceToHost, st));
+    CU(cudaStreamSynchronize(st));
+    h->stats.device_status = s;
+    if (s) return fail(MLXS_E_DEVICE_STATUS, "device status %u (%s)", s,
+                       s == ST_BAD_EXPERT_ID ? "expert id out of range" : s == ST_NOT_LOADED ? "a routed expert is not resident"
+                       : s == ST_WORKLIST_OVERFLOW ? "work list overflow" : "a bounded wait ran out");
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_forward_host(mlxs_moe* h, uint32_t layer, const void* x_host, const float* logits_host, uint32_t T,
+                                     void* y_host, void* stream) {
+    int rc = check_call(h, layer, T, "forward_host");
+    if (rc) return rc;
+    if (T == 0) return MLXS_OK;
+    if (!x_host || !logits_host || !y_host) return fail(MLXS_E_ARG, "forward_host: null buffer");
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t xb = (size_t)T * h->cfg.hidden * 2;
+    CU(cudaMemcpyAsync(h->x_io, x_host, xb, cudaMemcpyHostToDevice, st));
+    CU(cudaMemcpyAsync(h->logits_io, logits_host, (size_t)T * h->cfg.n_experts * 4, cudaMemcpyHostToDevice, st));
+    if ((rc = mlxs_moe_forward(h, layer, h->x_io, h->logits_io, T, h->y_io, stream))) return rc;
+    CU(cudaMemcpyAsync(y_host, h->y_io, xb, cudaMemcpyDeviceToHost, st));
+    return read_status(h, st);
+}
+
+extern "C" int mlxs_moe_exl3_gemv(mlxs_moe* h, uint32_t layer, uint32_t expert, uint32_t proj, const float* xh_dev,
+                                  uint32_t rows, float* z_dev, void* stream) {
+    if (!h || !xh_dev || !z_dev) return fail(MLXS_E_ARG, "exl3_gemv: null argument");
+    const mlxs_moe_config& c = h->cfg;
+    if (c.bank_kind != MLXS_BANK_EXL3_K3_MUL1) return fail(MLXS_E_CONFIG, "exl3_gemv: the handle's bank is not EXL3");
+    if (layer >= c.n_layers || expert >= c.n_experts || proj > 2) return fail(MLXS_E_ARG, "exl3_gemv: layer/expert/proj out of range");
+    if (expert < h->e_first || expert >= h->e_first + h->e_local || !h->layers[layer].loaded[expert])
+        return fail(MLXS_E_NOT_LOADED, "exl3_gemv: expert %u of layer %u is not resident on this rank", expert, layer);
+    if (rows == 0) return MLXS_OK;
+    if (rows > c.max_tokens * c.top_k) return fail(MLXS_E_TOO_MANY_TOKENS, "exl3_gemv: %u rows exceed the workspace", rows);
+    CU(cudaSetDevice(c.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    LayerBank& L = h->layers[layer];
+    const Exl3Dims d{c.hidden, c.inter};
+    const uint32_t le = expert - h->e_first;
+    // rows all belong to one pseudo expert 0 of a one-expert dispatch
+    CU(cudaMemsetAsync(h->ids_ws, 0, (size_t)rows * 4, st));
+    CU(launch_dispatch(h->ids_ws, rows, 1, nullptr, h->tabs, h->status, st));
+    const uint32_t in_dim = proj == 2 ? c.inter : c.hidden, out_dim = proj == 2 ? c.hidden : c.inter;
+    CU(launch_exl3_prep_raw(xh_dev, in_dim, h->tabs, h->xa_gu, st));
+    const uint32_t* code = proj == 2 ? L.d_code + (size_t)le * exl3_code_words(d) : L.gu_code + (size_t)le * 2 * exl3_code_words(d);
+    CU(launch_exl3_raw(code, in_dim, out_dim, proj == 2 ? 192u : 384u, proj == 1 ? 192u : 0u, h->tabs, h->xa_gu, z_dev,
+                       h->status, h->sm_count, st));
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_stats_get(mlxs_moe* h, mlxs_moe_stats* out) {
+    if (!h || !out) return fail(MLXS_E_ARG, "stats: null argument");
+    CU(cudaSetDevice(h->cfg.device));
+    uint32_t hdr[8] = {0}, s = 0;
+    CU(cudaDeviceSynchronize());
+    CU(cudaMemcpy(hdr, h->tabs.header, sizeof hdr, cudaMemcpyDeviceToHost));
+    CU(cudaMemcpy(&s, h->status, 4, cudaMemcpyDeviceToHost));
+    h->stats.device_status = s;
+    h->stats.distinct_experts_last = hdr[HDR_DISTINCT];
+    h->stats.weight_bytes_last = (uint64_t)hdr[HDR_DISTINCT] * h->logical_bytes;
+    h->stats.resident_bytes = h->resident;
+    *out = h->stats;
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_profile_enable(mlxs_moe* h, int on) {
+    if (!h) return fail(MLXS_E_ARG, "profile_enable: null handle");
+    h->prof_on = on != 0;
+    return MLXS_OK;
+}
+extern "C" int mlxs_moe_profile_read(mlxs_moe* h, mlxs_moe_profile* out) {
+    if (!h || !out) return fail(MLXS_E_ARG, "profile_read: null argument");
+    CU(cudaSetDevice(h->cfg.device));
+    for (auto& s : h->spans) {
+        CU(cudaEventSynchronize(s.b));
+        float ms = 0.f;
+        CU(cudaEventElapsedTime(&ms, s.a, s.b));
+        h->prof.ms[s.stage] += ms;
+        h->prof.launches[s.stage] += 1;
+        h->ev_pool.push_back(s.a);
+        h->ev_pool.push_back(s.b);
+    }
+    h->spans.clear();
+    *out = h->prof;
+    h->prof = mlxs_moe_profile{};
+    return MLXS_OK;
+}
+
+// ---- expert parallel ----
+extern "C" int mlxs_moe_ep_plan(const int32_t* ids, uint64_t n, uint32_t n_experts, uint32_t world, uint64_t* send_counts) {
+    if (!ids || !send_counts || world == 0 || n_experts == 0 || n_experts % world) return fail(MLXS_E_ARG, "ep_plan: bad argument");
+    const uint32_t per = n_experts / world;
+    for (uint32_t r = 0; r < world; ++r) send_counts[r] = 0;
+    for (uint64_t i = 0; i < n; ++i) {
+        if (ids[i] < 0 || (uint32_t)ids[i] >= n_experts) return fail(MLXS_E_ARG, "ep_plan: id %d at %llu outside 0..%u", ids[i], (unsigned long long)i, n_experts);
+        send_counts[(uint32_t)ids[i] / per] += 1;
+    }
+    return MLXS_OK;
+}
+extern "C" int mlxs_moe_ep_unique_id(void* id128_out) {
+    (void)id128_out;
+    return fail(MLXS_E_EP, "ep_unique_id: the exchange is not built in this version");
+}
+extern "C" int mlxs_moe_ep_init(mlxs_moe* h, const void* id128) {
+    (void)h; (void)id128;
+    return fail(MLXS_E_EP, "ep_init: the exchange is not built in this version");
+}

@@ -1,0 +1,428 @@
+// EXL3 (K=3, mul1 trellis, 128-wide Hadamard with suh/svh) expert kernels for decode-sized batches.
+//
+// One projection is y = H128( H128(x * suh) . W_hat ) * svh (src/arch/glm5_next/exl3_forms_ref.zig:137-152; op order
+// of the decode chain: src/arch/deepseek_v41/experts.zig:449-467).  The weight stream is the bound: a CTA owns one
+// 128-wide output block of one expert for up to 16 of its rows, streams that block's code once through a ring of
+// bulk-copied (TMA 1-D) shared-memory stages, decodes each 16x16 tile in registers straight into mma B fragments
+// (the trellis' tensor-core order makes a lane's 8 code positions exactly its fragment) and multiplies with the rows'
+// rotated activations held as f16 hi + f16 lo halves of the m16 tile, so the f32 precision of the reference's decode
+// chain is kept while the FMAs run on the tensor pipe.  The output-side Hadamard, svh, the clamped SwiGLU and the down
+// projection's input rotation are fused into the gate/up epilogue; H128 . svh into the down epilogue.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace mlxs {
+
+constexpr int KT = 8;             // k-tiles (16 inputs each) per pipeline stage = one 128-block of the input
+constexpr int A_TILE_WORDS = 128;  // one m-tile x k-tile of activations in fragment order: 32 lanes x 4 u32
+constexpr int ZS_STRIDE = 132;    // padded row stride of the epilogue's f32 staging
+
+// ------------------------------------------------------------------------------------------------------------
+// load-time repack: reference record -> kernel layout (bit-preserving: words move, no bit changes)
+// ------------------------------------------------------------------------------------------------------------
+__global__ void exl3_repack_kernel(const uint8_t* __restrict__ rec, uint32_t H, uint32_t I, uint32_t* __restrict__ gu,
+                                   uint32_t* __restrict__ dn, __half* __restrict__ sc) {
+    const size_t code_bytes = (size_t)(H / 16) * (I / 16) * 96;
+    // record offsets (src/expert/bank.zig:116-141): per projection code, rout [out], rin [in]
+    const size_t off_g = 0, off_g_rout = code_bytes, off_g_rin = off_g_rout + 2 * (size_t)I;
+    const size_t off_u = off_g_rin + 2 * (size_t)H, off_u_rout = off_u + code_bytes, off_u_rin = off_u_rout + 2 * (size_t)I;
+    const size_t off_d = off_u_rin + 2 * (size_t)H, off_d_rout = off_d + code_bytes, off_d_rin = off_d_rout + 2 * (size_t)H;
+    const size_t words = code_bytes / 4;
+    const size_t n_gu = 2 * words, n_all = 3 * words, n_sc = (size_t)3 * H + 3 * I;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_all + n_sc; i += stride) {
+        if (i < n_gu) {
+            // destination index -> (nb, kt, p, j, w)
+            size_t r = i;
+            const uint32_t w = r % 24; r /= 24;
+            const uint32_t j = r % 8; r /= 8;
+            const uint32_t p = r % 2; r /= 2;
+            const uint32_t kt = r % (H / 16); r /= (H / 16);
+            const uint32_t nb = (uint32_t)r;
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(rec + (p ? off_u : off_g));
+            gu[i] = src[((size_t)kt * (I / 16) + nb * 8 + j) * 24 + w];
+        } else if (i < n_all) {
+            size_t r = i - n_gu;
+            const uint32_t w = r % 24; r /= 24;
+            const uint32_t j = r % 8; r /= 8;
+            const uint32_t kt = r % (I / 16); r /= (I / 16);
+            const uint32_t nb = (uint32_t)r;
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(rec + off_d);
+            dn[i - n_gu] = src[((size_t)kt * (H / 16) + nb * 8 + j) * 24 + w];
+        } else {
+            const size_t s = i - n_all;
+            const __half* h;
+            if (s < H) h = reinterpret_cast<const __half*>(rec + off_g_rin) + s;                        // suh_g
+            else if (s < 2 * (size_t)H) h = reinterpret_cast<const __half*>(rec + off_u_rin) + (s - H);  // suh_u
+            else if (s < 2 * (size_t)H + I) h = reinterpret_cast<const __half*>(rec + off_g_rout) + (s - 2 * (size_t)H);
+            else if (s < 2 * (size_t)H + 2 * (size_t)I)
+                h = reinterpret_cast<const __half*>(rec + off_u_rout) + (s - 2 * (size_t)H - I);
+            else if (s < 2 * (size_t)H + 3 * (size_t)I)
+                h = reinterpret_cast<const __half*>(rec + off_d_rin) + (s - 2 * (size_t)H - 2 * (size_t)I);  // suh_d
+            else h = reinterpret_cast<const __half*>(rec + off_d_rout) + (s - 2 * (size_t)H - 3 * (size_t)I);  // svh_d
+            sc[s] = *h;
+        }
+    }
+}
+
+cudaError_t launch_exl3_repack(const uint8_t* record_dev, Exl3Dims d, uint32_t* gu_code_e, uint32_t* d_code_e,
+                               __half* scales_e, cudaStream_t st) {
+    exl3_repack_kernel<<<592, 256, 0, st>>>(record_dev, d.H, d.I, gu_code_e, d_code_e, scales_e);
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// activation staging: rows -> mma A-fragment order, f16 hi / lo
+// ------------------------------------------------------------------------------------------------------------
+// One k-tile x m-tile block is 32 lanes x 4 u32: lane (g = row, c) holds a0 = hi(k 2c,2c+1), a1 = lo(same),
+// a2 = hi(k 2c+8,2c+9), a3 = lo(same).  A warp lane that owns elements 4*lane..4*lane+3 of a 128-block writes the
+// k-tile lane/4, k = 4*(lane&3) + q.
+__device__ __forceinline__ void store_frag4(uint32_t* tile_base /* the 128-block's first k-tile */, uint32_t row,
+                                            uint32_t lane, const float (&v)[4]) {
+    const uint32_t cq = lane & 3u;
+    uint32_t* kt = tile_base + (lane >> 2) * A_TILE_WORDS;
+    const uint32_t idx0 = (row * 4u + 2u * (cq & 1u)) * 4u + (cq >> 1) * 2u;
+    __half h0, l0, h1, l1, h2, l2, h3, l3;
+    split_hi_lo(v[0], h0, l0); split_hi_lo(v[1], h1, l1); split_hi_lo(v[2], h2, l2); split_hi_lo(v[3], h3, l3);
+    *reinterpret_cast<uint2*>(kt + idx0) = make_uint2(pack_h2(h0, h1), pack_h2(l0, l1));
+    *reinterpret_cast<uint2*>(kt + idx0 + 4) = make_uint2(pack_h2(h2, h3), pack_h2(l2, l3));
+}
+
+template <bool RAW>
+__global__ void __launch_bounds__(256) exl3_prep_kernel(const void* __restrict__ xin, uint32_t top_k, uint32_t in_dim,
+                                                        const __half* __restrict__ scales, size_t scales_stride,
+                                                        DispatchTables t, uint32_t* __restrict__ xa) {
+    const uint32_t chunk = blockIdx.x;
+    if (chunk >= t.header[HDR_NCHUNKS]) return;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;  // warp = row of the chunk
+    const uint32_t e = t.chunk_expert[chunk], rows = t.chunk_rows[chunk];
+    const bool valid = warp < rows;
+    const uint32_t assign = valid ? t.order[t.chunk_row0[chunk] + warp] : 0u;
+    const uint32_t tok = assign / top_k;
+    const uint32_t nkt = in_dim / 16;
+    constexpr int NP = RAW ? 1 : 2;
+    const float S = __uint_as_float(SCALE_BITS);
+    for (int p = 0; p < NP; ++p) {
+        uint32_t* dst = xa + ((size_t)chunk * NP + p) * nkt * A_TILE_WORDS;
+        for (uint32_t b = 0; b < in_dim / 128; ++b) {
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (valid) {
+                if (RAW) {
+                    const float4 f = *reinterpret_cast<const float4*>(static_cast<const float*>(xin) +
+                                                                      (size_t)tok * in_dim + b * 128 + lane * 4);
+                    v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+                } else {
+                    const uint2 xb = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(xin) +
+                                                                     (size_t)tok * in_dim + b * 128 + lane * 4);
+                    const uint2 sb = *reinterpret_cast<const uint2*>(scales + (size_t)e * scales_stride +
+                                                                     (size_t)p * in_dim + b * 128 + lane * 4);
+                    const float x0 = __uint_as_float(xb.x << 16), x1 = __uint_as_float(xb.x & 0xFFFF0000u);
+                    const float x2 = __uint_as_float(xb.y << 16), x3 = __uint_as_float(xb.y & 0xFFFF0000u);
+                    const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sb.x));
+                    const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sb.y));
+                    v[0] = x0 * s01.x; v[1] = x1 * s01.y; v[2] = x2 * s23.x; v[3] = x3 * s23.y;
+                    hadamard128_warp(v, lane);
+                    v[0] *= S; v[1] *= S; v[2] *= S; v[3] *= S;
+                }
+            }
+            store_frag4(dst + (size_t)b * 8 * A_TILE_WORDS, warp, lane, v);
+        }
+    }
+}
+
+cudaError_t launch_exl3_prep_in(const __nv_bfloat16* x, uint32_t top_k, Exl3Layer L, Exl3Dims d, DispatchTables t,
+                                uint32_t* xa_gu, cudaStream_t st) {
+    exl3_prep_kernel<false><<<t.max_chunks, 256, 0, st>>>(x, top_k, d.H, L.scales, exl3_scales_per_expert(d), t, xa_gu);
+    return cudaGetLastError();
+}
+cudaError_t launch_exl3_prep_raw(const float* xh, uint32_t in_dim, DispatchTables t, uint32_t* xa, cudaStream_t st) {
+    exl3_prep_kernel<true><<<t.max_chunks, 256, 0, st>>>(xh, 1, in_dim, nullptr, 0, t, xa);
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// the streaming GEMV
+// ------------------------------------------------------------------------------------------------------------
+enum { EPI_GATE_UP = 0, EPI_DOWN = 1, EPI_RAW = 2 };
+
+struct GemvParams {
+    const uint32_t* code;        // layer base (or the expert's base when expert_stride_words == 0)
+    size_t expert_stride_words;
+    uint32_t n_blocks;           // out / 128
+    uint32_t nkt;                // in / 16
+    uint32_t kt_stride_words;    // words per k-tile in the block stream (192 per projection present)
+    uint32_t proj_off_words;     // where this kernel's (first) projection sits inside a k-tile
+    const uint32_t* xa;          // [chunk][NPROJ][nkt][128]
+    DispatchTables t;
+    uint32_t counter_idx;
+    const __half* scales;        // layer base
+    size_t scales_stride;
+    uint32_t H, I;
+    uint32_t* xa_d;              // gate/up epilogue output
+    float* out;                  // down: ro [A, H]; raw: z [rows, out_dim]
+    uint32_t out_dim;
+    float limit;
+    uint32_t* status;
+    uint32_t n_stages;
+    uint32_t stage_bytes, w_bytes;
+};
+
+struct StageMeta { int32_t item; uint32_t kt0, chunk0, mc, expert, nb; };
+
+template <int NPROJ, int EPI>
+__global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 2 : 1) exl3_gemv_kernel(const GemvParams P) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    constexpr int NCW = NPROJ * 8;         // consumer warps: projection x 16-column tile of the 128 block
+    constexpr int MAXS = 8;
+    __shared__ __align__(8) uint64_t full_bar[MAXS], empty_bar[MAXS], epi_bar;
+    __shared__ StageMeta meta[MAXS];
+    __shared__ volatile int s_abort;
+    // epilogue staging: [NPROJ][GROUP_CHUNKS][8 rows][ZS_STRIDE]
+    float* zs = reinterpret_cast<float*>(smem_raw);
+    uint8_t* ring = smem_raw + (size_t)NPROJ * GROUP_CHUNKS * 8 * ZS_STRIDE * sizeof(float);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t NS = P.n_stages;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < NS; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], NCW); }
+        mbar_init(&epi_bar, NCW);
+        s_abort = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    const uint32_t n_items = P.t.header[HDR_NGROUPS] * P.n_blocks;
+
+    if (warp == NCW) {
+        // ---------------- producer warp: one lane issues every copy ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            while (ok) {
+                const uint32_t item = atomicAdd(&P.t.header[P.counter_idx], 1u);
+                const bool last = item >= n_items;
+                uint32_t g = 0, nb = 0, chunk0 = 0, mc = 0, expert = 0;
+                if (!last) {
+                    g = item / P.n_blocks; nb = item % P.n_blocks;
+                    chunk0 = P.t.group_chunk0[g]; mc = P.t.group_mc[g]; expert = P.t.chunk_expert[chunk0];
+                }
+                const uint32_t* wsrc = P.code + (size_t)expert * P.expert_stride_words +
+                                       (size_t)nb * P.nkt * P.kt_stride_words;
+                for (uint32_t kt0 = 0; kt0 < (last ? 1u : P.nkt); kt0 += KT, ++it) {
+                    const uint32_t s = it % NS, ph = (it / NS) & 1u;
+                    if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, &s_abort)) {
+                        if (!s_abort) atomicMax(P.status, (uint32_t)ST_WAIT_EMPTY);
+                        s_abort = 1; ok = false; break;
+                    }
+                    meta[s].item = last ? -1 : (int32_t)item;
+                    meta[s].kt0 = kt0; meta[s].chunk0 = chunk0; meta[s].mc = mc; meta[s].expert = expert; meta[s].nb = nb;
+                    if (last) { mbar_arrive(&full_bar[s]); ok = false; break; }
+                    uint8_t* dst = ring + (size_t)s * P.stage_bytes;
+                    mbar_expect_tx(&full_bar[s], P.w_bytes + mc * NPROJ * KT * A_TILE_WORDS * 4);
+                    bulk_g2s(dst, wsrc + (size_t)kt0 * P.kt_stride_words, P.w_bytes, &full_bar[s]);
+                    for (uint32_t m = 0; m < mc; ++m)
+                        for (int p = 0; p < NPROJ; ++p)
+                            bulk_g2s(dst + P.w_bytes + (m * NPROJ + p) * (KT * A_TILE_WORDS * 4),
+                                     P.xa + (((size_t)(chunk0 + m) * NPROJ + p) * P.nkt + kt0) * A_TILE_WORDS,
+                                     KT * A_TILE_WORDS * 4, &full_bar[s]);
+                }
+            }
+            // after a give-up: let copies already issued land before the CTA's shared memory is released
+            if (s_abort) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+        }
+        return;
+    }
+
+    // ---------------- consumer warps ----------------
+    const uint32_t p = warp >> 3, j = warp & 7u;  // projection, 16-column tile
+    uint32_t wi, wj, lp;
+    exl3_lane_plan(lane, wi, wj, lp);
+    float acc[GROUP_CHUNKS][2][4];
+    const float S = __uint_as_float(SCALE_BITS);
+    uint32_t epi_ph = 0;
+    // every wait in this kernel is a bounded mbarrier wait: the epilogue's two rendezvous of the consumer warps too
+    auto epi_sync = [&]() -> bool {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&epi_bar);
+        const bool ok = mbar_wait_bounded(&epi_bar, epi_ph, &s_abort);
+        epi_ph ^= 1u;
+        if (!ok) { if (!s_abort) atomicMax(P.status, (uint32_t)ST_WAIT_FULL); s_abort = 1; }
+        return ok;
+    };
+    for (uint32_t it = 0;; ++it) {
+        const uint32_t s = it % NS, ph = (it / NS) & 1u;
+        if (!mbar_wait_bounded(&full_bar[s], ph, &s_abort)) {
+            if (!s_abort) atomicMax(P.status, (uint32_t)ST_WAIT_FULL);
+            s_abort = 1;
+            break;
+        }
+        const StageMeta m = meta[s];
+        if (m.item < 0) break;
+        if (m.kt0 == 0) {
+#pragma unroll
+            for (int a = 0; a < GROUP_CHUNKS; ++a)
+#pragma unroll
+                for (int b = 0; b < 2; ++b)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.f;
+        }
+        const uint8_t* st = ring + (size_t)s * P.stage_bytes;
+        const uint32_t* wt = reinterpret_cast<const uint32_t*>(st) + P.proj_off_words + p * 192u + j * 24u;
+        const uint4* at = reinterpret_cast<const uint4*>(st + P.w_bytes) + lane;
+#pragma unroll 4
+        for (int kt = 0; kt < KT; ++kt) {
+            const uint32_t lo = wt[kt * P.kt_stride_words + wi], hi = wt[kt * P.kt_stride_words + wj];
+            uint32_t b[4];
+            exl3_decode_lane(lo, hi, lp, b);
+#pragma unroll
+            for (int mt = 0; mt < GROUP_CHUNKS; ++mt) {
+                if (mt < (int)m.mc) {
+                    const uint4 av = at[((mt * NPROJ + p) * KT + kt) * 32];
+                    const uint32_t a[4] = {av.x, av.y, av.z, av.w};
+                    mma_f16(acc[mt][0], a, b[0], b[1]);
+                    mma_f16(acc[mt][1], a, b[2], b[3]);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[s]);
+        if (m.kt0 + KT < P.nkt) continue;
+
+        // ---------------- epilogue of the item ----------------
+        // z[row] = hi-part rows + lo-part rows of the m16 tile
+        const uint32_t g = lane >> 2, c = lane & 3u;
+#pragma unroll
+        for (int mt = 0; mt < GROUP_CHUNKS; ++mt) {
+            if (mt < (int)m.mc) {
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    float2 v = make_float2(acc[mt][nt][0] + acc[mt][nt][2], acc[mt][nt][1] + acc[mt][nt][3]);
+                    *reinterpret_cast<float2*>(zs + ((p * GROUP_CHUNKS + mt) * 8 + g) * ZS_STRIDE + j * 16 + nt * 8 + 2 * c) = v;
+                }
+            }
+        }
+        if (!epi_sync()) break;
+        for (uint32_t combo = warp; combo < (uint32_t)GROUP_CHUNKS * 8; combo += NCW) {
+            const uint32_t mt = combo >> 3, row = combo & 7u;
+            if (mt >= m.mc) continue;
+            const uint32_t chunk = m.chunk0 + mt;
+            const bool valid = row < P.t.chunk_rows[chunk];
+            const uint32_t col = m.nb * 128 + lane * 4;
+            if (EPI == EPI_GATE_UP) {
+                float v[4] = {0.f, 0.f, 0.f, 0.f};
+                if (valid) {
+                    const float4 zg = *reinterpret_cast<const float4*>(zs + ((0 * GROUP_CHUNKS + mt) * 8 + row) * ZS_STRIDE + lane * 4);
+                    const float4 zu = *reinterpret_cast<const float4*>(zs + ((1 * GROUP_CHUNKS + mt) * 8 + row) * ZS_STRIDE + lane * 4);
+                    float gq[4] = {zg.x, zg.y, zg.z, zg.w}, uq[4] = {zu.x, zu.y, zu.z, zu.w};
+                    hadamard128_warp(gq, lane);
+                    hadamard128_warp(uq, lane);
+                    const __half* sc = P.scales + (size_t)m.expert * P.scales_stride;
+                    const uint2 sg = *reinterpret_cast<const uint2*>(sc + 2 * (size_t)P.H + col);               // svh_g
+                    const uint2 su = *reinterpret_cast<const uint2*>(sc + 2 * (size_t)P.H + P.I + col);         // svh_u
+                    const uint2 sd = *reinterpret_cast<const uint2*>(sc + 2 * (size_t)P.H + 2 * (size_t)P.I + col);  // suh_d
+                    const float2 sg01 = __half22float2(*reinterpret_cast<const __half2*>(&sg.x));
+                    const float2 sg23 = __half22float2(*reinterpret_cast<const __half2*>(&sg.y));
+                    const float2 su01 = __half22float2(*reinterpret_cast<const __half2*>(&su.x));
+                    const float2 su23 = __half22float2(*reinterpret_cast<const __half2*>(&su.y));
+                    const float2 sd01 = __half22float2(*reinterpret_cast<const __half2*>(&sd.x));
+                    const float2 sd23 = __half22float2(*reinterpret_cast<const __half2*>(&sd.y));
+                    const float svg[4] = {sg01.x, sg01.y, sg23.x, sg23.y}, svu[4] = {su01.x, su01.y, su23.x, su23.y};
+                    const float shd[4] = {sd01.x, sd01.y, sd23.x, sd23.y};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        // src/kernels/exl3/q3_exl3_prep_gu_epi.metal:42-74
+                        const float gm = (gq[q] * S) * svg[q], um = (uq[q] * S) * svu[q];
+                        float gate = gm, up = um;
+                        if (P.limit > 0.f) {
+                            gate = (gm != gm) ? gm : (gm < P.limit ? gm : P.limit);
+                            const float u0 = (um != um) ? um : (um > -P.limit ? um : -P.limit);
+                            up = (u0 != u0) ? u0 : (u0 < P.limit ? u0 : P.limit);
+                        }
+                        const float yv = 1.0f / (1.0f + expf(fabsf(gate)));
+                        const float sgm = gate < 0.f ? yv : 1.0f - yv;
+                        v[q] = ((gate * sgm) * up) * shd[q];
+                    }
+                    hadamard128_warp(v, lane);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) v[q] *= S;
+                }
+                store_frag4(P.xa_d + ((size_t)chunk * (P.I / 16) + m.nb * 8) * A_TILE_WORDS, row, lane, v);
+            } else if (valid) {
+                const float4 z4 = *reinterpret_cast<const float4*>(zs + ((size_t)mt * 8 + row) * ZS_STRIDE + lane * 4);
+                float v[4] = {z4.x, z4.y, z4.z, z4.w};
+                const uint32_t assign = P.t.order[P.t.chunk_row0[chunk] + row];
+                if (EPI == EPI_DOWN) {
+                    hadamard128_warp(v, lane);
+                    const __half* sc = P.scales + (size_t)m.expert * P.scales_stride + 2 * (size_t)P.H + 3 * (size_t)P.I;  // svh_d
+                    const uint2 so = *reinterpret_cast<const uint2*>(sc + col);
+                    const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&so.x));
+                    const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&so.y));
+                    v[0] = (v[0] * S) * s01.x; v[1] = (v[1] * S) * s01.y; v[2] = (v[2] * S) * s23.x; v[3] = (v[3] * S) * s23.y;
+                }
+                *reinterpret_cast<float4*>(P.out + (size_t)assign * P.out_dim + col) = make_float4(v[0], v[1], v[2], v[3]);
+            }
+        }
+        if (!epi_sync()) break;
+    }
+}
+
+static cudaError_t launch_gemv(int nproj, int epi, GemvParams& P, int sm_count, cudaStream_t st) {
+    const uint32_t zs_bytes = (uint32_t)(nproj * GROUP_CHUNKS * 8 * ZS_STRIDE * sizeof(float));
+    P.w_bytes = KT * P.kt_stride_words * 4;
+    P.stage_bytes = P.w_bytes + GROUP_CHUNKS * nproj * KT * A_TILE_WORDS * 4;
+    const uint32_t budget = (nproj == 2 ? 200u : 100u) * 1024u;
+    uint32_t ns = (budget - zs_bytes) / P.stage_bytes;
+    if (ns > 8) ns = 8;
+    if (ns < 2) return cudaErrorInvalidValue;
+    P.n_stages = ns;
+    const size_t smem = zs_bytes + (size_t)ns * P.stage_bytes;
+    cudaError_t e;
+    const int ctas = nproj == 2 ? sm_count : 2 * sm_count;
+    if (nproj == 2) {
+        e = cudaFuncSetAttribute(exl3_gemv_kernel<2, EPI_GATE_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        exl3_gemv_kernel<2, EPI_GATE_UP><<<ctas, 2 * 256 + 32, smem, st>>>(P);
+    } else if (epi == EPI_DOWN) {
+        e = cudaFuncSetAttribute(exl3_gemv_kernel<1, EPI_DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        exl3_gemv_kernel<1, EPI_DOWN><<<ctas, 256 + 32, smem, st>>>(P);
+    } else {
+        e = cudaFuncSetAttribute(exl3_gemv_kernel<1, EPI_RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        exl3_gemv_kernel<1, EPI_RAW><<<ctas, 256 + 32, smem, st>>>(P);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_exl3_gate_up(const Exl3GemvArgs& a, cudaStream_t st) {
+    GemvParams P{};
+    P.code = a.L.gu_code;
+    P.expert_stride_words = 2 * exl3_code_words(a.d);
+    P.n_blocks = a.d.I / 128; P.nkt = a.d.H / 16; P.kt_stride_words = 384; P.proj_off_words = 0;
+    P.xa = a.xa_gu; P.t = a.t; P.counter_idx = HDR_CTR_GU;
+    P.scales = a.L.scales; P.scales_stride = exl3_scales_per_expert(a.d);
+    P.H = a.d.H; P.I = a.d.I; P.xa_d = a.xa_d; P.out = nullptr; P.out_dim = a.d.I; P.limit = a.limit; P.status = a.status;
+    return launch_gemv(2, EPI_GATE_UP, P, a.sm_count, st);
+}
+cudaError_t launch_exl3_down(const Exl3GemvArgs& a, cudaStream_t st) {
+    GemvParams P{};
+    P.code = a.L.d_code;
+    P.expert_stride_words = exl3_code_words(a.d);
+    P.n_blocks = a.d.H / 128; P.nkt = a.d.I / 16; P.kt_stride_words = 192; P.proj_off_words = 0;
+    P.xa = a.xa_d; P.t = a.t; P.counter_idx = HDR_CTR_DOWN;
+    P.scales = a.L.scales; P.scales_stride = exl3_scales_per_expert(a.d);
+    P.H = a.d.H; P.I = a.d.I; P.xa_d = nullptr; P.out = a.ro; P.out_dim = a.d.H; P.limit = a.limit; P.status = a.status;
+    return launch_gemv(1, EPI_DOWN, P, a.sm_count, st);
+}
+cudaError_t launch_exl3_raw(const uint32_t* code_e, uint32_t in_dim, uint32_t out_dim, uint32_t ktile_stride_words,
+                            uint32_t proj_off_words, DispatchTables t, const uint32_t* xa, float* z, uint32_t* status,
+                            int sm_count, cudaStream_t st) {
+    GemvParams P{};
+    P.code = code_e; P.expert_stride_words = 0;
+    P.n_blocks = out_dim / 128; P.nkt = in_dim / 16; P.kt_stride_words = ktile_stride_words; P.proj_off_words = proj_off_words;
+    P.xa = xa; P.t = t; P.counter_idx = HDR_CTR_AUX;
+    P.scales = nullptr; P.scales_stride = 0; P.H = 0; P.I = 0; P.xa_d = nullptr; P.out = z; P.out_dim = out_dim;
+    P.limit = 0.f; P.status = status;
+    return launch_gemv(1, EPI_RAW, P, sm_count, st);
+}
+
+}  // namespace mlxs

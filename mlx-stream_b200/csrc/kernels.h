@@ -1,0 +1,85 @@
+// Host-visible launchers of the routed-MoE kernels (internal to the library; the public surface is include/mlxs_moe.h).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mlxs {
+
+// Rows of one expert are processed in chunks of 8 (one mma m-tile: 8 rows as f16 hi + 8 rows as f16 lo) and a work
+// item carries up to GROUP_CHUNKS chunks of one expert.
+constexpr int CHUNK_ROWS = 8;
+constexpr int GROUP_CHUNKS = 2;
+
+// Device-side dispatch tables (all uint32), rebuilt by every call.
+struct DispatchTables {
+    uint32_t* header;        // [16]: 0 n_chunks, 1 n_groups, 2 counter gate/up, 3 counter down, 4 distinct experts,
+                             //       5 counter aux
+    uint32_t* offsets;       // [E + 1] sorted-row offsets per expert
+    uint32_t* order;         // [A] sorted row -> assignment index (stable)
+    uint32_t* chunk_expert;  // [max_chunks]
+    uint32_t* chunk_row0;    // [max_chunks] first sorted row
+    uint32_t* chunk_rows;    // [max_chunks] valid rows (1..8)
+    uint32_t* group_chunk0;  // [max_chunks]
+    uint32_t* group_mc;      // [max_chunks]
+    uint32_t max_chunks;
+};
+enum { HDR_NCHUNKS = 0, HDR_NGROUPS = 1, HDR_CTR_GU = 2, HDR_CTR_DOWN = 3, HDR_DISTINCT = 4, HDR_CTR_AUX = 5 };
+
+cudaError_t launch_router(const float* logits, const float* bias, int T, int E, int K, int scoring, int norm,
+                          float scale, int32_t* ids, float* weights, cudaStream_t st);
+
+// ids [A] (A = T*k) -> tables; expert ids outside [0, E) set *status and are treated as expert 0.
+// loaded: optional [E] bytes, 0 = expert not resident -> *status = ST_NOT_LOADED.
+cudaError_t launch_dispatch(const int32_t* ids, uint32_t A, uint32_t E, const uint8_t* loaded, DispatchTables t,
+                            uint32_t* status, cudaStream_t st);
+
+// ---- EXL3 ----
+struct Exl3Layer {            // one layer's resident bank, in the kernels' layout
+    const uint32_t* gu_code;  // [E][I/128][H/16][2][192] u32: per 128-wide output block, per k-tile, gate | up tiles
+    const uint32_t* d_code;   // [E][H/128][I/16][192] u32
+    const __half* scales;     // [E][2H + 2I + I + H]: suh_g, suh_u [H] | svh_g, svh_u [I] | suh_d [I] | svh_d [H]
+};
+struct Exl3Dims { uint32_t H, I; };
+static inline size_t exl3_scales_per_expert(Exl3Dims d) { return (size_t)3 * d.H + 3 * d.I; }
+static inline size_t exl3_code_words(Exl3Dims d) { return (size_t)(d.H / 16) * (d.I / 16) * 24; }
+
+// record (device, reference v2 layout) -> the expert's slices of the three arrays
+cudaError_t launch_exl3_repack(const uint8_t* record_dev, Exl3Dims d, uint32_t* gu_code_e, uint32_t* d_code_e,
+                               __half* scales_e, cudaStream_t st);
+
+// activation staging in mma A-fragment order: [chunk][proj][k-tile][32 lanes][4] u32 (512 B per k-tile)
+// gate/up inputs: xg = H128(x * suh_g) * 128^-0.5 and xu likewise, f16 hi/lo
+cudaError_t launch_exl3_prep_in(const __nv_bfloat16* x, uint32_t top_k, Exl3Layer L, Exl3Dims d, DispatchTables t,
+                                uint32_t* xa_gu, cudaStream_t st);
+// raw rows (no rotation) into the same order, one projection: xh f32 [rows, in]
+cudaError_t launch_exl3_prep_raw(const float* xh, uint32_t in_dim, DispatchTables t, uint32_t* xa, cudaStream_t st);
+
+struct Exl3GemvArgs {
+    Exl3Layer L;
+    Exl3Dims d;
+    DispatchTables t;
+    const uint32_t* xa_gu;  // [chunk][2][H/16][128] u32
+    uint32_t* xa_d;         // [chunk][I/16][128] u32 (written by gate/up, read by down)
+    float* ro;              // [A, H] f32 routed outputs in assignment order (CHAIN combine: bf16 [A, H])
+    int ro_bf16;
+    float limit;            // > 0: clamped SwiGLU
+    uint32_t* status;
+    int sm_count;
+};
+cudaError_t launch_exl3_gate_up(const Exl3GemvArgs& a, cudaStream_t st);
+cudaError_t launch_exl3_down(const Exl3GemvArgs& a, cudaStream_t st);
+// raw projection: z [rows, out] = xa . W_hat(code); `code` in the single-projection block layout with a k-tile
+// stride of `ktile_stride_words` and the projection at `proj_off_words` (192/0 for down, 384/{0,192} for gate/up)
+cudaError_t launch_exl3_raw(const uint32_t* code_e, uint32_t in_dim, uint32_t out_dim, uint32_t ktile_stride_words,
+                            uint32_t proj_off_words, DispatchTables t, const uint32_t* xa, float* z, uint32_t* status,
+                            int sm_count, cudaStream_t st);
+
+// ---- shared expert (bf16 dense) + combine ----
+cudaError_t launch_shared_expert(const __nv_bfloat16* x, const __nv_bfloat16* w1, const __nv_bfloat16* w3,
+                                 const __nv_bfloat16* w2, uint32_t T, uint32_t H, uint32_t I, float limit,
+                                 __nv_bfloat16* h_ws, float* out, cudaStream_t st);
+// y[t] = sum_k ro[t,k] w[t,k] (+ shared[t]) -> bf16
+cudaError_t launch_combine(const void* ro, int ro_bf16, const float* weights, const float* shared, uint32_t T,
+                           uint32_t K, uint32_t H, int chain, __nv_bfloat16* y, cudaStream_t st);
+
+}  // namespace mlxs

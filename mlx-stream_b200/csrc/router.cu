@@ -1,0 +1,113 @@
+// Router tail: fp32 logits -> top-k expert ids (rank order) + normalised weights.
+// One CTA per token row, one thread per expert (n_experts <= 1024), top_k <= 64.
+// Semantics: src/kernels/exl3/q3rc_router_tail.metal:12-40 (sqrt(softplus)), src/arch/mimo_v2/kernels/mimo_glue_top8.metal
+// and src/arch/glm5_next/kernels/glm5n_glue_top8.metal (sigmoid): key = score + bias, rank = number of experts that
+// precede (key descending, ties to the lower index, NaN last), ids[rank] = expert, weights from the unbiased score,
+// sum folded in rank order (total = w[j] + total), / (sum + 1e-20), x scale.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace mlxs {
+
+__device__ __forceinline__ float rt_log1p(float x) {  // src/kernels/exl3/header_router_tail.metal
+    float xp1 = __fadd_rn(1.0f, x);
+    if (xp1 == __int_as_float(0x7F800000)) return xp1;
+    if (xp1 == 1.0f) return x;
+    return __fmul_rn(x, __fdiv_rn(det_logf(xp1), __fsub_rn(xp1, 1.0f)));
+}
+__device__ __forceinline__ float rt_softplus(float g) {
+    if (g != g) return __int_as_float(0x7FC00000);
+    float maxval = g > 0.0f ? g : 0.0f, minval = g > 0.0f ? 0.0f : g;
+    const float inf = __int_as_float(0x7F800000);
+    if (minval == -inf || maxval == inf) return maxval;
+    return __fadd_rn(maxval, rt_log1p(det_expf(__fsub_rn(minval, maxval))));
+}
+
+__global__ void router_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int E, int K,
+                              int scoring, int norm, float scale, int32_t* __restrict__ ids,
+                              float* __restrict__ weights) {
+    extern __shared__ float sm[];
+    float* key_sh = sm;          // [E]
+    float* red = sm + E;         // [32] softmax partials, then [0] = sum, [1] = max
+    float* picked = red + 34;    // [K]
+    const int row = blockIdx.x, e = threadIdx.x;
+    const float x = e < E ? logits[(size_t)row * E + e] : 0.0f;
+    float score = 0.0f;
+    if (scoring == 1) {
+        float y = __fdiv_rn(1.0f, __fadd_rn(1.0f, det_expf(fabsf(x))));
+        score = x < 0.0f ? y : __fsub_rn(1.0f, y);
+    } else if (scoring == 0) {
+        score = __fsqrt_rn(rt_softplus(x));
+    } else {
+        // softmax: max (exact in any order), exp(x - max), sum = 32 strided partials in index order then an
+        // xor butterfly 16, 8, 4, 2, 1 (the order the host restatement folds in)
+        if (e < E) key_sh[e] = x;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            float m = -__int_as_float(0x7F800000);
+            bool has_nan = false;
+            for (int j = threadIdx.x; j < E; j += 32) {
+                float v = key_sh[j];
+                if (v != v) has_nan = true; else if (v > m) m = v;
+            }
+            for (int o = 16; o >= 1; o >>= 1) {
+                float om = __shfl_xor_sync(0xFFFFFFFFu, m, o);
+                m = om > m ? om : m;
+            }
+            has_nan = __any_sync(0xFFFFFFFFu, has_nan);
+            if (threadIdx.x == 0) { red[33] = m; red[32] = has_nan ? 1.0f : 0.0f; }
+        }
+        __syncthreads();
+        const float m = red[33];
+        const bool has_nan = red[32] != 0.0f;
+        float ex = has_nan ? __int_as_float(0x7FC00000) : det_expf(__fsub_rn(x, m));
+        __syncthreads();
+        if (e < E) key_sh[e] = ex;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            float p = 0.0f;
+            for (int j = threadIdx.x; j < E; j += 32) p = __fadd_rn(p, key_sh[j]);
+            for (int o = 16; o >= 1; o >>= 1) p = __fadd_rn(p, __shfl_xor_sync(0xFFFFFFFFu, p, o));
+            if (threadIdx.x == 0) red[0] = p;
+        }
+        __syncthreads();
+        score = __fdiv_rn(ex, red[0]);
+        __syncthreads();
+    }
+    const float biased = bias ? __fadd_rn(score, e < E ? bias[e] : 0.0f) : score;
+    if (e < E) key_sh[e] = biased;
+    __syncthreads();
+    if (e < E) {
+        const bool mn = biased != biased;
+        int rank = 0;
+        for (int j = 0; j < E; ++j) {
+            const float o = key_sh[j];
+            const bool on = o != o;
+            const bool before = mn ? (!on || j < e) : (!on && (o > biased || (o == biased && j < e)));
+            rank += before ? 1 : 0;
+        }
+        if (rank < K) {
+            ids[(size_t)row * K + rank] = e;
+            picked[rank] = score;
+        }
+    }
+    __syncthreads();
+    if (e < K) {
+        float total = 0.0f;
+        for (int j = 0; j < K; ++j) total = __fadd_rn(picked[j], total);
+        const float den = __fadd_rn(total, 1e-20f);
+        const float q = norm ? __fdiv_rn(picked[e], den) : picked[e];
+        weights[(size_t)row * K + e] = __fmul_rn(q, scale);
+    }
+}
+
+cudaError_t launch_router(const float* logits, const float* bias, int T, int E, int K, int scoring, int norm,
+                          float scale, int32_t* ids, float* weights, cudaStream_t st) {
+    if (T == 0) return cudaSuccess;
+    int threads = ((E > K ? E : K) + 31) / 32 * 32;
+    size_t smem = (size_t)(E + 34 + K) * sizeof(float);
+    router_kernel<<<T, threads, smem, st>>>(logits, bias, E, K, scoring, norm, scale, ids, weights);
+    return cudaGetLastError();
+}
+
+}  // namespace mlxs

@@ -1,0 +1,76 @@
+"""The C-ABI library without a GPU: it loads, exports every symbol the header declares, and refuses by name."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from __graft_entry__ import ROOT, load_package
+
+
+def header_symbols():
+    text = (ROOT / "include" / "mlxs_moe.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mlxs_moe_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    pkg = load_package()
+    L = pkg.lib()
+    syms = header_symbols()
+    assert len(syms) >= 15
+    for s in syms:
+        assert hasattr(L, s), s
+    assert sorted(pkg.EXPORTS) == syms
+    assert L.mlxs_moe_abi() == pkg.ABI
+    text = (ROOT / "include" / "mlxs_moe.h").read_text()
+    assert f"#define MLXS_MOE_ABI {pkg.ABI}" in text
+
+
+def test_config_struct_matches_header_layout():
+    pkg = load_package()
+    assert C.sizeof(pkg.Config) == 18 * 4
+    assert C.sizeof(pkg.Stats) == 9 * 8 + 8
+
+
+def test_create_refuses_by_name():
+    pkg = load_package()
+    bad = [
+        (dict(hidden=5000), "hidden"), (dict(inter=100), "inter"), (dict(n_experts=0), "n_experts"),
+        (dict(top_k=0), "top_k"), (dict(top_k=99), "top_k"), (dict(bank_kind=7), "bank_kind"), (dict(act=5), "act"),
+        (dict(act_limit=0.0), "act_limit"), (dict(scoring=9), "scoring"), (dict(combine=3), "combine"),
+        (dict(max_tokens=0), "max_tokens"), (dict(ep_world=3), "ep_world"), (dict(combine=1), "combine"),
+    ]
+    for kw, name in bad:
+        base = dict(hidden=512, inter=256, n_experts=8, top_k=2)
+        base.update(kw)
+        with pytest.raises(pkg.MlxsError) as ei:
+            pkg.MoE(pkg.make_config(**base))
+        assert ei.value.rc == -2 and name in ei.value.msg, (kw, ei.value.msg)
+    cfg = pkg.make_config(512, 256, 8, 2)
+    cfg.struct_size = 12
+    with pytest.raises(pkg.MlxsError) as ei:
+        pkg.MoE(cfg)
+    assert "struct_size" in ei.value.msg
+
+
+def test_no_cpu_fallback_without_a_device():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    pkg = load_package()
+    with pytest.raises(pkg.MlxsError) as ei:
+        pkg.MoE(pkg.make_config(512, 256, 8, 2))
+    assert ei.value.rc == -3 and "no CPU path" in ei.value.msg
+
+
+def test_ep_plan_counts():
+    pkg = load_package()
+    ids = np.array([0, 5, 7, 2, 3, 6, 1, 4, 7, 7], np.int32)
+    out = np.zeros(4, np.uint64)
+    rc = pkg.lib().mlxs_moe_ep_plan(ids.ctypes.data, ids.size, 8, 4, out.ctypes.data)
+    assert rc == 0 and out.tolist() == [2, 2, 2, 4]
+    bad = np.array([9], np.int32)
+    assert pkg.lib().mlxs_moe_ep_plan(bad.ctypes.data, 1, 8, 4, out.ctypes.data) == -1
+    assert "outside" in pkg.last_error()

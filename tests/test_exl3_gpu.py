@@ -1,0 +1,192 @@
+"""GPU parity of the EXL3 routed-MoE path against the CPU oracle, through the C ABI.
+
+Bars: router ids and decoded weights bit-exact; f32 routed rows within the reference's f32-stage tolerance
+(max |err| / rms < 1e-4: src/exl3/selfcheck.zig:1167); bf16 layer output within 1e-2 relative L2.
+"""
+import hashlib
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import oracle_lib as O
+from moe_cases import Exl3Case, max_err_over_rms, rel_l2
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).resolve().parent / "golden"
+TOL_F32 = 1e-4
+TOL_LAYER = 1e-2
+
+
+@pytest.fixture(scope="module")
+def c1():
+    # BASELINE config 1: hidden 5120, inter 2304, 16 experts, top-4, shared expert, clamped SwiGLU
+    case = Exl3Case(5120, 2304, 16, 4, seed=0, shared=True, max_tokens=64)
+    yield case
+    case.close()
+
+
+@pytest.mark.parametrize("scoring,E,k", [(0, 256, 8), (1, 256, 8), (2, 256, 8), (0, 16, 4), (1, 288, 8), (2, 16, 4)])
+def test_router_bit_exact(scoring, E, k):
+    case = Exl3Case(512, 256, E, k, seed=1, shared=False, scoring=scoring, max_tokens=256, experts_to_load=[])
+    try:
+        for T, seed in ((1, 3), (7, 4), (256, 5)):
+            _, logits = case.inputs(T, seed)
+            if seed == 5:
+                logits[3, :8] = logits[3, 8]  # exact ties -> lower index first
+                logits[4, 5] = np.nan
+                logits[5] = np.float32(0.25)
+            ids, w = case.gpu_route(logits)
+            rid, rw = case.cpu_route(logits, det=True)
+            assert (ids == rid).all()
+            assert (w.view(np.uint32) == rw.view(np.uint32)).all() or np.allclose(w, rw, rtol=1e-6, equal_nan=True)
+            lid, lw = case.cpu_route(logits, det=False)
+            assert (ids == lid).mean() > 0.999
+    finally:
+        case.close()
+
+
+def test_router_bias_changes_selection_not_weights():
+    # src/arch/mimo_v2/config.zig:503-514
+    case = Exl3Case(512, 256, 4, 2, seed=1, shared=False, scoring=1, max_tokens=8, experts_to_load=[], routed_scale=1.0)
+    try:
+        bias = np.array([0, 0, 10, 0], np.float32)
+        case.moe.set_router_bias(0, bias.ctypes.data)
+        ids, w = case.gpu_route(np.array([[0, 2, -2, 1]], np.float32))
+        assert ids.tolist() == [[2, 1]]
+        low, high = 1 / (1 + np.exp(2.0)), 1 / (1 + np.exp(-2.0))
+        assert abs(w[0, 0] - low / (low + high)) < 1e-6 and abs(w[0].sum() - 1) < 1e-6
+    finally:
+        case.close()
+
+
+def test_decoded_weights_bit_exact_against_golden_planes():
+    """The reference's decode_table check (src/exl3/selfcheck.zig:848-901): one-hot rows through the GEMV return
+    W_hat's rows bit for bit; their sha256 is the golden `onehot_rows_sha256` of src/kernels/exl3/manifest.json."""
+    dig = json.loads((GOLD / "exl3_digests.json").read_text())["planes"]
+    H, I = 5120, 2304
+    case = Exl3Case(H, I, 2, 1, seed=0, shared=False, max_tokens=512, experts_to_load=[])
+    try:
+        g = O.exl3_geometry(H, I)
+        rec = np.zeros(g.record_bytes, np.uint8)
+        gate = O.fill_code(dig["gate_up"]["seed"], g.len[0] // 2)
+        down = O.fill_code(dig["down"]["seed"], g.len[6] // 2)
+        rec[g.off[0]:g.off[0] + g.len[0]] = gate.view(np.uint8)
+        rec[g.off[3]:g.off[3] + g.len[3]] = gate.view(np.uint8)[::-1].copy()  # up: a different stream
+        rec[g.off[6]:g.off[6] + g.len[6]] = down.view(np.uint8)
+        case.moe.load_expert(0, 1, rec.ctypes.data, rec.size)
+        for proj, name, n_in in ((0, "gate_up", H), (2, "down", I)):
+            rows = dig[name]["onehot_rows"]
+            xh = np.zeros((rows, n_in), np.float32)
+            xh[np.arange(rows), np.arange(rows)] = 1.0
+            z = case.gpu_gemv(1, proj, xh)
+            z16 = z.astype(np.float16)
+            assert (z16.astype(np.float32) == z).all()
+            assert hashlib.sha256(z16.tobytes()).hexdigest() == dig[name]["onehot_rows_sha256"]
+        # the up projection decodes its own stream
+        up_code = rec[g.off[3]:g.off[3] + g.len[3]].view(np.int16)
+        w_up = O.reconstruct(up_code, H // 16, I // 16, 3).view(np.float16)
+        xh = np.zeros((24, H), np.float32)
+        sel = np.arange(24) * 211 % H
+        xh[np.arange(24), sel] = 1.0
+        assert (case.gpu_gemv(1, 1, xh) == w_up[sel].astype(np.float32)).all()
+        assert case.status() == 0
+    finally:
+        case.close()
+
+
+def test_gemv_against_f64(c1):
+    # src/arch/glm5_next/exl3_parity.zig:132-166: the GEMV against the f64 product
+    rng = np.random.default_rng(11)
+    g = O.exl3_geometry(c1.H, c1.I)
+    for proj, n_in, n_out in ((0, c1.H, c1.I), (1, c1.H, c1.I), (2, c1.I, c1.H)):
+        xh = rng.standard_normal((19, n_in)).astype(np.float32)
+        z = c1.gpu_gemv(3, proj, xh)
+        code = c1.records[3][g.off[3 * proj]:g.off[3 * proj] + g.len[3 * proj]].view(np.int16)
+        w = O.reconstruct(code, n_in // 16, n_out // 16, 3).view(np.float16).astype(np.float64)
+        ref = xh.astype(np.float64) @ w
+        assert max_err_over_rms(z, ref) < 2.0 ** -16 * 8
+
+
+@pytest.mark.parametrize("T", [1, 8])
+def test_layer_config1(c1, T):
+    x, logits = c1.inputs(T, seed=20 + T)
+    ids, w = c1.gpu_route(logits)
+    rid, rw = c1.cpu_route(logits)
+    assert (ids == rid).all()
+    ref_y, ref_ro = c1.cpu_layer(x, rid, rw, want_ro=True)
+    ro = c1.gpu_routed(x, ids)
+    assert max_err_over_rms(ro, ref_ro) < TOL_F32
+    y = c1.gpu_experts(x, ids, w)
+    assert rel_l2(y, ref_y) < TOL_LAYER
+    y2 = c1.gpu_forward(x, logits)
+    assert (y2 == y).all()
+    y3 = c1.gpu_forward_host(x, logits)
+    assert (y3 == y).all()
+    assert c1.status() == 0
+
+
+def test_row_invariance_and_determinism(c1):
+    # src/exl3/selfcheck.zig:747-846: a row's result does not depend on the batch around it; runs repeat bit for bit
+    x, logits = c1.inputs(8, seed=77)
+    ids, _ = c1.cpu_route(logits)
+    full = c1.gpu_routed(x, ids)
+    again = c1.gpu_routed(x, ids)
+    assert (full.view(np.uint32) == again.view(np.uint32)).all()
+    for t in (0, 5):
+        one = c1.gpu_routed(x[t:t + 1], ids[t:t + 1])
+        assert (one[0].view(np.uint32) == full[t].view(np.uint32)).all()
+
+
+def test_ragged_and_heavy_experts(c1):
+    # every token to the same experts (rows per expert > one work item), and an empty call
+    T = 40
+    x, _ = c1.inputs(T, seed=5)
+    ids = np.tile(np.array([[2, 9, 11, 0]], np.int32), (T, 1))
+    ids[::3, 3] = 15
+    w = np.full((T, 4), 0.25, np.float32)
+    ref = c1.cpu_layer(x, ids, w)
+    y = c1.gpu_experts(x, ids, w)
+    assert rel_l2(y, ref) < TOL_LAYER
+    assert c1.gpu_experts(x[:0], ids[:0], w[:0]).shape == (0, c1.H)
+    assert c1.status() == 0
+
+
+def test_bad_ids_and_missing_experts_are_reported_not_faulted():
+    case = Exl3Case(512, 256, 8, 2, seed=2, shared=False, max_tokens=8, experts_to_load=[0, 1, 2])
+    try:
+        x, _ = case.inputs(2, seed=1)
+        w = np.full((2, 2), 0.5, np.float32)
+        case.gpu_experts(x, np.array([[0, 1], [2, 1]], np.int32), w)
+        assert case.status() == 0
+        case.gpu_experts(x, np.array([[0, 5], [2, 1]], np.int32), w)  # expert 5 never loaded
+        assert case.status() == 5
+        with pytest.raises(case.pkg.MlxsError) as ei:
+            case.gpu_forward_host(x, np.zeros((2, 8), np.float32))
+        assert ei.value.rc == -7
+    finally:
+        case.close()
+    case = Exl3Case(512, 256, 8, 2, seed=2, shared=False, max_tokens=8)
+    try:
+        x, _ = case.inputs(2, seed=1)
+        case.gpu_experts(x, np.array([[0, 99], [-4, 1]], np.int32), np.full((2, 2), 0.5, np.float32))
+        assert case.status() == 1
+        with pytest.raises(case.pkg.MlxsError) as ei:
+            case.gpu_experts(np.zeros((9, 512), np.float32), np.zeros((9, 2), np.int32), np.zeros((9, 2), np.float32))
+        assert ei.value.rc == -6
+    finally:
+        case.close()
+
+
+def test_small_shape_layer_many_seeds():
+    case = Exl3Case(512, 256, 8, 2, seed=4, shared=True, max_tokens=64)
+    try:
+        for T in (1, 3, 17, 64):
+            x, logits = case.inputs(T, seed=T)
+            y = case.gpu_forward(x, logits)
+            ids, w = case.cpu_route(logits)
+            assert rel_l2(y, case.cpu_layer(x, ids, w)) < TOL_LAYER
+        assert case.status() == 0
+    finally:
+        case.close()
