@@ -150,7 +150,9 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=8)
     ap.add_argument("--routing", default="normal", choices=["normal", "zipf"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--experts", type=int, default=E, help="routed experts (smaller only for profiler captures)")
     args = ap.parse_args()
+    globals()["E"] = args.experts
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
     if args.impl == "reference":
         args.steps = min(args.steps, 3)

@@ -170,8 +170,8 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
     cudaMemset(h->tabs.header, 0, 64);
     if (c->bank_kind == MLXS_BANK_EXL3_K3_MUL1) {
         const size_t kmax = (H > I ? H : I) / 16;
-        if ((rc = h->alloc(&h->xa_gu, (size_t)max_chunks * 2 * kmax * 512)) ||
-            (rc = h->alloc(&h->xa_d, (size_t)max_chunks * kmax * 512)) || (rc = h->alloc(&h->ro, A * (H > I ? H : I) * 4)))
+        if ((rc = h->alloc(&h->xa_gu, (size_t)max_chunks * 2 * kmax * 256)) ||
+            (rc = h->alloc(&h->xa_d, (size_t)max_chunks * kmax * 256)) || (rc = h->alloc(&h->ro, A * (H > I ? H : I) * 4)))
             return bail(rc);
     }
     if (c->shared_expert) {

@@ -86,7 +86,7 @@ __device__ __forceinline__ uint32_t mul1_pair(uint32_t sa, uint32_t sb) {
     uint32_t xa = sa * MUL1, xb = sb * MUL1;
     uint32_t ha = __dp4a(xa, 0x01010101u, 0x6400u);  // 0x6400 + byte sum = the half bits of 1024 + s
     uint32_t hb = __dp4a(xb, 0x01010101u, 0x6400u);
-    uint32_t pk = __byte_perm(ha, hb, 0x5410);
+    uint32_t pk = hb * 65536u + ha;
     const uint32_t kinv = 0x1EEE1EEEu, kbias = 0xC931C931u;
     __half2 r = __hfma2(*reinterpret_cast<__half2*>(&pk), *reinterpret_cast<const __half2*>(&kinv),
                         *reinterpret_cast<const __half2*>(&kbias));
@@ -102,8 +102,14 @@ __device__ __forceinline__ void exl3_decode_lane(uint32_t lo, uint32_t hi, uint3
     uint32_t v0 = __funnelshift_r(lo, hi, lp);  // stream bits, window m at bits [3m, 3m+16)
     uint32_t vh = hi >> lp;
     uint32_t v1 = __funnelshift_r(v0, vh, 18);  // windows 6, 7 at bits 0 and 3
-    uint32_t w0 = v0 & 0xFFFFu, w1 = (v0 >> 3) & 0xFFFFu, w2 = (v0 >> 6) & 0xFFFFu, w3 = (v0 >> 9) & 0xFFFFu;
-    uint32_t w4 = (v0 >> 12) & 0xFFFFu, w5 = (v0 >> 15) & 0xFFFFu, w6 = v1 & 0xFFFFu, w7 = (v1 >> 3) & 0xFFFFu;
+    uint32_t w0 = v0 & 0xFFFFu;
+    uint32_t w1 = (v0 >> 3) & 0xFFFFu;
+    uint32_t w2 = (v0 >> 6) & 0xFFFFu;
+    uint32_t w3 = (v0 >> 9) & 0xFFFFu;
+    uint32_t w4 = (v0 >> 12) & 0xFFFFu;
+    uint32_t w5 = (v0 >> 15) & 0xFFFFu;
+    uint32_t w6 = v1 & 0xFFFFu;
+    uint32_t w7 = (v1 >> 3) & 0xFFFFu;
     // code position j = 7 - m; positions (0,1),(2,3) -> columns 0..7 rows (r0,r0+1),(r0+8,r0+9); (4,5),(6,7) -> 8..15
     b[0] = mul1_pair(w7, w6);
     b[1] = mul1_pair(w5, w4);

@@ -3,18 +3,21 @@
 // One projection is y = H128( H128(x * suh) . W_hat ) * svh (src/arch/glm5_next/exl3_forms_ref.zig:137-152; op order
 // of the decode chain: src/arch/deepseek_v41/experts.zig:449-467).  The weight stream is the bound: a CTA owns one
 // 128-wide output block of one expert for up to 16 of its rows, streams that block's code once through a ring of
-// bulk-copied (TMA 1-D) shared-memory stages, decodes each 16x16 tile in registers straight into mma B fragments
-// (the trellis' tensor-core order makes a lane's 8 code positions exactly its fragment) and multiplies with the rows'
-// rotated activations held as f16 hi + f16 lo halves of the m16 tile, so the f32 precision of the reference's decode
-// chain is kept while the FMAs run on the tensor pipe.  The output-side Hadamard, svh, the clamped SwiGLU and the down
+// bulk-copied (TMA 1-D) shared-memory stages, decodes each 16x16 tile in registers straight into one mma A fragment
+// (the trellis' tensor-core order makes a lane's 8 code positions exactly its fragment of W^T: 16 output columns x 16
+// inputs) and multiplies with the rows' rotated activations as the B operand: 8 token slots = 4 rows as f16 hi + the
+// same rows as f16 lo, so the f32 precision of the reference's decode chain is kept while the FMAs run on the tensor
+// pipe, one mma per tile for up to 4 rows.  The output-side Hadamard, svh, the clamped SwiGLU and the down
 // projection's input rotation are fused into the gate/up epilogue; H128 . svh into the down epilogue.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 
 namespace mlxs {
 
 constexpr int KT = 8;             // k-tiles (16 inputs each) per pipeline stage = one 128-block of the input
-constexpr int A_TILE_WORDS = 128;  // one m-tile x k-tile of activations in fragment order: 32 lanes x 4 u32
+constexpr int A_TILE_WORDS = 64;   // one chunk x k-tile of activations in B-fragment order: 32 lanes x 2 u32
 constexpr int ZS_STRIDE = 132;    // padded row stride of the epilogue's f32 staging
 
 // ------------------------------------------------------------------------------------------------------------
@@ -74,22 +77,24 @@ cudaError_t launch_exl3_repack(const uint8_t* record_dev, Exl3Dims d, uint32_t* 
 // ------------------------------------------------------------------------------------------------------------
 // activation staging: rows -> mma A-fragment order, f16 hi / lo
 // ------------------------------------------------------------------------------------------------------------
-// One k-tile x m-tile block is 32 lanes x 4 u32: lane (g = row, c) holds a0 = hi(k 2c,2c+1), a1 = lo(same),
-// a2 = hi(k 2c+8,2c+9), a3 = lo(same).  A warp lane that owns elements 4*lane..4*lane+3 of a 128-block writes the
-// k-tile lane/4, k = 4*(lane&3) + q.
+// One chunk x k-tile block is 32 lanes x 2 u32: lane (g = token slot, c) holds b0 = x[slot g][k 2c,2c+1],
+// b1 = x[slot g][k 2c+8,2c+9]; slots 0..3 are the f16 hi halves of rows 0..3, slots 4..7 their lo halves.  A warp lane
+// that owns elements 4*lane..4*lane+3 of a 128-block writes k-tile lane/4, k = 4*(lane&3) + q.
 __device__ __forceinline__ void store_frag4(uint32_t* tile_base /* the 128-block's first k-tile */, uint32_t row,
                                             uint32_t lane, const float (&v)[4]) {
     const uint32_t cq = lane & 3u;
     uint32_t* kt = tile_base + (lane >> 2) * A_TILE_WORDS;
-    const uint32_t idx0 = (row * 4u + 2u * (cq & 1u)) * 4u + (cq >> 1) * 2u;
+    const uint32_t c0 = 2u * (cq & 1u), reg = cq >> 1;
     __half h0, l0, h1, l1, h2, l2, h3, l3;
     split_hi_lo(v[0], h0, l0); split_hi_lo(v[1], h1, l1); split_hi_lo(v[2], h2, l2); split_hi_lo(v[3], h3, l3);
-    *reinterpret_cast<uint2*>(kt + idx0) = make_uint2(pack_h2(h0, h1), pack_h2(l0, l1));
-    *reinterpret_cast<uint2*>(kt + idx0 + 4) = make_uint2(pack_h2(h2, h3), pack_h2(l2, l3));
+    kt[(row * 4u + c0) * 2u + reg] = pack_h2(h0, h1);
+    kt[((row + 4u) * 4u + c0) * 2u + reg] = pack_h2(l0, l1);
+    kt[(row * 4u + c0 + 1u) * 2u + reg] = pack_h2(h2, h3);
+    kt[((row + 4u) * 4u + c0 + 1u) * 2u + reg] = pack_h2(l2, l3);
 }
 
 template <bool RAW>
-__global__ void __launch_bounds__(256) exl3_prep_kernel(const void* __restrict__ xin, uint32_t top_k, uint32_t in_dim,
+__global__ void __launch_bounds__(CHUNK_ROWS * 32) exl3_prep_kernel(const void* __restrict__ xin, uint32_t top_k, uint32_t in_dim,
                                                         const __half* __restrict__ scales, size_t scales_stride,
                                                         DispatchTables t, uint32_t* __restrict__ xa) {
     const uint32_t chunk = blockIdx.x;
@@ -104,7 +109,7 @@ __global__ void __launch_bounds__(256) exl3_prep_kernel(const void* __restrict__
     const float S = __uint_as_float(SCALE_BITS);
     for (int p = 0; p < NP; ++p) {
         uint32_t* dst = xa + ((size_t)chunk * NP + p) * nkt * A_TILE_WORDS;
-        for (uint32_t b = 0; b < in_dim / 128; ++b) {
+        for (uint32_t b = blockIdx.y; b < in_dim / 128; b += gridDim.y) {
             float v[4] = {0.f, 0.f, 0.f, 0.f};
             if (valid) {
                 if (RAW) {
@@ -132,11 +137,11 @@ __global__ void __launch_bounds__(256) exl3_prep_kernel(const void* __restrict__
 
 cudaError_t launch_exl3_prep_in(const __nv_bfloat16* x, uint32_t top_k, Exl3Layer L, Exl3Dims d, DispatchTables t,
                                 uint32_t* xa_gu, cudaStream_t st) {
-    exl3_prep_kernel<false><<<t.max_chunks, 256, 0, st>>>(x, top_k, d.H, L.scales, exl3_scales_per_expert(d), t, xa_gu);
+    exl3_prep_kernel<false><<<dim3(t.max_chunks, 8), CHUNK_ROWS * 32, 0, st>>>(x, top_k, d.H, L.scales, exl3_scales_per_expert(d), t, xa_gu);
     return cudaGetLastError();
 }
 cudaError_t launch_exl3_prep_raw(const float* xh, uint32_t in_dim, DispatchTables t, uint32_t* xa, cudaStream_t st) {
-    exl3_prep_kernel<true><<<t.max_chunks, 256, 0, st>>>(xh, 1, in_dim, nullptr, 0, t, xa);
+    exl3_prep_kernel<true><<<dim3(t.max_chunks, 8), CHUNK_ROWS * 32, 0, st>>>(xh, 1, in_dim, nullptr, 0, t, xa);
     return cudaGetLastError();
 }
 
@@ -169,17 +174,36 @@ struct GemvParams {
 
 struct StageMeta { int32_t item; uint32_t kt0, chunk0, mc, expert, nb; };
 
-template <int NPROJ, int EPI>
-__global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 2 : 1) exl3_gemv_kernel(const GemvParams P) {
+// one pipeline stage (KT k-tiles) of one warp's 16-column tile, MC chunks of activations
+template <int NPROJ, int KSTRIDE, int MC>
+__device__ __forceinline__ void gemv_stage(const uint32_t* __restrict__ wt, const uint2* __restrict__ at, uint32_t wi,
+                                           uint32_t wj, uint32_t lp, uint32_t p, float (&acc)[GROUP_CHUNKS][4]) {
+#pragma unroll
+    for (int kt = 0; kt < KT; ++kt) {
+        const uint32_t lo = wt[kt * KSTRIDE + wi], hi = wt[kt * KSTRIDE + wj];
+        uint32_t b[4];
+        exl3_decode_lane(lo, hi, lp, b);
+        // W^T as the A operand: rows = the tile's 16 output columns
+        const uint32_t a[4] = {b[0], b[2], b[1], b[3]};
+#pragma unroll
+        for (int mt = 0; mt < MC; ++mt) {
+            const uint2 xv = at[((mt * NPROJ + p) * KT + kt) * 32];
+            mma_f16(acc[mt], a, xv.x, xv.y);
+        }
+    }
+}
+
+template <int NPROJ, int EPI, int KSTRIDE>
+__global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gemv_kernel(const GemvParams P) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     constexpr int NCW = NPROJ * 8;         // consumer warps: projection x 16-column tile of the 128 block
     constexpr int MAXS = 8;
     __shared__ __align__(8) uint64_t full_bar[MAXS], empty_bar[MAXS], epi_bar;
     __shared__ StageMeta meta[MAXS];
     __shared__ volatile int s_abort;
-    // epilogue staging: [NPROJ][GROUP_CHUNKS][8 rows][ZS_STRIDE]
+    // epilogue staging: [NPROJ][GROUP_CHUNKS][CHUNK_ROWS][ZS_STRIDE]
     float* zs = reinterpret_cast<float*>(smem_raw);
-    uint8_t* ring = smem_raw + (size_t)NPROJ * GROUP_CHUNKS * 8 * ZS_STRIDE * sizeof(float);
+    uint8_t* ring = smem_raw + (size_t)NPROJ * GROUP_CHUNKS * CHUNK_ROWS * ZS_STRIDE * sizeof(float);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t NS = P.n_stages;
 
@@ -236,7 +260,7 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 2 : 1) exl3_gem
     const uint32_t p = warp >> 3, j = warp & 7u;  // projection, 16-column tile
     uint32_t wi, wj, lp;
     exl3_lane_plan(lane, wi, wj, lp);
-    float acc[GROUP_CHUNKS][2][4];
+    float acc[GROUP_CHUNKS][4];
     const float S = __uint_as_float(SCALE_BITS);
     uint32_t epi_ph = 0;
     // every wait in this kernel is a bounded mbarrier wait: the epilogue's two rendezvous of the consumer warps too
@@ -261,48 +285,38 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 2 : 1) exl3_gem
 #pragma unroll
             for (int a = 0; a < GROUP_CHUNKS; ++a)
 #pragma unroll
-                for (int b = 0; b < 2; ++b)
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.f;
+                for (int c = 0; c < 4; ++c) acc[a][c] = 0.f;
         }
         const uint8_t* st = ring + (size_t)s * P.stage_bytes;
         const uint32_t* wt = reinterpret_cast<const uint32_t*>(st) + P.proj_off_words + p * 192u + j * 24u;
-        const uint4* at = reinterpret_cast<const uint4*>(st + P.w_bytes) + lane;
-#pragma unroll 4
-        for (int kt = 0; kt < KT; ++kt) {
-            const uint32_t lo = wt[kt * P.kt_stride_words + wi], hi = wt[kt * P.kt_stride_words + wj];
-            uint32_t b[4];
-            exl3_decode_lane(lo, hi, lp, b);
-#pragma unroll
-            for (int mt = 0; mt < GROUP_CHUNKS; ++mt) {
-                if (mt < (int)m.mc) {
-                    const uint4 av = at[((mt * NPROJ + p) * KT + kt) * 32];
-                    const uint32_t a[4] = {av.x, av.y, av.z, av.w};
-                    mma_f16(acc[mt][0], a, b[0], b[1]);
-                    mma_f16(acc[mt][1], a, b[2], b[3]);
-                }
-            }
-        }
+        const uint2* at = reinterpret_cast<const uint2*>(st + P.w_bytes) + lane;
+        static_assert(GROUP_CHUNKS == 4, "the stage dispatch below enumerates the chunk counts");
+        if (m.mc == 1) gemv_stage<NPROJ, KSTRIDE, 1>(wt, at, wi, wj, lp, p, acc);
+        else if (m.mc == 2) gemv_stage<NPROJ, KSTRIDE, 2>(wt, at, wi, wj, lp, p, acc);
+        else if (m.mc == 3) gemv_stage<NPROJ, KSTRIDE, 3>(wt, at, wi, wj, lp, p, acc);
+        else gemv_stage<NPROJ, KSTRIDE, 4>(wt, at, wi, wj, lp, p, acc);
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[s]);
         if (m.kt0 + KT < P.nkt) continue;
 
         // ---------------- epilogue of the item ----------------
-        // z[row] = hi-part rows + lo-part rows of the m16 tile
+        // the D fragment holds (column g | g+8) x (token slots 2c, 2c+1); z[row] = hi slot + lo slot = lane c + lane c+2
         const uint32_t g = lane >> 2, c = lane & 3u;
 #pragma unroll
         for (int mt = 0; mt < GROUP_CHUNKS; ++mt) {
             if (mt < (int)m.mc) {
+                float v[4];
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
-                    float2 v = make_float2(acc[mt][nt][0] + acc[mt][nt][2], acc[mt][nt][1] + acc[mt][nt][3]);
-                    *reinterpret_cast<float2*>(zs + ((p * GROUP_CHUNKS + mt) * 8 + g) * ZS_STRIDE + j * 16 + nt * 8 + 2 * c) = v;
+                for (int q = 0; q < 4; ++q) v[q] = acc[mt][q] + __shfl_xor_sync(0xFFFFFFFFu, acc[mt][q], 2);
+                if (c < 2) {
+                    float* zr = zs + ((p * GROUP_CHUNKS + mt) * CHUNK_ROWS + 2 * c) * ZS_STRIDE + j * 16 + g;
+                    zr[0] = v[0]; zr[ZS_STRIDE] = v[1]; zr[8] = v[2]; zr[ZS_STRIDE + 8] = v[3];
                 }
             }
         }
         if (!epi_sync()) break;
-        for (uint32_t combo = warp; combo < (uint32_t)GROUP_CHUNKS * 8; combo += NCW) {
-            const uint32_t mt = combo >> 3, row = combo & 7u;
+        for (uint32_t combo = warp; combo < (uint32_t)GROUP_CHUNKS * CHUNK_ROWS; combo += NCW) {
+            const uint32_t mt = combo / CHUNK_ROWS, row = combo % CHUNK_ROWS;
             if (mt >= m.mc) continue;
             const uint32_t chunk = m.chunk0 + mt;
             const bool valid = row < P.t.chunk_rows[chunk];
@@ -310,8 +324,8 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 2 : 1) exl3_gem
             if (EPI == EPI_GATE_UP) {
                 float v[4] = {0.f, 0.f, 0.f, 0.f};
                 if (valid) {
-                    const float4 zg = *reinterpret_cast<const float4*>(zs + ((0 * GROUP_CHUNKS + mt) * 8 + row) * ZS_STRIDE + lane * 4);
-                    const float4 zu = *reinterpret_cast<const float4*>(zs + ((1 * GROUP_CHUNKS + mt) * 8 + row) * ZS_STRIDE + lane * 4);
+                    const float4 zg = *reinterpret_cast<const float4*>(zs + ((0 * GROUP_CHUNKS + mt) * CHUNK_ROWS + row) * ZS_STRIDE + lane * 4);
+                    const float4 zu = *reinterpret_cast<const float4*>(zs + ((1 * GROUP_CHUNKS + mt) * CHUNK_ROWS + row) * ZS_STRIDE + lane * 4);
                     float gq[4] = {zg.x, zg.y, zg.z, zg.w}, uq[4] = {zu.x, zu.y, zu.z, zu.w};
                     hadamard128_warp(gq, lane);
                     hadamard128_warp(uq, lane);
@@ -347,7 +361,7 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 2 : 1) exl3_gem
                 }
                 store_frag4(P.xa_d + ((size_t)chunk * (P.I / 16) + m.nb * 8) * A_TILE_WORDS, row, lane, v);
             } else if (valid) {
-                const float4 z4 = *reinterpret_cast<const float4*>(zs + ((size_t)mt * 8 + row) * ZS_STRIDE + lane * 4);
+                const float4 z4 = *reinterpret_cast<const float4*>(zs + ((size_t)mt * CHUNK_ROWS + row) * ZS_STRIDE + lane * 4);
                 float v[4] = {z4.x, z4.y, z4.z, z4.w};
                 const uint32_t assign = P.t.order[P.t.chunk_row0[chunk] + row];
                 if (EPI == EPI_DOWN) {
@@ -365,31 +379,40 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 2 : 1) exl3_gem
     }
 }
 
+static int tune_env(const char* name, int dflt, int lo, int hi) {
+    const char* v = getenv(name);
+    if (!v) return dflt;
+    int x = atoi(v);
+    return x < lo ? lo : (x > hi ? hi : x);
+}
+
 static cudaError_t launch_gemv(int nproj, int epi, GemvParams& P, int sm_count, cudaStream_t st) {
-    const uint32_t zs_bytes = (uint32_t)(nproj * GROUP_CHUNKS * 8 * ZS_STRIDE * sizeof(float));
+    const uint32_t zs_bytes = (uint32_t)(nproj * GROUP_CHUNKS * CHUNK_ROWS * ZS_STRIDE * sizeof(float));
     P.w_bytes = KT * P.kt_stride_words * 4;
     P.stage_bytes = P.w_bytes + GROUP_CHUNKS * nproj * KT * A_TILE_WORDS * 4;
-    const uint32_t budget = (nproj == 2 ? 200u : 100u) * 1024u;
+    // resident CTAs per SM (tunable for experiments: MLXS_GU_CTAS 1..2, MLXS_DN_CTAS 1..3); the shared-memory ring
+    // takes what the SM's 227 KB leave per CTA
+    static const int gu_ctas = tune_env("MLXS_GU_CTAS", 2, 1, 2), dn_ctas = tune_env("MLXS_DN_CTAS", 3, 1, 3);
+    const int per_sm = nproj == 2 ? gu_ctas : dn_ctas;
+    const uint32_t budget = (uint32_t)(225 * 1024 / per_sm) - 2048u;
     uint32_t ns = (budget - zs_bytes) / P.stage_bytes;
     if (ns > 8) ns = 8;
     if (ns < 2) return cudaErrorInvalidValue;
     P.n_stages = ns;
     const size_t smem = zs_bytes + (size_t)ns * P.stage_bytes;
     cudaError_t e;
-    const int ctas = nproj == 2 ? sm_count : 2 * sm_count;
-    if (nproj == 2) {
-        e = cudaFuncSetAttribute(exl3_gemv_kernel<2, EPI_GATE_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        exl3_gemv_kernel<2, EPI_GATE_UP><<<ctas, 2 * 256 + 32, smem, st>>>(P);
-    } else if (epi == EPI_DOWN) {
-        e = cudaFuncSetAttribute(exl3_gemv_kernel<1, EPI_DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        exl3_gemv_kernel<1, EPI_DOWN><<<ctas, 256 + 32, smem, st>>>(P);
-    } else {
-        e = cudaFuncSetAttribute(exl3_gemv_kernel<1, EPI_RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        exl3_gemv_kernel<1, EPI_RAW><<<ctas, 256 + 32, smem, st>>>(P);
-    }
+    const int ctas = per_sm * sm_count;
+#define MLXS_LAUNCH(NP, EP, KS)                                                                                   \
+    do {                                                                                                         \
+        e = cudaFuncSetAttribute(exl3_gemv_kernel<NP, EP, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) return e;                                                                          \
+        exl3_gemv_kernel<NP, EP, KS><<<ctas, NP * 256 + 32, smem, st>>>(P);                                      \
+    } while (0)
+    if (nproj == 2) MLXS_LAUNCH(2, EPI_GATE_UP, 384);
+    else if (epi == EPI_DOWN) MLXS_LAUNCH(1, EPI_DOWN, 192);
+    else if (P.kt_stride_words == 192) MLXS_LAUNCH(1, EPI_RAW, 192);
+    else MLXS_LAUNCH(1, EPI_RAW, 384);
+#undef MLXS_LAUNCH
     return cudaGetLastError();
 }
 

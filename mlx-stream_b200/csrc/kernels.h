@@ -5,10 +5,10 @@
 
 namespace mlxs {
 
-// Rows of one expert are processed in chunks of 8 (one mma m-tile: 8 rows as f16 hi + 8 rows as f16 lo) and a work
-// item carries up to GROUP_CHUNKS chunks of one expert.
-constexpr int CHUNK_ROWS = 8;
-constexpr int GROUP_CHUNKS = 2;
+// Rows of one expert are processed in chunks of 4 (one mma n-tile of 8 token slots: 4 rows as f16 hi + the same
+// 4 rows as f16 lo) and a work item carries up to GROUP_CHUNKS chunks of one expert.
+constexpr int CHUNK_ROWS = 4;
+constexpr int GROUP_CHUNKS = 4;
 
 // Device-side dispatch tables (all uint32), rebuilt by every call.
 struct DispatchTables {
@@ -47,7 +47,7 @@ static inline size_t exl3_code_words(Exl3Dims d) { return (size_t)(d.H / 16) * (
 cudaError_t launch_exl3_repack(const uint8_t* record_dev, Exl3Dims d, uint32_t* gu_code_e, uint32_t* d_code_e,
                                __half* scales_e, cudaStream_t st);
 
-// activation staging in mma A-fragment order: [chunk][proj][k-tile][32 lanes][4] u32 (512 B per k-tile)
+// activation staging in mma B-fragment order: [chunk][proj][k-tile][32 lanes][2] u32 (256 B per k-tile)
 // gate/up inputs: xg = H128(x * suh_g) * 128^-0.5 and xu likewise, f16 hi/lo
 cudaError_t launch_exl3_prep_in(const __nv_bfloat16* x, uint32_t top_k, Exl3Layer L, Exl3Dims d, DispatchTables t,
                                 uint32_t* xa_gu, cudaStream_t st);
@@ -58,8 +58,8 @@ struct Exl3GemvArgs {
     Exl3Layer L;
     Exl3Dims d;
     DispatchTables t;
-    const uint32_t* xa_gu;  // [chunk][2][H/16][128] u32
-    uint32_t* xa_d;         // [chunk][I/16][128] u32 (written by gate/up, read by down)
+    const uint32_t* xa_gu;  // [chunk][2][H/16][64] u32
+    uint32_t* xa_d;         // [chunk][I/16][64] u32 (written by gate/up, read by down)
     float* ro;              // [A, H] f32 routed outputs in assignment order (CHAIN combine: bf16 [A, H])
     int ro_bf16;
     float limit;            // > 0: clamped SwiGLU
