@@ -1,0 +1,89 @@
+//! extern-fn view of include/mlxs_moe.h for the Zig host (source only: this image has no Zig compiler; the C header
+//! is the compiled, tested statement of the same ABI).  One declaration per C entry point, same order.
+const std = @import("std");
+
+pub const abi_expected: i32 = 2026112501;
+
+pub const Moe = opaque {};
+
+pub const BankKind = enum(u32) { exl3_k3_mul1 = 0, mxfp4 = 1, nvfp4 = 2 };
+pub const Scoring = enum(u32) { sqrtsoftplus = 0, sigmoid = 1, softmax = 2 };
+pub const Act = enum(u32) { swiglu = 0, swiglu_clamped = 1 };
+pub const Combine = enum(u32) { f32 = 0, chain = 1 };
+
+pub const Config = extern struct {
+    struct_size: u32 = @sizeOf(Config),
+    hidden: u32,
+    inter: u32,
+    n_experts: u32,
+    top_k: u32,
+    n_layers: u32,
+    bank_kind: u32,
+    act: u32,
+    act_limit: f32,
+    scoring: u32,
+    norm_topk: u32,
+    routed_scale: f32,
+    shared_expert: u32,
+    combine: u32,
+    max_tokens: u32,
+    device: i32,
+    ep_world: u32 = 1,
+    ep_rank: u32 = 0,
+};
+
+pub const Stats = extern struct {
+    route_calls: u64,
+    expert_calls: u64,
+    tokens: u64,
+    assignments: u64,
+    distinct_experts_last: u64,
+    weight_bytes_last: u64,
+    a2a_bytes_sent: u64,
+    a2a_bytes_recv: u64,
+    resident_bytes: u64,
+    device_status: u32,
+    reserved: u32,
+};
+
+pub extern fn mlxs_moe_abi() i32;
+pub extern fn mlxs_moe_last_error() [*:0]const u8;
+pub extern fn mlxs_moe_create(cfg: *const Config, out: **Moe) c_int;
+pub extern fn mlxs_moe_destroy(h: ?*Moe) void;
+pub extern fn mlxs_moe_record_bytes(h: *const Moe, logical: ?*u64, stride: ?*u64) c_int;
+pub extern fn mlxs_moe_load_expert(h: *Moe, layer: u32, expert: u32, record: *const anyopaque, nbytes: u64, on_device: c_int) c_int;
+pub extern fn mlxs_moe_load_bank(h: *Moe, dir: [*:0]const u8) c_int;
+pub extern fn mlxs_moe_set_router_bias(h: *Moe, layer: u32, bias_host: ?[*]const f32) c_int;
+pub extern fn mlxs_moe_set_shared(h: *Moe, layer: u32, w1: *const anyopaque, w3: *const anyopaque, w2: *const anyopaque, on_device: c_int) c_int;
+pub extern fn mlxs_moe_route(h: *Moe, layer: u32, logits_dev: *const anyopaque, t: u32, ids_dev: *anyopaque, weights_dev: *anyopaque, stream: ?*anyopaque) c_int;
+pub extern fn mlxs_moe_routed(h: *Moe, layer: u32, x_dev: *const anyopaque, ids_dev: *const anyopaque, t: u32, out_dev: *anyopaque, stream: ?*anyopaque) c_int;
+pub extern fn mlxs_moe_experts(h: *Moe, layer: u32, x_dev: *const anyopaque, ids_dev: *const anyopaque, weights_dev: *const anyopaque, t: u32, y_dev: *anyopaque, stream: ?*anyopaque) c_int;
+pub extern fn mlxs_moe_forward(h: *Moe, layer: u32, x_dev: *const anyopaque, logits_dev: *const anyopaque, t: u32, y_dev: *anyopaque, stream: ?*anyopaque) c_int;
+pub extern fn mlxs_moe_forward_host(h: *Moe, layer: u32, x_host: *const anyopaque, logits_host: [*]const f32, t: u32, y_host: *anyopaque, stream: ?*anyopaque) c_int;
+pub extern fn mlxs_moe_exl3_gemv(h: *Moe, layer: u32, expert: u32, proj: u32, xh_dev: *const anyopaque, rows: u32, z_dev: *anyopaque, stream: ?*anyopaque) c_int;
+pub extern fn mlxs_moe_stats_get(h: *Moe, out: *Stats) c_int;
+
+pub const Error = error{ Arg, Config, Cuda, Bank, NotLoaded, TooManyTokens, DeviceStatus, Manifest, Ep };
+
+/// rc -> Zig error, the message left at mlxs_moe_last_error() (the reference's Diag carries the same kind of text,
+/// sdk/peek.zig:15-27).
+pub fn check(rc: c_int) Error!void {
+    return switch (rc) {
+        0 => {},
+        -1 => error.Arg,
+        -2 => error.Config,
+        -3 => error.Cuda,
+        -4 => error.Bank,
+        -5 => error.NotLoaded,
+        -6 => error.TooManyTokens,
+        -7 => error.DeviceStatus,
+        -8 => error.Manifest,
+        else => error.Ep,
+    };
+}
+
+/// Refuse a library built against another ABI, as the reference does for its read pool
+/// (src/sdk_ext/expert/io.zig:62-69).
+pub fn negotiate() Error!void {
+    if (mlxs_moe_abi() != abi_expected) return error.Config;
+}
