@@ -140,6 +140,17 @@ int mlxs_moe_forward_host(mlxs_moe *h, uint32_t layer, const void *x_host, const
 int mlxs_moe_exl3_gemv(mlxs_moe *h, uint32_t layer, uint32_t expert, uint32_t proj, const float *xh_dev,
                        uint32_t rows, float *z_dev, void *stream);
 
+/* The same projection for callers that may not allocate device memory: z f32 [rows, out_dim] = xh f32 [rows, in_dim]
+ * . W_hat of the code plane at code_dev (I16 [in_dim/16, out_dim/16, 48], the bank file's order).  It has no
+ * counterpart in the reference.  It needs no handle and calls no allocator: a host that fixes its device-memory
+ * budget at load time, or code running while a stream is being captured (where cudaMalloc is not allowed), can still
+ * use it.  Its scratch is a fixed 1 MiB array inside the library, which limits a call to rows <= 32 and
+ * in_dim <= 8192 (a multiple of 128; out_dim a multiple of 16); larger sizes are refused.  The first call on a device
+ * looks up the array's address (make that call before any stream capture).  All calls share the array: calls that
+ * overlap on the GPU race, so keep them on one stream or order them yourself. */
+int mlxs_moe_exl3_gemv_noalloc(const void *code_dev, uint32_t in_dim, uint32_t out_dim, const float *xh_dev,
+                               uint32_t rows, float *z_dev, void *stream);
+
 int mlxs_moe_stats_get(mlxs_moe *h, mlxs_moe_stats *out);
 
 /* per-stage device timing with CUDA events on the caller's stream, off by default (the reference's comptime profile

@@ -25,6 +25,7 @@ EXPORTS = [
     "mlxs_moe_abi", "mlxs_moe_last_error", "mlxs_moe_create", "mlxs_moe_destroy", "mlxs_moe_record_bytes",
     "mlxs_moe_load_expert", "mlxs_moe_load_bank", "mlxs_moe_set_router_bias", "mlxs_moe_set_shared", "mlxs_moe_route",
     "mlxs_moe_routed", "mlxs_moe_experts", "mlxs_moe_forward", "mlxs_moe_forward_host", "mlxs_moe_exl3_gemv",
+    "mlxs_moe_exl3_gemv_noalloc",
     "mlxs_moe_stats_get", "mlxs_moe_profile_enable", "mlxs_moe_profile_read", "mlxs_moe_ep_unique_id", "mlxs_moe_ep_init", "mlxs_moe_ep_plan",
 ]
 
@@ -86,6 +87,8 @@ def lib():
         L.mlxs_moe_forward_host.argtypes = L.mlxs_moe_forward.argtypes
         L.mlxs_moe_exl3_gemv.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32,
                                          C.c_void_p, C.c_void_p]
+        L.mlxs_moe_exl3_gemv_noalloc.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p,
+                                                 C.c_void_p]
         L.mlxs_moe_stats_get.argtypes = [C.c_void_p, C.POINTER(Stats)]
         L.mlxs_moe_profile_enable.argtypes = [C.c_void_p, C.c_int]
         L.mlxs_moe_profile_read.argtypes = [C.c_void_p, C.POINTER(Profile)]
@@ -112,6 +115,11 @@ def make_config(hidden, inter, n_experts, top_k, n_layers=1, bank_kind=BANK_EXL3
                 combine=COMBINE_F32, max_tokens=64, device=0, ep_world=1, ep_rank=0):
     return Config(C.sizeof(Config), hidden, inter, n_experts, top_k, n_layers, bank_kind, act, act_limit, scoring,
                   int(norm_topk), routed_scale, int(shared_expert), combine, max_tokens, device, ep_world, ep_rank)
+
+
+def exl3_gemv_noalloc(code, in_dim, out_dim, xh, rows, z, stream=None):
+    """z = xh . W_hat of one code plane with no handle and no allocation (fixed scratch inside the library)."""
+    _check(lib().mlxs_moe_exl3_gemv_noalloc(code, in_dim, out_dim, xh, rows, z, stream))
 
 
 class MoE:

@@ -27,6 +27,16 @@ static int fail(int rc, const char* fmt, ...) {
     g_err = buf;
     return rc;
 }
+// the same error channel for the library's other translation units
+int mlxs_fail(int rc, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_err = buf;
+    return rc;
+}
 #define CU(call)                                                                                          \
     do {                                                                                                  \
         cudaError_t e__ = (call);                                                                         \

@@ -61,6 +61,7 @@ pub extern fn mlxs_moe_experts(h: *Moe, layer: u32, x_dev: *const anyopaque, ids
 pub extern fn mlxs_moe_forward(h: *Moe, layer: u32, x_dev: *const anyopaque, logits_dev: *const anyopaque, t: u32, y_dev: *anyopaque, stream: ?*anyopaque) c_int;
 pub extern fn mlxs_moe_forward_host(h: *Moe, layer: u32, x_host: *const anyopaque, logits_host: [*]const f32, t: u32, y_host: *anyopaque, stream: ?*anyopaque) c_int;
 pub extern fn mlxs_moe_exl3_gemv(h: *Moe, layer: u32, expert: u32, proj: u32, xh_dev: *const anyopaque, rows: u32, z_dev: *anyopaque, stream: ?*anyopaque) c_int;
+pub extern fn mlxs_moe_exl3_gemv_noalloc(code_dev: *const anyopaque, in_dim: u32, out_dim: u32, xh_dev: *const anyopaque, rows: u32, z_dev: *anyopaque, stream: ?*anyopaque) c_int;
 pub extern fn mlxs_moe_stats_get(h: *Moe, out: *Stats) c_int;
 
 pub const Error = error{ Arg, Config, Cuda, Bank, NotLoaded, TooManyTokens, DeviceStatus, Manifest, Ep };
