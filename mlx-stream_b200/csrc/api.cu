@@ -47,6 +47,8 @@ struct LayerBank {
     uint32_t* gu_code = nullptr;
     uint32_t* d_code = nullptr;
     __half* scales = nullptr;
+    uint8_t *f4_gu = nullptr, *f4_dn = nullptr;  // FP4 banks: the two streams
+    float* f4_gscale = nullptr;                  // NVFP4 [E_local][3]
     uint8_t* loaded_dev = nullptr;  // [E] 1 = resident on this rank
     std::vector<uint8_t> loaded;
     float* bias = nullptr;          // [E] or null
@@ -68,6 +70,7 @@ struct mlxs_moe {
     uint32_t* xa_gu = nullptr;
     uint32_t* xa_d = nullptr;
     float* ro = nullptr;
+    uint32_t chunk_rows = CHUNK_ROWS, group_chunks = GROUP_CHUNKS;
     __nv_bfloat16* sh_h = nullptr;
     float* sh_out = nullptr;
     uint32_t* status = nullptr;
@@ -163,10 +166,16 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
             if ((rc = h->alloc(&L.gu_code, (size_t)h->e_local * 2 * exl3_code_words(d) * 4))) return bail(rc);
             if ((rc = h->alloc(&L.d_code, (size_t)h->e_local * exl3_code_words(d) * 4))) return bail(rc);
             if ((rc = h->alloc(&L.scales, (size_t)h->e_local * exl3_scales_per_expert(d) * 2))) return bail(rc);
+        } else {
+            const int nv = c->bank_kind == MLXS_BANK_NVFP4;
+            if ((rc = h->alloc(&L.f4_gu, (size_t)h->e_local * fp4_stream_bytes_per_expert(c->hidden, c->inter, nv, 0)))) return bail(rc);
+            if ((rc = h->alloc(&L.f4_dn, (size_t)h->e_local * fp4_stream_bytes_per_expert(c->hidden, c->inter, nv, 1)))) return bail(rc);
+            if ((rc = h->alloc(&L.f4_gscale, (size_t)h->e_local * 3 * 4))) return bail(rc);
         }
     }
     const size_t T = c->max_tokens, A = T * c->top_k;
-    const uint32_t max_chunks = (uint32_t)(A / CHUNK_ROWS + (A < c->n_experts ? A : c->n_experts) + 1);
+    if (c->bank_kind != MLXS_BANK_EXL3_K3_MUL1) { h->chunk_rows = FP4_CHUNK_ROWS; h->group_chunks = FP4_GROUP_CHUNKS; }
+    const uint32_t max_chunks = (uint32_t)(A / h->chunk_rows + (A < c->n_experts ? A : c->n_experts) + 1);
     h->tabs.max_chunks = max_chunks;
     if ((rc = h->alloc(&h->ids_ws, A * 4)) || (rc = h->alloc(&h->w_ws, A * 4)) || (rc = h->alloc(&h->tabs.header, 64)) ||
         (rc = h->alloc(&h->tabs.offsets, (c->n_experts + 1) * 4)) || (rc = h->alloc(&h->tabs.order, A * 4)) ||
@@ -182,6 +191,10 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
         const size_t kmax = (H > I ? H : I) / 16;
         if ((rc = h->alloc(&h->xa_gu, (size_t)max_chunks * 2 * kmax * 256)) ||
             (rc = h->alloc(&h->xa_d, (size_t)max_chunks * kmax * 256)) || (rc = h->alloc(&h->ro, A * (H > I ? H : I) * 4)))
+            return bail(rc);
+    } else {
+        if ((rc = h->alloc(&h->xa_gu, (size_t)max_chunks * (H / 32) * 512)) ||
+            (rc = h->alloc(&h->xa_d, (size_t)max_chunks * (I / 32) * 512)) || (rc = h->alloc(&h->ro, A * H * 4)))
             return bail(rc);
     }
     if (c->shared_expert) {
@@ -231,7 +244,11 @@ extern "C" int mlxs_moe_load_expert(mlxs_moe* h, uint32_t layer, uint32_t expert
         CU(launch_exl3_repack(src, d, L.gu_code + (size_t)le * 2 * exl3_code_words(d),
                               L.d_code + (size_t)le * exl3_code_words(d), L.scales + (size_t)le * exl3_scales_per_expert(d), 0));
     } else {
-        return fail(MLXS_E_CONFIG, "load_expert: bank kind %u has no resident layout yet", h->cfg.bank_kind);
+        const int nv = h->cfg.bank_kind == MLXS_BANK_NVFP4;
+        CU(launch_fp4_repack(src, h->cfg.hidden, h->cfg.inter, nv,
+                             L.f4_gu + (size_t)le * fp4_stream_bytes_per_expert(h->cfg.hidden, h->cfg.inter, nv, 0),
+                             L.f4_dn + (size_t)le * fp4_stream_bytes_per_expert(h->cfg.hidden, h->cfg.inter, nv, 1),
+                             L.f4_gscale + (size_t)le * 3, 0));
     }
     const uint8_t one = 1;
     CU(cudaMemcpyAsync(L.loaded_dev + expert, &one, 1, cudaMemcpyHostToDevice, 0));
@@ -306,15 +323,15 @@ extern "C" int mlxs_moe_route(mlxs_moe* h, uint32_t layer, const float* logits_d
 }
 
 // dispatch + the bank's expert kernels -> ro (unweighted rows in assignment order)
-static int run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, uint32_t T, float* ro,
-                      cudaStream_t st) {
+static int run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, uint32_t T, void* ro,
+                      int ro_bf16, cudaStream_t st) {
     const mlxs_moe_config& c = h->cfg;
     LayerBank& L = h->layers[layer];
     const uint32_t A = T * c.top_k;
     if (c.ep_world != 1) return fail(MLXS_E_EP, "experts: expert-parallel exchange is not initialised");
     {
         StageTimer tm(h, MLXS_STAGE_DISPATCH, st);
-        CU(launch_dispatch(ids_dev, A, c.n_experts, L.loaded_dev, h->tabs, h->status, st));
+        CU(launch_dispatch(ids_dev, A, c.n_experts, L.loaded_dev, h->tabs, h->chunk_rows, h->group_chunks, h->status, st));
     }
     if (c.bank_kind == MLXS_BANK_EXL3_K3_MUL1) {
         const Exl3Dims d{c.hidden, c.inter};
@@ -324,7 +341,7 @@ static int run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int3
             CU(launch_exl3_prep_in(static_cast<const __nv_bfloat16*>(x_dev), c.top_k, EL, d, h->tabs, h->xa_gu, st));
         }
         Exl3GemvArgs a{};
-        a.L = EL; a.d = d; a.t = h->tabs; a.xa_gu = h->xa_gu; a.xa_d = h->xa_d; a.ro = ro; a.ro_bf16 = 0;
+        a.L = EL; a.d = d; a.t = h->tabs; a.xa_gu = h->xa_gu; a.xa_d = h->xa_d; a.ro = static_cast<float*>(ro); a.ro_bf16 = 0;
         a.limit = c.act == MLXS_ACT_SWIGLU_CLAMPED ? c.act_limit : 0.f;
         a.status = h->status; a.sm_count = h->sm_count;
         {
@@ -336,7 +353,23 @@ static int run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int3
             CU(launch_exl3_down(a, st));
         }
     } else {
-        return fail(MLXS_E_CONFIG, "experts: bank kind %u kernels are not built yet", c.bank_kind);
+        {
+            StageTimer tm(h, MLXS_STAGE_PREP, st);
+            CU(launch_fp4_prep(static_cast<const __nv_bfloat16*>(x_dev), c.top_k, c.hidden, h->tabs, h->xa_gu, st));
+        }
+        Fp4GemvArgs a{};
+        a.gu = L.f4_gu; a.dn = L.f4_dn; a.nv = c.bank_kind == MLXS_BANK_NVFP4; a.gscale = a.nv ? L.f4_gscale : nullptr;
+        a.H = c.hidden; a.I = c.inter; a.t = h->tabs; a.xa = h->xa_gu; a.xa_d = h->xa_d; a.ro = ro;
+        a.ro_bf16 = ro_bf16; a.limit = c.act == MLXS_ACT_SWIGLU_CLAMPED ? c.act_limit : 0.f;
+        a.status = h->status; a.sm_count = h->sm_count;
+        {
+            StageTimer tm(h, MLXS_STAGE_GATE_UP, st);
+            CU(launch_fp4_gemv(a, 0, st));
+        }
+        {
+            StageTimer tm(h, MLXS_STAGE_DOWN, st);
+            CU(launch_fp4_gemv(a, 1, st));
+        }
     }
     h->stats.expert_calls += 1;
     h->stats.tokens += T;
@@ -350,7 +383,7 @@ extern "C" int mlxs_moe_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, c
     if (rc) return rc;
     if (T == 0) return MLXS_OK;
     if (!x_dev || !ids_dev || !out_dev) return fail(MLXS_E_ARG, "routed: null buffer");
-    return run_routed(h, layer, x_dev, ids_dev, T, out_dev, (cudaStream_t)stream);
+    return run_routed(h, layer, x_dev, ids_dev, T, out_dev, 0, (cudaStream_t)stream);
 }
 
 extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev,
@@ -363,7 +396,9 @@ extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, 
     LayerBank& L = h->layers[layer];
     cudaStream_t st = (cudaStream_t)stream;
     if (c.shared_expert && !L.sh_w1) return fail(MLXS_E_NOT_LOADED, "experts: layer %u has no shared expert weights", layer);
-    if ((rc = run_routed(h, layer, x_dev, ids_dev, T, h->ro, st))) return rc;
+    // FP4 banks with the chain combine keep the routed rows in bf16, as the reference's down texts store them
+    const int ro_bf16 = c.bank_kind != MLXS_BANK_EXL3_K3_MUL1 && c.combine == MLXS_COMBINE_CHAIN;
+    if ((rc = run_routed(h, layer, x_dev, ids_dev, T, h->ro, ro_bf16, st))) return rc;
     const float* shared = nullptr;
     if (c.shared_expert) {
         StageTimer tm(h, MLXS_STAGE_SHARED, st);
@@ -372,7 +407,7 @@ extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, 
         shared = h->sh_out;
     }
     StageTimer tm(h, MLXS_STAGE_COMBINE, st);
-    CU(launch_combine(h->ro, 0, weights_dev, shared, T, c.top_k, c.hidden, c.combine == MLXS_COMBINE_CHAIN,
+    CU(launch_combine(h->ro, ro_bf16, weights_dev, shared, T, c.top_k, c.hidden, c.combine == MLXS_COMBINE_CHAIN,
                       static_cast<__nv_bfloat16*>(y_dev), st));
     return MLXS_OK;
 }
@@ -427,7 +462,7 @@ extern "C" int mlxs_moe_exl3_gemv(mlxs_moe* h, uint32_t layer, uint32_t expert, 
     const uint32_t le = expert - h->e_first;
     // rows all belong to one pseudo expert 0 of a one-expert dispatch
     CU(cudaMemsetAsync(h->ids_ws, 0, (size_t)rows * 4, st));
-    CU(launch_dispatch(h->ids_ws, rows, 1, nullptr, h->tabs, h->status, st));
+    CU(launch_dispatch(h->ids_ws, rows, 1, nullptr, h->tabs, CHUNK_ROWS, GROUP_CHUNKS, h->status, st));
     const uint32_t in_dim = proj == 2 ? c.inter : c.hidden, out_dim = proj == 2 ? c.hidden : c.inter;
     CU(launch_exl3_prep_raw(xh_dev, in_dim, h->tabs, h->xa_gu, st));
     const uint32_t* code = proj == 2 ? L.d_code + (size_t)le * exl3_code_words(d) : L.gu_code + (size_t)le * 2 * exl3_code_words(d);

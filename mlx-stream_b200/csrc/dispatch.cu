@@ -11,6 +11,7 @@ constexpr int DTHREADS = 1024;
 
 __global__ void __launch_bounds__(DTHREADS) dispatch_kernel(const int32_t* __restrict__ ids, uint32_t A, uint32_t E,
                                                             const uint8_t* __restrict__ loaded, DispatchTables t,
+                                                            uint32_t CHUNK_ROWS, uint32_t GROUP_CHUNKS,
                                                             uint32_t* status) {
     extern __shared__ uint32_t dsm[];
     uint32_t* cnt = dsm;                // [E] counts, then running write positions
@@ -63,12 +64,12 @@ __global__ void __launch_bounds__(DTHREADS) dispatch_kernel(const int32_t* __res
                 const uint32_t ch = chunk_base[e] + i;
                 t.chunk_expert[ch] = e;
                 t.chunk_row0[ch] = row0 + i * CHUNK_ROWS;
-                t.chunk_rows[ch] = min((uint32_t)CHUNK_ROWS, c - i * CHUNK_ROWS);
+                t.chunk_rows[ch] = min(CHUNK_ROWS, c - i * CHUNK_ROWS);
             }
             const uint32_t ng = (nc + GROUP_CHUNKS - 1) / GROUP_CHUNKS;
             for (uint32_t i = 0; i < ng; ++i) {
                 t.group_chunk0[group_base[e] + i] = chunk_base[e] + i * GROUP_CHUNKS;
-                t.group_mc[group_base[e] + i] = min((uint32_t)GROUP_CHUNKS, nc - i * GROUP_CHUNKS);
+                t.group_mc[group_base[e] + i] = min(GROUP_CHUNKS, nc - i * GROUP_CHUNKS);
             }
         }
     }
@@ -97,9 +98,9 @@ __global__ void __launch_bounds__(DTHREADS) dispatch_kernel(const int32_t* __res
 }
 
 cudaError_t launch_dispatch(const int32_t* ids, uint32_t A, uint32_t E, const uint8_t* loaded, DispatchTables t,
-                            uint32_t* status, cudaStream_t st) {
+                            uint32_t chunk_rows, uint32_t group_chunks, uint32_t* status, cudaStream_t st) {
     size_t smem = (size_t)(3 * E + 2 + DTHREADS) * sizeof(uint32_t);
-    dispatch_kernel<<<1, DTHREADS, smem, st>>>(ids, A, E, loaded, t, status);
+    dispatch_kernel<<<1, DTHREADS, smem, st>>>(ids, A, E, loaded, t, chunk_rows, group_chunks, status);
     return cudaGetLastError();
 }
 

@@ -30,8 +30,9 @@ cudaError_t launch_router(const float* logits, const float* bias, int T, int E, 
 
 // ids [A] (A = T*k) -> tables; expert ids outside [0, E) set *status and are treated as expert 0.
 // loaded: optional [E] bytes, 0 = expert not resident -> *status = ST_NOT_LOADED.
+// chunk_rows / group_chunks: rows per chunk and chunks per work item of the bank's kernels (EXL3 4 x 4, FP4 8 x 2)
 cudaError_t launch_dispatch(const int32_t* ids, uint32_t A, uint32_t E, const uint8_t* loaded, DispatchTables t,
-                            uint32_t* status, cudaStream_t st);
+                            uint32_t chunk_rows, uint32_t group_chunks, uint32_t* status, cudaStream_t st);
 
 // ---- EXL3 ----
 struct Exl3Layer {            // one layer's resident bank, in the kernels' layout
@@ -73,6 +74,36 @@ cudaError_t launch_exl3_down(const Exl3GemvArgs& a, cudaStream_t st);
 cudaError_t launch_exl3_raw(const uint32_t* code_e, uint32_t in_dim, uint32_t out_dim, uint32_t ktile_stride_words,
                             uint32_t proj_off_words, DispatchTables t, const uint32_t* xa, float* z, uint32_t* status,
                             int sm_count, cudaStream_t st);
+
+// ---- MXFP4 / NVFP4 ----
+constexpr int FP4_CHUNK_ROWS = 8;
+constexpr int FP4_GROUP_CHUNKS = 2;
+static inline size_t fp4_stream_bytes_per_expert(uint32_t H, uint32_t I, int nv, int down) {
+    const size_t per_stage = (size_t)(down ? 1 : 2) * (8192 + (nv ? 1024 : 512));
+    return (size_t)(H / 128) * (I / 128) * per_stage;
+}
+// record (device, reference layout) -> the expert's slices of the gate/up stream, the down stream and the global scales
+cudaError_t launch_fp4_repack(const uint8_t* record_dev, uint32_t H, uint32_t I, int nv, uint8_t* gu_e, uint8_t* dn_e,
+                              float* gscale_e, cudaStream_t st);
+// x bf16 [T, H] -> f16 rows in the kernels' B-fragment order: [chunk][H/32][128] u32
+cudaError_t launch_fp4_prep(const __nv_bfloat16* x, uint32_t top_k, uint32_t H, DispatchTables t, uint32_t* xa,
+                            cudaStream_t st);
+struct Fp4GemvArgs {
+    const uint8_t* gu;      // layer base, [E] x fp4_stream_bytes_per_expert(.., 0)
+    const uint8_t* dn;      // layer base, [E] x fp4_stream_bytes_per_expert(.., 1)
+    const float* gscale;    // NVFP4: [E][3], else null
+    int nv;
+    uint32_t H, I;
+    DispatchTables t;
+    const uint32_t* xa;     // [chunk][H/32][128]
+    uint32_t* xa_d;         // [chunk][I/32][128]
+    void* ro;               // [A, H] bf16 (chain combine) or f32
+    int ro_bf16;
+    float limit;
+    uint32_t* status;
+    int sm_count;
+};
+cudaError_t launch_fp4_gemv(const Fp4GemvArgs& a, int down, cudaStream_t st);
 
 // ---- shared expert (bf16 dense) + combine ----
 cudaError_t launch_shared_expert(const __nv_bfloat16* x, const __nv_bfloat16* w1, const __nv_bfloat16* w3,

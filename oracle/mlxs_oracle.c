@@ -589,12 +589,22 @@ void orc_mxfp4_synth_record(uint64_t seed, uint64_t hidden, uint64_t inter, doub
     }
 }
 static uint8_t e4m3_encode_pos(double v) { /* nearest non-negative finite E4M3, ties to the even byte */
+    if (!(v > 0)) return 0;
+    if (v >= 448.0) return 0x7E;
+    int ex;
+    frexp(v, &ex);            /* v = f 2^ex, f in [0.5, 1) -> binade exponent ex - 1 */
+    int e = ex - 1;
+    if (e < -6) e = -6;       /* subnormals share the 2^-6 binade: steps of 2^-9 */
+    double step = ldexp(1.0, e - 3);
+    double q = nearbyint(v / step); /* ties to even; consecutive bytes alternate parity */
+    double r = q * step;
     int best = 0;
-    double bd = 1e300;
-    for (int b = 0; b < 0x7F; ++b) {
-        double dd = fabs(v - (double)orc_e4m3_value((uint8_t)b));
-        if (dd < bd || (dd == bd && (b & 1) == 0)) { bd = dd; best = b; }
-    }
+    /* r is exactly representable: find its byte by the format's definition */
+    if (r >= 448.0) return 0x7E;
+    if (r < 0.015625) return (uint8_t)nearbyint(r * 512.0);
+    frexp(r, &ex);
+    e = ex - 1;
+    best = ((e + 7) << 3) | ((int)nearbyint(r / ldexp(1.0, e - 3)) - 8);
     return (uint8_t)best;
 }
 void orc_nvfp4_synth_record(uint64_t seed, uint64_t hidden, uint64_t inter, double sigma, uint8_t *rec) {

@@ -19,22 +19,26 @@ def torch_mod():
 
 
 class Exl3Case:
-    """A routed-MoE layer over an EXL3 bank, on the GPU and in the oracle."""
+    """A routed-MoE layer over one bank kind (EXL3 by default), on the GPU and in the oracle."""
+
+    bank = O.BANK_EXL3
 
     def __init__(self, hidden, inter, n_experts, top_k, seed=0, shared=True, scoring=None, max_tokens=64,
-                 experts_to_load=None, routed_scale=1.5, limit=10.0, device=0):
+                 experts_to_load=None, routed_scale=1.5, limit=10.0, device=0, chain=False):
         self.pkg = load_package()
         pkg = self.pkg
         torch = torch_mod()
         self.H, self.I, self.E, self.k = hidden, inter, n_experts, top_k
         self.limit = limit
+        self.chain = chain
         self.scoring = pkg.SCORE_SQRTSOFTPLUS if scoring is None else scoring
         self.routed_scale = routed_scale
         self.dev = torch.device("cuda", device)
-        cfg = pkg.make_config(hidden, inter, n_experts, top_k, n_layers=1, bank_kind=pkg.BANK_EXL3_K3_MUL1,
-                              act=pkg.ACT_SWIGLU_CLAMPED, act_limit=limit, scoring=self.scoring, norm_topk=True,
-                              routed_scale=routed_scale, shared_expert=shared, combine=pkg.COMBINE_F32,
-                              max_tokens=max_tokens, device=device)
+        cfg = pkg.make_config(hidden, inter, n_experts, top_k, n_layers=1, bank_kind=self.bank,
+                              act=pkg.ACT_SWIGLU_CLAMPED if limit > 0 else pkg.ACT_SWIGLU, act_limit=limit,
+                              scoring=self.scoring, norm_topk=True, routed_scale=routed_scale, shared_expert=shared,
+                              combine=pkg.COMBINE_CHAIN if chain else pkg.COMBINE_F32, max_tokens=max_tokens,
+                              device=device)
         self.moe = pkg.MoE(cfg)
         self.records = {}
         self.seed = seed
@@ -52,8 +56,11 @@ class Exl3Case:
     def record_seed(self, e):
         return 0x5EED0000 + 1000 * self.seed + 17 * e
 
+    def synth(self, e):
+        return O.exl3_synth_record(self.record_seed(e), self.H, self.I, 1.0, 0.02)
+
     def load(self, e):
-        rec = O.exl3_synth_record(self.record_seed(e), self.H, self.I, 1.0, 0.02)
+        rec = self.synth(e)
         self.records[e] = rec
         self.moe.load_expert(0, e, rec.ctypes.data, rec.size, on_device=False)
 
@@ -134,14 +141,30 @@ class Exl3Case:
         return O.route(logits, None, self.k, self.scoring, norm=True, scale=self.routed_scale, det=det)
 
     def cpu_layer(self, x, ids, weights, want_ro=False):
-        return O.layer(O.BANK_EXL3, self.H, self.I, self.E, self.k, self.records, x, ids, weights, shared=self.shared,
-                       limit=self.limit, want_ro=want_ro)
+        return O.layer(self.bank, self.H, self.I, self.E, self.k, self.records, x, ids, weights, shared=self.shared,
+                       limit=self.limit, chain_rounding=self.chain, shared_bf16_add=self.chain, want_ro=want_ro)
 
     def status(self):
         return self.moe.stats().device_status
 
     def close(self):
         self.moe.close()
+
+
+class Mxfp4Case(Exl3Case):
+    """MiMo-style bank: MXFP4 codes with E8M0 block scales, unclamped SwiGLU, chain combine."""
+    bank = O.BANK_MXFP4
+
+    def synth(self, e):
+        return O.mxfp4_synth_record(self.record_seed(e), self.H, self.I, 0.02)
+
+
+class Nvfp4Case(Exl3Case):
+    """GLM-Flash-style bank: NVFP4 codes with E4M3 block scales and a global scale, clamped SwiGLU, chain combine."""
+    bank = O.BANK_NVFP4
+
+    def synth(self, e):
+        return O.nvfp4_synth_record(self.record_seed(e), self.H, self.I, 0.02)
 
 
 def rel_l2(got, ref):
