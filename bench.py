@@ -31,6 +31,46 @@ sys.path.insert(0, str(ROOT / "tests"))
 H, I, E, K_TOP = 5120, 2304, 256, 8
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
+# secondary workloads (decode lines of BASELINE configs 3 and 4), selected with --workload
+WORKLOADS = {
+    "c2": dict(name="c2: DeepSeek-V4.1-Flash-shaped routed MoE decode layer, EXL3 K=3 mul1 bank", H=5120, I=2304, E=256,
+               k=8, bank="exl3", shared=True, scoring="sqrtsoftplus", scale=1.5, limit=10.0, chain=False),
+    "c3": dict(name="c3: MiMo-shaped routed MoE layer, MXFP4 bank", H=4096, I=2048, E=256, k=8, bank="mxfp4",
+               shared=False, scoring="softmax", scale=1.0, limit=0.0, chain=True),
+    "c4": dict(name="c4: GLM-shaped routed MoE layer, NVFP4 bank", H=6144, I=2048, E=256, k=8, bank="nvfp4",
+               shared=True, scoring="sigmoid", scale=1.0, limit=10.0, chain=True),
+}
+WL = WORKLOADS["c2"]
+
+
+def fp4_quantise_torch(torch, w, nv):
+    """Test tooling: N(0, sigma) weights -> packed FP4 parts on the device (codes u32 [rows, cols/8], scale bytes,
+    global scale).  MXFP4: OCP shared exponent floor(log2 amax) - 2; NVFP4: g = tensor amax, block scale =
+    e4m3(amax_block / (6 g / 2688)).  Nearest e2m1 by magnitude thresholds."""
+    rows, cols = w.shape
+    bs = 16 if nv else 32
+    blk = w.view(rows, cols // bs, bs)
+    amax = blk.abs().amax(dim=2, keepdim=True).clamp_min(1e-30)
+    if nv:
+        g = w.abs().max()
+        inv = g / 2688.0
+        t = (amax / (6.0 * inv)).clamp(max=448.0)
+        sc8 = t.to(torch.float8_e4m3fn)
+        scale = sc8.to(torch.float32) * inv
+        sbytes = sc8.view(torch.uint8).reshape(rows, cols // bs)
+        scale = scale.clamp_min(1e-30)
+    else:
+        ex = torch.floor(torch.log2(amax)) - 2
+        scale = torch.exp2(ex)
+        sbytes = (ex + 127).to(torch.uint8).reshape(rows, cols // bs)
+        g = None
+    v = blk / scale
+    th = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], device=w.device)
+    code = torch.bucketize(v.abs(), th).to(torch.int32) | ((v < 0).to(torch.int32) << 3)
+    code = code.view(rows, cols // 8, 8).to(torch.int64)
+    shifts = torch.arange(0, 32, 4, device=w.device, dtype=torch.int64)
+    words = ((code << shifts).sum(dim=2) & 0xFFFFFFFF).to(torch.int32)  # the low 32 bits, as a bit pattern
+    return words.contiguous(), sbytes.contiguous(), g
 
 
 def peaks():
@@ -134,8 +174,9 @@ def reference_arm(args):
 
 
 def workload_config(args, T):
-    return {"workload": "c2: DeepSeek-V4.1-Flash-shaped routed MoE decode layer, EXL3 K=3 mul1 bank",
-            "hidden": H, "inter": I, "n_experts": E, "top_k": K_TOP, "shared_expert": "bf16", "tokens_per_call": T,
+    return {"workload": WL["name"],
+            "hidden": H, "inter": I, "n_experts": E, "top_k": K_TOP, "shared_expert": "bf16" if WL["shared"] else "none",
+            "tokens_per_call": T,
             "routing": args.routing, "l2": "inputs larger than L2 (each call streams >2 GB of distinct expert code)",
             "parallelism": "single GPU" if args.gpus == 1 else f"ep{args.gpus}"}
 
@@ -150,9 +191,11 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=8)
     ap.add_argument("--routing", default="normal", choices=["normal", "zipf"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
-    ap.add_argument("--experts", type=int, default=E, help="routed experts (smaller only for profiler captures)")
+    ap.add_argument("--experts", type=int, default=0, help="routed experts (smaller only for profiler captures)")
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     args = ap.parse_args()
-    globals()["E"] = args.experts
+    wl = WORKLOADS[args.workload]
+    globals().update(WL=wl, H=wl["H"], I=wl["I"], E=args.experts or wl["E"], K_TOP=wl["k"])
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
     if args.impl == "reference":
         args.steps = min(args.steps, 3)
@@ -173,29 +216,63 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     T = args.tokens
 
-    cfg = pkg.make_config(H, I, E, K_TOP, n_layers=1, bank_kind=pkg.BANK_EXL3_K3_MUL1, act=pkg.ACT_SWIGLU_CLAMPED,
-                          act_limit=10.0, scoring=pkg.SCORE_SQRTSOFTPLUS, norm_topk=True, routed_scale=1.5,
-                          shared_expert=True, combine=pkg.COMBINE_F32, max_tokens=max(T, 64), device=local)
+    bank_kind = {"exl3": pkg.BANK_EXL3_K3_MUL1, "mxfp4": pkg.BANK_MXFP4, "nvfp4": pkg.BANK_NVFP4}[WL["bank"]]
+    scoring = {"sqrtsoftplus": pkg.SCORE_SQRTSOFTPLUS, "sigmoid": pkg.SCORE_SIGMOID, "softmax": pkg.SCORE_SOFTMAX}[WL["scoring"]]
+    cfg = pkg.make_config(H, I, E, K_TOP, n_layers=1, bank_kind=bank_kind,
+                          act=pkg.ACT_SWIGLU_CLAMPED if WL["limit"] > 0 else pkg.ACT_SWIGLU, act_limit=WL["limit"],
+                          scoring=scoring, norm_topk=True, routed_scale=WL["scale"], shared_expert=WL["shared"],
+                          combine=pkg.COMBINE_CHAIN if WL["chain"] else pkg.COMBINE_F32, max_tokens=max(T, 64),
+                          device=local, ep_world=world, ep_rank=rank)
     moe = pkg.MoE(cfg)
+    if world > 1:
+        # expert parallel: experts sharded E/N per rank; the NCCL id of the library's own communicator travels through
+        # torch.distributed
+        idt = torch.zeros(128, dtype=torch.uint8, device=dev)
+        if rank == 0:
+            buf = (C.c_char * 128)()
+            if pkg.lib().mlxs_moe_ep_unique_id(buf) != 0:
+                raise SystemExit("bench.py: " + pkg.last_error())
+            idt.copy_(torch.frombuffer(bytearray(bytes(buf)), dtype=torch.uint8))
+        dist.broadcast(idt, 0)
+        if pkg.lib().mlxs_moe_ep_init(moe._h, bytes(idt.cpu().numpy().tobytes())) != 0:
+            raise SystemExit("bench.py: " + pkg.last_error())
+    e_lo, e_hi = rank * (E // world), (rank + 1) * (E // world)
     logical, stride = moe.record_bytes()
-    # synthetic bank generated on the device in the reference's record layout: random trellis codes, +-(0.5+u) scales
     g = torch.Generator(device=dev)
     g.manual_seed(1000 + rank)
     code_bytes = (H // 16) * (I // 16) * 96
-    for e in range(E):
-        rec = torch.randint(0, 256, (stride,), dtype=torch.uint8, device=dev, generator=g)
-        off = 0
-        for p in range(3):
-            off += code_bytes
-            n_out, n_in = (H, I) if p == 2 else (I, H)
-            for n, sc in ((n_out, 0.02), (n_in, 1.0)):
-                u = torch.rand(n, device=dev, generator=g)
-                sgn = torch.where(torch.rand(n, device=dev, generator=g) < 0.5, -1.0, 1.0)
-                rec[off:off + 2 * n] = ((0.5 + u) * sgn * sc).to(torch.float16).view(torch.uint8)
-                off += 2 * n
-        moe.load_expert(0, e, rec.data_ptr(), stride, on_device=True)
-    sw = [(torch.randn(s, device=dev, generator=g) * 0.02).to(torch.bfloat16) for s in ((I, H), (I, H), (H, I))]
-    moe.set_shared(0, sw[0].data_ptr(), sw[1].data_ptr(), sw[2].data_ptr(), on_device=True)
+    if WL["bank"] == "exl3":
+        # synthetic bank generated on the device in the reference's record layout: random trellis codes, +-(0.5+u) scales
+        for e in range(e_lo, e_hi):
+            rec = torch.randint(0, 256, (stride,), dtype=torch.uint8, device=dev, generator=g)
+            off = 0
+            for p in range(3):
+                off += code_bytes
+                n_out, n_in = (H, I) if p == 2 else (I, H)
+                for n, sc in ((n_out, 0.02), (n_in, 1.0)):
+                    u = torch.rand(n, device=dev, generator=g)
+                    sgn = torch.where(torch.rand(n, device=dev, generator=g) < 0.5, -1.0, 1.0)
+                    rec[off:off + 2 * n] = ((0.5 + u) * sgn * sc).to(torch.float16).view(torch.uint8)
+                    off += 2 * n
+            moe.load_expert(0, e, rec.data_ptr(), stride, on_device=True)
+    else:
+        nv = WL["bank"] == "nvfp4"
+        for e in range(e_lo, e_hi):
+            parts = []
+            for p in range(3):
+                rows, cols = (H, I) if p == 2 else (I, H)
+                w = torch.randn((rows, cols), device=dev, generator=g) * 0.02
+                words, sbytes, gs = fp4_quantise_torch(torch, w, nv)
+                parts += [words.view(torch.uint8).reshape(-1), sbytes.reshape(-1)]
+                if nv:
+                    parts.append(gs.to(torch.float32).reshape(1).view(torch.uint8))
+            rec = torch.cat(parts)
+            assert rec.numel() == logical, (rec.numel(), logical)
+            moe.load_expert(0, e, rec.data_ptr(), rec.numel(), on_device=True)
+    sw = None
+    if WL["shared"]:
+        sw = [(torch.randn(s, device=dev, generator=g) * 0.02).to(torch.bfloat16) for s in ((I, H), (I, H), (H, I))]
+        moe.set_shared(0, sw[0].data_ptr(), sw[1].data_ptr(), sw[2].data_ptr(), on_device=True)
 
     rng = np.random.default_rng(99 + rank)
     n_batches = 4  # rotate a few seeded batches so consecutive steps route differently
@@ -262,31 +339,40 @@ def main():
         raise SystemExit(f"bench.py: device status {st.device_status}")
 
     mean_distinct = sum(distinct[i % n_batches] for i in range(args.steps)) / args.steps
-    gu_bytes = 2 * code_bytes + 2 * (2 * I + 2 * H)  # one expert's gate + up code and sign/scale vectors
+    if WL["bank"] == "exl3":
+        gu_bytes = 2 * code_bytes + 2 * (2 * I + 2 * H)  # one expert's gate + up code and sign/scale vectors
+        kname = "exl3_gemv_kernel<2,gate_up>"
+    else:
+        gu_bytes = 2 * (H * I // 2 + H * I // (16 if WL["bank"] == "nvfp4" else 32))  # gate + up codes and block scales
+        kname = "fp4_gemv_kernel<2>"
     gu_ms, gu_n = prof["gate_up"]
     peak, which = peaks()
     achieved = mean_distinct * gu_bytes / (gu_ms / max(gu_n, 1) * 1e-3) / 1e9
-    layer_bytes = mean_distinct * logical + 3 * H * I * 2 + T * H * 2 * 2 + T * E * 4
+    layer_bytes = mean_distinct * logical + (3 * H * I * 2 if WL["shared"] else 0) + T * H * 2 * 2 + T * E * 4
     value = world * T * args.steps / (ms * 1e-3)
     out = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f16 trellis weights x f16 hi/lo activations, f32 accumulate", "data": "synthetic",
+        "dtype": "f16 decoded weights x f16 activations (hi/lo split for EXL3), f32 accumulate", "data": "synthetic",
         "config": workload_config(args, T),
         "layer_hbm": {"algorithmic_bytes_per_call": layer_bytes, "gb_s": layer_bytes / (ms / args.steps * 1e-3) / 1e9,
                       "frac_of_measured_peak": layer_bytes / (ms / args.steps * 1e-3) / 1e9 / peak,
                       "frac_of_nominal_8000": layer_bytes / (ms / args.steps * 1e-3) / 1e9 / 8000.0,
                       "distinct_experts_mean": mean_distinct},
-        "roofline": {"kernel": "exl3_gemv_kernel<2,gate_up>", "bound": "hbm", "achieved": achieved, "peak": peak,
+        "roofline": {"kernel": kname, "bound": "hbm", "achieved": achieved, "peak": peak,
                      "peak_source": which, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
                      "algorithmic_bytes_per_launch": mean_distinct * gu_bytes},
         "stage_ms_per_step": {k: v[0] / max(args.steps, 1) for k, v in prof.items() if v[1]},
         "e2e": {"value": world * T * args.steps / (ms_host * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": T * H * 2 + T * E * 4, "d2h_bytes_per_step": T * H * 2 + 4},
-        "gpu_launches": 8 * args.steps,
+        "gpu_launches": ((8 if WL["shared"] else 6) + (4 if world > 1 else 0)) * args.steps,
+        "exchange": None if world == 1 else {
+            "exposed_ms_per_step": prof["exchange"][0] / max(args.steps, 1),
+            "bytes_sent_per_step_rank0": st.a2a_bytes_sent / max(st.expert_calls, 1),
+            "note": "dispatch + combine all-to-all (NCCL send/recv) incl. the count exchange and its host read"},
         "clocks": clocks,
     }
-    if rank == 0 and world == 1 and not args.no_cpu:
+    if rank == 0 and world == 1 and not args.no_cpu and WL["bank"] == "exl3":
         import oracle_lib as O
         Tc = args.cpu_tokens
         crng = np.random.default_rng(1234)

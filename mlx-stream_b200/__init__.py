@@ -10,7 +10,7 @@ Pointers are plain integers (device or host addresses); nothing here touches tor
 the library is missing or the machine has no CUDA device the calls raise.
 """
 import ctypes as C
-from pathlib import Path
+from pathlib import Path  # noqa: E402
 
 HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "libmlxs_moe.so"

@@ -43,65 +43,7 @@ int mlxs_fail(int rc, const char* fmt, ...) {
         if (e__ != cudaSuccess) return fail(MLXS_E_CUDA, "%s: %s", #call, cudaGetErrorString(e__));     \
     } while (0)
 
-struct LayerBank {
-    uint32_t* gu_code = nullptr;
-    uint32_t* d_code = nullptr;
-    __half* scales = nullptr;
-    uint8_t *f4_gu = nullptr, *f4_dn = nullptr;  // FP4 banks: the two streams
-    float* f4_gscale = nullptr;                  // NVFP4 [E_local][3]
-    uint8_t* loaded_dev = nullptr;  // [E] 1 = resident on this rank
-    std::vector<uint8_t> loaded;
-    float* bias = nullptr;          // [E] or null
-    __nv_bfloat16 *sh_w1 = nullptr, *sh_w3 = nullptr, *sh_w2 = nullptr;
-};
-
-struct mlxs_moe {
-    mlxs_moe_config cfg{};
-    int sm_count = 0;
-    uint32_t e_local = 0, e_first = 0;
-    uint64_t logical_bytes = 0, record_stride = 0;
-    std::vector<LayerBank> layers;
-    std::vector<void*> allocs;
-    uint64_t resident = 0;
-    // workspaces
-    int32_t* ids_ws = nullptr;
-    float* w_ws = nullptr;
-    DispatchTables tabs{};
-    uint32_t* xa_gu = nullptr;
-    uint32_t* xa_d = nullptr;
-    float* ro = nullptr;
-    uint32_t chunk_rows = CHUNK_ROWS, group_chunks = GROUP_CHUNKS;
-    __nv_bfloat16* sh_h = nullptr;
-    float* sh_out = nullptr;
-    uint32_t* status = nullptr;
-    uint8_t* staging = nullptr;
-    void *x_io = nullptr, *y_io = nullptr;
-    float* logits_io = nullptr;
-    mlxs_moe_stats stats{};
-    // per-stage timing (off by default)
-    bool prof_on = false;
-    struct Span { int stage; cudaEvent_t a, b; };
-    std::vector<Span> spans;
-    std::vector<cudaEvent_t> ev_pool;
-    mlxs_moe_profile prof{};
-    cudaEvent_t ev_get() {
-        if (!ev_pool.empty()) { cudaEvent_t e = ev_pool.back(); ev_pool.pop_back(); return e; }
-        cudaEvent_t e = nullptr;
-        cudaEventCreate(&e);
-        return e;
-    }
-
-    template <class T>
-    int alloc(T** p, size_t n_bytes) {
-        void* q = nullptr;
-        cudaError_t e = cudaMalloc(&q, n_bytes ? n_bytes : 16);
-        if (e != cudaSuccess) return fail(MLXS_E_CUDA, "cudaMalloc(%zu): %s", n_bytes, cudaGetErrorString(e));
-        allocs.push_back(q);
-        resident += n_bytes;
-        *p = static_cast<T*>(q);
-        return 0;
-    }
-};
+#include "handle.h"
 
 extern "C" int32_t mlxs_moe_abi(void) { return MLXS_MOE_ABI; }
 extern "C" const char* mlxs_moe_last_error(void) { return g_err.c_str(); }
@@ -173,7 +115,10 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
             if ((rc = h->alloc(&L.f4_gscale, (size_t)h->e_local * 3 * 4))) return bail(rc);
         }
     }
-    const size_t T = c->max_tokens, A = T * c->top_k;
+    const size_t T = c->max_tokens, A_call = T * c->top_k;
+    // with expert parallelism a rank may receive more rows than it routes: workspaces hold up to 4 x (or world x) its own
+    const size_t A = c->ep_world == 1 ? A_call : A_call * (c->ep_world < 4 ? c->ep_world : 4);
+    h->rows_cap = (uint32_t)A;
     if (c->bank_kind != MLXS_BANK_EXL3_K3_MUL1) { h->chunk_rows = FP4_CHUNK_ROWS; h->group_chunks = FP4_GROUP_CHUNKS; }
     const uint32_t max_chunks = (uint32_t)(A / h->chunk_rows + (A < c->n_experts ? A : c->n_experts) + 1);
     h->tabs.max_chunks = max_chunks;
@@ -209,6 +154,7 @@ extern "C" void mlxs_moe_destroy(mlxs_moe* h) {
     if (!h) return;
     cudaSetDevice(h->cfg.device);
     cudaDeviceSynchronize();
+    mlxs_ep_destroy(h);
     for (void* p : h->allocs) cudaFree(p);
     for (auto& s : h->spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
     for (auto e : h->ev_pool) cudaEventDestroy(e);
@@ -289,17 +235,6 @@ extern "C" int mlxs_moe_set_shared(mlxs_moe* h, uint32_t layer, const void* w1, 
     return MLXS_OK;
 }
 
-// brackets one stage's launches with events when profiling is on
-struct StageTimer {
-    mlxs_moe* h; cudaStream_t st; cudaEvent_t a = nullptr, b = nullptr; int stage;
-    StageTimer(mlxs_moe* h_, int stage_, cudaStream_t st_) : h(h_), st(st_), stage(stage_) {
-        if (h->prof_on) { a = h->ev_get(); b = h->ev_get(); cudaEventRecord(a, st); }
-    }
-    ~StageTimer() {
-        if (a) { cudaEventRecord(b, st); h->spans.push_back({stage, a, b}); }
-    }
-};
-
 static int check_call(mlxs_moe* h, uint32_t layer, uint32_t T, const char* who) {
     if (!h) return fail(MLXS_E_ARG, "%s: null handle", who);
     if (layer >= h->cfg.n_layers) return fail(MLXS_E_ARG, "%s: layer %u of %u", who, layer, h->cfg.n_layers);
@@ -323,22 +258,22 @@ extern "C" int mlxs_moe_route(mlxs_moe* h, uint32_t layer, const float* logits_d
 }
 
 // dispatch + the bank's expert kernels -> ro (unweighted rows in assignment order)
-static int run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, uint32_t T, void* ro,
-                      int ro_bf16, cudaStream_t st) {
+int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, uint32_t T, uint32_t top_k,
+                    uint32_t n_exp, uint32_t first, void* ro, int ro_bf16, cudaStream_t st) {
     const mlxs_moe_config& c = h->cfg;
     LayerBank& L = h->layers[layer];
-    const uint32_t A = T * c.top_k;
-    if (c.ep_world != 1) return fail(MLXS_E_EP, "experts: expert-parallel exchange is not initialised");
+    const uint32_t A = T * top_k;
+    if (A > h->rows_cap) return fail(MLXS_E_TOO_MANY_TOKENS, "experts: %u rows exceed the workspace's %u", A, h->rows_cap);
     {
         StageTimer tm(h, MLXS_STAGE_DISPATCH, st);
-        CU(launch_dispatch(ids_dev, A, c.n_experts, L.loaded_dev, h->tabs, h->chunk_rows, h->group_chunks, h->status, st));
+        CU(launch_dispatch(ids_dev, A, n_exp, L.loaded_dev + first, h->tabs, h->chunk_rows, h->group_chunks, h->status, st));
     }
     if (c.bank_kind == MLXS_BANK_EXL3_K3_MUL1) {
         const Exl3Dims d{c.hidden, c.inter};
         Exl3Layer EL{L.gu_code, L.d_code, L.scales};
         {
             StageTimer tm(h, MLXS_STAGE_PREP, st);
-            CU(launch_exl3_prep_in(static_cast<const __nv_bfloat16*>(x_dev), c.top_k, EL, d, h->tabs, h->xa_gu, st));
+            CU(launch_exl3_prep_in(static_cast<const __nv_bfloat16*>(x_dev), top_k, EL, d, h->tabs, h->xa_gu, st));
         }
         Exl3GemvArgs a{};
         a.L = EL; a.d = d; a.t = h->tabs; a.xa_gu = h->xa_gu; a.xa_d = h->xa_d; a.ro = static_cast<float*>(ro); a.ro_bf16 = 0;
@@ -355,7 +290,7 @@ static int run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int3
     } else {
         {
             StageTimer tm(h, MLXS_STAGE_PREP, st);
-            CU(launch_fp4_prep(static_cast<const __nv_bfloat16*>(x_dev), c.top_k, c.hidden, h->tabs, h->xa_gu, st));
+            CU(launch_fp4_prep(static_cast<const __nv_bfloat16*>(x_dev), top_k, c.hidden, h->tabs, h->xa_gu, st));
         }
         Fp4GemvArgs a{};
         a.gu = L.f4_gu; a.dn = L.f4_dn; a.nv = c.bank_kind == MLXS_BANK_NVFP4; a.gscale = a.nv ? L.f4_gscale : nullptr;
@@ -372,9 +307,17 @@ static int run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int3
         }
     }
     h->stats.expert_calls += 1;
-    h->stats.tokens += T;
     h->stats.assignments += A;
     return MLXS_OK;
+}
+
+// the routed rows of a call: local when the handle is one rank, through the exchange otherwise
+static int run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, uint32_t T, void* ro,
+                      int ro_bf16, cudaStream_t st) {
+    h->stats.tokens += T;
+    if (h->cfg.ep_world == 1)
+        return mlxs_run_routed(h, layer, x_dev, ids_dev, T, h->cfg.top_k, h->cfg.n_experts, 0, ro, ro_bf16, st);
+    return mlxs_ep_routed(h, layer, x_dev, ids_dev, T, ro, ro_bf16, st);
 }
 
 extern "C" int mlxs_moe_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, uint32_t T,
@@ -390,8 +333,8 @@ extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, 
                                 const float* weights_dev, uint32_t T, void* y_dev, void* stream) {
     int rc = check_call(h, layer, T, "experts");
     if (rc) return rc;
-    if (T == 0) return MLXS_OK;
-    if (!x_dev || !ids_dev || !weights_dev || !y_dev) return fail(MLXS_E_ARG, "experts: null buffer");
+    if (T == 0 && h->cfg.ep_world == 1) return MLXS_OK;  // with expert parallelism an empty rank still serves its peers
+    if (T && (!x_dev || !ids_dev || !weights_dev || !y_dev)) return fail(MLXS_E_ARG, "experts: null buffer");
     const mlxs_moe_config& c = h->cfg;
     LayerBank& L = h->layers[layer];
     cudaStream_t st = (cudaStream_t)stream;
@@ -454,7 +397,7 @@ extern "C" int mlxs_moe_exl3_gemv(mlxs_moe* h, uint32_t layer, uint32_t expert, 
     if (expert < h->e_first || expert >= h->e_first + h->e_local || !h->layers[layer].loaded[expert])
         return fail(MLXS_E_NOT_LOADED, "exl3_gemv: expert %u of layer %u is not resident on this rank", expert, layer);
     if (rows == 0) return MLXS_OK;
-    if (rows > c.max_tokens * c.top_k) return fail(MLXS_E_TOO_MANY_TOKENS, "exl3_gemv: %u rows exceed the workspace", rows);
+    if (rows > h->rows_cap) return fail(MLXS_E_TOO_MANY_TOKENS, "exl3_gemv: %u rows exceed the workspace", rows);
     CU(cudaSetDevice(c.device));
     cudaStream_t st = (cudaStream_t)stream;
     LayerBank& L = h->layers[layer];
@@ -519,12 +462,4 @@ extern "C" int mlxs_moe_ep_plan(const int32_t* ids, uint64_t n, uint32_t n_exper
         send_counts[(uint32_t)ids[i] / per] += 1;
     }
     return MLXS_OK;
-}
-extern "C" int mlxs_moe_ep_unique_id(void* id128_out) {
-    (void)id128_out;
-    return fail(MLXS_E_EP, "ep_unique_id: the exchange is not built in this version");
-}
-extern "C" int mlxs_moe_ep_init(mlxs_moe* h, const void* id128) {
-    (void)h; (void)id128;
-    return fail(MLXS_E_EP, "ep_init: the exchange is not built in this version");
 }

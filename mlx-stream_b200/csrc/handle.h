@@ -1,0 +1,99 @@
+// The handle behind include/mlxs_moe.h (internal).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <vector>
+
+#include "../../include/mlxs_moe.h"
+#include "kernels.h"
+
+using namespace mlxs;
+
+int mlxs_fail(int rc, const char* fmt, ...);  // sets the thread's last-error text, returns rc
+
+struct EpState;  // expert-parallel exchange (ep.cu)
+
+struct LayerBank {
+    uint32_t* gu_code = nullptr;
+    uint32_t* d_code = nullptr;
+    __half* scales = nullptr;
+    uint8_t *f4_gu = nullptr, *f4_dn = nullptr;  // FP4 banks: the two streams
+    float* f4_gscale = nullptr;                  // NVFP4 [E_local][3]
+    uint8_t* loaded_dev = nullptr;  // [E] 1 = resident on this rank
+    std::vector<uint8_t> loaded;
+    float* bias = nullptr;          // [E] or null
+    __nv_bfloat16 *sh_w1 = nullptr, *sh_w3 = nullptr, *sh_w2 = nullptr;
+};
+
+struct mlxs_moe {
+    mlxs_moe_config cfg{};
+    int sm_count = 0;
+    uint32_t e_local = 0, e_first = 0;
+    uint64_t logical_bytes = 0, record_stride = 0;
+    std::vector<LayerBank> layers;
+    std::vector<void*> allocs;
+    uint64_t resident = 0;
+    // workspaces
+    int32_t* ids_ws = nullptr;
+    float* w_ws = nullptr;
+    DispatchTables tabs{};
+    uint32_t* xa_gu = nullptr;
+    uint32_t* xa_d = nullptr;
+    float* ro = nullptr;
+    uint32_t chunk_rows = CHUNK_ROWS, group_chunks = GROUP_CHUNKS;
+    __nv_bfloat16* sh_h = nullptr;
+    float* sh_out = nullptr;
+    uint32_t* status = nullptr;
+    uint8_t* staging = nullptr;
+    void *x_io = nullptr, *y_io = nullptr;
+    float* logits_io = nullptr;
+    mlxs_moe_stats stats{};
+    EpState* ep = nullptr;
+    uint32_t rows_cap = 0;  // rows the expert kernels' workspaces hold (assignments of one call, or received rows)
+    // per-stage timing (off by default)
+    bool prof_on = false;
+    struct Span { int stage; cudaEvent_t a, b; };
+    std::vector<Span> spans;
+    std::vector<cudaEvent_t> ev_pool;
+    mlxs_moe_profile prof{};
+    cudaEvent_t ev_get() {
+        if (!ev_pool.empty()) { cudaEvent_t e = ev_pool.back(); ev_pool.pop_back(); return e; }
+        cudaEvent_t e = nullptr;
+        cudaEventCreate(&e);
+        return e;
+    }
+
+    template <class T>
+    int alloc(T** p, size_t n_bytes) {
+        void* q = nullptr;
+        cudaError_t e = cudaMalloc(&q, n_bytes ? n_bytes : 16);
+        if (e != cudaSuccess) return mlxs_fail(MLXS_E_CUDA, "cudaMalloc(%zu): %s", n_bytes, cudaGetErrorString(e));
+        allocs.push_back(q);
+        resident += n_bytes;
+        *p = static_cast<T*>(q);
+        return 0;
+    }
+};
+
+
+// brackets one stage's launches with events when profiling is on
+struct StageTimer {
+    mlxs_moe* h; cudaStream_t st; cudaEvent_t a = nullptr, b = nullptr; int stage;
+    StageTimer(mlxs_moe* h_, int stage_, cudaStream_t st_) : h(h_), st(st_), stage(stage_) {
+        if (h->prof_on) { a = h->ev_get(); b = h->ev_get(); cudaEventRecord(a, st); }
+    }
+    ~StageTimer() {
+        if (a) { cudaEventRecord(b, st); h->spans.push_back({stage, a, b}); }
+    }
+};
+
+// dispatch + the bank's expert kernels over `rows` = n_tok * top_k assignment rows with ids in [0, n_exp) indexing this
+// rank's resident experts from `first`: unweighted rows in assignment order into ro (api.cu)
+int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, uint32_t n_tok,
+                    uint32_t top_k, uint32_t n_exp, uint32_t first, void* ro, int ro_bf16, cudaStream_t st);
+// the expert-parallel form of the same (ep.cu): dispatch all-to-all, local experts, combine all-to-all
+int mlxs_ep_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, uint32_t T, void* ro,
+                   int ro_bf16, cudaStream_t st);
+void mlxs_ep_destroy(mlxs_moe* h);

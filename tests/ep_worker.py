@@ -1,0 +1,79 @@
+"""One rank of the 2-GPU expert-parallel parity test (started by tests/test_ep_gpu.py).
+
+argv: rank world rendezvous_dir.  Each rank owns half the experts, routes its own tokens, runs the layer through the
+library's exchange and checks its output rows against the CPU oracle over the whole bank."""
+import os
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+
+sys.path.insert(0, str(Path(__file__).resolve().parent))
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+
+def main():
+    rank, world, rdv = int(sys.argv[1]), int(sys.argv[2]), Path(sys.argv[3])
+    import torch
+
+    import oracle_lib as O
+    from __graft_entry__ import load_package
+    from moe_cases import rel_l2
+    pkg = load_package()
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    H, I, E, k, T = 512, 256, 8, 2, 12 + 5 * rank
+    cfg = pkg.make_config(H, I, E, k, bank_kind=pkg.BANK_EXL3_K3_MUL1, act=pkg.ACT_SWIGLU_CLAMPED, act_limit=10.0,
+                          scoring=pkg.SCORE_SQRTSOFTPLUS, routed_scale=1.5, shared_expert=True, max_tokens=32, device=rank,
+                          ep_world=world, ep_rank=rank)
+    moe = pkg.MoE(cfg)
+    records = {e: O.exl3_synth_record(0x5EED0000 + 17 * e, H, I, 1.0, 0.02) for e in range(E)}
+    for e, rec in records.items():
+        moe.load_expert(0, e, rec.ctypes.data, rec.size)  # the library keeps only this rank's shard
+    rng = np.random.default_rng(991)
+    shared = [O.f32_to_bf16_bits((rng.standard_normal(s) * 0.02).astype(np.float32)) for s in ((I, H), (I, H), (H, I))]
+    moe.set_shared(0, shared[0].ctypes.data, shared[1].ctypes.data, shared[2].ctypes.data)
+    # rendezvous through files: rank 0 publishes the NCCL id
+    idf = rdv / "nccl_id.bin"
+    if rank == 0:
+        buf = (pkg.C.c_char * 128)()
+        rc = pkg.lib().mlxs_moe_ep_unique_id(buf)
+        assert rc == 0, pkg.last_error()
+        (rdv / "nccl_id.tmp").write_bytes(bytes(buf))
+        os.rename(rdv / "nccl_id.tmp", idf)
+    t0 = time.time()
+    while not idf.exists():
+        if time.time() - t0 > 60:
+            raise SystemExit("rendezvous timed out")
+        time.sleep(0.05)
+    idb = idf.read_bytes()
+    rc = pkg.lib().mlxs_moe_ep_init(moe._h, idb)
+    assert rc == 0, pkg.last_error()
+    ok = True
+    for it in range(3):
+        rs = np.random.default_rng(100 * rank + it)
+        x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(rs.standard_normal((T, H)).astype(np.float32)))
+        logits = rs.standard_normal((T, E)).astype(np.float32)
+        if it == 2:
+            logits[:, :E // 2] += 8.0  # every token to rank 0's experts: rank 1 computes nothing, rank 0 everything
+        xd = torch.from_numpy(O.f32_to_bf16_bits(x).view(np.int16)).to(dev).view(torch.bfloat16)
+        lg = torch.from_numpy(logits).to(dev)
+        y = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+        moe.forward(0, xd.data_ptr(), lg.data_ptr(), T, y.data_ptr(), None)
+        torch.cuda.synchronize()
+        ids, w = O.route(logits, None, k, O.SCORE_SQRTSOFTPLUS, scale=1.5)
+        ref = O.layer(O.BANK_EXL3, H, I, E, k, records, x, ids, w, shared=shared, limit=10.0)
+        err = rel_l2(y.float().cpu().numpy(), ref)
+        print(f"rank {rank} iter {it} rel-L2 {err:.3e}", flush=True)
+        ok = ok and err < 1e-2
+    st = moe.stats()
+    print(f"rank {rank} status {st.device_status} a2a sent {st.a2a_bytes_sent} recv {st.a2a_bytes_recv}", flush=True)
+    ok = ok and st.device_status == 0 and st.a2a_bytes_sent > 0
+    moe.close()
+    print(f"rank {rank} {'OK' if ok else 'FAIL'}", flush=True)
+    sys.exit(0 if ok else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,112 @@
+"""The expert-parallel protocol on CPU ranks (gloo, world size 2): destination plan, row exchange, local experts,
+return and re-ordering, with the oracle as every rank's expert math.  The result must equal the single-rank oracle."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+HERE = Path(__file__).resolve().parent
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _rank(rank, world, port, q):
+    sys.path.insert(0, str(HERE))
+    sys.path.insert(0, str(HERE.parent))
+    import torch
+    import torch.distributed as dist
+
+    import oracle_lib as O
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    H, I, E, k, T = 256, 128, 8, 2, 5 + 2 * rank
+    e_local = E // world
+    records = {e: O.exl3_synth_record(0xABC0 + e, H, I, 1.0, 0.02) for e in range(E)}
+    rs = np.random.default_rng(10 + rank)
+    x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(rs.standard_normal((T, H)).astype(np.float32)))
+    logits = rs.standard_normal((T, E)).astype(np.float32)
+    ids, w = O.route(logits, None, k, O.SCORE_SIGMOID)
+    flat = ids.reshape(-1)
+    # the library's host-side plan: rows per destination rank
+    counts = np.zeros(world, np.uint64)
+    assert pkg.lib().mlxs_moe_ep_plan(flat.ctypes.data, flat.size, E, world, counts.ctypes.data) == 0
+    dest = flat // e_local
+    assert (np.bincount(dest, minlength=world) == counts).all()
+    order = np.argsort(dest, kind="stable")           # rows in destination order, routed order kept inside a rank
+    send_x = x[order // k]
+    send_meta = (flat[order] % e_local).astype(np.int32)
+    all_counts = [torch.zeros(world, dtype=torch.int64) for _ in range(world)]
+    dist.all_gather(all_counts, torch.from_numpy(counts.astype(np.int64)))
+    recv_n = [int(all_counts[s][rank]) for s in range(world)]
+    send_split = [int(c) for c in counts]
+    rx = [torch.zeros((n, H), dtype=torch.float32) for n in recv_n]
+    rm = [torch.zeros(n, dtype=torch.int32) for n in recv_n]
+    # pairwise exchange with exact counts, as the library's grouped send / recv does
+    reqs = []
+    sx, sm = torch.from_numpy(send_x).split(send_split), torch.from_numpy(send_meta).split(send_split)
+    for peer in range(world):
+        if peer == rank:
+            rx[peer].copy_(sx[peer]); rm[peer].copy_(sm[peer])
+        else:
+            reqs += [dist.isend(sx[peer].contiguous(), peer, tag=1), dist.isend(sm[peer].contiguous(), peer, tag=2),
+                     dist.irecv(rx[peer], peer, tag=1), dist.irecv(rm[peer], peer, tag=2)]
+    for r in reqs:
+        r.wait()
+    recv_x = torch.cat(rx).numpy()
+    recv_meta = torch.cat(rm).numpy()
+    # local experts: every received row is its own token with one expert (global id = first + local index)
+    R = recv_x.shape[0]
+    local_recs = {e: records[rank * e_local + e] for e in range(e_local)}
+    if R:
+        ro = O.layer(O.BANK_EXL3, H, I, e_local, 1, local_recs, recv_x, recv_meta.reshape(-1, 1),
+                     np.ones((R, 1), np.float32), limit=10.0)
+    else:
+        ro = np.zeros((0, H))
+    back = [torch.zeros((n, H), dtype=torch.float64) for n in send_split]
+    parts = torch.from_numpy(np.ascontiguousarray(ro)).split(recv_n)
+    reqs = []
+    for peer in range(world):
+        if peer == rank:
+            back[peer].copy_(parts[peer])
+        else:
+            reqs += [dist.isend(parts[peer].contiguous(), peer, tag=3), dist.irecv(back[peer], peer, tag=3)]
+    for r in reqs:
+        r.wait()
+    ret = torch.cat(back).numpy()
+    rows = np.empty((T * k, H))
+    rows[order] = ret
+    y = (rows.reshape(T, k, H) * w[:, :, None].astype(np.float64)).sum(axis=1)
+    ref = O.layer(O.BANK_EXL3, H, I, E, k, records, x, ids, w, limit=10.0)
+    err = float(np.abs(y - ref).max() / (np.abs(ref).max() + 1e-30))
+    dist.barrier()
+    dist.destroy_process_group()
+    q.put((rank, err, int(R)))
+
+
+def test_ep_protocol_world2_gloo():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(r[0] for r in res) == [0, 1]
+    for rank, err, R in res:
+        assert err < 1e-12, (rank, err)
+    assert sum(r[2] for r in res) == (5 + 7) * 2
