@@ -201,6 +201,9 @@ def main():
         args.steps = min(args.steps, 3)
         return reference_arm(args)
 
+    # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION/INFO; the contract is one JSON line
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO", "TRACE"):
+        os.environ["NCCL_DEBUG"] = "WARN"
     import torch
     import torch.distributed as dist
     from __graft_entry__ import load_package
