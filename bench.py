@@ -95,7 +95,7 @@ class ClockSampler:
              "clocks_event_reasons.sw_power_cap")
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                          "--format=csv,noheader,nounits", "-lms", "20"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
@@ -184,7 +184,7 @@ def workload_config(args, T):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--tokens", type=int, default=64)
@@ -345,12 +345,15 @@ def main():
     if WL["bank"] == "exl3":
         gu_bytes = 2 * code_bytes + 2 * (2 * I + 2 * H)  # one expert's gate + up code and sign/scale vectors
         kname = "exl3_gemv_kernel<2,gate_up>"
+        traffic_ratio = 1.017  # dram read+write / algorithmic bytes of the ncu capture on the small case (profiles/)
     else:
         gu_bytes = 2 * (H * I // 2 + H * I // (16 if WL["bank"] == "nvfp4" else 32))  # gate + up codes and block scales
         kname = "fp4_gemv_kernel<2>"
+        traffic_ratio = 1.003
     gu_ms, gu_n = prof["gate_up"]
     peak, which = peaks()
     achieved = mean_distinct * gu_bytes / (gu_ms / max(gu_n, 1) * 1e-3) / 1e9
+    prefill_lane = WL["bank"] == "exl3" and T * K_TOP >= 24 * (E // world) and T * K_TOP >= 2048
     layer_bytes = mean_distinct * logical + (3 * H * I * 2 if WL["shared"] else 0) + T * H * 2 * 2 + T * E * 4
     value = world * T * args.steps / (ms * 1e-3)
     out = {
@@ -363,7 +366,9 @@ def main():
                       "frac_of_nominal_8000": layer_bytes / (ms / args.steps * 1e-3) / 1e9 / 8000.0,
                       "distinct_experts_mean": mean_distinct},
         "roofline": {"kernel": kname, "bound": "hbm", "achieved": achieved, "peak": peak,
-                     "peak_source": which, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "peak_source": which, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": traffic_ratio * mean_distinct * gu_bytes,
+                     "traffic_note": "ncu dram bytes of a smaller case (64 experts, 16 tokens) scaled by distinct experts",
                      "algorithmic_bytes_per_launch": mean_distinct * gu_bytes},
         "stage_ms_per_step": {k: v[0] / max(args.steps, 1) for k, v in prof.items() if v[1]},
         "e2e": {"value": world * T * args.steps / (ms_host * 1e-3), "unit": UNIT,
@@ -375,6 +380,15 @@ def main():
             "note": "dispatch + combine all-to-all (NCCL send/recv) incl. the count exchange and its host read"},
         "clocks": clocks,
     }
+    if prefill_lane:
+        # prefill-sized call: the tcgen05 lane (gate/up and down launches are timed together); tensor roofline
+        pk = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+        tpeak = float(pk.get("bf16_tflops_sustained", 1400.0))
+        flops = 6.0 * H * I * T * K_TOP
+        tf = flops / (gu_ms / max(gu_n, 1) * 1e-3) / 1e12
+        out["roofline"] = {"kernel": "exl3_prefill_kernel<2> + <1> (tcgen05 kind::f16)", "bound": "tensor", "achieved": tf,
+                           "peak": tpeak, "peak_source": "measured sustained bf16" if pk else "fallback", "unit": "TFLOP/s",
+                           "frac": tf / tpeak, "traffic": None, "flops_per_launch_pair": flops}
     if rank == 0 and world == 1 and not args.no_cpu and WL["bank"] == "exl3":
         import oracle_lib as O
         Tc = args.cpu_tokens

@@ -5,6 +5,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -127,6 +128,7 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
         (rc = h->alloc(&h->tabs.chunk_expert, max_chunks * 4)) || (rc = h->alloc(&h->tabs.chunk_row0, max_chunks * 4)) ||
         (rc = h->alloc(&h->tabs.chunk_rows, max_chunks * 4)) || (rc = h->alloc(&h->tabs.group_chunk0, max_chunks * 4)) ||
         (rc = h->alloc(&h->tabs.group_mc, max_chunks * 4)) || (rc = h->alloc(&h->status, 16)) ||
+        (rc = h->alloc(&h->blk_cnt, (A / 1024 + 1) * (size_t)c->n_experts * 4)) ||
         (rc = h->alloc(&h->staging, h->record_stride)) || (rc = h->alloc(&h->x_io, T * H * 2)) ||
         (rc = h->alloc(&h->y_io, T * H * 2)) || (rc = h->alloc(&h->logits_io, T * c->n_experts * 4)))
         return bail(rc);
@@ -137,6 +139,13 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
         if ((rc = h->alloc(&h->xa_gu, (size_t)max_chunks * 2 * kmax * 256)) ||
             (rc = h->alloc(&h->xa_d, (size_t)max_chunks * kmax * 256)) || (rc = h->alloc(&h->ro, A * (H > I ? H : I) * 4)))
             return bail(rc);
+        if (A >= 2048) {  // prefill-sized calls are possible: staging for the tensor-core lane
+            h->pf_max_tiles = (uint32_t)(A / PREFILL_TILE_ROWS + h->e_local + 1);
+            if ((rc = h->alloc(&h->pf_tiles, (1 + 3 * (size_t)h->pf_max_tiles) * 4)) ||
+                (rc = h->alloc(&h->pf_xa, exl3_prefill_xa_bytes(d, h->pf_max_tiles))) ||
+                (rc = h->alloc(&h->pf_xd, exl3_prefill_xd_bytes(d, h->pf_max_tiles))))
+                return bail(rc);
+        }
     } else {
         if ((rc = h->alloc(&h->xa_gu, (size_t)max_chunks * (H / 32) * 512)) ||
             (rc = h->alloc(&h->xa_d, (size_t)max_chunks * (I / 32) * 512)) || (rc = h->alloc(&h->ro, A * H * 4)))
@@ -144,6 +153,10 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
     }
     if (c->shared_expert) {
         if ((rc = h->alloc(&h->sh_h, T * I * 2)) || (rc = h->alloc(&h->sh_out, T * H * 4))) return bail(rc);
+        if (T > 64) {
+            if ((rc = h->alloc(&h->sh_gu, 2 * T * I * 4))) return bail(rc);
+            if (shared_gemm_create(&h->sh_gemm)) return bail(fail(MLXS_E_CUDA, "create: cublasCreate failed"));
+        }
     }
     if (cudaDeviceSynchronize() != cudaSuccess) return bail(fail(MLXS_E_CUDA, "create: device synchronize failed"));
     *out = h;
@@ -155,6 +168,7 @@ extern "C" void mlxs_moe_destroy(mlxs_moe* h) {
     cudaSetDevice(h->cfg.device);
     cudaDeviceSynchronize();
     mlxs_ep_destroy(h);
+    shared_gemm_destroy(h->sh_gemm);
     for (void* p : h->allocs) cudaFree(p);
     for (auto& s : h->spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
     for (auto e : h->ev_pool) cudaEventDestroy(e);
@@ -266,9 +280,26 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
     if (A > h->rows_cap) return fail(MLXS_E_TOO_MANY_TOKENS, "experts: %u rows exceed the workspace's %u", A, h->rows_cap);
     {
         StageTimer tm(h, MLXS_STAGE_DISPATCH, st);
-        CU(launch_dispatch(ids_dev, A, n_exp, L.loaded_dev + first, h->tabs, h->chunk_rows, h->group_chunks, h->status, st));
+        if (A > 2048)
+            CU(launch_dispatch_large(ids_dev, A, n_exp, L.loaded_dev + first, h->tabs, h->chunk_rows, h->group_chunks,
+                                     h->blk_cnt, h->status, st));
+        else
+            CU(launch_dispatch(ids_dev, A, n_exp, L.loaded_dev + first, h->tabs, h->chunk_rows, h->group_chunks, h->status, st));
     }
-    if (c.bank_kind == MLXS_BANK_EXL3_K3_MUL1) {
+    // lane choice by rows per expert, as the reference decides on logical M (src/sdk_ext/quant.zig:5-6,
+    // src/arch/deepseek_v41/experts.zig:1545-1547): the tensor-core lane amortises one decode over up to 128 rows
+    static const int pf_min = [] { const char* v = getenv("MLXS_PREFILL_MIN_ROWS"); return v ? atoi(v) : 24; }();
+    const bool prefill_lane = c.bank_kind == MLXS_BANK_EXL3_K3_MUL1 && h->pf_tiles && A >= (uint32_t)pf_min * n_exp;
+    if (prefill_lane) {
+        const Exl3Dims d{c.hidden, c.inter};
+        Exl3PrefillArgs a{};
+        a.L = Exl3Layer{L.gu_code, L.d_code, L.scales}; a.d = d; a.t = h->tabs; a.n_experts = n_exp;
+        a.x = static_cast<const __nv_bfloat16*>(x_dev); a.top_k = top_k; a.tiles = h->pf_tiles; a.max_tiles = h->pf_max_tiles;
+        a.xa = h->pf_xa; a.xd = h->pf_xd; a.ro = static_cast<float*>(ro);
+        a.limit = c.act == MLXS_ACT_SWIGLU_CLAMPED ? c.act_limit : 0.f; a.status = h->status; a.sm_count = h->sm_count;
+        StageTimer tm(h, MLXS_STAGE_GATE_UP, st);
+        CU(launch_exl3_prefill(a, st));
+    } else if (c.bank_kind == MLXS_BANK_EXL3_K3_MUL1) {
         const Exl3Dims d{c.hidden, c.inter};
         Exl3Layer EL{L.gu_code, L.d_code, L.scales};
         {
@@ -345,8 +376,15 @@ extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, 
     const float* shared = nullptr;
     if (c.shared_expert) {
         StageTimer tm(h, MLXS_STAGE_SHARED, st);
-        CU(launch_shared_expert(static_cast<const __nv_bfloat16*>(x_dev), L.sh_w1, L.sh_w3, L.sh_w2, T, c.hidden, c.inter,
-                                c.act == MLXS_ACT_SWIGLU_CLAMPED ? c.act_limit : 0.f, h->sh_h, h->sh_out, st));
+        const float lim = c.act == MLXS_ACT_SWIGLU_CLAMPED ? c.act_limit : 0.f;
+        if (T > 64 && h->sh_gemm) {
+            if (launch_shared_expert_gemm(h->sh_gemm, static_cast<const __nv_bfloat16*>(x_dev), L.sh_w1, L.sh_w3, L.sh_w2, T,
+                                          c.hidden, c.inter, lim, h->sh_gu, h->sh_h, h->sh_out, st))
+                return fail(MLXS_E_CUDA, "experts: the shared expert's GEMMs failed");
+        } else {
+            CU(launch_shared_expert(static_cast<const __nv_bfloat16*>(x_dev), L.sh_w1, L.sh_w3, L.sh_w2, T, c.hidden, c.inter,
+                                    lim, h->sh_h, h->sh_out, st));
+        }
         shared = h->sh_out;
     }
     StageTimer tm(h, MLXS_STAGE_COMBINE, st);

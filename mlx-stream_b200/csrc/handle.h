@@ -39,11 +39,18 @@ struct mlxs_moe {
     int32_t* ids_ws = nullptr;
     float* w_ws = nullptr;
     DispatchTables tabs{};
+    uint32_t* blk_cnt = nullptr;  // per-block histograms of the multi-CTA dispatch
     uint32_t* xa_gu = nullptr;
     uint32_t* xa_d = nullptr;
     float* ro = nullptr;
+    // prefill lane (EXL3): row-tile table and operand staging, allocated when the handle can see prefill-sized calls
+    uint32_t* pf_tiles = nullptr;
+    __half *pf_xa = nullptr, *pf_xd = nullptr;
+    uint32_t pf_max_tiles = 0;
     uint32_t chunk_rows = CHUNK_ROWS, group_chunks = GROUP_CHUNKS;
     __nv_bfloat16* sh_h = nullptr;
+    float* sh_gu = nullptr;   // f32 [2][T, I] for the GEMM form of the shared expert
+    void* sh_gemm = nullptr;  // cuBLAS handle (plain dense GEMMs only)
     float* sh_out = nullptr;
     uint32_t* status = nullptr;
     uint8_t* staging = nullptr;

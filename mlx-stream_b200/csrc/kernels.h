@@ -34,6 +34,11 @@ cudaError_t launch_router(const float* logits, const float* bias, int T, int E, 
 cudaError_t launch_dispatch(const int32_t* ids, uint32_t A, uint32_t E, const uint8_t* loaded, DispatchTables t,
                             uint32_t chunk_rows, uint32_t group_chunks, uint32_t* status, cudaStream_t st);
 
+// the same over several CTAs for prefill-sized calls; blk_cnt: scratch [ceil(A/1024)][E]
+cudaError_t launch_dispatch_large(const int32_t* ids, uint32_t A, uint32_t E, const uint8_t* loaded, DispatchTables t,
+                                  uint32_t chunk_rows, uint32_t group_chunks, uint32_t* blk_cnt, uint32_t* status,
+                                  cudaStream_t st);
+
 // ---- EXL3 ----
 struct Exl3Layer {            // one layer's resident bank, in the kernels' layout
     const uint32_t* gu_code;  // [E][I/128][H/16][2][192] u32: per 128-wide output block, per k-tile, gate | up tiles
@@ -75,6 +80,28 @@ cudaError_t launch_exl3_raw(const uint32_t* code_e, uint32_t in_dim, uint32_t ou
                             uint32_t proj_off_words, DispatchTables t, const uint32_t* xa, float* z, uint32_t* status,
                             int sm_count, cudaStream_t st);
 
+// prefill-sized batches: tcgen05 MMA over trellis tiles decoded to f16 in shared memory (exl3_prefill.cu)
+constexpr int PREFILL_TILE_ROWS = 128;
+struct Exl3PrefillArgs {
+    Exl3Layer L;
+    Exl3Dims d;
+    DispatchTables t;
+    uint32_t n_experts;      // experts the dispatch ran over
+    const __nv_bfloat16* x;  // [tokens, H]
+    uint32_t top_k;
+    uint32_t* tiles;         // [1 + 3 max_tiles] row-tile table (device scratch)
+    uint32_t max_tiles;
+    __half* xa;              // [max_tiles][2][H/64][128 x 64] f16: rotated rows in the MMA's B-operand order
+    __half* xd;              // [max_tiles][I/64][128 x 64] f16
+    float* ro;               // [A, H]
+    float limit;
+    uint32_t* status;
+    int sm_count;
+};
+static inline size_t exl3_prefill_xa_bytes(Exl3Dims d, uint32_t max_tiles) { return (size_t)max_tiles * 2 * d.H * PREFILL_TILE_ROWS * 2; }
+static inline size_t exl3_prefill_xd_bytes(Exl3Dims d, uint32_t max_tiles) { return (size_t)max_tiles * d.I * PREFILL_TILE_ROWS * 2; }
+cudaError_t launch_exl3_prefill(const Exl3PrefillArgs& a, cudaStream_t st);
+
 // ---- MXFP4 / NVFP4 ----
 constexpr int FP4_CHUNK_ROWS = 8;
 constexpr int FP4_GROUP_CHUNKS = 2;
@@ -109,6 +136,12 @@ cudaError_t launch_fp4_gemv(const Fp4GemvArgs& a, int down, cudaStream_t st);
 cudaError_t launch_shared_expert(const __nv_bfloat16* x, const __nv_bfloat16* w1, const __nv_bfloat16* w3,
                                  const __nv_bfloat16* w2, uint32_t T, uint32_t H, uint32_t I, float limit,
                                  __nv_bfloat16* h_ws, float* out, cudaStream_t st);
+// the same at prefill widths: the three plain GEMMs through cuBLAS, our activation kernel between them
+int shared_gemm_create(void** handle);
+void shared_gemm_destroy(void* handle);
+int launch_shared_expert_gemm(void* handle, const __nv_bfloat16* x, const __nv_bfloat16* w1, const __nv_bfloat16* w3,
+                              const __nv_bfloat16* w2, uint32_t T, uint32_t H, uint32_t I, float limit, float* gu_ws,
+                              __nv_bfloat16* h_ws, float* out, cudaStream_t st);
 // y[t] = sum_k ro[t,k] w[t,k] (+ shared[t]) -> bf16
 cudaError_t launch_combine(const void* ro, int ro_bf16, const float* weights, const float* shared, uint32_t T,
                            uint32_t K, uint32_t H, int chain, __nv_bfloat16* y, cudaStream_t st);

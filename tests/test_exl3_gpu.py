@@ -190,3 +190,35 @@ def test_small_shape_layer_many_seeds():
         assert case.status() == 0
     finally:
         case.close()
+
+
+def test_prefill_lane_tcgen05():
+    """Prefill-sized calls take the tensor-core lane (rows per expert >= 24): f16-rounded rotated activations as the
+    reference's prefill chain (src/kernels/exl3/dsv41_prefill_dig_take2v_5120.metal:57-58), f32 accumulate."""
+    case = Exl3Case(512, 256, 4, 2, seed=12, shared=True, max_tokens=1024)
+    try:
+        rng = np.random.default_rng(5)
+        # ragged: expert 0 gets 129+ rows (two row tiles), expert 3 a handful, every row count class appears
+        T = 300
+        x, logits = case.inputs(T, seed=31)
+        logits[:, 0] += 3.0
+        logits[:, 3] -= 2.5
+        ids, w = case.cpu_route(logits)
+        counts = np.bincount(ids.reshape(-1), minlength=4)
+        assert counts.max() > 128 and counts.min() < 128
+        ref_y, ref_ro = case.cpu_layer(x, ids, w, want_ro=True)
+        ro = case.gpu_routed(x, ids)
+        assert case.status() == 0
+        assert max_err_over_rms(ro, ref_ro) < 4e-3  # f16 rounding of the two GEMM inputs
+        assert rel_l2(ro, ref_ro) < 1e-3
+        y = case.gpu_experts(x, ids, w)
+        assert rel_l2(y, ref_y) < TOL_LAYER
+        again = case.gpu_routed(x, ids)
+        assert (again.view(np.uint32) == ro.view(np.uint32)).all()
+        # a token's rows do not depend on the batch around it (same lane, other rows removed)
+        keep = np.arange(0, T, 2)
+        sub = case.gpu_routed(x[keep], ids[keep])
+        if np.bincount(ids[keep].reshape(-1), minlength=4).sum() >= 24 * 4:
+            assert (sub.view(np.uint32) == ro[keep].view(np.uint32)).all()
+    finally:
+        case.close()
