@@ -139,7 +139,7 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
         if ((rc = h->alloc(&h->xa_gu, (size_t)max_chunks * 2 * kmax * 256)) ||
             (rc = h->alloc(&h->xa_d, (size_t)max_chunks * kmax * 256)) || (rc = h->alloc(&h->ro, A * (H > I ? H : I) * 4)))
             return bail(rc);
-        if (A >= 2048) {  // prefill-sized calls are possible: staging for the tensor-core lane
+        if (A >= 2048 && exl3_prefill_supported(d)) {  // prefill-sized calls are possible: staging for the tensor-core lane
             h->pf_max_tiles = (uint32_t)(A / PREFILL_TILE_ROWS + h->e_local + 1);
             if ((rc = h->alloc(&h->pf_tiles, (1 + 3 * (size_t)h->pf_max_tiles) * 4)) ||
                 (rc = h->alloc(&h->pf_xa, exl3_prefill_xa_bytes(d, h->pf_max_tiles))) ||

@@ -46,10 +46,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait: gives up after `limit` polls (each poll itself blocks for a hardware-defined slice) or as soon as
 // *abort_flag is set by another thread of the CTA.  Returns false when it gave up.
+// sleep_ns > 0: back off between polls (the single-lane producer / MMA-issuer roles wait most of the time; polling
+// flat out would take issue slots from the warps that do the arithmetic).
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                                  uint32_t limit = (1u << 20)) {
+                                                  uint32_t sleep_ns = 0, uint32_t limit = (1u << 20)) {
     for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (sleep_ns) __nanosleep(sleep_ns);
         if ((i & 63u) == 63u && *abort_flag) return false;
     }
     return false;

@@ -233,7 +233,7 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
                                        (size_t)nb * P.nkt * P.kt_stride_words;
                 for (uint32_t kt0 = 0; kt0 < (last ? 1u : P.nkt); kt0 += KT, ++it) {
                     const uint32_t s = it % NS, ph = (it / NS) & 1u;
-                    if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, &s_abort)) {
+                    if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, &s_abort, 128)) {
                         if (!s_abort) atomicMax(P.status, (uint32_t)ST_WAIT_EMPTY);
                         s_abort = 1; ok = false; break;
                     }

@@ -2,9 +2,11 @@
 //
 // The reference's prefill lane (src/exl3/quant.zig:1040-1271; texts dsv41_prefill_dig_gemm_*_m128*.metal) decodes
 // trellis tiles to f16 in threadgroup memory per K stage and feeds its MMA units with f16 rotated activations and an
-// f32 accumulator.  Here the same roles map to Blackwell: a CTA owns (expert, 128 output columns, up to 128 of the
-// expert's rows).  W^T is the MMA's A operand (M = 128 output columns) and the rows are the B operand (N = rows rounded
-// to 16), so a ragged expert pads to 16 rows, not 128, and the accumulator D[128 columns x rows] sits in tensor memory.
+// f32 accumulator.  Here the same roles map to Blackwell: a CTA owns (expert, 256 output columns of gate and up | 512
+// of down, up to 128 of the expert's rows).  W^T is the MMA's A operand (M = 128 output columns per accumulator
+// group) and the rows are the B operand (N = rows rounded to 16), so a ragged expert pads to 16 rows, not 128, and the
+// four accumulator groups D[128 columns x rows] fill the SM's tensor memory (512 columns).  One staged copy of the rows
+// serves all four groups: the rows, not the weights, are what travels most through L2 in this lane.
 //   * a producer warp streams the raw code (bulk copies) and the rows' rotated f16 activations, which a prep kernel
 //     laid out in global memory in the K-major core-matrix order the MMA reads, so a stage is one contiguous copy;
 //   * decode warps (one per 16-column tile and projection) turn each 16x16 tile into f16 with the same in-register
@@ -22,20 +24,23 @@
 namespace mlxs {
 
 constexpr int PF_NT = 128;        // rows per tile (MMA N, rounded up to 16 per item)
-constexpr int PF_KS = 64;         // inputs per pipeline stage (4 k-tiles)
+constexpr int PF_KS = 32;         // inputs per pipeline stage (2 k-tiles)
+constexpr int PF_KT = PF_KS / 16; // k-tiles per stage
 constexpr int PF_RAW_STAGES = 4;  // raw code ring
 constexpr int PF_A_STAGES = 2;    // decoded-A ring (decode -> MMA is a short hop)
 constexpr int PF_B_STAGES = 4;    // B-operand ring: deep, the rows come through L2 with a long latency
-constexpr int PF_OP_BYTES = PF_NT * PF_KS * 2;  // one operand (128 x 64 f16) per projection per stage: 16 KB
-constexpr int PF_LBO = (PF_NT / 8) * 128;       // byte distance of two core matrices along K
+constexpr int PF_A_BYTES = 128 * PF_KS * 2;     // decoded W^T (128 columns x 32 inputs f16) per projection per stage: 8 KB
+constexpr int PF_B_BYTES = PF_NT * PF_KS * 2;   // rows (128 x 32 f16) per projection per stage: 8 KB
+constexpr int PF_LBO_A = (128 / 8) * 128;       // byte distance of two core matrices along K, A operand
+constexpr int PF_LBO_B = (PF_NT / 8) * 128;     // the same, B operand
 constexpr int PF_SBO = 128;                     // byte distance of two core matrices along M / N
 constexpr int PF_EPI_ROWS = 32;                 // rows per epilogue batch
 constexpr int PF_ZS_STRIDE = 132;
 
 // ---- tcgen05 wrappers ----
-__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr) {
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo) {
     // K-major, no swizzle: start address, leading (K) byte offset, stride (M/N) byte offset, all >> 4; version 1
-    return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((PF_LBO >> 4) & 0x3FFFu) << 16) |
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) |
            ((uint64_t)((PF_SBO >> 4) & 0x3FFFu) << 32) | (1ull << 46);
 }
 __device__ __forceinline__ uint32_t umma_idesc_f16(uint32_t n) {
@@ -86,10 +91,13 @@ __global__ void pf_plan_kernel(DispatchTables t, uint32_t E, uint32_t max_tiles,
     __syncthreads();
     if (base[E] == 0) return;
     for (uint32_t e = tid; e < E; e += blockDim.x) {
+        // an expert's rows are split evenly over its tiles (a 16-row remainder tile would cost a full decode)
         const uint32_t c = t.offsets[e + 1] - t.offsets[e], r0 = t.offsets[e];
-        for (uint32_t i = 0; i * PF_NT < c; ++i) {
+        const uint32_t nt = (c + PF_NT - 1) / PF_NT;
+        const uint32_t per = nt ? ((c + nt - 1) / nt + 15) / 16 * 16 : 0;
+        for (uint32_t i = 0; i < nt; ++i) {
             uint32_t* d = tiles + 1 + 3 * (base[e] + i);
-            d[0] = e; d[1] = r0 + i * PF_NT; d[2] = min((uint32_t)PF_NT, c - i * PF_NT);
+            d[0] = e; d[1] = r0 + i * per; d[2] = min(per, c - i * per);
         }
     }
 }
@@ -97,9 +105,9 @@ __global__ void pf_plan_kernel(DispatchTables t, uint32_t E, uint32_t max_tiles,
 // ------------------------------------------------------------------------------------------------------------
 // prep: rows -> rotated f16 activations in the MMA's B-operand order
 // ------------------------------------------------------------------------------------------------------------
-// xa[tile][proj][stage = k/64][kc = (k%64)/8][rc = row/8][row%8][k%8] f16
+// xa[tile][proj][stage = k/32][kc = (k%32)/8][rc = row/8][row%8][k%8] f16
 __device__ __forceinline__ size_t pf_xa_off(uint32_t nstage, uint32_t tile, uint32_t np, uint32_t p, uint32_t row, uint32_t k) {
-    return ((((size_t)tile * np + p) * nstage + k / PF_KS) * 8 + (k % PF_KS) / 8) * (PF_NT * 8) + (row / 8) * 64 + (row % 8) * 8 + k % 8;
+    return ((((size_t)tile * np + p) * nstage + k / PF_KS) * (PF_KS / 8) + (k % PF_KS) / 8) * (PF_NT * 8) + (row / 8) * 64 + (row % 8) * 8 + k % 8;
 }
 __global__ void __launch_bounds__(256) pf_prep_kernel(const __nv_bfloat16* __restrict__ x, uint32_t top_k, uint32_t H,
                                                       const __half* __restrict__ scales, size_t scales_stride,
@@ -155,25 +163,27 @@ struct PfParams {
     uint32_t* status;
 };
 
-template <int NPROJ>
-__global__ void __launch_bounds__(NPROJ * 256 + 64, 1) exl3_prefill_kernel(const PfParams P) {
+// NPROJ projections x CB adjacent 128-column blocks = 4 accumulator groups of 128 TMEM columns each
+template <int NPROJ, int CB>
+__global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParams P) {
+    static_assert(NPROJ * CB == 4, "four accumulator groups fill the 512 tensor-memory columns at 128 rows");
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    constexpr int NCW = NPROJ * 8;
-    constexpr int KSTRIDE = NPROJ * 192;               // words per k-tile in the code stream
-    constexpr int RAW_BYTES = 4 * KSTRIDE * 4;         // 4 k-tiles per stage
-    constexpr int TMEM_COLS = NPROJ * PF_NT;
+    constexpr int NCW = 16;                            // decode warps
+    constexpr int NG = NPROJ * CB;                     // accumulator groups
+    constexpr int KSTRIDE = NPROJ * 192;               // words per k-tile in one block's code stream
+    constexpr int RAW_BLK = PF_KT * KSTRIDE * 4;       // bytes of one block's k-tiles of a stage
+    constexpr int RAW_BYTES = CB * RAW_BLK;
+    constexpr int TMEM_COLS = NG * PF_NT;
     __shared__ __align__(8) uint64_t raw_full[PF_RAW_STAGES], raw_empty[PF_RAW_STAGES];
     __shared__ __align__(8) uint64_t b_full[PF_B_STAGES], b_empty[PF_B_STAGES], a_full[PF_A_STAGES], a_empty[PF_A_STAGES];
     __shared__ __align__(8) uint64_t acc_full, acc_empty, epi_bar;
     __shared__ uint32_t s_tmem;
     __shared__ volatile int s_abort;
-    // carve: [A ring, aliased by the epilogue staging zs][B ring][raw ring].  zs is only touched between acc_full (all
-    // of the item's MMAs have completed, so the A ring is idle) and the epilogue's closing rendezvous.
+    // carve: [A ring: NG groups per stage][B ring: NPROJ operands per stage][raw ring][epilogue staging zs]
     uint8_t* a_ring = smem_raw;
-    uint8_t* b_ring = a_ring + PF_A_STAGES * NPROJ * PF_OP_BYTES;
-    uint8_t* raw_ring = b_ring + PF_B_STAGES * NPROJ * PF_OP_BYTES;
-    float* zs = reinterpret_cast<float*>(a_ring);
-    static_assert(NPROJ * PF_EPI_ROWS * PF_ZS_STRIDE * sizeof(float) <= (size_t)PF_A_STAGES * NPROJ * PF_OP_BYTES, "zs fits the A ring");
+    uint8_t* b_ring = a_ring + PF_A_STAGES * NG * PF_A_BYTES;
+    uint8_t* raw_ring = b_ring + PF_B_STAGES * NPROJ * PF_B_BYTES;
+    float* zs = reinterpret_cast<float*>(raw_ring + PF_RAW_STAGES * RAW_BYTES);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
 
     if (threadIdx.x == 0) {
@@ -195,8 +205,9 @@ __global__ void __launch_bounds__(NPROJ * 256 + 64, 1) exl3_prefill_kernel(const
     tc_fence_after();
     const uint32_t tmem = s_tmem;
     const uint32_t n_tiles = P.tiles[0];
-    const uint32_t n_items = n_tiles * P.n_blocks;
-    const uint32_t nstage = P.nkt / 4;
+    const uint32_t nbg = P.n_blocks / CB;              // column-block groups per row tile
+    const uint32_t n_items = n_tiles * nbg;
+    const uint32_t nstage = P.nkt / PF_KT;
     auto give_up = [&](uint32_t code) { if (!s_abort) atomicMax(P.status, code); s_abort = 1; };
 
     if (warp == NCW) {
@@ -204,19 +215,21 @@ __global__ void __launch_bounds__(NPROJ * 256 + 64, 1) exl3_prefill_kernel(const
         if (lane == 0) {
             uint32_t rit = 0, bit = 0;
             for (uint32_t item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
-                const uint32_t tile = item / P.n_blocks, nb = item % P.n_blocks, expert = P.tiles[1 + 3 * tile];
-                const uint32_t* wsrc = P.code + (size_t)expert * P.expert_stride_words + (size_t)nb * P.nkt * KSTRIDE;
+                const uint32_t tile = item / nbg, nb0 = (item % nbg) * CB, expert = P.tiles[1 + 3 * tile];
+                const uint32_t* wsrc = P.code + (size_t)expert * P.expert_stride_words + (size_t)nb0 * P.nkt * KSTRIDE;
                 for (uint32_t ks = 0; ks < nstage; ++ks, ++rit, ++bit) {
                     const uint32_t rs = rit % PF_RAW_STAGES, rph = (rit / PF_RAW_STAGES) & 1u;
-                    if (!mbar_wait_bounded(&raw_empty[rs], rph ^ 1u, &s_abort)) { give_up(ST_WAIT_EMPTY); break; }
+                    if (!mbar_wait_bounded(&raw_empty[rs], rph ^ 1u, &s_abort, 128)) { give_up(ST_WAIT_EMPTY); break; }
                     mbar_expect_tx(&raw_full[rs], RAW_BYTES);
-                    bulk_g2s(raw_ring + rs * RAW_BYTES, wsrc + (size_t)ks * 4 * KSTRIDE, RAW_BYTES, &raw_full[rs]);
+                    for (int cb = 0; cb < CB; ++cb)
+                        bulk_g2s(raw_ring + rs * RAW_BYTES + cb * RAW_BLK,
+                                 wsrc + (size_t)cb * P.nkt * KSTRIDE + (size_t)ks * PF_KT * KSTRIDE, RAW_BLK, &raw_full[rs]);
                     const uint32_t bs = bit % PF_B_STAGES, bph = (bit / PF_B_STAGES) & 1u;
-                    if (!mbar_wait_bounded(&b_empty[bs], bph ^ 1u, &s_abort)) { give_up(ST_WAIT_EMPTY); break; }
-                    mbar_expect_tx(&b_full[bs], NPROJ * PF_OP_BYTES);
+                    if (!mbar_wait_bounded(&b_empty[bs], bph ^ 1u, &s_abort, 128)) { give_up(ST_WAIT_EMPTY); break; }
+                    mbar_expect_tx(&b_full[bs], NPROJ * PF_B_BYTES);
                     for (int p = 0; p < NPROJ; ++p)
-                        bulk_g2s(b_ring + (bs * NPROJ + p) * PF_OP_BYTES,
-                                 P.xa + (((size_t)tile * NPROJ + p) * nstage + ks) * (PF_OP_BYTES / 2), PF_OP_BYTES, &b_full[bs]);
+                        bulk_g2s(b_ring + (bs * NPROJ + p) * PF_B_BYTES,
+                                 P.xa + (((size_t)tile * NPROJ + p) * nstage + ks) * (PF_B_BYTES / 2), PF_B_BYTES, &b_full[bs]);
                 }
             }
             if (s_abort) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
@@ -226,26 +239,27 @@ __global__ void __launch_bounds__(NPROJ * 256 + 64, 1) exl3_prefill_kernel(const
         if (lane == 0) {
             uint32_t bit = 0, nitem = 0;
             for (uint32_t item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++nitem) {
-                const uint32_t tile = item / P.n_blocks, rows = P.tiles[3 + 3 * tile];
+                const uint32_t tile = item / nbg, rows = P.tiles[3 + 3 * tile];
                 const uint32_t idesc = umma_idesc_f16((rows + 15) / 16 * 16);
-                if (!mbar_wait_bounded(&acc_empty, (nitem & 1u) ^ 1u, &s_abort)) { give_up(ST_WAIT_EMPTY); break; }
+                if (!mbar_wait_bounded(&acc_empty, (nitem & 1u) ^ 1u, &s_abort, 64)) { give_up(ST_WAIT_EMPTY); break; }
                 tc_fence_after();
                 bool ok = true;
                 for (uint32_t ks = 0; ks < nstage; ++ks, ++bit) {
                     const uint32_t as = bit % PF_A_STAGES, aph = (bit / PF_A_STAGES) & 1u;
                     const uint32_t bs = bit % PF_B_STAGES, bph = (bit / PF_B_STAGES) & 1u;
-                    if (!mbar_wait_bounded(&a_full[as], aph, &s_abort) || !mbar_wait_bounded(&b_full[bs], bph, &s_abort)) {
+                    if (!mbar_wait_bounded(&a_full[as], aph, &s_abort, 32) || !mbar_wait_bounded(&b_full[bs], bph, &s_abort, 32)) {
                         give_up(ST_WAIT_FULL); ok = false; break;
                     }
                     tc_fence_after();
 #pragma unroll
-                    for (int p = 0; p < NPROJ; ++p) {
-                        const uint32_t a0 = smem_u32(a_ring + (as * NPROJ + p) * PF_OP_BYTES);
-                        const uint32_t b0 = smem_u32(b_ring + (bs * NPROJ + p) * PF_OP_BYTES);
+                    for (int gq = 0; gq < NG; ++gq) {
+                        const int p = gq / CB;  // group = (projection, column block)
+                        const uint32_t a0 = smem_u32(a_ring + (as * NG + gq) * PF_A_BYTES);
+                        const uint32_t b0 = smem_u32(b_ring + (bs * NPROJ + p) * PF_B_BYTES);
 #pragma unroll
                         for (int i = 0; i < PF_KS / 16; ++i)
-                            umma_f16(tmem + p * PF_NT, umma_smem_desc(a0 + i * 2 * PF_LBO), umma_smem_desc(b0 + i * 2 * PF_LBO),
-                                     idesc, (ks | (uint32_t)i) ? 1u : 0u);
+                            umma_f16(tmem + gq * PF_NT, umma_smem_desc(a0 + i * 2 * PF_LBO_A, PF_LBO_A),
+                                     umma_smem_desc(b0 + i * 2 * PF_LBO_B, PF_LBO_B), idesc, (ks | (uint32_t)i) ? 1u : 0u);
                     }
                     umma_commit(&a_empty[as]);  // the stage's operands are free once these MMAs have read them
                     umma_commit(&b_empty[bs]);
@@ -256,7 +270,9 @@ __global__ void __launch_bounds__(NPROJ * 256 + 64, 1) exl3_prefill_kernel(const
         }
     } else {
         // ---------------- decode warps + epilogue ----------------
-        const uint32_t p = warp >> 3, j = warp & 7u;
+        // a warp owns 16-column tile j of two accumulator groups: gate/up: projection hi, both column blocks;
+        // down: column blocks 2 hi and 2 hi + 1.  Group index = NPROJ == 2 ? hi * CB + cb : 2 hi + cb.
+        const uint32_t hi = warp >> 3, j = warp & 7u;
         uint32_t wi, wj, lp;
         exl3_lane_plan(lane, wi, wj, lp);
         const uint32_t g = lane >> 2, c = lane & 3u;
@@ -271,104 +287,113 @@ __global__ void __launch_bounds__(NPROJ * 256 + 64, 1) exl3_prefill_kernel(const
             return ok;
         };
         for (uint32_t item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++nitem) {
-            const uint32_t tile = item / P.n_blocks, nb = item % P.n_blocks;
+            const uint32_t tile = item / nbg, nb0 = (item % nbg) * CB;
             const uint32_t expert = P.tiles[1 + 3 * tile], row0 = P.tiles[2 + 3 * tile], rows = P.tiles[3 + 3 * tile];
             bool ok = true;
             for (uint32_t ks = 0; ks < nstage; ++ks, ++rit, ++bit) {
                 const uint32_t rs = rit % PF_RAW_STAGES, rph = (rit / PF_RAW_STAGES) & 1u;
-                const uint32_t bs = bit % PF_A_STAGES, bph = (bit / PF_A_STAGES) & 1u;
-                if (!mbar_wait_bounded(&raw_full[rs], rph, &s_abort) || !mbar_wait_bounded(&a_empty[bs], bph ^ 1u, &s_abort)) {
+                const uint32_t as = bit % PF_A_STAGES, aph = (bit / PF_A_STAGES) & 1u;
+                if (!mbar_wait_bounded(&raw_full[rs], rph, &s_abort) || !mbar_wait_bounded(&a_empty[as], aph ^ 1u, &s_abort)) {
                     give_up(ST_WAIT_FULL); ok = false; break;
                 }
-                const uint32_t* wt = reinterpret_cast<const uint32_t*>(raw_ring + rs * RAW_BYTES) + p * 192u + j * 24u;
-                // this warp's 16 columns are core-matrix rows 2j and 2j+1; a lane's half2 pairs sit at g*16 + 4c bytes
-                uint8_t* ad = a_ring + (bs * NPROJ + p) * PF_OP_BYTES + (2 * j) * PF_SBO + g * 16 + c * 4;
 #pragma unroll
-                for (int kt = 0; kt < 4; ++kt) {
-                    uint32_t bq[4];
-                    exl3_decode_lane(wt[kt * KSTRIDE + wi], wt[kt * KSTRIDE + wj], lp, bq);
-                    uint8_t* d = ad + (2 * kt) * PF_LBO;
-                    *reinterpret_cast<uint32_t*>(d) = bq[0];                      // k 2c,2c+1      column g
-                    *reinterpret_cast<uint32_t*>(d + PF_LBO) = bq[1];             // k 2c+8,2c+9    column g
-                    *reinterpret_cast<uint32_t*>(d + PF_SBO) = bq[2];             // k 2c,2c+1      column g+8
-                    *reinterpret_cast<uint32_t*>(d + PF_SBO + PF_LBO) = bq[3];    // k 2c+8,2c+9    column g+8
+                for (int u = 0; u < 2; ++u) {
+                    const uint32_t cb = NPROJ == 2 ? (uint32_t)u : 2u * hi + u, p = NPROJ == 2 ? hi : 0u;
+                    const uint32_t gq = NPROJ == 2 ? hi * CB + u : cb;
+                    const uint32_t* wt = reinterpret_cast<const uint32_t*>(raw_ring + rs * RAW_BYTES + cb * RAW_BLK) + p * 192u + j * 24u;
+                    // the warp's 16 columns are core-matrix rows 2j and 2j+1; a lane's half2 pairs sit at g*16 + 4c bytes
+                    uint8_t* ad = a_ring + (as * NG + gq) * PF_A_BYTES + (2 * j) * PF_SBO + g * 16 + c * 4;
+#pragma unroll
+                    for (int kt = 0; kt < PF_KT; ++kt) {
+                        uint32_t bq[4];
+                        exl3_decode_lane(wt[kt * KSTRIDE + wi], wt[kt * KSTRIDE + wj], lp, bq);
+                        uint8_t* d = ad + (2 * kt) * PF_LBO_A;
+                        *reinterpret_cast<uint32_t*>(d) = bq[0];                        // k 2c,2c+1      column g
+                        *reinterpret_cast<uint32_t*>(d + PF_LBO_A) = bq[1];             // k 2c+8,2c+9    column g
+                        *reinterpret_cast<uint32_t*>(d + PF_SBO) = bq[2];               // k 2c,2c+1      column g+8
+                        *reinterpret_cast<uint32_t*>(d + PF_SBO + PF_LBO_A) = bq[3];    // k 2c+8,2c+9    column g+8
+                    }
                 }
                 fence_async_smem();
                 __syncwarp();
-                if (lane == 0) { mbar_arrive(&a_full[bs]); mbar_arrive(&raw_empty[rs]); }
+                if (lane == 0) { mbar_arrive(&a_full[as]); mbar_arrive(&raw_empty[rs]); }
             }
             if (!ok) break;
-            // ---- epilogue ----
+            // ---- epilogue: per column block, 32 rows at a time ----
             if (!mbar_wait_bounded(&acc_full, nitem & 1u, &s_abort)) { give_up(ST_WAIT_FULL); break; }
             tc_fence_after();
-            const uint32_t q = warp & 3u, sub = warp >> 2, ep = sub % NPROJ, half = sub / NPROJ;
+            const uint32_t q = warp & 3u, sub = warp >> 2;
             const uint32_t rows16 = (rows + 15) / 16 * 16;
-            for (uint32_t rb = 0; rb < rows16 && ok; rb += PF_EPI_ROWS) {
-                constexpr int ROWS_PER_LD = PF_EPI_ROWS / (NCW / 4 / NPROJ);  // 16 for both kernels
-                static_assert(ROWS_PER_LD == 16, "the epilogue loads 16 accumulator columns per warp");
-                uint32_t v[16];
-                tmem_ld16(tmem + ((q * 32u) << 16) + ep * PF_NT + rb + half * 16, v);
+            for (uint32_t cb = 0; cb < (uint32_t)CB && ok; ++cb) {
+                for (uint32_t rb = 0; rb < rows16 && ok; rb += PF_EPI_ROWS) {
+                    // 16 warps: lane quarter q, then (projection, 16-row half) for gate/up; down uses warps 0..7
+                    if (sub < 2u * NPROJ) {
+                        const uint32_t ep = sub % NPROJ, half = sub / NPROJ;
+                        uint32_t v[16];
+                        tmem_ld16(tmem + ((q * 32u) << 16) + (ep * CB + cb) * PF_NT + rb + half * 16, v);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) zs[(ep * PF_EPI_ROWS + half * 16 + i) * PF_ZS_STRIDE + q * 32 + lane] = __uint_as_float(v[i]);
-                if (!epi_sync()) { ok = false; break; }
-                for (uint32_t rr = warp; rr < PF_EPI_ROWS; rr += NCW) {
-                    const uint32_t r = rb + rr;
-                    if (r >= rows16) continue;
-                    const bool valid = r < rows;
-                    const uint32_t col = nb * 128 + lane * 4;
-                    if (NPROJ == 2) {
-                        float vv[4] = {0.f, 0.f, 0.f, 0.f};
-                        if (valid) {
-                            const float4 zg = *reinterpret_cast<const float4*>(zs + (0 * PF_EPI_ROWS + rr) * PF_ZS_STRIDE + lane * 4);
-                            const float4 zu = *reinterpret_cast<const float4*>(zs + (1 * PF_EPI_ROWS + rr) * PF_ZS_STRIDE + lane * 4);
-                            float gq[4] = {zg.x, zg.y, zg.z, zg.w}, uq[4] = {zu.x, zu.y, zu.z, zu.w};
-                            hadamard128_warp(gq, lane);
-                            hadamard128_warp(uq, lane);
-                            const __half* sc = P.scales + (size_t)expert * P.scales_stride;
-                            const uint2 sg = *reinterpret_cast<const uint2*>(sc + 2 * (size_t)P.H + col);
-                            const uint2 su = *reinterpret_cast<const uint2*>(sc + 2 * (size_t)P.H + P.I + col);
-                            const uint2 sd = *reinterpret_cast<const uint2*>(sc + 2 * (size_t)P.H + 2 * (size_t)P.I + col);
-                            const float2 sg01 = __half22float2(*reinterpret_cast<const __half2*>(&sg.x));
-                            const float2 sg23 = __half22float2(*reinterpret_cast<const __half2*>(&sg.y));
-                            const float2 su01 = __half22float2(*reinterpret_cast<const __half2*>(&su.x));
-                            const float2 su23 = __half22float2(*reinterpret_cast<const __half2*>(&su.y));
-                            const float2 sd01 = __half22float2(*reinterpret_cast<const __half2*>(&sd.x));
-                            const float2 sd23 = __half22float2(*reinterpret_cast<const __half2*>(&sd.y));
-                            const float svg[4] = {sg01.x, sg01.y, sg23.x, sg23.y}, svu[4] = {su01.x, su01.y, su23.x, su23.y};
-                            const float shd[4] = {sd01.x, sd01.y, sd23.x, sd23.y};
-#pragma unroll
-                            for (int qq = 0; qq < 4; ++qq) {
-                                const float gm = (gq[qq] * S) * svg[qq], um = (uq[qq] * S) * svu[qq];
-                                float gate = gm, up = um;
-                                if (P.limit > 0.f) {
-                                    gate = (gm != gm) ? gm : (gm < P.limit ? gm : P.limit);
-                                    const float u0 = (um != um) ? um : (um > -P.limit ? um : -P.limit);
-                                    up = (u0 != u0) ? u0 : (u0 < P.limit ? u0 : P.limit);
-                                }
-                                const float yv = 1.0f / (1.0f + expf(fabsf(gate)));
-                                const float sgm = gate < 0.f ? yv : 1.0f - yv;
-                                vv[qq] = ((gate * sgm) * up) * shd[qq];
-                            }
-                            hadamard128_warp(vv, lane);
-                        }
-                        // src/kernels/exl3/header_dig2_x.metal:104: the down input is rounded to f16
-                        const __half2 h01 = __floats2half2_rn(vv[0] * S, vv[1] * S), h23 = __floats2half2_rn(vv[2] * S, vv[3] * S);
-                        *reinterpret_cast<uint2*>(P.xd + pf_xa_off(P.I / PF_KS, tile, 1, 0, r, col)) =
-                            make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
-                    } else if (valid) {
-                        const float4 z4 = *reinterpret_cast<const float4*>(zs + rr * PF_ZS_STRIDE + lane * 4);
-                        float vv[4] = {z4.x, z4.y, z4.z, z4.w};
-                        hadamard128_warp(vv, lane);
-                        const __half* sc = P.scales + (size_t)expert * P.scales_stride + 2 * (size_t)P.H + 3 * (size_t)P.I;
-                        const uint2 so = *reinterpret_cast<const uint2*>(sc + col);
-                        const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&so.x));
-                        const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&so.y));
-                        const uint32_t assign = P.t.order[row0 + r];
-                        *reinterpret_cast<float4*>(P.ro + (size_t)assign * P.H + col) =
-                            make_float4((vv[0] * S) * s01.x, (vv[1] * S) * s01.y, (vv[2] * S) * s23.x, (vv[3] * S) * s23.y);
+                        for (int i = 0; i < 16; ++i) zs[(ep * PF_EPI_ROWS + half * 16 + i) * PF_ZS_STRIDE + q * 32 + lane] = __uint_as_float(v[i]);
                     }
+                    if (!epi_sync()) { ok = false; break; }
+                    for (uint32_t rr = warp; rr < PF_EPI_ROWS; rr += NCW) {
+                        const uint32_t r = rb + rr;
+                        if (r >= rows16) continue;
+                        const bool valid = r < rows;
+                        const uint32_t col = (nb0 + cb) * 128 + lane * 4;
+                        if (NPROJ == 2) {
+                            float vv[4] = {0.f, 0.f, 0.f, 0.f};
+                            if (valid) {
+                                const float4 zg = *reinterpret_cast<const float4*>(zs + (0 * PF_EPI_ROWS + rr) * PF_ZS_STRIDE + lane * 4);
+                                const float4 zu = *reinterpret_cast<const float4*>(zs + (1 * PF_EPI_ROWS + rr) * PF_ZS_STRIDE + lane * 4);
+                                float gq4[4] = {zg.x, zg.y, zg.z, zg.w}, uq4[4] = {zu.x, zu.y, zu.z, zu.w};
+                                hadamard128_warp(gq4, lane);
+                                hadamard128_warp(uq4, lane);
+                                const __half* sc = P.scales + (size_t)expert * P.scales_stride;
+                                const uint2 sg = *reinterpret_cast<const uint2*>(sc + 2 * (size_t)P.H + col);
+                                const uint2 su = *reinterpret_cast<const uint2*>(sc + 2 * (size_t)P.H + P.I + col);
+                                const uint2 sd = *reinterpret_cast<const uint2*>(sc + 2 * (size_t)P.H + 2 * (size_t)P.I + col);
+                                const float2 sg01 = __half22float2(*reinterpret_cast<const __half2*>(&sg.x));
+                                const float2 sg23 = __half22float2(*reinterpret_cast<const __half2*>(&sg.y));
+                                const float2 su01 = __half22float2(*reinterpret_cast<const __half2*>(&su.x));
+                                const float2 su23 = __half22float2(*reinterpret_cast<const __half2*>(&su.y));
+                                const float2 sd01 = __half22float2(*reinterpret_cast<const __half2*>(&sd.x));
+                                const float2 sd23 = __half22float2(*reinterpret_cast<const __half2*>(&sd.y));
+                                const float svg[4] = {sg01.x, sg01.y, sg23.x, sg23.y}, svu[4] = {su01.x, su01.y, su23.x, su23.y};
+                                const float shd[4] = {sd01.x, sd01.y, sd23.x, sd23.y};
+#pragma unroll
+                                for (int qq = 0; qq < 4; ++qq) {
+                                    const float gm = (gq4[qq] * S) * svg[qq], um = (uq4[qq] * S) * svu[qq];
+                                    float gate = gm, up = um;
+                                    if (P.limit > 0.f) {
+                                        gate = (gm != gm) ? gm : (gm < P.limit ? gm : P.limit);
+                                        const float u0 = (um != um) ? um : (um > -P.limit ? um : -P.limit);
+                                        up = (u0 != u0) ? u0 : (u0 < P.limit ? u0 : P.limit);
+                                    }
+                                    const float yv = 1.0f / (1.0f + expf(fabsf(gate)));
+                                    const float sgm = gate < 0.f ? yv : 1.0f - yv;
+                                    vv[qq] = ((gate * sgm) * up) * shd[qq];
+                                }
+                                hadamard128_warp(vv, lane);
+                            }
+                            // src/kernels/exl3/header_dig2_x.metal:104: the down input is rounded to f16
+                            const __half2 h01 = __floats2half2_rn(vv[0] * S, vv[1] * S), h23 = __floats2half2_rn(vv[2] * S, vv[3] * S);
+                            *reinterpret_cast<uint2*>(P.xd + pf_xa_off(P.I / PF_KS, tile, 1, 0, r, col)) =
+                                make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+                        } else if (valid) {
+                            const float4 z4 = *reinterpret_cast<const float4*>(zs + rr * PF_ZS_STRIDE + lane * 4);
+                            float vv[4] = {z4.x, z4.y, z4.z, z4.w};
+                            hadamard128_warp(vv, lane);
+                            const __half* sc = P.scales + (size_t)expert * P.scales_stride + 2 * (size_t)P.H + 3 * (size_t)P.I;
+                            const uint2 so = *reinterpret_cast<const uint2*>(sc + col);
+                            const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&so.x));
+                            const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&so.y));
+                            const uint32_t assign = P.t.order[row0 + r];
+                            *reinterpret_cast<float4*>(P.ro + (size_t)assign * P.H + col) =
+                                make_float4((vv[0] * S) * s01.x, (vv[1] * S) * s01.y, (vv[2] * S) * s23.x, (vv[3] * S) * s23.y);
+                        }
+                    }
+                    if (!epi_sync()) { ok = false; break; }
                 }
-                if (!epi_sync()) { ok = false; break; }
             }
             if (!ok) break;
             tc_fence_before();
@@ -384,8 +409,11 @@ __global__ void __launch_bounds__(NPROJ * 256 + 64, 1) exl3_prefill_kernel(const
 }
 
 static size_t pf_smem_bytes(int nproj) {
-    return (size_t)(PF_A_STAGES + PF_B_STAGES) * nproj * PF_OP_BYTES + (size_t)PF_RAW_STAGES * 4 * nproj * 192 * 4;
+    return (size_t)PF_A_STAGES * 4 * PF_A_BYTES + (size_t)PF_B_STAGES * nproj * PF_B_BYTES +
+           (size_t)PF_RAW_STAGES * PF_KT * 4 * 192 * 4 + (size_t)nproj * PF_EPI_ROWS * PF_ZS_STRIDE * sizeof(float);
 }
+
+bool exl3_prefill_supported(Exl3Dims d) { return (d.I / 128) % 2 == 0 && (d.H / 128) % 4 == 0; }
 
 cudaError_t launch_exl3_prefill(const Exl3PrefillArgs& a, cudaStream_t st) {
     const uint32_t E = a.n_experts;
@@ -398,19 +426,19 @@ cudaError_t launch_exl3_prefill(const Exl3PrefillArgs& a, cudaStream_t st) {
     PfParams P{};
     P.tiles = a.tiles; P.t = a.t; P.scales = a.L.scales; P.scales_stride = exl3_scales_per_expert(a.d);
     P.H = a.d.H; P.I = a.d.I; P.limit = a.limit; P.status = a.status;
-    // gate / up
+    // gate / up: two projections x two adjacent column blocks per CTA
     P.code = a.L.gu_code; P.expert_stride_words = 2 * exl3_code_words(a.d); P.n_blocks = a.d.I / 128; P.nkt = a.d.H / 16;
     P.xa = a.xa; P.xd = a.xd; P.ro = nullptr;
     size_t smem = pf_smem_bytes(2);
-    if ((e = cudaFuncSetAttribute(exl3_prefill_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
-    exl3_prefill_kernel<2><<<a.sm_count, 2 * 256 + 64, smem, st>>>(P);
+    if ((e = cudaFuncSetAttribute(exl3_prefill_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
+    exl3_prefill_kernel<2, 2><<<a.sm_count, 512 + 64, smem, st>>>(P);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
-    // down
+    // down: four adjacent column blocks per CTA
     P.code = a.L.d_code; P.expert_stride_words = exl3_code_words(a.d); P.n_blocks = a.d.H / 128; P.nkt = a.d.I / 16;
     P.xa = a.xd; P.xd = nullptr; P.ro = a.ro;
     smem = pf_smem_bytes(1);
-    if ((e = cudaFuncSetAttribute(exl3_prefill_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
-    exl3_prefill_kernel<1><<<a.sm_count, 256 + 64, smem, st>>>(P);
+    if ((e = cudaFuncSetAttribute(exl3_prefill_kernel<1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
+    exl3_prefill_kernel<1, 4><<<a.sm_count, 512 + 64, smem, st>>>(P);
     return cudaGetLastError();
 }
 

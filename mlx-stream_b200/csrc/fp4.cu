@@ -236,7 +236,7 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
                 const uint8_t* wsrc = P.w + (size_t)expert * P.expert_stride + (size_t)nb * P.n_stages_k * P.w_bytes;
                 for (uint32_t ks = 0; ks < (last ? 1u : P.n_stages_k); ++ks, ++it) {
                     const uint32_t s = it % NS, ph = (it / NS) & 1u;
-                    if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, &s_abort)) {
+                    if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, &s_abort, 128)) {
                         if (!s_abort) atomicMax(P.status, (uint32_t)ST_WAIT_EMPTY);
                         s_abort = 1; ok = false; break;
                     }

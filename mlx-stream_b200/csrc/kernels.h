@@ -91,8 +91,8 @@ struct Exl3PrefillArgs {
     uint32_t top_k;
     uint32_t* tiles;         // [1 + 3 max_tiles] row-tile table (device scratch)
     uint32_t max_tiles;
-    __half* xa;              // [max_tiles][2][H/64][128 x 64] f16: rotated rows in the MMA's B-operand order
-    __half* xd;              // [max_tiles][I/64][128 x 64] f16
+    __half* xa;              // [max_tiles][2][H/32][128 x 32] f16: rotated rows in the MMA's B-operand order
+    __half* xd;              // [max_tiles][I/32][128 x 32] f16
     float* ro;               // [A, H]
     float limit;
     uint32_t* status;
@@ -101,6 +101,7 @@ struct Exl3PrefillArgs {
 static inline size_t exl3_prefill_xa_bytes(Exl3Dims d, uint32_t max_tiles) { return (size_t)max_tiles * 2 * d.H * PREFILL_TILE_ROWS * 2; }
 static inline size_t exl3_prefill_xd_bytes(Exl3Dims d, uint32_t max_tiles) { return (size_t)max_tiles * d.I * PREFILL_TILE_ROWS * 2; }
 cudaError_t launch_exl3_prefill(const Exl3PrefillArgs& a, cudaStream_t st);
+bool exl3_prefill_supported(Exl3Dims d);  // the lane groups 2 (gate/up) and 4 (down) column blocks per CTA
 
 // ---- MXFP4 / NVFP4 ----
 constexpr int FP4_CHUNK_ROWS = 8;
