@@ -177,7 +177,7 @@ def workload_config(args, T):
     return {"workload": WL["name"],
             "hidden": H, "inter": I, "n_experts": E, "top_k": K_TOP, "shared_expert": "bf16" if WL["shared"] else "none",
             "tokens_per_call": T,
-            "routing": args.routing, "l2": "inputs larger than L2 (each call streams >2 GB of distinct expert code)",
+            "layers": getattr(args, "layers", 1), "routing": args.routing, "l2": "inputs larger than L2 (each call streams >2 GB of distinct expert code)",
             "parallelism": "single GPU" if args.gpus == 1 else f"ep{args.gpus}"}
 
 
@@ -193,6 +193,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--experts", type=int, default=0, help="routed experts (smaller only for profiler captures)")
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--layers", type=int, default=1,
+                    help="stack of identical-shape layers run back to back per step (BASELINE config 5 uses 24)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     globals().update(WL=wl, H=wl["H"], I=wl["I"], E=args.experts or wl["E"], K_TOP=wl["k"])
@@ -221,7 +223,8 @@ def main():
 
     bank_kind = {"exl3": pkg.BANK_EXL3_K3_MUL1, "mxfp4": pkg.BANK_MXFP4, "nvfp4": pkg.BANK_NVFP4}[WL["bank"]]
     scoring = {"sqrtsoftplus": pkg.SCORE_SQRTSOFTPLUS, "sigmoid": pkg.SCORE_SIGMOID, "softmax": pkg.SCORE_SOFTMAX}[WL["scoring"]]
-    cfg = pkg.make_config(H, I, E, K_TOP, n_layers=1, bank_kind=bank_kind,
+    NL = args.layers
+    cfg = pkg.make_config(H, I, E, K_TOP, n_layers=NL, bank_kind=bank_kind,
                           act=pkg.ACT_SWIGLU_CLAMPED if WL["limit"] > 0 else pkg.ACT_SWIGLU, act_limit=WL["limit"],
                           scoring=scoring, norm_topk=True, routed_scale=WL["scale"], shared_expert=WL["shared"],
                           combine=pkg.COMBINE_CHAIN if WL["chain"] else pkg.COMBINE_F32, max_tokens=max(T, 64),
@@ -257,7 +260,8 @@ def main():
                     sgn = torch.where(torch.rand(n, device=dev, generator=g) < 0.5, -1.0, 1.0)
                     rec[off:off + 2 * n] = ((0.5 + u) * sgn * sc).to(torch.float16).view(torch.uint8)
                     off += 2 * n
-            moe.load_expert(0, e, rec.data_ptr(), stride, on_device=True)
+            for l in range(NL):  # the stack's layers share one synthetic bank image (same bytes, separate residency)
+                moe.load_expert(l, e, rec.data_ptr(), stride, on_device=True)
     else:
         nv = WL["bank"] == "nvfp4"
         for e in range(e_lo, e_hi):
@@ -271,11 +275,13 @@ def main():
                     parts.append(gs.to(torch.float32).reshape(1).view(torch.uint8))
             rec = torch.cat(parts)
             assert rec.numel() == logical, (rec.numel(), logical)
-            moe.load_expert(0, e, rec.data_ptr(), rec.numel(), on_device=True)
+            for l in range(NL):
+                moe.load_expert(l, e, rec.data_ptr(), rec.numel(), on_device=True)
     sw = None
     if WL["shared"]:
         sw = [(torch.randn(s, device=dev, generator=g) * 0.02).to(torch.bfloat16) for s in ((I, H), (I, H), (H, I))]
-        moe.set_shared(0, sw[0].data_ptr(), sw[1].data_ptr(), sw[2].data_ptr(), on_device=True)
+        for l in range(NL):
+            moe.set_shared(l, sw[0].data_ptr(), sw[1].data_ptr(), sw[2].data_ptr(), on_device=True)
 
     rng = np.random.default_rng(99 + rank)
     n_batches = 4  # rotate a few seeded batches so consecutive steps route differently
@@ -288,16 +294,36 @@ def main():
         x_host.append(x.cpu().pin_memory())
         lg_host.append(torch.from_numpy(lg).pin_memory())
     y = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+    y2 = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
     y_host = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
     stream = torch.cuda.current_stream()
     sp = stream.cuda_stream
 
     def step(i):
-        moe.forward(0, xs[i % n_batches].data_ptr(), lgs[i % n_batches].data_ptr(), T, y.data_ptr(), sp)
+        # a stack feeds each layer's output to the next one (the trunk between MoE layers is out of scope); every
+        # layer routes with its own seeded logits
+        src, a, b = xs[i % n_batches], y, y2
+        for l in range(NL):
+            moe.forward(l, src.data_ptr(), lgs[(i + l) % n_batches].data_ptr(), T, a.data_ptr(), sp)
+            src, a, b = a, b, a
+
+    x_in = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+    lg_in = torch.empty((T, E), dtype=torch.float32, device=dev)
 
     def step_host(i):
-        moe.forward_host(0, x_host[i % n_batches].data_ptr(), lg_host[i % n_batches].data_ptr(), T,
-                         y_host.data_ptr(), sp)
+        if NL == 1:
+            moe.forward_host(0, x_host[i % n_batches].data_ptr(), lg_host[i % n_batches].data_ptr(), T,
+                             y_host.data_ptr(), sp)
+            return
+        # a stack: the step's inputs come from pinned host memory, the last layer's output goes back
+        x_in.copy_(x_host[i % n_batches], non_blocking=True)
+        lg_in.copy_(lg_host[i % n_batches], non_blocking=True)
+        src, a, b = x_in, y, y2
+        for l in range(NL):
+            moe.forward(l, src.data_ptr(), (lg_in if l == 0 else lgs[(i + l) % n_batches]).data_ptr(), T, a.data_ptr(), sp)
+            src, a, b = a, b, a
+        y_host.copy_(src, non_blocking=True)
+        stream.synchronize()
 
     def barrier():
         if world > 1:
@@ -341,7 +367,7 @@ def main():
     if st.device_status != 0:
         raise SystemExit(f"bench.py: device status {st.device_status}")
 
-    mean_distinct = sum(distinct[i % n_batches] for i in range(args.steps)) / args.steps
+    mean_distinct = sum(distinct[i % n_batches] for i in range(args.steps)) / args.steps * 1.0
     if WL["bank"] == "exl3":
         gu_bytes = 2 * code_bytes + 2 * (2 * I + 2 * H)  # one expert's gate + up code and sign/scale vectors
         kname = "exl3_gemv_kernel<2,gate_up>"
@@ -354,7 +380,7 @@ def main():
     peak, which = peaks()
     achieved = mean_distinct * gu_bytes / (gu_ms / max(gu_n, 1) * 1e-3) / 1e9
     prefill_lane = WL["bank"] == "exl3" and T * K_TOP >= 24 * (E // world) and T * K_TOP >= 2048
-    layer_bytes = mean_distinct * logical + (3 * H * I * 2 if WL["shared"] else 0) + T * H * 2 * 2 + T * E * 4
+    layer_bytes = NL * (mean_distinct * logical + (3 * H * I * 2 if WL["shared"] else 0) + T * H * 2 * 2 + T * E * 4)
     value = world * T * args.steps / (ms * 1e-3)
     out = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -373,7 +399,7 @@ def main():
         "stage_ms_per_step": {k: v[0] / max(args.steps, 1) for k, v in prof.items() if v[1]},
         "e2e": {"value": world * T * args.steps / (ms_host * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": T * H * 2 + T * E * 4, "d2h_bytes_per_step": T * H * 2 + 4},
-        "gpu_launches": ((8 if WL["shared"] else 6) + (4 if world > 1 else 0)) * args.steps,
+        "gpu_launches": NL * ((8 if WL["shared"] else 6) + (4 if world > 1 else 0)) * args.steps,
         "exchange": None if world == 1 else {
             "exposed_ms_per_step": prof["exchange"][0] / max(args.steps, 1),
             "bytes_sent_per_step_rank0": st.a2a_bytes_sent / max(st.expert_calls, 1),

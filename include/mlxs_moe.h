@@ -106,6 +106,17 @@ int mlxs_moe_load_expert(mlxs_moe *h, uint32_t layer, uint32_t expert, const voi
  * verifies geometry (and record sha256 when the manifest carries it) and loads this rank's experts. */
 int mlxs_moe_load_bank(mlxs_moe *h, const char *dir);
 
+/* Peek (src/expert/bank.zig:686-690, src/arch/glm5_next/bank.zig:395): the manifest of the bank at `dir`, or a manifest
+ * text, parsed and checked field by field without any device; refusals name the field (MLXS_E_MANIFEST). */
+typedef struct {
+    uint32_t bank_kind, has_sha256;
+    uint64_t hidden, inter, n_experts, n_layers, first_layer;
+    uint64_t logical_bytes, record_stride, data_bytes;
+    char data_file[64];
+} mlxs_bank_info;
+int mlxs_moe_bank_peek(const char *dir, mlxs_bank_info *out);
+int mlxs_moe_bank_peek_text(const char *manifest_json, mlxs_bank_info *out);
+
 /* the router's noaux_tc correction bias, f32 [n_experts] host, NULL = zeros (src/arch/deepseek_v41/graph.zig:2035) */
 int mlxs_moe_set_router_bias(mlxs_moe *h, uint32_t layer, const float *bias_host);
 /* the shared expert's bf16 linears: w1 (gate) [inter, hidden], w3 (up) [inter, hidden], w2 (down) [hidden, inter]

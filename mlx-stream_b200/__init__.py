@@ -23,7 +23,7 @@ COMBINE_F32, COMBINE_CHAIN = 0, 1
 
 EXPORTS = [
     "mlxs_moe_abi", "mlxs_moe_last_error", "mlxs_moe_create", "mlxs_moe_destroy", "mlxs_moe_record_bytes",
-    "mlxs_moe_load_expert", "mlxs_moe_load_bank", "mlxs_moe_set_router_bias", "mlxs_moe_set_shared", "mlxs_moe_route",
+    "mlxs_moe_load_expert", "mlxs_moe_load_bank", "mlxs_moe_bank_peek", "mlxs_moe_bank_peek_text", "mlxs_moe_set_router_bias", "mlxs_moe_set_shared", "mlxs_moe_route",
     "mlxs_moe_routed", "mlxs_moe_experts", "mlxs_moe_forward", "mlxs_moe_forward_host", "mlxs_moe_exl3_gemv",
     "mlxs_moe_exl3_gemv_noalloc",
     "mlxs_moe_stats_get", "mlxs_moe_profile_enable", "mlxs_moe_profile_read", "mlxs_moe_ep_unique_id", "mlxs_moe_ep_init", "mlxs_moe_ep_plan",
@@ -52,6 +52,13 @@ class Profile(C.Structure):
     _fields_ = [("ms", C.c_double * 8), ("launches", C.c_uint64 * 8)]
 
 
+class BankInfo(C.Structure):
+    _fields_ = [("bank_kind", C.c_uint32), ("has_sha256", C.c_uint32), ("hidden", C.c_uint64), ("inter", C.c_uint64),
+                ("n_experts", C.c_uint64), ("n_layers", C.c_uint64), ("first_layer", C.c_uint64),
+                ("logical_bytes", C.c_uint64), ("record_stride", C.c_uint64), ("data_bytes", C.c_uint64),
+                ("data_file", C.c_char * 64)]
+
+
 class MlxsError(RuntimeError):
     def __init__(self, rc, msg):
         super().__init__(f"mlxs_moe rc={rc}: {msg}")
@@ -77,6 +84,8 @@ def lib():
         L.mlxs_moe_record_bytes.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
         L.mlxs_moe_load_expert.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint64, C.c_int]
         L.mlxs_moe_load_bank.argtypes = [C.c_void_p, C.c_char_p]
+        L.mlxs_moe_bank_peek.argtypes = [C.c_char_p, C.POINTER(BankInfo)]
+        L.mlxs_moe_bank_peek_text.argtypes = [C.c_char_p, C.POINTER(BankInfo)]
         L.mlxs_moe_set_router_bias.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p]
         L.mlxs_moe_set_shared.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
         L.mlxs_moe_route.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p]
@@ -115,6 +124,16 @@ def make_config(hidden, inter, n_experts, top_k, n_layers=1, bank_kind=BANK_EXL3
                 combine=COMBINE_F32, max_tokens=64, device=0, ep_world=1, ep_rank=0):
     return Config(C.sizeof(Config), hidden, inter, n_experts, top_k, n_layers, bank_kind, act, act_limit, scoring,
                   int(norm_topk), routed_scale, int(shared_expert), combine, max_tokens, device, ep_world, ep_rank)
+
+
+def bank_peek(directory=None, text=None):
+    """Parses and checks a bank manifest (the directory's, or a manifest text) without a device."""
+    info = BankInfo()
+    if text is not None:
+        _check(lib().mlxs_moe_bank_peek_text(text.encode() if isinstance(text, str) else text, C.byref(info)))
+    else:
+        _check(lib().mlxs_moe_bank_peek(str(directory).encode(), C.byref(info)))
+    return info
 
 
 def exl3_gemv_noalloc(code, in_dim, out_dim, xh, rows, z, stream=None):

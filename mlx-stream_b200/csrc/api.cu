@@ -217,9 +217,17 @@ extern "C" int mlxs_moe_load_expert(mlxs_moe* h, uint32_t layer, uint32_t expert
     return MLXS_OK;
 }
 
+int mlxs_bank_for_each_record(const char* dir, uint32_t bank_kind, uint64_t H, uint64_t I, uint64_t E, uint64_t n_layers,
+                              uint32_t e_first, uint32_t e_count,
+                              int (*sink)(void* ctx, uint32_t layer, uint32_t expert, const void* rec, uint64_t n), void* ctx);
+
 extern "C" int mlxs_moe_load_bank(mlxs_moe* h, const char* dir) {
     if (!h || !dir) return fail(MLXS_E_ARG, "load_bank: null argument");
-    return fail(MLXS_E_MANIFEST, "load_bank: manifest reader not built in this version");
+    const mlxs_moe_config& c = h->cfg;
+    auto sink = [](void* ctx, uint32_t layer, uint32_t expert, const void* rec, uint64_t n) -> int {
+        return mlxs_moe_load_expert(static_cast<mlxs_moe*>(ctx), layer, expert, rec, n, 0);
+    };
+    return mlxs_bank_for_each_record(dir, c.bank_kind, c.hidden, c.inter, c.n_experts, c.n_layers, h->e_first, h->e_local, sink, h);
 }
 
 extern "C" int mlxs_moe_set_router_bias(mlxs_moe* h, uint32_t layer, const float* bias_host) {

@@ -53,6 +53,21 @@ pub extern fn mlxs_moe_destroy(h: ?*Moe) void;
 pub extern fn mlxs_moe_record_bytes(h: *const Moe, logical: ?*u64, stride: ?*u64) c_int;
 pub extern fn mlxs_moe_load_expert(h: *Moe, layer: u32, expert: u32, record: *const anyopaque, nbytes: u64, on_device: c_int) c_int;
 pub extern fn mlxs_moe_load_bank(h: *Moe, dir: [*:0]const u8) c_int;
+pub const BankInfo = extern struct {
+    bank_kind: u32,
+    has_sha256: u32,
+    hidden: u64,
+    inter: u64,
+    n_experts: u64,
+    n_layers: u64,
+    first_layer: u64,
+    logical_bytes: u64,
+    record_stride: u64,
+    data_bytes: u64,
+    data_file: [64]u8,
+};
+pub extern fn mlxs_moe_bank_peek(dir: [*:0]const u8, out: *BankInfo) c_int;
+pub extern fn mlxs_moe_bank_peek_text(manifest_json: [*:0]const u8, out: *BankInfo) c_int;
 pub extern fn mlxs_moe_set_router_bias(h: *Moe, layer: u32, bias_host: ?[*]const f32) c_int;
 pub extern fn mlxs_moe_set_shared(h: *Moe, layer: u32, w1: *const anyopaque, w3: *const anyopaque, w2: *const anyopaque, on_device: c_int) c_int;
 pub extern fn mlxs_moe_route(h: *Moe, layer: u32, logits_dev: *const anyopaque, t: u32, ids_dev: *anyopaque, weights_dev: *anyopaque, stream: ?*anyopaque) c_int;

@@ -5,6 +5,7 @@ reference's tests pin (digests and two small f32 vectors), never source:
   * src/kernels/exl3/manifest.json `golden`        -> the mul1 table digest and the four seeded planes
   * src/arch/glm5_next/exl3_parity.zig:19-23        -> the two GLM-shape plane digests (literals re-typed below)
   * src/arch/glm5_next/testdata/exl3-ref/           -> meta.json, h_mul1.f32, y_mul1.f32 (expert forward fixture)
+  * src/fixtures/dsv41_bank_peek.json               -> the v2 manifest sample the reference's claims tests mutate
 The parity tests read the copies, so they run where the reference is absent.
 """
 import json
@@ -46,6 +47,8 @@ def main(ref_root: str) -> None:
     dst.mkdir(exist_ok=True)
     for f in ("meta.json", "h_mul1.f32", "y_mul1.f32"):
         shutil.copyfile(fx / f, dst / f)
+    # the trimmed v2 manifest of the bank of record (format, quantization, dims, 40 layer tables): a data fixture
+    shutil.copyfile(ref / "src/fixtures/dsv41_bank_peek.json", here / "dsv41_bank_peek.json")
     print("wrote", here / "exl3_digests.json", "and", dst)
 
 

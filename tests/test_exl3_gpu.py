@@ -222,3 +222,28 @@ def test_prefill_lane_tcgen05():
             assert (sub.view(np.uint32) == ro[keep].view(np.uint32)).all()
     finally:
         case.close()
+
+
+def test_load_bank_from_reference_format_files(tmp_path):
+    """Bank.open + fill (src/expert/bank.zig:208-324): experts.bin + expert-manifest-v2.json written in the
+    reference's format, record digests verified, the layer equal to the one loaded record by record."""
+    import bank_files
+    H, I, E, k = 512, 256, 4, 2
+    a = Exl3Case(H, I, E, k, seed=21, shared=False, max_tokens=16)
+    b = Exl3Case(H, I, E, k, seed=21, shared=False, max_tokens=16, experts_to_load=[])
+    try:
+        bank_files.write_exl3_bank(tmp_path, H, I, E, 1, lambda l, e: a.records[e])
+        b.moe.load_bank(tmp_path)
+        x, logits = a.inputs(9, seed=3)
+        assert (a.gpu_forward(x, logits) == b.gpu_forward(x, logits)).all()
+        assert b.status() == 0
+        # a corrupted record is refused by its digest
+        raw = bytearray((tmp_path / "experts.bin").read_bytes())
+        raw[5000] ^= 1
+        (tmp_path / "experts.bin").write_bytes(bytes(raw))
+        with pytest.raises(b.pkg.MlxsError) as ei:
+            b.moe.load_bank(tmp_path)
+        assert "sha256" in ei.value.msg
+    finally:
+        a.close()
+        b.close()
