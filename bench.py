@@ -138,6 +138,25 @@ def make_logits(rng, T, routing):
     return lg
 
 
+LANE_MIN_ROWS = int(os.environ.get("MLXS_PREFILL_MIN_ROWS", "17"))  # the library's default lane threshold
+
+
+def own_launches_per_layer(T, world):
+    """Kernels of this library one layer call launches (library GEMMs and NCCL kernels are not counted)."""
+    A = T * K_TOP
+    n = 1                                   # router
+    n += 3 if A > 2048 else 1               # dispatch: count / scan / place above 2048 rows, one CTA below
+    n += 3                                  # streaming lane: prep, gate/up, down
+    if WL["bank"] == "exl3" and A >= LANE_MIN_ROWS:
+        n += 4                              # tensor-core lane: plan, prep, gate/up, down
+    if WL["shared"]:
+        n += 2 if T <= 64 else 1            # skinny kernels, or the activation between the library GEMMs
+    n += 1                                  # combine
+    if world > 1:
+        n += 4                              # destination ranks, rank sort, gather, scatter
+    return n
+
+
 def reference_arm(args):
     """The reference's CPU path for this layer, timed on the host cores.  The reference's own CPU lane (Zig tests over
     MLX's CPU device) cannot be built here (no zig, no mlx), so this runs the oracle's fast f32 form (kind "port")."""
@@ -189,7 +208,7 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--tokens", type=int, default=64)
     ap.add_argument("--cpu-tokens", type=int, default=8)
-    ap.add_argument("--routing", default="normal", choices=["normal", "zipf"])
+    ap.add_argument("--routing", default="normal", choices=["normal", "uniform", "zipf"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--experts", type=int, default=0, help="routed experts (smaller only for profiler captures)")
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
@@ -348,10 +367,21 @@ def main():
     for i in range(args.warmup):
         step(i)
     # distinct experts per batch (exact, from the routed ids) for the algorithmic byte count
-    distinct = []
+    distinct, lane_counts = [], []
+    ids_dev = torch.empty((T, K_TOP), dtype=torch.int32, device=dev)
+    w_dev = torch.empty((T, K_TOP), dtype=torch.float32, device=dev)
     for b in range(n_batches):
         step(b)
         distinct.append(int(moe.stats().distinct_experts_last))
+        # rows per resident expert of layer 0 (which lane each expert takes is decided on these counts)
+        moe.route(0, lgs[b].data_ptr(), T, ids_dev.data_ptr(), w_dev.data_ptr(), sp)
+        torch.cuda.synchronize()
+        all_ids = ids_dev
+        if world > 1:
+            all_ids = torch.empty((world * T, K_TOP), dtype=torch.int32, device=dev)
+            dist.all_gather_into_tensor(all_ids, ids_dev)
+        cnt = torch.bincount(all_ids.reshape(-1).long(), minlength=E).cpu().numpy()
+        lane_counts.append(cnt[rank * (E // world):(rank + 1) * (E // world)])
     sampler = ClockSampler(local)
     sampler.start()
     moe.profile_enable(True)
@@ -379,7 +409,9 @@ def main():
     gu_ms, gu_n = prof["gate_up"]
     peak, which = peaks()
     achieved = mean_distinct * gu_bytes / (gu_ms / max(gu_n, 1) * 1e-3) / 1e9
-    prefill_lane = WL["bank"] == "exl3" and T * K_TOP >= 24 * (E // world) and T * K_TOP >= 2048
+    tl_ms, tl_n = prof.get("tensor_lane", (0.0, 0))
+    # the tensor-core lane is the dominant kernel once it takes more of the step than the streaming gate/up kernel
+    prefill_lane = WL["bank"] == "exl3" and tl_n > 0 and tl_ms > gu_ms
     layer_bytes = NL * (mean_distinct * logical + (3 * H * I * 2 if WL["shared"] else 0) + T * H * 2 * 2 + T * E * 4)
     value = world * T * args.steps / (ms * 1e-3)
     out = {
@@ -399,7 +431,7 @@ def main():
         "stage_ms_per_step": {k: v[0] / max(args.steps, 1) for k, v in prof.items() if v[1]},
         "e2e": {"value": world * T * args.steps / (ms_host * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": T * H * 2 + T * E * 4, "d2h_bytes_per_step": T * H * 2 + 4},
-        "gpu_launches": NL * ((8 if WL["shared"] else 6) + (4 if world > 1 else 0)) * args.steps,
+        "gpu_launches": NL * own_launches_per_layer(T, world) * args.steps,
         "exchange": None if world == 1 else {
             "exposed_ms_per_step": prof["exchange"][0] / max(args.steps, 1),
             "bytes_sent_per_step_rank0": st.a2a_bytes_sent / max(st.expert_calls, 1),
@@ -410,11 +442,13 @@ def main():
         # prefill-sized call: the tcgen05 lane (gate/up and down launches are timed together); tensor roofline
         pk = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
         tpeak = float(pk.get("bf16_tflops_sustained", 1400.0))
-        flops = 6.0 * H * I * T * K_TOP
-        tf = flops / (gu_ms / max(gu_n, 1) * 1e-3) / 1e12
+        heavy_rows = float(np.mean([int(c[c >= LANE_MIN_ROWS].sum()) for c in lane_counts]))
+        flops = 6.0 * H * I * heavy_rows
+        tf = flops / (tl_ms / max(tl_n, 1) * 1e-3) / 1e12
         out["roofline"] = {"kernel": "exl3_prefill_kernel<2> + <1> (tcgen05 kind::f16)", "bound": "tensor", "achieved": tf,
                            "peak": tpeak, "peak_source": "measured sustained bf16" if pk else "fallback", "unit": "TFLOP/s",
-                           "frac": tf / tpeak, "traffic": None, "flops_per_launch_pair": flops}
+                           "frac": tf / tpeak, "traffic": None, "flops_per_launch_pair": flops,
+                           "rows_in_lane_mean": heavy_rows, "rows_total": T * K_TOP}
     if rank == 0 and world == 1 and not args.no_cpu and WL["bank"] == "exl3":
         import oracle_lib as O
         Tc = args.cpu_tokens

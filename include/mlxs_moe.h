@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define MLXS_MOE_ABI 2026112501
+#define MLXS_MOE_ABI 2026112502
 
 /* refusals (the names mirror the reference's refusal sets: src/sdk_ext/quant.zig:94-111, src/expert/bank.zig:79-101) */
 enum {
@@ -168,7 +168,9 @@ int mlxs_moe_stats_get(mlxs_moe *h, mlxs_moe_stats *out);
  * hooks and kernel bench: src/sdk_ext/profile.zig:1-60, src/arch/glm5_next/exl3_kbench.zig:1-23).  `read` synchronises
  * the pending events, returns the sums since the last read and clears them. */
 enum { MLXS_STAGE_ROUTER = 0, MLXS_STAGE_DISPATCH, MLXS_STAGE_PREP, MLXS_STAGE_GATE_UP, MLXS_STAGE_DOWN,
-       MLXS_STAGE_SHARED, MLXS_STAGE_COMBINE, MLXS_STAGE_EXCHANGE, MLXS_STAGE_COUNT };
+       MLXS_STAGE_SHARED, MLXS_STAGE_COMBINE, MLXS_STAGE_EXCHANGE,
+       MLXS_STAGE_TENSOR_LANE, /* gate/up + down of the experts that took the tensor-core lane */
+       MLXS_STAGE_COUNT };
 typedef struct {
     double ms[MLXS_STAGE_COUNT];
     uint64_t launches[MLXS_STAGE_COUNT];

@@ -14,7 +14,7 @@ from pathlib import Path  # noqa: E402
 
 HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "libmlxs_moe.so"
-ABI = 2026112501
+ABI = 2026112502
 
 BANK_EXL3_K3_MUL1, BANK_MXFP4, BANK_NVFP4 = 0, 1, 2
 SCORE_SQRTSOFTPLUS, SCORE_SIGMOID, SCORE_SOFTMAX = 0, 1, 2
@@ -45,11 +45,11 @@ class Stats(C.Structure):
                 ("device_status", C.c_uint32), ("reserved", C.c_uint32)]
 
 
-STAGES = ["router", "dispatch", "prep", "gate_up", "down", "shared", "combine", "exchange"]
+STAGES = ["router", "dispatch", "prep", "gate_up", "down", "shared", "combine", "exchange", "tensor_lane"]
 
 
 class Profile(C.Structure):
-    _fields_ = [("ms", C.c_double * 8), ("launches", C.c_uint64 * 8)]
+    _fields_ = [("ms", C.c_double * len(STAGES)), ("launches", C.c_uint64 * len(STAGES))]
 
 
 class BankInfo(C.Structure):
@@ -201,7 +201,7 @@ class MoE:
     def profile_read(self):
         p = Profile()
         _check(lib().mlxs_moe_profile_read(self._h, C.byref(p)))
-        return {STAGES[i]: (p.ms[i], p.launches[i]) for i in range(8)}
+        return {STAGES[i]: (p.ms[i], p.launches[i]) for i in range(len(STAGES))}
 
     def stats(self):
         s = Stats()

@@ -139,8 +139,14 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
         if ((rc = h->alloc(&h->xa_gu, (size_t)max_chunks * 2 * kmax * 256)) ||
             (rc = h->alloc(&h->xa_d, (size_t)max_chunks * kmax * 256)) || (rc = h->alloc(&h->ro, A * (H > I ? H : I) * 4)))
             return bail(rc);
-        if (A >= 2048 && exl3_prefill_supported(d)) {  // prefill-sized calls are possible: staging for the tensor-core lane
-            h->pf_max_tiles = (uint32_t)(A / PREFILL_TILE_ROWS + h->e_local + 1);
+        // one decode pass of the streaming lane serves 16 rows, one of the tensor-core lane up to 128 at about 1.5 times
+        // the instructions: from 17 rows on the tensor-core lane is the cheaper one
+        const char* ev = getenv("MLXS_PREFILL_MIN_ROWS");
+        const int min_rows = ev ? atoi(ev) : 17;
+        if (min_rows > 0 && A >= (size_t)min_rows && exl3_prefill_supported(d)) {  // staging for the tensor-core lane
+            h->pf_min_rows = (uint32_t)min_rows;
+            const size_t heavy_max = A / (size_t)min_rows < h->e_local ? A / (size_t)min_rows : h->e_local;
+            h->pf_max_tiles = (uint32_t)(A / PREFILL_TILE_ROWS + heavy_max + 1);
             if ((rc = h->alloc(&h->pf_tiles, (1 + 3 * (size_t)h->pf_max_tiles) * 4)) ||
                 (rc = h->alloc(&h->pf_xa, exl3_prefill_xa_bytes(d, h->pf_max_tiles))) ||
                 (rc = h->alloc(&h->pf_xd, exl3_prefill_xd_bytes(d, h->pf_max_tiles))))
@@ -286,28 +292,21 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
     LayerBank& L = h->layers[layer];
     const uint32_t A = T * top_k;
     if (A > h->rows_cap) return fail(MLXS_E_TOO_MANY_TOKENS, "experts: %u rows exceed the workspace's %u", A, h->rows_cap);
+    // Lane choice per expert by its row count, as the reference decides on logical M (src/sdk_ext/quant.zig:5-6,
+    // src/arch/deepseek_v41/experts.zig:1545-1547): experts with `heavy` rows or more go to the tensor-core lane, which
+    // amortises one decode over up to 128 rows; the others stream through the decode-batch lane.
+    const bool two_lanes = c.bank_kind == MLXS_BANK_EXL3_K3_MUL1 && h->pf_tiles && A >= h->pf_min_rows;
+    const uint32_t heavy = two_lanes ? h->pf_min_rows : 0u;
     {
         StageTimer tm(h, MLXS_STAGE_DISPATCH, st);
         if (A > 2048)
-            CU(launch_dispatch_large(ids_dev, A, n_exp, L.loaded_dev + first, h->tabs, h->chunk_rows, h->group_chunks,
+            CU(launch_dispatch_large(ids_dev, A, n_exp, L.loaded_dev + first, h->tabs, h->chunk_rows, h->group_chunks, heavy,
                                      h->blk_cnt, h->status, st));
         else
-            CU(launch_dispatch(ids_dev, A, n_exp, L.loaded_dev + first, h->tabs, h->chunk_rows, h->group_chunks, h->status, st));
+            CU(launch_dispatch(ids_dev, A, n_exp, L.loaded_dev + first, h->tabs, h->chunk_rows, h->group_chunks, heavy,
+                               h->status, st));
     }
-    // lane choice by rows per expert, as the reference decides on logical M (src/sdk_ext/quant.zig:5-6,
-    // src/arch/deepseek_v41/experts.zig:1545-1547): the tensor-core lane amortises one decode over up to 128 rows
-    static const int pf_min = [] { const char* v = getenv("MLXS_PREFILL_MIN_ROWS"); return v ? atoi(v) : 24; }();
-    const bool prefill_lane = c.bank_kind == MLXS_BANK_EXL3_K3_MUL1 && h->pf_tiles && A >= (uint32_t)pf_min * n_exp;
-    if (prefill_lane) {
-        const Exl3Dims d{c.hidden, c.inter};
-        Exl3PrefillArgs a{};
-        a.L = Exl3Layer{L.gu_code, L.d_code, L.scales}; a.d = d; a.t = h->tabs; a.n_experts = n_exp;
-        a.x = static_cast<const __nv_bfloat16*>(x_dev); a.top_k = top_k; a.tiles = h->pf_tiles; a.max_tiles = h->pf_max_tiles;
-        a.xa = h->pf_xa; a.xd = h->pf_xd; a.ro = static_cast<float*>(ro);
-        a.limit = c.act == MLXS_ACT_SWIGLU_CLAMPED ? c.act_limit : 0.f; a.status = h->status; a.sm_count = h->sm_count;
-        StageTimer tm(h, MLXS_STAGE_GATE_UP, st);
-        CU(launch_exl3_prefill(a, st));
-    } else if (c.bank_kind == MLXS_BANK_EXL3_K3_MUL1) {
+    if (c.bank_kind == MLXS_BANK_EXL3_K3_MUL1) {
         const Exl3Dims d{c.hidden, c.inter};
         Exl3Layer EL{L.gu_code, L.d_code, L.scales};
         {
@@ -325,6 +324,15 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
         {
             StageTimer tm(h, MLXS_STAGE_DOWN, st);
             CU(launch_exl3_down(a, st));
+        }
+        if (two_lanes) {
+            Exl3PrefillArgs pa{};
+            pa.L = EL; pa.d = d; pa.t = h->tabs; pa.n_experts = n_exp; pa.min_rows = heavy;
+            pa.x = static_cast<const __nv_bfloat16*>(x_dev); pa.top_k = top_k; pa.tiles = h->pf_tiles; pa.max_tiles = h->pf_max_tiles;
+            pa.xa = h->pf_xa; pa.xd = h->pf_xd; pa.ro = static_cast<float*>(ro);
+            pa.limit = a.limit; pa.status = h->status; pa.sm_count = h->sm_count;
+            StageTimer tm(h, MLXS_STAGE_TENSOR_LANE, st);
+            CU(launch_exl3_prefill(pa, st));
         }
     } else {
         {
@@ -451,7 +459,7 @@ extern "C" int mlxs_moe_exl3_gemv(mlxs_moe* h, uint32_t layer, uint32_t expert, 
     const uint32_t le = expert - h->e_first;
     // rows all belong to one pseudo expert 0 of a one-expert dispatch
     CU(cudaMemsetAsync(h->ids_ws, 0, (size_t)rows * 4, st));
-    CU(launch_dispatch(h->ids_ws, rows, 1, nullptr, h->tabs, CHUNK_ROWS, GROUP_CHUNKS, h->status, st));
+    CU(launch_dispatch(h->ids_ws, rows, 1, nullptr, h->tabs, CHUNK_ROWS, GROUP_CHUNKS, 0, h->status, st));
     const uint32_t in_dim = proj == 2 ? c.inter : c.hidden, out_dim = proj == 2 ? c.hidden : c.inter;
     CU(launch_exl3_prep_raw(xh_dev, in_dim, h->tabs, h->xa_gu, st));
     const uint32_t* code = proj == 2 ? L.d_code + (size_t)le * exl3_code_words(d) : L.gu_code + (size_t)le * 2 * exl3_code_words(d);

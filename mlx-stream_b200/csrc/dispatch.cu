@@ -11,17 +11,17 @@ constexpr int DTHREADS = 1024;
 
 __global__ void __launch_bounds__(DTHREADS) dispatch_kernel(const int32_t* __restrict__ ids, uint32_t A, uint32_t E,
                                                             const uint8_t* __restrict__ loaded, DispatchTables t,
-                                                            uint32_t CHUNK_ROWS, uint32_t GROUP_CHUNKS,
+                                                            uint32_t CHUNK_ROWS, uint32_t GROUP_CHUNKS, uint32_t HEAVY,
                                                             uint32_t* status) {
     extern __shared__ uint32_t dsm[];
     uint32_t* cnt = dsm;                // [E] counts, then running write positions
     uint32_t* chunk_base = dsm + E;     // [E + 1]
     uint32_t* group_base = chunk_base + E + 1;  // [E + 1]
     uint32_t* blk = group_base + E + 1;  // [DTHREADS] ids of the block being placed
-    __shared__ uint32_t s_distinct;
+    __shared__ uint32_t s_overflow;
     const uint32_t tid = threadIdx.x;
     for (uint32_t e = tid; e < E; e += DTHREADS) cnt[e] = 0;
-    if (tid == 0) s_distinct = 0;
+    if (tid == 0) s_overflow = 0;
     __syncthreads();
     for (uint32_t a = tid; a < A; a += DTHREADS) {
         int32_t id = ids[a];
@@ -37,7 +37,8 @@ __global__ void __launch_bounds__(DTHREADS) dispatch_kernel(const int32_t* __res
             t.offsets[e] = rows;
             chunk_base[e] = chunks;
             group_base[e] = groups;
-            uint32_t nc = (c + CHUNK_ROWS - 1) / CHUNK_ROWS;
+            // experts with HEAVY or more rows belong to the tensor-core lane: no chunks here
+            uint32_t nc = (HEAVY && c >= HEAVY) ? 0u : (c + CHUNK_ROWS - 1) / CHUNK_ROWS;
             rows += c;
             chunks += nc;
             groups += (nc + GROUP_CHUNKS - 1) / GROUP_CHUNKS;
@@ -46,20 +47,19 @@ __global__ void __launch_bounds__(DTHREADS) dispatch_kernel(const int32_t* __res
         t.offsets[E] = rows;
         chunk_base[E] = chunks;
         group_base[E] = groups;
-        if (chunks > t.max_chunks) { atomicMax(status, (uint32_t)ST_WORKLIST_OVERFLOW); chunks = 0; groups = 0; }
+        if (chunks > t.max_chunks) { atomicMax(status, (uint32_t)ST_WORKLIST_OVERFLOW); chunks = 0; groups = 0; s_overflow = 1; }
         t.header[HDR_NCHUNKS] = chunks;
         t.header[HDR_NGROUPS] = groups;
         t.header[HDR_CTR_GU] = 0;
         t.header[HDR_CTR_DOWN] = 0;
         t.header[HDR_CTR_AUX] = 0;
         t.header[HDR_DISTINCT] = distinct;
-        s_distinct = chunks;
     }
     __syncthreads();
-    const bool tables_ok = s_distinct != 0 || A == 0;
-    if (tables_ok) {
+    if (!s_overflow) {
         for (uint32_t e = tid; e < E; e += DTHREADS) {
-            const uint32_t c = cnt[e], nc = (c + CHUNK_ROWS - 1) / CHUNK_ROWS, row0 = t.offsets[e];
+            const uint32_t c = cnt[e], row0 = t.offsets[e];
+            const uint32_t nc = (HEAVY && c >= HEAVY) ? 0u : (c + CHUNK_ROWS - 1) / CHUNK_ROWS;
             for (uint32_t i = 0; i < nc; ++i) {
                 const uint32_t ch = chunk_base[e] + i;
                 t.chunk_expert[ch] = e;
@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(DTHREADS) dispatch_count_kernel(const int32_t*
 }
 __global__ void __launch_bounds__(DTHREADS) dispatch_scan_kernel(uint32_t nblk, uint32_t E, uint32_t* __restrict__ blk_cnt,
                                                                  DispatchTables t, uint32_t CHUNK_ROWS, uint32_t GROUP_CHUNKS,
-                                                                 uint32_t A, uint32_t* status) {
+                                                                 uint32_t HEAVY, uint32_t* status) {
     extern __shared__ uint32_t dsm[];
     uint32_t* cnt = dsm;
     uint32_t* chunk_base = dsm + E;
@@ -141,26 +141,27 @@ __global__ void __launch_bounds__(DTHREADS) dispatch_scan_kernel(uint32_t nblk, 
             t.offsets[e] = rows;
             chunk_base[e] = chunks;
             group_base[e] = groups;
-            const uint32_t nc = (c + CHUNK_ROWS - 1) / CHUNK_ROWS;
+            const uint32_t nc = (HEAVY && c >= HEAVY) ? 0u : (c + CHUNK_ROWS - 1) / CHUNK_ROWS;
             rows += c;
             chunks += nc;
             groups += (nc + GROUP_CHUNKS - 1) / GROUP_CHUNKS;
             distinct += c ? 1u : 0u;
         }
         t.offsets[E] = rows;
-        if (chunks > t.max_chunks) { atomicMax(status, (uint32_t)ST_WORKLIST_OVERFLOW); chunks = 0; groups = 0; }
+        s_ok = 1;
+        if (chunks > t.max_chunks) { atomicMax(status, (uint32_t)ST_WORKLIST_OVERFLOW); chunks = 0; groups = 0; s_ok = 0; }
         t.header[HDR_NCHUNKS] = chunks;
         t.header[HDR_NGROUPS] = groups;
         t.header[HDR_CTR_GU] = 0;
         t.header[HDR_CTR_DOWN] = 0;
         t.header[HDR_CTR_AUX] = 0;
         t.header[HDR_DISTINCT] = distinct;
-        s_ok = chunks != 0 || A == 0;
     }
     __syncthreads();
     if (!s_ok) return;
     for (uint32_t e = tid; e < E; e += DTHREADS) {
-        const uint32_t c = cnt[e], nc = (c + CHUNK_ROWS - 1) / CHUNK_ROWS, row0 = t.offsets[e];
+        const uint32_t c = cnt[e], row0 = t.offsets[e];
+        const uint32_t nc = (HEAVY && c >= HEAVY) ? 0u : (c + CHUNK_ROWS - 1) / CHUNK_ROWS;
         for (uint32_t i = 0; i < nc; ++i) {
             const uint32_t ch = chunk_base[e] + i;
             t.chunk_expert[ch] = e;
@@ -193,19 +194,19 @@ __global__ void __launch_bounds__(DTHREADS) dispatch_place_kernel(const int32_t*
 }
 
 cudaError_t launch_dispatch_large(const int32_t* ids, uint32_t A, uint32_t E, const uint8_t* loaded, DispatchTables t,
-                                  uint32_t chunk_rows, uint32_t group_chunks, uint32_t* blk_cnt, uint32_t* status,
-                                  cudaStream_t st) {
+                                  uint32_t chunk_rows, uint32_t group_chunks, uint32_t heavy, uint32_t* blk_cnt,
+                                  uint32_t* status, cudaStream_t st) {
     const uint32_t nblk = (A + DTHREADS - 1) / DTHREADS;
     dispatch_count_kernel<<<nblk, DTHREADS, E * sizeof(uint32_t), st>>>(ids, A, E, loaded, blk_cnt, status);
-    dispatch_scan_kernel<<<1, DTHREADS, (3 * E + 2) * sizeof(uint32_t), st>>>(nblk, E, blk_cnt, t, chunk_rows, group_chunks, A, status);
+    dispatch_scan_kernel<<<1, DTHREADS, (3 * E + 2) * sizeof(uint32_t), st>>>(nblk, E, blk_cnt, t, chunk_rows, group_chunks, heavy, status);
     dispatch_place_kernel<<<nblk, DTHREADS, 0, st>>>(ids, A, E, blk_cnt, t);
     return cudaGetLastError();
 }
 
 cudaError_t launch_dispatch(const int32_t* ids, uint32_t A, uint32_t E, const uint8_t* loaded, DispatchTables t,
-                            uint32_t chunk_rows, uint32_t group_chunks, uint32_t* status, cudaStream_t st) {
+                            uint32_t chunk_rows, uint32_t group_chunks, uint32_t heavy, uint32_t* status, cudaStream_t st) {
     size_t smem = (size_t)(3 * E + 2 + DTHREADS) * sizeof(uint32_t);
-    dispatch_kernel<<<1, DTHREADS, smem, st>>>(ids, A, E, loaded, t, chunk_rows, group_chunks, status);
+    dispatch_kernel<<<1, DTHREADS, smem, st>>>(ids, A, E, loaded, t, chunk_rows, group_chunks, heavy, status);
     return cudaGetLastError();
 }
 

@@ -190,7 +190,7 @@ int mlxs_ep_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t
     {
         StageTimer tm(h, MLXS_STAGE_EXCHANGE, st);
         if (A) ep_dest_kernel<<<(A + 255) / 256, 256, 0, st>>>(ids_dev, A, c.n_experts, h->e_local, ep->dest, ep->meta, h->status);
-        CU(launch_dispatch(ep->dest, A, W, nullptr, ep->rtab, h->chunk_rows, h->group_chunks, h->status, st));
+        CU(launch_dispatch(ep->dest, A, W, nullptr, ep->rtab, h->chunk_rows, h->group_chunks, 0, h->status, st));
         ep_gather_kernel<<<A ? A : 1, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x_dev), ep->meta, ep->rtab.order,
                                                    ep->rtab.offsets, A, c.top_k, H, W, ep->send_x, ep->send_meta,
                                                    ep->counts_dev);

@@ -74,15 +74,16 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 // plan: row tiles per expert from the dispatch tables
 // ------------------------------------------------------------------------------------------------------------
 // tile table: [0] = n_tiles, then per tile {expert, row0 (sorted row), rows}
-__global__ void pf_plan_kernel(DispatchTables t, uint32_t E, uint32_t max_tiles, uint32_t* __restrict__ tiles,
-                               uint32_t* status) {
+__global__ void pf_plan_kernel(DispatchTables t, uint32_t E, uint32_t min_rows, uint32_t max_tiles,
+                               uint32_t* __restrict__ tiles, uint32_t* status) {
     __shared__ uint32_t base[1025];
     const uint32_t tid = threadIdx.x;
     if (tid == 0) {
         uint32_t n = 0;
         for (uint32_t e = 0; e < E; ++e) {
             base[e] = n;
-            n += (t.offsets[e + 1] - t.offsets[e] + PF_NT - 1) / PF_NT;
+            const uint32_t c = t.offsets[e + 1] - t.offsets[e];
+            n += c >= min_rows ? (c + PF_NT - 1) / PF_NT : 0u;
         }
         if (n > max_tiles) { atomicMax(status, (uint32_t)ST_WORKLIST_OVERFLOW); n = 0; }
         base[E] = n;
@@ -93,7 +94,7 @@ __global__ void pf_plan_kernel(DispatchTables t, uint32_t E, uint32_t max_tiles,
     for (uint32_t e = tid; e < E; e += blockDim.x) {
         // an expert's rows are split evenly over its tiles (a 16-row remainder tile would cost a full decode)
         const uint32_t c = t.offsets[e + 1] - t.offsets[e], r0 = t.offsets[e];
-        const uint32_t nt = (c + PF_NT - 1) / PF_NT;
+        const uint32_t nt = c >= min_rows ? (c + PF_NT - 1) / PF_NT : 0u;
         const uint32_t per = nt ? ((c + nt - 1) / nt + 15) / 16 * 16 : 0;
         for (uint32_t i = 0; i < nt; ++i) {
             uint32_t* d = tiles + 1 + 3 * (base[e] + i);
@@ -185,6 +186,8 @@ __global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParam
     uint8_t* raw_ring = b_ring + PF_B_STAGES * NPROJ * PF_B_BYTES;
     float* zs = reinterpret_cast<float*>(raw_ring + PF_RAW_STAGES * RAW_BYTES);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    // a CTA without work leaves before it takes tensor memory (the whole CTA reads the same count)
+    if (blockIdx.x >= P.tiles[0] * (P.n_blocks / CB)) return;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < PF_RAW_STAGES; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], NCW); }
@@ -417,7 +420,7 @@ bool exl3_prefill_supported(Exl3Dims d) { return (d.I / 128) % 2 == 0 && (d.H / 
 
 cudaError_t launch_exl3_prefill(const Exl3PrefillArgs& a, cudaStream_t st) {
     const uint32_t E = a.n_experts;
-    pf_plan_kernel<<<1, 256, 0, st>>>(a.t, E, a.max_tiles, a.tiles, a.status);
+    pf_plan_kernel<<<1, 256, 0, st>>>(a.t, E, a.min_rows, a.max_tiles, a.tiles, a.status);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     pf_prep_kernel<<<dim3(a.max_tiles, a.d.H / 128), 256, 0, st>>>(a.x, a.top_k, a.d.H, a.L.scales, exl3_scales_per_expert(a.d),

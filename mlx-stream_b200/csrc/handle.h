@@ -47,6 +47,7 @@ struct mlxs_moe {
     uint32_t* pf_tiles = nullptr;
     __half *pf_xa = nullptr, *pf_xd = nullptr;
     uint32_t pf_max_tiles = 0;
+    uint32_t pf_min_rows = 0;   // experts with at least this many rows of a call take the tensor-core lane (0: lane off)
     uint32_t chunk_rows = CHUNK_ROWS, group_chunks = GROUP_CHUNKS;
     __nv_bfloat16* sh_h = nullptr;
     float* sh_gu = nullptr;   // f32 [2][T, I] for the GEMM form of the shared expert

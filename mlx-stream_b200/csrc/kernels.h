@@ -30,14 +30,15 @@ cudaError_t launch_router(const float* logits, const float* bias, int T, int E, 
 
 // ids [A] (A = T*k) -> tables; expert ids outside [0, E) set *status and are treated as expert 0.
 // loaded: optional [E] bytes, 0 = expert not resident -> *status = ST_NOT_LOADED.
-// chunk_rows / group_chunks: rows per chunk and chunks per work item of the bank's kernels (EXL3 4 x 4, FP4 8 x 2)
+// chunk_rows / group_chunks: rows per chunk and chunks per work item of the bank's kernels (EXL3 4 x 4, FP4 8 x 2).
+// heavy > 0: experts with that many rows or more get no chunks (the tensor-core lane serves them from `offsets`).
 cudaError_t launch_dispatch(const int32_t* ids, uint32_t A, uint32_t E, const uint8_t* loaded, DispatchTables t,
-                            uint32_t chunk_rows, uint32_t group_chunks, uint32_t* status, cudaStream_t st);
+                            uint32_t chunk_rows, uint32_t group_chunks, uint32_t heavy, uint32_t* status, cudaStream_t st);
 
 // the same over several CTAs for prefill-sized calls; blk_cnt: scratch [ceil(A/1024)][E]
 cudaError_t launch_dispatch_large(const int32_t* ids, uint32_t A, uint32_t E, const uint8_t* loaded, DispatchTables t,
-                                  uint32_t chunk_rows, uint32_t group_chunks, uint32_t* blk_cnt, uint32_t* status,
-                                  cudaStream_t st);
+                                  uint32_t chunk_rows, uint32_t group_chunks, uint32_t heavy, uint32_t* blk_cnt,
+                                  uint32_t* status, cudaStream_t st);
 
 // ---- EXL3 ----
 struct Exl3Layer {            // one layer's resident bank, in the kernels' layout
@@ -87,6 +88,7 @@ struct Exl3PrefillArgs {
     Exl3Dims d;
     DispatchTables t;
     uint32_t n_experts;      // experts the dispatch ran over
+    uint32_t min_rows;       // only experts with at least this many rows take this lane
     const __nv_bfloat16* x;  // [tokens, H]
     uint32_t top_k;
     uint32_t* tiles;         // [1 + 3 max_tiles] row-tile table (device scratch)

@@ -2,7 +2,7 @@
 //! is the compiled, tested statement of the same ABI).  One declaration per C entry point, same order.
 const std = @import("std");
 
-pub const abi_expected: i32 = 2026112501;
+pub const abi_expected: i32 = 2026112502;
 
 pub const Moe = opaque {};
 

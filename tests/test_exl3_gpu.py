@@ -193,7 +193,8 @@ def test_small_shape_layer_many_seeds():
 
 
 def test_prefill_lane_tcgen05():
-    """Prefill-sized calls take the tensor-core lane (rows per expert >= 24): f16-rounded rotated activations as the
+    """Experts with 17 rows or more take the tensor-core lane, the others of the same call the streaming lane (the
+    reference picks the lane on logical M: src/sdk_ext/quant.zig:5-6): f16-rounded rotated activations as the
     reference's prefill chain (src/kernels/exl3/dsv41_prefill_dig_take2v_5120.metal:57-58), f32 accumulate."""
     case = Exl3Case(512, 256, 4, 2, seed=12, shared=True, max_tokens=1024)
     try:
@@ -205,7 +206,7 @@ def test_prefill_lane_tcgen05():
         logits[:, 3] -= 2.5
         ids, w = case.cpu_route(logits)
         counts = np.bincount(ids.reshape(-1), minlength=4)
-        assert counts.max() > 128 and counts.min() < 128
+        assert counts.max() > 128 and 0 < counts.min() < 17  # both lanes in one call
         ref_y, ref_ro = case.cpu_layer(x, ids, w, want_ro=True)
         ro = case.gpu_routed(x, ids)
         assert case.status() == 0
@@ -215,11 +216,17 @@ def test_prefill_lane_tcgen05():
         assert rel_l2(y, ref_y) < TOL_LAYER
         again = case.gpu_routed(x, ids)
         assert (again.view(np.uint32) == ro.view(np.uint32)).all()
-        # a token's rows do not depend on the batch around it (same lane, other rows removed)
+        # a row does not depend on the batch around it as long as its expert stays in the same lane
         keep = np.arange(0, T, 2)
         sub = case.gpu_routed(x[keep], ids[keep])
-        if np.bincount(ids[keep].reshape(-1), minlength=4).sum() >= 24 * 4:
-            assert (sub.view(np.uint32) == ro[keep].view(np.uint32)).all()
+        sub_counts = np.bincount(ids[keep].reshape(-1), minlength=4)
+        same_lane = (counts >= 17) == (sub_counts >= 17)
+        assert same_lane.sum() >= 2
+        m = same_lane[ids[keep]]
+        assert (sub.view(np.uint32)[m] == ro[keep].view(np.uint32)[m]).all()
+        # the streaming lane alone (fewer rows than the threshold in the whole call) agrees within the f16 rounding
+        few = case.gpu_routed(x[:8], ids[:8])
+        assert max_err_over_rms(few, ro[:8]) < 4e-3
     finally:
         case.close()
 
