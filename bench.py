@@ -147,7 +147,7 @@ def own_launches_per_layer(T, world):
     n = 1                                   # router
     n += 3 if A > 2048 else 1               # dispatch: count / scan / place above 2048 rows, one CTA below
     n += 3                                  # streaming lane: prep, gate/up, down
-    if WL["bank"] == "exl3" and A >= LANE_MIN_ROWS:
+    if A >= LANE_MIN_ROWS:
         n += 4                              # tensor-core lane: plan, prep, gate/up, down
     if WL["shared"]:
         n += 2 if T <= 64 else 1            # skinny kernels, or the activation between the library GEMMs
@@ -411,7 +411,7 @@ def main():
     achieved = mean_distinct * gu_bytes / (gu_ms / max(gu_n, 1) * 1e-3) / 1e9
     tl_ms, tl_n = prof.get("tensor_lane", (0.0, 0))
     # the tensor-core lane is the dominant kernel once it takes more of the step than the streaming gate/up kernel
-    prefill_lane = WL["bank"] == "exl3" and tl_n > 0 and tl_ms > gu_ms
+    prefill_lane = tl_n > 0 and tl_ms > gu_ms
     layer_bytes = NL * (mean_distinct * logical + (3 * H * I * 2 if WL["shared"] else 0) + T * H * 2 * 2 + T * E * 4)
     value = world * T * args.steps / (ms * 1e-3)
     out = {
@@ -445,7 +445,7 @@ def main():
         heavy_rows = float(np.mean([int(c[c >= LANE_MIN_ROWS].sum()) for c in lane_counts]))
         flops = 6.0 * H * I * heavy_rows
         tf = flops / (tl_ms / max(tl_n, 1) * 1e-3) / 1e12
-        out["roofline"] = {"kernel": "exl3_prefill_kernel<2> + <1> (tcgen05 kind::f16)", "bound": "tensor", "achieved": tf,
+        out["roofline"] = {"kernel": ("exl3_prefill_kernel" if WL["bank"] == "exl3" else "fp4_prefill_kernel") + "<gate/up> + <down> (tcgen05 kind::f16)", "bound": "tensor", "achieved": tf,
                            "peak": tpeak, "peak_source": "measured sustained bf16" if pk else "fallback", "unit": "TFLOP/s",
                            "frac": tf / tpeak, "traffic": None, "flops_per_launch_pair": flops,
                            "rows_in_lane_mean": heavy_rows, "rows_total": T * K_TOP}

@@ -139,23 +139,28 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
         if ((rc = h->alloc(&h->xa_gu, (size_t)max_chunks * 2 * kmax * 256)) ||
             (rc = h->alloc(&h->xa_d, (size_t)max_chunks * kmax * 256)) || (rc = h->alloc(&h->ro, A * (H > I ? H : I) * 4)))
             return bail(rc);
-        // one decode pass of the streaming lane serves 16 rows, one of the tensor-core lane up to 128 at about 1.5 times
-        // the instructions: from 17 rows on the tensor-core lane is the cheaper one
-        const char* ev = getenv("MLXS_PREFILL_MIN_ROWS");
-        const int min_rows = ev ? atoi(ev) : 17;
-        if (min_rows > 0 && A >= (size_t)min_rows && exl3_prefill_supported(d)) {  // staging for the tensor-core lane
-            h->pf_min_rows = (uint32_t)min_rows;
-            const size_t heavy_max = A / (size_t)min_rows < h->e_local ? A / (size_t)min_rows : h->e_local;
-            h->pf_max_tiles = (uint32_t)(A / PREFILL_TILE_ROWS + heavy_max + 1);
-            if ((rc = h->alloc(&h->pf_tiles, (1 + 3 * (size_t)h->pf_max_tiles) * 4)) ||
-                (rc = h->alloc(&h->pf_xa, exl3_prefill_xa_bytes(d, h->pf_max_tiles))) ||
-                (rc = h->alloc(&h->pf_xd, exl3_prefill_xd_bytes(d, h->pf_max_tiles))))
-                return bail(rc);
-        }
     } else {
         if ((rc = h->alloc(&h->xa_gu, (size_t)max_chunks * (H / 32) * 512)) ||
             (rc = h->alloc(&h->xa_d, (size_t)max_chunks * (I / 32) * 512)) || (rc = h->alloc(&h->ro, A * H * 4)))
             return bail(rc);
+    }
+    {
+        // Staging for the tensor-core lane.  One decode pass of the streaming lane serves 16 rows, one of the
+        // tensor-core lane up to 128 at about 1.5 times the instructions: from 17 rows on the latter is the cheaper one.
+        const bool exl3 = c->bank_kind == MLXS_BANK_EXL3_K3_MUL1;
+        const char* ev = getenv("MLXS_PREFILL_MIN_ROWS");
+        const int min_rows = ev ? atoi(ev) : 17;
+        const bool supported = exl3 ? exl3_prefill_supported(d) : fp4_prefill_supported(c->hidden, c->inter);
+        if (min_rows > 0 && A >= (size_t)min_rows && supported) {
+            h->pf_min_rows = (uint32_t)min_rows;
+            const size_t heavy_max = A / (size_t)min_rows < h->e_local ? A / (size_t)min_rows : h->e_local;
+            h->pf_max_tiles = (uint32_t)(A / PREFILL_TILE_ROWS + heavy_max + 1);
+            const size_t xa_bytes = exl3 ? exl3_prefill_xa_bytes(d, h->pf_max_tiles) : fp4_prefill_xa_bytes(c->hidden, h->pf_max_tiles);
+            const size_t xd_bytes = exl3 ? exl3_prefill_xd_bytes(d, h->pf_max_tiles) : fp4_prefill_xa_bytes(c->inter, h->pf_max_tiles);
+            if ((rc = h->alloc(&h->pf_tiles, (1 + 3 * (size_t)h->pf_max_tiles) * 4)) || (rc = h->alloc(&h->pf_xa, xa_bytes)) ||
+                (rc = h->alloc(&h->pf_xd, xd_bytes)))
+                return bail(rc);
+        }
     }
     if (c->shared_expert) {
         if ((rc = h->alloc(&h->sh_h, T * I * 2)) || (rc = h->alloc(&h->sh_out, T * H * 4))) return bail(rc);
@@ -205,6 +210,9 @@ extern "C" int mlxs_moe_load_expert(mlxs_moe* h, uint32_t layer, uint32_t expert
         CU(cudaMemcpyAsync(h->staging, record, h->logical_bytes, cudaMemcpyHostToDevice, 0));
         src = h->staging;
     }
+    // the expert's entry of the per-expert table: 1 = resident; the FP4 repack may raise it to 3 (see takes_tensor_lane)
+    const uint8_t one = 1;
+    CU(cudaMemcpyAsync(L.loaded_dev + expert, &one, 1, cudaMemcpyHostToDevice, 0));
     if (h->cfg.bank_kind == MLXS_BANK_EXL3_K3_MUL1) {
         const Exl3Dims d{h->cfg.hidden, h->cfg.inter};
         CU(launch_exl3_repack(src, d, L.gu_code + (size_t)le * 2 * exl3_code_words(d),
@@ -214,10 +222,8 @@ extern "C" int mlxs_moe_load_expert(mlxs_moe* h, uint32_t layer, uint32_t expert
         CU(launch_fp4_repack(src, h->cfg.hidden, h->cfg.inter, nv,
                              L.f4_gu + (size_t)le * fp4_stream_bytes_per_expert(h->cfg.hidden, h->cfg.inter, nv, 0),
                              L.f4_dn + (size_t)le * fp4_stream_bytes_per_expert(h->cfg.hidden, h->cfg.inter, nv, 1),
-                             L.f4_gscale + (size_t)le * 3, 0));
+                             L.f4_gscale + (size_t)le * 3, L.loaded_dev + expert, 0));
     }
-    const uint8_t one = 1;
-    CU(cudaMemcpyAsync(L.loaded_dev + expert, &one, 1, cudaMemcpyHostToDevice, 0));
     CU(cudaStreamSynchronize(0));
     L.loaded[expert] = 1;
     return MLXS_OK;
@@ -295,7 +301,7 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
     // Lane choice per expert by its row count, as the reference decides on logical M (src/sdk_ext/quant.zig:5-6,
     // src/arch/deepseek_v41/experts.zig:1545-1547): experts with `heavy` rows or more go to the tensor-core lane, which
     // amortises one decode over up to 128 rows; the others stream through the decode-batch lane.
-    const bool two_lanes = c.bank_kind == MLXS_BANK_EXL3_K3_MUL1 && h->pf_tiles && A >= h->pf_min_rows;
+    const bool two_lanes = h->pf_tiles && A >= h->pf_min_rows;
     const uint32_t heavy = two_lanes ? h->pf_min_rows : 0u;
     {
         StageTimer tm(h, MLXS_STAGE_DISPATCH, st);
@@ -351,6 +357,16 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
         {
             StageTimer tm(h, MLXS_STAGE_DOWN, st);
             CU(launch_fp4_gemv(a, 1, st));
+        }
+        if (two_lanes) {
+            Fp4PrefillArgs pa{};
+            pa.gu = a.gu; pa.dn = a.dn; pa.gscale = a.gscale; pa.nv = a.nv; pa.H = a.H; pa.I = a.I; pa.t = h->tabs;
+            pa.n_experts = n_exp; pa.lane_flags = L.loaded_dev + first; pa.min_rows = heavy;
+            pa.x = static_cast<const __nv_bfloat16*>(x_dev); pa.top_k = top_k; pa.tiles = h->pf_tiles; pa.max_tiles = h->pf_max_tiles;
+            pa.xa = reinterpret_cast<uint16_t*>(h->pf_xa); pa.xd = reinterpret_cast<uint16_t*>(h->pf_xd);
+            pa.ro = ro; pa.ro_bf16 = ro_bf16; pa.limit = a.limit; pa.status = h->status; pa.sm_count = h->sm_count;
+            StageTimer tm(h, MLXS_STAGE_TENSOR_LANE, st);
+            CU(launch_fp4_prefill(pa, st));
         }
     }
     h->stats.expert_calls += 1;

@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(DTHREADS) dispatch_kernel(const int32_t* __res
             chunk_base[e] = chunks;
             group_base[e] = groups;
             // experts with HEAVY or more rows belong to the tensor-core lane: no chunks here
-            uint32_t nc = (HEAVY && c >= HEAVY) ? 0u : (c + CHUNK_ROWS - 1) / CHUNK_ROWS;
+            uint32_t nc = takes_tensor_lane(c, HEAVY, loaded, e) ? 0u : (c + CHUNK_ROWS - 1) / CHUNK_ROWS;
             rows += c;
             chunks += nc;
             groups += (nc + GROUP_CHUNKS - 1) / GROUP_CHUNKS;
@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(DTHREADS) dispatch_kernel(const int32_t* __res
     if (!s_overflow) {
         for (uint32_t e = tid; e < E; e += DTHREADS) {
             const uint32_t c = cnt[e], row0 = t.offsets[e];
-            const uint32_t nc = (HEAVY && c >= HEAVY) ? 0u : (c + CHUNK_ROWS - 1) / CHUNK_ROWS;
+            const uint32_t nc = takes_tensor_lane(c, HEAVY, loaded, e) ? 0u : (c + CHUNK_ROWS - 1) / CHUNK_ROWS;
             for (uint32_t i = 0; i < nc; ++i) {
                 const uint32_t ch = chunk_base[e] + i;
                 t.chunk_expert[ch] = e;
@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(DTHREADS) dispatch_count_kernel(const int32_t*
 }
 __global__ void __launch_bounds__(DTHREADS) dispatch_scan_kernel(uint32_t nblk, uint32_t E, uint32_t* __restrict__ blk_cnt,
                                                                  DispatchTables t, uint32_t CHUNK_ROWS, uint32_t GROUP_CHUNKS,
-                                                                 uint32_t HEAVY, uint32_t* status) {
+                                                                 uint32_t HEAVY, const uint8_t* __restrict__ loaded, uint32_t* status) {
     extern __shared__ uint32_t dsm[];
     uint32_t* cnt = dsm;
     uint32_t* chunk_base = dsm + E;
@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(DTHREADS) dispatch_scan_kernel(uint32_t nblk, 
             t.offsets[e] = rows;
             chunk_base[e] = chunks;
             group_base[e] = groups;
-            const uint32_t nc = (HEAVY && c >= HEAVY) ? 0u : (c + CHUNK_ROWS - 1) / CHUNK_ROWS;
+            const uint32_t nc = takes_tensor_lane(c, HEAVY, loaded, e) ? 0u : (c + CHUNK_ROWS - 1) / CHUNK_ROWS;
             rows += c;
             chunks += nc;
             groups += (nc + GROUP_CHUNKS - 1) / GROUP_CHUNKS;
@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(DTHREADS) dispatch_scan_kernel(uint32_t nblk, 
     if (!s_ok) return;
     for (uint32_t e = tid; e < E; e += DTHREADS) {
         const uint32_t c = cnt[e], row0 = t.offsets[e];
-        const uint32_t nc = (HEAVY && c >= HEAVY) ? 0u : (c + CHUNK_ROWS - 1) / CHUNK_ROWS;
+        const uint32_t nc = takes_tensor_lane(c, HEAVY, loaded, e) ? 0u : (c + CHUNK_ROWS - 1) / CHUNK_ROWS;
         for (uint32_t i = 0; i < nc; ++i) {
             const uint32_t ch = chunk_base[e] + i;
             t.chunk_expert[ch] = e;
@@ -198,7 +198,7 @@ cudaError_t launch_dispatch_large(const int32_t* ids, uint32_t A, uint32_t E, co
                                   uint32_t* status, cudaStream_t st) {
     const uint32_t nblk = (A + DTHREADS - 1) / DTHREADS;
     dispatch_count_kernel<<<nblk, DTHREADS, E * sizeof(uint32_t), st>>>(ids, A, E, loaded, blk_cnt, status);
-    dispatch_scan_kernel<<<1, DTHREADS, (3 * E + 2) * sizeof(uint32_t), st>>>(nblk, E, blk_cnt, t, chunk_rows, group_chunks, heavy, status);
+    dispatch_scan_kernel<<<1, DTHREADS, (3 * E + 2) * sizeof(uint32_t), st>>>(nblk, E, blk_cnt, t, chunk_rows, group_chunks, heavy, loaded, status);
     dispatch_place_kernel<<<nblk, DTHREADS, 0, st>>>(ids, A, E, blk_cnt, t);
     return cudaGetLastError();
 }

@@ -20,6 +20,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "umma.cuh"
 
 namespace mlxs {
 
@@ -37,45 +38,12 @@ constexpr int PF_SBO = 128;                     // byte distance of two core mat
 constexpr int PF_EPI_ROWS = 32;                 // rows per epilogue batch
 constexpr int PF_ZS_STRIDE = 132;
 
-// ---- tcgen05 wrappers ----
-__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo) {
-    // K-major, no swizzle: start address, leading (K) byte offset, stride (M/N) byte offset, all >> 4; version 1
-    return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) |
-           ((uint64_t)((PF_SBO >> 4) & 0x3FFFu) << 32) | (1ull << 46);
-}
-__device__ __forceinline__ uint32_t umma_idesc_f16(uint32_t n) {
-    // D f32 (bits 4-5 = 1), A = B = f16 (0), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
-    return (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24);
-}
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n\t"
-        "tcgen05.wait::ld.sync.aligned;"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr)
-        : "memory");
-}
-
 // ------------------------------------------------------------------------------------------------------------
 // plan: row tiles per expert from the dispatch tables
 // ------------------------------------------------------------------------------------------------------------
 // tile table: [0] = n_tiles, then per tile {expert, row0 (sorted row), rows}
-__global__ void pf_plan_kernel(DispatchTables t, uint32_t E, uint32_t min_rows, uint32_t max_tiles,
-                               uint32_t* __restrict__ tiles, uint32_t* status) {
+__global__ void pf_plan_kernel(DispatchTables t, uint32_t E, const uint8_t* __restrict__ flags, uint32_t min_rows,
+                               uint32_t max_tiles, uint32_t* __restrict__ tiles, uint32_t* status) {
     __shared__ uint32_t base[1025];
     const uint32_t tid = threadIdx.x;
     if (tid == 0) {
@@ -83,7 +51,7 @@ __global__ void pf_plan_kernel(DispatchTables t, uint32_t E, uint32_t min_rows, 
         for (uint32_t e = 0; e < E; ++e) {
             base[e] = n;
             const uint32_t c = t.offsets[e + 1] - t.offsets[e];
-            n += c >= min_rows ? (c + PF_NT - 1) / PF_NT : 0u;
+            n += takes_tensor_lane(c, min_rows, flags, e) ? (c + PF_NT - 1) / PF_NT : 0u;
         }
         if (n > max_tiles) { atomicMax(status, (uint32_t)ST_WORKLIST_OVERFLOW); n = 0; }
         base[E] = n;
@@ -94,7 +62,7 @@ __global__ void pf_plan_kernel(DispatchTables t, uint32_t E, uint32_t min_rows, 
     for (uint32_t e = tid; e < E; e += blockDim.x) {
         // an expert's rows are split evenly over its tiles (a 16-row remainder tile would cost a full decode)
         const uint32_t c = t.offsets[e + 1] - t.offsets[e], r0 = t.offsets[e];
-        const uint32_t nt = c >= min_rows ? (c + PF_NT - 1) / PF_NT : 0u;
+        const uint32_t nt = takes_tensor_lane(c, min_rows, flags, e) ? (c + PF_NT - 1) / PF_NT : 0u;
         const uint32_t per = nt ? ((c + nt - 1) / nt + 15) / 16 * 16 : 0;
         for (uint32_t i = 0; i < nt; ++i) {
             uint32_t* d = tiles + 1 + 3 * (base[e] + i);
@@ -199,10 +167,7 @@ __global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParam
         s_abort = 0;
         mbar_fence_init();
     }
-    if (warp == 0) {  // tensor memory for the accumulators (one warp allocates and later frees)
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"((uint32_t)TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
+    if (warp == 0) tmem_alloc(&s_tmem, TMEM_COLS);  // tensor memory for the accumulators (one warp allocates and frees)
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -243,7 +208,7 @@ __global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParam
             uint32_t bit = 0, nitem = 0;
             for (uint32_t item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++nitem) {
                 const uint32_t tile = item / nbg, rows = P.tiles[3 + 3 * tile];
-                const uint32_t idesc = umma_idesc_f16((rows + 15) / 16 * 16);
+                const uint32_t idesc = umma_idesc(UMMA_F16, (rows + 15) / 16 * 16);
                 if (!mbar_wait_bounded(&acc_empty, (nitem & 1u) ^ 1u, &s_abort, 64)) { give_up(ST_WAIT_EMPTY); break; }
                 tc_fence_after();
                 bool ok = true;
@@ -261,8 +226,8 @@ __global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParam
                         const uint32_t b0 = smem_u32(b_ring + (bs * NPROJ + p) * PF_B_BYTES);
 #pragma unroll
                         for (int i = 0; i < PF_KS / 16; ++i)
-                            umma_f16(tmem + gq * PF_NT, umma_smem_desc(a0 + i * 2 * PF_LBO_A, PF_LBO_A),
-                                     umma_smem_desc(b0 + i * 2 * PF_LBO_B, PF_LBO_B), idesc, (ks | (uint32_t)i) ? 1u : 0u);
+                            umma_f16(tmem + gq * PF_NT, umma_smem_desc(a0 + i * 2 * PF_LBO_A, PF_LBO_A, PF_SBO),
+                                     umma_smem_desc(b0 + i * 2 * PF_LBO_B, PF_LBO_B, PF_SBO), idesc, (ks | (uint32_t)i) ? 1u : 0u);
                     }
                     umma_commit(&a_empty[as]);  // the stage's operands are free once these MMAs have read them
                     umma_commit(&b_empty[bs]);
@@ -408,7 +373,7 @@ __global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParam
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TMEM_COLS) : "memory");
+    if (warp == 0) tmem_free(tmem, TMEM_COLS);
 }
 
 static size_t pf_smem_bytes(int nproj) {
@@ -418,10 +383,14 @@ static size_t pf_smem_bytes(int nproj) {
 
 bool exl3_prefill_supported(Exl3Dims d) { return (d.I / 128) % 2 == 0 && (d.H / 128) % 4 == 0; }
 
+cudaError_t launch_prefill_plan(DispatchTables t, uint32_t n_experts, const uint8_t* lane_flags, uint32_t min_rows,
+                                uint32_t max_tiles, uint32_t* tiles, uint32_t* status, cudaStream_t st) {
+    pf_plan_kernel<<<1, 256, 0, st>>>(t, n_experts, lane_flags, min_rows, max_tiles, tiles, status);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_exl3_prefill(const Exl3PrefillArgs& a, cudaStream_t st) {
-    const uint32_t E = a.n_experts;
-    pf_plan_kernel<<<1, 256, 0, st>>>(a.t, E, a.min_rows, a.max_tiles, a.tiles, a.status);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_prefill_plan(a.t, a.n_experts, nullptr, a.min_rows, a.max_tiles, a.tiles, a.status, st);
     if (e != cudaSuccess) return e;
     pf_prep_kernel<<<dim3(a.max_tiles, a.d.H / 128), 256, 0, st>>>(a.x, a.top_k, a.d.H, a.L.scales, exl3_scales_per_expert(a.d),
                                                                   a.t, a.tiles, a.xa);

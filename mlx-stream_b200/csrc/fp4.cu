@@ -35,7 +35,8 @@ __host__ __device__ inline uint32_t f4_scale_stage_bytes(bool nv) { return nv ? 
 //   MXFP4 scales [g 8][r 2] bytes; NVFP4 scales [blk 2][g 8][r 2] bytes.  lane = (g, c): word c of the 32-block for
 //   rows 16 warp + g (r = 0) and 16 warp + g + 8 (r = 1).
 __global__ void fp4_repack_kernel(const uint8_t* __restrict__ rec, uint32_t H, uint32_t I, int nv,
-                                  uint8_t* __restrict__ gu, uint8_t* __restrict__ dn, float* __restrict__ gscale) {
+                                  uint8_t* __restrict__ gu, uint8_t* __restrict__ dn, float* __restrict__ gscale,
+                                  uint8_t* lane_flag) {
     const size_t wbytes = (size_t)H * I / 2, sbytes = (size_t)H * I / (nv ? 16 : 32), tail = nv ? 4 : 0;
     const size_t part = wbytes + sbytes + tail;
     const uint32_t sstage = f4_scale_stage_bytes(nv != 0);
@@ -65,14 +66,18 @@ __global__ void fp4_repack_kernel(const uint8_t* __restrict__ rec, uint32_t H, u
             const uint32_t ks = blk32 / 4, sb = blk32 % 4;
             uint8_t* d = dst + ((size_t)nb * nstage + ks) * stage_bytes + (size_t)np * F4_W_STAGE + (size_t)pp * sstage;
             if (nv) d[(((wr * 4 + sb) * 2 + half) * 8 + g) * 2 + r] = s[i];
-            else d[((wr * 4 + sb) * 8 + g) * 2 + r] = s[i];
+            else {
+                d[((wr * 4 + sb) * 8 + g) * 2 + r] = s[i];
+                // the tensor-core lane forms 2^(b-1) as a bf16: b > 128 keeps this expert in the streaming lane
+                if (lane_flag && s[i] > 128u) *lane_flag = 3;
+            }
         }
     }
 }
 
 cudaError_t launch_fp4_repack(const uint8_t* record_dev, uint32_t H, uint32_t I, int nv, uint8_t* gu_e, uint8_t* dn_e,
-                              float* gscale_e, cudaStream_t st) {
-    fp4_repack_kernel<<<592, 256, 0, st>>>(record_dev, H, I, nv, gu_e, dn_e, gscale_e);
+                              float* gscale_e, uint8_t* lane_flag, cudaStream_t st) {
+    fp4_repack_kernel<<<592, 256, 0, st>>>(record_dev, H, I, nv, gu_e, dn_e, gscale_e, lane_flag);
     return cudaGetLastError();
 }
 

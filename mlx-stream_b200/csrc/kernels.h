@@ -83,6 +83,14 @@ cudaError_t launch_exl3_raw(const uint32_t* code_e, uint32_t in_dim, uint32_t ou
 
 // prefill-sized batches: tcgen05 MMA over trellis tiles decoded to f16 in shared memory (exl3_prefill.cu)
 constexpr int PREFILL_TILE_ROWS = 128;
+// An expert's lane in a call: the tensor-core lane when it has `min_rows` rows or more, unless its entry of the
+// per-expert table (1 = resident, bit 1 = its weights are outside that lane's exact range) says otherwise.
+__host__ __device__ inline bool takes_tensor_lane(uint32_t rows, uint32_t min_rows, const uint8_t* flags, uint32_t e) {
+    return min_rows && rows >= min_rows && !(flags && (flags[e] & 2u));
+}
+// row tiles {expert, first sorted row, rows} of the experts that take the tensor-core lane: tiles[0] = count
+cudaError_t launch_prefill_plan(DispatchTables t, uint32_t n_experts, const uint8_t* lane_flags, uint32_t min_rows,
+                                uint32_t max_tiles, uint32_t* tiles, uint32_t* status, cudaStream_t st);
 struct Exl3PrefillArgs {
     Exl3Layer L;
     Exl3Dims d;
@@ -113,8 +121,9 @@ static inline size_t fp4_stream_bytes_per_expert(uint32_t H, uint32_t I, int nv,
     return (size_t)(H / 128) * (I / 128) * per_stage;
 }
 // record (device, reference layout) -> the expert's slices of the gate/up stream, the down stream and the global scales
+// lane_flag: the expert's entry of the per-expert table; set to 3 when an MXFP4 block scale exceeds 2^1
 cudaError_t launch_fp4_repack(const uint8_t* record_dev, uint32_t H, uint32_t I, int nv, uint8_t* gu_e, uint8_t* dn_e,
-                              float* gscale_e, cudaStream_t st);
+                              float* gscale_e, uint8_t* lane_flag, cudaStream_t st);
 // x bf16 [T, H] -> f16 rows in the kernels' B-fragment order: [chunk][H/32][128] u32
 cudaError_t launch_fp4_prep(const __nv_bfloat16* x, uint32_t top_k, uint32_t H, DispatchTables t, uint32_t* xa,
                             cudaStream_t st);
@@ -134,6 +143,32 @@ struct Fp4GemvArgs {
     int sm_count;
 };
 cudaError_t launch_fp4_gemv(const Fp4GemvArgs& a, int down, cudaStream_t st);
+// experts with many rows: tcgen05 MMA over codes decoded to 16-bit operands in shared memory (fp4_prefill.cu)
+struct Fp4PrefillArgs {
+    const uint8_t* gu;       // the streams of Fp4GemvArgs
+    const uint8_t* dn;
+    const float* gscale;
+    int nv;
+    uint32_t H, I;
+    DispatchTables t;
+    uint32_t n_experts;      // experts the dispatch ran over
+    const uint8_t* lane_flags;  // [n_experts] per-expert table of takes_tensor_lane
+    uint32_t min_rows;
+    const __nv_bfloat16* x;  // [tokens, H]
+    uint32_t top_k;
+    uint32_t* tiles;         // [1 + 3 max_tiles]
+    uint32_t max_tiles;
+    uint16_t* xa;            // [max_tiles][128 x H] rows in the MMA's B-operand order (bf16 MXFP4, f16 NVFP4)
+    uint16_t* xd;            // [max_tiles][128 x I]
+    void* ro;                // [A, H] bf16 (chain combine) or f32
+    int ro_bf16;
+    float limit;
+    uint32_t* status;
+    int sm_count;
+};
+static inline size_t fp4_prefill_xa_bytes(uint32_t H, uint32_t max_tiles) { return (size_t)max_tiles * H * PREFILL_TILE_ROWS * 2; }
+cudaError_t launch_fp4_prefill(const Fp4PrefillArgs& a, cudaStream_t st);
+bool fp4_prefill_supported(uint32_t H, uint32_t I);
 
 // ---- shared expert (bf16 dense) + combine ----
 cudaError_t launch_shared_expert(const __nv_bfloat16* x, const __nv_bfloat16* w1, const __nv_bfloat16* w3,

@@ -68,3 +68,63 @@ def test_fp4_f32_combine_mode():
         assert rel_l2(y, case.cpu_layer(x, ids, w)) < TOL
     finally:
         case.close()
+
+
+def _skewed_batch(case, T, seed):
+    """Expert 0 takes every token, expert 3 a handful: both lanes and several row tiles in one call."""
+    x, logits = case.inputs(T, seed=seed)
+    logits[:, 0] += 3.0
+    logits[:, 3] -= 2.5
+    ids, w = case.cpu_route(logits)
+    return x, ids, w
+
+
+@pytest.mark.parametrize("cls,limit,shared", [(Mxfp4Case, 0.0, False), (Nvfp4Case, 10.0, True)])
+def test_fp4_tensor_lane(cls, limit, shared):
+    """Experts with 17 rows or more go through the tcgen05 lane (the reference's sorted quantised GEMM,
+    src/arch/mimo_v2/math.zig:426-447): same decoded weights and rounding chain as the streaming lane, f32 accumulate."""
+    case = cls(512, 256, 4, 2, seed=9, shared=shared, scoring=O.SCORE_SIGMOID, max_tokens=512, routed_scale=1.0,
+               limit=limit, chain=True)
+    try:
+        T = 300
+        x, ids, w = _skewed_batch(case, T, seed=31)
+        counts = np.bincount(ids.reshape(-1), minlength=4)
+        assert counts.max() > 256 and 0 < counts.min() < 17
+        y = case.gpu_experts(x, ids, w)
+        assert case.status() == 0
+        assert rel_l2(y, case.cpu_layer(x, ids, w)) < TOL
+        # the unweighted rows: the whole call against the same rows taken 8 tokens at a time (16 rows: streaming lane only)
+        ro = case.gpu_routed(x, ids)
+        assert np.isfinite(ro).all()
+        parts = [case.gpu_routed(x[i:i + 8], ids[i:i + 8]) for i in range(0, T, 8)]
+        ro_s = np.concatenate(parts, axis=0)
+        # both lanes multiply the same exact operands; a bf16 rounding boundary of the gate/up chain may fall either way
+        assert rel_l2(ro, ro_s) < 2e-3
+        again = case.gpu_routed(x, ids)
+        assert (again.view(np.uint32) == ro.view(np.uint32)).all()
+        assert case.status() == 0
+    finally:
+        case.close()
+
+
+def test_mxfp4_wide_scale_stays_in_streaming_lane():
+    """The tensor-core lane builds 2^(b-1) as a bf16, which exists for scale bytes b <= 128; an expert that holds a
+    larger byte is marked at load and streams, whatever its row count."""
+    case = Mxfp4Case(512, 256, 4, 2, seed=4, shared=False, scoring=O.SCORE_SIGMOID, max_tokens=256, routed_scale=1.0,
+                     limit=0.0, chain=True)
+    try:
+        H, I = case.H, case.I
+        rec = case.records[0].copy()
+        wbytes, sbytes = H * I // 2, H * I // 32
+        s0 = rec[wbytes:wbytes + sbytes]            # the gate projection's E8M0 bytes
+        s0[::97] = 131                              # 2^4: beyond the lane's range
+        case.records[0] = rec
+        case.moe.load_expert(0, 0, rec.ctypes.data, rec.size, on_device=False)
+        x, ids, w = _skewed_batch(case, 100, seed=12)
+        assert np.bincount(ids.reshape(-1), minlength=4)[0] >= 90
+        y = case.gpu_experts(x, ids, w)
+        assert case.status() == 0
+        assert np.isfinite(y).all()
+        assert rel_l2(y, case.cpu_layer(x, ids, w)) < TOL
+    finally:
+        case.close()
