@@ -155,9 +155,9 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
             h->pf_min_rows = (uint32_t)min_rows;
             const size_t heavy_max = A / (size_t)min_rows < h->e_local ? A / (size_t)min_rows : h->e_local;
             h->pf_max_tiles = (uint32_t)(A / PREFILL_TILE_ROWS + heavy_max + 1);
-            const size_t xa_bytes = exl3 ? exl3_prefill_xa_bytes(d, h->pf_max_tiles) : fp4_prefill_xa_bytes(c->hidden, h->pf_max_tiles);
-            const size_t xd_bytes = exl3 ? exl3_prefill_xd_bytes(d, h->pf_max_tiles) : fp4_prefill_xa_bytes(c->inter, h->pf_max_tiles);
-            if ((rc = h->alloc(&h->pf_tiles, (1 + 3 * (size_t)h->pf_max_tiles) * 4)) || (rc = h->alloc(&h->pf_xa, xa_bytes)) ||
+            const size_t xa_bytes = exl3 ? exl3_prefill_xa_bytes(d, h->pf_max_tiles) : fp4_prefill_xa_bytes(c->hidden, A, h->pf_max_tiles);
+            const size_t xd_bytes = exl3 ? exl3_prefill_xd_bytes(d, h->pf_max_tiles) : fp4_prefill_xa_bytes(c->inter, A, h->pf_max_tiles);
+            if ((rc = h->alloc(&h->pf_tiles, prefill_tile_words(h->pf_max_tiles) * 4)) || (rc = h->alloc(&h->pf_xa, xa_bytes)) ||
                 (rc = h->alloc(&h->pf_xd, xd_bytes)))
                 return bail(rc);
         }

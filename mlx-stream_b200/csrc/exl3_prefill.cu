@@ -41,32 +41,45 @@ constexpr int PF_ZS_STRIDE = 132;
 // ------------------------------------------------------------------------------------------------------------
 // plan: row tiles per expert from the dispatch tables
 // ------------------------------------------------------------------------------------------------------------
-// tile table: [0] = n_tiles, then per tile {expert, row0 (sorted row), rows}
+// Tile table: [0] = tiles of list 0 (experts with up to cap0 rows: one tile each; with cap1 = 0 every expert, in tiles
+// of up to cap0 rows), [1] = tiles of list 1 (the other experts, tiles of up to cap1 rows), then the entries {expert,
+// first sorted row, rows, first staging row}: list 0 from entry 0, list 1 from entry max_tiles.  An expert's rows are
+// split evenly over its tiles (a 16-row remainder tile would cost a full decode).
+// Staging rows: a tile's rows padded to 16, tiles in sorted order, so tile number n starts at its first row + 16 n.
 __global__ void pf_plan_kernel(DispatchTables t, uint32_t E, const uint8_t* __restrict__ flags, uint32_t min_rows,
-                               uint32_t max_tiles, uint32_t* __restrict__ tiles, uint32_t* status) {
-    __shared__ uint32_t base[1025];
+                               uint32_t cap0, uint32_t cap1, uint32_t max_tiles, uint32_t* __restrict__ tiles,
+                               uint32_t* status) {
+    __shared__ uint32_t base0[1025], base1[1025];
     const uint32_t tid = threadIdx.x;
     if (tid == 0) {
-        uint32_t n = 0;
+        uint32_t n0 = 0, n1 = 0;
         for (uint32_t e = 0; e < E; ++e) {
-            base[e] = n;
+            base0[e] = n0;
+            base1[e] = n1;
             const uint32_t c = t.offsets[e + 1] - t.offsets[e];
-            n += takes_tensor_lane(c, min_rows, flags, e) ? (c + PF_NT - 1) / PF_NT : 0u;
+            if (!takes_tensor_lane(c, min_rows, flags, e)) continue;
+            if (cap1 && c > cap0) n1 += (c + cap1 - 1) / cap1;
+            else n0 += (c + cap0 - 1) / cap0;
         }
-        if (n > max_tiles) { atomicMax(status, (uint32_t)ST_WORKLIST_OVERFLOW); n = 0; }
-        base[E] = n;
-        tiles[0] = n;
+        if (n0 > max_tiles || n1 > max_tiles) { atomicMax(status, (uint32_t)ST_WORKLIST_OVERFLOW); n0 = 0; n1 = 0; }
+        base0[E] = n0;
+        base1[E] = n1;
+        tiles[0] = n0;
+        tiles[1] = n1;
     }
     __syncthreads();
-    if (base[E] == 0) return;
+    if (base0[E] + base1[E] == 0) return;
     for (uint32_t e = tid; e < E; e += blockDim.x) {
-        // an expert's rows are split evenly over its tiles (a 16-row remainder tile would cost a full decode)
         const uint32_t c = t.offsets[e + 1] - t.offsets[e], r0 = t.offsets[e];
-        const uint32_t nt = takes_tensor_lane(c, min_rows, flags, e) ? (c + PF_NT - 1) / PF_NT : 0u;
-        const uint32_t per = nt ? ((c + nt - 1) / nt + 15) / 16 * 16 : 0;
+        if (!takes_tensor_lane(c, min_rows, flags, e)) continue;
+        const bool list1 = cap1 && c > cap0;
+        const uint32_t cap = list1 ? cap1 : cap0;
+        const uint32_t nt = (c + cap - 1) / cap;
+        const uint32_t per = ((c + nt - 1) / nt + 15) / 16 * 16;
+        const uint32_t first = list1 ? base1[e] : base0[e], ordinal = base0[e] + base1[e];
         for (uint32_t i = 0; i < nt; ++i) {
-            uint32_t* d = tiles + 1 + 3 * (base[e] + i);
-            d[0] = e; d[1] = r0 + i * per; d[2] = min(per, c - i * per);
+            uint32_t* d = prefill_tile(tiles, list1 ? 1 : 0, max_tiles, first + i);
+            d[0] = e; d[1] = r0 + i * per; d[2] = min(per, c - i * per); d[3] = r0 + i * per + 16 * (ordinal + i);
         }
     }
 }
@@ -84,7 +97,8 @@ __global__ void __launch_bounds__(256) pf_prep_kernel(const __nv_bfloat16* __res
                                                       __half* __restrict__ xa) {
     const uint32_t tile = blockIdx.x;
     if (tile >= tiles[0]) return;
-    const uint32_t e = tiles[1 + 3 * tile], row0 = tiles[2 + 3 * tile], rows = tiles[3 + 3 * tile];
+    const uint32_t* te = prefill_tile(tiles, 0, 0, tile);
+    const uint32_t e = te[0], row0 = te[1], rows = te[2];
     const uint32_t rows16 = (rows + 15) / 16 * 16, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, b = blockIdx.y;
     const float S = __uint_as_float(SCALE_BITS);
     const uint32_t nstage = H / PF_KS;
@@ -183,7 +197,7 @@ __global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParam
         if (lane == 0) {
             uint32_t rit = 0, bit = 0;
             for (uint32_t item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
-                const uint32_t tile = item / nbg, nb0 = (item % nbg) * CB, expert = P.tiles[1 + 3 * tile];
+                const uint32_t tile = item / nbg, nb0 = (item % nbg) * CB, expert = prefill_tile(P.tiles, 0, 0, tile)[0];
                 const uint32_t* wsrc = P.code + (size_t)expert * P.expert_stride_words + (size_t)nb0 * P.nkt * KSTRIDE;
                 for (uint32_t ks = 0; ks < nstage; ++ks, ++rit, ++bit) {
                     const uint32_t rs = rit % PF_RAW_STAGES, rph = (rit / PF_RAW_STAGES) & 1u;
@@ -207,7 +221,7 @@ __global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParam
         if (lane == 0) {
             uint32_t bit = 0, nitem = 0;
             for (uint32_t item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++nitem) {
-                const uint32_t tile = item / nbg, rows = P.tiles[3 + 3 * tile];
+                const uint32_t tile = item / nbg, rows = prefill_tile(P.tiles, 0, 0, tile)[2];
                 const uint32_t idesc = umma_idesc(UMMA_F16, (rows + 15) / 16 * 16);
                 if (!mbar_wait_bounded(&acc_empty, (nitem & 1u) ^ 1u, &s_abort, 64)) { give_up(ST_WAIT_EMPTY); break; }
                 tc_fence_after();
@@ -256,7 +270,8 @@ __global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParam
         };
         for (uint32_t item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++nitem) {
             const uint32_t tile = item / nbg, nb0 = (item % nbg) * CB;
-            const uint32_t expert = P.tiles[1 + 3 * tile], row0 = P.tiles[2 + 3 * tile], rows = P.tiles[3 + 3 * tile];
+            const uint32_t* te = prefill_tile(P.tiles, 0, 0, tile);
+            const uint32_t expert = te[0], row0 = te[1], rows = te[2];
             bool ok = true;
             for (uint32_t ks = 0; ks < nstage; ++ks, ++rit, ++bit) {
                 const uint32_t rs = rit % PF_RAW_STAGES, rph = (rit / PF_RAW_STAGES) & 1u;
@@ -384,13 +399,14 @@ static size_t pf_smem_bytes(int nproj) {
 bool exl3_prefill_supported(Exl3Dims d) { return (d.I / 128) % 2 == 0 && (d.H / 128) % 4 == 0; }
 
 cudaError_t launch_prefill_plan(DispatchTables t, uint32_t n_experts, const uint8_t* lane_flags, uint32_t min_rows,
-                                uint32_t max_tiles, uint32_t* tiles, uint32_t* status, cudaStream_t st) {
-    pf_plan_kernel<<<1, 256, 0, st>>>(t, n_experts, lane_flags, min_rows, max_tiles, tiles, status);
+                                uint32_t cap0, uint32_t cap1, uint32_t max_tiles, uint32_t* tiles, uint32_t* status,
+                                cudaStream_t st) {
+    pf_plan_kernel<<<1, 256, 0, st>>>(t, n_experts, lane_flags, min_rows, cap0, cap1, max_tiles, tiles, status);
     return cudaGetLastError();
 }
 
 cudaError_t launch_exl3_prefill(const Exl3PrefillArgs& a, cudaStream_t st) {
-    cudaError_t e = launch_prefill_plan(a.t, a.n_experts, nullptr, a.min_rows, a.max_tiles, a.tiles, a.status, st);
+    cudaError_t e = launch_prefill_plan(a.t, a.n_experts, nullptr, a.min_rows, PF_NT, 0, a.max_tiles, a.tiles, a.status, st);
     if (e != cudaSuccess) return e;
     pf_prep_kernel<<<dim3(a.max_tiles, a.d.H / 128), 256, 0, st>>>(a.x, a.top_k, a.d.H, a.L.scales, exl3_scales_per_expert(a.d),
                                                                   a.t, a.tiles, a.xa);

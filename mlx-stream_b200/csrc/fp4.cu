@@ -31,9 +31,10 @@ __host__ __device__ inline uint32_t f4_scale_stage_bytes(bool nv) { return nv ? 
 // ------------------------------------------------------------------------------------------------------------
 // load-time repack (bit-preserving)
 // ------------------------------------------------------------------------------------------------------------
-// dst per (128-row block nb, stage ks): [proj][warp 8][sb 4][lane 32][2] codes, then [proj][warp 8][sb 4][...] scales:
+// dst per (128-row block nb, stage ks): [proj][warp 8][sb 4][r 2][lane 32] codes, then [proj][warp 8][sb 4][...] scales:
 //   MXFP4 scales [g 8][r 2] bytes; NVFP4 scales [blk 2][g 8][r 2] bytes.  lane = (g, c): word c of the 32-block for
-//   rows 16 warp + g (r = 0) and 16 warp + g + 8 (r = 1).
+//   rows 16 warp + g (r = 0) and 16 warp + g + 8 (r = 1).  A warp of the streaming lane reads two runs of 32 words;
+//   a thread of the tensor-core lane reads the four words of one output row (r, g) as one 16-byte load.
 __global__ void fp4_repack_kernel(const uint8_t* __restrict__ rec, uint32_t H, uint32_t I, int nv,
                                   uint8_t* __restrict__ gu, uint8_t* __restrict__ dn, float* __restrict__ gscale,
                                   uint8_t* lane_flag) {
@@ -55,7 +56,7 @@ __global__ void fp4_repack_kernel(const uint8_t* __restrict__ rec, uint32_t H, u
             const uint32_t nb = row / 128, wr = (row % 128) / 16, rr = row % 16, g = rr % 8, r = rr / 8;
             const uint32_t ks = wi / 16, sb = (wi % 16) / 4, c = wi % 4;
             uint32_t* d = reinterpret_cast<uint32_t*>(dst + ((size_t)nb * nstage + ks) * stage_bytes + (size_t)pp * F4_W_STAGE);
-            d[((wr * 4 + sb) * 32 + g * 4 + c) * 2 + r] = w[i];
+            d[((wr * 4 + sb) * 2 + r) * 32 + g * 4 + c] = w[i];
         }
         // scales
         const uint32_t per_row = cols / (nv ? 16 : 32);
@@ -159,21 +160,22 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, __half2 s) {
 
 template <int NPROJ, bool NV, int MC>
 __device__ __forceinline__ void fp4_stage(const uint8_t* __restrict__ st, uint32_t w_bytes, uint32_t p, uint32_t j,
-                                          uint32_t lane, float (&acc)[F4_GROUP][4]) {
-    const uint2* wv = reinterpret_cast<const uint2*>(st + (size_t)p * F4_W_STAGE) + (j * 4) * 32 + lane;
+                                          uint32_t lane, const uint32_t* __restrict__ lut, float (&acc)[F4_GROUP][4]) {
+    const uint32_t* wv = reinterpret_cast<const uint32_t*>(st + (size_t)p * F4_W_STAGE) + (j * 4) * 64 + lane;
     const uint8_t* sc = st + (size_t)NPROJ * F4_W_STAGE + (size_t)p * f4_scale_stage_bytes(NV);
     const uint4* xv = reinterpret_cast<const uint4*>(st + w_bytes) + lane;
     const uint32_t g = lane >> 2, c = lane & 3u;
 #pragma unroll
     for (int sb = 0; sb < 4; ++sb) {
-        const uint2 ww = wv[sb * 32];
+        const uint2 ww = make_uint2(wv[sb * 64], wv[sb * 64 + 32]);
         uint32_t hx[4], hy[4];
         fp4_decode8(ww.x, hx);
         fp4_decode8(ww.y, hy);
         float s_lo = 1.f, s_hi = 1.f;
         if (NV) {
             const uint32_t bb = *reinterpret_cast<const uint16_t*>(sc + (((j * 4 + sb) * 2 + (c >> 1)) * 8 + g) * 2);
-            const __half2 sg = e4m3_half2(bb & 0xFFu), sg8 = e4m3_half2(bb >> 8);
+            const uint32_t u0 = lut[bb & 0xFFu], u1 = lut[bb >> 8];  // E4M3 byte -> f16x2 of its value
+            const __half2 sg = *reinterpret_cast<const __half2*>(&u0), sg8 = *reinterpret_cast<const __half2*>(&u1);
 #pragma unroll
             for (int i = 0; i < 4; ++i) { hx[i] = hmul2_u32(hx[i], sg); hy[i] = hmul2_u32(hy[i], sg8); }
         } else {
@@ -212,6 +214,7 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
     __shared__ __align__(8) uint64_t full_bar[MAXS], empty_bar[MAXS], epi_bar;
     __shared__ F4Meta meta[MAXS];
     __shared__ volatile int s_abort;
+    __shared__ uint32_t s_lut[NV ? 256 : 1];
     float* zs = reinterpret_cast<float*>(smem_raw);  // [NPROJ][F4_GROUP][8 rows][F4_ZS_STRIDE]
     uint8_t* ring = smem_raw + (size_t)NPROJ * F4_GROUP * F4_CHUNK * F4_ZS_STRIDE * sizeof(float);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -221,6 +224,10 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
         mbar_init(&epi_bar, NCW);
         s_abort = 0;
         mbar_fence_init();
+    }
+    if (NV && threadIdx.x < 256) {
+        const __half2 hv = e4m3_half2(threadIdx.x);
+        s_lut[threadIdx.x] = *reinterpret_cast<const uint32_t*>(&hv);
     }
     __syncthreads();
     const uint32_t n_items = P.t.header[HDR_NGROUPS] * P.n_blocks;
@@ -289,8 +296,8 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
                 for (int q = 0; q < 4; ++q) acc[a][q] = 0.f;
         }
         const uint8_t* st = ring + (size_t)s * P.stage_bytes;
-        if (m.mc == 1) fp4_stage<NPROJ, NV, 1>(st, P.w_bytes, p, j, lane, acc);
-        else fp4_stage<NPROJ, NV, 2>(st, P.w_bytes, p, j, lane, acc);
+        if (m.mc == 1) fp4_stage<NPROJ, NV, 1>(st, P.w_bytes, p, j, lane, s_lut, acc);
+        else fp4_stage<NPROJ, NV, 2>(st, P.w_bytes, p, j, lane, s_lut, acc);
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[s]);
         if (m.ks + 1 < P.n_stages_k) continue;

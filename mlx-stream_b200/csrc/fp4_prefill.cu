@@ -1,26 +1,37 @@
-// MXFP4 / NVFP4 expert kernels for experts with many rows: tcgen05 tensor cores over codes decoded in shared memory.
+// MXFP4 / NVFP4 expert kernels for experts with many rows: tcgen05 tensor cores, weights decoded into tensor memory.
 //
 // The reference sends prefill-sized FP4 work to a grouped quantised GEMM over rows sorted by expert
 // (src/arch/mimo_v2/math.zig:426-447, src/arch/glm5_next/nvfp4.zig:36-56): bf16 rows times dequantised weights, f32
-// accumulate.  Here a CTA owns (expert, up to 128 of its rows, 256 output columns of gate and up | 512 of down).  W^T
-// is the MMA's A operand (M = 128 output columns per accumulator group), the rows are the B operand (N = rows rounded
-// to 16), four accumulator groups fill the SM's tensor memory, and one staged copy of the rows serves all four groups
-// (gate and up read the same rows).
+// accumulate.  Here a CTA owns (expert, a tile of its rows, a group of 128-column blocks).  W^T is the MMA's A operand
+// (M = 128 output columns per accumulator group) and is written by the decode warps straight into tensor memory; the
+// rows are the B operand in shared memory (N = rows rounded to 16).  Shared memory carries only the packed codes and
+// the rows, which is what bounds a one-SM MMA fed from decoded operands: a decoded A tile in shared memory would be
+// written once and read once per use, as many bytes as the rows themselves.
+//   * tensor memory (512 columns) holds the f32 accumulators and a ring of two decoded A stages of 64 inputs.  Two
+//     shapes: 4 groups x 64 rows (experts with up to 64 rows; gate and up of two column blocks, or four column blocks
+//     of down; 256 + 256 columns) and 2 groups x 192 rows (the others: gate and up of one block, or two blocks of
+//     down; 384 + 128 columns), where a decoded operand serves three times the rows;
 //   * a producer thread streams the same repacked code/scale stream the decode-batch kernel reads (bulk copies, one
-//     stage = 128 inputs of a 128-column block) and the rows, which a prep kernel laid out in the core-matrix order;
-//   * 16 decode warps turn codes into 16-bit operands, two codes per integer op
-//     (src/arch/mimo_v2/kernels/header_mimo_moe_k1.metal:7-12), 8 weights of one output column per 16-byte store, which
-//     is exactly one row of a K-major core matrix.  The k order inside a group of 8 is the decode's (0,4,1,5,2,6,3,7)
-//     and the prep kernel stores the rows in the same order;
+//     stage = 128 inputs of a 128-column block) and the rows, which a prep kernel laid out in core-matrix order;
+//   * 16 decode warps: a thread owns one output column of one group, loads 32 of its codes as one 16-byte word, turns
+//     them into 16-bit values two per integer op
+//     (src/arch/mimo_v2/kernels/header_mimo_moe_k1.metal:7-12), applies the block scale and stores 16 tensor-memory
+//     columns (tcgen05.st).  The k order inside a group of 8 is the decode's (0,4,1,5,2,6,3,7); the prep kernel stores
+//     the rows in the same order;
 //   * MXFP4: operands are bf16.  The code's 3 magnitude bits placed at bits 6..8 are e2m1 x 2^-126 as bf16 (the 0.5
 //     code is a bf16 subnormal); one bf16x2 multiply by 2^(b-1) gives e2m1 x 2^(b-127) exactly, and the rows stay the
 //     bf16 they arrived as, so every product is exact.  This needs 2^(b-1) to be a bf16, b <= 128 (block scale <= 2):
 //     an expert with a larger scale byte is marked at load and always takes the streaming lane;
 //   * NVFP4: operands are f16, weights e2m1 x 2^-14 times the block's E4M3 scale (exact in f16, as in the streaming
 //     lane), rows rounded bf16 -> f16, the global g/2688 x 2^14 applied in the epilogue (decode_kernels_ref.zig:13-65);
-//   * one thread issues tcgen05.mma.kind::f16 (K = 16) and commits to mbarriers; the decode warps run the epilogue
-//     straight from tensor memory (a thread owns one output column of 16 rows): the reference's bf16 rounding chain
-//     for gate/up (mimo_moe_k1_gateup.metal:115-128, glm5n_nvfp4_gateup.metal:109-129), stores for down.
+//   * one thread issues tcgen05.mma.kind::f16 (K = 16, A from tensor memory) and commits to mbarriers.  The tensor
+//     pipe queues only about two MMAs behind the running one, so this thread's time between two stages shows: a
+//     stage therefore carries 64 inputs (8 or 16 MMAs), and the thread waits on one barrier per stage (decode warp 0
+//     arrives only after it has seen the rows of the stage land).  Measured per stage of 8 MMAs x 88 cycles: about
+//     150 cycles in the wait and 160 in fences, commits and loop;
+//   * the decode warps run the epilogue straight from tensor memory (a thread owns one output column of 16 rows):
+//     the reference's bf16 rounding chain for gate/up (mimo_moe_k1_gateup.metal:115-128,
+//     glm5n_nvfp4_gateup.metal:109-129), stores for down.
 // Every wait is bounded; on a give-up the CTA sets the status word, skips work and still frees its tensor memory.
 #include <cstdlib>
 
@@ -30,40 +41,38 @@
 
 namespace mlxs {
 
-constexpr int Q_NT = PREFILL_TILE_ROWS;       // rows per tile (MMA N, rounded up to 16 per item)
 constexpr int Q_KS = 128;                     // inputs per raw stage (the stream's stage)
-constexpr int Q_SB = 32;                      // inputs per operand stage
-constexpr int Q_RAW_STAGES = 2;
-constexpr int Q_A_STAGES = 2;
-constexpr int Q_B_STAGES = 4;
-constexpr int Q_NG = 4;                       // accumulator groups
-constexpr int Q_LBO_A = 16 * 128 + 32;        // K-direction distance of A core matrices; + 32 B keeps the 16-byte stores
-                                              // of a quarter warp (2 columns x 4 k-groups) on distinct banks
-constexpr int Q_A_BYTES = 4 * Q_LBO_A;        // one group's 128 columns x 32 inputs
-constexpr int Q_LBO_B = (Q_NT / 8) * 128;     // 2048
-constexpr int Q_B_BYTES = 4 * Q_LBO_B;        // 128 rows x 32 inputs: 8 KB
+constexpr int Q_SB = 32;                      // inputs per block of the staged rows' layout (one scale block of MXFP4)
+constexpr int Q_B_MAX = 12, Q_RAW_MAX = 6;   // most stages of the row ring and of the code ring
 constexpr int Q_SBO = 128;
+constexpr int Q_KST = 64;                     // inputs per operand stage
+constexpr int Q_CAP0 = 64, Q_CAP1 = 192;      // rows per tile of the two shapes: 4 groups x 64 rows, 2 groups x 192 rows
+                                              // (256 / 384 accumulator columns; the other columns hold decoded A stages)
 constexpr int Q_W_STAGE = 8192;               // code bytes per projection per raw stage (fp4.cu F4_W_STAGE)
 
 __host__ __device__ inline uint32_t q_scale_stage_bytes(bool nv) { return nv ? 1024u : 512u; }
 // position of input k % 8 inside its 16-byte group: the order the two-codes-per-op decode produces
 __host__ __device__ inline uint32_t q_pos8(uint32_t j) { return (j & 3u) * 2u + (j >> 2); }
-// element offset of (row, k) inside a tile's operand: [k/32][(k%32)/8][row/8][row%8][pos]
-__device__ __forceinline__ size_t q_b_off(uint32_t row, uint32_t k) {
-    return (size_t)(k / Q_SB) * (Q_B_BYTES / 2) + ((k % Q_SB) / 8) * (Q_LBO_B / 2) + (row / 8) * 64 + (row % 8) * 8 + q_pos8(k % 8);
+// Staged rows of a tile with rows16 rows (its rows padded to 16) over `width` inputs, as K-major core matrices:
+// [k/32][(k%32)/8][row/8][row%8][pos], so a block of 32 inputs is rows16 x 64 contiguous bytes, consecutive blocks
+// follow each other, and the K-direction distance of two core matrices is rows16 x 16 bytes throughout.  Element offset of (row, k):
+__device__ __forceinline__ size_t q_b_off(uint32_t rows16, uint32_t row, uint32_t k) {
+    return (size_t)(k / Q_SB) * (rows16 * Q_SB) + ((k % Q_SB) / 8) * (rows16 * 8) + (row / 8) * 64 + (row % 8) * 8 + q_pos8(k % 8);
 }
 
 // ------------------------------------------------------------------------------------------------------------
 // prep: gather the tile's rows into the B-operand order (bf16 kept for MXFP4, rounded to f16 for NVFP4)
 // ------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) q_prep_kernel(const __nv_bfloat16* __restrict__ x, uint32_t top_k, uint32_t H, int nv,
-                                                     DispatchTables t, const uint32_t* __restrict__ tiles,
+                                                     DispatchTables t, const uint32_t* __restrict__ tiles, uint32_t max_tiles,
                                                      uint16_t* __restrict__ xa) {
-    const uint32_t tile = blockIdx.x;
-    if (tile >= tiles[0]) return;
-    const uint32_t row0 = tiles[2 + 3 * tile], rows = tiles[3 + 3 * tile];
+    const int list = blockIdx.x >= max_tiles;
+    const uint32_t tile = blockIdx.x - (list ? max_tiles : 0u);
+    if (tile >= tiles[list]) return;
+    const uint32_t* te = prefill_tile(tiles, list, max_tiles, tile);
+    const uint32_t row0 = te[1], rows = te[2];
     const uint32_t rows16 = (rows + 15) / 16 * 16, groups = H / 8;
-    uint16_t* dst = xa + (size_t)tile * Q_NT * H;
+    uint16_t* dst = xa + (size_t)te[3] * H;
     // a thread moves 8 consecutive inputs of one row; consecutive threads take consecutive rows (one core matrix = 128 B)
     for (uint32_t i = blockIdx.y * blockDim.x + threadIdx.x; i < rows16 * groups; i += gridDim.y * blockDim.x) {
         const uint32_t r = i % rows16, kg = i / rows16;
@@ -84,7 +93,7 @@ __global__ void __launch_bounds__(256) q_prep_kernel(const __nv_bfloat16* __rest
         // stored order 0,4,1,5,2,6,3,7
         const uint4 o = make_uint4(e[0] | ((uint32_t)e[4] << 16), e[1] | ((uint32_t)e[5] << 16), e[2] | ((uint32_t)e[6] << 16),
                                    e[3] | ((uint32_t)e[7] << 16));
-        *reinterpret_cast<uint4*>(dst + q_b_off(r, kg * 8)) = o;
+        *reinterpret_cast<uint4*>(dst + q_b_off(rows16, r, kg * 8)) = o;
     }
 }
 
@@ -97,8 +106,9 @@ struct QParams {
     const float* gscale;         // NVFP4: [E][3]
     uint32_t n_blocks, n_stages_k;  // out / 128, in / 128
     uint32_t w_bytes;            // bytes of one (block, stage) of the stream
-    const uint16_t* xa;          // B operand: [tile][in/32][8 KB]
+    const uint16_t* xa;          // B operand: staged rows over this projection's inputs
     const uint32_t* tiles;
+    uint32_t max_tiles;
     DispatchTables t;
     uint32_t H, I;
     uint16_t* xd;                // gate/up output = down's B operand
@@ -106,6 +116,7 @@ struct QParams {
     int out_bf16;
     float limit;
     uint32_t* status;
+    uint32_t b_stages, raw_stages;   // ring depths (the launcher fits them to the shared-memory budget)
 };
 
 // MXFP4: 8 codes of a word -> 4 bf16x2 of e2m1 x 2^-126 (pairs (0,4), (1,5), (2,6), (3,7))
@@ -143,69 +154,81 @@ __device__ __forceinline__ float q_sigmoid(float x) {  // src/arch/mimo_v2/moe.z
     return x < 0.f ? y : 1.0f - y;
 }
 
-// NPROJ projections x CB adjacent 128-column blocks = 4 accumulator groups of 128 tensor-memory columns
-template <int NPROJ, int CB, bool NV>
+// NPROJ projections x CB adjacent 128-column blocks = NG accumulator groups of NT tensor-memory columns each; an
+// operand stage holds KST inputs (KST / 2 tensor-memory columns per group).  One synchronisation round trip (decode ->
+// MMA -> stage free) costs several hundred cycles whatever the stage holds, so a stage carries NG x KST / 16 MMAs.
+template <int NPROJ, int CB, int NT, int KST, bool NV>
 __global__ void __launch_bounds__(512 + 64, 1) fp4_prefill_kernel(const QParams P) {
-    static_assert(NPROJ * CB == Q_NG, "four accumulator groups fill the 512 tensor-memory columns at 128 rows");
+    constexpr int NG = NPROJ * CB;
+    constexpr int KB = KST / Q_SB;                                   // 32-input blocks per operand stage
+    constexpr int A_COLS = KST / 2;                                  // tensor-memory columns of one group's stage
+    constexpr int A_STAGES = (512 - NG * NT) / (NG * A_COLS);
+    constexpr int TASKS = NG * KB / 4;                               // (group, block) tasks of a warp per stage
+    static_assert((NG == 2 || NG == 4) && A_STAGES >= 2 && TASKS >= 1 && Q_KS % KST == 0, "shape");
     extern __shared__ __align__(128) uint8_t smem_raw[];
+    constexpr int LIST = NG == 4 ? 0 : 1;
     constexpr int NCW = 16;
-    constexpr int TMEM_COLS = Q_NG * Q_NT;
+    constexpr int B_SLOT = NT * KST * 2;
     constexpr uint32_t SSTAGE = NV ? 1024u : 512u;
     constexpr uint32_t W_BYTES = NPROJ * (Q_W_STAGE + SSTAGE);   // one block's stage of the stream
     constexpr uint32_t RAW_BYTES = CB * W_BYTES;
-    __shared__ __align__(8) uint64_t raw_full[Q_RAW_STAGES], raw_empty[Q_RAW_STAGES];
-    __shared__ __align__(8) uint64_t b_full[Q_B_STAGES], b_empty[Q_B_STAGES], a_full[Q_A_STAGES], a_empty[Q_A_STAGES];
+    __shared__ __align__(8) uint64_t raw_full[Q_RAW_MAX], raw_empty[Q_RAW_MAX];
+    __shared__ __align__(8) uint64_t b_full[Q_B_MAX], b_empty[Q_B_MAX], a_full[A_STAGES], a_empty[A_STAGES];
     __shared__ __align__(8) uint64_t acc_full, acc_empty;
     __shared__ uint32_t s_tmem;
     __shared__ volatile int s_abort;
-    uint8_t* a_ring = smem_raw;                                        // [stage][group][Q_A_BYTES]
-    uint8_t* b_ring = a_ring + Q_A_STAGES * Q_NG * Q_A_BYTES;          // [stage][Q_B_BYTES]
-    uint8_t* raw_ring = b_ring + Q_B_STAGES * Q_B_BYTES;               // [stage][CB][W_BYTES]
+    __shared__ uint32_t s_lut[NV ? 256 : 1];                           // E4M3 byte -> f16x2 of its value
+    uint8_t* b_ring = smem_raw;                                        // [stage][B_SLOT]
+    const uint32_t B_STAGES = P.b_stages, RAW_STAGES = P.raw_stages;
+    uint8_t* raw_ring = b_ring + B_STAGES * B_SLOT;                    // [stage][CB][W_BYTES]
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t nbg = P.n_blocks / CB;
+    const uint32_t n_items = P.tiles[LIST] * nbg;
     // a CTA without work leaves before it takes tensor memory (the whole CTA reads the same count)
-    if (blockIdx.x >= P.tiles[0] * nbg) return;
+    if (blockIdx.x >= n_items) return;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < Q_RAW_STAGES; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], NCW); }
-        for (int s = 0; s < Q_A_STAGES; ++s) { mbar_init(&a_full[s], NCW); mbar_init(&a_empty[s], 1); }
-        for (int s = 0; s < Q_B_STAGES; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
+        for (uint32_t s = 0; s < RAW_STAGES; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], NCW); }
+        for (int s = 0; s < A_STAGES; ++s) { mbar_init(&a_full[s], NCW); mbar_init(&a_empty[s], 1); }
+        for (uint32_t s = 0; s < B_STAGES; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
         mbar_init(&acc_full, 1);
         mbar_init(&acc_empty, NCW);
         s_abort = 0;
         mbar_fence_init();
     }
-    if (warp == 0) tmem_alloc(&s_tmem, TMEM_COLS);
+    if (NV && threadIdx.x < 256) s_lut[threadIdx.x] = q_e4m3_f16x2(threadIdx.x);
+    if (warp == 0) tmem_alloc(&s_tmem, 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = s_tmem;
-    const uint32_t n_items = P.tiles[0] * nbg;
-    const uint32_t nstage = P.n_stages_k;
+    const uint32_t tmem = s_tmem, tmem_a = tmem + NG * NT;
+    const uint32_t nstage = P.n_stages_k, width = nstage * Q_KS;
     auto give_up = [&](uint32_t code) { if (!s_abort) atomicMax(P.status, code); s_abort = 1; };
 
     if (warp == NCW) {
         // ---------------- producer: code/scale stream + rows ----------------
         if (lane == 0) {
-            uint32_t rit = 0, bit = 0;
+            uint32_t rs = 0, rph = 0, bs = 0, bph = 0;   // ring positions and phases
             for (uint32_t item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
-                const uint32_t tile = item / nbg, nb0 = (item % nbg) * CB, expert = P.tiles[1 + 3 * tile];
+                const uint32_t nb0 = (item % nbg) * CB;
+                const uint32_t* te = prefill_tile(P.tiles, LIST, P.max_tiles, item / nbg);
+                const uint32_t expert = te[0], rows16 = (te[2] + 15) / 16 * 16, b_bytes = rows16 * KST * 2;
                 const uint8_t* wsrc = P.w + (size_t)expert * P.expert_stride + (size_t)nb0 * nstage * W_BYTES;
-                const uint16_t* xsrc = P.xa + (size_t)tile * Q_NT * (nstage * Q_KS);
+                const uint16_t* xsrc = P.xa + (size_t)te[3] * width;
                 bool ok = true;
-                for (uint32_t ks = 0; ks < nstage && ok; ++ks, ++rit) {
-                    const uint32_t rs = rit % Q_RAW_STAGES, rph = (rit / Q_RAW_STAGES) & 1u;
-                    if (!mbar_wait_bounded(&raw_empty[rs], rph ^ 1u, &s_abort, 128)) { give_up(ST_WAIT_EMPTY); ok = false; break; }
+                for (uint32_t ks = 0; ks < nstage && ok; ++ks) {
+                    if (!mbar_wait_bounded(&raw_empty[rs], rph ^ 1u, &s_abort, 64)) { give_up(ST_WAIT_EMPTY); ok = false; break; }
                     mbar_expect_tx(&raw_full[rs], RAW_BYTES);
                     for (int cb = 0; cb < CB; ++cb)
                         bulk_g2s(raw_ring + rs * RAW_BYTES + cb * W_BYTES, wsrc + ((size_t)cb * nstage + ks) * W_BYTES, W_BYTES,
                                  &raw_full[rs]);
-                    for (uint32_t sb = 0; sb < Q_KS / Q_SB; ++sb, ++bit) {
-                        const uint32_t bs = bit % Q_B_STAGES, bph = (bit / Q_B_STAGES) & 1u;
-                        if (!mbar_wait_bounded(&b_empty[bs], bph ^ 1u, &s_abort, 128)) { give_up(ST_WAIT_EMPTY); ok = false; break; }
-                        mbar_expect_tx(&b_full[bs], Q_B_BYTES);
-                        bulk_g2s(b_ring + bs * Q_B_BYTES, xsrc + (size_t)(ks * (Q_KS / Q_SB) + sb) * (Q_B_BYTES / 2), Q_B_BYTES,
-                                 &b_full[bs]);
+                    if (++rs == RAW_STAGES) { rs = 0; rph ^= 1u; }
+                    for (uint32_t os = 0; os < Q_KS / KST; ++os) {
+                        if (!mbar_wait_bounded(&b_empty[bs], bph ^ 1u, &s_abort, 64)) { give_up(ST_WAIT_EMPTY); ok = false; break; }
+                        mbar_expect_tx(&b_full[bs], b_bytes);
+                        bulk_g2s(b_ring + bs * B_SLOT, xsrc, b_bytes, &b_full[bs]);
+                        xsrc += b_bytes / 2;
+                        if (++bs == B_STAGES) { bs = 0; bph ^= 1u; }
                     }
                 }
                 if (!ok) break;
@@ -215,31 +238,36 @@ __global__ void __launch_bounds__(512 + 64, 1) fp4_prefill_kernel(const QParams 
     } else if (warp == NCW + 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            uint32_t bit = 0, nitem = 0;
+            // The issue loop is the pipeline's critical path: the tensor pipe queues only about two MMAs behind the one
+            // that runs, so every cycle this thread spends between two stages shows.  Per stage: one barrier wait (a
+            // ready mbarrier costs about 130 cycles to test), the MMAs, two commits.  The rows' barrier is waited on by
+            // decode warp 0 before it arrives.
+            uint32_t as = 0, aph = 0, bs = 0, nitem = 0;
+            const uint32_t b_ring_s = smem_u32(b_ring);
             for (uint32_t item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++nitem) {
-                const uint32_t tile = item / nbg, rows = P.tiles[3 + 3 * tile];
-                const uint32_t idesc = umma_idesc(NV ? UMMA_F16 : UMMA_BF16, (rows + 15) / 16 * 16);
+                const uint32_t rows16 = (prefill_tile(P.tiles, LIST, P.max_tiles, item / nbg)[2] + 15) / 16 * 16;
+                const uint32_t idesc = umma_idesc(NV ? UMMA_F16 : UMMA_BF16, rows16), lbo_b = rows16 * 16;
+                const uint64_t bdesc0 = umma_smem_desc(b_ring_s, lbo_b, Q_SBO);   // + byte offset >> 4 in the low word
                 if (!mbar_wait_bounded(&acc_empty, (nitem & 1u) ^ 1u, &s_abort, 64)) { give_up(ST_WAIT_EMPTY); break; }
                 tc_fence_after();
                 bool ok = true;
-                for (uint32_t kk = 0; kk < nstage * (Q_KS / Q_SB); ++kk, ++bit) {
-                    const uint32_t as = bit % Q_A_STAGES, aph = (bit / Q_A_STAGES) & 1u;
-                    const uint32_t bs = bit % Q_B_STAGES, bph = (bit / Q_B_STAGES) & 1u;
-                    if (!mbar_wait_bounded(&a_full[as], aph, &s_abort, 32) || !mbar_wait_bounded(&b_full[bs], bph, &s_abort, 32)) {
-                        give_up(ST_WAIT_FULL); ok = false; break;
-                    }
+                const uint32_t nk = nstage * (Q_KS / KST);
+                for (uint32_t kk = 0; kk < nk; ++kk) {
+                    if (!mbar_wait_bounded(&a_full[as], aph, &s_abort)) { give_up(ST_WAIT_FULL); ok = false; break; }
                     tc_fence_after();
-                    const uint32_t b0 = smem_u32(b_ring + bs * Q_B_BYTES);
+                    const uint64_t bd = bdesc0 + ((bs * B_SLOT) >> 4);
+                    const uint32_t ta = tmem_a + as * (NG * A_COLS);
 #pragma unroll
-                    for (int gq = 0; gq < Q_NG; ++gq) {
-                        const uint32_t a0 = smem_u32(a_ring + (as * Q_NG + gq) * Q_A_BYTES);
+                    for (int gq = 0; gq < NG; ++gq) {
 #pragma unroll
-                        for (int i = 0; i < Q_SB / 16; ++i)
-                            umma_f16(tmem + gq * Q_NT, umma_smem_desc(a0 + i * 2 * Q_LBO_A, Q_LBO_A, Q_SBO),
-                                     umma_smem_desc(b0 + i * 2 * Q_LBO_B, Q_LBO_B, Q_SBO), idesc, (kk | (uint32_t)i) ? 1u : 0u);
+                        for (int i = 0; i < KST / 16; ++i)
+                            umma_f16_ts(tmem + gq * NT, ta + gq * A_COLS + i * 8, bd + ((i * 2 * lbo_b) >> 4), idesc,
+                                        (kk | (uint32_t)i) ? 1u : 0u);
                     }
                     umma_commit(&a_empty[as]);
                     umma_commit(&b_empty[bs]);
+                    if (++as == A_STAGES) { as = 0; aph ^= 1u; }
+                    if (++bs == B_STAGES) bs = 0;
                 }
                 if (!ok) break;
                 umma_commit(&acc_full);
@@ -247,65 +275,74 @@ __global__ void __launch_bounds__(512 + 64, 1) fp4_prefill_kernel(const QParams 
         }
     } else {
         // ---------------- decode warps + epilogue ----------------
-        // a warp owns 16 output columns (j) of two accumulator groups: gate/up: projection hi, both column blocks;
-        // down: column blocks 2 hi and 2 hi + 1
-        const uint32_t hi = warp >> 3, j = warp & 7u, g = lane >> 2, c = lane & 3u;
-        uint32_t rit = 0, nitem = 0;
+        // Warp = (lane quarter q = warp % 4, slot = warp / 4): a thread owns output column m = 32 q + lane of group
+        // slot % NG and decodes, per operand stage, the 32-input blocks slot / NG, slot / NG + 4 / NG, ...
+        const uint32_t q = warp & 3u, slot = warp >> 2;
+        const uint32_t gq = slot % NG, kb0 = slot / NG;
+        const uint32_t p = NPROJ == 2 ? gq / CB : 0u, cb = NPROJ == 2 ? gq % CB : gq;
+        const uint32_t m = q * 32u + lane, wr = m >> 4, r = (m >> 3) & 1u, g = m & 7u;
+        uint32_t rs = 0, rph = 0, as = 0, aph = 0, bs = 0, bph = 0, nitem = 0;
         for (uint32_t item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++nitem) {
-            const uint32_t tile = item / nbg, nb0 = (item % nbg) * CB;
-            const uint32_t expert = P.tiles[1 + 3 * tile], row0 = P.tiles[2 + 3 * tile], rows = P.tiles[3 + 3 * tile];
+            const uint32_t nb0 = (item % nbg) * CB;
+            const uint32_t* te = prefill_tile(P.tiles, LIST, P.max_tiles, item / nbg);
+            const uint32_t expert = te[0], row0 = te[1], rows = te[2], srow0 = te[3];
             bool ok = true;
-            for (uint32_t ks = 0; ks < nstage && ok; ++ks, ++rit) {
-                const uint32_t rs = rit % Q_RAW_STAGES, rph = (rit / Q_RAW_STAGES) & 1u;
+            for (uint32_t ks = 0; ks < nstage && ok; ++ks) {
                 if (!mbar_wait_bounded(&raw_full[rs], rph, &s_abort)) { give_up(ST_WAIT_FULL); ok = false; break; }
-                const uint8_t* raw = raw_ring + rs * RAW_BYTES;
+                const uint8_t* blk = raw_ring + rs * RAW_BYTES + cb * W_BYTES;
+                const uint8_t* sc = blk + NPROJ * Q_W_STAGE + p * SSTAGE;
 #pragma unroll
-                for (int sb = 0; sb < Q_KS / Q_SB; ++sb) {
-                    // 4 operand stages per raw stage and an even ring: stage and parity are compile-time
-                    const uint32_t as = sb % Q_A_STAGES, aph = (sb / Q_A_STAGES) & 1u;
+                for (int os = 0; os < Q_KS / KST; ++os) {
                     if (!mbar_wait_bounded(&a_empty[as], aph ^ 1u, &s_abort)) { give_up(ST_WAIT_FULL); ok = false; break; }
+
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const uint32_t cb = NPROJ == 2 ? (uint32_t)u : 2u * hi + u, p = NPROJ == 2 ? hi : 0u;
-                        const uint32_t gq = NPROJ == 2 ? hi * CB + u : cb;
-                        const uint8_t* blk = raw + cb * W_BYTES;
-                        const uint2 ww = *(reinterpret_cast<const uint2*>(blk + p * Q_W_STAGE) + (j * 4 + sb) * 32 + lane);
-                        const uint8_t* sc = blk + NPROJ * Q_W_STAGE + p * SSTAGE;
-                        uint32_t hx[4], hy[4];
+                    for (int n = 0; n < TASKS; ++n) {
+                        const uint32_t kb = kb0 + n * (4 / NG), sb = os * KB + kb;   // block of the stage, of the raw stage
+                        // the row's 32 codes of this block: words c = 0..3 of [wr][sb][r][g][c]
+                        const uint4 ww = *reinterpret_cast<const uint4*>(blk + p * Q_W_STAGE + (((wr * 4 + sb) * 2 + r) * 32 + g * 4) * 4);
+                        const uint32_t wds[4] = {ww.x, ww.y, ww.z, ww.w};
+                        uint32_t v[16];
                         if (NV) {
-                            const uint32_t bb = *reinterpret_cast<const uint16_t*>(sc + (((j * 4 + sb) * 2 + (c >> 1)) * 8 + g) * 2);
-                            const uint32_t s0 = q_e4m3_f16x2(bb & 0xFFu), s1 = q_e4m3_f16x2(bb >> 8);
-                            q_decode8_f16(ww.x, hx);
-                            q_decode8_f16(ww.y, hy);
+                            const uint32_t s0 = s_lut[sc[(((wr * 4 + sb) * 2 + 0) * 8 + g) * 2 + r]];
+                            const uint32_t s1 = s_lut[sc[(((wr * 4 + sb) * 2 + 1) * 8 + g) * 2 + r]];
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) { hx[i] = q_mul_f16x2(hx[i], s0); hy[i] = q_mul_f16x2(hy[i], s1); }
+                            for (int c = 0; c < 4; ++c) {
+                                uint32_t h[4];
+                                q_decode8_f16(wds[c], h);
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) v[4 * c + i] = q_mul_f16x2(h[i], c < 2 ? s0 : s1);
+                            }
                         } else {
-                            const uint32_t bb = *reinterpret_cast<const uint16_t*>(sc + ((j * 4 + sb) * 8 + g) * 2);
-                            const uint32_t s0 = (((bb & 0xFFu) + 126u) << 7) * 0x00010001u;   // 2^(b - 1) in both halves
-                            const uint32_t s1 = (((bb >> 8) + 126u) << 7) * 0x00010001u;
-                            q_decode8_bf16(ww.x, hx);
-                            q_decode8_bf16(ww.y, hy);
+                            const uint32_t bb = sc[((wr * 4 + sb) * 8 + g) * 2 + r];
+                            const uint32_t s0 = ((bb + 126u) << 7) * 0x00010001u;   // 2^(b - 1) in both halves
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) { hx[i] = q_mul_bf16x2(hx[i], s0); hy[i] = q_mul_bf16x2(hy[i], s1); }
+                            for (int c = 0; c < 4; ++c) {
+                                uint32_t h[4];
+                                q_decode8_bf16(wds[c], h);
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) v[4 * c + i] = q_mul_bf16x2(h[i], s0);
+                            }
                         }
-                        // columns 16 j + g and 16 j + g + 8 are row g of core matrices 2 j and 2 j + 1; k-group c
-                        uint8_t* ad = a_ring + (as * Q_NG + gq) * Q_A_BYTES + c * Q_LBO_A + (2 * j) * Q_SBO + g * 16;
-                        *reinterpret_cast<uint4*>(ad) = make_uint4(hx[0], hx[1], hx[2], hx[3]);
-                        *reinterpret_cast<uint4*>(ad + Q_SBO) = make_uint4(hy[0], hy[1], hy[2], hy[3]);
+                        tmem_st16(tmem_a + ((q * 32u) << 16) + (as * NG + gq) * A_COLS + kb * 16, v);
                     }
-                    fence_async_smem();
+                    tc_fence_before();
+                    if (warp == 0) {  // the stage's rows have landed too: the issuer then waits on one barrier only
+                        if (!mbar_wait_bounded(&b_full[bs], bph, &s_abort)) { give_up(ST_WAIT_FULL); ok = false; break; }
+                        if (++bs == B_STAGES) { bs = 0; bph ^= 1u; }
+                    }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&a_full[as]);
+                    if (++as == A_STAGES) { as = 0; aph ^= 1u; }
                 }
                 if (!ok) break;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&raw_empty[rs]);
+                if (++rs == RAW_STAGES) { rs = 0; rph ^= 1u; }
             }
             if (!ok) break;
             // ---- epilogue: a thread owns output column 32 q + lane of a group, 16 rows per tensor-memory load ----
             if (!mbar_wait_bounded(&acc_full, nitem & 1u, &s_abort)) { give_up(ST_WAIT_FULL); break; }
             tc_fence_after();
-            const uint32_t q = warp & 3u, sub = warp >> 2;
             const uint32_t rows16 = (rows + 15) / 16 * 16, nrb = rows16 / 16;
             if (NPROJ == 2) {
                 float gs_g = 1.f, gs_u = 1.f;
@@ -313,13 +350,13 @@ __global__ void __launch_bounds__(512 + 64, 1) fp4_prefill_kernel(const QParams 
                     gs_g = (P.gscale[expert * 3 + 0] / 2688.0f) * 16384.0f;
                     gs_u = (P.gscale[expert * 3 + 1] / 2688.0f) * 16384.0f;
                 }
-                uint16_t* xd_tile = P.xd + (size_t)tile * Q_NT * P.I;
-                for (uint32_t unit = sub; unit < CB * nrb; unit += 4) {
-                    const uint32_t cb = unit / nrb, rb = (unit % nrb) * 16;
+                uint16_t* xd_tile = P.xd + (size_t)srow0 * P.I;
+                for (uint32_t unit = slot; unit < CB * nrb; unit += 4) {
+                    const uint32_t ecb = unit / nrb, rb = (unit % nrb) * 16;
                     uint32_t vg[16], vu[16];
-                    tmem_ld16(tmem + ((q * 32u) << 16) + (0 * CB + cb) * Q_NT + rb, vg);
-                    tmem_ld16(tmem + ((q * 32u) << 16) + (1 * CB + cb) * Q_NT + rb, vu);
-                    const uint32_t col = (nb0 + cb) * 128 + q * 32 + lane;
+                    tmem_ld16(tmem + ((q * 32u) << 16) + (0 * CB + ecb) * NT + rb, vg);
+                    tmem_ld16(tmem + ((q * 32u) << 16) + (1 * CB + ecb) * NT + rb, vu);
+                    const uint32_t col = (nb0 + ecb) * 128 + m;
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         // mimo_moe_k1_gateup.metal:115-128 / glm5n_nvfp4_gateup.metal:109-129
@@ -329,25 +366,25 @@ __global__ void __launch_bounds__(512 + 64, 1) fp4_prefill_kernel(const QParams 
                             uf = uf > P.limit ? P.limit : (uf < -P.limit ? -P.limit : uf);
                         }
                         const float hq = bf16_round_f(bf16_round_f(gf * q_sigmoid(gf)) * uf);
-                        const uint32_t r = rb + i;
+                        const uint32_t rr = rb + i;
                         uint16_t bits = 0;
-                        if (r < rows) bits = NV ? __half_as_ushort(__float2half_rn(hq)) : (uint16_t)(__float_as_uint(hq) >> 16);
-                        xd_tile[q_b_off(r, col)] = bits;
+                        if (rr < rows) bits = NV ? __half_as_ushort(__float2half_rn(hq)) : (uint16_t)(__float_as_uint(hq) >> 16);
+                        xd_tile[q_b_off(rows16, rr, col)] = bits;
                     }
                 }
             } else {
                 float gs = 1.f;
                 if (NV) gs = (P.gscale[expert * 3 + 2] / 2688.0f) * 16384.0f;
-                for (uint32_t unit = sub; unit < CB * nrb; unit += 4) {
-                    const uint32_t cb = unit / nrb, rb = (unit % nrb) * 16;
+                for (uint32_t unit = slot; unit < CB * nrb; unit += 4) {
+                    const uint32_t ecb = unit / nrb, rb = (unit % nrb) * 16;
                     uint32_t v[16];
-                    tmem_ld16(tmem + ((q * 32u) << 16) + cb * Q_NT + rb, v);
-                    const uint32_t col = (nb0 + cb) * 128 + q * 32 + lane;
+                    tmem_ld16(tmem + ((q * 32u) << 16) + ecb * NT + rb, v);
+                    const uint32_t col = (nb0 + ecb) * 128 + m;
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const uint32_t r = rb + i;
-                        if (r >= rows) continue;
-                        const uint32_t assign = P.t.order[row0 + r];
+                        const uint32_t rr = rb + i;
+                        if (rr >= rows) continue;
+                        const uint32_t assign = P.t.order[row0 + rr];
                         const float z = __uint_as_float(v[i]) * gs;
                         if (P.out_bf16) static_cast<__nv_bfloat16*>(P.out)[(size_t)assign * P.H + col] = __float2bfloat16_rn(z);
                         else static_cast<float*>(P.out)[(size_t)assign * P.H + col] = z;
@@ -363,44 +400,59 @@ __global__ void __launch_bounds__(512 + 64, 1) fp4_prefill_kernel(const QParams 
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp == 0) tmem_free(tmem, TMEM_COLS);
+    if (warp == 0) tmem_free(tmem, 512);
 }
 
-static size_t q_smem_bytes(int nproj, int cb, bool nv) {
-    return (size_t)Q_A_STAGES * Q_NG * Q_A_BYTES + (size_t)Q_B_STAGES * Q_B_BYTES +
-           (size_t)Q_RAW_STAGES * cb * nproj * (Q_W_STAGE + q_scale_stage_bytes(nv));
+static int q_env(const char* name, int dflt, int lo, int hi) {
+    const char* v = getenv(name);
+    const int x = v ? atoi(v) : dflt;
+    return x < lo ? lo : (x > hi ? hi : x);
 }
 
 bool fp4_prefill_supported(uint32_t H, uint32_t I) { return H % 128 == 0 && I % 128 == 0 && (I / 128) % 2 == 0 && (H / 128) % 4 == 0; }
 
-template <int NPROJ, int CB, bool NV>
-static cudaError_t q_launch(const QParams& P, int sm_count, cudaStream_t st) {
-    const size_t smem = q_smem_bytes(NPROJ, CB, NV);
-    cudaError_t e = cudaFuncSetAttribute(fp4_prefill_kernel<NPROJ, CB, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+template <int NPROJ, int CB, int NT, int KST, bool NV>
+static cudaError_t q_launch(QParams P, int sm_count, cudaStream_t st) {
+    // ring depths: the code ring first (HBM latency), the rest of the budget to the rows
+    const size_t raw_bytes = (size_t)CB * NPROJ * (Q_W_STAGE + q_scale_stage_bytes(NV)), b_slot = (size_t)NT * KST * 2;
+    const size_t budget = 224 * 1024;
+    static const int raw_want = q_env("MLXS_Q_RAW_STAGES", 4, 2, Q_RAW_MAX), b_want = q_env("MLXS_Q_B_STAGES", Q_B_MAX, 2, Q_B_MAX);
+    P.raw_stages = (uint32_t)raw_want;
+    while (P.raw_stages > 2 && P.raw_stages * raw_bytes + 3 * b_slot > budget) --P.raw_stages;
+    size_t nb = (budget - P.raw_stages * raw_bytes) / b_slot;
+    P.b_stages = (uint32_t)(nb > (size_t)b_want ? (size_t)b_want : nb);
+    const size_t smem = P.b_stages * b_slot + P.raw_stages * raw_bytes;
+    cudaError_t e = cudaFuncSetAttribute(fp4_prefill_kernel<NPROJ, CB, NT, KST, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    fp4_prefill_kernel<NPROJ, CB, NV><<<sm_count, 512 + 64, smem, st>>>(P);
+    fp4_prefill_kernel<NPROJ, CB, NT, KST, NV><<<sm_count, 512 + 64, smem, st>>>(P);
     return cudaGetLastError();
 }
 
 cudaError_t launch_fp4_prefill(const Fp4PrefillArgs& a, cudaStream_t st) {
-    cudaError_t e = launch_prefill_plan(a.t, a.n_experts, a.lane_flags, a.min_rows, a.max_tiles, a.tiles, a.status, st);
+    cudaError_t e = launch_prefill_plan(a.t, a.n_experts, a.lane_flags, a.min_rows, Q_CAP0, Q_CAP1, a.max_tiles, a.tiles, a.status, st);
     if (e != cudaSuccess) return e;
-    q_prep_kernel<<<dim3(a.max_tiles, 8), 256, 0, st>>>(a.x, a.top_k, a.H, a.nv, a.t, a.tiles, a.xa);
+    q_prep_kernel<<<dim3(2 * a.max_tiles, 8), 256, 0, st>>>(a.x, a.top_k, a.H, a.nv, a.t, a.tiles, a.max_tiles, a.xa);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     const uint32_t sstage = q_scale_stage_bytes(a.nv != 0);
     QParams P{};
-    P.gscale = a.gscale; P.tiles = a.tiles; P.t = a.t; P.H = a.H; P.I = a.I; P.limit = a.limit; P.status = a.status;
-    // gate / up: two projections x two adjacent column blocks per CTA, one copy of the rows
+    P.gscale = a.gscale; P.tiles = a.tiles; P.max_tiles = a.max_tiles; P.t = a.t; P.H = a.H; P.I = a.I; P.limit = a.limit;
+    P.status = a.status;
+    // gate / up: both projections of two adjacent column blocks (tiles up to 96 rows) or of one (up to 192 rows), one
+    // copy of the rows
     P.w = a.gu; P.w_bytes = 2 * (Q_W_STAGE + sstage); P.n_blocks = a.I / 128; P.n_stages_k = a.H / Q_KS;
     P.expert_stride = (size_t)P.n_blocks * P.n_stages_k * P.w_bytes;
     P.xa = a.xa; P.xd = a.xd; P.out = nullptr; P.out_bf16 = 0;
-    e = a.nv ? q_launch<2, 2, true>(P, a.sm_count, st) : q_launch<2, 2, false>(P, a.sm_count, st);
+    e = a.nv ? q_launch<2, 2, Q_CAP0, Q_KST, true>(P, a.sm_count, st) : q_launch<2, 2, Q_CAP0, Q_KST, false>(P, a.sm_count, st);
     if (e != cudaSuccess) return e;
-    // down: four adjacent column blocks per CTA
+    e = a.nv ? q_launch<2, 1, Q_CAP1, Q_KST, true>(P, a.sm_count, st) : q_launch<2, 1, Q_CAP1, Q_KST, false>(P, a.sm_count, st);
+    if (e != cudaSuccess) return e;
+    // down: four adjacent column blocks per CTA, or two
     P.w = a.dn; P.w_bytes = Q_W_STAGE + sstage; P.n_blocks = a.H / 128; P.n_stages_k = a.I / Q_KS;
     P.expert_stride = (size_t)P.n_blocks * P.n_stages_k * P.w_bytes;
     P.xa = a.xd; P.xd = nullptr; P.out = a.ro; P.out_bf16 = a.ro_bf16;
-    return a.nv ? q_launch<1, 4, true>(P, a.sm_count, st) : q_launch<1, 4, false>(P, a.sm_count, st);
+    e = a.nv ? q_launch<1, 4, Q_CAP0, Q_KST, true>(P, a.sm_count, st) : q_launch<1, 4, Q_CAP0, Q_KST, false>(P, a.sm_count, st);
+    if (e != cudaSuccess) return e;
+    return a.nv ? q_launch<1, 2, Q_CAP1, Q_KST, true>(P, a.sm_count, st) : q_launch<1, 2, Q_CAP1, Q_KST, false>(P, a.sm_count, st);
 }
 
 }  // namespace mlxs

@@ -88,9 +88,20 @@ constexpr int PREFILL_TILE_ROWS = 128;
 __host__ __device__ inline bool takes_tensor_lane(uint32_t rows, uint32_t min_rows, const uint8_t* flags, uint32_t e) {
     return min_rows && rows >= min_rows && !(flags && (flags[e] & 2u));
 }
-// row tiles {expert, first sorted row, rows} of the experts that take the tensor-core lane: tiles[0] = count
+// Row tiles of the experts that take the tensor-core lane.  tiles[0], tiles[1] = tiles of list 0 (experts with up to
+// cap0 rows; with cap1 = 0 all experts, in tiles of up to cap0 rows) and list 1 (the others, tiles of up to cap1 rows);
+// entries {expert, first sorted row, rows, first staging row}, list 1 from entry max_tiles.  The table holds
+// prefill_tile_words(max_tiles) words.
+__host__ __device__ inline size_t prefill_tile_words(uint32_t max_tiles) { return 2 + 8 * (size_t)max_tiles; }
+__host__ __device__ inline uint32_t* prefill_tile(uint32_t* tiles, int list, uint32_t max_tiles, uint32_t i) {
+    return tiles + 2 + 4 * ((size_t)(list ? max_tiles : 0) + i);
+}
+__host__ __device__ inline const uint32_t* prefill_tile(const uint32_t* tiles, int list, uint32_t max_tiles, uint32_t i) {
+    return tiles + 2 + 4 * ((size_t)(list ? max_tiles : 0) + i);
+}
 cudaError_t launch_prefill_plan(DispatchTables t, uint32_t n_experts, const uint8_t* lane_flags, uint32_t min_rows,
-                                uint32_t max_tiles, uint32_t* tiles, uint32_t* status, cudaStream_t st);
+                                uint32_t cap0, uint32_t cap1, uint32_t max_tiles, uint32_t* tiles, uint32_t* status,
+                                cudaStream_t st);
 struct Exl3PrefillArgs {
     Exl3Layer L;
     Exl3Dims d;
@@ -99,7 +110,7 @@ struct Exl3PrefillArgs {
     uint32_t min_rows;       // only experts with at least this many rows take this lane
     const __nv_bfloat16* x;  // [tokens, H]
     uint32_t top_k;
-    uint32_t* tiles;         // [1 + 3 max_tiles] row-tile table (device scratch)
+    uint32_t* tiles;         // [prefill_tile_words(max_tiles)] row-tile table (device scratch)
     uint32_t max_tiles;
     __half* xa;              // [max_tiles][2][H/32][128 x 32] f16: rotated rows in the MMA's B-operand order
     __half* xd;              // [max_tiles][I/32][128 x 32] f16
@@ -156,17 +167,21 @@ struct Fp4PrefillArgs {
     uint32_t min_rows;
     const __nv_bfloat16* x;  // [tokens, H]
     uint32_t top_k;
-    uint32_t* tiles;         // [1 + 3 max_tiles]
+    uint32_t* tiles;         // [prefill_tile_words(max_tiles)]
     uint32_t max_tiles;
-    uint16_t* xa;            // [max_tiles][128 x H] rows in the MMA's B-operand order (bf16 MXFP4, f16 NVFP4)
-    uint16_t* xd;            // [max_tiles][128 x I]
+    uint16_t* xa;            // [staging rows][H] rows in the MMA's B-operand order (bf16 MXFP4, f16 NVFP4)
+    uint16_t* xd;            // [staging rows][I]
+    uint32_t rows_cap;       // assignment rows the staging was sized for
     void* ro;                // [A, H] bf16 (chain combine) or f32
     int ro_bf16;
     float limit;
     uint32_t* status;
     int sm_count;
 };
-static inline size_t fp4_prefill_xa_bytes(uint32_t H, uint32_t max_tiles) { return (size_t)max_tiles * H * PREFILL_TILE_ROWS * 2; }
+// staging rows: every tile's rows padded to 16
+static inline size_t fp4_prefill_xa_bytes(uint32_t width, size_t rows_cap, uint32_t max_tiles) {
+    return (rows_cap + 16 * (size_t)(2 * max_tiles + 1)) * width * 2;
+}
 cudaError_t launch_fp4_prefill(const Fp4PrefillArgs& a, cudaStream_t st);
 bool fp4_prefill_supported(uint32_t H, uint32_t I);
 
