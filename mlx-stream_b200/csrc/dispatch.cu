@@ -7,7 +7,105 @@
 
 namespace mlxs {
 
-constexpr int DTHREADS = 1024;
+constexpr int DTHREADS = 1024;   // one thread per expert in the scans (n_experts <= 1024), one per assignment of a block
+
+// Exclusive prefix sums of three per-thread values over the CTA (1024 threads): warp shuffles, then the 32 warp totals
+// by the first warp.  ws: [3][33] words of shared memory; the totals come back in tot[3].
+__device__ __forceinline__ void block_scan3(const uint32_t (&v)[3], uint32_t (&excl)[3], uint32_t (&tot)[3], uint32_t* ws) {
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    uint32_t inc[3];
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+        uint32_t x = v[k];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t y = __shfl_up_sync(0xFFFFFFFFu, x, o);
+            if (lane >= (uint32_t)o) x += y;
+        }
+        inc[k] = x;
+        if (lane == 31) ws[k * 33 + warp] = x;
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+            const uint32_t w = ws[k * 33 + lane];
+            uint32_t x = w;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t y = __shfl_up_sync(0xFFFFFFFFu, x, o);
+                if (lane >= (uint32_t)o) x += y;
+            }
+            ws[k * 33 + lane] = x - w;            // exclusive base of each warp
+            if (lane == 31) ws[k * 33 + 32] = x;  // total
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+        excl[k] = ws[k * 33 + warp] + inc[k] - v[k];
+        tot[k] = ws[k * 33 + 32];
+    }
+}
+
+// Work tables from the per-expert counts (cnt in shared memory, one thread per expert): offsets, chunks of CHUNK_ROWS
+// rows, groups of GROUP_CHUNKS chunks.  Experts that take the tensor-core lane get no chunks.  On a table overflow the
+// status word is set and no chunk is written.
+__device__ __forceinline__ void build_tables(const uint32_t* cnt, uint32_t E, const uint8_t* __restrict__ loaded,
+                                             DispatchTables t, uint32_t CHUNK_ROWS, uint32_t GROUP_CHUNKS, uint32_t HEAVY,
+                                             uint32_t* ws, uint32_t* status) {
+    const uint32_t e = threadIdx.x;
+    const uint32_t c = e < E ? cnt[e] : 0u;
+    const uint32_t nc = (e >= E || takes_tensor_lane(c, HEAVY, loaded, e)) ? 0u : (c + CHUNK_ROWS - 1) / CHUNK_ROWS;
+    const uint32_t ng = (nc + GROUP_CHUNKS - 1) / GROUP_CHUNKS;
+    const uint32_t v[3] = {c, nc, ng};
+    uint32_t ex[3], tot[3];
+    block_scan3(v, ex, tot, ws);
+    const uint32_t distinct = (uint32_t)__syncthreads_count(c != 0u);
+    if (e < E) t.offsets[e] = ex[0];
+    const bool ok = tot[1] <= t.max_chunks;
+    if (threadIdx.x == 0) {
+        t.offsets[E] = tot[0];
+        if (!ok) atomicMax(status, (uint32_t)ST_WORKLIST_OVERFLOW);
+        t.header[HDR_NCHUNKS] = ok ? tot[1] : 0u;
+        t.header[HDR_NGROUPS] = ok ? tot[2] : 0u;
+        t.header[HDR_CTR_GU] = 0;
+        t.header[HDR_CTR_DOWN] = 0;
+        t.header[HDR_CTR_AUX] = 0;
+        t.header[HDR_DISTINCT] = distinct;
+    }
+    if (ok && e < E) {
+        for (uint32_t i = 0; i < nc; ++i) {
+            const uint32_t ch = ex[1] + i;
+            t.chunk_expert[ch] = e;
+            t.chunk_row0[ch] = ex[0] + i * CHUNK_ROWS;
+            t.chunk_rows[ch] = min(CHUNK_ROWS, c - i * CHUNK_ROWS);
+        }
+        for (uint32_t i = 0; i < ng; ++i) {
+            t.group_chunk0[ex[2] + i] = ex[1] + i * GROUP_CHUNKS;
+            t.group_mc[ex[2] + i] = min(GROUP_CHUNKS, nc - i * GROUP_CHUNKS);
+        }
+    }
+}
+
+// Stable placement of one block of up to DTHREADS assignments (a = first + thread index, all threads call): the warps
+// take their turn in order; inside a warp the lanes with the same expert find each other (match) and take consecutive
+// positions from the expert's running position pos[id] in shared memory.
+__device__ __forceinline__ void place_block(uint32_t id, bool valid, uint32_t a, uint32_t n_warps_used, uint32_t* pos,
+                                            uint32_t* __restrict__ order) {
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t key = valid ? id : 0xFFFFFFFFu;
+    const uint32_t peers = __match_any_sync(0xFFFFFFFFu, key);
+    const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
+    for (uint32_t w = 0; w < n_warps_used; ++w) {
+        if (w == warp && valid) {
+            order[pos[id] + rank] = a;
+            __syncwarp(peers);
+            if (rank == 0) pos[id] += __popc(peers);
+        }
+        __syncthreads();
+    }
+}
 
 __global__ void __launch_bounds__(DTHREADS) dispatch_kernel(const int32_t* __restrict__ ids, uint32_t A, uint32_t E,
                                                             const uint8_t* __restrict__ loaded, DispatchTables t,
@@ -15,13 +113,9 @@ __global__ void __launch_bounds__(DTHREADS) dispatch_kernel(const int32_t* __res
                                                             uint32_t* status) {
     extern __shared__ uint32_t dsm[];
     uint32_t* cnt = dsm;                // [E] counts, then running write positions
-    uint32_t* chunk_base = dsm + E;     // [E + 1]
-    uint32_t* group_base = chunk_base + E + 1;  // [E + 1]
-    uint32_t* blk = group_base + E + 1;  // [DTHREADS] ids of the block being placed
-    __shared__ uint32_t s_overflow;
+    uint32_t* ws = dsm + E;             // [99] scan scratch
     const uint32_t tid = threadIdx.x;
     for (uint32_t e = tid; e < E; e += DTHREADS) cnt[e] = 0;
-    if (tid == 0) s_overflow = 0;
     __syncthreads();
     for (uint32_t a = tid; a < A; a += DTHREADS) {
         int32_t id = ids[a];
@@ -30,70 +124,18 @@ __global__ void __launch_bounds__(DTHREADS) dispatch_kernel(const int32_t* __res
         atomicAdd(&cnt[id], 1u);
     }
     __syncthreads();
-    if (tid == 0) {
-        uint32_t rows = 0, chunks = 0, groups = 0, distinct = 0;
-        for (uint32_t e = 0; e < E; ++e) {
-            uint32_t c = cnt[e];
-            t.offsets[e] = rows;
-            chunk_base[e] = chunks;
-            group_base[e] = groups;
-            // experts with HEAVY or more rows belong to the tensor-core lane: no chunks here
-            uint32_t nc = takes_tensor_lane(c, HEAVY, loaded, e) ? 0u : (c + CHUNK_ROWS - 1) / CHUNK_ROWS;
-            rows += c;
-            chunks += nc;
-            groups += (nc + GROUP_CHUNKS - 1) / GROUP_CHUNKS;
-            distinct += c ? 1u : 0u;
-        }
-        t.offsets[E] = rows;
-        chunk_base[E] = chunks;
-        group_base[E] = groups;
-        if (chunks > t.max_chunks) { atomicMax(status, (uint32_t)ST_WORKLIST_OVERFLOW); chunks = 0; groups = 0; s_overflow = 1; }
-        t.header[HDR_NCHUNKS] = chunks;
-        t.header[HDR_NGROUPS] = groups;
-        t.header[HDR_CTR_GU] = 0;
-        t.header[HDR_CTR_DOWN] = 0;
-        t.header[HDR_CTR_AUX] = 0;
-        t.header[HDR_DISTINCT] = distinct;
-    }
+    build_tables(cnt, E, loaded, t, CHUNK_ROWS, GROUP_CHUNKS, HEAVY, ws, status);
     __syncthreads();
-    if (!s_overflow) {
-        for (uint32_t e = tid; e < E; e += DTHREADS) {
-            const uint32_t c = cnt[e], row0 = t.offsets[e];
-            const uint32_t nc = takes_tensor_lane(c, HEAVY, loaded, e) ? 0u : (c + CHUNK_ROWS - 1) / CHUNK_ROWS;
-            for (uint32_t i = 0; i < nc; ++i) {
-                const uint32_t ch = chunk_base[e] + i;
-                t.chunk_expert[ch] = e;
-                t.chunk_row0[ch] = row0 + i * CHUNK_ROWS;
-                t.chunk_rows[ch] = min(CHUNK_ROWS, c - i * CHUNK_ROWS);
-            }
-            const uint32_t ng = (nc + GROUP_CHUNKS - 1) / GROUP_CHUNKS;
-            for (uint32_t i = 0; i < ng; ++i) {
-                t.group_chunk0[group_base[e] + i] = chunk_base[e] + i * GROUP_CHUNKS;
-                t.group_mc[group_base[e] + i] = min(GROUP_CHUNKS, nc - i * GROUP_CHUNKS);
-            }
-        }
-    }
+    if (tid < E) cnt[tid] = t.offsets[tid];   // the entry this thread wrote
     __syncthreads();
-    for (uint32_t e = tid; e < E; e += DTHREADS) cnt[e] = t.offsets[e];
-    __syncthreads();
-    // stable placement, a block of DTHREADS assignments at a time
     for (uint32_t a0 = 0; a0 < A; a0 += DTHREADS) {
-        const uint32_t a = a0 + tid;
-        uint32_t id = 0xFFFFFFFFu;
+        const uint32_t a = a0 + tid, left = A - a0;
+        uint32_t id = 0;
         if (a < A) {
-            int32_t v = ids[a];
+            const int32_t v = ids[a];
             id = (v < 0 || (uint32_t)v >= E) ? 0u : (uint32_t)v;
         }
-        blk[tid] = id;
-        __syncthreads();
-        if (a < A) {
-            uint32_t r = 0;
-            for (uint32_t j = 0; j < tid; ++j) r += (blk[j] == id) ? 1u : 0u;
-            t.order[cnt[id] + r] = a;
-        }
-        __syncthreads();
-        if (a < A) atomicAdd(&cnt[id], 1u);
-        __syncthreads();
+        place_block(id, a < A, a, left >= (uint32_t)DTHREADS ? DTHREADS / 32 : (left + 31) / 32, cnt, t.order);
     }
 }
 
@@ -120,9 +162,7 @@ __global__ void __launch_bounds__(DTHREADS) dispatch_scan_kernel(uint32_t nblk, 
                                                                  uint32_t HEAVY, const uint8_t* __restrict__ loaded, uint32_t* status) {
     extern __shared__ uint32_t dsm[];
     uint32_t* cnt = dsm;
-    uint32_t* chunk_base = dsm + E;
-    uint32_t* group_base = chunk_base + E + 1;
-    __shared__ uint32_t s_ok;
+    uint32_t* ws = dsm + E;
     const uint32_t tid = threadIdx.x;
     for (uint32_t e = tid; e < E; e += DTHREADS) {  // counts per expert; blk_cnt becomes the block's base inside the expert
         uint32_t run = 0;
@@ -134,79 +174,37 @@ __global__ void __launch_bounds__(DTHREADS) dispatch_scan_kernel(uint32_t nblk, 
         cnt[e] = run;
     }
     __syncthreads();
-    if (tid == 0) {
-        uint32_t rows = 0, chunks = 0, groups = 0, distinct = 0;
-        for (uint32_t e = 0; e < E; ++e) {
-            const uint32_t c = cnt[e];
-            t.offsets[e] = rows;
-            chunk_base[e] = chunks;
-            group_base[e] = groups;
-            const uint32_t nc = takes_tensor_lane(c, HEAVY, loaded, e) ? 0u : (c + CHUNK_ROWS - 1) / CHUNK_ROWS;
-            rows += c;
-            chunks += nc;
-            groups += (nc + GROUP_CHUNKS - 1) / GROUP_CHUNKS;
-            distinct += c ? 1u : 0u;
-        }
-        t.offsets[E] = rows;
-        s_ok = 1;
-        if (chunks > t.max_chunks) { atomicMax(status, (uint32_t)ST_WORKLIST_OVERFLOW); chunks = 0; groups = 0; s_ok = 0; }
-        t.header[HDR_NCHUNKS] = chunks;
-        t.header[HDR_NGROUPS] = groups;
-        t.header[HDR_CTR_GU] = 0;
-        t.header[HDR_CTR_DOWN] = 0;
-        t.header[HDR_CTR_AUX] = 0;
-        t.header[HDR_DISTINCT] = distinct;
-    }
-    __syncthreads();
-    if (!s_ok) return;
-    for (uint32_t e = tid; e < E; e += DTHREADS) {
-        const uint32_t c = cnt[e], row0 = t.offsets[e];
-        const uint32_t nc = takes_tensor_lane(c, HEAVY, loaded, e) ? 0u : (c + CHUNK_ROWS - 1) / CHUNK_ROWS;
-        for (uint32_t i = 0; i < nc; ++i) {
-            const uint32_t ch = chunk_base[e] + i;
-            t.chunk_expert[ch] = e;
-            t.chunk_row0[ch] = row0 + i * CHUNK_ROWS;
-            t.chunk_rows[ch] = min(CHUNK_ROWS, c - i * CHUNK_ROWS);
-        }
-        const uint32_t ng = (nc + GROUP_CHUNKS - 1) / GROUP_CHUNKS;
-        for (uint32_t i = 0; i < ng; ++i) {
-            t.group_chunk0[group_base[e] + i] = chunk_base[e] + i * GROUP_CHUNKS;
-            t.group_mc[group_base[e] + i] = min(GROUP_CHUNKS, nc - i * GROUP_CHUNKS);
-        }
-    }
+    build_tables(cnt, E, loaded, t, CHUNK_ROWS, GROUP_CHUNKS, HEAVY, ws, status);
 }
 __global__ void __launch_bounds__(DTHREADS) dispatch_place_kernel(const int32_t* __restrict__ ids, uint32_t A, uint32_t E,
                                                                   const uint32_t* __restrict__ blk_base, DispatchTables t) {
-    __shared__ uint32_t blk[DTHREADS];
-    const uint32_t tid = threadIdx.x, a = blockIdx.x * DTHREADS + tid;
-    uint32_t id = 0xFFFFFFFFu;
+    extern __shared__ uint32_t dsm[];   // [E] running positions of this block
+    const uint32_t tid = threadIdx.x, a0 = blockIdx.x * DTHREADS, a = a0 + tid, left = A - a0;
+    for (uint32_t e = tid; e < E; e += DTHREADS) dsm[e] = t.offsets[e] + blk_base[(size_t)blockIdx.x * E + e];
+    __syncthreads();
+    uint32_t id = 0;
     if (a < A) {
         const int32_t v = ids[a];
         id = (v < 0 || (uint32_t)v >= E) ? 0u : (uint32_t)v;
     }
-    blk[tid] = id;
-    __syncthreads();
-    if (a < A) {
-        uint32_t r = 0;
-        for (uint32_t j = 0; j < tid; ++j) r += (blk[j] == id) ? 1u : 0u;
-        t.order[t.offsets[id] + blk_base[(size_t)blockIdx.x * E + id] + r] = a;
-    }
+    place_block(id, a < A, a, left >= (uint32_t)DTHREADS ? DTHREADS / 32 : (left + 31) / 32, dsm, t.order);
 }
 
 cudaError_t launch_dispatch_large(const int32_t* ids, uint32_t A, uint32_t E, const uint8_t* loaded, DispatchTables t,
                                   uint32_t chunk_rows, uint32_t group_chunks, uint32_t heavy, uint32_t* blk_cnt,
                                   uint32_t* status, cudaStream_t st) {
+    if (E > (uint32_t)DTHREADS) return cudaErrorInvalidValue;
     const uint32_t nblk = (A + DTHREADS - 1) / DTHREADS;
     dispatch_count_kernel<<<nblk, DTHREADS, E * sizeof(uint32_t), st>>>(ids, A, E, loaded, blk_cnt, status);
-    dispatch_scan_kernel<<<1, DTHREADS, (3 * E + 2) * sizeof(uint32_t), st>>>(nblk, E, blk_cnt, t, chunk_rows, group_chunks, heavy, loaded, status);
-    dispatch_place_kernel<<<nblk, DTHREADS, 0, st>>>(ids, A, E, blk_cnt, t);
+    dispatch_scan_kernel<<<1, DTHREADS, (E + 99) * sizeof(uint32_t), st>>>(nblk, E, blk_cnt, t, chunk_rows, group_chunks, heavy, loaded, status);
+    dispatch_place_kernel<<<nblk, DTHREADS, E * sizeof(uint32_t), st>>>(ids, A, E, blk_cnt, t);
     return cudaGetLastError();
 }
 
 cudaError_t launch_dispatch(const int32_t* ids, uint32_t A, uint32_t E, const uint8_t* loaded, DispatchTables t,
                             uint32_t chunk_rows, uint32_t group_chunks, uint32_t heavy, uint32_t* status, cudaStream_t st) {
-    size_t smem = (size_t)(3 * E + 2 + DTHREADS) * sizeof(uint32_t);
-    dispatch_kernel<<<1, DTHREADS, smem, st>>>(ids, A, E, loaded, t, chunk_rows, group_chunks, heavy, status);
+    if (E > (uint32_t)DTHREADS) return cudaErrorInvalidValue;
+    dispatch_kernel<<<1, DTHREADS, (E + 99) * sizeof(uint32_t), st>>>(ids, A, E, loaded, t, chunk_rows, group_chunks, heavy, status);
     return cudaGetLastError();
 }
 

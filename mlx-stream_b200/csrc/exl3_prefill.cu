@@ -51,15 +51,22 @@ __global__ void pf_plan_kernel(DispatchTables t, uint32_t E, const uint8_t* __re
                                uint32_t* status) {
     __shared__ uint32_t base0[1025], base1[1025];
     const uint32_t tid = threadIdx.x;
+    // tiles per expert in parallel (base0 / base1 hold the counts first), then one thread turns them into offsets
+    for (uint32_t e = tid; e < E; e += blockDim.x) {
+        const uint32_t c = t.offsets[e + 1] - t.offsets[e];
+        const bool lane = takes_tensor_lane(c, min_rows, flags, e), list1 = cap1 && c > cap0;
+        base0[e] = lane && !list1 ? (c + cap0 - 1) / cap0 : 0u;
+        base1[e] = lane && list1 ? (c + cap1 - 1) / cap1 : 0u;
+    }
+    __syncthreads();
     if (tid == 0) {
         uint32_t n0 = 0, n1 = 0;
         for (uint32_t e = 0; e < E; ++e) {
+            const uint32_t c0 = base0[e], c1 = base1[e];
             base0[e] = n0;
             base1[e] = n1;
-            const uint32_t c = t.offsets[e + 1] - t.offsets[e];
-            if (!takes_tensor_lane(c, min_rows, flags, e)) continue;
-            if (cap1 && c > cap0) n1 += (c + cap1 - 1) / cap1;
-            else n0 += (c + cap0 - 1) / cap0;
+            n0 += c0;
+            n1 += c1;
         }
         if (n0 > max_tiles || n1 > max_tiles) { atomicMax(status, (uint32_t)ST_WORKLIST_OVERFLOW); n0 = 0; n1 = 0; }
         base0[E] = n0;

@@ -75,20 +75,83 @@ __global__ void router_kernel(const float* __restrict__ logits, const float* __r
         __syncthreads();
     }
     const float biased = bias ? __fadd_rn(score, e < E ? bias[e] : 0.0f) : score;
-    if (e < E) key_sh[e] = biased;
-    __syncthreads();
-    if (e < E) {
-        const bool mn = biased != biased;
-        int rank = 0;
-        for (int j = 0; j < E; ++j) {
-            const float o = key_sh[j];
-            const bool on = o != o;
-            const bool before = mn ? (!on || j < e) : (!on && (o > biased || (o == biased && j < e)));
-            rank += before ? 1 : 0;
+    const int nwarps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (K <= 32 && nwarps * K <= 256 && 2 * nwarps * K <= E + 34) {
+        // Selection by repeated maximum of a total order that is the rank rule: the float key mapped monotonically to
+        // an unsigned (NaN lowest, -0 folded into +0 so that equal floats tie), ties to the lower index.  Each warp
+        // takes the K best of its 32 experts with warp-wide max / min reductions, warp 0 then takes the K best of the
+        // nwarps x K candidates.  The result is the same permutation the rank count gives.
+        uint32_t* cand_key = reinterpret_cast<uint32_t*>(key_sh);          // [nwarps * K]
+        uint32_t* cand_idx = cand_key + nwarps * K;                         // needs 2 * nwarps * K <= E + 34 + K words
+        float* cand_score = picked + K;                                     // [nwarps * K]
+        uint32_t mykey = 0;
+        if (e < E && biased == biased) {
+            const uint32_t b = __float_as_uint(__fadd_rn(biased, 0.0f));
+            mykey = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+            // a NaN stays 0, the lowest; a real key is >= 1 (~0xFF800000 for -inf is 0x007FFFFF)
         }
-        if (rank < K) {
-            ids[(size_t)row * K + rank] = e;
-            picked[rank] = score;
+        bool alive = e < E;
+        for (int r = 0; r < K; ++r) {
+            const uint32_t k = alive ? mykey : 0u;
+            const uint32_t best = __reduce_max_sync(0xFFFFFFFFu, k);
+            const uint32_t who = __reduce_min_sync(0xFFFFFFFFu, (alive && k == best) ? (uint32_t)lane : 0xFFFFFFFFu);
+            if (who == 0xFFFFFFFFu) {  // fewer than K experts in this warp
+                if (lane == 0) { cand_key[warp * K + r] = 0; cand_idx[warp * K + r] = 0xFFFFFFFFu; }
+                continue;
+            }
+            if ((uint32_t)lane == who) {
+                cand_key[warp * K + r] = mykey; cand_idx[warp * K + r] = (uint32_t)e; cand_score[warp * K + r] = score;
+                alive = false;
+            }
+        }
+        __syncthreads();
+        if (warp == 0) {
+            const int C = nwarps * K, per = (C + 31) / 32;   // per <= 8
+            uint32_t ck[8], ci[8];
+            float cs[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int c = lane + 32 * i;
+                const bool ok = i < per && c < C;
+                ck[i] = ok ? cand_key[c] : 0u;
+                ci[i] = ok ? cand_idx[c] : 0xFFFFFFFFu;
+                cs[i] = ok ? cand_score[c] : 0.0f;
+            }
+            for (int r = 0; r < K; ++r) {
+                // this lane's best live candidate: highest key, then lowest expert index
+                uint32_t bk = 0, bi = 0xFFFFFFFFu;
+                int bslot = -1;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    if (ci[i] != 0xFFFFFFFFu && (bslot < 0 || ck[i] > bk || (ck[i] == bk && ci[i] < bi))) { bk = ck[i]; bi = ci[i]; bslot = i; }
+                }
+                const uint32_t best = __reduce_max_sync(0xFFFFFFFFu, bslot >= 0 ? bk : 0u);
+                const uint32_t who = __reduce_min_sync(0xFFFFFFFFu, (bslot >= 0 && bk == best) ? bi : 0xFFFFFFFFu);
+                if (bslot >= 0 && bi == who) {
+                    float sc = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) if (i == bslot) { sc = cs[i]; ci[i] = 0xFFFFFFFFu; }
+                    ids[(size_t)row * K + r] = (int32_t)who;
+                    picked[r] = sc;
+                }
+            }
+        }
+    } else {
+        if (e < E) key_sh[e] = biased;
+        __syncthreads();
+        if (e < E) {
+            const bool mn = biased != biased;
+            int rank = 0;
+            for (int j = 0; j < E; ++j) {
+                const float o = key_sh[j];
+                const bool on = o != o;
+                const bool before = mn ? (!on || j < e) : (!on && (o > biased || (o == biased && j < e)));
+                rank += before ? 1 : 0;
+            }
+            if (rank < K) {
+                ids[(size_t)row * K + rank] = e;
+                picked[rank] = score;
+            }
         }
     }
     __syncthreads();
@@ -105,7 +168,8 @@ cudaError_t launch_router(const float* logits, const float* bias, int T, int E, 
                           float scale, int32_t* ids, float* weights, cudaStream_t st) {
     if (T == 0) return cudaSuccess;
     int threads = ((E > K ? E : K) + 31) / 32 * 32;
-    size_t smem = (size_t)(E + 34 + K) * sizeof(float);
+    const int nwarps = threads / 32;
+    size_t smem = (size_t)(E + 34 + K + (nwarps * K <= 256 ? nwarps * K : 0)) * sizeof(float);
     router_kernel<<<T, threads, smem, st>>>(logits, bias, E, K, scoring, norm, scale, ids, weights);
     return cudaGetLastError();
 }
