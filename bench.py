@@ -160,32 +160,52 @@ def own_launches_per_layer(T, world):
 def reference_arm(args):
     """The reference's CPU path for this layer, timed on the host cores.  The reference's own CPU lane (Zig tests over
     MLX's CPU device) cannot be built here (no zig, no mlx), so this runs the oracle's fast f32 form (kind "port")."""
-    import oracle_lib as O
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    T = args.cpu_tokens
+    # all host threads this process may use (a launcher may have set OMP_NUM_THREADS=1 for its ranks)
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    os.environ["OMP_NUM_THREADS"] = str(threads)
+    import oracle_lib as O
     rng = np.random.default_rng(1234)
-    threads = O.max_threads()
-    lg = make_logits(rng, T, args.routing)
-    ids, w = O.route(lg, None, K_TOP, O.SCORE_SQRTSOFTPLUS, scale=1.5)
-    recs = {int(e): O.exl3_synth_record(0xB200 + int(e), H, I, 1.0, 0.02) for e in np.unique(ids)}
     srng = np.random.default_rng(7)
-    shared = [O.f32_to_bf16_bits((srng.standard_normal(s) * 0.02).astype(np.float32))
-              for s in ((I, H), (I, H), (H, I))]
-    x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(rng.standard_normal((T, H)).astype(np.float32)))
+    shared = None
+    if WL["shared"]:
+        shared = [O.f32_to_bf16_bits((srng.standard_normal(s) * 0.02).astype(np.float32))
+                  for s in ((I, H), (I, H), (H, I))]
+    if WL["bank"] == "exl3":
+        T = args.cpu_tokens
+        lg = make_logits(rng, T, args.routing)
+        ids, w = O.route(lg, None, K_TOP, O.SCORE_SQRTSOFTPLUS, scale=1.5)
+        recs = {int(e): O.exl3_synth_record(0xB200 + int(e), H, I, 1.0, 0.02) for e in np.unique(ids)}
+        x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(rng.standard_normal((T, H)).astype(np.float32)))
+        call = lambda: O.layer_fast(H, I, E, K_TOP, recs, x, ids, w, shared=shared, threads=threads)
+        form = "oracle fast f32 form"
+    else:
+        # FP4 banks: the oracle's f64 layer over exactly decoded weights (there is no faster CPU form of it)
+        T = min(args.cpu_tokens, 2)
+        nv = WL["bank"] == "nvfp4"
+        lg = make_logits(rng, T, args.routing)
+        ids, w = O.route(lg, None, K_TOP, O.SCORE_SIGMOID if nv else O.SCORE_SOFTMAX, scale=1.0)
+        synth = O.nvfp4_synth_record if nv else O.mxfp4_synth_record
+        recs = {int(e): synth(0xB200 + int(e), H, I, 0.02) for e in np.unique(ids)}
+        x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(rng.standard_normal((T, H)).astype(np.float32)))
+        bank = O.BANK_NVFP4 if nv else O.BANK_MXFP4
+        call = lambda: O.layer(bank, H, I, E, K_TOP, recs, x, ids, w, shared=shared, limit=10.0 if nv else 0.0,
+                               chain_rounding=True, shared_bf16_add=True)
+        form = "oracle f64 form"
     for _ in range(args.warmup):
-        O.layer_fast(H, I, E, K_TOP, recs, x, ids, w, shared=shared, threads=threads)
+        call()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        O.layer_fast(H, I, E, K_TOP, recs, x, ids, w, shared=shared, threads=threads)
+        call()
     dt = time.perf_counter() - t0
     v = T * args.steps / dt
-    sample = f"{T} tokens x top-{K_TOP} per step ({len(recs)} distinct experts), whole layer incl. shared expert"
+    sample = f"{T} tokens x top-{K_TOP} per step ({len(recs)} distinct experts), whole layer, {form}"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32 accumulate over f16-valued EXL3 weights", "data": "synthetic",
+        "vs_baseline": None, "dtype": "f32" if WL["bank"] == "exl3" else "f64", "data": "synthetic",
         "config": workload_config(args, T),
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
