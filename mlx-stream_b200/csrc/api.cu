@@ -404,7 +404,11 @@ extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, 
     if (c.shared_expert && !L.sh_w1) return fail(MLXS_E_NOT_LOADED, "experts: layer %u has no shared expert weights", layer);
     // FP4 banks with the chain combine keep the routed rows in bf16, as the reference's down texts store them
     const int ro_bf16 = c.bank_kind != MLXS_BANK_EXL3_K3_MUL1 && c.combine == MLXS_COMBINE_CHAIN;
-    if ((rc = run_routed(h, layer, x_dev, ids_dev, T, h->ro, ro_bf16, st))) return rc;
+    // expert parallel with the f32 combine: the exchange carries each token once per rank and brings weighted partial
+    // rows back (ep.cu); the chain combine needs every assignment's row in k order and keeps the per-assignment form
+    static const bool per_assignment = getenv("MLXS_EP_PER_ASSIGNMENT") != nullptr;
+    const bool ep_fused = c.ep_world > 1 && c.combine != MLXS_COMBINE_CHAIN && !per_assignment;
+    if (!ep_fused && (rc = run_routed(h, layer, x_dev, ids_dev, T, h->ro, ro_bf16, st))) return rc;
     const float* shared = nullptr;
     if (c.shared_expert) {
         StageTimer tm(h, MLXS_STAGE_SHARED, st);
@@ -418,6 +422,10 @@ extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, 
                                     lim, h->sh_h, h->sh_out, st));
         }
         shared = h->sh_out;
+    }
+    if (ep_fused) {
+        h->stats.tokens += T;
+        return mlxs_ep_combined(h, layer, x_dev, ids_dev, weights_dev, T, shared, y_dev, st);
     }
     StageTimer tm(h, MLXS_STAGE_COMBINE, st);
     CU(launch_combine(h->ro, ro_bf16, weights_dev, shared, T, c.top_k, c.hidden, c.combine == MLXS_COMBINE_CHAIN,

@@ -103,7 +103,7 @@ __global__ void __launch_bounds__(CHUNK_ROWS * 32) exl3_prep_kernel(const void* 
     const uint32_t e = t.chunk_expert[chunk], rows = t.chunk_rows[chunk];
     const bool valid = warp < rows;
     const uint32_t assign = valid ? t.order[t.chunk_row0[chunk] + warp] : 0u;
-    const uint32_t tok = assign / top_k;
+    const uint32_t tok = x_row_of(t, assign, top_k);
     const uint32_t nkt = in_dim / 16;
     constexpr int NP = RAW ? 1 : 2;
     const float S = __uint_as_float(SCALE_BITS);

@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(256) pf_prep_kernel(const __nv_bfloat16* __res
     const uint32_t nstage = H / PF_KS;
     for (uint32_t r = warp; r < rows16; r += 8) {
         const bool valid = r < rows;
-        const uint32_t tok = valid ? t.order[row0 + r] / top_k : 0u;
+        const uint32_t tok = valid ? x_row_of(t, t.order[row0 + r], top_k) : 0u;
         uint2 xb = make_uint2(0, 0);
         if (valid) xb = *reinterpret_cast<const uint2*>(x + (size_t)tok * H + b * 128 + lane * 4);
         const float x0 = __uint_as_float(xb.x << 16), x1 = __uint_as_float(xb.x & 0xFFFF0000u);

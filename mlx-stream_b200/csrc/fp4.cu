@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(256) fp4_prep_kernel(const __nv_bfloat16* __re
     if (chunk >= t.header[HDR_NCHUNKS]) return;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;  // warp = row slot
     const bool valid = warp < t.chunk_rows[chunk];
-    const uint32_t tok = valid ? t.order[t.chunk_row0[chunk] + warp] / top_k : 0u;
+    const uint32_t tok = valid ? x_row_of(t, t.order[t.chunk_row0[chunk] + warp], top_k) : 0u;
     // a lane converts 8 consecutive inputs: block sb = idx / 4, word c = idx % 4
     for (uint32_t idx = blockIdx.y * 32 + lane; idx < H / 8; idx += gridDim.y * 32) {
         uint4 raw = make_uint4(0, 0, 0, 0);

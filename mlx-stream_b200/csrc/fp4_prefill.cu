@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(256) q_prep_kernel(const __nv_bfloat16* __rest
     for (uint32_t i = blockIdx.y * blockDim.x + threadIdx.x; i < rows16 * groups; i += gridDim.y * blockDim.x) {
         const uint32_t r = i % rows16, kg = i / rows16;
         uint4 raw = make_uint4(0, 0, 0, 0);
-        if (r < rows) raw = *reinterpret_cast<const uint4*>(x + (size_t)(t.order[row0 + r] / top_k) * H + (size_t)kg * 8);
+        if (r < rows) raw = *reinterpret_cast<const uint4*>(x + (size_t)x_row_of(t, t.order[row0 + r], top_k) * H + (size_t)kg * 8);
         const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
         uint16_t e[8];
 #pragma unroll

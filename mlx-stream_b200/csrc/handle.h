@@ -104,4 +104,8 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
 // the expert-parallel form of the same (ep.cu): dispatch all-to-all, local experts, combine all-to-all
 int mlxs_ep_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, uint32_t T, void* ro,
                    int ro_bf16, cudaStream_t st);
+// the layer form with the f32 combine folded in: a token's row travels once per destination rank, weighted partial rows
+// come back; y = bf16(sum of partials + shared row)
+int mlxs_ep_combined(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, const float* weights_dev,
+                     uint32_t T, const float* shared, void* y_dev, cudaStream_t st);
 void mlxs_ep_destroy(mlxs_moe* h);

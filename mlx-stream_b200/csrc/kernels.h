@@ -22,7 +22,12 @@ struct DispatchTables {
     uint32_t* group_chunk0;  // [max_chunks]
     uint32_t* group_mc;      // [max_chunks]
     uint32_t max_chunks;
+    const uint32_t* xrow;    // optional [A]: row of x an assignment reads (null: assignment / top_k)
 };
+// the row of x behind assignment a
+__host__ __device__ inline uint32_t x_row_of(const DispatchTables& t, uint32_t a, uint32_t top_k) {
+    return t.xrow ? t.xrow[a] : a / top_k;
+}
 enum { HDR_NCHUNKS = 0, HDR_NGROUPS = 1, HDR_CTR_GU = 2, HDR_CTR_DOWN = 3, HDR_DISTINCT = 4, HDR_CTR_AUX = 5 };
 
 cudaError_t launch_router(const float* logits, const float* bias, int T, int E, int K, int scoring, int norm,

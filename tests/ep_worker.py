@@ -63,10 +63,16 @@ def main():
         moe.forward(0, xd.data_ptr(), lg.data_ptr(), T, y.data_ptr(), None)
         torch.cuda.synchronize()
         ids, w = O.route(logits, None, k, O.SCORE_SQRTSOFTPLUS, scale=1.5)
-        ref = O.layer(O.BANK_EXL3, H, I, E, k, records, x, ids, w, shared=shared, limit=10.0)
+        ref, ref_ro = O.layer(O.BANK_EXL3, H, I, E, k, records, x, ids, w, shared=shared, limit=10.0, want_ro=True)
         err = rel_l2(y.float().cpu().numpy(), ref)
-        print(f"rank {rank} iter {it} rel-L2 {err:.3e}", flush=True)
-        ok = ok and err < 1e-2
+        # the per-assignment form of the exchange (unweighted rows of every assignment, a collective call too)
+        idd = torch.from_numpy(np.ascontiguousarray(ids, np.int32)).to(dev)
+        ro = torch.full((T, k, H), float("nan"), dtype=torch.float32, device=dev)
+        moe.routed(0, xd.data_ptr(), idd.data_ptr(), T, ro.data_ptr(), None)
+        torch.cuda.synchronize()
+        err_ro = rel_l2(ro.cpu().numpy(), ref_ro)
+        print(f"rank {rank} iter {it} rel-L2 layer {err:.3e} rows {err_ro:.3e}", flush=True)
+        ok = ok and err < 1e-2 and err_ro < 1e-3
     st = moe.stats()
     print(f"rank {rank} status {st.device_status} a2a sent {st.a2a_bytes_sent} recv {st.a2a_bytes_recv}", flush=True)
     ok = ok and st.device_status == 0 and st.a2a_bytes_sent > 0

@@ -94,6 +94,106 @@ def _rank(rank, world, port, q):
     q.put((rank, err, int(R)))
 
 
+def _exchange(dist, torch, rank, world, pieces, recv_shapes, dtype, tag):
+    """Pairwise exchange with exact counts: pieces[peer] goes to peer, returns what every peer sent here."""
+    got = [torch.zeros(shape, dtype=dtype) for shape in recv_shapes]
+    reqs = []
+    for peer in range(world):
+        if peer == rank:
+            got[peer].copy_(pieces[peer])
+        else:
+            reqs += [dist.isend(pieces[peer].contiguous(), peer, tag=tag), dist.irecv(got[peer], peer, tag=tag)]
+    for r in reqs:
+        r.wait()
+    return got
+
+
+def _rank_dedup(rank, world, port, q):
+    """The layer form of the exchange: a token's row travels once per destination rank, the owning rank folds
+    weight x row over the token's experts it holds, one partial row per (token, rank) comes back."""
+    sys.path.insert(0, str(HERE))
+    sys.path.insert(0, str(HERE.parent))
+    import torch
+    import torch.distributed as dist
+
+    import oracle_lib as O
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    H, I, E, k, T = 256, 128, 8, 4, 6 + 3 * rank
+    e_local = E // world
+    records = {e: O.exl3_synth_record(0xABC0 + e, H, I, 1.0, 0.02) for e in range(E)}
+    rs = np.random.default_rng(20 + rank)
+    x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(rs.standard_normal((T, H)).astype(np.float32)))
+    logits = rs.standard_normal((T, E)).astype(np.float32)
+    ids, w = O.route(logits, None, k, O.SCORE_SIGMOID)
+    flat, wflat = ids.reshape(-1), w.reshape(-1)
+    dest = flat // e_local
+    order = np.argsort(dest, kind="stable")
+    tok = order // k
+    # first assignment of each (token, rank) pair in sorted order, and the unique row every position reads
+    first = np.ones(order.size, bool)
+    first[1:] = (tok[1:] != tok[:-1]) | (dest[order][1:] != dest[order][:-1])
+    urow = np.cumsum(first) - 1
+    n_a = np.bincount(dest, minlength=world)
+    n_u = np.array([int(first[dest[order] == r].sum()) for r in range(world)])
+    assert n_u.sum() < order.size  # top-4 over 2 ranks: rows are shared
+    a0, u0 = np.concatenate([[0], np.cumsum(n_a)]), np.concatenate([[0], np.cumsum(n_u)])
+    send_x = x[tok[first]]
+    send_meta = (flat[order] % e_local).astype(np.int32)
+    send_urow = (urow - u0[dest[order]]).astype(np.int32)
+    send_w = wflat[order].astype(np.float32)
+    counts = torch.from_numpy(np.stack([n_a, n_u], 1).astype(np.int64))
+    allc = [torch.zeros((world, 2), dtype=torch.int64) for _ in range(world)]
+    dist.all_gather(allc, counts)
+    ra = [int(allc[s][rank][0]) for s in range(world)]
+    ru = [int(allc[s][rank][1]) for s in range(world)]
+    sp = lambda arr, off: [torch.from_numpy(np.ascontiguousarray(arr[off[r]:off[r + 1]])) for r in range(world)]
+    rx = _exchange(dist, torch, rank, world, sp(send_x, u0), [(n, H) for n in ru], torch.float32, 1)
+    rm = _exchange(dist, torch, rank, world, sp(send_meta, a0), [(n,) for n in ra], torch.int32, 2)
+    rr = _exchange(dist, torch, rank, world, sp(send_urow, a0), [(n,) for n in ra], torch.int32, 3)
+    rw = _exchange(dist, torch, rank, world, sp(send_w, a0), [(n,) for n in ra], torch.float32, 4)
+    ubase = np.concatenate([[0], np.cumsum(ru)])
+    recv_x = torch.cat(rx).numpy()
+    recv_meta = torch.cat(rm).numpy()
+    recv_w = torch.cat(rw).numpy()
+    xrow = np.concatenate([rr[s].numpy() + ubase[s] for s in range(world)]) if sum(ra) else np.zeros(0, np.int64)
+    RA = recv_meta.size
+    local_recs = {e: records[rank * e_local + e] for e in range(e_local)}
+    partial = np.zeros((int(sum(ru)), H))
+    if RA:
+        ro = O.layer(O.BANK_EXL3, H, I, e_local, 1, local_recs, recv_x[xrow], recv_meta.reshape(-1, 1),
+                     np.ones((RA, 1), np.float32), limit=10.0)
+        np.add.at(partial, xrow, ro * recv_w[:, None].astype(np.float64))
+    back = _exchange(dist, torch, rank, world,
+                     [torch.from_numpy(np.ascontiguousarray(partial[ubase[s]:ubase[s + 1]])) for s in range(world)],
+                     [(int(n), H) for n in n_u], torch.float64, 5)
+    ret = torch.cat(back).numpy()
+    y = np.zeros((T, H))
+    np.add.at(y, tok[first], ret)
+    ref = O.layer(O.BANK_EXL3, H, I, E, k, records, x, ids, w, limit=10.0)
+    err = float(np.abs(y - ref).max() / (np.abs(ref).max() + 1e-30))
+    dist.barrier()
+    dist.destroy_process_group()
+    q.put((rank, err, int(RA)))
+
+
+def test_ep_dedup_protocol_world2_gloo():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_dedup, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, err, RA in res:
+        assert err < 1e-12, (rank, err)
+    assert sum(r[2] for r in res) == (6 + 9) * 4
+
+
 def test_ep_protocol_world2_gloo():
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
