@@ -128,13 +128,19 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def make_logits(rng, T, routing):
+def zipf_bias(layer):
+    """ln p_e of a layer's expert popularity: p_e ~ rank^-1.1 over a permutation seeded by the layer, the same on every
+    rank and for every batch (popularity is a property of the layer, which is what a usage-based placement relies on)."""
+    perm = np.random.default_rng(4242 + layer).permutation(E)
+    p = (np.arange(1, E + 1, dtype=np.float64) ** -1.1)
+    p /= p.sum()
+    return np.log(p)[np.argsort(perm)].astype(np.float32)
+
+
+def make_logits(rng, T, routing, layer=0):
     lg = rng.standard_normal((T, E)).astype(np.float32)
     if routing == "zipf":
-        perm = rng.permutation(E)
-        p = (np.arange(1, E + 1, dtype=np.float64) ** -1.1)
-        p /= p.sum()
-        lg = lg + np.log(p)[np.argsort(perm)].astype(np.float32)
+        lg = lg + zipf_bias(layer)
     return lg
 
 
@@ -217,7 +223,7 @@ def workload_config(args, T):
             "hidden": H, "inter": I, "n_experts": E, "top_k": K_TOP, "shared_expert": "bf16" if WL["shared"] else "none",
             "tokens_per_call": T,
             "layers": getattr(args, "layers", 1), "routing": args.routing, "l2": "inputs larger than L2 (each call streams >2 GB of distinct expert code)",
-            "parallelism": "single GPU" if args.gpus == 1 else f"ep{args.gpus}"}
+            "parallelism": "single GPU" if args.gpus == 1 else f"ep{args.gpus}, experts placed: {getattr(args, 'placement', 'contiguous')}"}
 
 
 def main():
@@ -232,6 +238,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--experts", type=int, default=0, help="routed experts (smaller only for profiler captures)")
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--placement", default="contiguous", choices=["contiguous", "usage"],
+                    help="expert parallel: experts in contiguous blocks, or dealt to the ranks by a routing histogram")
     ap.add_argument("--layers", type=int, default=1,
                     help="stack of identical-shape layers run back to back per step (BASELINE config 5 uses 24)")
     args = ap.parse_args()
@@ -281,14 +289,51 @@ def main():
         dist.broadcast(idt, 0)
         if pkg.lib().mlxs_moe_ep_init(moe._h, bytes(idt.cpu().numpy().tobytes())) != 0:
             raise SystemExit("bench.py: " + pkg.last_error())
-    e_lo, e_hi = rank * (E // world), (rank + 1) * (E // world)
-    logical, stride = moe.record_bytes()
+    rng = np.random.default_rng(99 + rank)
+    n_batches = 4  # rotate a few seeded batches so consecutive steps route differently
     g = torch.Generator(device=dev)
     g.manual_seed(1000 + rank)
+    xs, lgs, x_host, lg_host = [], [], [], []
+    biases = [torch.from_numpy(zipf_bias(l)).to(dev) for l in range(NL)] if args.routing == "zipf" else None
+    for b in range(n_batches):
+        noise = rng.standard_normal((T, E)).astype(np.float32)
+        x = torch.randn((T, H), device=dev, generator=g).to(torch.bfloat16)
+        xs.append(x)
+        nd = torch.from_numpy(noise).to(dev)
+        # logits of (batch, layer): the batch's noise + the layer's popularity (one tensor for all layers without skew)
+        lgs.append([nd + biases[l] for l in range(NL)] if biases else [nd] * NL)
+        x_host.append(x.cpu().pin_memory())
+        lg_host.append(lgs[b][0].cpu().pin_memory())
+    stream = torch.cuda.current_stream()
+    sp = stream.cuda_stream
+
+    # where the experts live: contiguous blocks, or dealt out by usage (a histogram of the routed ids of the batches,
+    # summed over the ranks; experts sorted by load and dealt to the ranks in snake order, E / N each)
+    rank_of = [np.arange(E) // (E // world) for _ in range(NL)]
+    if world > 1 and args.placement == "usage":
+        ids_dev = torch.empty((T, K_TOP), dtype=torch.int32, device=dev)
+        w_dev = torch.empty((T, K_TOP), dtype=torch.float32, device=dev)
+        for l in range(NL):
+            hist = torch.zeros(E, dtype=torch.int64, device=dev)
+            for b in range(n_batches):
+                moe.route(l, lgs[b][l].data_ptr(), T, ids_dev.data_ptr(), w_dev.data_ptr(), sp)
+                torch.cuda.synchronize()
+                hist += torch.bincount(ids_dev.reshape(-1).long(), minlength=E)
+            dist.all_reduce(hist)
+            by_load = np.argsort(-hist.cpu().numpy(), kind="stable")
+            ro = np.empty(E, np.uint16)
+            for pos, e in enumerate(by_load):
+                lap, j = divmod(pos, world)
+                ro[e] = j if lap % 2 == 0 else world - 1 - j
+            rank_of[l] = ro.astype(np.int64)
+            moe.set_placement(l, np.ascontiguousarray(ro).ctypes.data)
+    owned = [np.nonzero(rank_of[l] == rank)[0] for l in range(NL)]
+    n_local = E // world
+    logical, stride = moe.record_bytes()
     code_bytes = (H // 16) * (I // 16) * 96
     if WL["bank"] == "exl3":
         # synthetic bank generated on the device in the reference's record layout: random trellis codes, +-(0.5+u) scales
-        for e in range(e_lo, e_hi):
+        for j in range(n_local):
             rec = torch.randint(0, 256, (stride,), dtype=torch.uint8, device=dev, generator=g)
             off = 0
             for p in range(3):
@@ -300,10 +345,10 @@ def main():
                     rec[off:off + 2 * n] = ((0.5 + u) * sgn * sc).to(torch.float16).view(torch.uint8)
                     off += 2 * n
             for l in range(NL):  # the stack's layers share one synthetic bank image (same bytes, separate residency)
-                moe.load_expert(l, e, rec.data_ptr(), stride, on_device=True)
+                moe.load_expert(l, int(owned[l][j]), rec.data_ptr(), stride, on_device=True)
     else:
         nv = WL["bank"] == "nvfp4"
-        for e in range(e_lo, e_hi):
+        for j in range(n_local):
             parts = []
             for p in range(3):
                 rows, cols = (H, I) if p == 2 else (I, H)
@@ -315,35 +360,23 @@ def main():
             rec = torch.cat(parts)
             assert rec.numel() == logical, (rec.numel(), logical)
             for l in range(NL):
-                moe.load_expert(l, e, rec.data_ptr(), rec.numel(), on_device=True)
+                moe.load_expert(l, int(owned[l][j]), rec.data_ptr(), rec.numel(), on_device=True)
     sw = None
     if WL["shared"]:
         sw = [(torch.randn(s, device=dev, generator=g) * 0.02).to(torch.bfloat16) for s in ((I, H), (I, H), (H, I))]
         for l in range(NL):
             moe.set_shared(l, sw[0].data_ptr(), sw[1].data_ptr(), sw[2].data_ptr(), on_device=True)
 
-    rng = np.random.default_rng(99 + rank)
-    n_batches = 4  # rotate a few seeded batches so consecutive steps route differently
-    xs, lgs, x_host, lg_host = [], [], [], []
-    for b in range(n_batches):
-        lg = make_logits(rng, T, args.routing)
-        x = torch.randn((T, H), device=dev, generator=g).to(torch.bfloat16)
-        xs.append(x)
-        lgs.append(torch.from_numpy(lg).to(dev))
-        x_host.append(x.cpu().pin_memory())
-        lg_host.append(torch.from_numpy(lg).pin_memory())
     y = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
     y2 = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
     y_host = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
-    stream = torch.cuda.current_stream()
-    sp = stream.cuda_stream
 
     def step(i):
         # a stack feeds each layer's output to the next one (the trunk between MoE layers is out of scope); every
         # layer routes with its own seeded logits
         src, a, b = xs[i % n_batches], y, y2
         for l in range(NL):
-            moe.forward(l, src.data_ptr(), lgs[(i + l) % n_batches].data_ptr(), T, a.data_ptr(), sp)
+            moe.forward(l, src.data_ptr(), lgs[(i + l) % n_batches][l].data_ptr(), T, a.data_ptr(), sp)
             src, a, b = a, b, a
 
     x_in = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
@@ -359,7 +392,7 @@ def main():
         lg_in.copy_(lg_host[i % n_batches], non_blocking=True)
         src, a, b = x_in, y, y2
         for l in range(NL):
-            moe.forward(l, src.data_ptr(), (lg_in if l == 0 else lgs[(i + l) % n_batches]).data_ptr(), T, a.data_ptr(), sp)
+            moe.forward(l, src.data_ptr(), (lg_in if l == 0 else lgs[(i + l) % n_batches][l]).data_ptr(), T, a.data_ptr(), sp)
             src, a, b = a, b, a
         y_host.copy_(src, non_blocking=True)
         stream.synchronize()
@@ -394,14 +427,14 @@ def main():
         step(b)
         distinct.append(int(moe.stats().distinct_experts_last))
         # rows per resident expert of layer 0 (which lane each expert takes is decided on these counts)
-        moe.route(0, lgs[b].data_ptr(), T, ids_dev.data_ptr(), w_dev.data_ptr(), sp)
+        moe.route(0, lgs[b][0].data_ptr(), T, ids_dev.data_ptr(), w_dev.data_ptr(), sp)
         torch.cuda.synchronize()
         all_ids = ids_dev
         if world > 1:
             all_ids = torch.empty((world * T, K_TOP), dtype=torch.int32, device=dev)
             dist.all_gather_into_tensor(all_ids, ids_dev)
         cnt = torch.bincount(all_ids.reshape(-1).long(), minlength=E).cpu().numpy()
-        lane_counts.append(cnt[rank * (E // world):(rank + 1) * (E // world)])
+        lane_counts.append(cnt[owned[0]])
     sampler = ClockSampler(local)
     sampler.start()
     moe.profile_enable(True)

@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define MLXS_MOE_ABI 2026112502
+#define MLXS_MOE_ABI 2026112503
 
 /* refusals (the names mirror the reference's refusal sets: src/sdk_ext/quant.zig:94-111, src/expert/bank.zig:79-101) */
 enum {
@@ -185,6 +185,11 @@ int mlxs_moe_ep_unique_id(void *id128_out);
 int mlxs_moe_ep_init(mlxs_moe *h, const void *id128);
 /* host-side plan of one exchange (pure function, also used by the CPU tests): for `n` assignments with expert ids
  * `ids`, counts per destination rank */
+/* Where a layer's experts live: rank_of_expert[e] in [0, ep_world), every rank exactly n_experts / ep_world of them;
+ * an expert's local slot is its order among the rank's experts.  Default: contiguous blocks.  Call on every rank with
+ * the same table before the layer's experts are loaded.  (The reference keeps a usage tally per expert for its
+ * residency policy, src/sdk_ext/expert/usage.zig; here the same histogram can balance the ranks' load.) */
+int mlxs_moe_set_placement(mlxs_moe *h, uint32_t layer, const uint16_t *rank_of_expert);
 int mlxs_moe_ep_plan(const int32_t *ids, uint64_t n, uint32_t n_experts, uint32_t world, uint64_t *send_counts);
 
 #ifdef __cplusplus

@@ -14,7 +14,7 @@ from pathlib import Path  # noqa: E402
 
 HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "libmlxs_moe.so"
-ABI = 2026112502
+ABI = 2026112503
 
 BANK_EXL3_K3_MUL1, BANK_MXFP4, BANK_NVFP4 = 0, 1, 2
 SCORE_SQRTSOFTPLUS, SCORE_SIGMOID, SCORE_SOFTMAX = 0, 1, 2
@@ -27,6 +27,7 @@ EXPORTS = [
     "mlxs_moe_routed", "mlxs_moe_experts", "mlxs_moe_forward", "mlxs_moe_forward_host", "mlxs_moe_exl3_gemv",
     "mlxs_moe_exl3_gemv_noalloc",
     "mlxs_moe_stats_get", "mlxs_moe_profile_enable", "mlxs_moe_profile_read", "mlxs_moe_ep_unique_id", "mlxs_moe_ep_init", "mlxs_moe_ep_plan",
+    "mlxs_moe_set_placement",
 ]
 
 
@@ -104,6 +105,7 @@ def lib():
         L.mlxs_moe_ep_unique_id.argtypes = [C.c_void_p]
         L.mlxs_moe_ep_init.argtypes = [C.c_void_p, C.c_void_p]
         L.mlxs_moe_ep_plan.argtypes = [C.c_void_p, C.c_uint64, C.c_uint32, C.c_uint32, C.c_void_p]
+        L.mlxs_moe_set_placement.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p]
         if L.mlxs_moe_abi() != ABI:
             raise RuntimeError(f"libmlxs_moe.so ABI {L.mlxs_moe_abi()} != binding ABI {ABI}")
         _lib = L
@@ -170,6 +172,9 @@ class MoE:
 
     def load_bank(self, directory):
         _check(lib().mlxs_moe_load_bank(self._h, str(directory).encode()))
+
+    def set_placement(self, layer, rank_of_expert_u16_ptr):
+        _check(lib().mlxs_moe_set_placement(self._h, layer, rank_of_expert_u16_ptr))
 
     def set_router_bias(self, layer, bias_host_ptr):
         _check(lib().mlxs_moe_set_router_bias(self._h, layer, bias_host_ptr))

@@ -103,8 +103,17 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
     const Exl3Dims d{c->hidden, c->inter};
     for (auto& L : h->layers) {
         L.loaded.assign(c->n_experts, 0);
-        if ((rc = h->alloc(&L.loaded_dev, c->n_experts))) return bail(rc);
+        if ((rc = h->alloc(&L.loaded_dev, c->n_experts)) || (rc = h->alloc(&L.place_dev, (size_t)c->n_experts * 4))) return bail(rc);
         cudaMemset(L.loaded_dev, 0, c->n_experts);
+        L.place_rank.resize(c->n_experts);
+        L.place_slot.resize(c->n_experts);
+        std::vector<uint32_t> packed(c->n_experts);
+        for (uint32_t e = 0; e < c->n_experts; ++e) {
+            L.place_rank[e] = (uint16_t)(e / h->e_local);
+            L.place_slot[e] = (uint16_t)(e % h->e_local);
+            packed[e] = ((uint32_t)L.place_rank[e] << 16) | L.place_slot[e];
+        }
+        cudaMemcpy(L.place_dev, packed.data(), packed.size() * 4, cudaMemcpyHostToDevice);
         if (c->bank_kind == MLXS_BANK_EXL3_K3_MUL1) {
             if ((rc = h->alloc(&L.gu_code, (size_t)h->e_local * 2 * exl3_code_words(d) * 4))) return bail(rc);
             if ((rc = h->alloc(&L.d_code, (size_t)h->e_local * exl3_code_words(d) * 4))) return bail(rc);
@@ -201,10 +210,10 @@ extern "C" int mlxs_moe_load_expert(mlxs_moe* h, uint32_t layer, uint32_t expert
     if (nbytes < h->logical_bytes)
         return fail(MLXS_E_BANK, "load_expert: record has %llu bytes, the bank kind's record is %llu (RecordGeometry)",
                     (unsigned long long)nbytes, (unsigned long long)h->logical_bytes);
-    if (expert < h->e_first || expert >= h->e_first + h->e_local) return MLXS_OK;  // another rank's shard
-    CU(cudaSetDevice(h->cfg.device));
     LayerBank& L = h->layers[layer];
-    const uint32_t le = expert - h->e_first;
+    if (L.place_rank[expert] != h->cfg.ep_rank) return MLXS_OK;  // another rank's shard
+    CU(cudaSetDevice(h->cfg.device));
+    const uint32_t le = L.place_slot[expert];
     const uint8_t* src = static_cast<const uint8_t*>(record);
     if (!on_device) {
         CU(cudaMemcpyAsync(h->staging, record, h->logical_bytes, cudaMemcpyHostToDevice, 0));
@@ -212,7 +221,7 @@ extern "C" int mlxs_moe_load_expert(mlxs_moe* h, uint32_t layer, uint32_t expert
     }
     // the expert's entry of the per-expert table: 1 = resident; the FP4 repack may raise it to 3 (see takes_tensor_lane)
     const uint8_t one = 1;
-    CU(cudaMemcpyAsync(L.loaded_dev + expert, &one, 1, cudaMemcpyHostToDevice, 0));
+    CU(cudaMemcpyAsync(L.loaded_dev + le, &one, 1, cudaMemcpyHostToDevice, 0));
     if (h->cfg.bank_kind == MLXS_BANK_EXL3_K3_MUL1) {
         const Exl3Dims d{h->cfg.hidden, h->cfg.inter};
         CU(launch_exl3_repack(src, d, L.gu_code + (size_t)le * 2 * exl3_code_words(d),
@@ -222,7 +231,7 @@ extern "C" int mlxs_moe_load_expert(mlxs_moe* h, uint32_t layer, uint32_t expert
         CU(launch_fp4_repack(src, h->cfg.hidden, h->cfg.inter, nv,
                              L.f4_gu + (size_t)le * fp4_stream_bytes_per_expert(h->cfg.hidden, h->cfg.inter, nv, 0),
                              L.f4_dn + (size_t)le * fp4_stream_bytes_per_expert(h->cfg.hidden, h->cfg.inter, nv, 1),
-                             L.f4_gscale + (size_t)le * 3, L.loaded_dev + expert, 0));
+                             L.f4_gscale + (size_t)le * 3, L.loaded_dev + le, 0));
     }
     CU(cudaStreamSynchronize(0));
     L.loaded[expert] = 1;
@@ -233,13 +242,40 @@ int mlxs_bank_for_each_record(const char* dir, uint32_t bank_kind, uint64_t H, u
                               uint32_t e_first, uint32_t e_count,
                               int (*sink)(void* ctx, uint32_t layer, uint32_t expert, const void* rec, uint64_t n), void* ctx);
 
+extern "C" int mlxs_moe_set_placement(mlxs_moe* h, uint32_t layer, const uint16_t* rank_of_expert) {
+    if (!h || !rank_of_expert) return fail(MLXS_E_ARG, "set_placement: null argument");
+    if (layer >= h->cfg.n_layers) return fail(MLXS_E_ARG, "set_placement: layer %u of %u", layer, h->cfg.n_layers);
+    LayerBank& L = h->layers[layer];
+    const uint32_t E = h->cfg.n_experts, W = h->cfg.ep_world;
+    for (uint32_t e = 0; e < E; ++e)
+        if (L.loaded[e]) return fail(MLXS_E_CONFIG, "set_placement: layer %u already holds experts; place before loading", layer);
+    std::vector<uint32_t> fill(W, 0), packed(E);
+    for (uint32_t e = 0; e < E; ++e) {
+        const uint32_t r = rank_of_expert[e];
+        if (r >= W) return fail(MLXS_E_CONFIG, "set_placement: expert %u on rank %u of %u", e, r, W);
+        if (fill[r] >= h->e_local)
+            return fail(MLXS_E_CONFIG, "set_placement: rank %u would hold more than %u experts (every rank holds n_experts / ep_world)", r, h->e_local);
+        packed[e] = (r << 16) | fill[r]++;
+    }
+    CU(cudaSetDevice(h->cfg.device));
+    CU(cudaMemcpy(L.place_dev, packed.data(), (size_t)E * 4, cudaMemcpyHostToDevice));
+    for (uint32_t e = 0; e < E; ++e) { L.place_rank[e] = (uint16_t)(packed[e] >> 16); L.place_slot[e] = (uint16_t)(packed[e] & 0xFFFFu); }
+    L.placement_custom = true;
+    return MLXS_OK;
+}
+
 extern "C" int mlxs_moe_load_bank(mlxs_moe* h, const char* dir) {
     if (!h || !dir) return fail(MLXS_E_ARG, "load_bank: null argument");
     const mlxs_moe_config& c = h->cfg;
     auto sink = [](void* ctx, uint32_t layer, uint32_t expert, const void* rec, uint64_t n) -> int {
         return mlxs_moe_load_expert(static_cast<mlxs_moe*>(ctx), layer, expert, rec, n, 0);
     };
-    return mlxs_bank_for_each_record(dir, c.bank_kind, c.hidden, c.inter, c.n_experts, c.n_layers, h->e_first, h->e_local, sink, h);
+    // with the default placement only this rank's block of records is read; a custom placement scatters a rank's experts
+    // over the file, so every record is visited and load_expert keeps the local ones
+    bool custom = false;
+    for (const LayerBank& L : h->layers) custom = custom || L.placement_custom;
+    return mlxs_bank_for_each_record(dir, c.bank_kind, c.hidden, c.inter, c.n_experts, c.n_layers, custom ? 0 : h->e_first,
+                                     custom ? c.n_experts : h->e_local, sink, h);
 }
 
 extern "C" int mlxs_moe_set_router_bias(mlxs_moe* h, uint32_t layer, const float* bias_host) {
@@ -472,7 +508,7 @@ extern "C" int mlxs_moe_exl3_gemv(mlxs_moe* h, uint32_t layer, uint32_t expert, 
     const mlxs_moe_config& c = h->cfg;
     if (c.bank_kind != MLXS_BANK_EXL3_K3_MUL1) return fail(MLXS_E_CONFIG, "exl3_gemv: the handle's bank is not EXL3");
     if (layer >= c.n_layers || expert >= c.n_experts || proj > 2) return fail(MLXS_E_ARG, "exl3_gemv: layer/expert/proj out of range");
-    if (expert < h->e_first || expert >= h->e_first + h->e_local || !h->layers[layer].loaded[expert])
+    if (h->layers[layer].place_rank[expert] != c.ep_rank || !h->layers[layer].loaded[expert])
         return fail(MLXS_E_NOT_LOADED, "exl3_gemv: expert %u of layer %u is not resident on this rank", expert, layer);
     if (rows == 0) return MLXS_OK;
     if (rows > h->rows_cap) return fail(MLXS_E_TOO_MANY_TOKENS, "exl3_gemv: %u rows exceed the workspace", rows);
@@ -480,7 +516,7 @@ extern "C" int mlxs_moe_exl3_gemv(mlxs_moe* h, uint32_t layer, uint32_t expert, 
     cudaStream_t st = (cudaStream_t)stream;
     LayerBank& L = h->layers[layer];
     const Exl3Dims d{c.hidden, c.inter};
-    const uint32_t le = expert - h->e_first;
+    const uint32_t le = h->layers[layer].place_slot[expert];
     // rows all belong to one pseudo expert 0 of a one-expert dispatch
     CU(cudaMemsetAsync(h->ids_ws, 0, (size_t)rows * 4, st));
     CU(launch_dispatch(h->ids_ws, rows, 1, nullptr, h->tabs, CHUNK_ROWS, GROUP_CHUNKS, 0, h->status, st));

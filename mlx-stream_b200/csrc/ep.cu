@@ -93,15 +93,17 @@ struct EpState {
 
 namespace mlxs {
 
-// dest rank and local expert index of every assignment; ids outside [0, E) set the status word and go to expert 0
-__global__ void ep_dest_kernel(const int32_t* __restrict__ ids, uint32_t A, uint32_t E, uint32_t e_local,
+// dest rank and local slot of every assignment from the layer's placement table; ids outside [0, E) set the status
+// word and go to expert 0
+__global__ void ep_dest_kernel(const int32_t* __restrict__ ids, uint32_t A, uint32_t E, const uint32_t* __restrict__ place,
                                int32_t* __restrict__ dest, int32_t* __restrict__ meta, uint32_t* status) {
     const uint32_t a = blockIdx.x * blockDim.x + threadIdx.x;
     if (a >= A) return;
     int32_t id = ids[a];
     if (id < 0 || (uint32_t)id >= E) { atomicMax(status, (uint32_t)ST_BAD_EXPERT_ID); id = 0; }
-    dest[a] = id / (int32_t)e_local;
-    meta[a] = id % (int32_t)e_local;
+    const uint32_t pl = place[id];   // rank << 16 | local slot
+    dest[a] = (int32_t)(pl >> 16);
+    meta[a] = (int32_t)(pl & 0xFFFFu);
 }
 // rows in destination order: send_x[i] = x[order[i] / k], send_meta[i] = meta[order[i]]; counts[r] from the offsets
 __global__ void ep_gather_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ meta,
@@ -339,7 +341,7 @@ int mlxs_ep_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t
     const ncclDataType_t ro_type = ro_bf16 ? ncclBfloat16 : ncclFloat32;
     {
         StageTimer tm(h, MLXS_STAGE_EXCHANGE, st);
-        if (A) ep_dest_kernel<<<(A + 255) / 256, 256, 0, st>>>(ids_dev, A, c.n_experts, h->e_local, ep->dest, ep->meta, h->status);
+        if (A) ep_dest_kernel<<<(A + 255) / 256, 256, 0, st>>>(ids_dev, A, c.n_experts, h->layers[layer].place_dev, ep->dest, ep->meta, h->status);
         CU(launch_dispatch(ep->dest, A, W, nullptr, ep->rtab, h->chunk_rows, h->group_chunks, 0, h->status, st));
         ep_gather_kernel<<<A ? A : 1, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x_dev), ep->meta, ep->rtab.order,
                                                    ep->rtab.offsets, A, c.top_k, H, W, ep->send_x, ep->send_meta,
@@ -377,7 +379,7 @@ int mlxs_ep_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t
     h->stats.a2a_bytes_sent += (S - (size_t)cnt[me * W + me]) * ((size_t)H * 2 + 4) + (R - (size_t)cnt[me * W + me]) * H * es;
     h->stats.a2a_bytes_recv += (R - (size_t)cnt[me * W + me]) * ((size_t)H * 2 + 4) + (S - (size_t)cnt[me * W + me]) * H * es;
     // the single-GPU kernels over the received rows: every row is its own "token" with one expert
-    int rc = mlxs_run_routed(h, layer, ep->recv_x, ep->recv_meta, (uint32_t)R, 1, h->e_local, h->e_first, ep->recv_ro, ro_bf16, st);
+    int rc = mlxs_run_routed(h, layer, ep->recv_x, ep->recv_meta, (uint32_t)R, 1, h->e_local, 0, ep->recv_ro, ro_bf16, st);
     if (rc) return rc;
     {
         StageTimer tm(h, MLXS_STAGE_EXCHANGE, st);
@@ -405,7 +407,7 @@ int mlxs_ep_combined(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32
     if (W > 64) return mlxs_fail(MLXS_E_EP, "experts: ep_world %u > 64", W);
     {
         StageTimer tm(h, MLXS_STAGE_EXCHANGE, st);
-        if (A) mlxs::ep_dest_kernel<<<(A + 255) / 256, 256, 0, st>>>(ids_dev, A, c.n_experts, h->e_local, ep->dest, ep->meta, h->status);
+        if (A) mlxs::ep_dest_kernel<<<(A + 255) / 256, 256, 0, st>>>(ids_dev, A, c.n_experts, h->layers[layer].place_dev, ep->dest, ep->meta, h->status);
         CU(launch_dispatch(ep->dest, A, W, nullptr, ep->rtab, h->chunk_rows, h->group_chunks, 0, h->status, st));
         mlxs::ep_dedup_kernel<<<1, 1024, 0, st>>>(ep->rtab.order, ep->rtab.offsets, ep->dest, A, W, c.top_k, ep->urow, ep->ustart,
                                                  ep->counts_dev);
@@ -465,7 +467,7 @@ int mlxs_ep_combined(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32
     // the single-GPU kernels over the received assignments: each is its own "token" with one expert, its row of x
     // through the table; then the weighted fold per unique row into the handle's row workspace
     h->tabs.xrow = ep->xrow;
-    int rc = mlxs_run_routed(h, layer, ep->recv_x, ep->recv_meta, (uint32_t)RA, 1, h->e_local, h->e_first, ep->recv_ro, 0, st);
+    int rc = mlxs_run_routed(h, layer, ep->recv_x, ep->recv_meta, (uint32_t)RA, 1, h->e_local, 0, ep->recv_ro, 0, st);
     h->tabs.xrow = nullptr;
     if (rc) return rc;
     float* partial = static_cast<float*>(h->ro);

@@ -21,8 +21,12 @@ struct LayerBank {
     __half* scales = nullptr;
     uint8_t *f4_gu = nullptr, *f4_dn = nullptr;  // FP4 banks: the two streams
     float* f4_gscale = nullptr;                  // NVFP4 [E_local][3]
-    uint8_t* loaded_dev = nullptr;  // [E] 1 = resident on this rank
-    std::vector<uint8_t> loaded;
+    uint8_t* loaded_dev = nullptr;  // [E_local] per local slot: 1 = loaded (bit 1: see takes_tensor_lane)
+    std::vector<uint8_t> loaded;    // [E] by expert id, host copy
+    // where each expert lives: rank and local slot (contiguous blocks unless mlxs_moe_set_placement changed it)
+    std::vector<uint16_t> place_rank, place_slot;
+    uint32_t* place_dev = nullptr;  // [E] rank << 16 | slot
+    bool placement_custom = false;
     float* bias = nullptr;          // [E] or null
     __nv_bfloat16 *sh_w1 = nullptr, *sh_w3 = nullptr, *sh_w2 = nullptr;
 };

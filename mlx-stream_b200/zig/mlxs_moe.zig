@@ -2,7 +2,7 @@
 //! is the compiled, tested statement of the same ABI).  One declaration per C entry point, same order.
 const std = @import("std");
 
-pub const abi_expected: i32 = 2026112502;
+pub const abi_expected: i32 = 2026112503;
 
 pub const Moe = opaque {};
 
@@ -78,6 +78,19 @@ pub extern fn mlxs_moe_forward_host(h: *Moe, layer: u32, x_host: *const anyopaqu
 pub extern fn mlxs_moe_exl3_gemv(h: *Moe, layer: u32, expert: u32, proj: u32, xh_dev: *const anyopaque, rows: u32, z_dev: *anyopaque, stream: ?*anyopaque) c_int;
 pub extern fn mlxs_moe_exl3_gemv_noalloc(code_dev: *const anyopaque, in_dim: u32, out_dim: u32, xh_dev: *const anyopaque, rows: u32, z_dev: *anyopaque, stream: ?*anyopaque) c_int;
 pub extern fn mlxs_moe_stats_get(h: *Moe, out: *Stats) c_int;
+
+/// stage order of the profile arrays (include/mlxs_moe.h MLXS_STAGE_*)
+pub const Stage = enum(u32) { router, dispatch, prep, gate_up, down, shared, combine, exchange, tensor_lane };
+pub const stage_count = 9;
+pub const Profile = extern struct { ms: [stage_count]f64, launches: [stage_count]u64 };
+pub extern fn mlxs_moe_profile_enable(h: *Moe, on: c_int) c_int;
+pub extern fn mlxs_moe_profile_read(h: *Moe, out: *Profile) c_int;
+
+// expert parallel: one process per GPU, rank 0 makes the id, the host hands it to every rank
+pub extern fn mlxs_moe_ep_unique_id(id128_out: *[128]u8) c_int;
+pub extern fn mlxs_moe_ep_init(h: *Moe, id128: *const [128]u8) c_int;
+pub extern fn mlxs_moe_ep_plan(ids: [*]const i32, n: u64, n_experts: u32, world: u32, send_counts: [*]u64) c_int;
+pub extern fn mlxs_moe_set_placement(h: *Moe, layer: u32, rank_of_expert: [*]const u16) c_int;
 
 pub const Error = error{ Arg, Config, Cuda, Bank, NotLoaded, TooManyTokens, DeviceStatus, Manifest, Ep };
 

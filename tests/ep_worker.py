@@ -1,6 +1,7 @@
 """One rank of the 2-GPU expert-parallel parity test (started by tests/test_ep_gpu.py).
 
-argv: rank world rendezvous_dir.  Each rank owns half the experts, routes its own tokens, runs the layer through the
+argv: rank world rendezvous_dir [placement].  Each rank owns half the experts (contiguous halves, or with
+"interleaved" the experts dealt alternately through mlxs_moe_set_placement), routes its own tokens, runs the layer through the
 library's exchange and checks its output rows against the CPU oracle over the whole bank."""
 import os
 import sys
@@ -28,6 +29,9 @@ def main():
                           scoring=pkg.SCORE_SQRTSOFTPLUS, routed_scale=1.5, shared_expert=True, max_tokens=32, device=rank,
                           ep_world=world, ep_rank=rank)
     moe = pkg.MoE(cfg)
+    if len(sys.argv) > 4 and sys.argv[4] == "interleaved":
+        place = (np.arange(E) % world).astype(np.uint16)
+        moe.set_placement(0, place.ctypes.data)
     records = {e: O.exl3_synth_record(0x5EED0000 + 17 * e, H, I, 1.0, 0.02) for e in range(E)}
     for e, rec in records.items():
         moe.load_expert(0, e, rec.ctypes.data, rec.size)  # the library keeps only this rank's shard

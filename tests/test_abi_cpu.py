@@ -74,3 +74,17 @@ def test_ep_plan_counts():
     bad = np.array([9], np.int32)
     assert pkg.lib().mlxs_moe_ep_plan(bad.ctypes.data, 1, 8, 4, out.ctypes.data) == -1
     assert "outside" in pkg.last_error()
+
+
+def test_zig_binding_declares_every_header_entry():
+    """The Zig host file is shipped as source (no Zig compiler in the build image): at least keep it complete."""
+    import re
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    header = (root / "include" / "mlxs_moe.h").read_text()
+    zig = (root / "mlx-stream_b200" / "zig" / "mlxs_moe.zig").read_text()
+    declared = set(re.findall(r"\b(mlxs_moe_[a-z0-9_]+)\s*\(", header))
+    bound = set(re.findall(r"pub extern fn (mlxs_moe_[a-z0-9_]+)\(", zig))
+    assert declared - bound == set(), declared - bound
+    abi = re.search(r"#define MLXS_MOE_ABI (\d+)", header).group(1)
+    assert f"abi_expected: i32 = {abi}" in zig

@@ -12,13 +12,14 @@ pytestmark = pytest.mark.gpu
 HERE = Path(__file__).resolve().parent
 
 
-def test_two_rank_exchange_matches_oracle():
+@pytest.mark.parametrize("placement", ["contiguous", "interleaved"])
+def test_two_rank_exchange_matches_oracle(placement):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     with tempfile.TemporaryDirectory() as rdv:
-        procs = [subprocess.Popen([sys.executable, str(HERE / "ep_worker.py"), str(r), "2", rdv], env=env,
+        procs = [subprocess.Popen([sys.executable, str(HERE / "ep_worker.py"), str(r), "2", rdv, placement], env=env,
                                   stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
         outs = []
         for p in procs:
