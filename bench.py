@@ -153,8 +153,10 @@ def own_launches_per_layer(T, world):
     n = 1                                   # router
     n += 3 if A > 2048 else 1               # dispatch: count / scan / place above 2048 rows, one CTA below
     n += 3                                  # streaming lane: prep, gate/up, down
-    if A >= LANE_MIN_ROWS:
-        n += 4                              # tensor-core lane: plan, prep, gate/up, down
+    # the lane's kernels launch when the local call has enough "tokens" for an expert to reach the threshold (with expert
+    # parallelism every received assignment is a token of the local call)
+    if (T if world == 1 else A) >= LANE_MIN_ROWS:
+        n += 4 if WL["bank"] == "exl3" else 6   # plan, prep, gate/up, down (FP4: two tile shapes of each)
     if WL["shared"]:
         n += 2 if T <= 64 else 1            # skinny kernels, or the activation between the library GEMMs
     n += 1                                  # combine

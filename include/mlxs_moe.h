@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define MLXS_MOE_ABI 2026112503
+#define MLXS_MOE_ABI 2026112504
 
 /* refusals (the names mirror the reference's refusal sets: src/sdk_ext/quant.zig:94-111, src/expert/bank.zig:79-101) */
 enum {
@@ -119,6 +119,14 @@ int mlxs_moe_bank_peek_text(const char *manifest_json, mlxs_bank_info *out);
 
 /* the router's noaux_tc correction bias, f32 [n_experts] host, NULL = zeros (src/arch/deepseek_v41/graph.zig:2035) */
 int mlxs_moe_set_router_bias(mlxs_moe *h, uint32_t layer, const float *bias_host);
+/* Router weight W_g bf16 [n_experts, hidden] (src/arch/deepseek_v41/graph.zig:2033): with it the layer can start from x. */
+int mlxs_moe_set_router_weight(mlxs_moe *h, uint32_t layer, const void *w_gate_bf16, int on_device);
+/* logits[T, n_experts] f32 = f32(x) . f32(W_g)^T, f32 accumulate in a fixed order (own kernel up to 64 tokens, one
+ * library GEMM above) */
+int mlxs_moe_logits(mlxs_moe *h, uint32_t layer, const void *x_dev, uint32_t T, float *logits_dev, void *stream);
+/* mlxs_moe_logits into the handle's workspace, then mlxs_moe_forward: the whole layer from x
+ * (Source.forward's real caller, src/arch/glm5_next/experts.zig:566-595) */
+int mlxs_moe_forward_x(mlxs_moe *h, uint32_t layer, const void *x_dev, uint32_t T, void *y_dev, void *stream);
 /* the shared expert's bf16 linears: w1 (gate) [inter, hidden], w3 (up) [inter, hidden], w2 (down) [hidden, inter]
  * (src/arch/deepseek_v41/graph.zig:2162-2172 sh_w1 / sh_w3 / sh_w2) */
 int mlxs_moe_set_shared(mlxs_moe *h, uint32_t layer, const void *w1, const void *w3, const void *w2, int on_device);

@@ -14,12 +14,14 @@ from pathlib import Path  # noqa: E402
 
 HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "libmlxs_moe.so"
-ABI = 2026112503
+ABI = 2026112504
 
 BANK_EXL3_K3_MUL1, BANK_MXFP4, BANK_NVFP4 = 0, 1, 2
 SCORE_SQRTSOFTPLUS, SCORE_SIGMOID, SCORE_SOFTMAX = 0, 1, 2
 ACT_SWIGLU, ACT_SWIGLU_CLAMPED = 0, 1
 COMBINE_F32, COMBINE_CHAIN = 0, 1
+# return codes (include/mlxs_moe.h)
+(E_ARG, E_CONFIG, E_CUDA, E_BANK, E_NOT_LOADED, E_TOO_MANY_TOKENS, E_DEVICE_STATUS, E_MANIFEST, E_EP) = range(-1, -10, -1)
 
 EXPORTS = [
     "mlxs_moe_abi", "mlxs_moe_last_error", "mlxs_moe_create", "mlxs_moe_destroy", "mlxs_moe_record_bytes",
@@ -27,7 +29,7 @@ EXPORTS = [
     "mlxs_moe_routed", "mlxs_moe_experts", "mlxs_moe_forward", "mlxs_moe_forward_host", "mlxs_moe_exl3_gemv",
     "mlxs_moe_exl3_gemv_noalloc",
     "mlxs_moe_stats_get", "mlxs_moe_profile_enable", "mlxs_moe_profile_read", "mlxs_moe_ep_unique_id", "mlxs_moe_ep_init", "mlxs_moe_ep_plan",
-    "mlxs_moe_set_placement",
+    "mlxs_moe_set_placement", "mlxs_moe_set_router_weight", "mlxs_moe_logits", "mlxs_moe_forward_x",
 ]
 
 
@@ -106,6 +108,9 @@ def lib():
         L.mlxs_moe_ep_init.argtypes = [C.c_void_p, C.c_void_p]
         L.mlxs_moe_ep_plan.argtypes = [C.c_void_p, C.c_uint64, C.c_uint32, C.c_uint32, C.c_void_p]
         L.mlxs_moe_set_placement.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p]
+        L.mlxs_moe_set_router_weight.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_int]
+        L.mlxs_moe_logits.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
+        L.mlxs_moe_forward_x.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
         if L.mlxs_moe_abi() != ABI:
             raise RuntimeError(f"libmlxs_moe.so ABI {L.mlxs_moe_abi()} != binding ABI {ABI}")
         _lib = L
@@ -175,6 +180,15 @@ class MoE:
 
     def set_placement(self, layer, rank_of_expert_u16_ptr):
         _check(lib().mlxs_moe_set_placement(self._h, layer, rank_of_expert_u16_ptr))
+
+    def set_router_weight(self, layer, w_ptr, on_device=False):
+        _check(lib().mlxs_moe_set_router_weight(self._h, layer, w_ptr, int(on_device)))
+
+    def logits(self, layer, x, T, out, stream=None):
+        _check(lib().mlxs_moe_logits(self._h, layer, x, T, out, stream))
+
+    def forward_x(self, layer, x, T, y, stream=None):
+        _check(lib().mlxs_moe_forward_x(self._h, layer, x, T, y, stream))
 
     def set_router_bias(self, layer, bias_host_ptr):
         _check(lib().mlxs_moe_set_router_bias(self._h, layer, bias_host_ptr))

@@ -148,10 +148,16 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
         if ((rc = h->alloc(&h->xa_gu, (size_t)max_chunks * 2 * kmax * 256)) ||
             (rc = h->alloc(&h->xa_d, (size_t)max_chunks * kmax * 256)) || (rc = h->alloc(&h->ro, A * (H > I ? H : I) * 4)))
             return bail(rc);
+        if ((rc = h->alloc(&h->ks_scratch, exl3_ksplit_scratch_bytes(h->sm_count))) || (rc = h->alloc(&h->ks_count, (size_t)3 * h->sm_count * 4)))
+            return bail(rc);
+        cudaMemset(h->ks_count, 0, (size_t)3 * h->sm_count * 4);
     } else {
         if ((rc = h->alloc(&h->xa_gu, (size_t)max_chunks * (H / 32) * 512)) ||
             (rc = h->alloc(&h->xa_d, (size_t)max_chunks * (I / 32) * 512)) || (rc = h->alloc(&h->ro, A * H * 4)))
             return bail(rc);
+        if ((rc = h->alloc(&h->ks_scratch, exl3_ksplit_scratch_bytes(h->sm_count))) || (rc = h->alloc(&h->ks_count, (size_t)3 * h->sm_count * 4)))
+            return bail(rc);
+        cudaMemset(h->ks_count, 0, (size_t)3 * h->sm_count * 4);
     }
     {
         // Staging for the tensor-core lane.  One decode pass of the streaming lane serves 16 rows, one of the
@@ -178,6 +184,12 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
             if (shared_gemm_create(&h->sh_gemm)) return bail(fail(MLXS_E_CUDA, "create: cublasCreate failed"));
         }
     }
+    if (c->shared_expert) {
+        if (cudaStreamCreateWithFlags(&h->aux_stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&h->aux_fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&h->aux_join, cudaEventDisableTiming) != cudaSuccess)
+            return bail(fail(MLXS_E_CUDA, "create: second stream for the shared expert"));
+    }
     if (cudaDeviceSynchronize() != cudaSuccess) return bail(fail(MLXS_E_CUDA, "create: device synchronize failed"));
     *out = h;
     return MLXS_OK;
@@ -189,6 +201,9 @@ extern "C" void mlxs_moe_destroy(mlxs_moe* h) {
     cudaDeviceSynchronize();
     mlxs_ep_destroy(h);
     shared_gemm_destroy(h->sh_gemm);
+    if (h->aux_fork) cudaEventDestroy(h->aux_fork);
+    if (h->aux_join) cudaEventDestroy(h->aux_join);
+    if (h->aux_stream) cudaStreamDestroy(h->aux_stream);
     for (void* p : h->allocs) cudaFree(p);
     for (auto& s : h->spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
     for (auto e : h->ev_pool) cudaEventDestroy(e);
@@ -327,6 +342,48 @@ extern "C" int mlxs_moe_route(mlxs_moe* h, uint32_t layer, const float* logits_d
     return MLXS_OK;
 }
 
+extern "C" int mlxs_moe_set_router_weight(mlxs_moe* h, uint32_t layer, const void* w_gate_bf16, int on_device) {
+    if (!h || !w_gate_bf16) return fail(MLXS_E_ARG, "set_router_weight: null argument");
+    if (layer >= h->cfg.n_layers) return fail(MLXS_E_ARG, "set_router_weight: layer %u of %u", layer, h->cfg.n_layers);
+    CU(cudaSetDevice(h->cfg.device));
+    LayerBank& L = h->layers[layer];
+    const size_t n = (size_t)h->cfg.n_experts * h->cfg.hidden * 2;
+    int rc;
+    if (!L.router_w && (rc = h->alloc(&L.router_w, n))) return rc;
+    if (!h->logits_ws && (rc = h->alloc(&h->logits_ws, (size_t)h->cfg.max_tokens * h->cfg.n_experts * 4))) return rc;
+    if (!h->sh_gemm && h->cfg.max_tokens > 64 && shared_gemm_create(&h->sh_gemm)) return fail(MLXS_E_CUDA, "set_router_weight: cublasCreate failed");
+    CU(cudaMemcpy(L.router_w, w_gate_bf16, n, on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice));
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_logits(mlxs_moe* h, uint32_t layer, const void* x_dev, uint32_t T, float* logits_dev, void* stream) {
+    int rc = check_call(h, layer, T, "logits");
+    if (rc) return rc;
+    if (T == 0) return MLXS_OK;
+    if (!x_dev || !logits_dev) return fail(MLXS_E_ARG, "logits: null buffer");
+    const mlxs_moe_config& c = h->cfg;
+    LayerBank& L = h->layers[layer];
+    if (!L.router_w) return fail(MLXS_E_NOT_LOADED, "logits: layer %u has no router weight (mlxs_moe_set_router_weight)", layer);
+    cudaStream_t st = (cudaStream_t)stream;
+    StageTimer tm(h, MLXS_STAGE_ROUTER, st);
+    if (T > 64 && h->sh_gemm) {
+        if (launch_router_logits_gemm(h->sh_gemm, static_cast<const __nv_bfloat16*>(x_dev), L.router_w, T, c.n_experts, c.hidden,
+                                      logits_dev, st))
+            return fail(MLXS_E_CUDA, "logits: the library GEMM failed");
+    } else {
+        CU(launch_router_logits(static_cast<const __nv_bfloat16*>(x_dev), L.router_w, T, c.n_experts, c.hidden, logits_dev, st));
+    }
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_forward_x(mlxs_moe* h, uint32_t layer, const void* x_dev, uint32_t T, void* y_dev, void* stream) {
+    if (!h) return fail(MLXS_E_ARG, "forward_x: null handle");
+    if (!h->logits_ws) return fail(MLXS_E_NOT_LOADED, "forward_x: no router weight was set (mlxs_moe_set_router_weight)");
+    int rc = mlxs_moe_logits(h, layer, x_dev, T, h->logits_ws, stream);
+    if (rc) return rc;
+    return mlxs_moe_forward(h, layer, x_dev, h->logits_ws, T, y_dev, stream);
+}
+
 // dispatch + the bank's expert kernels -> ro (unweighted rows in assignment order)
 int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, uint32_t T, uint32_t top_k,
                     uint32_t n_exp, uint32_t first, void* ro, int ro_bf16, cudaStream_t st) {
@@ -337,7 +394,8 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
     // Lane choice per expert by its row count, as the reference decides on logical M (src/sdk_ext/quant.zig:5-6,
     // src/arch/deepseek_v41/experts.zig:1545-1547): experts with `heavy` rows or more go to the tensor-core lane, which
     // amortises one decode over up to 128 rows; the others stream through the decode-batch lane.
-    const bool two_lanes = h->pf_tiles && A >= h->pf_min_rows;
+    // a token's experts are distinct, so no expert has more rows than the call has tokens
+    const bool two_lanes = h->pf_tiles && T >= h->pf_min_rows;
     const uint32_t heavy = two_lanes ? h->pf_min_rows : 0u;
     {
         StageTimer tm(h, MLXS_STAGE_DISPATCH, st);
@@ -358,7 +416,7 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
         Exl3GemvArgs a{};
         a.L = EL; a.d = d; a.t = h->tabs; a.xa_gu = h->xa_gu; a.xa_d = h->xa_d; a.ro = static_cast<float*>(ro); a.ro_bf16 = 0;
         a.limit = c.act == MLXS_ACT_SWIGLU_CLAMPED ? c.act_limit : 0.f;
-        a.status = h->status; a.sm_count = h->sm_count;
+        a.status = h->status; a.sm_count = h->sm_count; a.ks_scratch = h->ks_scratch; a.ks_count = h->ks_count;
         {
             StageTimer tm(h, MLXS_STAGE_GATE_UP, st);
             CU(launch_exl3_gate_up(a, st));
@@ -385,7 +443,7 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
         a.gu = L.f4_gu; a.dn = L.f4_dn; a.nv = c.bank_kind == MLXS_BANK_NVFP4; a.gscale = a.nv ? L.f4_gscale : nullptr;
         a.H = c.hidden; a.I = c.inter; a.t = h->tabs; a.xa = h->xa_gu; a.xa_d = h->xa_d; a.ro = ro;
         a.ro_bf16 = ro_bf16; a.limit = c.act == MLXS_ACT_SWIGLU_CLAMPED ? c.act_limit : 0.f;
-        a.status = h->status; a.sm_count = h->sm_count;
+        a.status = h->status; a.sm_count = h->sm_count; a.ks_scratch = h->ks_scratch; a.ks_count = h->ks_count;
         {
             StageTimer tm(h, MLXS_STAGE_GATE_UP, st);
             CU(launch_fp4_gemv(a, 0, st));
@@ -444,23 +502,43 @@ extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, 
     // rows back (ep.cu); the chain combine needs every assignment's row in k order and keeps the per-assignment form
     static const bool per_assignment = getenv("MLXS_EP_PER_ASSIGNMENT") != nullptr;
     const bool ep_fused = c.ep_world > 1 && c.combine != MLXS_COMBINE_CHAIN && !per_assignment;
-    if (!ep_fused && (rc = run_routed(h, layer, x_dev, ids_dev, T, h->ro, ro_bf16, st))) return rc;
+    // Decode-sized batches leave SMs idle in the routed kernels (T = 1: 144 work items for 296 CTA slots): the shared
+    // expert, which only reads x, then runs beside them on the handle's second stream.  Larger batches keep one stream
+    // (the routed kernels' persistent CTAs own the SMs anyway).
+    const bool shared_aside = c.shared_expert && T <= 16 && h->aux_stream;
     const float* shared = nullptr;
-    if (c.shared_expert) {
-        StageTimer tm(h, MLXS_STAGE_SHARED, st);
+    auto run_shared = [&](cudaStream_t s) -> int {
         const float lim = c.act == MLXS_ACT_SWIGLU_CLAMPED ? c.act_limit : 0.f;
         if (T > 64 && h->sh_gemm) {
             if (launch_shared_expert_gemm(h->sh_gemm, static_cast<const __nv_bfloat16*>(x_dev), L.sh_w1, L.sh_w3, L.sh_w2, T,
-                                          c.hidden, c.inter, lim, h->sh_gu, h->sh_h, h->sh_out, st))
+                                          c.hidden, c.inter, lim, h->sh_gu, h->sh_h, h->sh_out, s))
                 return fail(MLXS_E_CUDA, "experts: the shared expert's GEMMs failed");
         } else {
             CU(launch_shared_expert(static_cast<const __nv_bfloat16*>(x_dev), L.sh_w1, L.sh_w3, L.sh_w2, T, c.hidden, c.inter,
-                                    lim, h->sh_h, h->sh_out, st));
+                                    lim, h->sh_h, h->sh_out, s));
         }
+        return MLXS_OK;
+    };
+    if (shared_aside) {
+        CU(cudaEventRecord(h->aux_fork, st));
+        CU(cudaStreamWaitEvent(h->aux_stream, h->aux_fork, 0));
+        {
+            StageTimer tm(h, MLXS_STAGE_SHARED, h->aux_stream);
+            if ((rc = run_shared(h->aux_stream))) return rc;
+        }
+        CU(cudaEventRecord(h->aux_join, h->aux_stream));
         shared = h->sh_out;
     }
+    if (!ep_fused && (rc = run_routed(h, layer, x_dev, ids_dev, T, h->ro, ro_bf16, st))) return rc;
+    if (c.shared_expert && !shared_aside) {
+        StageTimer tm(h, MLXS_STAGE_SHARED, st);
+        if ((rc = run_shared(st))) return rc;
+        shared = h->sh_out;
+    }
+    if (shared_aside && !ep_fused) CU(cudaStreamWaitEvent(st, h->aux_join, 0));
     if (ep_fused) {
         h->stats.tokens += T;
+        if (shared_aside) CU(cudaStreamWaitEvent(st, h->aux_join, 0));  // before the exchange's final sum reads the row
         return mlxs_ep_combined(h, layer, x_dev, ids_dev, weights_dev, T, shared, y_dev, st);
     }
     StageTimer tm(h, MLXS_STAGE_COMBINE, st);

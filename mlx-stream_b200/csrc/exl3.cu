@@ -170,9 +170,15 @@ struct GemvParams {
     uint32_t* status;
     uint32_t n_stages;
     uint32_t stage_bytes, w_bytes;
+    // The sum over the inputs is always taken in `parts` equal parts, folded left in part order: a fixed function of the
+    // shape, so a row's bits do not depend on the batch around it.  Calls with fewer work items than CTAs spread an
+    // item's parts over 2 or 4 CTAs: each leaves its parts here and the last to arrive folds them and runs the epilogue.
+    float* ks_scratch;           // [2 x CTAs][zs words] or null (one CTA per item always)
+    uint32_t* ks_count;          // [CTAs] arrivals per item, zero between launches
 };
 
-struct StageMeta { int32_t item; uint32_t kt0, chunk0, mc, expert, nb; };
+// flags: 1 = first stage of a part of the sum, 2 = last stage of a part, 4 = last stage of this CTA's share of the item
+struct StageMeta { int32_t item; uint32_t kt0, chunk0, mc, expert, nb, part, flags; };
 
 // one pipeline stage (KT k-tiles) of one warp's 16-column tile, MC chunks of activations
 template <int NPROJ, int KSTRIDE, int MC>
@@ -201,6 +207,7 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
     __shared__ __align__(8) uint64_t full_bar[MAXS], empty_bar[MAXS], epi_bar;
     __shared__ StageMeta meta[MAXS];
     __shared__ volatile int s_abort;
+    __shared__ volatile int s_last_part;
     // epilogue staging: [NPROJ][GROUP_CHUNKS][CHUNK_ROWS][ZS_STRIDE]
     float* zs = reinterpret_cast<float*>(smem_raw);
     uint8_t* ring = smem_raw + (size_t)NPROJ * GROUP_CHUNKS * CHUNK_ROWS * ZS_STRIDE * sizeof(float);
@@ -215,6 +222,13 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
     }
     __syncthreads();
     const uint32_t n_items = P.t.header[HDR_NGROUPS] * P.n_blocks;
+    // parts of the sum (shape only), and over how many CTAs an item's parts are spread (this call's item count)
+    const uint32_t LP = P.nkt % (4 * KT) == 0 ? 4u : (P.nkt % (2 * KT) == 0 ? 2u : 1u);
+    const uint32_t part_kt = P.nkt / LP;
+    uint32_t NP = 1;
+    if (P.ks_scratch && n_items)
+        while (NP < LP && n_items * (NP * 2) <= gridDim.x) NP *= 2;
+    const uint32_t share_kt = P.nkt / NP;
 
     if (warp == NCW) {
         // ---------------- producer warp: one lane issues every copy ----------------
@@ -222,8 +236,9 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
             uint32_t it = 0;
             bool ok = true;
             while (ok) {
-                const uint32_t item = atomicAdd(&P.t.header[P.counter_idx], 1u);
-                const bool last = item >= n_items;
+                const uint32_t unit = atomicAdd(&P.t.header[P.counter_idx], 1u);
+                const bool last = unit >= n_items * NP;
+                const uint32_t item = unit / NP, share = unit % NP;
                 uint32_t g = 0, nb = 0, chunk0 = 0, mc = 0, expert = 0;
                 if (!last) {
                     g = item / P.n_blocks; nb = item % P.n_blocks;
@@ -231,7 +246,8 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
                 }
                 const uint32_t* wsrc = P.code + (size_t)expert * P.expert_stride_words +
                                        (size_t)nb * P.nkt * P.kt_stride_words;
-                for (uint32_t kt0 = 0; kt0 < (last ? 1u : P.nkt); kt0 += KT, ++it) {
+                const uint32_t k_begin = share * share_kt, k_end = last ? k_begin + 1 : k_begin + share_kt;
+                for (uint32_t kt0 = k_begin; kt0 < k_end; kt0 += KT, ++it) {
                     const uint32_t s = it % NS, ph = (it / NS) & 1u;
                     if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, &s_abort, 128)) {
                         if (!s_abort) atomicMax(P.status, (uint32_t)ST_WAIT_EMPTY);
@@ -239,6 +255,8 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
                     }
                     meta[s].item = last ? -1 : (int32_t)item;
                     meta[s].kt0 = kt0; meta[s].chunk0 = chunk0; meta[s].mc = mc; meta[s].expert = expert; meta[s].nb = nb;
+                    meta[s].part = kt0 / part_kt;
+                    meta[s].flags = (kt0 % part_kt == 0 ? 1u : 0u) | ((kt0 + KT) % part_kt == 0 ? 2u : 0u) | (kt0 + KT >= k_end ? 4u : 0u);
                     if (last) { mbar_arrive(&full_bar[s]); ok = false; break; }
                     uint8_t* dst = ring + (size_t)s * P.stage_bytes;
                     mbar_expect_tx(&full_bar[s], P.w_bytes + mc * NPROJ * KT * A_TILE_WORDS * 4);
@@ -281,7 +299,7 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
         }
         const StageMeta m = meta[s];
         if (m.item < 0) break;
-        if (m.kt0 == 0) {
+        if (m.flags & 1u) {
 #pragma unroll
             for (int a = 0; a < GROUP_CHUNKS; ++a)
 #pragma unroll
@@ -290,6 +308,7 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
         const uint8_t* st = ring + (size_t)s * P.stage_bytes;
         const uint32_t* wt = reinterpret_cast<const uint32_t*>(st) + P.proj_off_words + p * 192u + j * 24u;
         const uint2* at = reinterpret_cast<const uint2*>(st + P.w_bytes) + lane;
+        static_assert(GROUP_CHUNKS * CHUNK_ROWS == 16, "the K-split workspace is sized for 16 rows per item");
         static_assert(GROUP_CHUNKS == 4, "the stage dispatch below enumerates the chunk counts");
         if (m.mc == 1) gemv_stage<NPROJ, KSTRIDE, 1>(wt, at, wi, wj, lp, p, acc);
         else if (m.mc == 2) gemv_stage<NPROJ, KSTRIDE, 2>(wt, at, wi, wj, lp, p, acc);
@@ -297,11 +316,13 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
         else gemv_stage<NPROJ, KSTRIDE, 4>(wt, at, wi, wj, lp, p, acc);
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[s]);
-        if (m.kt0 + KT < P.nkt) continue;
+        if (!(m.flags & 2u)) continue;
 
-        // ---------------- epilogue of the item ----------------
-        // the D fragment holds (column g | g+8) x (token slots 2c, 2c+1); z[row] = hi slot + lo slot = lane c + lane c+2
+        // ---------------- end of a part of the sum ----------------
+        // the D fragment holds (column g | g+8) x (token slots 2c, 2c+1); z[row] = hi slot + lo slot = lane c + lane c+2.
+        // One CTA per item: the parts are folded left in the staging array.  Several CTAs: every part goes to its slot.
         const uint32_t g = lane >> 2, c = lane & 3u;
+        const bool fold = NP == 1 && m.part != 0;
 #pragma unroll
         for (int mt = 0; mt < GROUP_CHUNKS; ++mt) {
             if (mt < (int)m.mc) {
@@ -310,11 +331,45 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
                 for (int q = 0; q < 4; ++q) v[q] = acc[mt][q] + __shfl_xor_sync(0xFFFFFFFFu, acc[mt][q], 2);
                 if (c < 2) {
                     float* zr = zs + ((p * GROUP_CHUNKS + mt) * CHUNK_ROWS + 2 * c) * ZS_STRIDE + j * 16 + g;
-                    zr[0] = v[0]; zr[ZS_STRIDE] = v[1]; zr[8] = v[2]; zr[ZS_STRIDE + 8] = v[3];
+                    if (fold) { zr[0] += v[0]; zr[ZS_STRIDE] += v[1]; zr[8] += v[2]; zr[ZS_STRIDE + 8] += v[3]; }
+                    else { zr[0] = v[0]; zr[ZS_STRIDE] = v[1]; zr[8] = v[2]; zr[ZS_STRIDE + 8] = v[3]; }
                 }
             }
         }
-        if (!epi_sync()) break;
+        constexpr uint32_t ZS_VEC = NPROJ * GROUP_CHUNKS * CHUNK_ROWS * ZS_STRIDE / 4;
+        if (NP > 1) {
+            if (!epi_sync()) break;
+            float4* slot = reinterpret_cast<float4*>(P.ks_scratch) + ((size_t)m.item * LP + m.part) * ZS_VEC;
+            for (uint32_t i = threadIdx.x; i < ZS_VEC; i += NCW * 32) slot[i] = reinterpret_cast<const float4*>(zs)[i];
+            __threadfence();
+            if (!epi_sync()) break;
+        }
+        if (!(m.flags & 4u)) continue;
+        if (NP == 1) {
+            if (!epi_sync()) break;
+        } else {
+            // the last CTA of the item to arrive folds the parts in part order (whoever it is) and goes on to the
+            // epilogue; the others take the next unit
+            if (threadIdx.x == 0) {
+                const uint32_t seen = atomicAdd(&P.ks_count[m.item], 1u);
+                s_last_part = seen == NP - 1 ? 1 : 0;
+                if (seen == NP - 1) P.ks_count[m.item] = 0;
+            }
+            if (!epi_sync()) break;
+            if (!s_last_part) continue;
+            __threadfence();
+            const float4* base = reinterpret_cast<const float4*>(P.ks_scratch) + (size_t)m.item * LP * ZS_VEC;
+            for (uint32_t i = threadIdx.x; i < ZS_VEC; i += NCW * 32) {
+                float4 a = __ldcg(base + i);
+                for (uint32_t q = 1; q < LP; ++q) {
+                    const float4 b = __ldcg(base + (size_t)q * ZS_VEC + i);
+                    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+                }
+                reinterpret_cast<float4*>(zs)[i] = a;
+            }
+            if (!epi_sync()) break;
+        }
+        // ---------------- epilogue of the item ----------------
         for (uint32_t combo = warp; combo < (uint32_t)GROUP_CHUNKS * CHUNK_ROWS; combo += NCW) {
             const uint32_t mt = combo / CHUNK_ROWS, row = combo % CHUNK_ROWS;
             if (mt >= m.mc) continue;
@@ -424,6 +479,7 @@ cudaError_t launch_exl3_gate_up(const Exl3GemvArgs& a, cudaStream_t st) {
     P.xa = a.xa_gu; P.t = a.t; P.counter_idx = HDR_CTR_GU;
     P.scales = a.L.scales; P.scales_stride = exl3_scales_per_expert(a.d);
     P.H = a.d.H; P.I = a.d.I; P.xa_d = a.xa_d; P.out = nullptr; P.out_dim = a.d.I; P.limit = a.limit; P.status = a.status;
+    P.ks_scratch = a.ks_scratch; P.ks_count = a.ks_count;
     return launch_gemv(2, EPI_GATE_UP, P, a.sm_count, st);
 }
 cudaError_t launch_exl3_down(const Exl3GemvArgs& a, cudaStream_t st) {
@@ -434,6 +490,7 @@ cudaError_t launch_exl3_down(const Exl3GemvArgs& a, cudaStream_t st) {
     P.xa = a.xa_d; P.t = a.t; P.counter_idx = HDR_CTR_DOWN;
     P.scales = a.L.scales; P.scales_stride = exl3_scales_per_expert(a.d);
     P.H = a.d.H; P.I = a.d.I; P.xa_d = nullptr; P.out = a.ro; P.out_dim = a.d.H; P.limit = a.limit; P.status = a.status;
+    P.ks_scratch = a.ks_scratch; P.ks_count = a.ks_count;
     return launch_gemv(1, EPI_DOWN, P, a.sm_count, st);
 }
 cudaError_t launch_exl3_raw(const uint32_t* code_e, uint32_t in_dim, uint32_t out_dim, uint32_t ktile_stride_words,

@@ -135,9 +135,15 @@ struct Fp4Params {
     float limit;                 // > 0: clamped epilogue (glm5n_nvfp4_gateup.metal:109-129), else MiMo's
     uint32_t* status;
     uint32_t n_ring, stage_bytes, w_bytes;
+    // The sum over the inputs is taken in `parts` equal parts folded left in part order (a function of the shape only, so
+    // a row's bits do not depend on the batch); calls with fewer items than CTAs spread an item's parts over 2 or 4
+    // CTAs, as the EXL3 streaming kernel does
+    float* ks_scratch;           // [2 x CTAs][zs words] or null
+    uint32_t* ks_count;          // [CTAs], zero between launches
 };
 
-struct F4Meta { int32_t item; uint32_t ks, chunk0, mc, expert, nb; };
+// flags: 1 = first stage of a part of the sum, 2 = last stage of a part, 4 = last stage of this CTA's share of the item
+struct F4Meta { int32_t item; uint32_t ks, chunk0, mc, expert, nb, part, flags; };
 
 __device__ __forceinline__ void fp4_decode8(uint32_t w, uint32_t (&h)[4]) {
     h[0] = ((w << 9) & 0x0E000E00u) | ((w << 12) & 0x80008000u);
@@ -214,6 +220,7 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
     __shared__ __align__(8) uint64_t full_bar[MAXS], empty_bar[MAXS], epi_bar;
     __shared__ F4Meta meta[MAXS];
     __shared__ volatile int s_abort;
+    __shared__ volatile int s_last_part;
     __shared__ uint32_t s_lut[NV ? 256 : 1];
     float* zs = reinterpret_cast<float*>(smem_raw);  // [NPROJ][F4_GROUP][8 rows][F4_ZS_STRIDE]
     uint8_t* ring = smem_raw + (size_t)NPROJ * F4_GROUP * F4_CHUNK * F4_ZS_STRIDE * sizeof(float);
@@ -232,21 +239,29 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
     __syncthreads();
     const uint32_t n_items = P.t.header[HDR_NGROUPS] * P.n_blocks;
     const uint32_t xa_chunk_words = (NPROJ == 2 ? P.H : P.I) / 32 * F4_XA_SB_WORDS;
+    const uint32_t LP = P.n_stages_k % 4 == 0 ? 4u : (P.n_stages_k % 2 == 0 ? 2u : 1u);   // parts of the sum (shape only)
+    const uint32_t part_stages = P.n_stages_k / LP;
+    uint32_t NP = 1;   // CTAs an item's parts are spread over (this call's item count)
+    if (P.ks_scratch && n_items)
+        while (NP < LP && n_items * (NP * 2) <= gridDim.x) NP *= 2;
+    const uint32_t share_stages = P.n_stages_k / NP;
 
     if (warp == NCW) {
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
             while (ok) {
-                const uint32_t item = atomicAdd(&P.t.header[P.counter_idx], 1u);
-                const bool last = item >= n_items;
+                const uint32_t unit = atomicAdd(&P.t.header[P.counter_idx], 1u);
+                const bool last = unit >= n_items * NP;
+                const uint32_t item = unit / NP, share = unit % NP;
                 uint32_t g = 0, nb = 0, chunk0 = 0, mc = 0, expert = 0;
                 if (!last) {
                     g = item / P.n_blocks; nb = item % P.n_blocks;
                     chunk0 = P.t.group_chunk0[g]; mc = P.t.group_mc[g]; expert = P.t.chunk_expert[chunk0];
                 }
                 const uint8_t* wsrc = P.w + (size_t)expert * P.expert_stride + (size_t)nb * P.n_stages_k * P.w_bytes;
-                for (uint32_t ks = 0; ks < (last ? 1u : P.n_stages_k); ++ks, ++it) {
+                const uint32_t ks_begin = share * share_stages, ks_end = last ? ks_begin + 1 : ks_begin + share_stages;
+                for (uint32_t ks = ks_begin; ks < ks_end; ++ks, ++it) {
                     const uint32_t s = it % NS, ph = (it / NS) & 1u;
                     if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, &s_abort, 128)) {
                         if (!s_abort) atomicMax(P.status, (uint32_t)ST_WAIT_EMPTY);
@@ -254,6 +269,8 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
                     }
                     meta[s].item = last ? -1 : (int32_t)item;
                     meta[s].ks = ks; meta[s].chunk0 = chunk0; meta[s].mc = mc; meta[s].expert = expert; meta[s].nb = nb;
+                    meta[s].part = ks / part_stages;
+                    meta[s].flags = (ks % part_stages == 0 ? 1u : 0u) | ((ks + 1) % part_stages == 0 ? 2u : 0u) | (ks + 1 >= ks_end ? 4u : 0u);
                     if (last) { mbar_arrive(&full_bar[s]); ok = false; break; }
                     uint8_t* dst = ring + (size_t)s * P.stage_bytes;
                     mbar_expect_tx(&full_bar[s], P.w_bytes + mc * 4 * F4_XA_SB_WORDS * 4);
@@ -289,7 +306,7 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
         }
         const F4Meta m = meta[s];
         if (m.item < 0) break;
-        if (m.ks == 0) {
+        if (m.flags & 1u) {
 #pragma unroll
             for (int a = 0; a < F4_GROUP; ++a)
 #pragma unroll
@@ -300,21 +317,59 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
         else fp4_stage<NPROJ, NV, 2>(st, P.w_bytes, p, j, lane, s_lut, acc);
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[s]);
-        if (m.ks + 1 < P.n_stages_k) continue;
+        if (!(m.flags & 2u)) continue;
 
-        // ---- epilogue: D fragment = (output row g | g+8) x (token slots 2c, 2c+1) ----
+        // ---- end of a part of the sum: D fragment = (output row g | g+8) x (token slots 2c, 2c+1) ----
+        // One CTA per item: the parts are folded left in the staging array.  Several CTAs: every part goes to its slot.
         const uint32_t g = lane >> 2, c = lane & 3u;
         float gs = 1.f;
         if (NV) gs = (P.gscale[m.expert * 3 + (NPROJ == 2 ? p : 2)] / 2688.0f) * 16384.0f;
+        const bool fold = NP == 1 && m.part != 0;
 #pragma unroll
         for (int mt = 0; mt < F4_GROUP; ++mt) {
             if (mt < (int)m.mc) {
                 float* zr = zs + ((p * F4_GROUP + mt) * F4_CHUNK + 2 * c) * F4_ZS_STRIDE + j * 16 + g;
-                zr[0] = acc[mt][0] * gs; zr[F4_ZS_STRIDE] = acc[mt][1] * gs;
-                zr[8] = acc[mt][2] * gs; zr[F4_ZS_STRIDE + 8] = acc[mt][3] * gs;
+                if (fold) {
+                    zr[0] += acc[mt][0] * gs; zr[F4_ZS_STRIDE] += acc[mt][1] * gs;
+                    zr[8] += acc[mt][2] * gs; zr[F4_ZS_STRIDE + 8] += acc[mt][3] * gs;
+                } else {
+                    zr[0] = acc[mt][0] * gs; zr[F4_ZS_STRIDE] = acc[mt][1] * gs;
+                    zr[8] = acc[mt][2] * gs; zr[F4_ZS_STRIDE + 8] = acc[mt][3] * gs;
+                }
             }
         }
-        if (!epi_sync()) break;
+        constexpr uint32_t ZS_VEC = NPROJ * F4_GROUP * F4_CHUNK * F4_ZS_STRIDE / 4;
+        if (NP > 1) {
+            if (!epi_sync()) break;
+            float4* slot = reinterpret_cast<float4*>(P.ks_scratch) + ((size_t)m.item * LP + m.part) * ZS_VEC;
+            for (uint32_t i = threadIdx.x; i < ZS_VEC; i += NCW * 32) slot[i] = reinterpret_cast<const float4*>(zs)[i];
+            __threadfence();
+            if (!epi_sync()) break;
+        }
+        if (!(m.flags & 4u)) continue;
+        if (NP == 1) {
+            if (!epi_sync()) break;
+        } else {
+            if (threadIdx.x == 0) {
+                const uint32_t seen = atomicAdd(&P.ks_count[m.item], 1u);
+                s_last_part = seen == NP - 1 ? 1 : 0;
+                if (seen == NP - 1) P.ks_count[m.item] = 0;
+            }
+            if (!epi_sync()) break;
+            if (!s_last_part) continue;
+            __threadfence();
+            const float4* base = reinterpret_cast<const float4*>(P.ks_scratch) + (size_t)m.item * LP * ZS_VEC;
+            for (uint32_t i = threadIdx.x; i < ZS_VEC; i += NCW * 32) {
+                float4 a = __ldcg(base + i);
+                for (uint32_t q = 1; q < LP; ++q) {
+                    const float4 b = __ldcg(base + (size_t)q * ZS_VEC + i);
+                    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+                }
+                reinterpret_cast<float4*>(zs)[i] = a;
+            }
+            if (!epi_sync()) break;
+        }
+        // ---- epilogue of the item ----
         for (uint32_t combo = warp; combo < (uint32_t)F4_GROUP * F4_CHUNK; combo += NCW) {
             const uint32_t mt = combo / F4_CHUNK, row = combo % F4_CHUNK;
             if (mt >= m.mc) continue;
@@ -384,6 +439,7 @@ cudaError_t launch_fp4_gemv(const Fp4GemvArgs& a, int down, cudaStream_t st) {
     P.t = a.t;
     P.counter_idx = down ? HDR_CTR_DOWN : HDR_CTR_GU;
     P.H = a.H; P.I = a.I; P.xa_d = a.xa_d; P.out = a.ro; P.out_bf16 = a.ro_bf16; P.limit = a.limit; P.status = a.status;
+    P.ks_scratch = a.ks_scratch; P.ks_count = a.ks_count;
     P.stage_bytes = P.w_bytes + F4_GROUP * 4 * F4_XA_SB_WORDS * 4;
     static const int gu_ctas = f4_tune_env("MLXS_F4_GU_CTAS", 2, 1, 2), dn_ctas = f4_tune_env("MLXS_F4_DN_CTAS", 3, 1, 3);
     const int per_sm = down ? dn_ctas : gu_ctas;

@@ -28,6 +28,7 @@ struct LayerBank {
     uint32_t* place_dev = nullptr;  // [E] rank << 16 | slot
     bool placement_custom = false;
     float* bias = nullptr;          // [E] or null
+    __nv_bfloat16* router_w = nullptr;  // [E, H] bf16 or null (logits supplied by the caller)
     __nv_bfloat16 *sh_w1 = nullptr, *sh_w3 = nullptr, *sh_w2 = nullptr;
 };
 
@@ -56,6 +57,12 @@ struct mlxs_moe {
     __nv_bfloat16* sh_h = nullptr;
     float* sh_gu = nullptr;   // f32 [2][T, I] for the GEMM form of the shared expert
     void* sh_gemm = nullptr;  // cuBLAS handle (plain dense GEMMs only)
+    // small batches: the shared expert runs beside the routed kernels on a second stream (they leave SMs free)
+    float* logits_ws = nullptr;       // [max_tokens, E] logits of mlxs_moe_forward_x
+    float* ks_scratch = nullptr;      // K-split workspace of the streaming kernels (exl3.cu)
+    uint32_t* ks_count = nullptr;
+    cudaStream_t aux_stream = nullptr;
+    cudaEvent_t aux_fork = nullptr, aux_join = nullptr;
     float* sh_out = nullptr;
     uint32_t* status = nullptr;
     uint8_t* staging = nullptr;

@@ -30,6 +30,11 @@ __host__ __device__ inline uint32_t x_row_of(const DispatchTables& t, uint32_t a
 }
 enum { HDR_NCHUNKS = 0, HDR_NGROUPS = 1, HDR_CTR_GU = 2, HDR_CTR_DOWN = 3, HDR_DISTINCT = 4, HDR_CTR_AUX = 5 };
 
+// logits[T, E] = f32(x) . f32(W)^T for decode-sized batches (own kernel), and the same through one library GEMM
+cudaError_t launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* w, uint32_t T, uint32_t E, uint32_t H,
+                                 float* logits, cudaStream_t st);
+int launch_router_logits_gemm(void* cublas, const __nv_bfloat16* x, const __nv_bfloat16* w, uint32_t T, uint32_t E, uint32_t H,
+                              float* logits, cudaStream_t st);
 cudaError_t launch_router(const float* logits, const float* bias, int T, int E, int K, int scoring, int norm,
                           float scale, int32_t* ids, float* weights, cudaStream_t st);
 
@@ -77,7 +82,10 @@ struct Exl3GemvArgs {
     float limit;            // > 0: clamped SwiGLU
     uint32_t* status;
     int sm_count;
+    float* ks_scratch;      // optional K-split workspace: exl3_ksplit_scratch_bytes(sm_count) bytes
+    uint32_t* ks_count;     // [3 * sm_count] zeroed once
 };
+static inline size_t exl3_ksplit_scratch_bytes(int sm_count) { return (size_t)2 * 3 * sm_count * 2 * 16 * 132 * 4; }
 cudaError_t launch_exl3_gate_up(const Exl3GemvArgs& a, cudaStream_t st);
 cudaError_t launch_exl3_down(const Exl3GemvArgs& a, cudaStream_t st);
 // raw projection: z [rows, out] = xa . W_hat(code); `code` in the single-projection block layout with a k-tile
@@ -157,6 +165,8 @@ struct Fp4GemvArgs {
     float limit;
     uint32_t* status;
     int sm_count;
+    float* ks_scratch;      // optional K-split workspace, exl3_ksplit_scratch_bytes(sm_count) bytes
+    uint32_t* ks_count;     // [3 * sm_count] zeroed once
 };
 cudaError_t launch_fp4_gemv(const Fp4GemvArgs& a, int down, cudaStream_t st);
 // experts with many rows: tcgen05 MMA over codes decoded to 16-bit operands in shared memory (fp4_prefill.cu)

@@ -141,6 +141,16 @@ int shared_gemm_create(void** handle) {
 void shared_gemm_destroy(void* handle) {
     if (handle) cublasDestroy(static_cast<cublasHandle_t>(handle));
 }
+// router logits at prefill widths: one plain library GEMM, logits[T, E] = X[T, H] . W[E, H]^T, f32 out
+int launch_router_logits_gemm(void* handle, const __nv_bfloat16* x, const __nv_bfloat16* w, uint32_t T, uint32_t E, uint32_t H,
+                              float* logits, cudaStream_t st) {
+    cublasHandle_t cb = static_cast<cublasHandle_t>(handle);
+    if (cublasSetStream(cb, st) != CUBLAS_STATUS_SUCCESS) return -1;
+    const float one = 1.f, zero = 0.f;
+    if (cublasGemmEx(cb, CUBLAS_OP_T, CUBLAS_OP_N, (int)E, (int)T, (int)H, &one, w, CUDA_R_16BF, (int)H, x, CUDA_R_16BF, (int)H,
+                     &zero, logits, CUDA_R_32F, (int)E, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT) != CUBLAS_STATUS_SUCCESS) return -2;
+    return 0;
+}
 // gu_ws: f32 [2][T, I]
 int launch_shared_expert_gemm(void* handle, const __nv_bfloat16* x, const __nv_bfloat16* w1, const __nv_bfloat16* w3,
                               const __nv_bfloat16* w2, uint32_t T, uint32_t H, uint32_t I, float limit, float* gu_ws,

@@ -2,7 +2,7 @@
 //! is the compiled, tested statement of the same ABI).  One declaration per C entry point, same order.
 const std = @import("std");
 
-pub const abi_expected: i32 = 2026112503;
+pub const abi_expected: i32 = 2026112504;
 
 pub const Moe = opaque {};
 
@@ -69,6 +69,9 @@ pub const BankInfo = extern struct {
 pub extern fn mlxs_moe_bank_peek(dir: [*:0]const u8, out: *BankInfo) c_int;
 pub extern fn mlxs_moe_bank_peek_text(manifest_json: [*:0]const u8, out: *BankInfo) c_int;
 pub extern fn mlxs_moe_set_router_bias(h: *Moe, layer: u32, bias_host: ?[*]const f32) c_int;
+pub extern fn mlxs_moe_set_router_weight(h: *Moe, layer: u32, w_gate_bf16: *const anyopaque, on_device: c_int) c_int;
+pub extern fn mlxs_moe_logits(h: *Moe, layer: u32, x_dev: *const anyopaque, t: u32, logits_dev: [*]f32, stream: ?*anyopaque) c_int;
+pub extern fn mlxs_moe_forward_x(h: *Moe, layer: u32, x_dev: *const anyopaque, t: u32, y_dev: *anyopaque, stream: ?*anyopaque) c_int;
 pub extern fn mlxs_moe_set_shared(h: *Moe, layer: u32, w1: *const anyopaque, w3: *const anyopaque, w2: *const anyopaque, on_device: c_int) c_int;
 pub extern fn mlxs_moe_route(h: *Moe, layer: u32, logits_dev: *const anyopaque, t: u32, ids_dev: *anyopaque, weights_dev: *anyopaque, stream: ?*anyopaque) c_int;
 pub extern fn mlxs_moe_routed(h: *Moe, layer: u32, x_dev: *const anyopaque, ids_dev: *const anyopaque, t: u32, out_dev: *anyopaque, stream: ?*anyopaque) c_int;

@@ -254,3 +254,131 @@ def test_load_bank_from_reference_format_files(tmp_path):
     finally:
         a.close()
         b.close()
+
+
+def test_forward_is_capturable_in_a_cuda_graph():
+    """A layer call allocates nothing and never synchronises, so a host can capture it into a CUDA graph and replay it
+    (the second stream of the shared expert forks from and joins the capturing stream)."""
+    import torch
+    case = Exl3Case(512, 256, 8, 2, seed=5, shared=True, max_tokens=8)
+    try:
+        T = 3
+        x, logits = case.inputs(T, seed=9)
+        ref = case.gpu_forward(x, logits)          # also warms every kernel up outside the capture
+        xd = case.to_dev_bf16(x)
+        lg = torch.from_numpy(logits).to(case.dev)
+        y = torch.zeros((T, case.H), dtype=torch.bfloat16, device=case.dev)
+        side = torch.cuda.Stream(device=case.dev)
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                case.moe.forward(0, xd.data_ptr(), lg.data_ptr(), T, y.data_ptr(), side.cuda_stream)
+        torch.cuda.synchronize()
+        for _ in range(2):
+            y.zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            assert (y.float().cpu().numpy() == ref).all()
+        assert case.status() == 0
+    finally:
+        case.close()
+
+
+def test_placement_refusals():
+    case = Exl3Case(512, 256, 4, 2, seed=1, shared=False, max_tokens=8, experts_to_load=[])
+    try:
+        lib = case.pkg.lib()
+        ok = np.zeros(4, np.uint16)
+        assert lib.mlxs_moe_set_placement(case.moe._h, 0, ok.ctypes.data) == 0      # one rank: everything on rank 0
+        bad = np.array([0, 1, 0, 0], np.uint16)
+        assert lib.mlxs_moe_set_placement(case.moe._h, 0, bad.ctypes.data) != 0     # rank 1 of a world of 1
+        assert "rank" in case.pkg.last_error()
+        case.load(2)
+        assert lib.mlxs_moe_set_placement(case.moe._h, 0, ok.ctypes.data) != 0      # after loading: refused
+        assert "before loading" in case.pkg.last_error()
+    finally:
+        case.close()
+
+
+def test_many_assignments_take_the_multi_cta_dispatch():
+    """More than 2048 assignment rows: the sort runs over several CTAs (count, scan, place) and both lanes are busy."""
+    case = Exl3Case(512, 256, 8, 4, seed=14, shared=True, max_tokens=640)
+    try:
+        T = 600
+        x, logits = case.inputs(T, seed=77)
+        logits[:, 5] -= 3.0          # one expert with few rows (streaming lane), the others heavy (tensor-core lane)
+        ids, w = case.cpu_route(logits)
+        assert ids.size > 2048 and 0 < np.bincount(ids.reshape(-1), minlength=8)[5] < 17
+        y = case.gpu_experts(x, ids, w)
+        assert case.status() == 0
+        assert rel_l2(y, case.cpu_layer(x, ids, w)) < TOL_LAYER
+        gid, gw = case.gpu_route(logits)
+        assert (gid == ids).all()
+    finally:
+        case.close()
+
+
+def test_limits_empty_call_too_many_tokens_and_the_widest_router():
+    case = Exl3Case(512, 256, 1024, 64, seed=2, shared=False, scoring=1, max_tokens=16, experts_to_load=[],
+                    routed_scale=1.0)
+    try:
+        import torch
+        # the widest configuration the library accepts: 1024 experts, top-64 (the rank-count selection path)
+        _, logits = case.inputs(5, seed=8)
+        ids, w = case.gpu_route(logits)
+        rid, rw = case.cpu_route(logits)
+        assert (ids == rid).all() and np.allclose(w, rw, rtol=1e-6)
+        # only the experts a small batch touches are loaded; the layer over them matches the oracle
+        x, logits = case.inputs(2, seed=9)
+        ids, w = case.cpu_route(logits)
+        for e in np.unique(ids):
+            case.load(int(e))
+        y = case.gpu_experts(x, ids, w)
+        assert case.status() == 0
+        assert rel_l2(y, case.cpu_layer(x, ids, w)) < TOL_LAYER
+        # an empty call is a no-op, one token too many is refused by name
+        lib = case.pkg.lib()
+        assert lib.mlxs_moe_forward(case.moe._h, 0, None, None, 0, None, None) == 0
+        big = torch.zeros((17, 512), dtype=torch.bfloat16, device=case.dev)
+        lg = torch.zeros((17, 1024), dtype=torch.float32, device=case.dev)
+        rc = lib.mlxs_moe_forward(case.moe._h, 0, big.data_ptr(), lg.data_ptr(), 17, big.data_ptr(), None)
+        assert rc == case.pkg.E_TOO_MANY_TOKENS, (rc, case.pkg.last_error())
+    finally:
+        case.close()
+
+
+def test_router_logits_product_and_the_layer_from_x():
+    """logits = f32(x) . f32(W_g)^T (src/arch/deepseek_v41/graph.zig:2033) in both forms (own kernel up to 64 tokens, the
+    library GEMM above), and the layer started from x.  The f32 sum order is the kernel's own, so ids are compared only
+    where the k-th and (k+1)-th keys are not a near-tie."""
+    import torch
+    case = Exl3Case(512, 256, 8, 2, seed=6, shared=True, max_tokens=128)
+    try:
+        rng = np.random.default_rng(17)
+        wg = O.f32_to_bf16_bits((rng.standard_normal((8, 512)) * 0.05).astype(np.float32))
+        case.moe.set_router_weight(0, wg.ctypes.data)
+        wf = O.bf16_bits_to_f32(wg).astype(np.float64)
+        for T in (1, 7, 64, 100):
+            x, _ = case.inputs(T, seed=40 + T)
+            ref_logits = (x.astype(np.float64) @ wf.T).astype(np.float32)
+            xd = case.to_dev_bf16(x)
+            lg = torch.full((T, 8), float("nan"), dtype=torch.float32, device=case.dev)
+            case.moe.logits(0, xd.data_ptr(), T, lg.data_ptr(), None)
+            torch.cuda.synchronize()
+            got = lg.cpu().numpy()
+            assert np.allclose(got, ref_logits, rtol=2e-5, atol=2e-5), np.abs(got - ref_logits).max()
+            again = torch.empty_like(lg)
+            case.moe.logits(0, xd.data_ptr(), T, again.data_ptr(), None)
+            torch.cuda.synchronize()
+            assert (again.cpu().numpy().view(np.uint32) == got.view(np.uint32)).all()
+            # the layer from x equals the layer from these logits
+            y = torch.empty((T, 512), dtype=torch.bfloat16, device=case.dev)
+            case.moe.forward_x(0, xd.data_ptr(), T, y.data_ptr(), None)
+            torch.cuda.synchronize()
+            assert (y.float().cpu().numpy() == case.gpu_forward(x, got)).all()
+            ids, w = case.cpu_route(got)
+            assert rel_l2(y.float().cpu().numpy(), case.cpu_layer(x, ids, w)) < TOL_LAYER
+        assert case.status() == 0
+    finally:
+        case.close()
