@@ -2,7 +2,7 @@
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--tokens T] [--routing normal|zipf]
 
-Workload at N=1 (BASELINE config 1 of the list after the CPU-runnable case, "c2"): DeepSeek-V4.1-Flash-shaped decode
+Workload at N=1 (the benchmark list's first configuration after the CPU-runnable case, "c2"): DeepSeek-V4.1-Flash-shaped decode
 layer, EXL3 K=3 bank, hidden 5120, inter 2304, 256 routed experts, top-8, one bf16 shared expert, T = 64 tokens per
 call.  Weights are synthetic (seeded random trellis codes, +-(0.5+u) sign/scale vectors), activations bf16 N(0,1),
 logits N(0,1) or Zipf(1.1)-skewed.  Prints ONE JSON line (rank 0).
@@ -31,7 +31,7 @@ sys.path.insert(0, str(ROOT / "tests"))
 H, I, E, K_TOP = 5120, 2304, 256, 8
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
-# secondary workloads (decode lines of BASELINE configs 3 and 4), selected with --workload
+# secondary workloads (the MXFP4 and NVFP4 configurations of the benchmark list), selected with --workload
 WORKLOADS = {
     "c2": dict(name="c2: DeepSeek-V4.1-Flash-shaped routed MoE decode layer, EXL3 K=3 mul1 bank", H=5120, I=2304, E=256,
                k=8, bank="exl3", shared=True, scoring="sqrtsoftplus", scale=1.5, limit=10.0, chain=False),
@@ -39,6 +39,9 @@ WORKLOADS = {
                shared=False, scoring="softmax", scale=1.0, limit=0.0, chain=True),
     "c4": dict(name="c4: GLM-shaped routed MoE layer, NVFP4 bank", H=6144, I=2048, E=256, k=8, bank="nvfp4",
                shared=True, scoring="sigmoid", scale=1.0, limit=10.0, chain=True),
+    # not in the benchmark list: the reference's other EXL3 shape (GLM-Flash experts, src/arch/glm5_next/exl3_forms_ref.zig:17-37)
+    "glm": dict(name="glm: GLM-Flash-shaped routed MoE layer, EXL3 K=3 mul1 bank", H=4096, I=2048, E=256, k=8, bank="exl3",
+                shared=True, scoring="sigmoid", scale=2.5, limit=10.0, chain=False),
 }
 WL = WORKLOADS["c2"]
 
@@ -243,7 +246,7 @@ def main():
     ap.add_argument("--placement", default="contiguous", choices=["contiguous", "usage"],
                     help="expert parallel: experts in contiguous blocks, or dealt to the ranks by a routing histogram")
     ap.add_argument("--layers", type=int, default=1,
-                    help="stack of identical-shape layers run back to back per step (BASELINE config 5 uses 24)")
+                    help="stack of identical-shape layers run back to back per step (the stack configuration of the benchmark list uses 24)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     globals().update(WL=wl, H=wl["H"], I=wl["I"], E=args.experts or wl["E"], K_TOP=wl["k"])

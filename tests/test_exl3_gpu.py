@@ -21,7 +21,7 @@ TOL_LAYER = 1e-2
 
 @pytest.fixture(scope="module")
 def c1():
-    # BASELINE config 1: hidden 5120, inter 2304, 16 experts, top-4, shared expert, clamped SwiGLU
+    # the benchmark list's CPU-runnable configuration: hidden 5120, inter 2304, 16 experts, top-4, shared expert, clamped SwiGLU
     case = Exl3Case(5120, 2304, 16, 4, seed=0, shared=True, max_tokens=64)
     yield case
     case.close()
@@ -379,6 +379,38 @@ def test_router_logits_product_and_the_layer_from_x():
             assert (y.float().cpu().numpy() == case.gpu_forward(x, got)).all()
             ids, w = case.cpu_route(got)
             assert rel_l2(y.float().cpu().numpy(), case.cpu_layer(x, ids, w)) < TOL_LAYER
+        assert case.status() == 0
+    finally:
+        case.close()
+
+
+@pytest.mark.parametrize("H,I,proj,which", [(5120, 2304, 0, "gate_up"), (5120, 2304, 2, "down"), (4096, 2048, 0, 0),
+                                            (4096, 2048, 2, 1)])
+def test_whole_golden_planes_decode_bit_exact(H, I, proj, which):
+    """Every row of the reference's seeded planes through the GPU decode: the f16 plane's sha256 is the golden
+    `w_hat_sha256` (src/kernels/exl3/manifest.json planes; src/arch/glm5_next/exl3_parity.zig:19-23 for the GLM shape)."""
+    gold = json.loads((GOLD / "exl3_digests.json").read_text())
+    plane = gold["planes"][which] if isinstance(which, str) else gold["glm_planes"][which]
+    n_in, n_out = (I, H) if proj == 2 else (H, I)
+    case = Exl3Case(H, I, 1, 1, seed=0, shared=False, max_tokens=1024, experts_to_load=[])
+    try:
+        g = O.exl3_geometry(H, I)
+        rec = np.zeros(g.record_bytes, np.uint8)
+        seg = 6 if proj == 2 else 0
+        code = O.fill_code(plane["seed"], g.len[seg] // 2)
+        assert hashlib.sha256(code.tobytes()).hexdigest() == plane["code_sha256"]
+        rec[g.off[seg]:g.off[seg] + g.len[seg]] = code.view(np.uint8)
+        case.moe.load_expert(0, 0, rec.ctypes.data, rec.size)
+        digest = hashlib.sha256()
+        for r0 in range(0, n_in, 1024):
+            rows = min(1024, n_in - r0)
+            xh = np.zeros((rows, n_in), np.float32)
+            xh[np.arange(rows), r0 + np.arange(rows)] = 1.0
+            z = case.gpu_gemv(0, proj, xh)
+            z16 = z.astype(np.float16)
+            assert (z16.astype(np.float32) == z).all()
+            digest.update(z16.tobytes())
+        assert digest.hexdigest() == plane["w_hat_sha256"]
         assert case.status() == 0
     finally:
         case.close()

@@ -38,7 +38,7 @@ def test_fp4_small_layer(cls, limit, shared):
 
 @pytest.mark.parametrize("cls,H,I,limit,shared", [(Mxfp4Case, 4096, 2048, 0.0, False), (Nvfp4Case, 6144, 2048, 10.0, True)])
 def test_fp4_config_shapes(cls, H, I, limit, shared):
-    # BASELINE configs 3 (MiMo shape) and 4 (GLM shape) at a reduced expert count
+    # the benchmark list's MXFP4 (MiMo shape) and NVFP4 (GLM shape) configurations at a reduced expert count
     case = cls(H, I, 4, 2, seed=2, shared=shared, scoring=O.SCORE_SIGMOID, max_tokens=16, routed_scale=1.0, limit=limit,
                chain=True)
     try:
