@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define MLXS_MOE_ABI 2026112504
+#define MLXS_MOE_ABI 2026112505
 
 /* refusals (the names mirror the reference's refusal sets: src/sdk_ext/quant.zig:94-111, src/expert/bank.zig:79-101) */
 enum {
@@ -41,8 +41,10 @@ enum {
  *  MXFP4:        six parts gate/up/down x {weight U32 [out,in/8], scales U8 E8M0 [out,in/32]}
  *                (src/arch/mimo_v2/bank.zig:13-27, 341-345)
  *  NVFP4:        nine parts gate/up/down x {weight U32 [out,in/8], scales U8 E4M3 [out,in/16], global F32}
- *                (src/arch/glm5_next/bank.zig:5-13) */
-enum { MLXS_BANK_EXL3_K3_MUL1 = 0, MLXS_BANK_MXFP4 = 1, MLXS_BANK_NVFP4 = 2 };
+ *                (src/arch/glm5_next/bank.zig:5-13)
+ *  EXL3_K2_MUL1: the EXL3 record at 2 bits per weight, code I16 [in/16,out/16,32] (the reference's K = 2 layers,
+ *                src/exl3/kernels.zig:163-177; a model that mixes K = 2 and K = 3 layers uses one handle per width) */
+enum { MLXS_BANK_EXL3_K3_MUL1 = 0, MLXS_BANK_MXFP4 = 1, MLXS_BANK_NVFP4 = 2, MLXS_BANK_EXL3_K2_MUL1 = 3 };
 /* router scoring: sqrt(softplus) = DeepSeek-V4.1 (src/arch/deepseek_v41/graph.zig:2032-2051), sigmoid = MiMo / GLM
  * (src/arch/mimo_v2/kernels/mimo_glue_top8.metal, src/arch/glm5_next/kernels/glm5n_glue_top8.metal); softmax has no
  * counterpart in the reference (every arch refuses it) and is provided for the MiMo-shaped benchmark config. */

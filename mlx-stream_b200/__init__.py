@@ -14,9 +14,9 @@ from pathlib import Path  # noqa: E402
 
 HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "libmlxs_moe.so"
-ABI = 2026112504
+ABI = 2026112505
 
-BANK_EXL3_K3_MUL1, BANK_MXFP4, BANK_NVFP4 = 0, 1, 2
+BANK_EXL3_K3_MUL1, BANK_MXFP4, BANK_NVFP4, BANK_EXL3_K2_MUL1 = 0, 1, 2, 3
 SCORE_SQRTSOFTPLUS, SCORE_SIGMOID, SCORE_SOFTMAX = 0, 1, 2
 ACT_SWIGLU, ACT_SWIGLU_CLAMPED = 0, 1
 COMBINE_F32, COMBINE_CHAIN = 0, 1

@@ -49,7 +49,9 @@ int mlxs_fail(int rc, const char* fmt, ...) {
 extern "C" int32_t mlxs_moe_abi(void) { return MLXS_MOE_ABI; }
 extern "C" const char* mlxs_moe_last_error(void) { return g_err.c_str(); }
 
-static uint64_t exl3_logical(uint64_t H, uint64_t I) { return 3 * ((H / 16) * (I / 16) * 96) + 6 * H + 6 * I; }
+static uint64_t exl3_logical(uint64_t H, uint64_t I, uint64_t K) { return 3 * ((H / 16) * (I / 16) * 32 * K) + 6 * H + 6 * I; }
+static inline bool is_exl3(uint32_t kind) { return kind == MLXS_BANK_EXL3_K3_MUL1 || kind == MLXS_BANK_EXL3_K2_MUL1; }
+static inline uint32_t exl3_bits(uint32_t kind) { return kind == MLXS_BANK_EXL3_K2_MUL1 ? 2u : 3u; }
 static uint64_t mxfp4_logical(uint64_t H, uint64_t I) { return 3 * (H * I / 2 + H * I / 32); }
 static uint64_t nvfp4_logical(uint64_t H, uint64_t I) { return 3 * (H * I / 2 + H * I / 16 + 4); }
 
@@ -65,7 +67,7 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
     if (c->top_k == 0 || c->top_k > 64 || c->top_k > c->n_experts)
         return fail(MLXS_E_CONFIG, "create: top_k %u outside 1..min(64, n_experts)", c->top_k);
     if (c->n_layers == 0) return fail(MLXS_E_CONFIG, "create: n_layers is 0");
-    if (c->bank_kind > MLXS_BANK_NVFP4) return fail(MLXS_E_CONFIG, "create: bank_kind %u unknown", c->bank_kind);
+    if (c->bank_kind > MLXS_BANK_EXL3_K2_MUL1) return fail(MLXS_E_CONFIG, "create: bank_kind %u unknown", c->bank_kind);
     if (c->act > MLXS_ACT_SWIGLU_CLAMPED) return fail(MLXS_E_CONFIG, "create: act %u unknown (ActivationUnsupported)", c->act);
     if (c->act == MLXS_ACT_SWIGLU_CLAMPED && !(c->act_limit > 0.f))
         return fail(MLXS_E_CONFIG, "create: act_limit must be > 0 for the clamped SwiGLU");
@@ -74,7 +76,7 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
     if (c->max_tokens == 0 || c->max_tokens > 65536) return fail(MLXS_E_CONFIG, "create: max_tokens %u outside 1..65536", c->max_tokens);
     if (c->ep_world == 0 || c->ep_rank >= c->ep_world || c->n_experts % c->ep_world)
         return fail(MLXS_E_CONFIG, "create: ep_world %u / ep_rank %u do not shard %u experts", c->ep_world, c->ep_rank, c->n_experts);
-    if (c->bank_kind == MLXS_BANK_EXL3_K3_MUL1 && c->combine != MLXS_COMBINE_F32)
+    if (is_exl3(c->bank_kind) && c->combine != MLXS_COMBINE_F32)
         return fail(MLXS_E_CONFIG, "create: the EXL3 bank's routed rows are f32; combine must be MLXS_COMBINE_F32");
     int ndev = 0;
     cudaError_t ce = cudaGetDeviceCount(&ndev);
@@ -93,14 +95,14 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
     h->e_local = c->n_experts / c->ep_world;
     h->e_first = c->ep_rank * h->e_local;
     const uint64_t H = c->hidden, I = c->inter;
-    h->logical_bytes = c->bank_kind == MLXS_BANK_EXL3_K3_MUL1 ? exl3_logical(H, I)
+    h->logical_bytes = is_exl3(c->bank_kind)               ? exl3_logical(H, I, exl3_bits(c->bank_kind))
                        : c->bank_kind == MLXS_BANK_MXFP4      ? mxfp4_logical(H, I)
                                                               : nvfp4_logical(H, I);
     h->record_stride = (h->logical_bytes + 4095) / 4096 * 4096;
     h->layers.resize(c->n_layers);
     int rc = 0;
     auto bail = [&](int r) { mlxs_moe_destroy(h); return r; };
-    const Exl3Dims d{c->hidden, c->inter};
+    const Exl3Dims d{c->hidden, c->inter, exl3_bits(c->bank_kind)};
     for (auto& L : h->layers) {
         L.loaded.assign(c->n_experts, 0);
         if ((rc = h->alloc(&L.loaded_dev, c->n_experts)) || (rc = h->alloc(&L.place_dev, (size_t)c->n_experts * 4))) return bail(rc);
@@ -114,7 +116,7 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
             packed[e] = ((uint32_t)L.place_rank[e] << 16) | L.place_slot[e];
         }
         cudaMemcpy(L.place_dev, packed.data(), packed.size() * 4, cudaMemcpyHostToDevice);
-        if (c->bank_kind == MLXS_BANK_EXL3_K3_MUL1) {
+        if (is_exl3(c->bank_kind)) {
             if ((rc = h->alloc(&L.gu_code, (size_t)h->e_local * 2 * exl3_code_words(d) * 4))) return bail(rc);
             if ((rc = h->alloc(&L.d_code, (size_t)h->e_local * exl3_code_words(d) * 4))) return bail(rc);
             if ((rc = h->alloc(&L.scales, (size_t)h->e_local * exl3_scales_per_expert(d) * 2))) return bail(rc);
@@ -129,7 +131,7 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
     // with expert parallelism a rank may receive more rows than it routes: workspaces hold up to 4 x (or world x) its own
     const size_t A = c->ep_world == 1 ? A_call : A_call * (c->ep_world < 4 ? c->ep_world : 4);
     h->rows_cap = (uint32_t)A;
-    if (c->bank_kind != MLXS_BANK_EXL3_K3_MUL1) { h->chunk_rows = FP4_CHUNK_ROWS; h->group_chunks = FP4_GROUP_CHUNKS; }
+    if (!is_exl3(c->bank_kind)) { h->chunk_rows = FP4_CHUNK_ROWS; h->group_chunks = FP4_GROUP_CHUNKS; }
     const uint32_t max_chunks = (uint32_t)(A / h->chunk_rows + (A < c->n_experts ? A : c->n_experts) + 1);
     h->tabs.max_chunks = max_chunks;
     if ((rc = h->alloc(&h->ids_ws, A * 4)) || (rc = h->alloc(&h->w_ws, A * 4)) || (rc = h->alloc(&h->tabs.header, 64)) ||
@@ -143,7 +145,7 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
         return bail(rc);
     cudaMemset(h->status, 0, 16);
     cudaMemset(h->tabs.header, 0, 64);
-    if (c->bank_kind == MLXS_BANK_EXL3_K3_MUL1) {
+    if (is_exl3(c->bank_kind)) {
         const size_t kmax = (H > I ? H : I) / 16;
         if ((rc = h->alloc(&h->xa_gu, (size_t)max_chunks * 2 * kmax * 256)) ||
             (rc = h->alloc(&h->xa_d, (size_t)max_chunks * kmax * 256)) || (rc = h->alloc(&h->ro, A * (H > I ? H : I) * 4)))
@@ -162,7 +164,7 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
     {
         // Staging for the tensor-core lane.  One decode pass of the streaming lane serves 16 rows, one of the
         // tensor-core lane up to 128 at about 1.5 times the instructions: from 17 rows on the latter is the cheaper one.
-        const bool exl3 = c->bank_kind == MLXS_BANK_EXL3_K3_MUL1;
+        const bool exl3 = is_exl3(c->bank_kind);
         const char* ev = getenv("MLXS_PREFILL_MIN_ROWS");
         const int min_rows = ev ? atoi(ev) : 17;
         const bool supported = exl3 ? exl3_prefill_supported(d) : fp4_prefill_supported(c->hidden, c->inter);
@@ -237,8 +239,8 @@ extern "C" int mlxs_moe_load_expert(mlxs_moe* h, uint32_t layer, uint32_t expert
     // the expert's entry of the per-expert table: 1 = resident; the FP4 repack may raise it to 3 (see takes_tensor_lane)
     const uint8_t one = 1;
     CU(cudaMemcpyAsync(L.loaded_dev + le, &one, 1, cudaMemcpyHostToDevice, 0));
-    if (h->cfg.bank_kind == MLXS_BANK_EXL3_K3_MUL1) {
-        const Exl3Dims d{h->cfg.hidden, h->cfg.inter};
+    if (is_exl3(h->cfg.bank_kind)) {
+        const Exl3Dims d{h->cfg.hidden, h->cfg.inter, exl3_bits(h->cfg.bank_kind)};
         CU(launch_exl3_repack(src, d, L.gu_code + (size_t)le * 2 * exl3_code_words(d),
                               L.d_code + (size_t)le * exl3_code_words(d), L.scales + (size_t)le * exl3_scales_per_expert(d), 0));
     } else {
@@ -406,8 +408,8 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
             CU(launch_dispatch(ids_dev, A, n_exp, L.loaded_dev + first, h->tabs, h->chunk_rows, h->group_chunks, heavy,
                                h->status, st));
     }
-    if (c.bank_kind == MLXS_BANK_EXL3_K3_MUL1) {
-        const Exl3Dims d{c.hidden, c.inter};
+    if (is_exl3(c.bank_kind)) {
+        const Exl3Dims d{c.hidden, c.inter, exl3_bits(c.bank_kind)};
         Exl3Layer EL{L.gu_code, L.d_code, L.scales};
         {
             StageTimer tm(h, MLXS_STAGE_PREP, st);
@@ -497,7 +499,7 @@ extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, 
     cudaStream_t st = (cudaStream_t)stream;
     if (c.shared_expert && !L.sh_w1) return fail(MLXS_E_NOT_LOADED, "experts: layer %u has no shared expert weights", layer);
     // FP4 banks with the chain combine keep the routed rows in bf16, as the reference's down texts store them
-    const int ro_bf16 = c.bank_kind != MLXS_BANK_EXL3_K3_MUL1 && c.combine == MLXS_COMBINE_CHAIN;
+    const int ro_bf16 = !is_exl3(c.bank_kind) && c.combine == MLXS_COMBINE_CHAIN;
     // expert parallel with the f32 combine: the exchange carries each token once per rank and brings weighted partial
     // rows back (ep.cu); the chain combine needs every assignment's row in k order and keeps the per-assignment form
     static const bool per_assignment = getenv("MLXS_EP_PER_ASSIGNMENT") != nullptr;
@@ -584,7 +586,7 @@ extern "C" int mlxs_moe_exl3_gemv(mlxs_moe* h, uint32_t layer, uint32_t expert, 
                                   uint32_t rows, float* z_dev, void* stream) {
     if (!h || !xh_dev || !z_dev) return fail(MLXS_E_ARG, "exl3_gemv: null argument");
     const mlxs_moe_config& c = h->cfg;
-    if (c.bank_kind != MLXS_BANK_EXL3_K3_MUL1) return fail(MLXS_E_CONFIG, "exl3_gemv: the handle's bank is not EXL3");
+    if (!is_exl3(c.bank_kind)) return fail(MLXS_E_CONFIG, "exl3_gemv: the handle's bank is not EXL3");
     if (layer >= c.n_layers || expert >= c.n_experts || proj > 2) return fail(MLXS_E_ARG, "exl3_gemv: layer/expert/proj out of range");
     if (h->layers[layer].place_rank[expert] != c.ep_rank || !h->layers[layer].loaded[expert])
         return fail(MLXS_E_NOT_LOADED, "exl3_gemv: expert %u of layer %u is not resident on this rank", expert, layer);
@@ -593,7 +595,7 @@ extern "C" int mlxs_moe_exl3_gemv(mlxs_moe* h, uint32_t layer, uint32_t expert, 
     CU(cudaSetDevice(c.device));
     cudaStream_t st = (cudaStream_t)stream;
     LayerBank& L = h->layers[layer];
-    const Exl3Dims d{c.hidden, c.inter};
+    const Exl3Dims d{c.hidden, c.inter, exl3_bits(c.bank_kind)};
     const uint32_t le = h->layers[layer].place_slot[expert];
     // rows all belong to one pseudo expert 0 of a one-expert dispatch
     CU(cudaMemsetAsync(h->ids_ws, 0, (size_t)rows * 4, st));
@@ -601,7 +603,8 @@ extern "C" int mlxs_moe_exl3_gemv(mlxs_moe* h, uint32_t layer, uint32_t expert, 
     const uint32_t in_dim = proj == 2 ? c.inter : c.hidden, out_dim = proj == 2 ? c.hidden : c.inter;
     CU(launch_exl3_prep_raw(xh_dev, in_dim, h->tabs, h->xa_gu, st));
     const uint32_t* code = proj == 2 ? L.d_code + (size_t)le * exl3_code_words(d) : L.gu_code + (size_t)le * 2 * exl3_code_words(d);
-    CU(launch_exl3_raw(code, in_dim, out_dim, proj == 2 ? 192u : 384u, proj == 1 ? 192u : 0u, h->tabs, h->xa_gu, z_dev,
+    const uint32_t tw8 = 8u * exl3_tile_words(d);   // words of one projection's eight tiles of a k-tile
+    CU(launch_exl3_raw(code, in_dim, out_dim, proj == 2 ? tw8 : 2u * tw8, proj == 1 ? tw8 : 0u, (int)d.K, h->tabs, h->xa_gu, z_dev,
                        h->status, h->sm_count, st));
     return MLXS_OK;
 }

@@ -124,6 +124,36 @@ __device__ __forceinline__ void exl3_lane_plan(uint32_t lane, uint32_t& wi, uint
     wj = (wi + 23u) % 24u;             // the word before it, circular
     lp = 8u * ((lane + 1u) & 3u);
 }
+// The same for K = 2 (a tile is 16 words): lane L's 8 states end at stream bits 16 L + 2 .. 16 L + 16, i.e. they live in
+// the 30 bits ending with halfword L.  `lo` = the word holding halfword L, `hi` = the word before it (circular),
+// lp = 0 when halfword L is the word's low half, 16 when it is the high half; window m at bits [2m, 2m + 16).
+// Bit-level definition: src/exl3/kernels.zig:988-1020 (tileStates at K = 2), generic window formulas
+// scripts/dsv41_exl3_k2_gen.py:96-112.
+__device__ __forceinline__ void exl3_decode_lane_k2(uint32_t lo, uint32_t hi, uint32_t lp, uint32_t (&b)[4]) {
+    const uint32_t v0 = __funnelshift_r(lo, hi, lp);
+    const uint32_t w0 = v0 & 0xFFFFu, w1 = (v0 >> 2) & 0xFFFFu, w2 = (v0 >> 4) & 0xFFFFu, w3 = (v0 >> 6) & 0xFFFFu;
+    const uint32_t w4 = (v0 >> 8) & 0xFFFFu, w5 = (v0 >> 10) & 0xFFFFu, w6 = (v0 >> 12) & 0xFFFFu, w7 = (v0 >> 14) & 0xFFFFu;
+    b[0] = mul1_pair(w7, w6);
+    b[1] = mul1_pair(w5, w4);
+    b[2] = mul1_pair(w3, w2);
+    b[3] = mul1_pair(w1, w0);
+}
+__device__ __forceinline__ void exl3_lane_plan_k2(uint32_t lane, uint32_t& wi, uint32_t& wj, uint32_t& lp) {
+    wi = lane >> 1;
+    wj = (wi + 15u) % 16u;
+    lp = (lane & 1u) ? 0u : 16u;
+}
+// by code width
+template <int KB>
+__device__ __forceinline__ void exl3_decode_lane_kb(uint32_t lo, uint32_t hi, uint32_t lp, uint32_t (&b)[4]) {
+    if (KB == 3) exl3_decode_lane(lo, hi, lp, b);
+    else exl3_decode_lane_k2(lo, hi, lp, b);
+}
+template <int KB>
+__device__ __forceinline__ void exl3_lane_plan_kb(uint32_t lane, uint32_t& wi, uint32_t& wj, uint32_t& lp) {
+    if (KB == 3) exl3_lane_plan(lane, wi, wj, lp);
+    else exl3_lane_plan_k2(lane, wi, wj, lp);
+}
 
 // ---- 128-point Sylvester-natural Hadamard over a warp: lane holds elements 4*lane .. 4*lane+3 ----
 // (unnormalised; src/arch/glm5_next/exl3_forms_ref.zig:116-135)

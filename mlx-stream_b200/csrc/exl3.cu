@@ -23,9 +23,9 @@ constexpr int ZS_STRIDE = 132;    // padded row stride of the epilogue's f32 sta
 // ------------------------------------------------------------------------------------------------------------
 // load-time repack: reference record -> kernel layout (bit-preserving: words move, no bit changes)
 // ------------------------------------------------------------------------------------------------------------
-__global__ void exl3_repack_kernel(const uint8_t* __restrict__ rec, uint32_t H, uint32_t I, uint32_t* __restrict__ gu,
-                                   uint32_t* __restrict__ dn, __half* __restrict__ sc) {
-    const size_t code_bytes = (size_t)(H / 16) * (I / 16) * 96;
+__global__ void exl3_repack_kernel(const uint8_t* __restrict__ rec, uint32_t H, uint32_t I, uint32_t TW,
+                                   uint32_t* __restrict__ gu, uint32_t* __restrict__ dn, __half* __restrict__ sc) {
+    const size_t code_bytes = (size_t)(H / 16) * (I / 16) * TW * 4;   // TW words per 16x16 tile (24 at K = 3, 16 at K = 2)
     // record offsets (src/expert/bank.zig:116-141): per projection code, rout [out], rin [in]
     const size_t off_g = 0, off_g_rout = code_bytes, off_g_rin = off_g_rout + 2 * (size_t)I;
     const size_t off_u = off_g_rin + 2 * (size_t)H, off_u_rout = off_u + code_bytes, off_u_rin = off_u_rout + 2 * (size_t)I;
@@ -37,21 +37,21 @@ __global__ void exl3_repack_kernel(const uint8_t* __restrict__ rec, uint32_t H, 
         if (i < n_gu) {
             // destination index -> (nb, kt, p, j, w)
             size_t r = i;
-            const uint32_t w = r % 24; r /= 24;
+            const uint32_t w = r % TW; r /= TW;
             const uint32_t j = r % 8; r /= 8;
             const uint32_t p = r % 2; r /= 2;
             const uint32_t kt = r % (H / 16); r /= (H / 16);
             const uint32_t nb = (uint32_t)r;
             const uint32_t* src = reinterpret_cast<const uint32_t*>(rec + (p ? off_u : off_g));
-            gu[i] = src[((size_t)kt * (I / 16) + nb * 8 + j) * 24 + w];
+            gu[i] = src[((size_t)kt * (I / 16) + nb * 8 + j) * TW + w];
         } else if (i < n_all) {
             size_t r = i - n_gu;
-            const uint32_t w = r % 24; r /= 24;
+            const uint32_t w = r % TW; r /= TW;
             const uint32_t j = r % 8; r /= 8;
             const uint32_t kt = r % (I / 16); r /= (I / 16);
             const uint32_t nb = (uint32_t)r;
             const uint32_t* src = reinterpret_cast<const uint32_t*>(rec + off_d);
-            dn[i - n_gu] = src[((size_t)kt * (H / 16) + nb * 8 + j) * 24 + w];
+            dn[i - n_gu] = src[((size_t)kt * (H / 16) + nb * 8 + j) * TW + w];
         } else {
             const size_t s = i - n_all;
             const __half* h;
@@ -70,7 +70,7 @@ __global__ void exl3_repack_kernel(const uint8_t* __restrict__ rec, uint32_t H, 
 
 cudaError_t launch_exl3_repack(const uint8_t* record_dev, Exl3Dims d, uint32_t* gu_code_e, uint32_t* d_code_e,
                                __half* scales_e, cudaStream_t st) {
-    exl3_repack_kernel<<<592, 256, 0, st>>>(record_dev, d.H, d.I, gu_code_e, d_code_e, scales_e);
+    exl3_repack_kernel<<<592, 256, 0, st>>>(record_dev, d.H, d.I, exl3_tile_words(d), gu_code_e, d_code_e, scales_e);
     return cudaGetLastError();
 }
 
@@ -178,17 +178,18 @@ struct GemvParams {
 };
 
 // flags: 1 = first stage of a part of the sum, 2 = last stage of a part, 4 = last stage of this CTA's share of the item
-struct StageMeta { int32_t item; uint32_t kt0, chunk0, mc, expert, nb, part, flags; };
+// Only `item` and `flags` (with the chunk count in bits 8..) are read every stage, the rest at the end of a part.
+struct StageMeta { int32_t item; uint32_t flags, mc, kt0, chunk0, expert, nb, part; };
 
 // one pipeline stage (KT k-tiles) of one warp's 16-column tile, MC chunks of activations
-template <int NPROJ, int KSTRIDE, int MC>
+template <int NPROJ, int KSTRIDE, int KB, int MC>
 __device__ __forceinline__ void gemv_stage(const uint32_t* __restrict__ wt, const uint2* __restrict__ at, uint32_t wi,
                                            uint32_t wj, uint32_t lp, uint32_t p, float (&acc)[GROUP_CHUNKS][4]) {
 #pragma unroll
     for (int kt = 0; kt < KT; ++kt) {
         const uint32_t lo = wt[kt * KSTRIDE + wi], hi = wt[kt * KSTRIDE + wj];
         uint32_t b[4];
-        exl3_decode_lane(lo, hi, lp, b);
+        exl3_decode_lane_kb<KB>(lo, hi, lp, b);
         // W^T as the A operand: rows = the tile's 16 output columns
         const uint32_t a[4] = {b[0], b[2], b[1], b[3]};
 #pragma unroll
@@ -199,13 +200,15 @@ __device__ __forceinline__ void gemv_stage(const uint32_t* __restrict__ wt, cons
     }
 }
 
-template <int NPROJ, int EPI, int KSTRIDE>
+// KSTRIDE = words per k-tile of the block stream (8 tiles x 8 KB words per projection present), KB = bits per weight
+template <int NPROJ, int EPI, int KSTRIDE, int KB>
 __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gemv_kernel(const GemvParams P) {
+    constexpr uint32_t TW = 8 * KB;        // words per 16x16 tile
     extern __shared__ __align__(128) uint8_t smem_raw[];
     constexpr int NCW = NPROJ * 8;         // consumer warps: projection x 16-column tile of the 128 block
     constexpr int MAXS = 8;
     __shared__ __align__(8) uint64_t full_bar[MAXS], empty_bar[MAXS], epi_bar;
-    __shared__ StageMeta meta[MAXS];
+    __shared__ __align__(8) StageMeta meta[MAXS];
     __shared__ volatile int s_abort;
     __shared__ volatile int s_last_part;
     // epilogue staging: [NPROJ][GROUP_CHUNKS][CHUNK_ROWS][ZS_STRIDE]
@@ -256,7 +259,8 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
                     meta[s].item = last ? -1 : (int32_t)item;
                     meta[s].kt0 = kt0; meta[s].chunk0 = chunk0; meta[s].mc = mc; meta[s].expert = expert; meta[s].nb = nb;
                     meta[s].part = kt0 / part_kt;
-                    meta[s].flags = (kt0 % part_kt == 0 ? 1u : 0u) | ((kt0 + KT) % part_kt == 0 ? 2u : 0u) | (kt0 + KT >= k_end ? 4u : 0u);
+                    meta[s].flags = (kt0 % part_kt == 0 ? 1u : 0u) | ((kt0 + KT) % part_kt == 0 ? 2u : 0u) |
+                                    (kt0 + KT >= k_end ? 4u : 0u) | (mc << 8);
                     if (last) { mbar_arrive(&full_bar[s]); ok = false; break; }
                     uint8_t* dst = ring + (size_t)s * P.stage_bytes;
                     mbar_expect_tx(&full_bar[s], P.w_bytes + mc * NPROJ * KT * A_TILE_WORDS * 4);
@@ -277,7 +281,7 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
     // ---------------- consumer warps ----------------
     const uint32_t p = warp >> 3, j = warp & 7u;  // projection, 16-column tile
     uint32_t wi, wj, lp;
-    exl3_lane_plan(lane, wi, wj, lp);
+    exl3_lane_plan_kb<KB>(lane, wi, wj, lp);
     float acc[GROUP_CHUNKS][4];
     const float S = __uint_as_float(SCALE_BITS);
     uint32_t epi_ph = 0;
@@ -297,26 +301,29 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
             s_abort = 1;
             break;
         }
-        const StageMeta m = meta[s];
-        if (m.item < 0) break;
-        if (m.flags & 1u) {
+        const uint2 hot = *reinterpret_cast<const uint2*>(&meta[s]);   // item, flags | chunk count << 8
+        if ((int32_t)hot.x < 0) break;
+        const uint32_t flags = hot.y, stage_mc = hot.y >> 8;
+        if (flags & 1u) {
 #pragma unroll
             for (int a = 0; a < GROUP_CHUNKS; ++a)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) acc[a][c] = 0.f;
         }
         const uint8_t* st = ring + (size_t)s * P.stage_bytes;
-        const uint32_t* wt = reinterpret_cast<const uint32_t*>(st) + P.proj_off_words + p * 192u + j * 24u;
+        const uint32_t* wt = reinterpret_cast<const uint32_t*>(st) + P.proj_off_words + p * (8u * TW) + j * TW;
         const uint2* at = reinterpret_cast<const uint2*>(st + P.w_bytes) + lane;
         static_assert(GROUP_CHUNKS * CHUNK_ROWS == 16, "the K-split workspace is sized for 16 rows per item");
         static_assert(GROUP_CHUNKS == 4, "the stage dispatch below enumerates the chunk counts");
-        if (m.mc == 1) gemv_stage<NPROJ, KSTRIDE, 1>(wt, at, wi, wj, lp, p, acc);
-        else if (m.mc == 2) gemv_stage<NPROJ, KSTRIDE, 2>(wt, at, wi, wj, lp, p, acc);
-        else if (m.mc == 3) gemv_stage<NPROJ, KSTRIDE, 3>(wt, at, wi, wj, lp, p, acc);
-        else gemv_stage<NPROJ, KSTRIDE, 4>(wt, at, wi, wj, lp, p, acc);
+        if (stage_mc == 1) gemv_stage<NPROJ, KSTRIDE, KB, 1>(wt, at, wi, wj, lp, p, acc);
+        else if (stage_mc == 2) gemv_stage<NPROJ, KSTRIDE, KB, 2>(wt, at, wi, wj, lp, p, acc);
+        else if (stage_mc == 3) gemv_stage<NPROJ, KSTRIDE, KB, 3>(wt, at, wi, wj, lp, p, acc);
+        else gemv_stage<NPROJ, KSTRIDE, KB, 4>(wt, at, wi, wj, lp, p, acc);
+        StageMeta m;
+        if (flags & 2u) m = meta[s];       // the slot may be refilled once this warp has arrived below
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[s]);
-        if (!(m.flags & 2u)) continue;
+        if (!(flags & 2u)) continue;
 
         // ---------------- end of a part of the sum ----------------
         // the D fragment holds (column g | g+8) x (token slots 2c, 2c+1); z[row] = hi slot + lo slot = lane c + lane c+2.
@@ -344,7 +351,7 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
             __threadfence();
             if (!epi_sync()) break;
         }
-        if (!(m.flags & 4u)) continue;
+        if (!(flags & 4u)) continue;
         if (NP == 1) {
             if (!epi_sync()) break;
         } else {
@@ -441,7 +448,7 @@ static int tune_env(const char* name, int dflt, int lo, int hi) {
     return x < lo ? lo : (x > hi ? hi : x);
 }
 
-static cudaError_t launch_gemv(int nproj, int epi, GemvParams& P, int sm_count, cudaStream_t st) {
+static cudaError_t launch_gemv(int nproj, int epi, int kbits, GemvParams& P, int sm_count, cudaStream_t st) {
     const uint32_t zs_bytes = (uint32_t)(nproj * GROUP_CHUNKS * CHUNK_ROWS * ZS_STRIDE * sizeof(float));
     P.w_bytes = KT * P.kt_stride_words * 4;
     P.stage_bytes = P.w_bytes + GROUP_CHUNKS * nproj * KT * A_TILE_WORDS * 4;
@@ -457,16 +464,25 @@ static cudaError_t launch_gemv(int nproj, int epi, GemvParams& P, int sm_count, 
     const size_t smem = zs_bytes + (size_t)ns * P.stage_bytes;
     cudaError_t e;
     const int ctas = per_sm * sm_count;
-#define MLXS_LAUNCH(NP, EP, KS)                                                                                   \
+#define MLXS_LAUNCH(NP, EP, KS, KBITS)                                                                            \
     do {                                                                                                         \
-        e = cudaFuncSetAttribute(exl3_gemv_kernel<NP, EP, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        e = cudaFuncSetAttribute(exl3_gemv_kernel<NP, EP, KS, KBITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e != cudaSuccess) return e;                                                                          \
-        exl3_gemv_kernel<NP, EP, KS><<<ctas, NP * 256 + 32, smem, st>>>(P);                                      \
+        exl3_gemv_kernel<NP, EP, KS, KBITS><<<ctas, NP * 256 + 32, smem, st>>>(P);                               \
     } while (0)
-    if (nproj == 2) MLXS_LAUNCH(2, EPI_GATE_UP, 384);
-    else if (epi == EPI_DOWN) MLXS_LAUNCH(1, EPI_DOWN, 192);
-    else if (P.kt_stride_words == 192) MLXS_LAUNCH(1, EPI_RAW, 192);
-    else MLXS_LAUNCH(1, EPI_RAW, 384);
+    if (kbits == 3) {
+        if (nproj == 2) MLXS_LAUNCH(2, EPI_GATE_UP, 384, 3);
+        else if (epi == EPI_DOWN) MLXS_LAUNCH(1, EPI_DOWN, 192, 3);
+        else if (P.kt_stride_words == 192) MLXS_LAUNCH(1, EPI_RAW, 192, 3);
+        else MLXS_LAUNCH(1, EPI_RAW, 384, 3);
+    } else if (kbits == 2) {
+        if (nproj == 2) MLXS_LAUNCH(2, EPI_GATE_UP, 256, 2);
+        else if (epi == EPI_DOWN) MLXS_LAUNCH(1, EPI_DOWN, 128, 2);
+        else if (P.kt_stride_words == 128) MLXS_LAUNCH(1, EPI_RAW, 128, 2);
+        else MLXS_LAUNCH(1, EPI_RAW, 256, 2);
+    } else {
+        return cudaErrorInvalidValue;
+    }
 #undef MLXS_LAUNCH
     return cudaGetLastError();
 }
@@ -475,34 +491,34 @@ cudaError_t launch_exl3_gate_up(const Exl3GemvArgs& a, cudaStream_t st) {
     GemvParams P{};
     P.code = a.L.gu_code;
     P.expert_stride_words = 2 * exl3_code_words(a.d);
-    P.n_blocks = a.d.I / 128; P.nkt = a.d.H / 16; P.kt_stride_words = 384; P.proj_off_words = 0;
+    P.n_blocks = a.d.I / 128; P.nkt = a.d.H / 16; P.kt_stride_words = 16 * exl3_tile_words(a.d); P.proj_off_words = 0;
     P.xa = a.xa_gu; P.t = a.t; P.counter_idx = HDR_CTR_GU;
     P.scales = a.L.scales; P.scales_stride = exl3_scales_per_expert(a.d);
     P.H = a.d.H; P.I = a.d.I; P.xa_d = a.xa_d; P.out = nullptr; P.out_dim = a.d.I; P.limit = a.limit; P.status = a.status;
     P.ks_scratch = a.ks_scratch; P.ks_count = a.ks_count;
-    return launch_gemv(2, EPI_GATE_UP, P, a.sm_count, st);
+    return launch_gemv(2, EPI_GATE_UP, (int)a.d.K, P, a.sm_count, st);
 }
 cudaError_t launch_exl3_down(const Exl3GemvArgs& a, cudaStream_t st) {
     GemvParams P{};
     P.code = a.L.d_code;
     P.expert_stride_words = exl3_code_words(a.d);
-    P.n_blocks = a.d.H / 128; P.nkt = a.d.I / 16; P.kt_stride_words = 192; P.proj_off_words = 0;
+    P.n_blocks = a.d.H / 128; P.nkt = a.d.I / 16; P.kt_stride_words = 8 * exl3_tile_words(a.d); P.proj_off_words = 0;
     P.xa = a.xa_d; P.t = a.t; P.counter_idx = HDR_CTR_DOWN;
     P.scales = a.L.scales; P.scales_stride = exl3_scales_per_expert(a.d);
     P.H = a.d.H; P.I = a.d.I; P.xa_d = nullptr; P.out = a.ro; P.out_dim = a.d.H; P.limit = a.limit; P.status = a.status;
     P.ks_scratch = a.ks_scratch; P.ks_count = a.ks_count;
-    return launch_gemv(1, EPI_DOWN, P, a.sm_count, st);
+    return launch_gemv(1, EPI_DOWN, (int)a.d.K, P, a.sm_count, st);
 }
 cudaError_t launch_exl3_raw(const uint32_t* code_e, uint32_t in_dim, uint32_t out_dim, uint32_t ktile_stride_words,
-                            uint32_t proj_off_words, DispatchTables t, const uint32_t* xa, float* z, uint32_t* status,
-                            int sm_count, cudaStream_t st) {
+                            uint32_t proj_off_words, int kbits, DispatchTables t, const uint32_t* xa, float* z,
+                            uint32_t* status, int sm_count, cudaStream_t st) {
     GemvParams P{};
     P.code = code_e; P.expert_stride_words = 0;
     P.n_blocks = out_dim / 128; P.nkt = in_dim / 16; P.kt_stride_words = ktile_stride_words; P.proj_off_words = proj_off_words;
     P.xa = xa; P.t = t; P.counter_idx = HDR_CTR_AUX;
     P.scales = nullptr; P.scales_stride = 0; P.H = 0; P.I = 0; P.xa_d = nullptr; P.out = z; P.out_dim = out_dim;
     P.limit = 0.f; P.status = status;
-    return launch_gemv(1, EPI_RAW, P, sm_count, st);
+    return launch_gemv(1, EPI_RAW, kbits, P, sm_count, st);
 }
 
 }  // namespace mlxs

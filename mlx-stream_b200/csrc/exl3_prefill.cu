@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(256) pf_prep_kernel(const __nv_bfloat16* __res
 // the kernel
 // ------------------------------------------------------------------------------------------------------------
 struct PfParams {
-    const uint32_t* code;        // layer base of the block stream (gate/up: 384 words per k-tile, down: 192)
+    const uint32_t* code;        // layer base of the block stream (8 tiles of 8 K words per k-tile and projection)
     size_t expert_stride_words;
     uint32_t n_blocks, nkt;      // out / 128, in / 16
     const __half* xa;            // B operand, layout of pf_xa_off
@@ -154,13 +154,14 @@ struct PfParams {
 };
 
 // NPROJ projections x CB adjacent 128-column blocks = 4 accumulator groups of 128 TMEM columns each
-template <int NPROJ, int CB>
+template <int NPROJ, int CB, int KB>
 __global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParams P) {
     static_assert(NPROJ * CB == 4, "four accumulator groups fill the 512 tensor-memory columns at 128 rows");
     extern __shared__ __align__(128) uint8_t smem_raw[];
     constexpr int NCW = 16;                            // decode warps
     constexpr int NG = NPROJ * CB;                     // accumulator groups
-    constexpr int KSTRIDE = NPROJ * 192;               // words per k-tile in one block's code stream
+    constexpr int TW = 8 * KB;                         // words per 16x16 tile (KB bits per weight)
+    constexpr int KSTRIDE = NPROJ * 8 * TW;            // words per k-tile in one block's code stream
     constexpr int RAW_BLK = PF_KT * KSTRIDE * 4;       // bytes of one block's k-tiles of a stage
     constexpr int RAW_BYTES = CB * RAW_BLK;
     constexpr int TMEM_COLS = NG * PF_NT;
@@ -263,7 +264,7 @@ __global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParam
         // down: column blocks 2 hi and 2 hi + 1.  Group index = NPROJ == 2 ? hi * CB + cb : 2 hi + cb.
         const uint32_t hi = warp >> 3, j = warp & 7u;
         uint32_t wi, wj, lp;
-        exl3_lane_plan(lane, wi, wj, lp);
+        exl3_lane_plan_kb<KB>(lane, wi, wj, lp);
         const uint32_t g = lane >> 2, c = lane & 3u;
         const float S = __uint_as_float(SCALE_BITS);
         uint32_t rit = 0, bit = 0, nitem = 0, epi_ph = 0;
@@ -290,13 +291,13 @@ __global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParam
                 for (int u = 0; u < 2; ++u) {
                     const uint32_t cb = NPROJ == 2 ? (uint32_t)u : 2u * hi + u, p = NPROJ == 2 ? hi : 0u;
                     const uint32_t gq = NPROJ == 2 ? hi * CB + u : cb;
-                    const uint32_t* wt = reinterpret_cast<const uint32_t*>(raw_ring + rs * RAW_BYTES + cb * RAW_BLK) + p * 192u + j * 24u;
+                    const uint32_t* wt = reinterpret_cast<const uint32_t*>(raw_ring + rs * RAW_BYTES + cb * RAW_BLK) + p * (8u * TW) + j * TW;
                     // the warp's 16 columns are core-matrix rows 2j and 2j+1; a lane's half2 pairs sit at g*16 + 4c bytes
                     uint8_t* ad = a_ring + (as * NG + gq) * PF_A_BYTES + (2 * j) * PF_SBO + g * 16 + c * 4;
 #pragma unroll
                     for (int kt = 0; kt < PF_KT; ++kt) {
                         uint32_t bq[4];
-                        exl3_decode_lane(wt[kt * KSTRIDE + wi], wt[kt * KSTRIDE + wj], lp, bq);
+                        exl3_decode_lane_kb<KB>(wt[kt * KSTRIDE + wi], wt[kt * KSTRIDE + wj], lp, bq);
                         uint8_t* d = ad + (2 * kt) * PF_LBO_A;
                         *reinterpret_cast<uint32_t*>(d) = bq[0];                        // k 2c,2c+1      column g
                         *reinterpret_cast<uint32_t*>(d + PF_LBO_A) = bq[1];             // k 2c+8,2c+9    column g
@@ -425,15 +426,25 @@ cudaError_t launch_exl3_prefill(const Exl3PrefillArgs& a, cudaStream_t st) {
     P.code = a.L.gu_code; P.expert_stride_words = 2 * exl3_code_words(a.d); P.n_blocks = a.d.I / 128; P.nkt = a.d.H / 16;
     P.xa = a.xa; P.xd = a.xd; P.ro = nullptr;
     size_t smem = pf_smem_bytes(2);
-    if ((e = cudaFuncSetAttribute(exl3_prefill_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
-    exl3_prefill_kernel<2, 2><<<a.sm_count, 512 + 64, smem, st>>>(P);
+    if (a.d.K == 3) {
+        if ((e = cudaFuncSetAttribute(exl3_prefill_kernel<2, 2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
+        exl3_prefill_kernel<2, 2, 3><<<a.sm_count, 512 + 64, smem, st>>>(P);
+    } else {
+        if ((e = cudaFuncSetAttribute(exl3_prefill_kernel<2, 2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
+        exl3_prefill_kernel<2, 2, 2><<<a.sm_count, 512 + 64, smem, st>>>(P);
+    }
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     // down: four adjacent column blocks per CTA
     P.code = a.L.d_code; P.expert_stride_words = exl3_code_words(a.d); P.n_blocks = a.d.H / 128; P.nkt = a.d.I / 16;
     P.xa = a.xd; P.xd = nullptr; P.ro = a.ro;
     smem = pf_smem_bytes(1);
-    if ((e = cudaFuncSetAttribute(exl3_prefill_kernel<1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
-    exl3_prefill_kernel<1, 4><<<a.sm_count, 512 + 64, smem, st>>>(P);
+    if (a.d.K == 3) {
+        if ((e = cudaFuncSetAttribute(exl3_prefill_kernel<1, 4, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
+        exl3_prefill_kernel<1, 4, 3><<<a.sm_count, 512 + 64, smem, st>>>(P);
+    } else {
+        if ((e = cudaFuncSetAttribute(exl3_prefill_kernel<1, 4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
+        exl3_prefill_kernel<1, 4, 2><<<a.sm_count, 512 + 64, smem, st>>>(P);
+    }
     return cudaGetLastError();
 }
 

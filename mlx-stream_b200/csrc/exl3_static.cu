@@ -59,20 +59,28 @@ __global__ void __launch_bounds__(128) na_gemv_kernel(const uint32_t* __restrict
     if (tn >= ntn) return;
     uint32_t wi, wj, lp;
     exl3_lane_plan(lane, wi, wj, lp);
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
     const uint2* xv = reinterpret_cast<const uint2*>(xa + (size_t)chunk * nkt * NA_FRAG_WORDS) + lane;
-    for (uint32_t kt = 0; kt < nkt; ++kt) {
-        const uint32_t* tile = code + ((size_t)kt * ntn + tn) * 24;
-        uint32_t b[4];
-        exl3_decode_lane(tile[wi], tile[wj], lp, b);
-        const uint32_t a[4] = {b[0], b[2], b[1], b[3]};
-        const uint2 x2 = xv[(size_t)kt * 32];
-        mma_f16(acc, a, x2.x, x2.y);
-    }
+    // the sum over the inputs in the same equal parts, folded left, as the handle's streaming kernel takes it (4 parts
+    // when the k-tiles divide by 32, else 2 by 16, else one): the two entries then agree bit for bit
+    const uint32_t parts = nkt % 32 == 0 ? 4u : (nkt % 16 == 0 ? 2u : 1u), part_kt = nkt / parts;
     const uint32_t g = lane >> 2, c = lane & 3u;
-    float v[4];
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    for (uint32_t part = 0; part < parts; ++part) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (uint32_t kt = part * part_kt; kt < (part + 1) * part_kt; ++kt) {
+            const uint32_t* tile = code + ((size_t)kt * ntn + tn) * 24;
+            uint32_t b[4];
+            exl3_decode_lane(tile[wi], tile[wj], lp, b);
+            const uint32_t a[4] = {b[0], b[2], b[1], b[3]};
+            const uint2 x2 = xv[(size_t)kt * 32];
+            mma_f16(acc, a, x2.x, x2.y);
+        }
 #pragma unroll
-    for (int q = 0; q < 4; ++q) v[q] = acc[q] + __shfl_xor_sync(0xFFFFFFFFu, acc[q], 2);
+        for (int q = 0; q < 4; ++q) {
+            const float pv = acc[q] + __shfl_xor_sync(0xFFFFFFFFu, acc[q], 2);
+            v[q] = part == 0 ? pv : v[q] + pv;
+        }
+    }
     if (c < 2) {
         const uint32_t r0 = chunk * 4 + 2 * c;
         if (r0 < rows) {

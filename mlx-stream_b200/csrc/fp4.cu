@@ -143,7 +143,8 @@ struct Fp4Params {
 };
 
 // flags: 1 = first stage of a part of the sum, 2 = last stage of a part, 4 = last stage of this CTA's share of the item
-struct F4Meta { int32_t item; uint32_t ks, chunk0, mc, expert, nb, part, flags; };
+// Only `item` and `flags` (with the chunk count in bits 8..) are read every stage, the rest at the end of a part.
+struct F4Meta { int32_t item; uint32_t flags, mc, ks, chunk0, expert, nb, part; };
 
 __device__ __forceinline__ void fp4_decode8(uint32_t w, uint32_t (&h)[4]) {
     h[0] = ((w << 9) & 0x0E000E00u) | ((w << 12) & 0x80008000u);
@@ -218,7 +219,7 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
     constexpr int NCW = NPROJ * 8;
     constexpr int MAXS = 8;
     __shared__ __align__(8) uint64_t full_bar[MAXS], empty_bar[MAXS], epi_bar;
-    __shared__ F4Meta meta[MAXS];
+    __shared__ __align__(8) F4Meta meta[MAXS];
     __shared__ volatile int s_abort;
     __shared__ volatile int s_last_part;
     __shared__ uint32_t s_lut[NV ? 256 : 1];
@@ -270,7 +271,8 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
                     meta[s].item = last ? -1 : (int32_t)item;
                     meta[s].ks = ks; meta[s].chunk0 = chunk0; meta[s].mc = mc; meta[s].expert = expert; meta[s].nb = nb;
                     meta[s].part = ks / part_stages;
-                    meta[s].flags = (ks % part_stages == 0 ? 1u : 0u) | ((ks + 1) % part_stages == 0 ? 2u : 0u) | (ks + 1 >= ks_end ? 4u : 0u);
+                    meta[s].flags = (ks % part_stages == 0 ? 1u : 0u) | ((ks + 1) % part_stages == 0 ? 2u : 0u) |
+                                    (ks + 1 >= ks_end ? 4u : 0u) | (mc << 8);
                     if (last) { mbar_arrive(&full_bar[s]); ok = false; break; }
                     uint8_t* dst = ring + (size_t)s * P.stage_bytes;
                     mbar_expect_tx(&full_bar[s], P.w_bytes + mc * 4 * F4_XA_SB_WORDS * 4);
@@ -304,20 +306,23 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
             s_abort = 1;
             break;
         }
-        const F4Meta m = meta[s];
-        if (m.item < 0) break;
-        if (m.flags & 1u) {
+        const uint2 hot = *reinterpret_cast<const uint2*>(&meta[s]);   // item, flags | chunk count << 8
+        if ((int32_t)hot.x < 0) break;
+        const uint32_t flags = hot.y, stage_mc = hot.y >> 8;
+        if (flags & 1u) {
 #pragma unroll
             for (int a = 0; a < F4_GROUP; ++a)
 #pragma unroll
                 for (int q = 0; q < 4; ++q) acc[a][q] = 0.f;
         }
         const uint8_t* st = ring + (size_t)s * P.stage_bytes;
-        if (m.mc == 1) fp4_stage<NPROJ, NV, 1>(st, P.w_bytes, p, j, lane, s_lut, acc);
+        if (stage_mc == 1) fp4_stage<NPROJ, NV, 1>(st, P.w_bytes, p, j, lane, s_lut, acc);
         else fp4_stage<NPROJ, NV, 2>(st, P.w_bytes, p, j, lane, s_lut, acc);
+        F4Meta m;
+        if (flags & 2u) m = meta[s];       // the slot may be refilled once this warp has arrived below
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[s]);
-        if (!(m.flags & 2u)) continue;
+        if (!(flags & 2u)) continue;
 
         // ---- end of a part of the sum: D fragment = (output row g | g+8) x (token slots 2c, 2c+1) ----
         // One CTA per item: the parts are folded left in the staging array.  Several CTAs: every part goes to its slot.
@@ -346,7 +351,7 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
             __threadfence();
             if (!epi_sync()) break;
         }
-        if (!(m.flags & 4u)) continue;
+        if (!(flags & 4u)) continue;
         if (NP == 1) {
             if (!epi_sync()) break;
         } else {

@@ -56,9 +56,10 @@ struct Exl3Layer {            // one layer's resident bank, in the kernels' layo
     const uint32_t* d_code;   // [E][H/128][I/16][192] u32
     const __half* scales;     // [E][2H + 2I + I + H]: suh_g, suh_u [H] | svh_g, svh_u [I] | suh_d [I] | svh_d [H]
 };
-struct Exl3Dims { uint32_t H, I; };
+struct Exl3Dims { uint32_t H, I, K; };   // K = bits per weight of the trellis code (3 or 2): a 16x16 tile is 8 K words
 static inline size_t exl3_scales_per_expert(Exl3Dims d) { return (size_t)3 * d.H + 3 * d.I; }
-static inline size_t exl3_code_words(Exl3Dims d) { return (size_t)(d.H / 16) * (d.I / 16) * 24; }
+static inline uint32_t exl3_tile_words(Exl3Dims d) { return 8u * d.K; }
+static inline size_t exl3_code_words(Exl3Dims d) { return (size_t)(d.H / 16) * (d.I / 16) * exl3_tile_words(d); }
 
 // record (device, reference v2 layout) -> the expert's slices of the three arrays
 cudaError_t launch_exl3_repack(const uint8_t* record_dev, Exl3Dims d, uint32_t* gu_code_e, uint32_t* d_code_e,
@@ -89,10 +90,11 @@ static inline size_t exl3_ksplit_scratch_bytes(int sm_count) { return (size_t)2 
 cudaError_t launch_exl3_gate_up(const Exl3GemvArgs& a, cudaStream_t st);
 cudaError_t launch_exl3_down(const Exl3GemvArgs& a, cudaStream_t st);
 // raw projection: z [rows, out] = xa . W_hat(code); `code` in the single-projection block layout with a k-tile
-// stride of `ktile_stride_words` and the projection at `proj_off_words` (192/0 for down, 384/{0,192} for gate/up)
+// stride of `ktile_stride_words` and the projection at `proj_off_words` (at K = 3: 192/0 for down, 384/{0,192} for
+// gate/up; at K = 2: 128/0 and 256/{0,128}); kbits = bits per weight
 cudaError_t launch_exl3_raw(const uint32_t* code_e, uint32_t in_dim, uint32_t out_dim, uint32_t ktile_stride_words,
-                            uint32_t proj_off_words, DispatchTables t, const uint32_t* xa, float* z, uint32_t* status,
-                            int sm_count, cudaStream_t st);
+                            uint32_t proj_off_words, int kbits, DispatchTables t, const uint32_t* xa, float* z,
+                            uint32_t* status, int sm_count, cudaStream_t st);
 
 // prefill-sized batches: tcgen05 MMA over trellis tiles decoded to f16 in shared memory (exl3_prefill.cu)
 constexpr int PREFILL_TILE_ROWS = 128;

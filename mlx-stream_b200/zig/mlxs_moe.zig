@@ -2,11 +2,11 @@
 //! is the compiled, tested statement of the same ABI).  One declaration per C entry point, same order.
 const std = @import("std");
 
-pub const abi_expected: i32 = 2026112504;
+pub const abi_expected: i32 = 2026112505;
 
 pub const Moe = opaque {};
 
-pub const BankKind = enum(u32) { exl3_k3_mul1 = 0, mxfp4 = 1, nvfp4 = 2 };
+pub const BankKind = enum(u32) { exl3_k3_mul1 = 0, mxfp4 = 1, nvfp4 = 2, exl3_k2_mul1 = 3 };
 pub const Scoring = enum(u32) { sqrtsoftplus = 0, sigmoid = 1, softmax = 2 };
 pub const Act = enum(u32) { swiglu = 0, swiglu_clamped = 1 };
 pub const Combine = enum(u32) { f32 = 0, chain = 1 };

@@ -174,15 +174,20 @@ int orc_exl3_geometry(int K, uint64_t hidden, uint64_t inter, orc_exl3_geom *g) 
     return 0;
 }
 
-void orc_exl3_synth_record(uint64_t seed, uint64_t hidden, uint64_t inter, double suh_scale, double svh_scale,
-                           uint8_t *rec) {
+void orc_exl3_synth_record_k(int K, uint64_t seed, uint64_t hidden, uint64_t inter, double suh_scale, double svh_scale,
+                             uint8_t *rec) {
     orc_exl3_geom g;
-    orc_exl3_geometry(3, hidden, inter, &g);
+    orc_exl3_geometry(K, hidden, inter, &g);
     for (int p = 0; p < 3; ++p) {
         orc_fill_code(seed + 1 + 3 * p, (int16_t *)(rec + g.off[3 * p]), g.len[3 * p] / 2);
         orc_fill_scales(seed + 2 + 3 * p, suh_scale, (uint16_t *)(rec + g.off[3 * p + 2]), g.len[3 * p + 2] / 2);
         orc_fill_scales(seed + 3 + 3 * p, svh_scale, (uint16_t *)(rec + g.off[3 * p + 1]), g.len[3 * p + 1] / 2);
     }
+}
+
+void orc_exl3_synth_record(uint64_t seed, uint64_t hidden, uint64_t inter, double suh_scale, double svh_scale,
+                           uint8_t *rec) {
+    orc_exl3_synth_record_k(3, seed, hidden, inter, suh_scale, svh_scale, rec);
 }
 
 /* ------------------------------------------------------------------------------------------------ */
@@ -239,18 +244,18 @@ typedef struct {
     float *fg, *fu, *fd;    /* the same as f32 (optional) */
 } exl3_dec;
 
-static int exl3_decode_record(const uint8_t *rec, uint64_t hidden, uint64_t inter, const uint16_t *table,
+static int exl3_decode_record(int K, const uint8_t *rec, uint64_t hidden, uint64_t inter, const uint16_t *table,
                               exl3_dec *d) {
     orc_exl3_geom g;
-    if (orc_exl3_geometry(3, hidden, inter, &g)) return -1;
+    if (orc_exl3_geometry(K, hidden, inter, &g)) return -1;
     size_t n = (size_t)hidden * inter;
     d->wg = (uint16_t *)malloc(n * 2);
     d->wu = (uint16_t *)malloc(n * 2);
     d->wd = (uint16_t *)malloc(n * 2);
     if (!d->wg || !d->wu || !d->wd) return -2;
-    orc_reconstruct((const int16_t *)(rec + g.off[0]), hidden / 16, inter / 16, 3, table, d->wg, NULL);
-    orc_reconstruct((const int16_t *)(rec + g.off[3]), hidden / 16, inter / 16, 3, table, d->wu, NULL);
-    orc_reconstruct((const int16_t *)(rec + g.off[6]), inter / 16, hidden / 16, 3, table, d->wd, NULL);
+    orc_reconstruct((const int16_t *)(rec + g.off[0]), hidden / 16, inter / 16, K, table, d->wg, NULL);
+    orc_reconstruct((const int16_t *)(rec + g.off[3]), hidden / 16, inter / 16, K, table, d->wu, NULL);
+    orc_reconstruct((const int16_t *)(rec + g.off[6]), inter / 16, hidden / 16, K, table, d->wd, NULL);
     return 0;
 }
 static void exl3_dec_free(exl3_dec *d) { free(d->wg); free(d->wu); free(d->wd); }
@@ -300,11 +305,16 @@ static void exl3_forward_rows(const double *x, size_t rows, size_t in, const uin
 /* src/arch/glm5_next/exl3_forms_ref.zig:159-195 */
 int orc_exl3_expert_f64(const uint8_t *rec, uint64_t hidden, uint64_t inter, double limit, const double *x,
                         size_t rows, double *h_out, double *y_out) {
+    return orc_exl3_expert_f64_k(3, rec, hidden, inter, limit, x, rows, h_out, y_out);
+}
+/* the same at any K (the record's code segments shrink to 16 K int16 per tile, src/exl3/kernels.zig:163-177) */
+int orc_exl3_expert_f64_k(int K, const uint8_t *rec, uint64_t hidden, uint64_t inter, double limit, const double *x,
+                          size_t rows, double *h_out, double *y_out) {
     orc_exl3_geom g;
-    if (orc_exl3_geometry(3, hidden, inter, &g)) return -1;
+    if (orc_exl3_geometry(K, hidden, inter, &g)) return -1;
     if (hidden % 128 || inter % 128) return -1;
     exl3_dec d;
-    int rc = exl3_decode_record(rec, hidden, inter, table_once(), &d);
+    int rc = exl3_decode_record(K, rec, hidden, inter, table_once(), &d);
     if (rc) return rc;
     const uint16_t *g_rout = (const uint16_t *)(rec + g.off[1]), *g_rin = (const uint16_t *)(rec + g.off[2]);
     const uint16_t *u_rout = (const uint16_t *)(rec + g.off[4]), *u_rin = (const uint16_t *)(rec + g.off[5]);
@@ -382,7 +392,7 @@ int orc_exl3_expert_f32chain(const uint8_t *rec, uint64_t hidden, uint64_t inter
     orc_exl3_geom g;
     if (orc_exl3_geometry(3, hidden, inter, &g) || hidden % 128 || inter % 128) return -1;
     exl3_dec d;
-    int rc = exl3_decode_record(rec, hidden, inter, table_once(), &d);
+    int rc = exl3_decode_record(3, rec, hidden, inter, table_once(), &d);
     if (rc) return rc;
     const uint16_t *og = (const uint16_t *)(rec + g.off[1]), *rg = (const uint16_t *)(rec + g.off[2]);
     const uint16_t *ou = (const uint16_t *)(rec + g.off[4]), *ru = (const uint16_t *)(rec + g.off[5]);
@@ -896,8 +906,8 @@ int orc_layer(const orc_layer_cfg *c, const uint8_t *const *records, const float
             size_t tok = order[offs[e] + r] / k;
             for (size_t j = 0; j < H; ++j) xe[r * H + j] = x[tok * H + j];
         }
-        if (c->bank == ORC_BANK_EXL3) {
-            rc = orc_exl3_expert_f64(records[e], H, I, c->limit, xe, n, NULL, ye);
+        if (c->bank == ORC_BANK_EXL3 || c->bank == ORC_BANK_EXL3_K2) {
+            rc = orc_exl3_expert_f64_k(c->bank == ORC_BANK_EXL3 ? 3 : 2, records[e], H, I, c->limit, xe, n, NULL, ye);
         } else {
             size_t nw = H * I;
             float *wg = (float *)malloc(nw * 4), *wu = (float *)malloc(nw * 4), *wd = (float *)malloc(nw * 4);
@@ -931,7 +941,7 @@ int orc_layer(const orc_layer_cfg *c, const uint8_t *const *records, const float
         }
         for (size_t t = 0; t < T; ++t)
             for (size_t j = 0; j < H; ++j) {
-                if (c->bank != ORC_BANK_EXL3 && c->chain_rounding) {
+                if (c->bank != ORC_BANK_EXL3 && c->bank != ORC_BANK_EXL3_K2 && c->chain_rounding) {
                     /* mimo_v2/moe.zig:363-372: products added to 0, folded k = 0..top_k-1, bf16 once */
                     float acc = (float)ro[(t * k) * H + j] * weights[t * k] + 0.0f;
                     for (size_t q = 1; q < k; ++q) {

@@ -50,6 +50,8 @@ int orc_exl3_geometry(int K, uint64_t hidden, uint64_t inter, orc_exl3_geom *g);
  * (src/arch/glm5_next/exl3_forms_ref.zig:81-93, at any shape and with the two scales as arguments) */
 void orc_exl3_synth_record(uint64_t seed, uint64_t hidden, uint64_t inter, double suh_scale, double svh_scale,
                            uint8_t *rec);
+void orc_exl3_synth_record_k(int K, uint64_t seed, uint64_t hidden, uint64_t inter, double suh_scale, double svh_scale,
+                             uint8_t *rec);
 
 /* ---- EXL3 f64 forward: src/arch/glm5_next/exl3_forms_ref.zig:116-195 ---- */
 void orc_fwht128(double *v, size_t n);
@@ -59,6 +61,8 @@ double orc_swiglu_clamped(double g, double u, double limit); /* limit <= 0: plai
 /* one expert on `rows` input rows (f64): h [rows, inter], y [rows, hidden] (either may be NULL) */
 int orc_exl3_expert_f64(const uint8_t *rec, uint64_t hidden, uint64_t inter, double limit, const double *x,
                         size_t rows, double *h, double *y);
+int orc_exl3_expert_f64_k(int K, const uint8_t *rec, uint64_t hidden, uint64_t inter, double limit, const double *x,
+                          size_t rows, double *h_out, double *y_out);
 /* the f32 seam chain per output word: src/arch/glm5_next/exl3_forms_ref.zig:231-343 */
 int orc_exl3_expert_f32chain(const uint8_t *rec, uint64_t hidden, uint64_t inter, const float *x, size_t rows,
                              float *h, float *y);
@@ -97,7 +101,7 @@ void orc_dispatch(const int32_t *slot, size_t n, size_t n_slots, uint32_t *order
                   uint32_t *inv, uint32_t *offsets /* [n_slots+1] */);
 
 /* ---- layer (router outputs given): per expert decode once, run its rows, weighted combine ---- */
-enum { ORC_BANK_EXL3 = 0, ORC_BANK_MXFP4 = 1, ORC_BANK_NVFP4 = 2 };
+enum { ORC_BANK_EXL3 = 0, ORC_BANK_MXFP4 = 1, ORC_BANK_NVFP4 = 2, ORC_BANK_EXL3_K2 = 3 };
 typedef struct {
     int bank;
     uint64_t hidden, inter, n_experts, top_k;

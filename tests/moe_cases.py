@@ -151,6 +151,14 @@ class Exl3Case:
         self.moe.close()
 
 
+class Exl3K2Case(Exl3Case):
+    """The EXL3 bank at 2 bits per weight (the reference's K = 2 layers, src/exl3/kernels.zig:163-177)."""
+    bank = O.BANK_EXL3_K2
+
+    def synth(self, e):
+        return O.exl3_synth_record(self.record_seed(e), self.H, self.I, 1.0, 0.02, K=2)
+
+
 class Mxfp4Case(Exl3Case):
     """MiMo-style bank: MXFP4 codes with E8M0 block scales, unclamped SwiGLU, chain combine."""
     bank = O.BANK_MXFP4

@@ -11,7 +11,7 @@ ORACLE_DIR = ROOT / "oracle"
 _LIB = None
 
 SCORE_SQRTSOFTPLUS, SCORE_SIGMOID, SCORE_SOFTMAX = 0, 1, 2
-BANK_EXL3, BANK_MXFP4, BANK_NVFP4 = 0, 1, 2
+BANK_EXL3, BANK_MXFP4, BANK_NVFP4, BANK_EXL3_K2 = 0, 1, 2, 3
 
 
 class Geom(C.Structure):
@@ -68,6 +68,7 @@ def lib():
         L.orc_fill_code.argtypes = [C.c_uint64, C.c_void_p, C.c_size_t]
         L.orc_fill_x_bf16.argtypes = [C.c_uint64, C.c_void_p, C.c_size_t]
         L.orc_exl3_synth_record.argtypes = [C.c_uint64, C.c_uint64, C.c_uint64, C.c_double, C.c_double, C.c_void_p]
+        L.orc_exl3_synth_record_k.argtypes = [C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_double, C.c_double, C.c_void_p]
         L.orc_mxfp4_synth_record.argtypes = [C.c_uint64, C.c_uint64, C.c_uint64, C.c_double, C.c_void_p]
         L.orc_nvfp4_synth_record.argtypes = [C.c_uint64, C.c_uint64, C.c_uint64, C.c_double, C.c_void_p]
         L.orc_exl3_expert_f64.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_double, C.c_void_p, C.c_size_t,
@@ -138,10 +139,10 @@ def exl3_geometry(hidden, inter, K=3):
     return g
 
 
-def exl3_synth_record(seed, hidden, inter, suh_scale=1.0, svh_scale=0.02):
-    g = exl3_geometry(hidden, inter)
+def exl3_synth_record(seed, hidden, inter, suh_scale=1.0, svh_scale=0.02, K=3):
+    g = exl3_geometry(hidden, inter, K)
     rec = np.zeros(g.record_bytes, np.uint8)
-    lib().orc_exl3_synth_record(seed, hidden, inter, suh_scale, svh_scale, _p(rec))
+    lib().orc_exl3_synth_record_k(K, seed, hidden, inter, suh_scale, svh_scale, _p(rec))
     return rec
 
 

@@ -414,3 +414,59 @@ def test_whole_golden_planes_decode_bit_exact(H, I, proj, which):
         assert case.status() == 0
     finally:
         case.close()
+
+
+# ---- EXL3 at 2 bits per weight (the reference's K = 2 layers) ----
+@pytest.mark.parametrize("proj,which", [(0, "gate_up_k2"), (2, "down_k2")])
+def test_k2_whole_golden_planes_decode_bit_exact(proj, which):
+    """src/kernels/exl3/manifest.json golden planes at K = 2 (scripts/dsv41_exl3_k2_goldens.json): every row of the
+    plane through the GPU decode, the f16 plane's sha256 against `w_hat_sha256`."""
+    from moe_cases import Exl3K2Case
+    plane = json.loads((GOLD / "exl3_digests.json").read_text())["planes"][which]
+    H, I = 5120, 2304
+    n_in = I if proj == 2 else H
+    case = Exl3K2Case(H, I, 1, 1, seed=0, shared=False, max_tokens=1024, experts_to_load=[])
+    try:
+        g = O.exl3_geometry(H, I, 2)
+        rec = np.zeros(g.record_bytes, np.uint8)
+        seg = 6 if proj == 2 else 0
+        code = O.fill_code(plane["seed"], g.len[seg] // 2)
+        assert hashlib.sha256(code.tobytes()).hexdigest() == plane["code_sha256"]
+        rec[g.off[seg]:g.off[seg] + g.len[seg]] = code.view(np.uint8)
+        case.moe.load_expert(0, 0, rec.ctypes.data, rec.size)
+        digest = hashlib.sha256()
+        for r0 in range(0, n_in, 1024):
+            rows = min(1024, n_in - r0)
+            xh = np.zeros((rows, n_in), np.float32)
+            xh[np.arange(rows), r0 + np.arange(rows)] = 1.0
+            z16 = case.gpu_gemv(0, proj, xh).astype(np.float16)
+            digest.update(z16.tobytes())
+        assert digest.hexdigest() == plane["w_hat_sha256"]
+        assert case.status() == 0
+    finally:
+        case.close()
+
+
+def test_k2_layer_both_lanes():
+    from moe_cases import Exl3K2Case
+    case = Exl3K2Case(512, 256, 4, 2, seed=12, shared=True, max_tokens=512)
+    try:
+        for T in (1, 9):
+            x, logits = case.inputs(T, seed=3 + T)
+            y = case.gpu_forward(x, logits)
+            ids, w = case.cpu_route(logits)
+            assert rel_l2(y, case.cpu_layer(x, ids, w)) < TOL_LAYER
+        T = 300
+        x, logits = case.inputs(T, seed=31)
+        logits[:, 0] += 3.0
+        logits[:, 3] -= 2.5
+        ids, w = case.cpu_route(logits)
+        counts = np.bincount(ids.reshape(-1), minlength=4)
+        assert counts.max() > 128 and 0 < counts.min() < 17
+        ref_y, ref_ro = case.cpu_layer(x, ids, w, want_ro=True)
+        ro = case.gpu_routed(x, ids)
+        assert rel_l2(ro, ref_ro) < 1e-3
+        assert rel_l2(case.gpu_experts(x, ids, w), ref_y) < TOL_LAYER
+        assert case.status() == 0
+    finally:
+        case.close()

@@ -239,3 +239,46 @@ def test_dispatch_known_answer():
     slot = rng.integers(0, 37, 5000)
     order, sorted_slot, inv, offs = O.dispatch(slot, 37)
     assert (order == np.argsort(slot, kind="stable")).all()
+
+
+def test_k2_expert_forward_uses_the_k2_planes():
+    """The oracle's expert forward at K = 2 multiplies by exactly the planes `reconstruct` gives at K = 2 (whose digests
+    are pinned above): a dense f64 restatement over those planes gives the same row."""
+    H, I = 256, 128
+    rec = O.exl3_synth_record(0x1234, H, I, 1.0, 0.02, K=2)
+    g = O.exl3_geometry(H, I, 2)
+    assert g.len[0] == (H // 16) * (I // 16) * 64          # 16 K int16 per tile
+    rng = np.random.default_rng(4)
+    x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(rng.standard_normal((1, H)).astype(np.float32)))
+    ids = np.zeros((1, 1), np.int32)
+    w = np.ones((1, 1), np.float32)
+    y = O.layer(O.BANK_EXL3_K2, H, I, 1, 1, {0: rec}, x, ids, w, limit=10.0)
+
+    def f16(seg, n):
+        return rec[g.off[seg]:g.off[seg] + 2 * n].view(np.float16).astype(np.float64)
+
+    def plane(seg, n_in, n_out):
+        code = rec[g.off[seg]:g.off[seg] + g.len[seg]].view(np.int16)
+        return O.reconstruct(code, n_in // 16, n_out // 16, 2).view(np.float16).astype(np.float64).reshape(n_in, n_out)
+
+    def had(v):
+        v = v.reshape(-1, 128).copy()
+        h = 1
+        while h < 128:
+            v = v.reshape(-1, 128 // (2 * h), 2, h)
+            a, b = v[:, :, 0, :].copy(), v[:, :, 1, :].copy()
+            v[:, :, 0, :], v[:, :, 1, :] = a + b, a - b
+            v = v.reshape(-1, 128)
+            h *= 2
+        return (v / np.sqrt(128.0)).reshape(-1)
+
+    def proj(v, seg, n_in, n_out):
+        return had(had(v * f16(seg + 2, n_in)) @ plane(seg, n_in, n_out)) * f16(seg + 1, n_out)
+
+    xv = x[0].astype(np.float64)
+    gate, up = proj(xv, 0, H, I), proj(xv, 3, H, I)
+    gate = np.minimum(gate, 10.0)
+    up = np.clip(up, -10.0, 10.0)
+    hmid = gate / (1.0 + np.exp(-gate)) * up
+    ref = proj(hmid, 6, I, H)
+    assert np.abs(y[0] - ref).max() / (np.sqrt((ref * ref).mean()) + 1e-30) < 1e-9
