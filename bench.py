@@ -312,26 +312,21 @@ def main():
     stream = torch.cuda.current_stream()
     sp = stream.cuda_stream
 
-    # where the experts live: contiguous blocks, or dealt out by usage (a histogram of the routed ids of the batches,
-    # summed over the ranks; experts sorted by load and dealt to the ranks in snake order, E / N each)
+    # where the experts live: contiguous blocks, or dealt out by usage: the library's tally counts the routed ids of the
+    # batches on the device, sums them over the ranks, and its planner deals the experts out (most used first, snake order)
     rank_of = [np.arange(E) // (E // world) for _ in range(NL)]
     if world > 1 and args.placement == "usage":
         ids_dev = torch.empty((T, K_TOP), dtype=torch.int32, device=dev)
         w_dev = torch.empty((T, K_TOP), dtype=torch.float32, device=dev)
+        moe.usage_enable(True)
         for l in range(NL):
-            hist = torch.zeros(E, dtype=torch.int64, device=dev)
             for b in range(n_batches):
                 moe.route(l, lgs[b][l].data_ptr(), T, ids_dev.data_ptr(), w_dev.data_ptr(), sp)
-                torch.cuda.synchronize()
-                hist += torch.bincount(ids_dev.reshape(-1).long(), minlength=E)
-            dist.all_reduce(hist)
-            by_load = np.argsort(-hist.cpu().numpy(), kind="stable")
-            ro = np.empty(E, np.uint16)
-            for pos, e in enumerate(by_load):
-                lap, j = divmod(pos, world)
-                ro[e] = j if lap % 2 == 0 else world - 1 - j
+            torch.cuda.synchronize()
+            ro = np.asarray(pkg.plan_placement(moe.usage_read(l, all_ranks=True), world), np.uint16)
             rank_of[l] = ro.astype(np.int64)
             moe.set_placement(l, np.ascontiguousarray(ro).ctypes.data)
+        moe.usage_enable(False)
     owned = [np.nonzero(rank_of[l] == rank)[0] for l in range(NL)]
     n_local = E // world
     logical, stride = moe.record_bytes()

@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define MLXS_MOE_ABI 2026112505
+#define MLXS_MOE_ABI 2026112507
 
 /* refusals (the names mirror the reference's refusal sets: src/sdk_ext/quant.zig:94-111, src/expert/bank.zig:79-101) */
 enum {
@@ -98,6 +98,15 @@ void mlxs_moe_destroy(mlxs_moe *h);
  * stride records have in an experts.bin */
 int mlxs_moe_record_bytes(const mlxs_moe *h, uint64_t *logical_bytes, uint64_t *record_stride);
 
+/* An EXL3 bank may mix layer widths (the reference's 2.9 bpw DeepSeek bank keeps layers 18-22 at K = 2 inside a K = 3
+ * bank, src/exl3/quant.zig:39-41, 73; src/expert/bank.zig:288-298): the handle's bank kind names the default width,
+ * this call gives one layer its own (bits = 2 or 3) before any of its experts is loaded and re-sizes the layer's HBM
+ * arrays.  mlxs_moe_load_bank applies the manifest's per-layer K by itself. */
+int mlxs_moe_set_layer_bits(mlxs_moe *h, uint32_t layer, uint32_t bits);
+/* one layer's width and record size (equal to mlxs_moe_record_bytes unless the layer's width was changed) */
+int mlxs_moe_layer_record_bytes(const mlxs_moe *h, uint32_t layer, uint32_t *bits, uint64_t *logical_bytes,
+                                uint64_t *record_stride);
+
 /* Replaces the expert source's fill of a slot row (src/sdk_ext/expert.zig:226-264; csrc/q3_lookahead4_exl3.c): one
  * expert's record, in the reference's layout, becomes HBM resident.  `record` is a host pointer (on_device = 0) or a
  * device pointer (1); nbytes >= logical bytes.  Experts outside this rank's shard are accepted and ignored. */
@@ -115,9 +124,15 @@ typedef struct {
     uint64_t hidden, inter, n_experts, n_layers, first_layer;
     uint64_t logical_bytes, record_stride, data_bytes;
     char data_file[64];
+    /* EXL3: narrowest and widest layer of the bank; bank_kind, logical_bytes and record_stride are the widest layer's.
+     * 0 for the FP4 banks. */
+    uint32_t bits_min, bits_max;
 } mlxs_bank_info;
 int mlxs_moe_bank_peek(const char *dir, mlxs_bank_info *out);
 int mlxs_moe_bank_peek_text(const char *manifest_json, mlxs_bank_info *out);
+/* K of every layer of an EXL3 manifest text (v2 peek, src/expert/bank.zig:641-662): writes min(n_layers, cap) widths
+ * and the layer count */
+int mlxs_moe_bank_layer_bits_text(const char *manifest_json, uint32_t *bits_out, uint32_t cap, uint32_t *n_layers_out);
 
 /* the router's noaux_tc correction bias, f32 [n_experts] host, NULL = zeros (src/arch/deepseek_v41/graph.zig:2035) */
 int mlxs_moe_set_router_bias(mlxs_moe *h, uint32_t layer, const float *bias_host);
@@ -201,6 +216,20 @@ int mlxs_moe_ep_init(mlxs_moe *h, const void *id128);
  * residency policy, src/sdk_ext/expert/usage.zig; here the same histogram can balance the ranks' load.) */
 int mlxs_moe_set_placement(mlxs_moe *h, uint32_t layer, const uint16_t *rank_of_expert);
 int mlxs_moe_ep_plan(const int32_t *ids, uint64_t n, uint32_t n_experts, uint32_t world, uint64_t *send_counts);
+
+/* Usage tally (src/sdk_ext/expert/usage.zig:202-224 keeps per-layer per-expert route counts to seed residency; here
+ * the same counts decide which rank holds which expert).  While enabled, every mlxs_moe_route (and so every
+ * mlxs_moe_forward*) adds its ids to the layer's device-side counts: one small kernel per call, nothing read back.
+ * A host that routes elsewhere adds its ids with mlxs_moe_usage_add.  usage_read copies a layer's counts to the host;
+ * with all_ranks != 0 on an expert-parallel handle the ranks' counts are summed first (every rank must call it). */
+int mlxs_moe_usage_enable(mlxs_moe *h, int on);
+int mlxs_moe_usage_add(mlxs_moe *h, uint32_t layer, const void *ids_dev, uint64_t n_ids, void *stream);
+int mlxs_moe_usage_read(mlxs_moe *h, uint32_t layer, uint64_t *counts_host, int all_ranks);
+int mlxs_moe_usage_reset(mlxs_moe *h);
+/* counts -> placement: experts in order of use (most used first, ties to the lower id: Profile.order,
+ * src/sdk_ext/expert/usage.zig:352-366) dealt to the ranks in snake order, n_experts / world per rank, so the ranks'
+ * expected rows come out even under skewed routing.  Pure host arithmetic; feed the result to mlxs_moe_set_placement. */
+int mlxs_moe_plan_placement(const uint64_t *counts, uint32_t n_experts, uint32_t world, uint16_t *rank_of_expert);
 
 #ifdef __cplusplus
 }

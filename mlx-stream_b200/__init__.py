@@ -14,7 +14,7 @@ from pathlib import Path  # noqa: E402
 
 HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "libmlxs_moe.so"
-ABI = 2026112505
+ABI = 2026112507
 
 BANK_EXL3_K3_MUL1, BANK_MXFP4, BANK_NVFP4, BANK_EXL3_K2_MUL1 = 0, 1, 2, 3
 SCORE_SQRTSOFTPLUS, SCORE_SIGMOID, SCORE_SOFTMAX = 0, 1, 2
@@ -30,6 +30,8 @@ EXPORTS = [
     "mlxs_moe_exl3_gemv_noalloc",
     "mlxs_moe_stats_get", "mlxs_moe_profile_enable", "mlxs_moe_profile_read", "mlxs_moe_ep_unique_id", "mlxs_moe_ep_init", "mlxs_moe_ep_plan",
     "mlxs_moe_set_placement", "mlxs_moe_set_router_weight", "mlxs_moe_logits", "mlxs_moe_forward_x",
+    "mlxs_moe_set_layer_bits", "mlxs_moe_layer_record_bytes", "mlxs_moe_bank_layer_bits_text",
+    "mlxs_moe_usage_enable", "mlxs_moe_usage_add", "mlxs_moe_usage_read", "mlxs_moe_usage_reset", "mlxs_moe_plan_placement",
 ]
 
 
@@ -59,7 +61,7 @@ class BankInfo(C.Structure):
     _fields_ = [("bank_kind", C.c_uint32), ("has_sha256", C.c_uint32), ("hidden", C.c_uint64), ("inter", C.c_uint64),
                 ("n_experts", C.c_uint64), ("n_layers", C.c_uint64), ("first_layer", C.c_uint64),
                 ("logical_bytes", C.c_uint64), ("record_stride", C.c_uint64), ("data_bytes", C.c_uint64),
-                ("data_file", C.c_char * 64)]
+                ("data_file", C.c_char * 64), ("bits_min", C.c_uint32), ("bits_max", C.c_uint32)]
 
 
 class MlxsError(RuntimeError):
@@ -86,6 +88,14 @@ def lib():
         L.mlxs_moe_destroy.restype = None
         L.mlxs_moe_record_bytes.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
         L.mlxs_moe_load_expert.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint64, C.c_int]
+        L.mlxs_moe_set_layer_bits.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32]
+        L.mlxs_moe_usage_enable.argtypes = [C.c_void_p, C.c_int]
+        L.mlxs_moe_usage_add.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint64, C.c_void_p]
+        L.mlxs_moe_usage_read.argtypes = [C.c_void_p, C.c_uint32, C.POINTER(C.c_uint64), C.c_int]
+        L.mlxs_moe_usage_reset.argtypes = [C.c_void_p]
+        L.mlxs_moe_plan_placement.argtypes = [C.POINTER(C.c_uint64), C.c_uint32, C.c_uint32, C.POINTER(C.c_uint16)]
+        L.mlxs_moe_layer_record_bytes.argtypes = [C.c_void_p, C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
+        L.mlxs_moe_bank_layer_bits_text.argtypes = [C.c_char_p, C.POINTER(C.c_uint32), C.c_uint32, C.POINTER(C.c_uint32)]
         L.mlxs_moe_load_bank.argtypes = [C.c_void_p, C.c_char_p]
         L.mlxs_moe_bank_peek.argtypes = [C.c_char_p, C.POINTER(BankInfo)]
         L.mlxs_moe_bank_peek_text.argtypes = [C.c_char_p, C.POINTER(BankInfo)]
@@ -143,6 +153,25 @@ def bank_peek(directory=None, text=None):
     return info
 
 
+def plan_placement(counts, world):
+    """Route counts per expert -> the rank of every expert (most used first, dealt to the ranks in snake order)."""
+    n = len(counts)
+    cin = (C.c_uint64 * n)(*[int(c) for c in counts])
+    out = (C.c_uint16 * n)()
+    _check(lib().mlxs_moe_plan_placement(cin, n, world, out))
+    return list(out)
+
+
+def bank_layer_bits(text):
+    """K of every layer of an EXL3 manifest text."""
+    raw = text.encode() if isinstance(text, str) else text
+    n = C.c_uint32()
+    _check(lib().mlxs_moe_bank_layer_bits_text(raw, None, 0, C.byref(n)))
+    out = (C.c_uint32 * n.value)()
+    _check(lib().mlxs_moe_bank_layer_bits_text(raw, out, n.value, C.byref(n)))
+    return list(out)
+
+
 def exl3_gemv_noalloc(code, in_dim, out_dim, xh, rows, z, stream=None):
     """z = xh . W_hat of one code plane with no handle and no allocation (fixed scratch inside the library)."""
     _check(lib().mlxs_moe_exl3_gemv_noalloc(code, in_dim, out_dim, xh, rows, z, stream))
@@ -171,6 +200,30 @@ class MoE:
         a, b = C.c_uint64(), C.c_uint64()
         _check(lib().mlxs_moe_record_bytes(self._h, C.byref(a), C.byref(b)))
         return a.value, b.value
+
+    def usage_enable(self, on=True):
+        """While on, every route / forward call adds its ids to the layer's device-side route counts."""
+        _check(lib().mlxs_moe_usage_enable(self._h, int(on)))
+
+    def usage_add(self, layer, ids_ptr, n_ids, stream=None):
+        _check(lib().mlxs_moe_usage_add(self._h, layer, ids_ptr, n_ids, stream))
+
+    def usage_read(self, layer, all_ranks=False):
+        out = (C.c_uint64 * self.cfg.n_experts)()
+        _check(lib().mlxs_moe_usage_read(self._h, layer, out, int(all_ranks)))
+        return list(out)
+
+    def usage_reset(self):
+        _check(lib().mlxs_moe_usage_reset(self._h))
+
+    def set_layer_bits(self, layer, bits):
+        """EXL3 banks of mixed width: this layer's bits per weight (2 or 3), before its experts are loaded."""
+        _check(lib().mlxs_moe_set_layer_bits(self._h, layer, bits))
+
+    def layer_record_bytes(self, layer):
+        k, a, b = C.c_uint32(), C.c_uint64(), C.c_uint64()
+        _check(lib().mlxs_moe_layer_record_bytes(self._h, layer, C.byref(k), C.byref(a), C.byref(b)))
+        return k.value, a.value, b.value
 
     def load_expert(self, layer, expert, record_ptr, nbytes, on_device=False):
         _check(lib().mlxs_moe_load_expert(self._h, layer, expert, record_ptr, nbytes, int(on_device)))

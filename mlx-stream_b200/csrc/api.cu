@@ -9,6 +9,7 @@
 #include <cstring>
 #include <new>
 #include <string>
+#include <algorithm>
 #include <vector>
 
 #include "../../include/mlxs_moe.h"
@@ -116,7 +117,10 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
             packed[e] = ((uint32_t)L.place_rank[e] << 16) | L.place_slot[e];
         }
         cudaMemcpy(L.place_dev, packed.data(), packed.size() * 4, cudaMemcpyHostToDevice);
+        L.logical_bytes = h->logical_bytes;
+        L.record_stride = h->record_stride;
         if (is_exl3(c->bank_kind)) {
+            L.kbits = d.K;
             if ((rc = h->alloc(&L.gu_code, (size_t)h->e_local * 2 * exl3_code_words(d) * 4))) return bail(rc);
             if ((rc = h->alloc(&L.d_code, (size_t)h->e_local * exl3_code_words(d) * 4))) return bail(rc);
             if ((rc = h->alloc(&L.scales, (size_t)h->e_local * exl3_scales_per_expert(d) * 2))) return bail(rc);
@@ -140,7 +144,8 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
         (rc = h->alloc(&h->tabs.chunk_rows, max_chunks * 4)) || (rc = h->alloc(&h->tabs.group_chunk0, max_chunks * 4)) ||
         (rc = h->alloc(&h->tabs.group_mc, max_chunks * 4)) || (rc = h->alloc(&h->status, 16)) ||
         (rc = h->alloc(&h->blk_cnt, (A / 1024 + 1) * (size_t)c->n_experts * 4)) ||
-        (rc = h->alloc(&h->staging, h->record_stride)) || (rc = h->alloc(&h->x_io, T * H * 2)) ||
+        (rc = h->alloc(&h->staging, is_exl3(c->bank_kind) ? exl3_logical(H, I, 3) : h->logical_bytes)) ||
+        (rc = h->alloc(&h->x_io, T * H * 2)) ||
         (rc = h->alloc(&h->y_io, T * H * 2)) || (rc = h->alloc(&h->logits_io, T * c->n_experts * 4)))
         return bail(rc);
     cudaMemset(h->status, 0, 16);
@@ -219,28 +224,64 @@ extern "C" int mlxs_moe_record_bytes(const mlxs_moe* h, uint64_t* logical_bytes,
     return MLXS_OK;
 }
 
+extern "C" int mlxs_moe_layer_record_bytes(const mlxs_moe* h, uint32_t layer, uint32_t* bits, uint64_t* logical_bytes,
+                                           uint64_t* record_stride) {
+    if (!h) return fail(MLXS_E_ARG, "layer_record_bytes: null handle");
+    if (layer >= h->cfg.n_layers) return fail(MLXS_E_ARG, "layer_record_bytes: layer %u of %u", layer, h->cfg.n_layers);
+    const LayerBank& L = h->layers[layer];
+    if (bits) *bits = is_exl3(h->cfg.bank_kind) ? L.kbits : 4u;
+    if (logical_bytes) *logical_bytes = L.logical_bytes;
+    if (record_stride) *record_stride = L.record_stride;
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_set_layer_bits(mlxs_moe* h, uint32_t layer, uint32_t bits) {
+    if (!h) return fail(MLXS_E_ARG, "set_layer_bits: null handle");
+    const mlxs_moe_config& c = h->cfg;
+    if (layer >= c.n_layers) return fail(MLXS_E_ARG, "set_layer_bits: layer %u of %u", layer, c.n_layers);
+    if (!is_exl3(c.bank_kind)) return fail(MLXS_E_CONFIG, "set_layer_bits: the handle's bank is not EXL3");
+    if (bits != 2 && bits != 3) return fail(MLXS_E_CONFIG, "set_layer_bits: K=%u not implemented by the installed lanes (KNotImplemented)", bits);
+    LayerBank& L = h->layers[layer];
+    if (L.kbits == bits) return MLXS_OK;
+    for (uint32_t e = 0; e < c.n_experts; ++e)
+        if (L.loaded[e]) return fail(MLXS_E_CONFIG, "set_layer_bits: layer %u already holds experts; set the width before loading", layer);
+    CU(cudaSetDevice(c.device));
+    CU(cudaDeviceSynchronize());
+    const Exl3Dims was{c.hidden, c.inter, L.kbits}, now{c.hidden, c.inter, bits};
+    h->release(&L.gu_code, (size_t)h->e_local * 2 * exl3_code_words(was) * 4);
+    h->release(&L.d_code, (size_t)h->e_local * exl3_code_words(was) * 4);
+    int rc;
+    if ((rc = h->alloc(&L.gu_code, (size_t)h->e_local * 2 * exl3_code_words(now) * 4)) ||
+        (rc = h->alloc(&L.d_code, (size_t)h->e_local * exl3_code_words(now) * 4)))
+        return rc;
+    L.kbits = bits;
+    L.logical_bytes = exl3_logical(c.hidden, c.inter, bits);
+    L.record_stride = (L.logical_bytes + 4095) / 4096 * 4096;
+    return MLXS_OK;
+}
+
 extern "C" int mlxs_moe_load_expert(mlxs_moe* h, uint32_t layer, uint32_t expert, const void* record, uint64_t nbytes,
                                     int on_device) {
     if (!h || !record) return fail(MLXS_E_ARG, "load_expert: null argument");
     if (layer >= h->cfg.n_layers) return fail(MLXS_E_ARG, "load_expert: layer %u of %u", layer, h->cfg.n_layers);
     if (expert >= h->cfg.n_experts) return fail(MLXS_E_ARG, "load_expert: expert %u of %u", expert, h->cfg.n_experts);
-    if (nbytes < h->logical_bytes)
-        return fail(MLXS_E_BANK, "load_expert: record has %llu bytes, the bank kind's record is %llu (RecordGeometry)",
-                    (unsigned long long)nbytes, (unsigned long long)h->logical_bytes);
     LayerBank& L = h->layers[layer];
+    if (nbytes < L.logical_bytes)
+        return fail(MLXS_E_BANK, "load_expert: record has %llu bytes, the layer's record is %llu (RecordGeometry)",
+                    (unsigned long long)nbytes, (unsigned long long)L.logical_bytes);
     if (L.place_rank[expert] != h->cfg.ep_rank) return MLXS_OK;  // another rank's shard
     CU(cudaSetDevice(h->cfg.device));
     const uint32_t le = L.place_slot[expert];
     const uint8_t* src = static_cast<const uint8_t*>(record);
     if (!on_device) {
-        CU(cudaMemcpyAsync(h->staging, record, h->logical_bytes, cudaMemcpyHostToDevice, 0));
+        CU(cudaMemcpyAsync(h->staging, record, L.logical_bytes, cudaMemcpyHostToDevice, 0));
         src = h->staging;
     }
     // the expert's entry of the per-expert table: 1 = resident; the FP4 repack may raise it to 3 (see takes_tensor_lane)
     const uint8_t one = 1;
     CU(cudaMemcpyAsync(L.loaded_dev + le, &one, 1, cudaMemcpyHostToDevice, 0));
     if (is_exl3(h->cfg.bank_kind)) {
-        const Exl3Dims d{h->cfg.hidden, h->cfg.inter, exl3_bits(h->cfg.bank_kind)};
+        const Exl3Dims d{h->cfg.hidden, h->cfg.inter, L.kbits};
         CU(launch_exl3_repack(src, d, L.gu_code + (size_t)le * 2 * exl3_code_words(d),
                               L.d_code + (size_t)le * exl3_code_words(d), L.scales + (size_t)le * exl3_scales_per_expert(d), 0));
     } else {
@@ -256,7 +297,7 @@ extern "C" int mlxs_moe_load_expert(mlxs_moe* h, uint32_t layer, uint32_t expert
 }
 
 int mlxs_bank_for_each_record(const char* dir, uint32_t bank_kind, uint64_t H, uint64_t I, uint64_t E, uint64_t n_layers,
-                              uint32_t e_first, uint32_t e_count,
+                              uint32_t e_first, uint32_t e_count, int (*layer_begin)(void* ctx, uint32_t layer, uint32_t bits),
                               int (*sink)(void* ctx, uint32_t layer, uint32_t expert, const void* rec, uint64_t n), void* ctx);
 
 extern "C" int mlxs_moe_set_placement(mlxs_moe* h, uint32_t layer, const uint16_t* rank_of_expert) {
@@ -287,12 +328,15 @@ extern "C" int mlxs_moe_load_bank(mlxs_moe* h, const char* dir) {
     auto sink = [](void* ctx, uint32_t layer, uint32_t expert, const void* rec, uint64_t n) -> int {
         return mlxs_moe_load_expert(static_cast<mlxs_moe*>(ctx), layer, expert, rec, n, 0);
     };
+    auto layer_begin = [](void* ctx, uint32_t layer, uint32_t bits) -> int {
+        return mlxs_moe_set_layer_bits(static_cast<mlxs_moe*>(ctx), layer, bits);
+    };
     // with the default placement only this rank's block of records is read; a custom placement scatters a rank's experts
     // over the file, so every record is visited and load_expert keeps the local ones
     bool custom = false;
     for (const LayerBank& L : h->layers) custom = custom || L.placement_custom;
     return mlxs_bank_for_each_record(dir, c.bank_kind, c.hidden, c.inter, c.n_experts, c.n_layers, custom ? 0 : h->e_first,
-                                     custom ? c.n_experts : h->e_local, sink, h);
+                                     custom ? c.n_experts : h->e_local, layer_begin, sink, h);
 }
 
 extern "C" int mlxs_moe_set_router_bias(mlxs_moe* h, uint32_t layer, const float* bias_host) {
@@ -341,6 +385,80 @@ extern "C" int mlxs_moe_route(mlxs_moe* h, uint32_t layer, const float* logits_d
     CU(launch_router(logits_dev, h->layers[layer].bias, (int)T, (int)c.n_experts, (int)c.top_k, (int)c.scoring,
                      (int)c.norm_topk, c.routed_scale, ids_dev, weights_dev, (cudaStream_t)stream));
     h->stats.route_calls += 1;
+    if (h->usage_on && T)
+        CU(launch_usage_count(ids_dev, (uint64_t)T * c.top_k, c.n_experts, h->layers[layer].usage, (cudaStream_t)stream));
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_usage_enable(mlxs_moe* h, int on) {
+    if (!h) return fail(MLXS_E_ARG, "usage_enable: null handle");
+    CU(cudaSetDevice(h->cfg.device));
+    if (on)
+        for (LayerBank& L : h->layers)
+            if (!L.usage) {
+                int rc = h->alloc(&L.usage, (size_t)h->cfg.n_experts * 8);
+                if (rc) return rc;
+                CU(cudaMemset(L.usage, 0, (size_t)h->cfg.n_experts * 8));
+            }
+    h->usage_on = on != 0;
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_usage_add(mlxs_moe* h, uint32_t layer, const void* ids_dev, uint64_t n_ids, void* stream) {
+    if (!h || (n_ids && !ids_dev)) return fail(MLXS_E_ARG, "usage_add: null argument");
+    if (layer >= h->cfg.n_layers) return fail(MLXS_E_ARG, "usage_add: layer %u of %u", layer, h->cfg.n_layers);
+    if (!h->layers[layer].usage) return fail(MLXS_E_CONFIG, "usage_add: the tally is off (mlxs_moe_usage_enable)");
+    CU(cudaSetDevice(h->cfg.device));
+    CU(launch_usage_count(static_cast<const int32_t*>(ids_dev), n_ids, h->cfg.n_experts, h->layers[layer].usage, (cudaStream_t)stream));
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_usage_read(mlxs_moe* h, uint32_t layer, uint64_t* counts_host, int all_ranks) {
+    if (!h || !counts_host) return fail(MLXS_E_ARG, "usage_read: null argument");
+    if (layer >= h->cfg.n_layers) return fail(MLXS_E_ARG, "usage_read: layer %u of %u", layer, h->cfg.n_layers);
+    LayerBank& L = h->layers[layer];
+    if (!L.usage) return fail(MLXS_E_CONFIG, "usage_read: the tally is off (mlxs_moe_usage_enable)");
+    CU(cudaSetDevice(h->cfg.device));
+    CU(cudaDeviceSynchronize());
+    const size_t n = h->cfg.n_experts;
+    if (all_ranks && h->cfg.ep_world > 1) {
+        // the sum goes through a scratch copy, so this rank's own counts keep counting from where they were
+        unsigned long long* tmp = nullptr;
+        CU(cudaMalloc(&tmp, n * 8));
+        cudaMemcpy(tmp, L.usage, n * 8, cudaMemcpyDeviceToDevice);
+        int rc = mlxs_ep_allreduce_u64(h, tmp, n, 0);
+        cudaError_t ce = cudaStreamSynchronize(0);
+        if (!rc && ce == cudaSuccess) ce = cudaMemcpy(counts_host, tmp, n * 8, cudaMemcpyDeviceToHost);
+        cudaFree(tmp);
+        if (rc) return rc;
+        CU(ce);
+        return MLXS_OK;
+    }
+    CU(cudaMemcpy(counts_host, L.usage, n * 8, cudaMemcpyDeviceToHost));
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_usage_reset(mlxs_moe* h) {
+    if (!h) return fail(MLXS_E_ARG, "usage_reset: null handle");
+    CU(cudaSetDevice(h->cfg.device));
+    CU(cudaDeviceSynchronize());
+    for (LayerBank& L : h->layers)
+        if (L.usage) CU(cudaMemset(L.usage, 0, (size_t)h->cfg.n_experts * 8));
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_plan_placement(const uint64_t* counts, uint32_t n_experts, uint32_t world, uint16_t* rank_of_expert) {
+    if (!counts || !rank_of_expert) return fail(MLXS_E_ARG, "plan_placement: null argument");
+    if (world == 0 || n_experts == 0 || n_experts % world || world > 65535)
+        return fail(MLXS_E_CONFIG, "plan_placement: %u ranks do not shard %u experts", world, n_experts);
+    std::vector<uint32_t> order(n_experts);
+    for (uint32_t e = 0; e < n_experts; ++e) order[e] = e;
+    std::stable_sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) { return counts[a] > counts[b]; });
+    // snake deal: ranks 0..W-1, then W-1..0, ...: each rank takes one expert of every band of W, alternating ends
+    for (uint32_t i = 0; i < n_experts; ++i) {
+        const uint32_t band = i / world, pos = i % world;
+        rank_of_expert[order[i]] = (uint16_t)((band & 1u) ? world - 1 - pos : pos);
+    }
     return MLXS_OK;
 }
 
@@ -399,6 +517,7 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
     // a token's experts are distinct, so no expert has more rows than the call has tokens
     const bool two_lanes = h->pf_tiles && T >= h->pf_min_rows;
     const uint32_t heavy = two_lanes ? h->pf_min_rows : 0u;
+    h->last_logical = L.logical_bytes;
     {
         StageTimer tm(h, MLXS_STAGE_DISPATCH, st);
         if (A > 2048)
@@ -409,7 +528,7 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
                                h->status, st));
     }
     if (is_exl3(c.bank_kind)) {
-        const Exl3Dims d{c.hidden, c.inter, exl3_bits(c.bank_kind)};
+        const Exl3Dims d{c.hidden, c.inter, L.kbits};
         Exl3Layer EL{L.gu_code, L.d_code, L.scales};
         {
             StageTimer tm(h, MLXS_STAGE_PREP, st);
@@ -595,7 +714,7 @@ extern "C" int mlxs_moe_exl3_gemv(mlxs_moe* h, uint32_t layer, uint32_t expert, 
     CU(cudaSetDevice(c.device));
     cudaStream_t st = (cudaStream_t)stream;
     LayerBank& L = h->layers[layer];
-    const Exl3Dims d{c.hidden, c.inter, exl3_bits(c.bank_kind)};
+    const Exl3Dims d{c.hidden, c.inter, L.kbits};
     const uint32_t le = h->layers[layer].place_slot[expert];
     // rows all belong to one pseudo expert 0 of a one-expert dispatch
     CU(cudaMemsetAsync(h->ids_ws, 0, (size_t)rows * 4, st));
@@ -618,7 +737,7 @@ extern "C" int mlxs_moe_stats_get(mlxs_moe* h, mlxs_moe_stats* out) {
     CU(cudaMemcpy(&s, h->status, 4, cudaMemcpyDeviceToHost));
     h->stats.device_status = s;
     h->stats.distinct_experts_last = hdr[HDR_DISTINCT];
-    h->stats.weight_bytes_last = (uint64_t)hdr[HDR_DISTINCT] * h->logical_bytes;
+    h->stats.weight_bytes_last = (uint64_t)hdr[HDR_DISTINCT] * (h->last_logical ? h->last_logical : h->logical_bytes);
     h->stats.resident_bytes = h->resident;
     *out = h->stats;
     return MLXS_OK;

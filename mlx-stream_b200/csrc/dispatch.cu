@@ -208,4 +208,27 @@ cudaError_t launch_dispatch(const int32_t* ids, uint32_t A, uint32_t E, const ui
     return cudaGetLastError();
 }
 
+// ---- usage tally: a block's ids are counted in shared memory first, then its non-zero counts join the layer's ----
+__global__ void __launch_bounds__(256) usage_count_kernel(const int32_t* __restrict__ ids, uint64_t n, uint32_t E,
+                                                          unsigned long long* __restrict__ usage) {
+    extern __shared__ uint32_t hist[];
+    for (uint32_t e = threadIdx.x; e < E; e += blockDim.x) hist[e] = 0;
+    __syncthreads();
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        const int32_t v = ids[i];
+        if (v >= 0 && (uint32_t)v < E) atomicAdd(&hist[v], 1u);   // ids out of range are the dispatch's to report
+    }
+    __syncthreads();
+    for (uint32_t e = threadIdx.x; e < E; e += blockDim.x)
+        if (hist[e]) atomicAdd(&usage[e], (unsigned long long)hist[e]);
+}
+
+cudaError_t launch_usage_count(const int32_t* ids, uint64_t n, uint32_t E, unsigned long long* usage, cudaStream_t st) {
+    if (n == 0) return cudaSuccess;
+    const uint64_t want = (n + 2047) / 2048;
+    const uint32_t grid = (uint32_t)(want < 148 ? want : 148);
+    usage_count_kernel<<<grid, 256, E * sizeof(uint32_t), st>>>(ids, n, E, usage);
+    return cudaGetLastError();
+}
+
 }  // namespace mlxs

@@ -32,6 +32,7 @@ struct NcclApi {
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
     ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*GroupStart)() = nullptr;
@@ -52,12 +53,13 @@ NcclApi* nccl_api() {
             MLXS_SYM(CommDestroy, "ncclCommDestroy");
             MLXS_SYM(GetErrorString, "ncclGetErrorString");
             MLXS_SYM(AllGather, "ncclAllGather");
+            MLXS_SYM(AllReduce, "ncclAllReduce");
             MLXS_SYM(Send, "ncclSend");
             MLXS_SYM(Recv, "ncclRecv");
             MLXS_SYM(GroupStart, "ncclGroupStart");
             MLXS_SYM(GroupEnd, "ncclGroupEnd");
 #undef MLXS_SYM
-            if (!api.GetUniqueId || !api.CommInitRank || !api.CommDestroy || !api.AllGather || !api.Send || !api.Recv ||
+            if (!api.GetUniqueId || !api.CommInitRank || !api.CommDestroy || !api.AllGather || !api.AllReduce || !api.Send || !api.Recv ||
                 !api.GroupStart || !api.GroupEnd || !api.GetErrorString)
                 api.lib = nullptr;
         }
@@ -328,6 +330,14 @@ void mlxs_ep_destroy(mlxs_moe* h) {
     if (h->ep->all_counts_host) cudaFreeHost(h->ep->all_counts_host);
     delete h->ep;
     h->ep = nullptr;
+}
+
+int mlxs_ep_allreduce_u64(mlxs_moe* h, unsigned long long* buf_dev, size_t n, cudaStream_t st) {
+    EpState* ep = h->ep;
+    NcclApi* api = nccl_api();
+    if (!ep || !api) return mlxs_fail(MLXS_E_EP, "expert parallelism is not initialised (mlxs_moe_ep_init)");
+    NC(api->AllReduce(buf_dev, buf_dev, n, ncclUint64, ncclSum, ep->comm, st));
+    return MLXS_OK;
 }
 
 int mlxs_ep_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, uint32_t T, void* ro,

@@ -170,6 +170,7 @@ struct GemvParams {
     uint32_t* status;
     uint32_t n_stages;
     uint32_t stage_bytes, w_bytes;
+    uint32_t max_parts;          // cap on the parts of the sum (4; a tuning knob for measurements, MLXS_K_PARTS)
     // The sum over the inputs is always taken in `parts` equal parts, folded left in part order: a fixed function of the
     // shape, so a row's bits do not depend on the batch around it.  Calls with fewer work items than CTAs spread an
     // item's parts over 2 or 4 CTAs: each leaves its parts here and the last to arrive folds them and runs the epilogue.
@@ -178,7 +179,6 @@ struct GemvParams {
 };
 
 // flags: 1 = first stage of a part of the sum, 2 = last stage of a part, 4 = last stage of this CTA's share of the item
-// Only `item` and `flags` (with the chunk count in bits 8..) are read every stage, the rest at the end of a part.
 struct StageMeta { int32_t item; uint32_t flags, mc, kt0, chunk0, expert, nb, part; };
 
 // one pipeline stage (KT k-tiles) of one warp's 16-column tile, MC chunks of activations
@@ -226,7 +226,8 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
     __syncthreads();
     const uint32_t n_items = P.t.header[HDR_NGROUPS] * P.n_blocks;
     // parts of the sum (shape only), and over how many CTAs an item's parts are spread (this call's item count)
-    const uint32_t LP = P.nkt % (4 * KT) == 0 ? 4u : (P.nkt % (2 * KT) == 0 ? 2u : 1u);
+    uint32_t LP = P.nkt % (4 * KT) == 0 ? 4u : (P.nkt % (2 * KT) == 0 ? 2u : 1u);
+    LP = LP < P.max_parts ? LP : P.max_parts;
     const uint32_t part_kt = P.nkt / LP;
     uint32_t NP = 1;
     if (P.ks_scratch && n_items)
@@ -236,12 +237,13 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
     if (warp == NCW) {
         // ---------------- producer warp: one lane issues every copy ----------------
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t s = 0, ph = 0;     // ring slot and phase
+            const uint32_t np_mask = NP - 1, np_shift = NP == 4 ? 2u : (NP == 2 ? 1u : 0u);
             bool ok = true;
             while (ok) {
                 const uint32_t unit = atomicAdd(&P.t.header[P.counter_idx], 1u);
                 const bool last = unit >= n_items * NP;
-                const uint32_t item = unit / NP, share = unit % NP;
+                const uint32_t item = unit >> np_shift, share = unit & np_mask;
                 uint32_t g = 0, nb = 0, chunk0 = 0, mc = 0, expert = 0;
                 if (!last) {
                     g = item / P.n_blocks; nb = item % P.n_blocks;
@@ -250,17 +252,20 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
                 const uint32_t* wsrc = P.code + (size_t)expert * P.expert_stride_words +
                                        (size_t)nb * P.nkt * P.kt_stride_words;
                 const uint32_t k_begin = share * share_kt, k_end = last ? k_begin + 1 : k_begin + share_kt;
-                for (uint32_t kt0 = k_begin; kt0 < k_end; kt0 += KT, ++it) {
-                    const uint32_t s = it % NS, ph = (it / NS) & 1u;
+                // k_begin is a multiple of the part length: the place inside a part advances with the stages
+                uint32_t part = share * (LP / NP), in_part = 0;
+                for (uint32_t kt0 = k_begin; kt0 < k_end; kt0 += KT, s = (s + 1 == NS) ? (ph ^= 1u, 0u) : s + 1) {
                     if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, &s_abort, 128)) {
                         if (!s_abort) atomicMax(P.status, (uint32_t)ST_WAIT_EMPTY);
                         s_abort = 1; ok = false; break;
                     }
                     meta[s].item = last ? -1 : (int32_t)item;
                     meta[s].kt0 = kt0; meta[s].chunk0 = chunk0; meta[s].mc = mc; meta[s].expert = expert; meta[s].nb = nb;
-                    meta[s].part = kt0 / part_kt;
-                    meta[s].flags = (kt0 % part_kt == 0 ? 1u : 0u) | ((kt0 + KT) % part_kt == 0 ? 2u : 0u) |
-                                    (kt0 + KT >= k_end ? 4u : 0u) | (mc << 8);
+                    meta[s].part = part;
+                    const bool part_ends = in_part + KT == part_kt;
+                    meta[s].flags = (in_part == 0 ? 1u : 0u) | (part_ends ? 2u : 0u) | (kt0 + KT >= k_end ? 4u : 0u);
+                    in_part = part_ends ? 0u : in_part + KT;
+                    part += part_ends ? 1u : 0u;
                     if (last) { mbar_arrive(&full_bar[s]); ok = false; break; }
                     uint8_t* dst = ring + (size_t)s * P.stage_bytes;
                     mbar_expect_tx(&full_bar[s], P.w_bytes + mc * NPROJ * KT * A_TILE_WORDS * 4);
@@ -294,16 +299,16 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
         if (!ok) { if (!s_abort) atomicMax(P.status, (uint32_t)ST_WAIT_FULL); s_abort = 1; }
         return ok;
     };
-    for (uint32_t it = 0;; ++it) {
-        const uint32_t s = it % NS, ph = (it / NS) & 1u;
+    // ring slot and its phase advance by increment-and-wrap (the ring depth is a run-time value: no division per stage)
+    for (uint32_t s = 0, ph = 0;; s = (s + 1 == NS) ? (ph ^= 1u, 0u) : s + 1) {
         if (!mbar_wait_bounded(&full_bar[s], ph, &s_abort)) {
             if (!s_abort) atomicMax(P.status, (uint32_t)ST_WAIT_FULL);
             s_abort = 1;
             break;
         }
-        const uint2 hot = *reinterpret_cast<const uint2*>(&meta[s]);   // item, flags | chunk count << 8
-        if ((int32_t)hot.x < 0) break;
-        const uint32_t flags = hot.y, stage_mc = hot.y >> 8;
+        const StageMeta m = meta[s];
+        if (m.item < 0) break;
+        const uint32_t flags = m.flags, stage_mc = m.mc;
         if (flags & 1u) {
 #pragma unroll
             for (int a = 0; a < GROUP_CHUNKS; ++a)
@@ -319,8 +324,6 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
         else if (stage_mc == 2) gemv_stage<NPROJ, KSTRIDE, KB, 2>(wt, at, wi, wj, lp, p, acc);
         else if (stage_mc == 3) gemv_stage<NPROJ, KSTRIDE, KB, 3>(wt, at, wi, wj, lp, p, acc);
         else gemv_stage<NPROJ, KSTRIDE, KB, 4>(wt, at, wi, wj, lp, p, acc);
-        StageMeta m;
-        if (flags & 2u) m = meta[s];       // the slot may be refilled once this warp has arrived below
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[s]);
         if (!(flags & 2u)) continue;
@@ -464,6 +467,8 @@ static cudaError_t launch_gemv(int nproj, int epi, int kbits, GemvParams& P, int
     const size_t smem = zs_bytes + (size_t)ns * P.stage_bytes;
     cudaError_t e;
     const int ctas = per_sm * sm_count;
+    static const int k_parts = tune_env("MLXS_K_PARTS", 4, 1, 4);
+    P.max_parts = (uint32_t)k_parts;
 #define MLXS_LAUNCH(NP, EP, KS, KBITS)                                                                            \
     do {                                                                                                         \
         e = cudaFuncSetAttribute(exl3_gemv_kernel<NP, EP, KS, KBITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \

@@ -125,6 +125,7 @@ struct Fp4Params {
     size_t expert_stride;        // bytes per expert in that stream
     const float* gscale;         // NVFP4: [E][3] global scales, else null
     uint32_t n_blocks, n_stages_k;  // out / 128, in / 128
+    uint32_t max_parts;          // cap on the parts of the sum (4; a tuning knob for measurements, MLXS_K_PARTS)
     const uint32_t* xa;          // [chunk][in/32][128] u32
     DispatchTables t;
     uint32_t counter_idx;
@@ -240,7 +241,8 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
     __syncthreads();
     const uint32_t n_items = P.t.header[HDR_NGROUPS] * P.n_blocks;
     const uint32_t xa_chunk_words = (NPROJ == 2 ? P.H : P.I) / 32 * F4_XA_SB_WORDS;
-    const uint32_t LP = P.n_stages_k % 4 == 0 ? 4u : (P.n_stages_k % 2 == 0 ? 2u : 1u);   // parts of the sum (shape only)
+    uint32_t LP = P.n_stages_k % 4 == 0 ? 4u : (P.n_stages_k % 2 == 0 ? 2u : 1u);   // parts of the sum (shape only)
+    LP = LP < P.max_parts ? LP : P.max_parts;
     const uint32_t part_stages = P.n_stages_k / LP;
     uint32_t NP = 1;   // CTAs an item's parts are spread over (this call's item count)
     if (P.ks_scratch && n_items)
@@ -249,12 +251,13 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
 
     if (warp == NCW) {
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t s = 0, ph = 0;     // ring slot and phase
+            const uint32_t np_mask = NP - 1, np_shift = NP == 4 ? 2u : (NP == 2 ? 1u : 0u);
             bool ok = true;
             while (ok) {
                 const uint32_t unit = atomicAdd(&P.t.header[P.counter_idx], 1u);
                 const bool last = unit >= n_items * NP;
-                const uint32_t item = unit / NP, share = unit % NP;
+                const uint32_t item = unit >> np_shift, share = unit & np_mask;
                 uint32_t g = 0, nb = 0, chunk0 = 0, mc = 0, expert = 0;
                 if (!last) {
                     g = item / P.n_blocks; nb = item % P.n_blocks;
@@ -262,17 +265,19 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
                 }
                 const uint8_t* wsrc = P.w + (size_t)expert * P.expert_stride + (size_t)nb * P.n_stages_k * P.w_bytes;
                 const uint32_t ks_begin = share * share_stages, ks_end = last ? ks_begin + 1 : ks_begin + share_stages;
-                for (uint32_t ks = ks_begin; ks < ks_end; ++ks, ++it) {
-                    const uint32_t s = it % NS, ph = (it / NS) & 1u;
+                uint32_t part = share * (LP / NP), in_part = 0;
+                for (uint32_t ks = ks_begin; ks < ks_end; ++ks, s = (s + 1 == NS) ? (ph ^= 1u, 0u) : s + 1) {
                     if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, &s_abort, 128)) {
                         if (!s_abort) atomicMax(P.status, (uint32_t)ST_WAIT_EMPTY);
                         s_abort = 1; ok = false; break;
                     }
                     meta[s].item = last ? -1 : (int32_t)item;
                     meta[s].ks = ks; meta[s].chunk0 = chunk0; meta[s].mc = mc; meta[s].expert = expert; meta[s].nb = nb;
-                    meta[s].part = ks / part_stages;
-                    meta[s].flags = (ks % part_stages == 0 ? 1u : 0u) | ((ks + 1) % part_stages == 0 ? 2u : 0u) |
-                                    (ks + 1 >= ks_end ? 4u : 0u) | (mc << 8);
+                    meta[s].part = part;
+                    const bool part_ends = in_part + 1 == part_stages;
+                    meta[s].flags = (in_part == 0 ? 1u : 0u) | (part_ends ? 2u : 0u) | (ks + 1 >= ks_end ? 4u : 0u) | (mc << 8);
+                    in_part = part_ends ? 0u : in_part + 1;
+                    part += part_ends ? 1u : 0u;
                     if (last) { mbar_arrive(&full_bar[s]); ok = false; break; }
                     uint8_t* dst = ring + (size_t)s * P.stage_bytes;
                     mbar_expect_tx(&full_bar[s], P.w_bytes + mc * 4 * F4_XA_SB_WORDS * 4);
@@ -299,8 +304,8 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
         if (!ok) { if (!s_abort) atomicMax(P.status, (uint32_t)ST_WAIT_FULL); s_abort = 1; }
         return ok;
     };
-    for (uint32_t it = 0;; ++it) {
-        const uint32_t s = it % NS, ph = (it / NS) & 1u;
+    // ring slot and its phase advance by increment-and-wrap (the ring depth is a run-time value: no division per stage)
+    for (uint32_t s = 0, ph = 0;; s = (s + 1 == NS) ? (ph ^= 1u, 0u) : s + 1) {
         if (!mbar_wait_bounded(&full_bar[s], ph, &s_abort)) {
             if (!s_abort) atomicMax(P.status, (uint32_t)ST_WAIT_FULL);
             s_abort = 1;
@@ -446,6 +451,8 @@ cudaError_t launch_fp4_gemv(const Fp4GemvArgs& a, int down, cudaStream_t st) {
     P.H = a.H; P.I = a.I; P.xa_d = a.xa_d; P.out = a.ro; P.out_bf16 = a.ro_bf16; P.limit = a.limit; P.status = a.status;
     P.ks_scratch = a.ks_scratch; P.ks_count = a.ks_count;
     P.stage_bytes = P.w_bytes + F4_GROUP * 4 * F4_XA_SB_WORDS * 4;
+    static const int k_parts = f4_tune_env("MLXS_K_PARTS", 4, 1, 4);
+    P.max_parts = (uint32_t)k_parts;
     static const int gu_ctas = f4_tune_env("MLXS_F4_GU_CTAS", 2, 1, 2), dn_ctas = f4_tune_env("MLXS_F4_DN_CTAS", 3, 1, 3);
     const int per_sm = down ? dn_ctas : gu_ctas;
     const uint32_t zs_bytes = (uint32_t)(nproj * F4_GROUP * F4_CHUNK * F4_ZS_STRIDE * sizeof(float));

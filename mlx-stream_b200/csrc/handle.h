@@ -23,10 +23,14 @@ struct LayerBank {
     float* f4_gscale = nullptr;                  // NVFP4 [E_local][3]
     uint8_t* loaded_dev = nullptr;  // [E_local] per local slot: 1 = loaded (bit 1: see takes_tensor_lane)
     std::vector<uint8_t> loaded;    // [E] by expert id, host copy
+    // EXL3: this layer's bits per weight and record size (a bank may mix widths; mlxs_moe_set_layer_bits)
+    uint32_t kbits = 3;
+    uint64_t logical_bytes = 0, record_stride = 0;
     // where each expert lives: rank and local slot (contiguous blocks unless mlxs_moe_set_placement changed it)
     std::vector<uint16_t> place_rank, place_slot;
     uint32_t* place_dev = nullptr;  // [E] rank << 16 | slot
     bool placement_custom = false;
+    unsigned long long* usage = nullptr;  // [E] route counts (mlxs_moe_usage_enable), or null
     float* bias = nullptr;          // [E] or null
     __nv_bfloat16* router_w = nullptr;  // [E, H] bf16 or null (logits supplied by the caller)
     __nv_bfloat16 *sh_w1 = nullptr, *sh_w3 = nullptr, *sh_w2 = nullptr;
@@ -37,6 +41,8 @@ struct mlxs_moe {
     int sm_count = 0;
     uint32_t e_local = 0, e_first = 0;
     uint64_t logical_bytes = 0, record_stride = 0;
+    bool usage_on = false;
+    uint64_t last_logical = 0;  // record size of the layer the last expert call ran
     std::vector<LayerBank> layers;
     std::vector<void*> allocs;
     uint64_t resident = 0;
@@ -94,6 +100,16 @@ struct mlxs_moe {
         *p = static_cast<T*>(q);
         return 0;
     }
+    // gives back one allocation of alloc() (a layer whose width changed before its load)
+    template <class T>
+    void release(T** p, size_t n_bytes) {
+        if (!*p) return;
+        for (size_t i = 0; i < allocs.size(); ++i)
+            if (allocs[i] == static_cast<void*>(*p)) { allocs[i] = allocs.back(); allocs.pop_back(); break; }
+        cudaFree(*p);
+        resident -= n_bytes;
+        *p = nullptr;
+    }
 };
 
 
@@ -120,3 +136,5 @@ int mlxs_ep_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t
 int mlxs_ep_combined(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, const float* weights_dev,
                      uint32_t T, const float* shared, void* y_dev, cudaStream_t st);
 void mlxs_ep_destroy(mlxs_moe* h);
+// sum of a u64 array over the ranks, in place (expert-parallel handles)
+int mlxs_ep_allreduce_u64(mlxs_moe* h, unsigned long long* buf_dev, size_t n, cudaStream_t st);

@@ -50,6 +50,9 @@ cudaError_t launch_dispatch_large(const int32_t* ids, uint32_t A, uint32_t E, co
                                   uint32_t chunk_rows, uint32_t group_chunks, uint32_t heavy, uint32_t* blk_cnt,
                                   uint32_t* status, cudaStream_t st);
 
+// usage tally: usage[e] += number of ids equal to e
+cudaError_t launch_usage_count(const int32_t* ids, uint64_t n, uint32_t E, unsigned long long* usage, cudaStream_t st);
+
 // ---- EXL3 ----
 struct Exl3Layer {            // one layer's resident bank, in the kernels' layout
     const uint32_t* gu_code;  // [E][I/128][H/16][2][192] u32: per 128-wide output block, per k-tile, gate | up tiles

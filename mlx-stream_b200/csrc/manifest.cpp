@@ -200,9 +200,13 @@ struct Record { uint64_t offset = 0; std::string sha256; bool present = false; }
 struct Bank {
     mlxs_bank_info info{};
     std::vector<Record> records;  // [layer][expert]
+    // EXL3 only: every layer's K, record size and place in the sidecar (a bank may mix widths)
+    std::vector<uint32_t> layer_bits;
+    std::vector<uint64_t> layer_logical, layer_stride, layer_base;
 };
 
-uint64_t exl3_logical(uint64_t H, uint64_t I) { return 3 * ((H / 16) * (I / 16) * 96) + 6 * H + 6 * I; }
+// src/expert/bank.zig:116-141: three code planes of 16x16 tiles at 32 K bytes each, six f16 scale vectors
+uint64_t exl3_logical(uint64_t H, uint64_t I, uint64_t K) { return 3 * ((H / 16) * (I / 16) * 32 * K) + 6 * H + 6 * I; }
 
 int parse_exl3(const JVal& m, Bank& b) {
     // src/exl3/quant.zig:174-197 (claims) and src/expert/bank.zig:253-324 (adoptV2), field by field
@@ -232,7 +236,6 @@ int parse_exl3(const JVal& m, Bank& b) {
     const JVal* layers = m.get("layers");
     if (!layers || layers->kind != JVal::Arr || layers->arr.size() != L)
         return mlxs_fail(MLXS_E_MANIFEST, "v2: %zu layer entries != dims.n_layers %llu", layers ? layers->arr.size() : 0, (unsigned long long)L);
-    const uint64_t logical = exl3_logical(H, I), stride = (logical + 4095) / 4096 * 4096;
     static const char* proj[3] = {"gate_proj", "up_proj", "down_proj"};
     static const char* part[3] = {"code", "rout", "rin"};
     uint64_t base = 0;
@@ -240,7 +243,8 @@ int parse_exl3(const JVal& m, Bank& b) {
         const JVal& t = layers->arr[li];
         uint64_t ln = 0, K = 0, rb = 0, lb = 0, bo = 0;
         if (!geti(&t, "layer", ln) || ln != li) return mlxs_fail(MLXS_E_MANIFEST, "v2: layer entry %zu names layer %llu", li, (unsigned long long)ln);
-        if (!geti(&t, "K", K) || K != 3) return mlxs_fail(MLXS_E_MANIFEST, "v2: layer %zu K %llu not implemented by the installed lanes", li, (unsigned long long)K);
+        if (!geti(&t, "K", K) || (K != 3 && K != 2)) return mlxs_fail(MLXS_E_MANIFEST, "v2: layer %zu K %llu not implemented by the installed lanes", li, (unsigned long long)K);
+        const uint64_t logical = exl3_logical(H, I, K), stride = (logical + 4095) / 4096 * 4096;
         const JVal* segs = t.get("segments");
         if (!segs || segs->kind != JVal::Arr || segs->arr.size() != 9) return mlxs_fail(MLXS_E_MANIFEST, "v2: layer %zu has no 9-segment table", li);
         uint64_t off = 0;
@@ -258,12 +262,12 @@ int parse_exl3(const JVal& m, Bank& b) {
                     return mlxs_fail(MLXS_E_MANIFEST, "v2: segment %s: %s", got.c_str(),
                                      !known_p ? "an unknown projection" : !known_t ? "an unknown tensor" : "out of order");
                 }
-                const uint64_t len = j == 0 ? (in / 16) * (out / 16) * 96 : (j == 1 ? out * 2 : in * 2);
+                const uint64_t len = j == 0 ? (in / 16) * (out / 16) * 32 * K : (j == 1 ? out * 2 : in * 2);
                 if (gets(&s, "dtype") != (j == 0 ? "I16" : "F16")) return mlxs_fail(MLXS_E_MANIFEST, "v2: segment %s: its dtype", want.c_str());
                 const JVal* shp = s.get("shape");
                 bool shape_ok = shp && shp->kind == JVal::Arr;
                 if (shape_ok) {
-                    if (j == 0) shape_ok = shp->arr.size() == 3 && shp->arr[0].u == in / 16 && shp->arr[1].u == out / 16 && shp->arr[2].u == 48;
+                    if (j == 0) shape_ok = shp->arr.size() == 3 && shp->arr[0].u == in / 16 && shp->arr[1].u == out / 16 && shp->arr[2].u == 16 * K;
                     else shape_ok = shp->arr.size() == 1 && shp->arr[0].u == (j == 1 ? out : in);
                 }
                 if (!shape_ok) return mlxs_fail(MLXS_E_MANIFEST, "v2: segment %s: its shape", want.c_str());
@@ -274,13 +278,21 @@ int parse_exl3(const JVal& m, Bank& b) {
             }
         }
         if (!geti(&t, "record_bytes", rb) || !geti(&t, "logical_bytes", lb) || rb != stride || lb != logical)
-            return mlxs_fail(MLXS_E_MANIFEST, "v2: layer %zu segment table / record size differs from the v2 geometry for K=3", li);
+            return mlxs_fail(MLXS_E_MANIFEST, "v2: layer %zu segment table / record size differs from the v2 geometry for K=%llu", li, (unsigned long long)K);
         if (!geti(&t, "base_offset", bo) || bo != base) return mlxs_fail(MLXS_E_MANIFEST, "v2: layer %zu base_offset %llu != %llu", li, (unsigned long long)bo, (unsigned long long)base);
+        b.layer_bits.push_back((uint32_t)K);
+        b.layer_logical.push_back(logical);
+        b.layer_stride.push_back(stride);
+        b.layer_base.push_back(base);
         base += E * stride;
     }
-    b.info.bank_kind = MLXS_BANK_EXL3_K3_MUL1;
+    uint32_t kmin = 8, kmax = 0;
+    for (uint32_t k : b.layer_bits) { kmin = k < kmin ? k : kmin; kmax = k > kmax ? k : kmax; }
+    b.info.bank_kind = kmax == 3 ? MLXS_BANK_EXL3_K3_MUL1 : MLXS_BANK_EXL3_K2_MUL1;
+    b.info.bits_min = kmin; b.info.bits_max = kmax;
     b.info.hidden = H; b.info.inter = I; b.info.n_experts = E; b.info.n_layers = L; b.info.first_layer = 0;
-    b.info.logical_bytes = logical; b.info.record_stride = stride; b.info.data_bytes = base;
+    b.info.logical_bytes = exl3_logical(H, I, kmax); b.info.record_stride = (b.info.logical_bytes + 4095) / 4096 * 4096;
+    b.info.data_bytes = base;
     // sidecar / records / parity: required for a load, absent from a trimmed description
     const JVal* scd = m.get("sidecar");
     if (scd) {
@@ -302,7 +314,7 @@ int parse_exl3(const JVal& m, Bank& b) {
             Record& dst = b.records[rl * E + re];
             if (dst.present) return mlxs_fail(MLXS_E_MANIFEST, "v2: record (%llu,%llu) duplicated", (unsigned long long)rl, (unsigned long long)re);
             if (!geti(&r, "sidecar_offset", so) || !geti(&r, "record_bytes", rb) || !geti(&r, "logical_bytes", lb) ||
-                so != rl * E * stride + re * stride || rb != stride || lb != logical)
+                so != b.layer_base[rl] + re * b.layer_stride[rl] || rb != b.layer_stride[rl] || lb != b.layer_logical[rl])
                 return mlxs_fail(MLXS_E_MANIFEST, "v2: record (%llu,%llu) offset/size differs from its layer geometry", (unsigned long long)rl, (unsigned long long)re);
             dst.sha256 = gets(&r, "sha256");
             if (dst.sha256.size() != 64) return mlxs_fail(MLXS_E_MANIFEST, "v2: record (%llu,%llu) has no sha256", (unsigned long long)rl, (unsigned long long)re);
@@ -438,16 +450,31 @@ extern "C" int mlxs_moe_bank_peek(const char* dir, mlxs_bank_info* out) {
     return MLXS_OK;
 }
 
+extern "C" int mlxs_moe_bank_layer_bits_text(const char* manifest_json, uint32_t* bits_out, uint32_t cap, uint32_t* n_layers_out) {
+    if (!manifest_json || !n_layers_out || (cap && !bits_out)) return mlxs_fail(MLXS_E_ARG, "bank_layer_bits_text: null argument");
+    Bank b;
+    int rc = parse_text(manifest_json, "manifest", b);
+    if (rc) return rc;
+    if (b.layer_bits.empty()) return mlxs_fail(MLXS_E_MANIFEST, "bank_layer_bits_text: not an EXL3 manifest");
+    *n_layers_out = (uint32_t)b.layer_bits.size();
+    for (uint32_t i = 0; i < cap && i < b.layer_bits.size(); ++i) bits_out[i] = b.layer_bits[i];
+    return MLXS_OK;
+}
+
 // mlxs_moe_load_bank's host half: opens the bank, checks it against the handle's shape and hands every record of
-// layers [0, n_layers) to `sink` (the caller keeps only its shard).
+// layers [0, n_layers) to `sink` (the caller keeps only its shard).  For an EXL3 bank `layer_begin` hears every
+// layer's K before the layer's first record.
 int mlxs_bank_for_each_record(const char* dir, uint32_t bank_kind, uint64_t H, uint64_t I, uint64_t E, uint64_t n_layers,
-                              uint32_t e_first, uint32_t e_count,
+                              uint32_t e_first, uint32_t e_count, int (*layer_begin)(void* ctx, uint32_t layer, uint32_t bits),
                               int (*sink)(void* ctx, uint32_t layer, uint32_t expert, const void* rec, uint64_t n), void* ctx) {
     Bank b;
     int rc = open_bank(dir, b);
     if (rc) return rc;
     const mlxs_bank_info& bi = b.info;
-    if (bi.bank_kind != bank_kind) return mlxs_fail(MLXS_E_MANIFEST, "load_bank: the bank at %s is kind %u, the handle is kind %u", dir, bi.bank_kind, bank_kind);
+    const bool exl3 = !b.layer_bits.empty();
+    const bool handle_exl3 = bank_kind == MLXS_BANK_EXL3_K3_MUL1 || bank_kind == MLXS_BANK_EXL3_K2_MUL1;
+    if (exl3 ? !handle_exl3 : bi.bank_kind != bank_kind)
+        return mlxs_fail(MLXS_E_MANIFEST, "load_bank: the bank at %s is kind %u, the handle is kind %u", dir, bi.bank_kind, bank_kind);
     if (bi.hidden != H || bi.inter != I || bi.n_experts != E || bi.n_layers != n_layers)
         return mlxs_fail(MLXS_E_MANIFEST, "load_bank: dims %llu/%llu/%llu experts/%llu layers != the handle's %llu/%llu/%llu/%llu (DimsNotImplemented)",
                          (unsigned long long)bi.hidden, (unsigned long long)bi.inter, (unsigned long long)bi.n_experts, (unsigned long long)bi.n_layers,
@@ -464,8 +491,11 @@ int mlxs_bank_for_each_record(const char* dir, uint32_t bank_kind, uint64_t H, u
     const char* vs = getenv("MLXS_VERIFY_SHA256");
     const bool verify = vs ? atoi(vs) != 0 : bi.data_bytes <= (1ull << 30);  // small banks always, large ones on request
     // the v2 (EXL3) digests cover the padded record, the FP4 banks' cover the record's own bytes
-    std::vector<uint8_t> buf(bi.bank_kind == MLXS_BANK_EXL3_K3_MUL1 ? bi.record_stride : bi.logical_bytes);
-    for (uint64_t l = 0; l < n_layers && !rc; ++l)
+    std::vector<uint8_t> buf;
+    for (uint64_t l = 0; l < n_layers && !rc; ++l) {
+        const uint64_t logical = exl3 ? b.layer_logical[l] : bi.logical_bytes;
+        buf.resize(exl3 ? b.layer_stride[l] : bi.logical_bytes);
+        if (exl3 && layer_begin && (rc = layer_begin(ctx, (uint32_t)l, b.layer_bits[l]))) break;
         for (uint64_t e = e_first; e < (uint64_t)e_first + e_count && !rc; ++e) {
             const Record& r = b.records[l * E + e];
             if (!r.present) { rc = mlxs_fail(MLXS_E_MANIFEST, "load_bank: record (%llu,%llu) missing", (unsigned long long)l, (unsigned long long)e); break; }
@@ -481,8 +511,9 @@ int mlxs_bank_for_each_record(const char* dir, uint32_t bank_kind, uint64_t H, u
                 s.update(buf.data(), buf.size());
                 if (s.hex() != r.sha256) { rc = mlxs_fail(MLXS_E_MANIFEST, "load_bank: record (%llu,%llu) sha256 mismatch (RecordSha256)", (unsigned long long)l, (unsigned long long)e); break; }
             }
-            rc = sink(ctx, (uint32_t)l, (uint32_t)e, buf.data(), bi.logical_bytes);
+            rc = sink(ctx, (uint32_t)l, (uint32_t)e, buf.data(), logical);
         }
+    }
     close(fd);
     return rc;
 }

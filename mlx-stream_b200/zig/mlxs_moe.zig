@@ -2,7 +2,7 @@
 //! is the compiled, tested statement of the same ABI).  One declaration per C entry point, same order.
 const std = @import("std");
 
-pub const abi_expected: i32 = 2026112505;
+pub const abi_expected: i32 = 2026112507;
 
 pub const Moe = opaque {};
 
@@ -51,6 +51,8 @@ pub extern fn mlxs_moe_last_error() [*:0]const u8;
 pub extern fn mlxs_moe_create(cfg: *const Config, out: **Moe) c_int;
 pub extern fn mlxs_moe_destroy(h: ?*Moe) void;
 pub extern fn mlxs_moe_record_bytes(h: *const Moe, logical: ?*u64, stride: ?*u64) c_int;
+pub extern fn mlxs_moe_set_layer_bits(h: *Moe, layer: u32, bits: u32) c_int;
+pub extern fn mlxs_moe_layer_record_bytes(h: *const Moe, layer: u32, bits: ?*u32, logical: ?*u64, stride: ?*u64) c_int;
 pub extern fn mlxs_moe_load_expert(h: *Moe, layer: u32, expert: u32, record: *const anyopaque, nbytes: u64, on_device: c_int) c_int;
 pub extern fn mlxs_moe_load_bank(h: *Moe, dir: [*:0]const u8) c_int;
 pub const BankInfo = extern struct {
@@ -65,9 +67,12 @@ pub const BankInfo = extern struct {
     record_stride: u64,
     data_bytes: u64,
     data_file: [64]u8,
+    bits_min: u32,
+    bits_max: u32,
 };
 pub extern fn mlxs_moe_bank_peek(dir: [*:0]const u8, out: *BankInfo) c_int;
 pub extern fn mlxs_moe_bank_peek_text(manifest_json: [*:0]const u8, out: *BankInfo) c_int;
+pub extern fn mlxs_moe_bank_layer_bits_text(manifest_json: [*:0]const u8, bits_out: ?[*]u32, cap: u32, n_layers_out: *u32) c_int;
 pub extern fn mlxs_moe_set_router_bias(h: *Moe, layer: u32, bias_host: ?[*]const f32) c_int;
 pub extern fn mlxs_moe_set_router_weight(h: *Moe, layer: u32, w_gate_bf16: *const anyopaque, on_device: c_int) c_int;
 pub extern fn mlxs_moe_logits(h: *Moe, layer: u32, x_dev: *const anyopaque, t: u32, logits_dev: [*]f32, stream: ?*anyopaque) c_int;
@@ -93,6 +98,11 @@ pub extern fn mlxs_moe_profile_read(h: *Moe, out: *Profile) c_int;
 pub extern fn mlxs_moe_ep_unique_id(id128_out: *[128]u8) c_int;
 pub extern fn mlxs_moe_ep_init(h: *Moe, id128: *const [128]u8) c_int;
 pub extern fn mlxs_moe_ep_plan(ids: [*]const i32, n: u64, n_experts: u32, world: u32, send_counts: [*]u64) c_int;
+pub extern fn mlxs_moe_usage_enable(h: *Moe, on: c_int) c_int;
+pub extern fn mlxs_moe_usage_add(h: *Moe, layer: u32, ids_dev: *const anyopaque, n_ids: u64, stream: ?*anyopaque) c_int;
+pub extern fn mlxs_moe_usage_read(h: *Moe, layer: u32, counts_host: [*]u64, all_ranks: c_int) c_int;
+pub extern fn mlxs_moe_usage_reset(h: *Moe) c_int;
+pub extern fn mlxs_moe_plan_placement(counts: [*]const u64, n_experts: u32, world: u32, rank_of_expert: [*]u16) c_int;
 pub extern fn mlxs_moe_set_placement(h: *Moe, layer: u32, rank_of_expert: [*]const u16) c_int;
 
 pub const Error = error{ Arg, Config, Cuda, Bank, NotLoaded, TooManyTokens, DeviceStatus, Manifest, Ep };

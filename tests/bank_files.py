@@ -13,21 +13,27 @@ import numpy as np
 import oracle_lib as O
 
 
-def exl3_manifest(H, I, E, L, records_sha=None):
-    g = O.exl3_geometry(H, I)
+def exl3_manifest(H, I, E, L, records_sha=None, bits=None):
+    """bits: K per layer (default 3 everywhere); the sidecar places a layer after the layers before it."""
+    bits = list(bits) if bits is not None else [3] * L
+    geoms = [O.exl3_geometry(H, I, k) for k in bits]
+    base = [0]
+    for g in geoms:
+        base.append(base[-1] + E * int(g.record_bytes))
     names = ["gate_proj", "up_proj", "down_proj"]
     parts = ["code", "rout", "rin"]
     layers = []
     for l in range(L):
         segs = []
+        g = geoms[l]
         for p in range(3):
             n_in, n_out = (I, H) if p == 2 else (H, I)
-            shapes = [[n_in // 16, n_out // 16, 48], [n_out], [n_in]]
+            shapes = [[n_in // 16, n_out // 16, 16 * bits[l]], [n_out], [n_in]]
             for j in range(3):
                 segs.append({"component": f"{names[p]}.{parts[j]}", "dtype": "I16" if j == 0 else "F16",
                              "shape": shapes[j], "offset": int(g.off[3 * p + j]), "length": int(g.len[3 * p + j])})
-        layers.append({"layer": l, "K": 3, "record_bytes": int(g.record_bytes), "logical_bytes": int(g.logical_bytes),
-                       "base_offset": l * E * int(g.record_bytes), "segments": segs})
+        layers.append({"layer": l, "K": bits[l], "record_bytes": int(g.record_bytes), "logical_bytes": int(g.logical_bytes),
+                       "base_offset": base[l], "segments": segs})
     m = {"format": "mtplx-expert-manifest-v2",
          "quantization": {"mode": "exl3", "codebook": "mul1", "codebook_multiplier": 2212286765,
                           "tile": {"size": 16, "layout": "exl3-tensor-core", "bitstream": "msb-first-swap16"},
@@ -35,28 +41,29 @@ def exl3_manifest(H, I, E, L, records_sha=None):
                           "scales": {"rin": "exl3.suh", "rout": "exl3.svh"}},
          "dims": {"hidden": H, "inter": I, "n_experts": E, "n_layers": L}, "layers": layers}
     if records_sha is not None:
-        m["sidecar"] = {"file": "experts.bin", "alignment": 4096, "size": L * E * int(g.record_bytes)}
-        m["records"] = [{"layer": l, "expert": e, "sidecar_offset": (l * E + e) * int(g.record_bytes),
-                         "record_bytes": int(g.record_bytes), "logical_bytes": int(g.logical_bytes),
+        m["sidecar"] = {"file": "experts.bin", "alignment": 4096, "size": base[L]}
+        m["records"] = [{"layer": l, "expert": e, "sidecar_offset": base[l] + e * int(geoms[l].record_bytes),
+                         "record_bytes": int(geoms[l].record_bytes), "logical_bytes": int(geoms[l].logical_bytes),
                          "sha256": records_sha[l * E + e]} for l in range(L) for e in range(E)]
         m["parity"] = {"all_pass": True}
     return m
 
 
-def write_exl3_bank(directory, H, I, E, L, record_of):
-    """record_of(layer, expert) -> uint8 record (padded to the record stride)."""
+def write_exl3_bank(directory, H, I, E, L, record_of, bits=None):
+    """record_of(layer, expert) -> uint8 record (padded to the record stride); bits: K per layer."""
     directory = Path(directory)
-    g = O.exl3_geometry(H, I)
+    bits = list(bits) if bits is not None else [3] * L
     shas = []
     with open(directory / "experts.bin", "wb") as f:
         for l in range(L):
+            g = O.exl3_geometry(H, I, bits[l])
             for e in range(E):
                 rec = np.zeros(g.record_bytes, np.uint8)
                 r = record_of(l, e)
                 rec[:r.size] = r
                 shas.append(hashlib.sha256(rec.tobytes()).hexdigest())
                 f.write(rec.tobytes())
-    (directory / "expert-manifest-v2.json").write_text(json.dumps(exl3_manifest(H, I, E, L, shas), separators=(",", ":")))
+    (directory / "expert-manifest-v2.json").write_text(json.dumps(exl3_manifest(H, I, E, L, shas, bits), separators=(",", ":")))
 
 
 def fp4_manifest(H, I, E, L, nv, first=1, shas=None):

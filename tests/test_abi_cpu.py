@@ -76,6 +76,27 @@ def test_ep_plan_counts():
     assert "outside" in pkg.last_error()
 
 
+def test_plan_placement_deals_by_use():
+    """Most used first (ties to the lower id, as Profile.order, src/sdk_ext/expert/usage.zig:352-366), dealt to the
+    ranks in snake order: every rank gets n_experts / world experts and the ranks' loads come out close."""
+    import numpy as np
+    pkg = load_package()
+    assert pkg.plan_placement([5, 9, 9, 1, 0, 7, 3, 3], 2) == [0, 0, 1, 1, 0, 1, 0, 1]
+    #   order: 1 2 5 0 6 7 3 4 -> ranks 0 1 1 0 0 1 1 0
+    rng = np.random.default_rng(3)
+    for E, W in ((384, 8), (256, 4), (16, 16)):
+        counts = (1e4 * (1.0 + np.arange(E)) ** -1.1).astype(np.int64)[rng.permutation(E)]
+        place = np.asarray(pkg.plan_placement(counts, W))
+        assert all((place == r).sum() == E // W for r in range(W))
+        loads = np.array([counts[place == r].sum() for r in range(W)])
+        blocks = np.array([counts[r * (E // W):(r + 1) * (E // W)].sum() for r in range(W)])
+        assert loads.max() - loads.min() <= counts.max()
+        assert E == W or loads.max() <= blocks.max()
+    with pytest.raises(pkg.MlxsError) as ei:
+        pkg.plan_placement([1, 2, 3], 2)
+    assert "do not shard" in ei.value.msg
+
+
 def test_zig_binding_declares_every_header_entry():
     """The Zig host file is shipped as source (no Zig compiler in the build image): at least keep it complete."""
     import re

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 HERE = Path(__file__).resolve().parent
 
 
-@pytest.mark.parametrize("placement", ["contiguous", "interleaved"])
+@pytest.mark.parametrize("placement", ["contiguous", "interleaved", "usage"])
 def test_two_rank_exchange_matches_oracle(placement):
     import torch
     if torch.cuda.device_count() < 2:

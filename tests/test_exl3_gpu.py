@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 
 import oracle_lib as O
-from moe_cases import Exl3Case, max_err_over_rms, rel_l2
+from moe_cases import Exl3Case, Exl3K2Case, max_err_over_rms, rel_l2
 
 pytestmark = pytest.mark.gpu
 GOLD = Path(__file__).resolve().parent / "golden"
@@ -254,6 +254,97 @@ def test_load_bank_from_reference_format_files(tmp_path):
     finally:
         a.close()
         b.close()
+
+
+def test_bank_of_mixed_layer_widths(tmp_path):
+    """A bank whose layers differ in K (the reference's 2.9 bpw DeepSeek banks, src/exl3/quant.zig:39-41, 73): the
+    load gives every layer its own width from the manifest, and each layer computes what a one-width handle computes
+    over the same records, bit for bit."""
+    import bank_files
+    import torch
+    H, I, E, k, T = 512, 256, 4, 2, 9
+    bits = [3, 2, 3]
+    cases = [(Exl3K2Case if b == 2 else Exl3Case)(H, I, E, k, seed=40 + l, shared=False, max_tokens=16) for l, b in enumerate(bits)]
+    pkg = cases[0].pkg
+    cfg = pkg.make_config(H, I, E, k, n_layers=3, bank_kind=pkg.BANK_EXL3_K3_MUL1, act=pkg.ACT_SWIGLU_CLAMPED, act_limit=10.0,
+                          scoring=pkg.SCORE_SQRTSOFTPLUS, norm_topk=True, routed_scale=1.5, shared_expert=False,
+                          combine=pkg.COMBINE_F32, max_tokens=16, device=0)
+    moe = pkg.MoE(cfg)
+    try:
+        bank_files.write_exl3_bank(tmp_path, H, I, E, 3, lambda l, e: cases[l].records[e], bits)
+        resident_before = moe.stats().resident_bytes
+        moe.load_bank(tmp_path)
+        assert [moe.layer_record_bytes(l)[0] for l in range(3)] == bits
+        g3, g2 = O.exl3_geometry(H, I, 3), O.exl3_geometry(H, I, 2)
+        assert moe.layer_record_bytes(1)[1:] == (g2.logical_bytes, g2.record_bytes)
+        assert moe.record_bytes() == (g3.logical_bytes, g3.record_bytes)
+        # the narrower layer gave HBM back: one third of its three code planes
+        assert resident_before - moe.stats().resident_bytes == E * 3 * (H // 16) * (I // 16) * 32
+        for l, c in enumerate(cases):
+            x, logits = c.inputs(T, seed=70 + l)
+            xd, lg = c.to_dev_bf16(x), torch.from_numpy(logits).to(c.dev)
+            y = torch.empty((T, H), dtype=torch.bfloat16, device=c.dev)
+            moe.forward(l, xd.data_ptr(), lg.data_ptr(), T, y.data_ptr(), None)
+            torch.cuda.synchronize()
+            assert (y.float().cpu().numpy() == c.gpu_forward(x, logits)).all(), l
+            ids, w = c.cpu_route(logits)
+            assert rel_l2(y.float().cpu().numpy(), c.cpu_layer(x, ids, w)) < 1e-2
+        assert moe.stats().device_status == 0
+        # a layer that holds experts keeps its width; unknown widths are refused by name
+        with pytest.raises(pkg.MlxsError) as ei:
+            moe.set_layer_bits(0, 2)
+        assert "already holds experts" in ei.value.msg
+        with pytest.raises(pkg.MlxsError) as ei:
+            moe.set_layer_bits(0, 4)
+        assert "KNotImplemented" in ei.value.msg
+        # a K = 3 record offered to the K = 2 layer's neighbour is fine, a K = 2 record to a K = 3 layer is too short
+        rec2 = cases[1].records[0]
+        with pytest.raises(pkg.MlxsError) as ei:
+            moe.load_expert(0, 0, rec2.ctypes.data, int(g2.logical_bytes), on_device=False)
+        assert "RecordGeometry" in ei.value.msg
+    finally:
+        moe.close()
+        for c in cases:
+            c.close()
+
+
+def test_usage_tally_counts_routes_per_layer():
+    """The route tally (the reference counts routes per layer and expert, src/sdk_ext/expert/usage.zig:202-224): off
+    by default, counts every routed id of route / forward while on, per layer, and adds ids a host routed elsewhere."""
+    import torch
+    case = Exl3Case(512, 256, 16, 4, seed=8, shared=False, max_tokens=4096)
+    try:
+        moe, E, k = case.moe, case.E, case.k
+        with pytest.raises(case.pkg.MlxsError) as ei:
+            moe.usage_read(0)
+        assert "tally is off" in ei.value.msg
+        moe.usage_enable(True)
+        want = np.zeros(E, np.int64)
+        for T, seed in ((1, 1), (37, 2), (3000, 3)):
+            x, logits = case.inputs(T, seed=seed)
+            logits[:, 3] += 2.0                      # a popular expert
+            ids, _ = case.gpu_route(logits)
+            want += np.bincount(ids.reshape(-1), minlength=E)
+        x, logits = case.inputs(9, seed=4)
+        case.gpu_forward(x, logits)                  # forward routes too
+        want += np.bincount(case.cpu_route(logits)[0].reshape(-1), minlength=E)
+        assert moe.usage_read(0) == list(want) and moe.usage_read(0, all_ranks=True) == list(want)
+        # ids from elsewhere, out-of-range ones ignored (the dispatch reports those)
+        ext = np.array([0, 5, 5, 15, 16, -1, 5], np.int32)
+        d = torch.from_numpy(ext).to(case.dev)
+        moe.usage_add(0, d.data_ptr(), ext.size, None)
+        want += np.bincount(ext[(ext >= 0) & (ext < E)], minlength=E)
+        assert moe.usage_read(0) == list(want)
+        place = case.pkg.plan_placement(moe.usage_read(0), 4)
+        assert sorted(place.count(r) for r in range(4)) == [4, 4, 4, 4] and place[3] == 0   # the hottest expert leads
+        moe.usage_enable(False)
+        case.gpu_route(logits)
+        assert moe.usage_read(0) == list(want)       # off: nothing is counted, the counts stay readable
+        moe.usage_reset()
+        assert sum(moe.usage_read(0)) == 0
+        assert case.status() == 0
+    finally:
+        case.close()
 
 
 def test_forward_is_capturable_in_a_cuda_graph():

@@ -73,6 +73,36 @@ def test_v2_full_manifest_records_and_parity():
     assert "plain file name" in ei.value.msg
 
 
+def test_v2_bank_of_mixed_layer_widths():
+    """The reference's 2.9 bpw banks keep some layers at K = 2 inside a K = 3 bank (src/exl3/quant.zig:73,
+    src/expert/bank.zig:288-298): per-layer record sizes, each layer after the ones before it."""
+    pkg = load_package()
+    H, I, E = 512, 256, 4
+    bits = [3, 2, 2, 3]
+    m = bank_files.exl3_manifest(H, I, E, 4, ["cd" * 32] * 16, bits)
+    info = pkg.bank_peek(text=json.dumps(m))
+    g3, g2 = bank_files.O.exl3_geometry(H, I, 3), bank_files.O.exl3_geometry(H, I, 2)
+    assert (info.bank_kind, info.bits_min, info.bits_max) == (pkg.BANK_EXL3_K3_MUL1, 2, 3)
+    assert info.logical_bytes == g3.logical_bytes and info.data_bytes == 2 * E * (g3.record_bytes + g2.record_bytes)
+    assert pkg.bank_layer_bits(json.dumps(m)) == bits
+    all2 = bank_files.exl3_manifest(H, I, E, 2, None, [2, 2])
+    info = pkg.bank_peek(text=json.dumps(all2))
+    assert (info.bank_kind, info.bits_min, info.bits_max, info.logical_bytes) == (pkg.BANK_EXL3_K2_MUL1, 2, 2, g2.logical_bytes)
+    # a K = 2 layer that claims the K = 3 record size, and a layer placed as if the one before it were K = 3
+    bad = json.loads(json.dumps(m)); bad["layers"][1]["record_bytes"] = int(g3.record_bytes)
+    with pytest.raises(pkg.MlxsError) as ei:
+        pkg.bank_peek(text=json.dumps(bad))
+    assert "geometry for K=2" in ei.value.msg
+    bad = json.loads(json.dumps(m)); bad["layers"][2]["base_offset"] = 2 * E * int(g3.record_bytes)
+    with pytest.raises(pkg.MlxsError) as ei:
+        pkg.bank_peek(text=json.dumps(bad))
+    assert "layer 2 base_offset" in ei.value.msg
+    bad = json.loads(json.dumps(m)); bad["layers"][3]["K"] = 1
+    with pytest.raises(pkg.MlxsError) as ei:
+        pkg.bank_peek(text=json.dumps(bad))
+    assert "layer 3 K 1 not implemented" in ei.value.msg
+
+
 @pytest.mark.parametrize("nv", [False, True])
 def test_fp4_manifests(nv):
     pkg = load_package()
