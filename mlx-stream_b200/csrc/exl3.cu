@@ -178,13 +178,15 @@ struct GemvParams {
     uint32_t* ks_count;          // [CTAs] arrivals per item, zero between launches
 };
 
-// flags: 1 = first stage of a part of the sum, 2 = last stage of a part, 4 = last stage of this CTA's share of the item
+// flags: 1 = first stage of a part of the sum, 2 = last stage of a part, 4 = last stage of this CTA's share of the item;
+// bits 16.. = sub-stages (of KT k-tiles each) this ring slot carries
 struct StageMeta { int32_t item; uint32_t flags, mc, kt0, chunk0, expert, nb, part; };
 
 // one pipeline stage (KT k-tiles) of one warp's 16-column tile, MC chunks of activations
 template <int NPROJ, int KSTRIDE, int KB, int MC>
-__device__ __forceinline__ void gemv_stage(const uint32_t* __restrict__ wt, const uint2* __restrict__ at, uint32_t wi,
-                                           uint32_t wj, uint32_t lp, uint32_t p, float (&acc)[GROUP_CHUNKS][4]) {
+__device__ __forceinline__ void gemv_stage(const uint32_t* __restrict__ wt, const uint2* __restrict__ at, uint32_t mt_stride,
+                                           uint32_t wi, uint32_t wj, uint32_t lp, float (&acc)[GROUP_CHUNKS][4]) {
+    // at: this projection's KT activation tiles of the first chunk (B-fragment order), the next chunk's mt_stride uint2 on
 #pragma unroll
     for (int kt = 0; kt < KT; ++kt) {
         const uint32_t lo = wt[kt * KSTRIDE + wi], hi = wt[kt * KSTRIDE + wj];
@@ -194,10 +196,19 @@ __device__ __forceinline__ void gemv_stage(const uint32_t* __restrict__ wt, cons
         const uint32_t a[4] = {b[0], b[2], b[1], b[3]};
 #pragma unroll
         for (int mt = 0; mt < MC; ++mt) {
-            const uint2 xv = at[((mt * NPROJ + p) * KT + kt) * 32];
+            const uint2 xv = at[mt * mt_stride + kt * 32];
             mma_f16(acc[mt], a, xv.x, xv.y);
         }
     }
+}
+
+// SUB sub-stages of one ring slot, unrolled
+template <int NPROJ, int KSTRIDE, int KB, int MC, int SUB>
+__device__ __forceinline__ void gemv_slot(const uint32_t* __restrict__ wt, const uint2* __restrict__ at, uint32_t mt_stride,
+                                          uint32_t wi, uint32_t wj, uint32_t lp, float (&acc)[GROUP_CHUNKS][4]) {
+#pragma unroll
+    for (int u = 0; u < SUB; ++u)
+        gemv_stage<NPROJ, KSTRIDE, KB, MC>(wt + u * KT * KSTRIDE, at + u * KT * 32, mt_stride, wi, wj, lp, acc);
 }
 
 // KSTRIDE = words per k-tile of the block stream (8 tiles x 8 KB words per projection present), KB = bits per weight
@@ -252,9 +263,16 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
                 const uint32_t* wsrc = P.code + (size_t)expert * P.expert_stride_words +
                                        (size_t)nb * P.nkt * P.kt_stride_words;
                 const uint32_t k_begin = share * share_kt, k_end = last ? k_begin + 1 : k_begin + share_kt;
+                // One barrier round trip serves `sub` sub-stages of KT k-tiles: the most (up to 3; 1 for rows in 3 or 4 chunks) that divide a part of
+                // the sum and fit the ring slot with this item's chunks of rows.
+                uint32_t sub = 1;
+                if (!last)
+                    for (uint32_t c = mc > 2 ? 1u : 3u; c > 1; --c)
+                        if ((part_kt / KT) % c == 0 && c * (P.w_bytes + mc * NPROJ * KT * A_TILE_WORDS * 4) <= P.stage_bytes) { sub = c; break; }
+                const uint32_t step = sub * KT, xa_bytes = step * A_TILE_WORDS * 4;
                 // k_begin is a multiple of the part length: the place inside a part advances with the stages
                 uint32_t part = share * (LP / NP), in_part = 0;
-                for (uint32_t kt0 = k_begin; kt0 < k_end; kt0 += KT, s = (s + 1 == NS) ? (ph ^= 1u, 0u) : s + 1) {
+                for (uint32_t kt0 = k_begin; kt0 < k_end; kt0 += step, s = (s + 1 == NS) ? (ph ^= 1u, 0u) : s + 1) {
                     if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, &s_abort, 128)) {
                         if (!s_abort) atomicMax(P.status, (uint32_t)ST_WAIT_EMPTY);
                         s_abort = 1; ok = false; break;
@@ -262,19 +280,19 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
                     meta[s].item = last ? -1 : (int32_t)item;
                     meta[s].kt0 = kt0; meta[s].chunk0 = chunk0; meta[s].mc = mc; meta[s].expert = expert; meta[s].nb = nb;
                     meta[s].part = part;
-                    const bool part_ends = in_part + KT == part_kt;
-                    meta[s].flags = (in_part == 0 ? 1u : 0u) | (part_ends ? 2u : 0u) | (kt0 + KT >= k_end ? 4u : 0u);
-                    in_part = part_ends ? 0u : in_part + KT;
+                    const bool part_ends = in_part + step == part_kt;
+                    meta[s].flags = (in_part == 0 ? 1u : 0u) | (part_ends ? 2u : 0u) | (kt0 + step >= k_end ? 4u : 0u) | (sub << 16);
+                    in_part = part_ends ? 0u : in_part + step;
                     part += part_ends ? 1u : 0u;
                     if (last) { mbar_arrive(&full_bar[s]); ok = false; break; }
                     uint8_t* dst = ring + (size_t)s * P.stage_bytes;
-                    mbar_expect_tx(&full_bar[s], P.w_bytes + mc * NPROJ * KT * A_TILE_WORDS * 4);
-                    bulk_g2s(dst, wsrc + (size_t)kt0 * P.kt_stride_words, P.w_bytes, &full_bar[s]);
+                    mbar_expect_tx(&full_bar[s], sub * P.w_bytes + mc * NPROJ * xa_bytes);
+                    bulk_g2s(dst, wsrc + (size_t)kt0 * P.kt_stride_words, sub * P.w_bytes, &full_bar[s]);
                     for (uint32_t m = 0; m < mc; ++m)
                         for (int p = 0; p < NPROJ; ++p)
-                            bulk_g2s(dst + P.w_bytes + (m * NPROJ + p) * (KT * A_TILE_WORDS * 4),
-                                     P.xa + (((size_t)(chunk0 + m) * NPROJ + p) * P.nkt + kt0) * A_TILE_WORDS,
-                                     KT * A_TILE_WORDS * 4, &full_bar[s]);
+                            bulk_g2s(dst + sub * P.w_bytes + (m * NPROJ + p) * xa_bytes,
+                                     P.xa + (((size_t)(chunk0 + m) * NPROJ + p) * P.nkt + kt0) * A_TILE_WORDS, xa_bytes,
+                                     &full_bar[s]);
                 }
             }
             // after a give-up: let copies already issued land before the CTA's shared memory is released
@@ -315,15 +333,28 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
 #pragma unroll
                 for (int c = 0; c < 4; ++c) acc[a][c] = 0.f;
         }
+        // slot: [sub x KT k-tiles of codes][chunk][projection][sub x KT activation tiles]
+        const uint32_t sub = flags >> 16;
         const uint8_t* st = ring + (size_t)s * P.stage_bytes;
         const uint32_t* wt = reinterpret_cast<const uint32_t*>(st) + P.proj_off_words + p * (8u * TW) + j * TW;
-        const uint2* at = reinterpret_cast<const uint2*>(st + P.w_bytes) + lane;
+        const uint2* at = reinterpret_cast<const uint2*>(st + sub * P.w_bytes) + p * (sub * KT * 32) + lane;
+        const uint32_t mt_stride = NPROJ * sub * KT * 32;
         static_assert(GROUP_CHUNKS * CHUNK_ROWS == 16, "the K-split workspace is sized for 16 rows per item");
         static_assert(GROUP_CHUNKS == 4, "the stage dispatch below enumerates the chunk counts");
-        if (stage_mc == 1) gemv_stage<NPROJ, KSTRIDE, KB, 1>(wt, at, wi, wj, lp, p, acc);
-        else if (stage_mc == 2) gemv_stage<NPROJ, KSTRIDE, KB, 2>(wt, at, wi, wj, lp, p, acc);
-        else if (stage_mc == 3) gemv_stage<NPROJ, KSTRIDE, KB, 3>(wt, at, wi, wj, lp, p, acc);
-        else gemv_stage<NPROJ, KSTRIDE, KB, 4>(wt, at, wi, wj, lp, p, acc);
+        // straight-line code per (chunks, sub-stages): rows in 3 or 4 chunks always come one sub-stage per slot
+        if (stage_mc == 1) {
+            if (sub == 2) gemv_slot<NPROJ, KSTRIDE, KB, 1, 2>(wt, at, mt_stride, wi, wj, lp, acc);
+            else if (sub == 3) gemv_slot<NPROJ, KSTRIDE, KB, 1, 3>(wt, at, mt_stride, wi, wj, lp, acc);
+            else gemv_slot<NPROJ, KSTRIDE, KB, 1, 1>(wt, at, mt_stride, wi, wj, lp, acc);
+        } else if (stage_mc == 2) {
+            if (sub == 2) gemv_slot<NPROJ, KSTRIDE, KB, 2, 2>(wt, at, mt_stride, wi, wj, lp, acc);
+            else if (sub == 3) gemv_slot<NPROJ, KSTRIDE, KB, 2, 3>(wt, at, mt_stride, wi, wj, lp, acc);
+            else gemv_slot<NPROJ, KSTRIDE, KB, 2, 1>(wt, at, mt_stride, wi, wj, lp, acc);
+        } else if (stage_mc == 3) {
+            gemv_slot<NPROJ, KSTRIDE, KB, 3, 1>(wt, at, mt_stride, wi, wj, lp, acc);
+        } else {
+            gemv_slot<NPROJ, KSTRIDE, KB, 4, 1>(wt, at, mt_stride, wi, wj, lp, acc);
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[s]);
         if (!(flags & 2u)) continue;
@@ -454,15 +485,21 @@ static int tune_env(const char* name, int dflt, int lo, int hi) {
 static cudaError_t launch_gemv(int nproj, int epi, int kbits, GemvParams& P, int sm_count, cudaStream_t st) {
     const uint32_t zs_bytes = (uint32_t)(nproj * GROUP_CHUNKS * CHUNK_ROWS * ZS_STRIDE * sizeof(float));
     P.w_bytes = KT * P.kt_stride_words * 4;
-    P.stage_bytes = P.w_bytes + GROUP_CHUNKS * nproj * KT * A_TILE_WORDS * 4;
+    const uint32_t stage_one = P.w_bytes + GROUP_CHUNKS * nproj * KT * A_TILE_WORDS * 4;   // one sub-stage, 4 chunks of rows
     // resident CTAs per SM (tunable for experiments: MLXS_GU_CTAS 1..2, MLXS_DN_CTAS 1..3); the shared-memory ring
     // takes what the SM's 227 KB leave per CTA
     static const int gu_ctas = tune_env("MLXS_GU_CTAS", 2, 1, 2), dn_ctas = tune_env("MLXS_DN_CTAS", 3, 1, 3);
     const int per_sm = nproj == 2 ? gu_ctas : dn_ctas;
     const uint32_t budget = (uint32_t)(225 * 1024 / per_sm) - 2048u;
-    uint32_t ns = (budget - zs_bytes) / P.stage_bytes;
-    if (ns > 8) ns = 8;
+    // Ring: two large slots (each carries as many sub-stages of an item as fit, see the producer) rather than many
+    // small ones: the barrier round trip per slot is what the consumers pay for.  MLXS_EXL3_RING = n forces n slots of
+    // the largest size that fits.
+    static const int ring_slots = tune_env("MLXS_EXL3_RING", 2, 2, 8);
+    uint32_t ns = (uint32_t)ring_slots;
+    P.stage_bytes = ((budget - zs_bytes) / ns) & ~127u;
+    if (P.stage_bytes < stage_one) { ns = (budget - zs_bytes) / stage_one; P.stage_bytes = stage_one; }
     if (ns < 2) return cudaErrorInvalidValue;
+    if (ns > 8) ns = 8;
     P.n_stages = ns;
     const size_t smem = zs_bytes + (size_t)ns * P.stage_bytes;
     cudaError_t e;

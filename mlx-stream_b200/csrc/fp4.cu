@@ -126,6 +126,7 @@ struct Fp4Params {
     const float* gscale;         // NVFP4: [E][3] global scales, else null
     uint32_t n_blocks, n_stages_k;  // out / 128, in / 128
     uint32_t max_parts;          // cap on the parts of the sum (4; a tuning knob for measurements, MLXS_K_PARTS)
+    uint32_t sub;                // 128-input sub-stages per ring stage (one barrier round trip serves `sub` of them)
     const uint32_t* xa;          // [chunk][in/32][128] u32
     DispatchTables t;
     uint32_t counter_idx;
@@ -167,11 +168,14 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, __half2 s) {
 }
 
 template <int NPROJ, bool NV, int MC>
-__device__ __forceinline__ void fp4_stage(const uint8_t* __restrict__ st, uint32_t w_bytes, uint32_t p, uint32_t j,
-                                          uint32_t lane, const uint32_t* __restrict__ lut, float (&acc)[F4_GROUP][4]) {
+__device__ __forceinline__ void fp4_stage(const uint8_t* __restrict__ st, const uint8_t* __restrict__ xs, uint32_t x_mt_stride,
+                                          uint32_t p, uint32_t j, uint32_t lane, const uint32_t* __restrict__ lut,
+                                          float (&acc)[F4_GROUP][4]) {
+    // st: one 128-input sub-stage of codes and scales; xs: the same sub-stage of the first chunk's rows, the next
+    // chunk's x_mt_stride uint4 further
     const uint32_t* wv = reinterpret_cast<const uint32_t*>(st + (size_t)p * F4_W_STAGE) + (j * 4) * 64 + lane;
     const uint8_t* sc = st + (size_t)NPROJ * F4_W_STAGE + (size_t)p * f4_scale_stage_bytes(NV);
-    const uint4* xv = reinterpret_cast<const uint4*>(st + w_bytes) + lane;
+    const uint4* xv = reinterpret_cast<const uint4*>(xs) + lane;
     const uint32_t g = lane >> 2, c = lane & 3u;
 #pragma unroll
     for (int sb = 0; sb < 4; ++sb) {
@@ -194,7 +198,7 @@ __device__ __forceinline__ void fp4_stage(const uint8_t* __restrict__ st, uint32
         const uint32_t a1[4] = {hx[0], hy[0], hx[1], hy[1]}, a2[4] = {hx[2], hy[2], hx[3], hy[3]};
 #pragma unroll
         for (int mt = 0; mt < MC; ++mt) {
-            const uint4 xq = xv[(mt * 4 + sb) * 32];
+            const uint4 xq = xv[mt * x_mt_stride + sb * 32];
             if (NV) {
                 mma_f16(acc[mt], a1, xq.x, xq.y);
                 mma_f16(acc[mt], a2, xq.z, xq.w);
@@ -207,6 +211,16 @@ __device__ __forceinline__ void fp4_stage(const uint8_t* __restrict__ st, uint32
             }
         }
     }
+}
+
+// SUB sub-stages of one ring slot, unrolled
+template <int NPROJ, bool NV, int MC, int SUB>
+__device__ __forceinline__ void fp4_slot(const uint8_t* __restrict__ st, const uint8_t* __restrict__ xs, uint32_t w_bytes,
+                                         uint32_t x_mt_stride, uint32_t p, uint32_t j, uint32_t lane,
+                                         const uint32_t* __restrict__ lut, float (&acc)[F4_GROUP][4]) {
+#pragma unroll
+    for (int u = 0; u < SUB; ++u)
+        fp4_stage<NPROJ, NV, MC>(st + u * w_bytes, xs + u * (4 * F4_XA_SB_WORDS * 4), x_mt_stride, p, j, lane, lut, acc);
 }
 
 __device__ __forceinline__ float sigmoid_ref(float x) {  // src/arch/mimo_v2/moe.zig:341-344 (MLX's f32 sigmoid)
@@ -266,7 +280,8 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
                 const uint8_t* wsrc = P.w + (size_t)expert * P.expert_stride + (size_t)nb * P.n_stages_k * P.w_bytes;
                 const uint32_t ks_begin = share * share_stages, ks_end = last ? ks_begin + 1 : ks_begin + share_stages;
                 uint32_t part = share * (LP / NP), in_part = 0;
-                for (uint32_t ks = ks_begin; ks < ks_end; ++ks, s = (s + 1 == NS) ? (ph ^= 1u, 0u) : s + 1) {
+                const uint32_t sub = P.sub, xa_sub_bytes = sub * (4 * F4_XA_SB_WORDS * 4);
+                for (uint32_t ks = ks_begin; ks < ks_end; ks += sub, s = (s + 1 == NS) ? (ph ^= 1u, 0u) : s + 1) {
                     if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, &s_abort, 128)) {
                         if (!s_abort) atomicMax(P.status, (uint32_t)ST_WAIT_EMPTY);
                         s_abort = 1; ok = false; break;
@@ -274,18 +289,18 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
                     meta[s].item = last ? -1 : (int32_t)item;
                     meta[s].ks = ks; meta[s].chunk0 = chunk0; meta[s].mc = mc; meta[s].expert = expert; meta[s].nb = nb;
                     meta[s].part = part;
-                    const bool part_ends = in_part + 1 == part_stages;
-                    meta[s].flags = (in_part == 0 ? 1u : 0u) | (part_ends ? 2u : 0u) | (ks + 1 >= ks_end ? 4u : 0u) | (mc << 8);
-                    in_part = part_ends ? 0u : in_part + 1;
+                    const bool part_ends = in_part + sub == part_stages;
+                    meta[s].flags = (in_part == 0 ? 1u : 0u) | (part_ends ? 2u : 0u) | (ks + sub >= ks_end ? 4u : 0u) | (mc << 8);
+                    in_part = part_ends ? 0u : in_part + sub;
                     part += part_ends ? 1u : 0u;
                     if (last) { mbar_arrive(&full_bar[s]); ok = false; break; }
                     uint8_t* dst = ring + (size_t)s * P.stage_bytes;
-                    mbar_expect_tx(&full_bar[s], P.w_bytes + mc * 4 * F4_XA_SB_WORDS * 4);
-                    bulk_g2s(dst, wsrc + (size_t)ks * P.w_bytes, P.w_bytes, &full_bar[s]);
+                    mbar_expect_tx(&full_bar[s], sub * P.w_bytes + mc * xa_sub_bytes);
+                    bulk_g2s(dst, wsrc + (size_t)ks * P.w_bytes, sub * P.w_bytes, &full_bar[s]);
                     for (uint32_t m = 0; m < mc; ++m)
-                        bulk_g2s(dst + P.w_bytes + m * (4 * F4_XA_SB_WORDS * 4),
+                        bulk_g2s(dst + sub * P.w_bytes + m * xa_sub_bytes,
                                  P.xa + (size_t)(chunk0 + m) * xa_chunk_words + (size_t)ks * 4 * F4_XA_SB_WORDS,
-                                 4 * F4_XA_SB_WORDS * 4, &full_bar[s]);
+                                 xa_sub_bytes, &full_bar[s]);
                 }
             }
             if (s_abort) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
@@ -321,8 +336,17 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
                 for (int q = 0; q < 4; ++q) acc[a][q] = 0.f;
         }
         const uint8_t* st = ring + (size_t)s * P.stage_bytes;
-        if (stage_mc == 1) fp4_stage<NPROJ, NV, 1>(st, P.w_bytes, p, j, lane, s_lut, acc);
-        else fp4_stage<NPROJ, NV, 2>(st, P.w_bytes, p, j, lane, s_lut, acc);
+        const uint8_t* xs = st + P.sub * P.w_bytes;
+        const uint32_t x_mt_stride = P.sub * (4 * F4_XA_SB_WORDS / 4);
+        if (P.sub == 2) {
+            if (stage_mc == 1) fp4_slot<NPROJ, NV, 1, 2>(st, xs, P.w_bytes, x_mt_stride, p, j, lane, s_lut, acc);
+            else fp4_slot<NPROJ, NV, 2, 2>(st, xs, P.w_bytes, x_mt_stride, p, j, lane, s_lut, acc);
+        } else {
+            for (uint32_t u = 0; u < P.sub; ++u, st += P.w_bytes, xs += 4 * F4_XA_SB_WORDS * 4) {
+                if (stage_mc == 1) fp4_stage<NPROJ, NV, 1>(st, xs, x_mt_stride, p, j, lane, s_lut, acc);
+                else fp4_stage<NPROJ, NV, 2>(st, xs, x_mt_stride, p, j, lane, s_lut, acc);
+            }
+        }
         F4Meta m;
         if (flags & 2u) m = meta[s];       // the slot may be refilled once this warp has arrived below
         __syncwarp();
@@ -450,13 +474,22 @@ cudaError_t launch_fp4_gemv(const Fp4GemvArgs& a, int down, cudaStream_t st) {
     P.counter_idx = down ? HDR_CTR_DOWN : HDR_CTR_GU;
     P.H = a.H; P.I = a.I; P.xa_d = a.xa_d; P.out = a.ro; P.out_bf16 = a.ro_bf16; P.limit = a.limit; P.status = a.status;
     P.ks_scratch = a.ks_scratch; P.ks_count = a.ks_count;
-    P.stage_bytes = P.w_bytes + F4_GROUP * 4 * F4_XA_SB_WORDS * 4;
     static const int k_parts = f4_tune_env("MLXS_K_PARTS", 4, 1, 4);
     P.max_parts = (uint32_t)k_parts;
     static const int gu_ctas = f4_tune_env("MLXS_F4_GU_CTAS", 2, 1, 2), dn_ctas = f4_tune_env("MLXS_F4_DN_CTAS", 3, 1, 3);
     const int per_sm = down ? dn_ctas : gu_ctas;
     const uint32_t zs_bytes = (uint32_t)(nproj * F4_GROUP * F4_CHUNK * F4_ZS_STRIDE * sizeof(float));
     const uint32_t budget = (uint32_t)(225 * 1024 / per_sm) - 2048u;
+    // One barrier round trip of the ring serves `sub` 128-input sub-stages: the largest of 4, 2, 1 that divides a part
+    // of the sum and still leaves a ring of two slots.
+    static const int sub_max = f4_tune_env("MLXS_F4_SUB", 2, 1, 4);
+    uint32_t lp = P.n_stages_k % 4 == 0 ? 4u : (P.n_stages_k % 2 == 0 ? 2u : 1u);
+    lp = lp < P.max_parts ? lp : P.max_parts;
+    const uint32_t one = P.w_bytes + F4_GROUP * 4 * F4_XA_SB_WORDS * 4;
+    uint32_t sub = (uint32_t)sub_max;
+    while (sub > 1 && ((P.n_stages_k / lp) % sub != 0 || (budget - zs_bytes) / (sub * one) < 2)) sub >>= 1;
+    P.sub = sub;
+    P.stage_bytes = sub * one;
     uint32_t ns = (budget - zs_bytes) / P.stage_bytes;
     if (ns > 8) ns = 8;
     if (ns < 2) return cudaErrorInvalidValue;
