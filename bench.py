@@ -454,7 +454,7 @@ def main():
     if WL["bank"] == "exl3":
         gu_bytes = 2 * code_bytes + 2 * (2 * I + 2 * H)  # one expert's gate + up code and sign/scale vectors
         kname = "exl3_gemv_kernel<2,gate_up>"
-        traffic_ratio = 1.017  # dram read+write / algorithmic bytes of the ncu capture on the small case (profiles/)
+        traffic_ratio = 1.014  # dram read+write / algorithmic bytes of the ncu capture on the small case (profiles/)
     else:
         gu_bytes = 2 * (H * I // 2 + H * I // (16 if WL["bank"] == "nvfp4" else 32))  # gate + up codes and block scales
         kname = "fp4_gemv_kernel<2>"
