@@ -14,17 +14,21 @@
 
 namespace mlxs {
 
-constexpr int SH_WARPS = 8;
+// warps of a CTA (they split the reduction dimension).  The down kernel has 320 row tiles for 148 SMs: with 4 warps
+// and about 100 registers every CTA is resident at once (2-3 per SM) instead of running in two waves.
+constexpr int sh_warps(int mode) { return mode == 0 ? 8 : 4; }
 constexpr int SH_TOK = 64;  // tokens per pass
+constexpr int SH_AHEAD = 2;  // weight chunks in flight per warp
 
 template <int MODE>  // 0: gate/up + activation -> h bf16 [T, N]; 1: down -> out f32 [T, N]
-__global__ void __launch_bounds__(SH_WARPS * 32) shared_kernel(const __nv_bfloat16* __restrict__ x, uint32_t T,
+__global__ void __launch_bounds__(sh_warps(MODE) * 32) shared_kernel(const __nv_bfloat16* __restrict__ x, uint32_t T,
                                                                uint32_t Kdim, uint32_t N,
                                                                const __nv_bfloat16* __restrict__ wa,
                                                                const __nv_bfloat16* __restrict__ wb, float limit,
                                                                __nv_bfloat16* __restrict__ h_out,
                                                                float* __restrict__ f_out) {
     extern __shared__ float red[];  // [SH_WARPS][NW][8 tiles][32 lanes][4]
+    constexpr int SH_WARPS = sh_warps(MODE);
     constexpr int NW = MODE == 0 ? 2 : 1;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, g = lane >> 2, c = lane & 3u;
     const uint32_t row0 = blockIdx.x * 16;
@@ -38,27 +42,59 @@ __global__ void __launch_bounds__(SH_WARPS * 32) shared_kernel(const __nv_bfloat
             for (int i = 0; i < 8; ++i)
 #pragma unroll
                 for (int q = 0; q < 4; ++q) acc[w][i][q] = 0.f;
-        for (uint32_t kc = warp; kc < Kdim / 32; kc += SH_WARPS) {
-            const size_t ko = (size_t)kc * 32 + c * 8;
-            uint4 a_lo[NW], a_hi[NW];
-            a_lo[0] = *reinterpret_cast<const uint4*>(wa + (size_t)(row0 + g) * Kdim + ko);
-            a_hi[0] = *reinterpret_cast<const uint4*>(wa + (size_t)(row0 + g + 8) * Kdim + ko);
-            if (NW == 2) {
-                a_lo[NW - 1] = *reinterpret_cast<const uint4*>(wb + (size_t)(row0 + g) * Kdim + ko);
-                a_hi[NW - 1] = *reinterpret_cast<const uint4*>(wb + (size_t)(row0 + g + 8) * Kdim + ko);
+        // A warp walks its share of the reduction dimension 32 inputs at a time.  The weights come straight from HBM and
+        // are used once, so the loads of the next SH_AHEAD chunks are always in flight (a register ring, statically
+        // indexed) while the current chunk's mma run: with one chunk in flight the kernel was bound by the load latency.
+        const uint32_t nchunk = Kdim / 32;
+        uint4 ring[SH_AHEAD][2 * NW];
+        auto load_chunk = [&](uint4 (&dst)[2 * NW], uint32_t kc) {
+            if (kc < nchunk) {
+                const size_t ko = (size_t)kc * 32 + c * 8;
+                dst[0] = __ldcs(reinterpret_cast<const uint4*>(wa + (size_t)(row0 + g) * Kdim + ko));
+                dst[1] = __ldcs(reinterpret_cast<const uint4*>(wa + (size_t)(row0 + g + 8) * Kdim + ko));
+                if (NW == 2) {
+                    dst[2 * NW - 2] = __ldcs(reinterpret_cast<const uint4*>(wb + (size_t)(row0 + g) * Kdim + ko));
+                    dst[2 * NW - 1] = __ldcs(reinterpret_cast<const uint4*>(wb + (size_t)(row0 + g + 8) * Kdim + ko));
+                }
             }
+        };
+        // the rows of a chunk's token tiles come from L2: they too are loaded one chunk ahead, all eight at once
+        // (predicated, no branch between them)
+        static_assert(SH_AHEAD == 2, "the row buffers alternate with the chunk's place in the weight ring");
+        uint4 xr[2][8];
+        auto load_rows = [&](uint4 (&dst)[8], uint32_t kc) {
+            const size_t ko = (size_t)kc * 32 + c * 8;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                if (i < (int)ntiles) {
-                    const uint32_t tok = t0 + i * 8 + g;
-                    uint4 xb = make_uint4(0, 0, 0, 0);
-                    if (tok < T) xb = *reinterpret_cast<const uint4*>(x + (size_t)tok * Kdim + ko);
+                const uint32_t tok = t0 + i * 8 + g;
+                dst[i] = make_uint4(0, 0, 0, 0);
+                if (kc < nchunk && i < (int)ntiles && tok < T) dst[i] = *reinterpret_cast<const uint4*>(x + (size_t)tok * Kdim + ko);
+            }
+        };
 #pragma unroll
-                    for (int w = 0; w < NW; ++w) {
-                        const uint32_t a1[4] = {a_lo[w].x, a_hi[w].x, a_lo[w].y, a_hi[w].y};
-                        const uint32_t a2[4] = {a_lo[w].z, a_hi[w].z, a_lo[w].w, a_hi[w].w};
-                        mma_bf16(acc[w][i], a1, xb.x, xb.y);
-                        mma_bf16(acc[w][i], a2, xb.z, xb.w);
+        for (int r = 0; r < SH_AHEAD; ++r) load_chunk(ring[r], warp + r * SH_WARPS);
+        load_rows(xr[0], warp);
+        for (uint32_t kc0 = warp; kc0 < nchunk; kc0 += SH_AHEAD * SH_WARPS) {
+#pragma unroll
+            for (int r = 0; r < SH_AHEAD; ++r) {
+                const uint32_t kc = kc0 + r * SH_WARPS;
+                if (kc < nchunk) {
+                    uint4 a[2 * NW];
+#pragma unroll
+                    for (int q = 0; q < 2 * NW; ++q) a[q] = ring[r][q];
+                    load_chunk(ring[r], kc + SH_AHEAD * SH_WARPS);
+                    load_rows(xr[r ^ 1], kc + SH_WARPS);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        if (i < (int)ntiles) {
+#pragma unroll
+                            for (int w = 0; w < NW; ++w) {
+                                const uint32_t a1[4] = {a[2 * w].x, a[2 * w + 1].x, a[2 * w].y, a[2 * w + 1].y};
+                                const uint32_t a2[4] = {a[2 * w].z, a[2 * w + 1].z, a[2 * w].w, a[2 * w + 1].w};
+                                mma_bf16(acc[w][i], a1, xr[r][i].x, xr[r][i].y);
+                                mma_bf16(acc[w][i], a2, xr[r][i].z, xr[r][i].w);
+                            }
+                        }
                     }
                 }
             }
@@ -106,13 +142,13 @@ cudaError_t launch_shared_expert(const __nv_bfloat16* x, const __nv_bfloat16* w1
                                  const __nv_bfloat16* w2, uint32_t T, uint32_t H, uint32_t I, float limit,
                                  __nv_bfloat16* h_ws, float* out, cudaStream_t st) {
     if (T == 0) return cudaSuccess;
-    const size_t smem0 = (size_t)SH_WARPS * 2 * 8 * 32 * 4 * sizeof(float), smem1 = smem0 / 2;
+    const size_t smem0 = (size_t)sh_warps(0) * 2 * 8 * 32 * 4 * sizeof(float), smem1 = (size_t)sh_warps(1) * 8 * 32 * 4 * sizeof(float);
     cudaError_t e = cudaFuncSetAttribute(shared_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem0);
     if (e != cudaSuccess) return e;
-    shared_kernel<0><<<I / 16, SH_WARPS * 32, smem0, st>>>(x, T, H, I, w1, w3, limit, h_ws, nullptr);
+    shared_kernel<0><<<I / 16, sh_warps(0) * 32, smem0, st>>>(x, T, H, I, w1, w3, limit, h_ws, nullptr);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    shared_kernel<1><<<H / 16, SH_WARPS * 32, smem1, st>>>(h_ws, T, I, H, w2, nullptr, 0.f, nullptr, out);
+    shared_kernel<1><<<H / 16, sh_warps(1) * 32, smem1, st>>>(h_ws, T, I, H, w2, nullptr, 0.f, nullptr, out);
     return cudaGetLastError();
 }
 
