@@ -243,6 +243,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--experts", type=int, default=0, help="routed experts (smaller only for profiler captures)")
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--graph", action="store_true", help="also time the steps replayed from CUDA graphs (one GPU)")
     ap.add_argument("--placement", default="contiguous", choices=["contiguous", "usage"],
                     help="expert parallel: experts in contiguous blocks, or dealt to the ranks by a routing histogram")
     ap.add_argument("--layers", type=int, default=1,
@@ -443,6 +444,24 @@ def main():
     prof = moe.profile_read()
     moe.profile_enable(False)
     clocks = sampler.stop()
+    # the same steps replayed from CUDA graphs (one per batch): what a host gains for launch-bound small batches
+    graph_ms = None
+    if args.graph and world == 1:
+        side = torch.cuda.Stream()
+        graphs = []
+        for b in range(n_batches):
+            gph = torch.cuda.CUDAGraph()
+            side.wait_stream(stream)
+            with torch.cuda.graph(gph, stream=side):
+                cs = torch.cuda.current_stream().cuda_stream
+                src, a, bb = xs[b], y, y2
+                for l in range(NL):
+                    moe.forward(l, src.data_ptr(), lgs[(b + l) % n_batches][l].data_ptr(), T, a.data_ptr(), cs)
+                    src, a, bb = a, bb, a
+            graphs.append(gph)
+        for i in range(args.warmup):
+            graphs[i % n_batches].replay()
+        graph_ms = timed(lambda i: graphs[i % n_batches].replay(), args.steps)
     for i in range(args.warmup):
         step_host(i)
     ms_host = timed(step_host, args.steps)
@@ -485,6 +504,8 @@ def main():
         "e2e": {"value": world * T * args.steps / (ms_host * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": T * H * 2 + T * E * 4, "d2h_bytes_per_step": T * H * 2 + 4},
         "gpu_launches": NL * own_launches_per_layer(T, world) * args.steps,
+        "graph_replay": None if graph_ms is None else {"ms_per_step": graph_ms / args.steps,
+                                                        "value": T * args.steps / (graph_ms * 1e-3), "unit": UNIT},
         "exchange": None if world == 1 else {
             "exposed_ms_per_step": prof["exchange"][0] / max(args.steps, 1),
             "bytes_sent_per_step_rank0": st.a2a_bytes_sent / max(st.expert_calls, 1),
