@@ -482,8 +482,11 @@ def main():
     peak, which = peaks()
     achieved = mean_distinct * gu_bytes / (gu_ms / max(gu_n, 1) * 1e-3) / 1e9
     tl_ms, tl_n = prof.get("tensor_lane", (0.0, 0))
-    # the tensor-core lane is the dominant kernel once it takes more of the step than the streaming gate/up kernel
-    prefill_lane = tl_n > 0 and tl_ms > gu_ms
+    # the tensor-core lane is the dominant kernel once most of the rows this rank serves belong to its experts (the lanes
+    # run on two streams, so their event spans overlap and do not rank them)
+    rows_heavy = float(np.mean([int(c[c >= LANE_MIN_ROWS].sum()) for c in lane_counts])) if lane_counts else 0.0
+    rows_served = float(np.mean([int(c.sum()) for c in lane_counts])) if lane_counts else 0.0
+    prefill_lane = tl_n > 0 and rows_heavy > 0.5 * rows_served
     layer_bytes = NL * (mean_distinct * logical + (3 * H * I * 2 if WL["shared"] else 0) + T * H * 2 * 2 + T * E * 4)
     value = world * T * args.steps / (ms * 1e-3)
     out = {

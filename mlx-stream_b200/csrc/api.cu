@@ -191,11 +191,13 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
             if (shared_gemm_create(&h->sh_gemm)) return bail(fail(MLXS_E_CUDA, "create: cublasCreate failed"));
         }
     }
-    if (c->shared_expert) {
+    if (c->shared_expert || h->pf_tiles) {
         if (cudaStreamCreateWithFlags(&h->aux_stream, cudaStreamNonBlocking) != cudaSuccess ||
             cudaEventCreateWithFlags(&h->aux_fork, cudaEventDisableTiming) != cudaSuccess ||
-            cudaEventCreateWithFlags(&h->aux_join, cudaEventDisableTiming) != cudaSuccess)
-            return bail(fail(MLXS_E_CUDA, "create: second stream for the shared expert"));
+            cudaEventCreateWithFlags(&h->aux_join, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&h->lane_fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&h->lane_join, cudaEventDisableTiming) != cudaSuccess)
+            return bail(fail(MLXS_E_CUDA, "create: second stream"));
     }
     if (cudaDeviceSynchronize() != cudaSuccess) return bail(fail(MLXS_E_CUDA, "create: device synchronize failed"));
     *out = h;
@@ -208,6 +210,8 @@ extern "C" void mlxs_moe_destroy(mlxs_moe* h) {
     cudaDeviceSynchronize();
     mlxs_ep_destroy(h);
     shared_gemm_destroy(h->sh_gemm);
+    if (h->lane_fork) cudaEventDestroy(h->lane_fork);
+    if (h->lane_join) cudaEventDestroy(h->lane_join);
     if (h->aux_fork) cudaEventDestroy(h->aux_fork);
     if (h->aux_join) cudaEventDestroy(h->aux_join);
     if (h->aux_stream) cudaStreamDestroy(h->aux_stream);
@@ -527,16 +531,37 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
             CU(launch_dispatch(ids_dev, A, n_exp, L.loaded_dev + first, h->tabs, h->chunk_rows, h->group_chunks, heavy,
                                h->status, st));
     }
+    // The two lanes serve disjoint experts from separate staging buffers: the tensor-core lane (tile plan, row prep and
+    // its two kernels) is queued on the handle's second stream beside the streaming lane, forked after the dispatch
+    // and joined before the rows are read.  Its launches, most of all the ones that find no heavy expert and return at
+    // once, then cost the step nothing, and the lanes' tails overlap.
+    static const bool lane_serial = getenv("MLXS_LANES_ONE_STREAM") != nullptr;
+    const bool lane_aside = two_lanes && h->aux_stream && !lane_serial;
+    const cudaStream_t tl = lane_aside ? h->aux_stream : st;
+    if (lane_aside) {
+        CU(cudaEventRecord(h->lane_fork, st));
+        CU(cudaStreamWaitEvent(h->aux_stream, h->lane_fork, 0));
+    }
+    const float limit = c.act == MLXS_ACT_SWIGLU_CLAMPED ? c.act_limit : 0.f;
     if (is_exl3(c.bank_kind)) {
         const Exl3Dims d{c.hidden, c.inter, L.kbits};
         Exl3Layer EL{L.gu_code, L.d_code, L.scales};
+        if (two_lanes) {
+            Exl3PrefillArgs pa{};
+            pa.L = EL; pa.d = d; pa.t = h->tabs; pa.n_experts = n_exp; pa.min_rows = heavy;
+            pa.x = static_cast<const __nv_bfloat16*>(x_dev); pa.top_k = top_k; pa.tiles = h->pf_tiles; pa.max_tiles = h->pf_max_tiles;
+            pa.xa = h->pf_xa; pa.xd = h->pf_xd; pa.ro = static_cast<float*>(ro);
+            pa.limit = limit; pa.status = h->status; pa.sm_count = h->sm_count;
+            StageTimer tm(h, MLXS_STAGE_TENSOR_LANE, tl);
+            CU(launch_exl3_prefill(pa, tl));
+        }
         {
             StageTimer tm(h, MLXS_STAGE_PREP, st);
             CU(launch_exl3_prep_in(static_cast<const __nv_bfloat16*>(x_dev), top_k, EL, d, h->tabs, h->xa_gu, st));
         }
         Exl3GemvArgs a{};
         a.L = EL; a.d = d; a.t = h->tabs; a.xa_gu = h->xa_gu; a.xa_d = h->xa_d; a.ro = static_cast<float*>(ro); a.ro_bf16 = 0;
-        a.limit = c.act == MLXS_ACT_SWIGLU_CLAMPED ? c.act_limit : 0.f;
+        a.limit = limit;
         a.status = h->status; a.sm_count = h->sm_count; a.ks_scratch = h->ks_scratch; a.ks_count = h->ks_count;
         {
             StageTimer tm(h, MLXS_STAGE_GATE_UP, st);
@@ -546,16 +571,18 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
             StageTimer tm(h, MLXS_STAGE_DOWN, st);
             CU(launch_exl3_down(a, st));
         }
-        if (two_lanes) {
-            Exl3PrefillArgs pa{};
-            pa.L = EL; pa.d = d; pa.t = h->tabs; pa.n_experts = n_exp; pa.min_rows = heavy;
-            pa.x = static_cast<const __nv_bfloat16*>(x_dev); pa.top_k = top_k; pa.tiles = h->pf_tiles; pa.max_tiles = h->pf_max_tiles;
-            pa.xa = h->pf_xa; pa.xd = h->pf_xd; pa.ro = static_cast<float*>(ro);
-            pa.limit = a.limit; pa.status = h->status; pa.sm_count = h->sm_count;
-            StageTimer tm(h, MLXS_STAGE_TENSOR_LANE, st);
-            CU(launch_exl3_prefill(pa, st));
-        }
     } else {
+        if (two_lanes) {
+            Fp4PrefillArgs pa{};
+            pa.gu = L.f4_gu; pa.dn = L.f4_dn; pa.nv = c.bank_kind == MLXS_BANK_NVFP4; pa.gscale = pa.nv ? L.f4_gscale : nullptr;
+            pa.H = c.hidden; pa.I = c.inter; pa.t = h->tabs;
+            pa.n_experts = n_exp; pa.lane_flags = L.loaded_dev + first; pa.min_rows = heavy;
+            pa.x = static_cast<const __nv_bfloat16*>(x_dev); pa.top_k = top_k; pa.tiles = h->pf_tiles; pa.max_tiles = h->pf_max_tiles;
+            pa.xa = reinterpret_cast<uint16_t*>(h->pf_xa); pa.xd = reinterpret_cast<uint16_t*>(h->pf_xd);
+            pa.ro = ro; pa.ro_bf16 = ro_bf16; pa.limit = limit; pa.status = h->status; pa.sm_count = h->sm_count;
+            StageTimer tm(h, MLXS_STAGE_TENSOR_LANE, tl);
+            CU(launch_fp4_prefill(pa, tl));
+        }
         {
             StageTimer tm(h, MLXS_STAGE_PREP, st);
             CU(launch_fp4_prep(static_cast<const __nv_bfloat16*>(x_dev), top_k, c.hidden, h->tabs, h->xa_gu, st));
@@ -563,7 +590,7 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
         Fp4GemvArgs a{};
         a.gu = L.f4_gu; a.dn = L.f4_dn; a.nv = c.bank_kind == MLXS_BANK_NVFP4; a.gscale = a.nv ? L.f4_gscale : nullptr;
         a.H = c.hidden; a.I = c.inter; a.t = h->tabs; a.xa = h->xa_gu; a.xa_d = h->xa_d; a.ro = ro;
-        a.ro_bf16 = ro_bf16; a.limit = c.act == MLXS_ACT_SWIGLU_CLAMPED ? c.act_limit : 0.f;
+        a.ro_bf16 = ro_bf16; a.limit = limit;
         a.status = h->status; a.sm_count = h->sm_count; a.ks_scratch = h->ks_scratch; a.ks_count = h->ks_count;
         {
             StageTimer tm(h, MLXS_STAGE_GATE_UP, st);
@@ -573,16 +600,10 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
             StageTimer tm(h, MLXS_STAGE_DOWN, st);
             CU(launch_fp4_gemv(a, 1, st));
         }
-        if (two_lanes) {
-            Fp4PrefillArgs pa{};
-            pa.gu = a.gu; pa.dn = a.dn; pa.gscale = a.gscale; pa.nv = a.nv; pa.H = a.H; pa.I = a.I; pa.t = h->tabs;
-            pa.n_experts = n_exp; pa.lane_flags = L.loaded_dev + first; pa.min_rows = heavy;
-            pa.x = static_cast<const __nv_bfloat16*>(x_dev); pa.top_k = top_k; pa.tiles = h->pf_tiles; pa.max_tiles = h->pf_max_tiles;
-            pa.xa = reinterpret_cast<uint16_t*>(h->pf_xa); pa.xd = reinterpret_cast<uint16_t*>(h->pf_xd);
-            pa.ro = ro; pa.ro_bf16 = ro_bf16; pa.limit = a.limit; pa.status = h->status; pa.sm_count = h->sm_count;
-            StageTimer tm(h, MLXS_STAGE_TENSOR_LANE, st);
-            CU(launch_fp4_prefill(pa, st));
-        }
+    }
+    if (lane_aside) {
+        CU(cudaEventRecord(h->lane_join, h->aux_stream));
+        CU(cudaStreamWaitEvent(st, h->lane_join, 0));
     }
     h->stats.expert_calls += 1;
     h->stats.assignments += A;

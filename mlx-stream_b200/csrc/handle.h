@@ -69,6 +69,7 @@ struct mlxs_moe {
     uint32_t* ks_count = nullptr;
     cudaStream_t aux_stream = nullptr;
     cudaEvent_t aux_fork = nullptr, aux_join = nullptr;
+    cudaEvent_t lane_fork = nullptr, lane_join = nullptr;  // the tensor-core lane runs on the second stream beside the streaming lane
     float* sh_out = nullptr;
     uint32_t* status = nullptr;
     uint8_t* staging = nullptr;
