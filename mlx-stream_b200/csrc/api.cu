@@ -195,6 +195,7 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
         if (cudaStreamCreateWithFlags(&h->aux_stream, cudaStreamNonBlocking) != cudaSuccess ||
             cudaEventCreateWithFlags(&h->aux_fork, cudaEventDisableTiming) != cudaSuccess ||
             cudaEventCreateWithFlags(&h->aux_join, cudaEventDisableTiming) != cudaSuccess ||
+            cudaStreamCreateWithFlags(&h->lane_stream, cudaStreamNonBlocking) != cudaSuccess ||
             cudaEventCreateWithFlags(&h->lane_fork, cudaEventDisableTiming) != cudaSuccess ||
             cudaEventCreateWithFlags(&h->lane_join, cudaEventDisableTiming) != cudaSuccess)
             return bail(fail(MLXS_E_CUDA, "create: second stream"));
@@ -215,6 +216,7 @@ extern "C" void mlxs_moe_destroy(mlxs_moe* h) {
     if (h->aux_fork) cudaEventDestroy(h->aux_fork);
     if (h->aux_join) cudaEventDestroy(h->aux_join);
     if (h->aux_stream) cudaStreamDestroy(h->aux_stream);
+    if (h->lane_stream) cudaStreamDestroy(h->lane_stream);
     for (void* p : h->allocs) cudaFree(p);
     for (auto& s : h->spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
     for (auto e : h->ev_pool) cudaEventDestroy(e);
@@ -532,15 +534,15 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
                                h->status, st));
     }
     // The two lanes serve disjoint experts from separate staging buffers: the tensor-core lane (tile plan, row prep and
-    // its two kernels) is queued on the handle's second stream beside the streaming lane, forked after the dispatch
+    // its two kernels) is queued on a stream of its own beside the streaming lane, forked after the dispatch
     // and joined before the rows are read.  Its launches, most of all the ones that find no heavy expert and return at
     // once, then cost the step nothing, and the lanes' tails overlap.
     static const bool lane_serial = getenv("MLXS_LANES_ONE_STREAM") != nullptr;
-    const bool lane_aside = two_lanes && h->aux_stream && !lane_serial;
-    const cudaStream_t tl = lane_aside ? h->aux_stream : st;
+    const bool lane_aside = two_lanes && h->lane_stream && !lane_serial;
+    const cudaStream_t tl = lane_aside ? h->lane_stream : st;
     if (lane_aside) {
         CU(cudaEventRecord(h->lane_fork, st));
-        CU(cudaStreamWaitEvent(h->aux_stream, h->lane_fork, 0));
+        CU(cudaStreamWaitEvent(h->lane_stream, h->lane_fork, 0));
     }
     const float limit = c.act == MLXS_ACT_SWIGLU_CLAMPED ? c.act_limit : 0.f;
     if (is_exl3(c.bank_kind)) {
@@ -602,7 +604,7 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
         }
     }
     if (lane_aside) {
-        CU(cudaEventRecord(h->lane_join, h->aux_stream));
+        CU(cudaEventRecord(h->lane_join, h->lane_stream));
         CU(cudaStreamWaitEvent(st, h->lane_join, 0));
     }
     h->stats.expert_calls += 1;
@@ -644,10 +646,11 @@ extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, 
     // rows back (ep.cu); the chain combine needs every assignment's row in k order and keeps the per-assignment form
     static const bool per_assignment = getenv("MLXS_EP_PER_ASSIGNMENT") != nullptr;
     const bool ep_fused = c.ep_world > 1 && c.combine != MLXS_COMBINE_CHAIN && !per_assignment;
-    // Decode-sized batches leave SMs idle in the routed kernels (T = 1: 144 work items for 296 CTA slots): the shared
-    // expert, which only reads x, then runs beside them on the handle's second stream.  Larger batches keep one stream
-    // (the routed kernels' persistent CTAs own the SMs anyway).
-    const bool shared_aside = c.shared_expert && T <= 16 && h->aux_stream;
+    // The shared expert only reads x: it runs beside the routed kernels on the handle's second stream.  Decode-sized
+    // batches leave SMs idle in the routed kernels (T = 1: 144 work items for 296 CTA slots); larger ones still have
+    // the dispatch and the staging of the rows at their start, about as long as the shared expert itself.
+    static const bool shared_serial = getenv("MLXS_SHARED_ONE_STREAM") != nullptr;
+    const bool shared_aside = c.shared_expert && h->aux_stream && !shared_serial;
     const float* shared = nullptr;
     auto run_shared = [&](cudaStream_t s) -> int {
         const float lim = c.act == MLXS_ACT_SWIGLU_CLAMPED ? c.act_limit : 0.f;

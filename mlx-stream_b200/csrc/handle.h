@@ -69,7 +69,9 @@ struct mlxs_moe {
     uint32_t* ks_count = nullptr;
     cudaStream_t aux_stream = nullptr;
     cudaEvent_t aux_fork = nullptr, aux_join = nullptr;
-    cudaEvent_t lane_fork = nullptr, lane_join = nullptr;  // the tensor-core lane runs on the second stream beside the streaming lane
+    // the tensor-core lane runs on a stream of its own beside the streaming lane
+    cudaStream_t lane_stream = nullptr;
+    cudaEvent_t lane_fork = nullptr, lane_join = nullptr;
     float* sh_out = nullptr;
     uint32_t* status = nullptr;
     uint8_t* staging = nullptr;
