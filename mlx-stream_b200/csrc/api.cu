@@ -537,8 +537,10 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
     // its two kernels) is queued on a stream of its own beside the streaming lane, forked after the dispatch
     // and joined before the rows are read.  Its launches, most of all the ones that find no heavy expert and return at
     // once, then cost the step nothing, and the lanes' tails overlap.
-    static const bool lane_serial = getenv("MLXS_LANES_ONE_STREAM") != nullptr;
-    const bool lane_aside = two_lanes && h->lane_stream && !lane_serial;
+    // Prefill-sized calls (nearly every expert in the tensor-core lane, nothing to overlap) keep one stream: with two,
+    // C4 at 16384 tokens went from 13.0 to 14.4 ms.  MLXS_LANES_ASIDE_MAX moves the limit (0: always one stream).
+    static const uint32_t lanes_aside_max = getenv("MLXS_LANES_ASIDE_MAX") ? (uint32_t)atoi(getenv("MLXS_LANES_ASIDE_MAX")) : 2048u;
+    const bool lane_aside = two_lanes && h->lane_stream && T <= lanes_aside_max;
     const cudaStream_t tl = lane_aside ? h->lane_stream : st;
     if (lane_aside) {
         CU(cudaEventRecord(h->lane_fork, st));
@@ -649,8 +651,11 @@ extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, 
     // The shared expert only reads x: it runs beside the routed kernels on the handle's second stream.  Decode-sized
     // batches leave SMs idle in the routed kernels (T = 1: 144 work items for 296 CTA slots); larger ones still have
     // the dispatch and the staging of the rows at their start, about as long as the shared expert itself.
-    static const bool shared_serial = getenv("MLXS_SHARED_ONE_STREAM") != nullptr;
-    const bool shared_aside = c.shared_expert && h->aux_stream && !shared_serial;
+    // Prefill-sized calls keep it on the caller's stream after the routed kernels: its library GEMMs are full-GPU
+    // kernels, and running them among the tensor-core lane's persistent CTAs stretched that lane (C4 at 16384 tokens:
+    // 12.9 -> 14.6 ms).  MLXS_SHARED_ASIDE_MAX moves the limit (0: never aside).
+    static const uint32_t aside_max = getenv("MLXS_SHARED_ASIDE_MAX") ? (uint32_t)atoi(getenv("MLXS_SHARED_ASIDE_MAX")) : 64u;
+    const bool shared_aside = c.shared_expert && h->aux_stream && T <= aside_max;
     const float* shared = nullptr;
     auto run_shared = [&](cudaStream_t s) -> int {
         const float lim = c.act == MLXS_ACT_SWIGLU_CLAMPED ? c.act_limit : 0.f;
