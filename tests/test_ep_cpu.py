@@ -210,3 +210,59 @@ def test_ep_protocol_world2_gloo():
     for rank, err, R in res:
         assert err < 1e-12, (rank, err)
     assert sum(r[2] for r in res) == (5 + 7) * 2
+
+
+def _rank_placement(rank, world, port, q):
+    """Placement by usage on CPU ranks: each rank tallies its own routes (numpy stands in for the device tally), the
+    counts are summed over the ranks, and the library's planner must give every rank the same table; the ranks'
+    expected rows come out closer than with contiguous blocks."""
+    sys.path.insert(0, str(HERE))
+    sys.path.insert(0, str(HERE.parent))
+    import torch
+    import torch.distributed as dist
+
+    import oracle_lib as O
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    E, k, T = 32, 4, 300 + 50 * rank
+    rs = np.random.default_rng(77 + rank)
+    pop = np.log((1.0 + np.random.default_rng(5).permutation(E)) ** -1.1)   # one popularity order for every rank
+    logits = (rs.standard_normal((T, E)) + pop).astype(np.float32)
+    ids, _ = O.route(logits, None, k, O.SCORE_SIGMOID)
+    mine = np.bincount(ids.reshape(-1), minlength=E).astype(np.int64)
+    total = torch.from_numpy(mine.copy())
+    dist.all_reduce(total)
+    total = total.numpy()
+    place = np.asarray(pkg.plan_placement(total, world))
+    # every rank must hold the same table
+    tables = [torch.zeros(E, dtype=torch.int64) for _ in range(world)]
+    dist.all_gather(tables, torch.from_numpy(place.astype(np.int64)))
+    same = all((t.numpy() == place).all() for t in tables)
+    by_use = [int(total[place == r].sum()) for r in range(world)]
+    blocks = [int(total[r * (E // world):(r + 1) * (E // world)].sum()) for r in range(world)]
+    # the destination plan of this rank's assignments under the table: counts per rank add up
+    dest = place[ids.reshape(-1)]
+    sent = np.bincount(dest, minlength=world)
+    dist.destroy_process_group()
+    q.put((rank, same, by_use, blocks, int(sent.sum()), int(total.sum())))
+
+
+def test_usage_placement_world2_gloo():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_placement, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, same, by_use, blocks, sent, total in res:
+        assert same, rank
+        assert sent == (300 + 50 * rank) * 4 and total == (300 + 350) * 4
+        assert max(by_use) - min(by_use) < max(blocks) - min(blocks), (by_use, blocks)
+    assert res[0][2] == res[1][2]
