@@ -539,9 +539,17 @@ def main():
         t0 = time.perf_counter()
         O.layer_fast(H, I, E, K_TOP, recs, xc, ids, w, shared=shared, threads=threads)
         dt = time.perf_counter() - t0
+        # the same form on one thread, over the first two tokens of the sample (their experts only)
+        T1 = min(2, Tc)
+        recs1 = {int(e): recs[int(e)] for e in np.unique(ids[:T1])}
+        t0 = time.perf_counter()
+        O.layer_fast(H, I, E, K_TOP, recs1, xc[:T1], ids[:T1], w[:T1], shared=shared, threads=1)
+        dt1 = time.perf_counter() - t0
         out["cpu_baseline"] = {"value": Tc / dt, "unit": UNIT, "cores": threads, "kind": "port",
                                "sample": f"{Tc} tokens x top-{K_TOP} ({len(recs)} distinct experts), one call, "
-                                         "oracle fast f32 form with OpenMP"}
+                                         "oracle fast f32 form with OpenMP",
+                               "one_thread": {"value": T1 / dt1, "unit": UNIT,
+                                              "sample": f"{T1} tokens x top-{K_TOP} ({len(recs1)} distinct experts)"}}
     if rank == 0:
         print(json.dumps(out))
     moe.close()
