@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define MLXS_MOE_ABI 2026112507
+#define MLXS_MOE_ABI 2026112508
 
 /* refusals (the names mirror the reference's refusal sets: src/sdk_ext/quant.zig:94-111, src/expert/bank.zig:79-101) */
 enum {
@@ -130,6 +130,11 @@ typedef struct {
 } mlxs_bank_info;
 int mlxs_moe_bank_peek(const char *dir, mlxs_bank_info *out);
 int mlxs_moe_bank_peek_text(const char *manifest_json, mlxs_bank_info *out);
+/* Bank.open without a device (src/expert/bank.zig:228-251, 326-400): the manifests of the bank at `dir` (for an EXL3
+ * bank both of them: the v2 geometry and the v1 runtime manifest expert-manifest.json, which must describe exactly the
+ * v2 records), the sidecar file (present, not a symbolic link, at least the manifest's size) and, with verify_sha256,
+ * every record's digests (v2: the padded record, v1: its logical bytes).  mlxs_moe_load_bank runs the same checks. */
+int mlxs_moe_bank_verify(const char *dir, mlxs_bank_info *out, int verify_sha256);
 /* K of every layer of an EXL3 manifest text (v2 peek, src/expert/bank.zig:641-662): writes min(n_layers, cap) widths
  * and the layer count */
 int mlxs_moe_bank_layer_bits_text(const char *manifest_json, uint32_t *bits_out, uint32_t cap, uint32_t *n_layers_out);

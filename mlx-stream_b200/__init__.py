@@ -14,7 +14,7 @@ from pathlib import Path  # noqa: E402
 
 HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "libmlxs_moe.so"
-ABI = 2026112507
+ABI = 2026112508
 
 BANK_EXL3_K3_MUL1, BANK_MXFP4, BANK_NVFP4, BANK_EXL3_K2_MUL1 = 0, 1, 2, 3
 SCORE_SQRTSOFTPLUS, SCORE_SIGMOID, SCORE_SOFTMAX = 0, 1, 2
@@ -31,7 +31,7 @@ EXPORTS = [
     "mlxs_moe_stats_get", "mlxs_moe_profile_enable", "mlxs_moe_profile_read", "mlxs_moe_ep_unique_id", "mlxs_moe_ep_init", "mlxs_moe_ep_plan",
     "mlxs_moe_set_placement", "mlxs_moe_set_router_weight", "mlxs_moe_logits", "mlxs_moe_forward_x",
     "mlxs_moe_set_layer_bits", "mlxs_moe_layer_record_bytes", "mlxs_moe_bank_layer_bits_text",
-    "mlxs_moe_usage_enable", "mlxs_moe_usage_add", "mlxs_moe_usage_read", "mlxs_moe_usage_reset", "mlxs_moe_plan_placement",
+    "mlxs_moe_bank_verify", "mlxs_moe_usage_enable", "mlxs_moe_usage_add", "mlxs_moe_usage_read", "mlxs_moe_usage_reset", "mlxs_moe_plan_placement",
 ]
 
 
@@ -99,6 +99,7 @@ def lib():
         L.mlxs_moe_load_bank.argtypes = [C.c_void_p, C.c_char_p]
         L.mlxs_moe_bank_peek.argtypes = [C.c_char_p, C.POINTER(BankInfo)]
         L.mlxs_moe_bank_peek_text.argtypes = [C.c_char_p, C.POINTER(BankInfo)]
+        L.mlxs_moe_bank_verify.argtypes = [C.c_char_p, C.POINTER(BankInfo), C.c_int]
         L.mlxs_moe_set_router_bias.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p]
         L.mlxs_moe_set_shared.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
         L.mlxs_moe_route.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p]
@@ -150,6 +151,14 @@ def bank_peek(directory=None, text=None):
         _check(lib().mlxs_moe_bank_peek_text(text.encode() if isinstance(text, str) else text, C.byref(info)))
     else:
         _check(lib().mlxs_moe_bank_peek(str(directory).encode(), C.byref(info)))
+    return info
+
+
+def bank_verify(directory, verify_sha256=True):
+    """Opens a bank as the load does, without a device: manifests (EXL3: v2 and the v1 runtime manifest), sidecar,
+    and on request every record's digests."""
+    info = BankInfo()
+    _check(lib().mlxs_moe_bank_verify(str(directory).encode(), C.byref(info), int(verify_sha256)))
     return info
 
 

@@ -196,7 +196,7 @@ struct Sha256 {
     }
 };
 
-struct Record { uint64_t offset = 0; std::string sha256; bool present = false; };
+struct Record { uint64_t offset = 0; std::string sha256; std::string sha256_logical; bool present = false; };
 struct Bank {
     mlxs_bank_info info{};
     std::vector<Record> records;  // [layer][expert]
@@ -430,6 +430,137 @@ int open_bank(const char* dir, Bank& b) {
     return mlxs_fail(MLXS_E_MANIFEST, "%s: neither expert-manifest-v2.json nor expert-manifest.json can be read", dir);
 }
 
+bool lower_hex64(const std::string& h) {
+    if (h.size() != 64) return false;
+    for (char ch : h) if (!((ch >= '0' && ch <= '9') || (ch >= 'a' && ch <= 'f'))) return false;
+    return true;
+}
+
+// An EXL3 bank carries two manifests: the v2 geometry and the v1 runtime manifest <dir>/expert-manifest.json, which must
+// describe exactly the v2 records: same offsets, logical sizes and segment table (absolute offsets), every record once,
+// the same sidecar (src/expert/bank.zig:326-400, refusals :1064-1072).  Keeps each record's logical-bytes digest.
+int check_v1(const std::string& dir, Bank& b) {
+    static const char* name = "expert-manifest.json";
+    std::string text;
+    if (!read_file(dir + "/" + name, text))
+        return mlxs_fail(MLXS_E_MANIFEST, "%s: the v1 runtime manifest cannot be read (ManifestMissing)", name);
+    JParser jp{text.data(), text.data() + text.size()};
+    JVal m = jp.value();
+    jp.ws();
+    if (!jp.ok || m.kind != JVal::Obj || jp.p != jp.end) return mlxs_fail(MLXS_E_MANIFEST, "%s: not a JSON object (ManifestSyntax)", name);
+    const std::string fmt = gets(&m, "format");
+    if (fmt != "mtplx-expert-manifest-v1") return mlxs_fail(MLXS_E_MANIFEST, "%s: format \"%s\" is not mtplx-expert-manifest-v1 (ManifestFormat)", name, fmt.c_str());
+    const std::string mode = gets(m.get("quantization"), "mode");
+    if (mode != "exl3-mul1") return mlxs_fail(MLXS_E_MANIFEST, "%s: quantization.mode \"%s\" is not exl3-mul1 (RuntimeModeNotExl3)", name, mode.c_str());
+    const mlxs_bank_info& bi = b.info;
+    const uint64_t H = bi.hidden, I = bi.inter, E = bi.n_experts, L = bi.n_layers;
+    const JVal* recs = m.get("records");
+    if (!recs || recs->kind != JVal::Arr || recs->arr.size() != L * E)
+        return mlxs_fail(MLXS_E_MANIFEST, "%s: %zu records != %llu (RecordCount)", name, recs && recs->kind == JVal::Arr ? recs->arr.size() : (size_t)0,
+                         (unsigned long long)(L * E));
+    static const char* proj[3] = {"gate_proj", "up_proj", "down_proj"};
+    static const char* part[3] = {"code", "rout", "rin"};
+    std::vector<bool> seen(L * E, false);
+    for (const JVal& r : recs->arr) {
+        uint64_t rl = 0, re = 0, lb = 0, so = 0, sl = 0;
+        if (!geti(&r, "layer", rl) || !geti(&r, "expert", re) || rl >= L || re >= E)
+            return mlxs_fail(MLXS_E_MANIFEST, "v1: record (%llu,%llu) is not in the v2 bank (RuntimeRecordMismatch)", (unsigned long long)rl, (unsigned long long)re);
+        const size_t i = rl * E + re;
+        if (seen[i]) return mlxs_fail(MLXS_E_MANIFEST, "v1: record (%llu,%llu) duplicated (RecordDuplicate)", (unsigned long long)rl, (unsigned long long)re);
+        seen[i] = true;
+        const uint64_t off = b.layer_base[rl] + re * b.layer_stride[rl], logical = b.layer_logical[rl], K = b.layer_bits[rl];
+        if (!geti(&r, "logical_bytes", lb) || !geti(&r, "sidecar_offset", so) || !geti(&r, "sidecar_length", sl) || so != off || lb != logical || sl != logical)
+            return mlxs_fail(MLXS_E_MANIFEST, "v1: record (%llu,%llu) offset/length differs from the v2 manifest (RuntimeRecordMismatch)", (unsigned long long)rl, (unsigned long long)re);
+        const JVal* segs = r.get("segments");
+        if (!segs || segs->kind != JVal::Arr || segs->arr.size() != 9)
+            return mlxs_fail(MLXS_E_MANIFEST, "v1: record (%llu,%llu) has %zu segments (RuntimeRecordMismatch)", (unsigned long long)rl, (unsigned long long)re,
+                             segs && segs->kind == JVal::Arr ? segs->arr.size() : (size_t)0);
+        for (const JVal& sg : segs->arr)
+            if (gets(&sg, "shard") != bi.data_file)
+                return mlxs_fail(MLXS_E_MANIFEST, "v1: record (%llu,%llu) reads shard \"%s\" (RuntimeRecordMismatch)", (unsigned long long)rl, (unsigned long long)re, gets(&sg, "shard").c_str());
+        // absolute offsets equal to the record's offset + the v2 table: contiguous, in record order
+        uint64_t rel = 0;
+        bool match = true;
+        for (int p = 0; p < 3 && match; ++p) {
+            const uint64_t in = p == 2 ? I : H, out = p == 2 ? H : I;
+            for (int j = 0; j < 3 && match; ++j) {
+                const JVal& sg = segs->arr[p * 3 + j];
+                const uint64_t len = j == 0 ? (in / 16) * (out / 16) * 32 * K : (j == 1 ? out * 2 : in * 2);
+                uint64_t go = 0, gl = 0;
+                const JVal* shp = sg.get("shape");
+                match = gets(&sg, "component") == std::string(proj[p]) + "." + part[j] && gets(&sg, "dtype") == (j == 0 ? "I16" : "F16") &&
+                        geti(&sg, "offset", go) && geti(&sg, "length", gl) && go == off + rel && gl == len && shp && shp->kind == JVal::Arr;
+                if (match) {
+                    if (j == 0) match = shp->arr.size() == 3 && shp->arr[0].u == in / 16 && shp->arr[1].u == out / 16 && shp->arr[2].u == 16 * K;
+                    else match = shp->arr.size() == 1 && shp->arr[0].u == (j == 1 ? out : in);
+                }
+                rel += len;
+            }
+        }
+        if (!match)
+            return mlxs_fail(MLXS_E_MANIFEST, "v1: record (%llu,%llu) segments differ from the v2 layer table (order, offsets, lengths, dtype, shape) (RuntimeRecordMismatch)",
+                             (unsigned long long)rl, (unsigned long long)re);
+        const std::string sha = gets(&r, "sha256");
+        if (!lower_hex64(sha)) return mlxs_fail(MLXS_E_MANIFEST, "v1: record (%llu,%llu) has no sha256 (RecordSha256)", (unsigned long long)rl, (unsigned long long)re);
+        b.records[i].sha256_logical = sha;
+    }
+    const JVal* sc = m.get("sidecar");
+    uint64_t sz = 0, al = 0;
+    if (!sc) return mlxs_fail(MLXS_E_MANIFEST, "%s: no sidecar (ManifestSyntax)", name);
+    if (gets(sc, "file") != bi.data_file || !geti(sc, "size", sz) || sz != bi.data_bytes || !geti(sc, "alignment", al) || al != 4096)
+        return mlxs_fail(MLXS_E_MANIFEST, "%s: sidecar %s (%llu B, align %llu) differs from the v2 manifest (SidecarGeometry)", name, gets(sc, "file").c_str(),
+                         (unsigned long long)sz, (unsigned long long)al);
+    return MLXS_OK;
+}
+
+// Bank.open without a device (src/expert/bank.zig:228-251): the manifests, the v1 cross-check of an EXL3 bank, the
+// sidecar (a plain file of at least the manifest's size; a symbolic link is refused).  Returns the open descriptor.
+int open_checked(const char* dir, Bank& b, int& fd_out) {
+    int rc = open_bank(dir, b);
+    if (rc) return rc;
+    const mlxs_bank_info& bi = b.info;
+    if (!bi.data_file[0] || b.records.empty()) return mlxs_fail(MLXS_E_MANIFEST, "load_bank: the manifest names no sidecar / records");
+    if (!b.layer_bits.empty() && (rc = check_v1(dir, b))) return rc;
+    const std::string path = std::string(dir) + "/" + bi.data_file;
+    const int fd = open(path.c_str(), O_RDONLY | O_NOFOLLOW);
+    if (fd < 0) return mlxs_fail(MLXS_E_MANIFEST, "load_bank: cannot open %s (SidecarMissing / SidecarOpen)", path.c_str());
+    struct stat st;
+    if (fstat(fd, &st) || (uint64_t)st.st_size < bi.data_bytes) {
+        close(fd);
+        return mlxs_fail(MLXS_E_MANIFEST, "load_bank: %s is shorter than the manifest's %llu bytes (SidecarGeometry)", path.c_str(), (unsigned long long)bi.data_bytes);
+    }
+    fd_out = fd;
+    return MLXS_OK;
+}
+
+// one record into buf (the padded record of an EXL3 bank, the record's own bytes otherwise), digests checked on request
+int read_record(int fd, const Bank& b, uint64_t l, uint64_t e, bool verify, std::vector<uint8_t>& buf) {
+    const bool exl3 = !b.layer_bits.empty();
+    const Record& r = b.records[l * b.info.n_experts + e];
+    if (!r.present) return mlxs_fail(MLXS_E_MANIFEST, "load_bank: record (%llu,%llu) missing", (unsigned long long)l, (unsigned long long)e);
+    buf.resize(exl3 ? b.layer_stride[l] : b.info.logical_bytes);
+    size_t got = 0;
+    while (got < buf.size()) {
+        const ssize_t n = pread(fd, buf.data() + got, buf.size() - got, (off_t)(r.offset + got));
+        if (n <= 0) break;
+        got += (size_t)n;
+    }
+    if (got != buf.size()) return mlxs_fail(MLXS_E_MANIFEST, "load_bank: short read of record (%llu,%llu)", (unsigned long long)l, (unsigned long long)e);
+    if (verify) {
+        // the v2 (EXL3) digests cover the padded record, the v1 ones its logical bytes; the FP4 banks' the record's own bytes
+        Sha256 s;
+        s.update(buf.data(), buf.size());
+        if (s.hex() != r.sha256) return mlxs_fail(MLXS_E_MANIFEST, "load_bank: record (%llu,%llu) sha256 mismatch (RecordSha256)", (unsigned long long)l, (unsigned long long)e);
+        if (exl3 && !r.sha256_logical.empty()) {
+            Sha256 s1;
+            s1.update(buf.data(), b.layer_logical[l]);
+            if (s1.hex() != r.sha256_logical)
+                return mlxs_fail(MLXS_E_MANIFEST, "load_bank: record (%llu,%llu) differs from its v1 sha256 (RecordSha256)", (unsigned long long)l, (unsigned long long)e);
+        }
+    }
+    return MLXS_OK;
+}
+
 }  // namespace
 
 extern "C" int mlxs_moe_bank_peek_text(const char* manifest_json, mlxs_bank_info* out) {
@@ -468,52 +599,50 @@ int mlxs_bank_for_each_record(const char* dir, uint32_t bank_kind, uint64_t H, u
                               uint32_t e_first, uint32_t e_count, int (*layer_begin)(void* ctx, uint32_t layer, uint32_t bits),
                               int (*sink)(void* ctx, uint32_t layer, uint32_t expert, const void* rec, uint64_t n), void* ctx) {
     Bank b;
-    int rc = open_bank(dir, b);
+    int fd = -1;
+    int rc = open_checked(dir, b, fd);
     if (rc) return rc;
     const mlxs_bank_info& bi = b.info;
     const bool exl3 = !b.layer_bits.empty();
     const bool handle_exl3 = bank_kind == MLXS_BANK_EXL3_K3_MUL1 || bank_kind == MLXS_BANK_EXL3_K2_MUL1;
-    if (exl3 ? !handle_exl3 : bi.bank_kind != bank_kind)
+    if (exl3 ? !handle_exl3 : bi.bank_kind != bank_kind) {
+        close(fd);
         return mlxs_fail(MLXS_E_MANIFEST, "load_bank: the bank at %s is kind %u, the handle is kind %u", dir, bi.bank_kind, bank_kind);
-    if (bi.hidden != H || bi.inter != I || bi.n_experts != E || bi.n_layers != n_layers)
+    }
+    if (bi.hidden != H || bi.inter != I || bi.n_experts != E || bi.n_layers != n_layers) {
+        close(fd);
         return mlxs_fail(MLXS_E_MANIFEST, "load_bank: dims %llu/%llu/%llu experts/%llu layers != the handle's %llu/%llu/%llu/%llu (DimsNotImplemented)",
                          (unsigned long long)bi.hidden, (unsigned long long)bi.inter, (unsigned long long)bi.n_experts, (unsigned long long)bi.n_layers,
                          (unsigned long long)H, (unsigned long long)I, (unsigned long long)E, (unsigned long long)n_layers);
-    if (!bi.data_file[0] || b.records.empty()) return mlxs_fail(MLXS_E_MANIFEST, "load_bank: the manifest names no sidecar / records");
-    const std::string path = std::string(dir) + "/" + bi.data_file;
-    const int fd = open(path.c_str(), O_RDONLY | O_NOFOLLOW);
-    if (fd < 0) return mlxs_fail(MLXS_E_MANIFEST, "load_bank: cannot open %s", path.c_str());
-    struct stat st;
-    if (fstat(fd, &st) || (uint64_t)st.st_size < bi.data_bytes) {
-        close(fd);
-        return mlxs_fail(MLXS_E_MANIFEST, "load_bank: %s is shorter than the manifest's %llu bytes", path.c_str(), (unsigned long long)bi.data_bytes);
     }
     const char* vs = getenv("MLXS_VERIFY_SHA256");
     const bool verify = vs ? atoi(vs) != 0 : bi.data_bytes <= (1ull << 30);  // small banks always, large ones on request
-    // the v2 (EXL3) digests cover the padded record, the FP4 banks' cover the record's own bytes
     std::vector<uint8_t> buf;
     for (uint64_t l = 0; l < n_layers && !rc; ++l) {
         const uint64_t logical = exl3 ? b.layer_logical[l] : bi.logical_bytes;
-        buf.resize(exl3 ? b.layer_stride[l] : bi.logical_bytes);
         if (exl3 && layer_begin && (rc = layer_begin(ctx, (uint32_t)l, b.layer_bits[l]))) break;
         for (uint64_t e = e_first; e < (uint64_t)e_first + e_count && !rc; ++e) {
-            const Record& r = b.records[l * E + e];
-            if (!r.present) { rc = mlxs_fail(MLXS_E_MANIFEST, "load_bank: record (%llu,%llu) missing", (unsigned long long)l, (unsigned long long)e); break; }
-            size_t got = 0;
-            while (got < buf.size()) {
-                const ssize_t n = pread(fd, buf.data() + got, buf.size() - got, (off_t)(r.offset + got));
-                if (n <= 0) break;
-                got += (size_t)n;
-            }
-            if (got != buf.size()) { rc = mlxs_fail(MLXS_E_MANIFEST, "load_bank: short read of record (%llu,%llu)", (unsigned long long)l, (unsigned long long)e); break; }
-            if (verify) {
-                Sha256 s;
-                s.update(buf.data(), buf.size());
-                if (s.hex() != r.sha256) { rc = mlxs_fail(MLXS_E_MANIFEST, "load_bank: record (%llu,%llu) sha256 mismatch (RecordSha256)", (unsigned long long)l, (unsigned long long)e); break; }
-            }
+            if ((rc = read_record(fd, b, l, e, verify, buf))) break;
             rc = sink(ctx, (uint32_t)l, (uint32_t)e, buf.data(), logical);
         }
     }
     close(fd);
+    return rc;
+}
+
+// Bank.open for a host that only wants the check (src/expert/bank.zig:228-251): both manifests, the sidecar, and with
+// verify_sha256 every record's digests; no device involved.
+extern "C" int mlxs_moe_bank_verify(const char* dir, mlxs_bank_info* out, int verify_sha256) {
+    if (!dir) return mlxs_fail(MLXS_E_ARG, "bank_verify: null argument");
+    Bank b;
+    int fd = -1;
+    int rc = open_checked(dir, b, fd);
+    if (rc) return rc;
+    std::vector<uint8_t> buf;
+    if (verify_sha256)
+        for (uint64_t l = 0; l < b.info.n_layers && !rc; ++l)
+            for (uint64_t e = 0; e < b.info.n_experts && !rc; ++e) rc = read_record(fd, b, l, e, true, buf);
+    close(fd);
+    if (!rc && out) *out = b.info;
     return rc;
 }

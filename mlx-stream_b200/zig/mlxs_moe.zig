@@ -2,7 +2,7 @@
 //! is the compiled, tested statement of the same ABI).  One declaration per C entry point, same order.
 const std = @import("std");
 
-pub const abi_expected: i32 = 2026112507;
+pub const abi_expected: i32 = 2026112508;
 
 pub const Moe = opaque {};
 
@@ -72,6 +72,7 @@ pub const BankInfo = extern struct {
 };
 pub extern fn mlxs_moe_bank_peek(dir: [*:0]const u8, out: *BankInfo) c_int;
 pub extern fn mlxs_moe_bank_peek_text(manifest_json: [*:0]const u8, out: *BankInfo) c_int;
+pub extern fn mlxs_moe_bank_verify(dir: [*:0]const u8, out: ?*BankInfo, verify_sha256: c_int) c_int;
 pub extern fn mlxs_moe_bank_layer_bits_text(manifest_json: [*:0]const u8, bits_out: ?[*]u32, cap: u32, n_layers_out: *u32) c_int;
 pub extern fn mlxs_moe_set_router_bias(h: *Moe, layer: u32, bias_host: ?[*]const f32) c_int;
 pub extern fn mlxs_moe_set_router_weight(h: *Moe, layer: u32, w_gate_bf16: *const anyopaque, on_device: c_int) c_int;

@@ -49,11 +49,30 @@ def exl3_manifest(H, I, E, L, records_sha=None, bits=None):
     return m
 
 
-def write_exl3_bank(directory, H, I, E, L, record_of, bits=None):
-    """record_of(layer, expert) -> uint8 record (padded to the record stride); bits: K per layer."""
+def exl3_manifest_v1(v2, logical_shas):
+    """The v1 runtime manifest of the same bank (src/expert/bank.zig:924-946): per record the v2 segment table at
+    absolute offsets, the digest of the record's logical bytes, the sidecar again."""
+    E = v2["dims"]["n_experts"]
+    recs = []
+    for r in v2["records"]:
+        l, e, off = r["layer"], r["expert"], r["sidecar_offset"]
+        segs = [{"component": sg["component"], "dtype": sg["dtype"], "length": sg["length"], "offset": off + sg["offset"],
+                 "shape": sg["shape"], "shard": v2["sidecar"]["file"], "tensor": f"layers.{l}.ffn.experts.{e}"}
+                for sg in v2["layers"][l]["segments"]]
+        recs.append({"expert": e, "layer": l, "logical_bytes": r["logical_bytes"], "segments": segs,
+                     "sha256": logical_shas[l * E + e], "sidecar_length": r["logical_bytes"], "sidecar_offset": off})
+    return {"artifact": {"record_count": len(recs)}, "format": "mtplx-expert-manifest-v1", "model_key": "synthetic",
+            "quantization": {"bits": 3, "group_size": 32, "mode": "exl3-mul1"}, "records": recs,
+            "shards": [{"name": v2["sidecar"]["file"], "size": v2["sidecar"]["size"]}],
+            "sidecar": dict(v2["sidecar"]), "source_repo": "synthetic"}
+
+
+def write_exl3_bank(directory, H, I, E, L, record_of, bits=None, v1=True):
+    """record_of(layer, expert) -> uint8 record (padded to the record stride); bits: K per layer; v1: also write the
+    runtime manifest the reference's Bank.open requires beside the v2 one."""
     directory = Path(directory)
     bits = list(bits) if bits is not None else [3] * L
-    shas = []
+    shas, lshas = [], []
     with open(directory / "experts.bin", "wb") as f:
         for l in range(L):
             g = O.exl3_geometry(H, I, bits[l])
@@ -62,8 +81,13 @@ def write_exl3_bank(directory, H, I, E, L, record_of, bits=None):
                 r = record_of(l, e)
                 rec[:r.size] = r
                 shas.append(hashlib.sha256(rec.tobytes()).hexdigest())
+                lshas.append(hashlib.sha256(rec[:int(g.logical_bytes)].tobytes()).hexdigest())
                 f.write(rec.tobytes())
-    (directory / "expert-manifest-v2.json").write_text(json.dumps(exl3_manifest(H, I, E, L, shas, bits), separators=(",", ":")))
+    v2 = exl3_manifest(H, I, E, L, shas, bits)
+    (directory / "expert-manifest-v2.json").write_text(json.dumps(v2, separators=(",", ":")))
+    if v1:
+        (directory / "expert-manifest.json").write_text(json.dumps(exl3_manifest_v1(v2, lshas), separators=(",", ":")))
+    return v2, lshas
 
 
 def fp4_manifest(H, I, E, L, nv, first=1, shas=None):

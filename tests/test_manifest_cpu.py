@@ -137,3 +137,109 @@ def test_peek_of_a_directory(tmp_path):
     assert "neither" in ei.value.msg
     (tmp_path / "expert-manifest-v2.json").write_text(json.dumps(bank_files.exl3_manifest(256, 128, 2, 1)))
     assert pkg.bank_peek(directory=tmp_path).hidden == 256
+
+
+def _small_bank(tmp_path, bits=(3, 2)):
+    import numpy as np
+    H, I, E, L = 256, 128, 3, len(bits)
+    recs = {(l, e): bank_files.O.exl3_synth_record(900 + 10 * l + e, H, I, 1.0, 0.02, K=bits[l]) for l in range(L) for e in range(E)}
+    v2, lshas = bank_files.write_exl3_bank(tmp_path, H, I, E, L, lambda l, e: recs[(l, e)], list(bits))
+    return v2, lshas, (H, I, E, L)
+
+
+def test_bank_open_without_a_device(tmp_path):
+    """Bank.open's checks with no device (src/expert/bank.zig:228-251): both manifests, the sidecar, every digest."""
+    pkg = load_package()
+    v2, lshas, (H, I, E, L) = _small_bank(tmp_path)
+    info = pkg.bank_verify(tmp_path)
+    assert (info.hidden, info.inter, info.n_experts, info.n_layers, info.bits_min, info.bits_max) == (H, I, E, L, 2, 3)
+    assert info.data_bytes == (tmp_path / "experts.bin").stat().st_size
+    # a flipped bit inside a record's logical bytes: both digests catch it; in the padding: only the v2 one exists for it
+    raw = bytearray((tmp_path / "experts.bin").read_bytes())
+    raw[100] ^= 1
+    (tmp_path / "experts.bin").write_bytes(bytes(raw))
+    with pytest.raises(pkg.MlxsError) as ei:
+        pkg.bank_verify(tmp_path)
+    assert "RecordSha256" in ei.value.msg and "record (0,0)" in ei.value.msg
+    assert pkg.bank_verify(tmp_path, verify_sha256=False).n_experts == E   # the geometry alone still opens
+
+
+def test_v1_runtime_manifest_refusals_by_name(tmp_path):
+    """The v1 half of the reference's refusal table (src/expert/bank.zig:1064-1072): no v1 manifest, another format,
+    another mode, a moved record, swapped segments, a gap, a short digest, a dropped record, a truncated file; and the
+    sidecar cases (missing, short, a symbolic link)."""
+    import os
+    pkg = load_package()
+    v2, lshas, (H, I, E, L) = _small_bank(tmp_path)
+    good = bank_files.exl3_manifest_v1(v2, lshas)
+    v1_path = tmp_path / "expert-manifest.json"
+
+    def refused(doc, words, text=None):
+        v1_path.write_text(text if text is not None else json.dumps(doc, separators=(",", ":")))
+        with pytest.raises(pkg.MlxsError) as ei:
+            pkg.bank_verify(tmp_path, verify_sha256=False)
+        assert ei.value.rc == -8 and words in ei.value.msg, (words, ei.value.msg)
+
+    def mutated(fn):
+        d = json.loads(json.dumps(good))
+        fn(d)
+        return d
+
+    v1_path.unlink()
+    with pytest.raises(pkg.MlxsError) as ei:
+        pkg.bank_verify(tmp_path)
+    assert "ManifestMissing" in ei.value.msg
+    refused(mutated(lambda d: d.update(format="mtplx-expert-manifest-v2")), "ManifestFormat")
+    refused(mutated(lambda d: d["quantization"].update(mode="tcq3")), "RuntimeModeNotExl3")
+    refused(mutated(lambda d: d["records"][E + 1].update(sidecar_offset=d["records"][E + 1]["sidecar_offset"] + 4096)),
+            "record (1,1) offset/length differs")
+
+    def swap(d):
+        sg = d["records"][2]["segments"]
+        sg[1], sg[2] = sg[2], sg[1]
+    refused(mutated(swap), "record (0,2) segments differ")
+    refused(mutated(lambda d: d["records"][1]["segments"][6].update(offset=d["records"][1]["segments"][6]["offset"] + 2)),
+            "record (0,1) segments differ")
+    refused(mutated(lambda d: d["records"][0].update(sha256="abcd")), "record (0,0) has no sha256")
+    refused(mutated(lambda d: d["records"].pop(E)), "RecordCount")
+    refused(mutated(lambda d: d["records"].__setitem__(1, d["records"][0])), "RecordDuplicate")
+    refused(mutated(lambda d: d["records"][0]["segments"][3].update(shard="other.bin")), 'reads shard "other.bin"')
+    refused(mutated(lambda d: d["sidecar"].update(size=d["sidecar"]["size"] + 4096)), "SidecarGeometry")
+    text = json.dumps(good, separators=(",", ":"))
+    refused(None, "ManifestSyntax", text=text[:text.index('},{"expert"') + 1])
+    # the good one opens again; then the sidecar cases
+    v1_path.write_text(text)
+    pkg.bank_verify(tmp_path)
+    side = tmp_path / "experts.bin"
+    data = side.read_bytes()
+    side.write_bytes(data[:-4096])
+    with pytest.raises(pkg.MlxsError) as ei:
+        pkg.bank_verify(tmp_path, verify_sha256=False)
+    assert "SidecarGeometry" in ei.value.msg
+    side.unlink()
+    with pytest.raises(pkg.MlxsError) as ei:
+        pkg.bank_verify(tmp_path, verify_sha256=False)
+    assert "cannot open" in ei.value.msg
+    (tmp_path / "real.bin").write_bytes(data)
+    os.symlink(tmp_path / "real.bin", side)
+    with pytest.raises(pkg.MlxsError) as ei:
+        pkg.bank_verify(tmp_path, verify_sha256=False)
+    assert "cannot open" in ei.value.msg and "SidecarOpen" in ei.value.msg
+
+
+@pytest.mark.parametrize("nv", [False, True])
+def test_fp4_bank_opens_without_a_device(tmp_path, nv):
+    import numpy as np
+    pkg = load_package()
+    H, I, E, L = 128, 64, 2, 2
+    O = bank_files.O
+    synth = O.nvfp4_synth_record if nv else O.mxfp4_synth_record
+    bank_files.write_fp4_bank(tmp_path, H, I, E, L, nv, lambda l, e: synth(50 + 7 * l + e, H, I, 0.02))
+    info = pkg.bank_verify(tmp_path)
+    assert (info.bank_kind, info.n_experts, info.n_layers) == (pkg.BANK_NVFP4 if nv else pkg.BANK_MXFP4, E, L)
+    raw = bytearray((tmp_path / "experts.bin").read_bytes())
+    raw[-1 if not nv else 10] ^= 4
+    (tmp_path / "experts.bin").write_bytes(bytes(raw))
+    with pytest.raises(pkg.MlxsError) as ei:
+        pkg.bank_verify(tmp_path)
+    assert "RecordSha256" in ei.value.msg
