@@ -419,6 +419,8 @@ int parse_text(const std::string& text, const char* name, Bank& b) {
     if (fmt == "mtplx-expert-manifest-v2") return parse_exl3(m, b);
     if (fmt == "mlx-stream-mxfp4-expert-bank-v1") return parse_fp4(m, b, false);
     if (fmt == "mlx-stream-nvfp4-expert-bank-v1") return parse_fp4(m, b, true);
+    if (fmt == "mtplx-expert-manifest-v1")
+        return mlxs_fail(MLXS_E_MANIFEST, "%s is the v1 runtime manifest of an EXL3 bank; its expert-manifest-v2.json cannot be read (ManifestMissing)", name);
     return mlxs_fail(MLXS_E_MANIFEST, "%s: format \"%s\" is none of the three bank formats", name, fmt.c_str());
 }
 

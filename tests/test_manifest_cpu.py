@@ -243,3 +243,48 @@ def test_fp4_bank_opens_without_a_device(tmp_path, nv):
     with pytest.raises(pkg.MlxsError) as ei:
         pkg.bank_verify(tmp_path)
     assert "RecordSha256" in ei.value.msg
+
+
+def test_v2_refusal_table_of_the_reference(tmp_path):
+    """The v2 half of the reference's refusal table (src/expert/bank.zig:1045-1063), each case on a bank that opens
+    before the mutation."""
+    import hashlib
+    pkg = load_package()
+    v2, lshas, (H, I, E, L) = _small_bank(tmp_path, bits=(3, 3))
+    v2_path = tmp_path / "expert-manifest-v2.json"
+    good = json.loads(v2_path.read_text())
+    pkg.bank_verify(tmp_path)
+
+    def refused(fn, words, text=None, verify=False):
+        d = json.loads(json.dumps(good))
+        if fn:
+            fn(d)
+        v2_path.write_text(text if text is not None else json.dumps(d, separators=(",", ":")))
+        with pytest.raises(pkg.MlxsError) as ei:
+            pkg.bank_verify(tmp_path, verify_sha256=verify)
+        assert ei.value.rc == -8 and words in ei.value.msg, (words, ei.value.msg)
+
+    text = json.dumps(good, separators=(",", ":"))
+    refused(None, "not a JSON object", text=text[:len(text) // 2])                                   # ManifestSyntax
+    refused(lambda d: d.update(format="mtplx-expert-manifest-v3"), "format")                        # ManifestFormat
+    refused(lambda d: d["quantization"].update(codebook="mcg"), 'codebook "mcg" not implemented')   # CodebookNotImplemented
+    refused(lambda d: d["quantization"].update(codebook_multiplier=0x83DCD12E), "codebook_multiplier")
+    refused(lambda d: d["dims"].update(hidden=72), "dims hidden=72")                                # DimsInvalid
+    refused(lambda d: d["layers"].pop(), "layer entries != dims.n_layers")                          # LayerGeometry
+    refused(lambda d: d["layers"][1].update(layer=5), "names layer 5")
+    refused(lambda d: d["layers"][0].update(K=4), "K 4 not implemented")                            # KNotImplemented
+    refused(lambda d: d["layers"][0]["segments"][0].update(length=d["layers"][0]["segments"][0]["length"] + 2), "its place")
+    refused(lambda d: d["layers"][1].update(base_offset=d["layers"][1]["base_offset"] + 4096), "layer 1 base_offset")
+    refused(lambda d: d["sidecar"].update(size=d["sidecar"]["size"] + 4096), "sidecar.size")        # SidecarGeometry
+    refused(lambda d: d["sidecar"].update(alignment=8192), "sidecar alignment 8192")
+    refused(lambda d: d["records"].pop(), "records !=")                                             # RecordCount
+    refused(lambda d: d["records"][0].update(expert=E), "out of range")                             # RecordGeometry
+    refused(lambda d: d["records"].__setitem__(1, d["records"][0]), "duplicated")                   # RecordDuplicate
+    refused(lambda d: d["records"][2].update(sidecar_offset=d["records"][2]["sidecar_offset"] + 4096), "offset/size differs")
+    refused(lambda d: d["records"][0].update(sha256=hashlib.sha256(b"x").hexdigest()), "RecordSha256", verify=True)
+    refused(lambda d: d["parity"].update(all_pass=False), "parity.all_pass")                        # ParityNotPassed
+    v2_path.unlink()
+    with pytest.raises(pkg.MlxsError) as ei:
+        pkg.bank_verify(tmp_path)
+    # without the v2 manifest the v1 one is not a bank description of its own
+    assert ei.value.rc == -8 and "ManifestMissing" in ei.value.msg
