@@ -8,6 +8,7 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <cctype>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
@@ -337,7 +338,7 @@ int parse_fp4(const JVal& m, Bank& b, bool nv) {
     const JVal* q = m.get("quantization");
     uint64_t bits = 0, gs = 0;
     if (gets(q, "mode") != tag || !geti(q, "bits", bits) || bits != 4 || !geti(q, "group_size", gs) || gs != (nv ? 16u : 32u))
-        return mlxs_fail(MLXS_E_MANIFEST, "%s: quantization mode \"%s\" bits %llu group_size %llu", tag, gets(q, "mode").c_str(), (unsigned long long)bits, (unsigned long long)gs);
+        return mlxs_fail(MLXS_E_MANIFEST, "%s: quantization mode \"%s\" bits %llu group_size %llu (InvalidQuantization)", tag, gets(q, "mode").c_str(), (unsigned long long)bits, (unsigned long long)gs);
     uint64_t H = 0, I = 0, E = 0, first = 0, L = 0, rb = 0, gub = 0;
     if (!geti(&m, "hidden_size", H) || !geti(&m, "intermediate_size", I) || !geti(&m, "num_experts", E) || !geti(&m, "first_moe_layer", first) ||
         !geti(&m, "num_moe_layers", L) || !H || !I || !E || !L || H % 32 || I % 32)
@@ -352,11 +353,11 @@ int parse_fp4(const JVal& m, Bank& b, bool nv) {
         if (!geti(&m, "record_stride", rs) || rs != stride) return mlxs_fail(MLXS_E_MANIFEST, "nvfp4: record_stride %llu != %llu", (unsigned long long)rs, (unsigned long long)stride);
         if (!geti(&m, "down_bytes", db) || db != part) return mlxs_fail(MLXS_E_MANIFEST, "nvfp4: down_bytes %llu != %llu", (unsigned long long)db, (unsigned long long)part);
     }
-    if (!geti(&m, "record_bytes", rb) || rb != logical) return mlxs_fail(MLXS_E_MANIFEST, "%s: record_bytes %llu != %llu", tag, (unsigned long long)rb, (unsigned long long)logical);
-    if (!geti(&m, "gate_up_bytes", gub) || gub != 2 * part) return mlxs_fail(MLXS_E_MANIFEST, "%s: gate_up_bytes %llu != %llu", tag, (unsigned long long)gub, (unsigned long long)(2 * part));
+    if (!geti(&m, "record_bytes", rb) || rb != logical) return mlxs_fail(MLXS_E_MANIFEST, "%s: record_bytes %llu != %llu (InvalidGeometry)", tag, (unsigned long long)rb, (unsigned long long)logical);
+    if (!geti(&m, "gate_up_bytes", gub) || gub != 2 * part) return mlxs_fail(MLXS_E_MANIFEST, "%s: gate_up_bytes %llu != %llu (InvalidGeometry)", tag, (unsigned long long)gub, (unsigned long long)(2 * part));
     const JVal* segs = m.get(nv ? "parts" : "segments");
     const size_t nseg = nv ? 9 : 6;
-    if (!segs || segs->kind != JVal::Arr || segs->arr.size() != nseg) return mlxs_fail(MLXS_E_MANIFEST, "%s: no %zu-part table", tag, nseg);
+    if (!segs || segs->kind != JVal::Arr || segs->arr.size() != nseg) return mlxs_fail(MLXS_E_MANIFEST, "%s: no %zu-part table (InvalidSegment)", tag, nseg);
     static const char* proj[3] = {"gate_proj", "up_proj", "down_proj"};
     uint64_t off = 0;
     for (int p = 0; p < 3; ++p) {
@@ -369,7 +370,7 @@ int parse_fp4(const JVal& m, Bank& b, bool nv) {
             const std::string want = std::string(proj[p]) + "." + names[j];
             uint64_t so = 0, sl = 0;
             if (gets(&s, "name") != want || gets(&s, "dtype") != dts[j] || !geti(&s, "offset", so) || !geti(&s, "length", sl) || so != off || sl != lens[j])
-                return mlxs_fail(MLXS_E_MANIFEST, "%s: part %s: its name, dtype or place", tag, want.c_str());
+                return mlxs_fail(MLXS_E_MANIFEST, "%s: part %s: its name, dtype or place (InvalidSegment)", tag, want.c_str());
             const JVal* shp = s.get("shape");
             bool shape_ok = shp && shp->kind == JVal::Arr;
             if (shape_ok) {
@@ -377,23 +378,25 @@ int parse_fp4(const JVal& m, Bank& b, bool nv) {
                 else if (j == 1) shape_ok = shp->arr.size() == 2 && shp->arr[0].u == rows && shp->arr[1].u == cols / blk;
                 else shape_ok = shp->arr.empty();
             }
-            if (!shape_ok) return mlxs_fail(MLXS_E_MANIFEST, "%s: part %s: its shape", tag, want.c_str());
+            if (!shape_ok) return mlxs_fail(MLXS_E_MANIFEST, "%s: part %s: its shape (InvalidSegment)", tag, want.c_str());
             off += lens[j];
         }
     }
     const JVal* src = m.get("source");
-    if (gets(src, "repository").empty() || gets(src, "revision").size() != 40) return mlxs_fail(MLXS_E_MANIFEST, "%s: source repository / revision", tag);
+    bool rev_hex = true;
+    for (char ch : gets(src, "revision")) rev_hex = rev_hex && isxdigit((unsigned char)ch);
+    if (gets(src, "repository").empty() || gets(src, "revision").size() != 40 || !rev_hex) return mlxs_fail(MLXS_E_MANIFEST, "%s: source repository / revision (InvalidSource)", tag);
     const JVal* recs = m.get("records");
-    if (!recs || recs->kind != JVal::Arr || recs->arr.size() != L * E) return mlxs_fail(MLXS_E_MANIFEST, "%s: %zu records != %llu", tag, recs ? recs->arr.size() : 0, (unsigned long long)(L * E));
+    if (!recs || recs->kind != JVal::Arr || recs->arr.size() != L * E) return mlxs_fail(MLXS_E_MANIFEST, "%s: %zu records != %llu (InvalidRecord)", tag, recs ? recs->arr.size() : 0, (unsigned long long)(L * E));
     b.records.assign(L * E, Record{});
     for (size_t i = 0; i < recs->arr.size(); ++i) {
         const JVal& r = recs->arr[i];
         uint64_t rl = 0, re = 0, ro = 0, rlen = 0;
         if (!geti(&r, "layer", rl) || !geti(&r, "expert", re) || !geti(&r, "offset", ro) || !geti(&r, "length", rlen) ||
             rl != first + i / E || re != i % E || ro != i * stride || rlen != logical)
-            return mlxs_fail(MLXS_E_MANIFEST, "%s: record %zu: its layer, expert or place", tag, i);
+            return mlxs_fail(MLXS_E_MANIFEST, "%s: record %zu: its layer, expert or place (InvalidRecord)", tag, i);
         b.records[i].sha256 = gets(&r, "sha256");
-        if (b.records[i].sha256.size() != 64) return mlxs_fail(MLXS_E_MANIFEST, "%s: record %zu has no sha256", tag, i);
+        if (b.records[i].sha256.size() != 64) return mlxs_fail(MLXS_E_MANIFEST, "%s: record %zu has no sha256 (InvalidDigest)", tag, i);
         b.records[i].offset = ro;
         b.records[i].present = true;
     }
@@ -402,7 +405,7 @@ int parse_fp4(const JVal& m, Bank& b, bool nv) {
     uint64_t sz = 0;
     const uint64_t total = nv ? L * E * stride : L * E * logical;
     if (!eb || !geti(eb, "size", sz) || sz != total || gets(eb, "sha256").size() != 64)
-        return mlxs_fail(MLXS_E_MANIFEST, "%s: output_files experts.bin size %llu != %llu", tag, (unsigned long long)sz, (unsigned long long)total);
+        return mlxs_fail(MLXS_E_MANIFEST, "%s: output_files experts.bin size %llu != %llu (InvalidOutputFile)", tag, (unsigned long long)sz, (unsigned long long)total);
     b.info.bank_kind = nv ? MLXS_BANK_NVFP4 : MLXS_BANK_MXFP4;
     b.info.hidden = H; b.info.inter = I; b.info.n_experts = E; b.info.n_layers = L; b.info.first_layer = first;
     b.info.logical_bytes = logical; b.info.record_stride = stride; b.info.data_bytes = total; b.info.has_sha256 = 1;

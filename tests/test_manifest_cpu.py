@@ -128,6 +128,25 @@ def test_fp4_manifests(nv):
     with pytest.raises(pkg.MlxsError) as ei:
         pkg.bank_peek(text=json.dumps(bad))
     assert "record 1" in ei.value.msg
+    # the reference's parse refusals by name (src/arch/mimo_v2/bank.zig:210-239, tests :397-403)
+    def refused(fn, name):
+        bad = json.loads(json.dumps(m))
+        fn(bad)
+        with pytest.raises(pkg.MlxsError) as ei:
+            pkg.bank_peek(text=json.dumps(bad))
+        assert name in ei.value.msg, (name, ei.value.msg)
+    table = "parts" if nv else "segments"
+    refused(lambda d: d["quantization"].update(mode="affine"), "InvalidQuantization")
+    refused(lambda d: d[table][0].update(dtype="U16"), "InvalidSegment")
+    refused(lambda d: d[table].pop(), "InvalidSegment")
+    refused(lambda d: d["records"][0].update(offset=4), "InvalidRecord")
+    refused(lambda d: d["records"].pop(), "InvalidRecord")
+    refused(lambda d: d["records"][0].update(sha256="12"), "InvalidDigest")
+    refused(lambda d: d["source"].update(revision="z" * 40), "InvalidSource")
+    refused(lambda d: d["source"].update(repository=""), "InvalidSource")
+    refused(lambda d: d["output_files"]["experts.bin"].update(size=1), "InvalidOutputFile")
+    refused(lambda d: d.update(output_files={}), "InvalidOutputFile")
+    refused(lambda d: d.update(record_bytes=d["record_bytes"] + 1), "InvalidGeometry")
 
 
 def test_peek_of_a_directory(tmp_path):
