@@ -163,7 +163,10 @@ int mlxs_moe_route(mlxs_moe *h, uint32_t layer, const float *logits_dev, uint32_
 int mlxs_moe_routed(mlxs_moe *h, uint32_t layer, const void *x_dev, const int32_t *ids_dev, uint32_t T,
                     float *out_dev, void *stream);
 /* Source.forward + forwardShared (src/arch/glm5_next/experts.zig:566-595, 639-653): x bf16 [T, hidden], ids, weights
- * -> y bf16 [T, hidden] (routed experts, weighted combine, + shared expert when configured). */
+ * -> y bf16 [T, hidden] (routed experts, weighted combine, + shared expert when configured).
+ * Everything is ordered on `stream`: the handle's own side streams (the shared expert beside the routed kernels, the
+ * tensor-core lane beside the streaming lane) fork from it by an event and join it before the result is written, so
+ * the caller sees one stream, and a call can be captured into a CUDA graph (one GPU). */
 int mlxs_moe_experts(mlxs_moe *h, uint32_t layer, const void *x_dev, const int32_t *ids_dev,
                      const float *weights_dev, uint32_t T, void *y_dev, void *stream);
 /* Tr.moe (src/arch/deepseek_v41/graph.zig:2196-2240) from the router's logits on: route + experts in one call; the
