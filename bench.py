@@ -1,15 +1,23 @@
-"""Benchmark of the routed-MoE layer (one "step" = one layer call over one batch of synthetic tokens).
+"""Benchmark of the routed-MoE layer (one "step" = one pass of the hot path over one batch of synthetic tokens).
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--tokens T] [--routing normal|zipf]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c4|c5|glm]
+                  [--tokens T] [--routing normal|zipf] [--layers L] [--placement contiguous|usage]
 
-Workload at N=1 (the benchmark list's first configuration after the CPU-runnable case, "c2"): DeepSeek-V4.1-Flash-shaped decode
-layer, EXL3 K=3 bank, hidden 5120, inter 2304, 256 routed experts, top-8, one bf16 shared expert, T = 64 tokens per
-call.  Weights are synthetic (seeded random trellis codes, +-(0.5+u) sign/scale vectors), activations bf16 N(0,1),
-logits N(0,1) or Zipf(1.1)-skewed.  Prints ONE JSON line (rank 0).
+Default workloads (the benchmark list's configurations; every flag above overrides a piece):
+  N = 1   "c2": the DeepSeek-V4.1-Flash-shaped decode layer, EXL3 K=3 bank, hidden 5120, inter 2304, 256 routed experts,
+          top-8, one bf16 shared expert, 64 tokens per call, N(0,1) logits, one layer.  The same run also measures the
+          24-layer Zipf stack of "c5" on the one GPU and reports it under "c5_stack" (skip with --no-stack).
+  N > 1   "c5": the expert-parallel stack of 24 such layers, experts sharded 256/N per GPU and placed by usage,
+          Zipf(1.1)-skewed routing, 64 tokens per rank per step (tokens data parallel, so the global batch is 64 N:
+          "weak" scaling in tokens while the bank is split N ways; per_gpu_hbm_frac and exchange.exposed_ms_per_step say
+          what each GPU streams and how long the exchange shows).
+Weights are synthetic (seeded random trellis codes, +-(0.5+u) sign/scale vectors; FP4: N(0, 0.02) quantised on the
+device), activations bf16 N(0,1).  Prints ONE JSON line (rank 0).
 
-`value` = tokens/s with inputs resident in HBM; `e2e` = the same through the host-buffer entry (mlxs_moe_forward_host,
-pinned host memory, copies inside the timed region); `roofline` = the gate/up streaming kernel against the measured
-HBM peak; `cpu_baseline` = the CPU oracle's fast f32 form on a bounded sample of the same workload.
+`value` = tokens/s with inputs resident in HBM; `e2e` = the same through host buffers (pinned memory, copies inside the
+timed region); `roofline` = the dominant kernel against the measured peak; `cpu_baseline` = the CPU oracle's fast f32
+form on a bounded sample of the same workload; `parity_check` = a handful of each rank's tokens of one timed batch
+against the CPU oracle, outside the timed region.  `--impl reference` times the CPU oracle alone on the same workload.
 """
 import argparse
 import ctypes as C
@@ -28,10 +36,8 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(ROOT / "tests"))
 
-H, I, E, K_TOP = 5120, 2304, 256, 8
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
-# secondary workloads (the MXFP4 and NVFP4 configurations of the benchmark list), selected with --workload
 WORKLOADS = {
     "c2": dict(name="c2: DeepSeek-V4.1-Flash-shaped routed MoE decode layer, EXL3 K=3 mul1 bank", H=5120, I=2304, E=256,
                k=8, bank="exl3", shared=True, scoring="sqrtsoftplus", scale=1.5, limit=10.0, chain=False),
@@ -39,11 +45,14 @@ WORKLOADS = {
                shared=False, scoring="softmax", scale=1.0, limit=0.0, chain=True),
     "c4": dict(name="c4: GLM-shaped routed MoE layer, NVFP4 bank", H=6144, I=2048, E=256, k=8, bank="nvfp4",
                shared=True, scoring="sigmoid", scale=1.0, limit=10.0, chain=True),
+    "c5": dict(name="c5: expert-parallel stack of DeepSeek-V4.1-Flash-shaped layers, EXL3 K=3 mul1 bank", H=5120, I=2304,
+               E=256, k=8, bank="exl3", shared=True, scoring="sqrtsoftplus", scale=1.5, limit=10.0, chain=False),
     # not in the benchmark list: the reference's other EXL3 shape (GLM-Flash experts, src/arch/glm5_next/exl3_forms_ref.zig:17-37)
     "glm": dict(name="glm: GLM-Flash-shaped routed MoE layer, EXL3 K=3 mul1 bank", H=4096, I=2048, E=256, k=8, bank="exl3",
                 shared=True, scoring="sigmoid", scale=2.5, limit=10.0, chain=False),
 }
-WL = WORKLOADS["c2"]
+LANE_MIN_ROWS = int(os.environ.get("MLXS_PREFILL_MIN_ROWS", "17"))  # the library's default lane threshold
+N_BATCHES = 4  # a few seeded batches in rotation, so that consecutive steps route differently
 
 
 def fp4_quantise_torch(torch, w, nv):
@@ -80,12 +89,13 @@ def peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         d = json.loads(p.read_text())
-        return float(d["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops_sustained", 1400.0)), "measured"
+    return 6650.0, 1400.0, "fallback"
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons during the timed region."""
+    """nvidia-smi clocks and throttle reasons; started before the warm-up so that even a timed region of a few
+    milliseconds has samples around it, and read back for the window of the timed region."""
 
     def __init__(self, index):
         self.index = index
@@ -106,16 +116,21 @@ class ClockSampler:
 
     def _read(self):
         for ln in self.proc.stdout:
-            self.lines.append(ln.strip())
+            self.lines.append((time.perf_counter(), ln.strip()))
 
-    def stop(self):
+    def window(self, t0, t1):
+        """Samples that arrived inside [t0, t1] (perf_counter); if the region was shorter than the sampling period, the
+        samples nearest to it."""
         if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.06)
+        rows = [(t, ln) for t, ln in list(self.lines)]
+        inside = [r for r in rows if t0 - 0.02 <= r[0] <= t1 + 0.04]
+        if not inside and rows:
+            inside = sorted(rows, key=lambda r: min(abs(r[0] - t0), abs(r[0] - t1)))[:2]
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        for _, ln in inside:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 7:
                 continue
@@ -130,8 +145,12 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "samples": len(sm), "reasons": sorted(reasons)}
 
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
 
-def zipf_bias(layer):
+
+def zipf_bias(E, layer):
     """ln p_e of a layer's expert popularity: p_e ~ rank^-1.1 over a permutation seeded by the layer, the same on every
     rank and for every batch (popularity is a property of the layer, which is what a usage-based placement relies on)."""
     perm = np.random.default_rng(4242 + layer).permutation(E)
@@ -140,125 +159,500 @@ def zipf_bias(layer):
     return np.log(p)[np.argsort(perm)].astype(np.float32)
 
 
-def make_logits(rng, T, routing, layer=0):
-    lg = rng.standard_normal((T, E)).astype(np.float32)
-    if routing == "zipf":
-        lg = lg + zipf_bias(layer)
-    return lg
+def workload_config(wl, E, T, layers, routing, gpus, placement):
+    return {"workload": wl["name"],
+            "hidden": wl["H"], "inter": wl["I"], "n_experts": E, "top_k": wl["k"],
+            "shared_expert": "bf16" if wl["shared"] else "none", "tokens_per_call": T,
+            "tokens_meaning": "per rank per step (tokens are data parallel)" if gpus > 1 else "per step",
+            "layers": layers, "routing": routing,
+            "l2": "inputs larger than L2 (each call streams far more distinct expert code than the 126 MB L2 holds)",
+            "parallelism": "single GPU" if gpus == 1 else f"ep{gpus}, experts placed: {placement}"}
 
 
-LANE_MIN_ROWS = int(os.environ.get("MLXS_PREFILL_MIN_ROWS", "17"))  # the library's default lane threshold
-
-
-def own_launches_per_layer(T, world):
-    """Kernels of this library one layer call launches (library GEMMs and NCCL kernels are not counted)."""
-    A = T * K_TOP
+def own_launches_per_layer(wl, T, world):
+    """Kernels of this library one layer call launches (NCCL's kernels are not counted)."""
+    A = T * wl["k"]
     n = 1                                   # router
     n += 3 if A > 2048 else 1               # dispatch: count / scan / place above 2048 rows, one CTA below
     n += 3                                  # streaming lane: prep, gate/up, down
-    # the lane's kernels launch when the local call has enough "tokens" for an expert to reach the threshold (with expert
-    # parallelism every received assignment is a token of the local call)
+    # the tensor-core lane's kernels launch when the local call has enough "tokens" for an expert to reach the threshold
+    # (with expert parallelism every received assignment is a token of the local call)
     if (T if world == 1 else A) >= LANE_MIN_ROWS:
-        n += 4 if WL["bank"] == "exl3" else 6   # plan, prep, gate/up, down (FP4: two tile shapes of each)
-    if WL["shared"]:
-        n += 2 if T <= 64 else 1            # skinny kernels, or the activation between the library GEMMs
+        n += 4 if wl["bank"] == "exl3" else 6   # plan, prep, gate/up, down (FP4: two tile shapes of each)
+    if wl["shared"]:
+        n += 2                              # gate/up + activation, down
     n += 1                                  # combine
     if world > 1:
-        n += 4                              # destination ranks, rank sort, gather, scatter
+        n += 6                              # destination ranks, rank sort, dedup, gather, rebase / partial, final sum
     return n
 
 
-def reference_arm(args):
-    """The reference's CPU path for this layer, timed on the host cores.  The reference's own CPU lane (Zig tests over
-    MLX's CPU device) cannot be built here (no zig, no mlx), so this runs the oracle's fast f32 form (kind "port")."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+# ----------------------------------------------------------------------------------------------------------------
+# the reference arm: the CPU oracle alone
+# ----------------------------------------------------------------------------------------------------------------
+def reference_arm(args, wl, E):
+    """The reference's CPU path for this workload, timed on the host cores.  The reference's own CPU lane (Zig tests
+    over MLX's CPU device) cannot be built here (no zig, no mlx), so this runs the oracle's fast f32 form (kind "port")
+    on the same shapes, token count and routing as the GPU arm.  A stack is sampled: as many of its layers per step as
+    fit the time budget, scaled to the whole stack."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    # all host threads this process may use (a launcher may have set OMP_NUM_THREADS=1 for its ranks)
     threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
-    os.environ["OMP_NUM_THREADS"] = str(threads)
+    os.environ["OMP_NUM_THREADS"] = str(threads)   # a launcher may have set 1 for its ranks
     import oracle_lib as O
+    H, I, K = wl["H"], wl["I"], wl["k"]
+    # the whole job's batch: with N ranks the GPU arm runs `tokens` per rank per step, N x tokens in all
+    T, NL = args.tokens * max(args.gpus, 1), args.layers
     rng = np.random.default_rng(1234)
     srng = np.random.default_rng(7)
     shared = None
-    if WL["shared"]:
-        shared = [O.f32_to_bf16_bits((srng.standard_normal(s) * 0.02).astype(np.float32))
-                  for s in ((I, H), (I, H), (H, I))]
-    if WL["bank"] == "exl3":
-        T = args.cpu_tokens
-        lg = make_logits(rng, T, args.routing)
-        ids, w = O.route(lg, None, K_TOP, O.SCORE_SQRTSOFTPLUS, scale=1.5)
-        recs = {int(e): O.exl3_synth_record(0xB200 + int(e), H, I, 1.0, 0.02) for e in np.unique(ids)}
-        x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(rng.standard_normal((T, H)).astype(np.float32)))
-        call = lambda: O.layer_fast(H, I, E, K_TOP, recs, x, ids, w, shared=shared, threads=threads)
-        form = "oracle fast f32 form"
-    else:
-        # FP4 banks: the oracle's f64 layer over exactly decoded weights (there is no faster CPU form of it)
-        T = min(args.cpu_tokens, 2)
-        nv = WL["bank"] == "nvfp4"
-        lg = make_logits(rng, T, args.routing)
-        ids, w = O.route(lg, None, K_TOP, O.SCORE_SIGMOID if nv else O.SCORE_SOFTMAX, scale=1.0)
-        synth = O.nvfp4_synth_record if nv else O.mxfp4_synth_record
-        recs = {int(e): synth(0xB200 + int(e), H, I, 0.02) for e in np.unique(ids)}
-        x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(rng.standard_normal((T, H)).astype(np.float32)))
-        bank = O.BANK_NVFP4 if nv else O.BANK_MXFP4
-        call = lambda: O.layer(bank, H, I, E, K_TOP, recs, x, ids, w, shared=shared, limit=10.0 if nv else 0.0,
-                               chain_rounding=True, shared_bf16_add=True)
-        form = "oracle f64 form"
+    if wl["shared"]:
+        shared = [O.f32_to_bf16_bits((srng.standard_normal(s) * 0.02).astype(np.float32)) for s in ((I, H), (I, H), (H, I))]
+    exl3 = wl["bank"] == "exl3"
+    if not exl3:
+        T = min(T, 2)   # FP4 banks: only the f64 oracle exists on the CPU; a two-token sample of the call
+    score = {"sqrtsoftplus": O.SCORE_SQRTSOFTPLUS, "sigmoid": O.SCORE_SIGMOID, "softmax": O.SCORE_SOFTMAX}[wl["scoring"]]
+    x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(rng.standard_normal((T, H)).astype(np.float32)))
+    noise = rng.standard_normal((T, E)).astype(np.float32)
+    recs_cache = {}
+
+    def layer_inputs(l):
+        lg = noise + zipf_bias(E, l) if args.routing == "zipf" else noise
+        ids, w = O.route(lg, None, K, score, scale=wl["scale"])
+        for e in np.unique(ids):
+            e = int(e)
+            if e not in recs_cache:
+                recs_cache[e] = (O.exl3_synth_record(0xB200 + e, H, I, 1.0, 0.02) if exl3 else
+                                 (O.nvfp4_synth_record if wl["bank"] == "nvfp4" else O.mxfp4_synth_record)(0xB200 + e, H, I, 0.02))
+        return ids, w
+
+    def run_layer(l, ids, w):
+        recs = {int(e): recs_cache[int(e)] for e in np.unique(ids)}
+        if exl3:
+            return O.layer_fast(H, I, E, K, recs, x, ids, w, shared=shared, limit=wl["limit"], threads=threads)
+        bank = O.BANK_NVFP4 if wl["bank"] == "nvfp4" else O.BANK_MXFP4
+        return O.layer(bank, H, I, E, K, recs, x, ids, w, shared=shared, limit=wl["limit"], chain_rounding=True,
+                       shared_bf16_add=True)
+
+    # size the sample: one layer call first, then as many layers per step as the budget allows
+    first = layer_inputs(0)
+    t0 = time.perf_counter()
+    run_layer(0, *first)
+    t_layer = time.perf_counter() - t0
+    budget_s = float(os.environ.get("MLXS_REF_BUDGET_S", "200"))
+    calls = args.steps + args.warmup
+    ls = int(max(1, min(NL, budget_s / max(t_layer * calls, 1e-9))))
+    plan = [layer_inputs(l) for l in range(ls)]
+    distinct = float(np.mean([len(np.unique(p[0])) for p in plan]))
     for _ in range(args.warmup):
-        call()
+        for l in range(ls):
+            run_layer(l, *plan[l])
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        call()
+        for l in range(ls):
+            run_layer(l, *plan[l])
     dt = time.perf_counter() - t0
-    v = T * args.steps / dt
-    sample = f"{T} tokens x top-{K_TOP} per step ({len(recs)} distinct experts), whole layer, {form}"
+    ms_step = 1e3 * dt / args.steps * (NL / ls)      # the sampled layers scaled to the stack
+    v = T / (ms_step * 1e-3)
+    sample = (f"{T} tokens (the global batch of {max(args.gpus, 1)} rank(s)) x top-{K} per layer call ({distinct:.0f} distinct experts per call), {ls} of {NL} layer(s) timed per "
+              f"step and scaled to {NL}, whole layer incl. shared expert, oracle {'fast f32' if exl3 else 'f64'} form, OpenMP")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32" if WL["bank"] == "exl3" else "f64", "data": "synthetic",
-        "config": workload_config(args, T),
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32" if exl3 else "f64", "data": "synthetic",
+        "config": workload_config(wl, E, args.tokens, NL, args.routing, args.gpus, args.placement),
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
-def workload_config(args, T):
-    return {"workload": WL["name"],
-            "hidden": H, "inter": I, "n_experts": E, "top_k": K_TOP, "shared_expert": "bf16" if WL["shared"] else "none",
-            "tokens_per_call": T,
-            "layers": getattr(args, "layers", 1), "routing": args.routing, "l2": "inputs larger than L2 (each call streams >2 GB of distinct expert code)",
-            "parallelism": "single GPU" if args.gpus == 1 else f"ep{args.gpus}, experts placed: {getattr(args, 'placement', 'contiguous')}"}
+# ----------------------------------------------------------------------------------------------------------------
+# the GPU arm
+# ----------------------------------------------------------------------------------------------------------------
+class Rig:
+    """One handle with its synthetic bank, batches and step functions."""
+
+    def __init__(self, env, wl, E, T, NL, routing, placement):
+        torch, pkg, dev = env["torch"], env["pkg"], env["dev"]
+        self.env, self.wl, self.E, self.T, self.NL, self.routing = env, wl, E, T, NL, routing
+        world, rank = env["world"], env["rank"]
+        H, I, K = wl["H"], wl["I"], wl["k"]
+        bank_kind = {"exl3": pkg.BANK_EXL3_K3_MUL1, "mxfp4": pkg.BANK_MXFP4, "nvfp4": pkg.BANK_NVFP4}[wl["bank"]]
+        scoring = {"sqrtsoftplus": pkg.SCORE_SQRTSOFTPLUS, "sigmoid": pkg.SCORE_SIGMOID, "softmax": pkg.SCORE_SOFTMAX}[wl["scoring"]]
+        cfg = pkg.make_config(H, I, E, K, n_layers=NL, bank_kind=bank_kind,
+                              act=pkg.ACT_SWIGLU_CLAMPED if wl["limit"] > 0 else pkg.ACT_SWIGLU, act_limit=wl["limit"],
+                              scoring=scoring, norm_topk=True, routed_scale=wl["scale"], shared_expert=wl["shared"],
+                              combine=pkg.COMBINE_CHAIN if wl["chain"] else pkg.COMBINE_F32, max_tokens=max(T, 64),
+                              device=env["local"], ep_world=world, ep_rank=rank)
+        self.moe = moe = pkg.MoE(cfg)
+        dist = env["dist"]
+        if world > 1:
+            # the NCCL id of the library's own communicator travels through torch.distributed
+            idt = torch.zeros(128, dtype=torch.uint8, device=dev)
+            if rank == 0:
+                buf = (C.c_char * 128)()
+                if pkg.lib().mlxs_moe_ep_unique_id(buf) != 0:
+                    raise SystemExit("bench.py: " + pkg.last_error())
+                idt.copy_(torch.frombuffer(bytearray(bytes(buf)), dtype=torch.uint8))
+            dist.broadcast(idt, 0)
+            if pkg.lib().mlxs_moe_ep_init(moe._h, bytes(idt.cpu().numpy().tobytes())) != 0:
+                raise SystemExit("bench.py: " + pkg.last_error())
+        rng = np.random.default_rng(99 + rank)
+        g = torch.Generator(device=dev)
+        g.manual_seed(1000 + rank)
+        self.xs, self.lgs, self.x_host, self.lg_host = [], [], [], []
+        biases = [torch.from_numpy(zipf_bias(E, l)).to(dev) for l in range(NL)] if routing == "zipf" else None
+        for b in range(N_BATCHES):
+            noise = rng.standard_normal((T, E)).astype(np.float32)
+            x = torch.randn((T, H), device=dev, generator=g).to(torch.bfloat16)
+            self.xs.append(x)
+            nd = torch.from_numpy(noise).to(dev)
+            # logits of (batch, layer): the batch's noise + the layer's popularity (one tensor for all layers without skew)
+            self.lgs.append([nd + biases[l] for l in range(NL)] if biases else [nd] * NL)
+            self.x_host.append(x.cpu().pin_memory())
+            self.lg_host.append(self.lgs[b][0].cpu().pin_memory())
+        self.stream = torch.cuda.current_stream()
+        self.sp = self.stream.cuda_stream
+
+        # where the experts live: contiguous blocks, or dealt out by usage: the library's tally counts the routed ids of
+        # the batches on the device, sums them over the ranks, and its planner deals the experts out
+        rank_of = [np.arange(E) // (E // world) for _ in range(NL)]
+        if world > 1 and placement == "usage":
+            ids_dev = torch.empty((T, K), dtype=torch.int32, device=dev)
+            w_dev = torch.empty((T, K), dtype=torch.float32, device=dev)
+            moe.usage_enable(True)
+            for l in range(NL):
+                for b in range(N_BATCHES):
+                    moe.route(l, self.lgs[b][l].data_ptr(), T, ids_dev.data_ptr(), w_dev.data_ptr(), self.sp)
+                torch.cuda.synchronize()
+                ro = np.asarray(pkg.plan_placement(moe.usage_read(l, all_ranks=True), world), np.uint16)
+                rank_of[l] = ro.astype(np.int64)
+                moe.set_placement(l, np.ascontiguousarray(ro).ctypes.data)
+            moe.usage_enable(False)
+        self.owned = [np.nonzero(rank_of[l] == rank)[0] for l in range(NL)]
+        self.logical, self.stride = moe.record_bytes()
+        self._rec_cache = {}
+        for l in range(NL):
+            for e in self.owned[l]:
+                rec = self.expert_record(int(e))
+                moe.load_expert(l, int(e), rec.data_ptr(), rec.numel(), on_device=True)
+        self._rec_cache.clear()
+        self.sw = None
+        if wl["shared"]:
+            self.sw = [(torch.randn(s, device=dev, generator=g) * 0.02).to(torch.bfloat16) for s in ((I, H), (I, H), (H, I))]
+            for l in range(NL):
+                moe.set_shared(l, self.sw[0].data_ptr(), self.sw[1].data_ptr(), self.sw[2].data_ptr(), on_device=True)
+        self.y = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+        self.y2 = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+        self.y_host = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
+        self.x_in = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+        self.lg_in = torch.empty((T, E), dtype=torch.float32, device=dev)
+
+    def expert_record(self, e):
+        """The synthetic record of expert e in the reference's layout, a function of e alone (every rank and the parity
+        check can regenerate it; the layers of a stack hold the same image)."""
+        if e in self._rec_cache:
+            return self._rec_cache[e]
+        torch, dev, wl = self.env["torch"], self.env["dev"], self.wl
+        H, I = wl["H"], wl["I"]
+        g = torch.Generator(device=dev)
+        g.manual_seed(0xB2000 + e)
+        if wl["bank"] == "exl3":
+            code_bytes = (H // 16) * (I // 16) * 96
+            rec = torch.randint(0, 256, (self.stride,), dtype=torch.uint8, device=dev, generator=g)
+            off = 0
+            for p in range(3):
+                off += code_bytes
+                n_out, n_in = (H, I) if p == 2 else (I, H)
+                for n, sc in ((n_out, 0.02), (n_in, 1.0)):
+                    u = torch.rand(n, device=dev, generator=g)
+                    sgn = torch.where(torch.rand(n, device=dev, generator=g) < 0.5, -1.0, 1.0)
+                    rec[off:off + 2 * n] = ((0.5 + u) * sgn * sc).to(torch.float16).view(torch.uint8)
+                    off += 2 * n
+        else:
+            nv = wl["bank"] == "nvfp4"
+            parts = []
+            for p in range(3):
+                rows, cols = (H, I) if p == 2 else (I, H)
+                w = torch.randn((rows, cols), device=dev, generator=g) * 0.02
+                words, sbytes, gs = fp4_quantise_torch(torch, w, nv)
+                parts += [words.view(torch.uint8).reshape(-1), sbytes.reshape(-1)]
+                if nv:
+                    parts.append(gs.to(torch.float32).reshape(1).view(torch.uint8))
+            rec = torch.cat(parts)
+            assert rec.numel() == self.logical, (rec.numel(), self.logical)
+        if len(self._rec_cache) < 300:
+            self._rec_cache[e] = rec
+        return rec
+
+    def step(self, i):
+        # a stack feeds each layer's output to the next one (the trunk between MoE layers is out of scope); every
+        # layer routes with its own seeded logits
+        src, a, b = self.xs[i % N_BATCHES], self.y, self.y2
+        for l in range(self.NL):
+            self.moe.forward(l, src.data_ptr(), self.lgs[(i + l) % N_BATCHES][l].data_ptr(), self.T, a.data_ptr(), self.sp)
+            src, a, b = a, b, a
+
+    def step_host(self, i):
+        if self.NL == 1:
+            self.moe.forward_host(0, self.x_host[i % N_BATCHES].data_ptr(), self.lg_host[i % N_BATCHES].data_ptr(), self.T,
+                                  self.y_host.data_ptr(), self.sp)
+            return
+        # a stack: the step's inputs come from pinned host memory, the last layer's output goes back
+        self.x_in.copy_(self.x_host[i % N_BATCHES], non_blocking=True)
+        self.lg_in.copy_(self.lg_host[i % N_BATCHES], non_blocking=True)
+        src, a, b = self.x_in, self.y, self.y2
+        for l in range(self.NL):
+            lg = self.lg_in if l == 0 else self.lgs[(i + l) % N_BATCHES][l]
+            self.moe.forward(l, src.data_ptr(), lg.data_ptr(), self.T, a.data_ptr(), self.sp)
+            src, a, b = a, b, a
+        self.y_host.copy_(src, non_blocking=True)
+        self.stream.synchronize()
+
+    def barrier(self):
+        if self.env["world"] > 1:
+            self.env["dist"].barrier()
+        self.env["torch"].cuda.synchronize()
+
+    def timed(self, fn, steps):
+        torch = self.env["torch"]
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record(self.stream)
+        for i in range(steps):
+            fn(i)
+        e1.record(self.stream)
+        self.barrier()
+        t1 = time.perf_counter()
+        ms = e0.elapsed_time(e1)
+        if self.env["world"] > 1:
+            t = torch.tensor([ms], device=self.env["dev"])
+            self.env["dist"].all_reduce(t, op=self.env["dist"].ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, (t0, t1)
+
+    def row_counts(self):
+        """rows per expert this rank serves, per (batch, layer): from the routed ids of every rank's tokens"""
+        torch, dev, dist = self.env["torch"], self.env["dev"], self.env["dist"]
+        world, K, E, T = self.env["world"], self.wl["k"], self.E, self.T
+        ids_dev = torch.empty((T, K), dtype=torch.int32, device=dev)
+        w_dev = torch.empty((T, K), dtype=torch.float32, device=dev)
+        out = []
+        for b in range(N_BATCHES):
+            per_layer = []
+            for l in range(self.NL):
+                self.moe.route(l, self.lgs[b][l].data_ptr(), T, ids_dev.data_ptr(), w_dev.data_ptr(), self.sp)
+                all_ids = ids_dev
+                if world > 1:
+                    all_ids = torch.empty((world * T, K), dtype=torch.int32, device=dev)
+                    dist.all_gather_into_tensor(all_ids, ids_dev)
+                cnt = torch.bincount(all_ids.reshape(-1).long(), minlength=E).cpu().numpy()
+                per_layer.append(cnt[self.owned[l]])
+            out.append(per_layer)
+        return out
+
+    def parity_check(self, n_tok=4):
+        """A few of this rank's tokens of batch 0 through layer 0 (the whole batch runs, every rank takes part in the
+        exchange) against the CPU oracle over the touched experts.  Outside the timed region."""
+        import oracle_lib as O
+        torch, dev, wl = self.env["torch"], self.env["dev"], self.wl
+        H, I, K, E, T = wl["H"], wl["I"], wl["k"], self.E, self.T
+        n_tok = min(n_tok, T)
+        ids_dev = torch.empty((T, K), dtype=torch.int32, device=dev)
+        w_dev = torch.empty((T, K), dtype=torch.float32, device=dev)
+        self.moe.route(0, self.lgs[0][0].data_ptr(), T, ids_dev.data_ptr(), w_dev.data_ptr(), self.sp)
+        self.moe.forward(0, self.xs[0].data_ptr(), self.lgs[0][0].data_ptr(), T, self.y.data_ptr(), self.sp)
+        torch.cuda.synchronize()
+        ids = ids_dev[:n_tok].cpu().numpy()
+        w = w_dev[:n_tok].cpu().numpy()
+        got = self.y[:n_tok].float().cpu().numpy()
+        x = self.xs[0][:n_tok].float().cpu().numpy()
+        self._rec_cache.clear()
+        recs = {}
+        for e in np.unique(ids):
+            r = self.expert_record(int(e)).cpu().numpy()
+            self._rec_cache.clear()
+            recs[int(e)] = r
+        shared = [s.view(torch.int16).cpu().numpy().view(np.uint16) for s in self.sw] if self.sw else None
+        if wl["bank"] == "exl3":
+            ref = O.layer_fast(H, I, E, K, recs, x, ids, w, shared=shared, limit=wl["limit"], threads=0)
+        else:
+            bank = O.BANK_NVFP4 if wl["bank"] == "nvfp4" else O.BANK_MXFP4
+            ref = O.layer(bank, H, I, E, K, recs, x, ids, w, shared=shared, limit=wl["limit"], chain_rounding=wl["chain"],
+                          shared_bf16_add=wl["chain"])
+        ref = np.asarray(ref, np.float64)
+        rel = float(np.linalg.norm(got - ref) / (np.linalg.norm(ref) + 1e-30))
+        world = self.env["world"]
+        if world > 1:
+            t = torch.tensor([rel], device=dev, dtype=torch.float64)
+            self.env["dist"].all_reduce(t, op=self.env["dist"].ReduceOp.MAX)
+            rel = float(t.item())
+        return {"rel_l2": rel, "tokens": n_tok * world, "ranks": world, "bar": 1e-2,
+                "against": "CPU oracle (fast f32 form) over the touched experts; layer 0, batch 0; max over ranks"}
+
+    def close(self):
+        self.moe.close()
+
+
+def measure(rig, args, sampler, want_e2e=True):
+    """Warm-up, the timed steps with per-stage spans, the host-buffer form; returns the pieces of the JSON line."""
+    env, wl = rig.env, rig.wl
+    torch = env["torch"]
+    world = env["world"]
+    H, I, K, E, T, NL = wl["H"], wl["I"], wl["k"], rig.E, rig.T, rig.NL
+    for i in range(args.warmup):
+        rig.step(i)
+    counts = rig.row_counts()                      # [batch][layer] -> rows per resident expert
+    moe = rig.moe
+    moe.profile_enable(True)
+    moe.profile_read()
+    ms, window = rig.timed(rig.step, args.steps)
+    prof = moe.profile_read()
+    moe.profile_enable(False)
+    clocks = sampler.window(*window) if sampler else None
+    graph_ms = None
+    if args.graph and world == 1:
+        side = torch.cuda.Stream()
+        graphs = []
+        for b in range(N_BATCHES):
+            gph = torch.cuda.CUDAGraph()
+            side.wait_stream(rig.stream)
+            with torch.cuda.graph(gph, stream=side):
+                cs = torch.cuda.current_stream().cuda_stream
+                src, a, bb = rig.xs[b], rig.y, rig.y2
+                for l in range(NL):
+                    moe.forward(l, src.data_ptr(), rig.lgs[(b + l) % N_BATCHES][l].data_ptr(), T, a.data_ptr(), cs)
+                    src, a, bb = a, bb, a
+            graphs.append(gph)
+        for i in range(args.warmup):
+            graphs[i % N_BATCHES].replay()
+        graph_ms, _ = rig.timed(lambda i: graphs[i % N_BATCHES].replay(), args.steps)
+    ms_host = None
+    if want_e2e:
+        for i in range(args.warmup):
+            rig.step_host(i)
+        ms_host, _ = rig.timed(rig.step_host, args.steps)
+    st = moe.stats()
+    if st.device_status != 0:
+        raise SystemExit(f"bench.py: device status {st.device_status}")
+
+    # which (batch, layer) each timed layer call ran: step i, layer l uses batch (i + l) % N_BATCHES
+    def mean_over_calls(fn):
+        tot = 0.0
+        for i in range(args.steps):
+            for l in range(NL):
+                tot += fn(counts[(i + l) % N_BATCHES][l])
+        return tot / args.steps     # per step (summed over the stack's layers)
+
+    distinct_step = mean_over_calls(lambda c: float((c > 0).sum()))
+    light_step = mean_over_calls(lambda c: float(((c > 0) & (c < LANE_MIN_ROWS)).sum()) if T >= LANE_MIN_ROWS or world > 1 else float((c > 0).sum()))
+    rows_heavy = mean_over_calls(lambda c: float(c[c >= LANE_MIN_ROWS].sum()))
+    rows_served = mean_over_calls(lambda c: float(c.sum()))
+    if wl["bank"] == "exl3":
+        code_bytes = (H // 16) * (I // 16) * 96
+        gu_bytes = 2 * code_bytes + 2 * (2 * I + 2 * H)  # one expert's gate + up code and sign/scale vectors
+        kname = "exl3_gemv_kernel<2,gate_up>"
+        traffic_ratio = 1.014  # dram read+write / algorithmic bytes of the ncu capture on the small case (profiles/)
+    else:
+        gu_bytes = 2 * (H * I // 2 + H * I // (16 if wl["bank"] == "nvfp4" else 32))  # gate + up codes and block scales
+        kname = "fp4_gemv_kernel<2>"
+        traffic_ratio = 1.003
+    hbm_peak, tpeak, which = peaks()
+    gu_ms, gu_n = prof["gate_up"]
+    per_launch_s = gu_ms / max(gu_n, 1) * 1e-3
+    streamed_per_launch = light_step / NL      # experts the streaming lane serves per layer call (the others take the tensor lane)
+    achieved = streamed_per_launch * gu_bytes / max(per_launch_s, 1e-12) / 1e9
+    tl_ms, tl_n = prof.get("tensor_lane", (0.0, 0))
+    prefill_lane = tl_n > 0 and rows_heavy > 0.5 * rows_served
+    shared_bytes = 3 * H * I * 2 if wl["shared"] else 0
+    step_bytes = distinct_step * rig.logical + NL * (shared_bytes + T * H * 2 * 2 + T * E * 4)
+    step_s = ms / args.steps * 1e-3
+    if world > 1:
+        t = torch.tensor([step_bytes], device=env["dev"], dtype=torch.float64)
+        env["dist"].all_reduce(t)
+        step_bytes_mean = float(t.item()) / world
+    else:
+        step_bytes_mean = step_bytes
+    out = {
+        "value": world * T * args.steps / (ms * 1e-3), "ms_per_step": ms / args.steps,
+        "layer_hbm": {"algorithmic_bytes_per_step_per_gpu": step_bytes_mean, "gb_s_per_gpu": step_bytes_mean / step_s / 1e9,
+                      "frac_of_measured_peak": step_bytes_mean / step_s / 1e9 / hbm_peak,
+                      "frac_of_nominal_8000": step_bytes_mean / step_s / 1e9 / 8000.0,
+                      "distinct_experts_per_layer_call_rank0": distinct_step / NL},
+        "per_gpu_hbm_frac": step_bytes_mean / step_s / 1e9 / hbm_peak,
+        "roofline": {"kernel": kname, "bound": "hbm", "achieved": achieved, "peak": hbm_peak,
+                     "peak_source": which, "unit": "GB/s", "frac": achieved / hbm_peak,
+                     "traffic": traffic_ratio * streamed_per_launch * gu_bytes,
+                     "traffic_note": "ncu dram bytes of a smaller case (64 experts, 16 tokens) scaled by the experts streamed",
+                     "algorithmic_bytes_per_launch": streamed_per_launch * gu_bytes,
+                     "experts_streamed_per_launch": streamed_per_launch, "launch_ms": per_launch_s * 1e3},
+        "stage_ms_per_step": {k: v[0] / max(args.steps, 1) for k, v in prof.items()
+                              if v[1] and not (k == "tensor_lane" and rows_heavy == 0)},
+        "gpu_launches": NL * own_launches_per_layer(wl, T, world) * args.steps,
+        "graph_replay": None if graph_ms is None else {"ms_per_step": graph_ms / args.steps,
+                                                        "value": T * args.steps / (graph_ms * 1e-3), "unit": UNIT},
+        "exchange": None if world == 1 else {
+            "exposed_ms_per_step": prof["exchange"][0] / max(args.steps, 1),
+            "frac_of_step": prof["exchange"][0] / max(args.steps, 1) / (ms / args.steps),
+            "bytes_sent_per_layer_call_rank0": st.a2a_bytes_sent / max(st.expert_calls, 1),
+            "note": "CUDA-event span of the dispatch and combine exchanges on rank 0; with skewed routing it contains the wait for the busiest rank"},
+        "clocks": clocks,
+    }
+    if ms_host is not None:
+        out["e2e"] = {"value": world * T * args.steps / (ms_host * 1e-3), "unit": UNIT,
+                      "h2d_bytes_per_step": T * H * 2 + T * E * 4, "d2h_bytes_per_step": T * H * 2 + 4}
+    if prefill_lane:
+        # prefill-sized call: the tcgen05 lane (gate/up and down launches are timed together); tensor roofline
+        flops = 6.0 * H * I * rows_heavy / NL
+        tf = flops / (tl_ms / max(tl_n, 1) * 1e-3) / 1e12
+        out["roofline"] = {"kernel": ("exl3_prefill_kernel" if wl["bank"] == "exl3" else "fp4_prefill_kernel") + "<gate/up> + <down> (tcgen05)",
+                           "bound": "tensor", "achieved": tf, "peak": tpeak,
+                           "peak_source": "measured sustained bf16" if which == "measured" else "fallback", "unit": "TFLOP/s",
+                           "frac": tf / tpeak, "traffic": None, "flops_per_launch_pair": flops,
+                           "rows_in_lane_per_layer_call": rows_heavy / NL, "rows_served_per_layer_call": rows_served / NL}
+    return out
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--tokens", type=int, default=64)
-    ap.add_argument("--cpu-tokens", type=int, default=8)
-    ap.add_argument("--routing", default="normal", choices=["normal", "uniform", "zipf"])
+    ap.add_argument("--cpu-tokens", type=int, default=8, help="tokens of the cpu_baseline sample inside the GPU arm")
+    ap.add_argument("--routing", default=None, choices=["normal", "uniform", "zipf"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--no-stack", action="store_true", help="N = 1: skip the 24-layer stack measured beside the layer")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of a few tokens")
     ap.add_argument("--experts", type=int, default=0, help="routed experts (smaller only for profiler captures)")
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--graph", action="store_true", help="also time the steps replayed from CUDA graphs (one GPU)")
-    ap.add_argument("--placement", default="contiguous", choices=["contiguous", "usage"],
+    ap.add_argument("--placement", default=None, choices=["contiguous", "usage"],
                     help="expert parallel: experts in contiguous blocks, or dealt to the ranks by a routing histogram")
-    ap.add_argument("--layers", type=int, default=1,
-                    help="stack of identical-shape layers run back to back per step (the stack configuration of the benchmark list uses 24)")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="stack of identical-shape layers run back to back per step (the stack configuration uses 24)")
     args = ap.parse_args()
+    default_workload = args.workload is None
+    if args.workload is None:
+        args.workload = "c2" if args.gpus == 1 else "c5"
+    stack = args.workload == "c5"
+    if args.routing is None:
+        args.routing = "zipf" if stack else "normal"
+    if args.layers == 0:
+        args.layers = 24 if stack else 1
+    if args.placement is None:
+        args.placement = "usage" if (stack and args.gpus > 1) else "contiguous"
     wl = WORKLOADS[args.workload]
-    globals().update(WL=wl, H=wl["H"], I=wl["I"], E=args.experts or wl["E"], K_TOP=wl["k"])
+    E = args.experts or wl["E"]
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
     if args.impl == "reference":
-        args.steps = min(args.steps, 3)
-        return reference_arm(args)
+        return reference_arm(args, wl, E)
 
-    # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION/INFO; the contract is one JSON line
-    if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO", "TRACE"):
-        os.environ["NCCL_DEBUG"] = "WARN"
+    # NCCL writes its INFO lines to stdout by default; the contract is one JSON line there, so they go to stderr
+    if os.environ.get("NCCL_DEBUG") and not os.environ.get("NCCL_DEBUG_FILE"):
+        os.environ["NCCL_DEBUG_FILE"] = "/dev/stderr"
     import torch
     import torch.distributed as dist
     from __graft_entry__ import load_package
@@ -272,287 +666,71 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    T = args.tokens
-
-    bank_kind = {"exl3": pkg.BANK_EXL3_K3_MUL1, "mxfp4": pkg.BANK_MXFP4, "nvfp4": pkg.BANK_NVFP4}[WL["bank"]]
-    scoring = {"sqrtsoftplus": pkg.SCORE_SQRTSOFTPLUS, "sigmoid": pkg.SCORE_SIGMOID, "softmax": pkg.SCORE_SOFTMAX}[WL["scoring"]]
-    NL = args.layers
-    cfg = pkg.make_config(H, I, E, K_TOP, n_layers=NL, bank_kind=bank_kind,
-                          act=pkg.ACT_SWIGLU_CLAMPED if WL["limit"] > 0 else pkg.ACT_SWIGLU, act_limit=WL["limit"],
-                          scoring=scoring, norm_topk=True, routed_scale=WL["scale"], shared_expert=WL["shared"],
-                          combine=pkg.COMBINE_CHAIN if WL["chain"] else pkg.COMBINE_F32, max_tokens=max(T, 64),
-                          device=local, ep_world=world, ep_rank=rank)
-    moe = pkg.MoE(cfg)
-    if world > 1:
-        # expert parallel: experts sharded E/N per rank; the NCCL id of the library's own communicator travels through
-        # torch.distributed
-        idt = torch.zeros(128, dtype=torch.uint8, device=dev)
-        if rank == 0:
-            buf = (C.c_char * 128)()
-            if pkg.lib().mlxs_moe_ep_unique_id(buf) != 0:
-                raise SystemExit("bench.py: " + pkg.last_error())
-            idt.copy_(torch.frombuffer(bytearray(bytes(buf)), dtype=torch.uint8))
-        dist.broadcast(idt, 0)
-        if pkg.lib().mlxs_moe_ep_init(moe._h, bytes(idt.cpu().numpy().tobytes())) != 0:
-            raise SystemExit("bench.py: " + pkg.last_error())
-    rng = np.random.default_rng(99 + rank)
-    n_batches = 4  # rotate a few seeded batches so consecutive steps route differently
-    g = torch.Generator(device=dev)
-    g.manual_seed(1000 + rank)
-    xs, lgs, x_host, lg_host = [], [], [], []
-    biases = [torch.from_numpy(zipf_bias(l)).to(dev) for l in range(NL)] if args.routing == "zipf" else None
-    for b in range(n_batches):
-        noise = rng.standard_normal((T, E)).astype(np.float32)
-        x = torch.randn((T, H), device=dev, generator=g).to(torch.bfloat16)
-        xs.append(x)
-        nd = torch.from_numpy(noise).to(dev)
-        # logits of (batch, layer): the batch's noise + the layer's popularity (one tensor for all layers without skew)
-        lgs.append([nd + biases[l] for l in range(NL)] if biases else [nd] * NL)
-        x_host.append(x.cpu().pin_memory())
-        lg_host.append(lgs[b][0].cpu().pin_memory())
-    stream = torch.cuda.current_stream()
-    sp = stream.cuda_stream
-
-    # where the experts live: contiguous blocks, or dealt out by usage: the library's tally counts the routed ids of the
-    # batches on the device, sums them over the ranks, and its planner deals the experts out (most used first, snake order)
-    rank_of = [np.arange(E) // (E // world) for _ in range(NL)]
-    if world > 1 and args.placement == "usage":
-        ids_dev = torch.empty((T, K_TOP), dtype=torch.int32, device=dev)
-        w_dev = torch.empty((T, K_TOP), dtype=torch.float32, device=dev)
-        moe.usage_enable(True)
-        for l in range(NL):
-            for b in range(n_batches):
-                moe.route(l, lgs[b][l].data_ptr(), T, ids_dev.data_ptr(), w_dev.data_ptr(), sp)
-            torch.cuda.synchronize()
-            ro = np.asarray(pkg.plan_placement(moe.usage_read(l, all_ranks=True), world), np.uint16)
-            rank_of[l] = ro.astype(np.int64)
-            moe.set_placement(l, np.ascontiguousarray(ro).ctypes.data)
-        moe.usage_enable(False)
-    owned = [np.nonzero(rank_of[l] == rank)[0] for l in range(NL)]
-    n_local = E // world
-    logical, stride = moe.record_bytes()
-    code_bytes = (H // 16) * (I // 16) * 96
-    if WL["bank"] == "exl3":
-        # synthetic bank generated on the device in the reference's record layout: random trellis codes, +-(0.5+u) scales
-        for j in range(n_local):
-            rec = torch.randint(0, 256, (stride,), dtype=torch.uint8, device=dev, generator=g)
-            off = 0
-            for p in range(3):
-                off += code_bytes
-                n_out, n_in = (H, I) if p == 2 else (I, H)
-                for n, sc in ((n_out, 0.02), (n_in, 1.0)):
-                    u = torch.rand(n, device=dev, generator=g)
-                    sgn = torch.where(torch.rand(n, device=dev, generator=g) < 0.5, -1.0, 1.0)
-                    rec[off:off + 2 * n] = ((0.5 + u) * sgn * sc).to(torch.float16).view(torch.uint8)
-                    off += 2 * n
-            for l in range(NL):  # the stack's layers share one synthetic bank image (same bytes, separate residency)
-                moe.load_expert(l, int(owned[l][j]), rec.data_ptr(), stride, on_device=True)
-    else:
-        nv = WL["bank"] == "nvfp4"
-        for j in range(n_local):
-            parts = []
-            for p in range(3):
-                rows, cols = (H, I) if p == 2 else (I, H)
-                w = torch.randn((rows, cols), device=dev, generator=g) * 0.02
-                words, sbytes, gs = fp4_quantise_torch(torch, w, nv)
-                parts += [words.view(torch.uint8).reshape(-1), sbytes.reshape(-1)]
-                if nv:
-                    parts.append(gs.to(torch.float32).reshape(1).view(torch.uint8))
-            rec = torch.cat(parts)
-            assert rec.numel() == logical, (rec.numel(), logical)
-            for l in range(NL):
-                moe.load_expert(l, int(owned[l][j]), rec.data_ptr(), rec.numel(), on_device=True)
-    sw = None
-    if WL["shared"]:
-        sw = [(torch.randn(s, device=dev, generator=g) * 0.02).to(torch.bfloat16) for s in ((I, H), (I, H), (H, I))]
-        for l in range(NL):
-            moe.set_shared(l, sw[0].data_ptr(), sw[1].data_ptr(), sw[2].data_ptr(), on_device=True)
-
-    y = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
-    y2 = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
-    y_host = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
-
-    def step(i):
-        # a stack feeds each layer's output to the next one (the trunk between MoE layers is out of scope); every
-        # layer routes with its own seeded logits
-        src, a, b = xs[i % n_batches], y, y2
-        for l in range(NL):
-            moe.forward(l, src.data_ptr(), lgs[(i + l) % n_batches][l].data_ptr(), T, a.data_ptr(), sp)
-            src, a, b = a, b, a
-
-    x_in = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
-    lg_in = torch.empty((T, E), dtype=torch.float32, device=dev)
-
-    def step_host(i):
-        if NL == 1:
-            moe.forward_host(0, x_host[i % n_batches].data_ptr(), lg_host[i % n_batches].data_ptr(), T,
-                             y_host.data_ptr(), sp)
-            return
-        # a stack: the step's inputs come from pinned host memory, the last layer's output goes back
-        x_in.copy_(x_host[i % n_batches], non_blocking=True)
-        lg_in.copy_(lg_host[i % n_batches], non_blocking=True)
-        src, a, b = x_in, y, y2
-        for l in range(NL):
-            moe.forward(l, src.data_ptr(), (lg_in if l == 0 else lgs[(i + l) % n_batches][l]).data_ptr(), T, a.data_ptr(), sp)
-            src, a, b = a, b, a
-        y_host.copy_(src, non_blocking=True)
-        stream.synchronize()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for i in range(steps):
-            fn(i)
-        e1.record(stream)
-        barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
-
-    for i in range(args.warmup):
-        step(i)
-    # distinct experts per batch (exact, from the routed ids) for the algorithmic byte count
-    distinct, lane_counts = [], []
-    ids_dev = torch.empty((T, K_TOP), dtype=torch.int32, device=dev)
-    w_dev = torch.empty((T, K_TOP), dtype=torch.float32, device=dev)
-    for b in range(n_batches):
-        step(b)
-        distinct.append(int(moe.stats().distinct_experts_last))
-        # rows per resident expert of layer 0 (which lane each expert takes is decided on these counts)
-        moe.route(0, lgs[b][0].data_ptr(), T, ids_dev.data_ptr(), w_dev.data_ptr(), sp)
-        torch.cuda.synchronize()
-        all_ids = ids_dev
-        if world > 1:
-            all_ids = torch.empty((world * T, K_TOP), dtype=torch.int32, device=dev)
-            dist.all_gather_into_tensor(all_ids, ids_dev)
-        cnt = torch.bincount(all_ids.reshape(-1).long(), minlength=E).cpu().numpy()
-        lane_counts.append(cnt[owned[0]])
+    env = dict(torch=torch, dist=dist, pkg=pkg, dev=dev, rank=rank, world=world, local=local)
     sampler = ClockSampler(local)
     sampler.start()
-    moe.profile_enable(True)
-    moe.profile_read()
-    ms = timed(step, args.steps)
-    prof = moe.profile_read()
-    moe.profile_enable(False)
-    clocks = sampler.stop()
-    # the same steps replayed from CUDA graphs (one per batch): what a host gains for launch-bound small batches
-    graph_ms = None
-    if args.graph and world == 1:
-        side = torch.cuda.Stream()
-        graphs = []
-        for b in range(n_batches):
-            gph = torch.cuda.CUDAGraph()
-            side.wait_stream(stream)
-            with torch.cuda.graph(gph, stream=side):
-                cs = torch.cuda.current_stream().cuda_stream
-                src, a, bb = xs[b], y, y2
-                for l in range(NL):
-                    moe.forward(l, src.data_ptr(), lgs[(b + l) % n_batches][l].data_ptr(), T, a.data_ptr(), cs)
-                    src, a, bb = a, bb, a
-            graphs.append(gph)
-        for i in range(args.warmup):
-            graphs[i % n_batches].replay()
-        graph_ms = timed(lambda i: graphs[i % n_batches].replay(), args.steps)
-    for i in range(args.warmup):
-        step_host(i)
-    ms_host = timed(step_host, args.steps)
-    st = moe.stats()
-    if st.device_status != 0:
-        raise SystemExit(f"bench.py: device status {st.device_status}")
-
-    mean_distinct = sum(distinct[i % n_batches] for i in range(args.steps)) / args.steps * 1.0
-    if WL["bank"] == "exl3":
-        gu_bytes = 2 * code_bytes + 2 * (2 * I + 2 * H)  # one expert's gate + up code and sign/scale vectors
-        kname = "exl3_gemv_kernel<2,gate_up>"
-        traffic_ratio = 1.014  # dram read+write / algorithmic bytes of the ncu capture on the small case (profiles/)
-    else:
-        gu_bytes = 2 * (H * I // 2 + H * I // (16 if WL["bank"] == "nvfp4" else 32))  # gate + up codes and block scales
-        kname = "fp4_gemv_kernel<2>"
-        traffic_ratio = 1.003
-    gu_ms, gu_n = prof["gate_up"]
-    peak, which = peaks()
-    achieved = mean_distinct * gu_bytes / (gu_ms / max(gu_n, 1) * 1e-3) / 1e9
-    tl_ms, tl_n = prof.get("tensor_lane", (0.0, 0))
-    # the tensor-core lane is the dominant kernel once most of the rows this rank serves belong to its experts (the lanes
-    # run on two streams, so their event spans overlap and do not rank them)
-    rows_heavy = float(np.mean([int(c[c >= LANE_MIN_ROWS].sum()) for c in lane_counts])) if lane_counts else 0.0
-    rows_served = float(np.mean([int(c.sum()) for c in lane_counts])) if lane_counts else 0.0
-    prefill_lane = tl_n > 0 and rows_heavy > 0.5 * rows_served
-    layer_bytes = NL * (mean_distinct * logical + (3 * H * I * 2 if WL["shared"] else 0) + T * H * 2 * 2 + T * E * 4)
-    value = world * T * args.steps / (ms * 1e-3)
+    T, NL = args.tokens, args.layers
+    rig = Rig(env, wl, E, T, NL, args.routing, args.placement)
+    m = measure(rig, args, sampler)
     out = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "metric": METRIC, "value": m.pop("value"), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": m.pop("ms_per_step"), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16 decoded weights x f16 activations (hi/lo split for EXL3), f32 accumulate", "data": "synthetic",
-        "config": workload_config(args, T),
-        "layer_hbm": {"algorithmic_bytes_per_call": layer_bytes, "gb_s": layer_bytes / (ms / args.steps * 1e-3) / 1e9,
-                      "frac_of_measured_peak": layer_bytes / (ms / args.steps * 1e-3) / 1e9 / peak,
-                      "frac_of_nominal_8000": layer_bytes / (ms / args.steps * 1e-3) / 1e9 / 8000.0,
-                      "distinct_experts_mean": mean_distinct},
-        "roofline": {"kernel": kname, "bound": "hbm", "achieved": achieved, "peak": peak,
-                     "peak_source": which, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": traffic_ratio * mean_distinct * gu_bytes,
-                     "traffic_note": "ncu dram bytes of a smaller case (64 experts, 16 tokens) scaled by distinct experts",
-                     "algorithmic_bytes_per_launch": mean_distinct * gu_bytes},
-        "stage_ms_per_step": {k: v[0] / max(args.steps, 1) for k, v in prof.items() if v[1]},
-        "e2e": {"value": world * T * args.steps / (ms_host * 1e-3), "unit": UNIT,
-                "h2d_bytes_per_step": T * H * 2 + T * E * 4, "d2h_bytes_per_step": T * H * 2 + 4},
-        "gpu_launches": NL * own_launches_per_layer(T, world) * args.steps,
-        "graph_replay": None if graph_ms is None else {"ms_per_step": graph_ms / args.steps,
-                                                        "value": T * args.steps / (graph_ms * 1e-3), "unit": UNIT},
-        "exchange": None if world == 1 else {
-            "exposed_ms_per_step": prof["exchange"][0] / max(args.steps, 1),
-            "bytes_sent_per_step_rank0": st.a2a_bytes_sent / max(st.expert_calls, 1),
-            "note": "dispatch + combine all-to-all (NCCL send/recv) incl. the count exchange and its host read"},
-        "clocks": clocks,
+        "config": workload_config(wl, E, T, NL, args.routing, world, args.placement),
     }
-    if prefill_lane:
-        # prefill-sized call: the tcgen05 lane (gate/up and down launches are timed together); tensor roofline
-        pk = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
-        tpeak = float(pk.get("bf16_tflops_sustained", 1400.0))
-        heavy_rows = float(np.mean([int(c[c >= LANE_MIN_ROWS].sum()) for c in lane_counts]))
-        flops = 6.0 * H * I * heavy_rows
-        tf = flops / (tl_ms / max(tl_n, 1) * 1e-3) / 1e12
-        out["roofline"] = {"kernel": ("exl3_prefill_kernel" if WL["bank"] == "exl3" else "fp4_prefill_kernel") + "<gate/up> + <down> (tcgen05 kind::f16)", "bound": "tensor", "achieved": tf,
-                           "peak": tpeak, "peak_source": "measured sustained bf16" if pk else "fallback", "unit": "TFLOP/s",
-                           "frac": tf / tpeak, "traffic": None, "flops_per_launch_pair": flops,
-                           "rows_in_lane_mean": heavy_rows, "rows_total": T * K_TOP}
-    if rank == 0 and world == 1 and not args.no_cpu and WL["bank"] == "exl3":
+    out.update(m)
+    if not args.no_parity:
+        out["parity_check"] = rig.parity_check()
+    if rank == 0 and world == 1 and not args.no_cpu and wl["bank"] == "exl3":
         import oracle_lib as O
+        H, I, K = wl["H"], wl["I"], wl["k"]
         Tc = args.cpu_tokens
         crng = np.random.default_rng(1234)
-        lg = make_logits(crng, Tc, args.routing)
-        ids, w = O.route(lg, None, K_TOP, O.SCORE_SQRTSOFTPLUS, scale=1.5)
+        lg = crng.standard_normal((Tc, E)).astype(np.float32)
+        if args.routing == "zipf":
+            lg = lg + zipf_bias(E, 0)
+        score = {"sqrtsoftplus": O.SCORE_SQRTSOFTPLUS, "sigmoid": O.SCORE_SIGMOID, "softmax": O.SCORE_SOFTMAX}[wl["scoring"]]
+        ids, w = O.route(lg, None, K, score, scale=wl["scale"])
         recs = {int(e): O.exl3_synth_record(0xB200 + int(e), H, I, 1.0, 0.02) for e in np.unique(ids)}
-        shared = [s.view(torch.int16).cpu().numpy().view(np.uint16) for s in sw]
+        shared = [s.view(torch.int16).cpu().numpy().view(np.uint16) for s in rig.sw] if rig.sw else None
         xc = O.bf16_bits_to_f32(O.f32_to_bf16_bits(crng.standard_normal((Tc, H)).astype(np.float32)))
         threads = O.max_threads()
         t0 = time.perf_counter()
-        O.layer_fast(H, I, E, K_TOP, recs, xc, ids, w, shared=shared, threads=threads)
+        O.layer_fast(H, I, E, K, recs, xc, ids, w, shared=shared, threads=threads)
         dt = time.perf_counter() - t0
         # the same form on one thread, over the first two tokens of the sample (their experts only)
         T1 = min(2, Tc)
         recs1 = {int(e): recs[int(e)] for e in np.unique(ids[:T1])}
         t0 = time.perf_counter()
-        O.layer_fast(H, I, E, K_TOP, recs1, xc[:T1], ids[:T1], w[:T1], shared=shared, threads=1)
+        O.layer_fast(H, I, E, K, recs1, xc[:T1], ids[:T1], w[:T1], shared=shared, threads=1)
         dt1 = time.perf_counter() - t0
         out["cpu_baseline"] = {"value": Tc / dt, "unit": UNIT, "cores": threads, "kind": "port",
-                               "sample": f"{Tc} tokens x top-{K_TOP} ({len(recs)} distinct experts), one call, "
-                                         "oracle fast f32 form with OpenMP",
+                               "sample": f"{Tc} tokens x top-{K} ({len(recs)} distinct experts), one layer call, "
+                                         "oracle fast f32 form with OpenMP (the whole workload at its own token count: --impl reference)",
                                "one_thread": {"value": T1 / dt1, "unit": UNIT,
-                                              "sample": f"{T1} tokens x top-{K_TOP} ({len(recs1)} distinct experts)"}}
+                                              "sample": f"{T1} tokens x top-{K} ({len(recs1)} distinct experts)"}}
+    rig.close()
+    del rig
+    # N = 1, default workload: the 24-layer Zipf stack of the expert-parallel configuration on the one GPU, so that the
+    # stack's N = 1 point exists beside the N > 1 lines
+    if world == 1 and default_workload and not args.no_stack and not args.experts:
+        torch.cuda.empty_cache()
+        swl = WORKLOADS["c5"]
+        sargs = argparse.Namespace(**vars(args))
+        sargs.graph = False
+        sargs.steps = max(3, min(args.steps, 10))
+        srig = Rig(env, swl, swl["E"], T, 24, "zipf", "contiguous")
+        sm = measure(srig, sargs, sampler, want_e2e=False)
+        out["c5_stack"] = {"config": workload_config(swl, swl["E"], T, 24, "zipf", 1, "contiguous"), "steps": sargs.steps,
+                           "value": sm["value"], "unit": UNIT, "ms_per_step": sm["ms_per_step"],
+                           "per_gpu_hbm_frac": sm["per_gpu_hbm_frac"], "stage_ms_per_step": sm["stage_ms_per_step"],
+                           "roofline": sm["roofline"]}
+        if not args.no_parity:
+            out["c5_stack"]["parity_check"] = srig.parity_check()
+        srig.close()
+    sampler.stop()
     if rank == 0:
         print(json.dumps(out))
-    moe.close()
     if world > 1:
         dist.destroy_process_group()
 

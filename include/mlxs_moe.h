@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define MLXS_MOE_ABI 2026112508
+#define MLXS_MOE_ABI 2026112601
 
 /* refusals (the names mirror the reference's refusal sets: src/sdk_ext/quant.zig:94-111, src/expert/bank.zig:79-101) */
 enum {
@@ -185,8 +185,9 @@ int mlxs_moe_exl3_gemv(mlxs_moe *h, uint32_t layer, uint32_t expert, uint32_t pr
                        uint32_t rows, float *z_dev, void *stream);
 
 /* The same projection for callers that may not allocate device memory: z f32 [rows, out_dim] = xh f32 [rows, in_dim]
- * . W_hat of the code plane at code_dev (I16 [in_dim/16, out_dim/16, 48], the bank file's order).  It has no
- * counterpart in the reference.  It needs no handle and calls no allocator: a host that fixes its device-memory
+ * . W_hat of the code plane at code_dev (I16 [in_dim/16, out_dim/16, 48], the bank file's order; K = 3 planes only,
+ * a K = 2 plane has 32 values per tile and is not accepted here).  xh_dev must be 16-byte aligned, code_dev and z_dev
+ * 4-byte aligned (refused by name otherwise).  It has no counterpart in the reference.  It needs no handle and calls no allocator: a host that fixes its device-memory
  * budget at load time, or code running while a stream is being captured (where cudaMalloc is not allowed), can still
  * use it.  Its scratch is a fixed 1 MiB array inside the library, which limits a call to rows <= 32 and
  * in_dim <= 8192 (a multiple of 128; out_dim a multiple of 16); larger sizes are refused.  The first call on a device
@@ -196,6 +197,24 @@ int mlxs_moe_exl3_gemv_noalloc(const void *code_dev, uint32_t in_dim, uint32_t o
                                uint32_t rows, float *z_dev, void *stream);
 
 int mlxs_moe_stats_get(mlxs_moe *h, mlxs_moe_stats *out);
+/* The device status word is sticky (a host must see a fault it did not poll for): once a kernel has recorded an error
+ * every mlxs_moe_forward_host returns MLXS_E_DEVICE_STATUS until the host acknowledges it here.  Synchronises the
+ * device, clears the word and the streaming kernels' arrival counters a call that gave up may have left behind.
+ * No counterpart in the reference (its kernels have no device-side error word). */
+int mlxs_moe_status_clear(mlxs_moe *h);
+/* The dispatch permutation by itself (src/sdk_ext/quant.zig:269-301 counting sort; src/arch/glm5_next/exl3_math.zig:
+ * 192-225): rows with slot ids slot_dev[n] in [0, n_slots) -> order_dev[n] (sorted position -> row, rows of one slot
+ * keep their order) and offsets_dev[n_slots + 1] (first sorted position of every slot).  It runs the layer path's own
+ * dispatch kernels (one CTA up to 2048 rows, count / scan / place above) on the handle's tables and copies the two
+ * arrays out; n_slots <= n_experts, n <= the handle's row capacity. */
+int mlxs_moe_sort_rows(mlxs_moe *h, const int32_t *slot_dev, uint32_t n, uint32_t n_slots, uint32_t *order_dev,
+                       uint32_t *offsets_dev, void *stream);
+/* Self-test of the bounded waits (no counterpart in the reference).  Every wait inside a kernel gives up after a
+ * number of polls, records MLXS_E_DEVICE_STATUS's word and lets the CTA return; poll_limit sets that number for the
+ * EXL3 streaming kernels (0 = the default, 2^20).  withhold_stage = n > 0 makes every gate/up producer leave out the
+ * copies of its n-th ring stage, so the wait for that stage runs out: the call completes, the status word reads
+ * "a bounded wait ran out", nothing faults and nothing is left in flight.  (0, 0) restores normal operation. */
+int mlxs_moe_debug_wait(mlxs_moe *h, uint32_t poll_limit, uint32_t withhold_stage);
 
 /* per-stage device timing with CUDA events on the caller's stream, off by default (the reference's comptime profile
  * hooks and kernel bench: src/sdk_ext/profile.zig:1-60, src/arch/glm5_next/exl3_kbench.zig:1-23).  `read` synchronises
@@ -216,13 +235,13 @@ int mlxs_moe_profile_read(mlxs_moe *h, mlxs_moe_profile *out);
 /* 128-byte NCCL unique id made on rank 0 and handed to every rank by the host */
 int mlxs_moe_ep_unique_id(void *id128_out);
 int mlxs_moe_ep_init(mlxs_moe *h, const void *id128);
-/* host-side plan of one exchange (pure function, also used by the CPU tests): for `n` assignments with expert ids
- * `ids`, counts per destination rank */
 /* Where a layer's experts live: rank_of_expert[e] in [0, ep_world), every rank exactly n_experts / ep_world of them;
  * an expert's local slot is its order among the rank's experts.  Default: contiguous blocks.  Call on every rank with
  * the same table before the layer's experts are loaded.  (The reference keeps a usage tally per expert for its
  * residency policy, src/sdk_ext/expert/usage.zig; here the same histogram can balance the ranks' load.) */
 int mlxs_moe_set_placement(mlxs_moe *h, uint32_t layer, const uint16_t *rank_of_expert);
+/* host-side plan of one exchange (pure function, also used by the CPU tests): for `n` assignments with expert ids
+ * `ids`, counts per destination rank */
 int mlxs_moe_ep_plan(const int32_t *ids, uint64_t n, uint32_t n_experts, uint32_t world, uint64_t *send_counts);
 
 /* Usage tally (src/sdk_ext/expert/usage.zig:202-224 keeps per-layer per-expert route counts to seed residency; here

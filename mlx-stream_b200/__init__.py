@@ -14,7 +14,7 @@ from pathlib import Path  # noqa: E402
 
 HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "libmlxs_moe.so"
-ABI = 2026112508
+ABI = 2026112601
 
 BANK_EXL3_K3_MUL1, BANK_MXFP4, BANK_NVFP4, BANK_EXL3_K2_MUL1 = 0, 1, 2, 3
 SCORE_SQRTSOFTPLUS, SCORE_SIGMOID, SCORE_SOFTMAX = 0, 1, 2
@@ -31,6 +31,7 @@ EXPORTS = [
     "mlxs_moe_stats_get", "mlxs_moe_profile_enable", "mlxs_moe_profile_read", "mlxs_moe_ep_unique_id", "mlxs_moe_ep_init", "mlxs_moe_ep_plan",
     "mlxs_moe_set_placement", "mlxs_moe_set_router_weight", "mlxs_moe_logits", "mlxs_moe_forward_x",
     "mlxs_moe_set_layer_bits", "mlxs_moe_layer_record_bytes", "mlxs_moe_bank_layer_bits_text",
+    "mlxs_moe_status_clear", "mlxs_moe_sort_rows", "mlxs_moe_debug_wait",
     "mlxs_moe_bank_verify", "mlxs_moe_usage_enable", "mlxs_moe_usage_add", "mlxs_moe_usage_read", "mlxs_moe_usage_reset", "mlxs_moe_plan_placement",
 ]
 
@@ -122,6 +123,9 @@ def lib():
         L.mlxs_moe_set_router_weight.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_int]
         L.mlxs_moe_logits.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
         L.mlxs_moe_forward_x.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
+        L.mlxs_moe_status_clear.argtypes = [C.c_void_p]
+        L.mlxs_moe_sort_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.mlxs_moe_debug_wait.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32]
         if L.mlxs_moe_abi() != ABI:
             raise RuntimeError(f"libmlxs_moe.so ABI {L.mlxs_moe_abi()} != binding ABI {ABI}")
         _lib = L
@@ -275,6 +279,18 @@ class MoE:
 
     def exl3_gemv(self, layer, expert, proj, xh, rows, z, stream=None):
         _check(lib().mlxs_moe_exl3_gemv(self._h, layer, expert, proj, xh, rows, z, stream))
+
+    def status_clear(self):
+        """Acknowledges a recorded device error: the sticky status word is cleared."""
+        _check(lib().mlxs_moe_status_clear(self._h))
+
+    def sort_rows(self, slot, n, n_slots, order, offsets, stream=None):
+        """The dispatch permutation alone: slot ids -> order (sorted position -> row) and per-slot offsets."""
+        _check(lib().mlxs_moe_sort_rows(self._h, slot, n, n_slots, order, offsets, stream))
+
+    def debug_wait(self, poll_limit=0, withhold_stage=0):
+        """Self-test hook of the bounded waits: a short poll limit and one withheld ring stage."""
+        _check(lib().mlxs_moe_debug_wait(self._h, poll_limit, withhold_stage))
 
     def profile_enable(self, on=True):
         _check(lib().mlxs_moe_profile_enable(self._h, int(on)))

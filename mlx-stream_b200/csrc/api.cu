@@ -107,7 +107,7 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
     for (auto& L : h->layers) {
         L.loaded.assign(c->n_experts, 0);
         if ((rc = h->alloc(&L.loaded_dev, c->n_experts)) || (rc = h->alloc(&L.place_dev, (size_t)c->n_experts * 4))) return bail(rc);
-        cudaMemset(L.loaded_dev, 0, c->n_experts);
+        if (cudaMemset(L.loaded_dev, 0, c->n_experts) != cudaSuccess) return bail(fail(MLXS_E_CUDA, "create: cudaMemset failed"));
         L.place_rank.resize(c->n_experts);
         L.place_slot.resize(c->n_experts);
         std::vector<uint32_t> packed(c->n_experts);
@@ -116,7 +116,8 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
             L.place_slot[e] = (uint16_t)(e % h->e_local);
             packed[e] = ((uint32_t)L.place_rank[e] << 16) | L.place_slot[e];
         }
-        cudaMemcpy(L.place_dev, packed.data(), packed.size() * 4, cudaMemcpyHostToDevice);
+        if (cudaMemcpy(L.place_dev, packed.data(), packed.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess)
+            return bail(fail(MLXS_E_CUDA, "create: cudaMemcpy of the placement table failed"));
         L.logical_bytes = h->logical_bytes;
         L.record_stride = h->record_stride;
         if (is_exl3(c->bank_kind)) {
@@ -148,8 +149,8 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
         (rc = h->alloc(&h->x_io, T * H * 2)) ||
         (rc = h->alloc(&h->y_io, T * H * 2)) || (rc = h->alloc(&h->logits_io, T * c->n_experts * 4)))
         return bail(rc);
-    cudaMemset(h->status, 0, 16);
-    cudaMemset(h->tabs.header, 0, 64);
+    if (cudaMemset(h->status, 0, 16) != cudaSuccess || cudaMemset(h->tabs.header, 0, 64) != cudaSuccess)
+        return bail(fail(MLXS_E_CUDA, "create: cudaMemset failed"));
     if (is_exl3(c->bank_kind)) {
         const size_t kmax = (H > I ? H : I) / 16;
         if ((rc = h->alloc(&h->xa_gu, (size_t)max_chunks * 2 * kmax * 256)) ||
@@ -157,14 +158,14 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
             return bail(rc);
         if ((rc = h->alloc(&h->ks_scratch, exl3_ksplit_scratch_bytes(h->sm_count))) || (rc = h->alloc(&h->ks_count, (size_t)3 * h->sm_count * 4)))
             return bail(rc);
-        cudaMemset(h->ks_count, 0, (size_t)3 * h->sm_count * 4);
+        if (cudaMemset(h->ks_count, 0, (size_t)3 * h->sm_count * 4) != cudaSuccess) return bail(fail(MLXS_E_CUDA, "create: cudaMemset failed"));
     } else {
         if ((rc = h->alloc(&h->xa_gu, (size_t)max_chunks * (H / 32) * 512)) ||
             (rc = h->alloc(&h->xa_d, (size_t)max_chunks * (I / 32) * 512)) || (rc = h->alloc(&h->ro, A * H * 4)))
             return bail(rc);
         if ((rc = h->alloc(&h->ks_scratch, exl3_ksplit_scratch_bytes(h->sm_count))) || (rc = h->alloc(&h->ks_count, (size_t)3 * h->sm_count * 4)))
             return bail(rc);
-        cudaMemset(h->ks_count, 0, (size_t)3 * h->sm_count * 4);
+        if (cudaMemset(h->ks_count, 0, (size_t)3 * h->sm_count * 4) != cudaSuccess) return bail(fail(MLXS_E_CUDA, "create: cudaMemset failed"));
     }
     {
         // Staging for the tensor-core lane.  One decode pass of the streaming lane serves 16 rows, one of the
@@ -381,11 +382,42 @@ static int check_call(mlxs_moe* h, uint32_t layer, uint32_t T, const char* who) 
     return 0;
 }
 
+// Rows are read and written as 16-byte vectors, ids / weights / logits as 4-byte words: a misaligned base pointer would
+// fault on the device, so it is refused by name here.
+static int check_aligned(const void* p, uintptr_t align, const char* who, const char* what) {
+    if (reinterpret_cast<uintptr_t>(p) & (align - 1))
+        return fail(MLXS_E_ARG, "%s: %s must be %u-byte aligned", who, what, (unsigned)align);
+    return 0;
+}
+
+// Joins the handle's side streams back into the caller's stream on every way out of a layer call (also the refusals
+// after a fork): the caller's stream then always orders after the side work, and a stream capture never ends with an
+// unjoined fork.
+struct ForkGuard {
+    cudaStream_t st;
+    cudaStream_t side = nullptr;
+    cudaEvent_t join = nullptr;
+    bool armed = false;
+    explicit ForkGuard(cudaStream_t s) : st(s) {}
+    void arm(cudaStream_t side_, cudaEvent_t join_) { side = side_; join = join_; armed = true; }
+    // the normal path: the side stream's work is recorded here, the wait may come later (wait_now) or at scope exit
+    cudaError_t record() { return cudaEventRecord(join, side); }
+    cudaError_t wait_now() { armed = false; return cudaStreamWaitEvent(st, join, 0); }
+    ~ForkGuard() {
+        if (!armed) return;
+        cudaEventRecord(join, side);
+        cudaStreamWaitEvent(st, join, 0);
+    }
+};
+
 extern "C" int mlxs_moe_route(mlxs_moe* h, uint32_t layer, const float* logits_dev, uint32_t T, int32_t* ids_dev,
                               float* weights_dev, void* stream) {
     int rc = check_call(h, layer, T, "route");
     if (rc) return rc;
     if (T && (!logits_dev || !ids_dev || !weights_dev)) return fail(MLXS_E_ARG, "route: null buffer");
+    if ((rc = check_aligned(logits_dev, 4, "route", "logits_dev")) || (rc = check_aligned(ids_dev, 4, "route", "ids_dev")) ||
+        (rc = check_aligned(weights_dev, 4, "route", "weights_dev")))
+        return rc;
     const mlxs_moe_config& c = h->cfg;
     StageTimer tm(h, MLXS_STAGE_ROUTER, (cudaStream_t)stream);
     CU(launch_router(logits_dev, h->layers[layer].bias, (int)T, (int)c.n_experts, (int)c.top_k, (int)c.scoring,
@@ -542,9 +574,11 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
     static const uint32_t lanes_aside_max = getenv("MLXS_LANES_ASIDE_MAX") ? (uint32_t)atoi(getenv("MLXS_LANES_ASIDE_MAX")) : 2048u;
     const bool lane_aside = two_lanes && h->lane_stream && T <= lanes_aside_max;
     const cudaStream_t tl = lane_aside ? h->lane_stream : st;
+    ForkGuard lane_guard(st);
     if (lane_aside) {
         CU(cudaEventRecord(h->lane_fork, st));
         CU(cudaStreamWaitEvent(h->lane_stream, h->lane_fork, 0));
+        lane_guard.arm(h->lane_stream, h->lane_join);
     }
     const float limit = c.act == MLXS_ACT_SWIGLU_CLAMPED ? c.act_limit : 0.f;
     if (is_exl3(c.bank_kind)) {
@@ -567,6 +601,7 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
         a.L = EL; a.d = d; a.t = h->tabs; a.xa_gu = h->xa_gu; a.xa_d = h->xa_d; a.ro = static_cast<float*>(ro); a.ro_bf16 = 0;
         a.limit = limit;
         a.status = h->status; a.sm_count = h->sm_count; a.ks_scratch = h->ks_scratch; a.ks_count = h->ks_count;
+        a.poll_limit = h->dbg_poll_limit; a.withhold = h->dbg_withhold;
         {
             StageTimer tm(h, MLXS_STAGE_GATE_UP, st);
             CU(launch_exl3_gate_up(a, st));
@@ -606,8 +641,8 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
         }
     }
     if (lane_aside) {
-        CU(cudaEventRecord(h->lane_join, h->lane_stream));
-        CU(cudaStreamWaitEvent(st, h->lane_join, 0));
+        CU(lane_guard.record());
+        CU(lane_guard.wait_now());
     }
     h->stats.expert_calls += 1;
     h->stats.assignments += A;
@@ -627,8 +662,11 @@ extern "C" int mlxs_moe_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, c
                                float* out_dev, void* stream) {
     int rc = check_call(h, layer, T, "routed");
     if (rc) return rc;
-    if (T == 0) return MLXS_OK;
-    if (!x_dev || !ids_dev || !out_dev) return fail(MLXS_E_ARG, "routed: null buffer");
+    if (T == 0 && h->cfg.ep_world == 1) return MLXS_OK;  // with expert parallelism an empty rank still serves its peers
+    if (T && (!x_dev || !ids_dev || !out_dev)) return fail(MLXS_E_ARG, "routed: null buffer");
+    if ((rc = check_aligned(x_dev, 16, "routed", "x_dev")) || (rc = check_aligned(ids_dev, 4, "routed", "ids_dev")) ||
+        (rc = check_aligned(out_dev, 16, "routed", "out_dev")))
+        return rc;
     return run_routed(h, layer, x_dev, ids_dev, T, out_dev, 0, (cudaStream_t)stream);
 }
 
@@ -638,6 +676,9 @@ extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, 
     if (rc) return rc;
     if (T == 0 && h->cfg.ep_world == 1) return MLXS_OK;  // with expert parallelism an empty rank still serves its peers
     if (T && (!x_dev || !ids_dev || !weights_dev || !y_dev)) return fail(MLXS_E_ARG, "experts: null buffer");
+    if ((rc = check_aligned(x_dev, 16, "experts", "x_dev")) || (rc = check_aligned(y_dev, 16, "experts", "y_dev")) ||
+        (rc = check_aligned(ids_dev, 4, "experts", "ids_dev")) || (rc = check_aligned(weights_dev, 4, "experts", "weights_dev")))
+        return rc;
     const mlxs_moe_config& c = h->cfg;
     LayerBank& L = h->layers[layer];
     cudaStream_t st = (cudaStream_t)stream;
@@ -669,14 +710,16 @@ extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, 
         }
         return MLXS_OK;
     };
+    ForkGuard aux_guard(st);
     if (shared_aside) {
         CU(cudaEventRecord(h->aux_fork, st));
         CU(cudaStreamWaitEvent(h->aux_stream, h->aux_fork, 0));
+        aux_guard.arm(h->aux_stream, h->aux_join);
         {
             StageTimer tm(h, MLXS_STAGE_SHARED, h->aux_stream);
             if ((rc = run_shared(h->aux_stream))) return rc;
         }
-        CU(cudaEventRecord(h->aux_join, h->aux_stream));
+        CU(aux_guard.record());
         shared = h->sh_out;
     }
     if (!ep_fused && (rc = run_routed(h, layer, x_dev, ids_dev, T, h->ro, ro_bf16, st))) return rc;
@@ -685,10 +728,9 @@ extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, 
         if ((rc = run_shared(st))) return rc;
         shared = h->sh_out;
     }
-    if (shared_aside && !ep_fused) CU(cudaStreamWaitEvent(st, h->aux_join, 0));
+    if (shared_aside) CU(aux_guard.wait_now());  // before the combine (or the exchange's final sum) reads the row
     if (ep_fused) {
         h->stats.tokens += T;
-        if (shared_aside) CU(cudaStreamWaitEvent(st, h->aux_join, 0));  // before the exchange's final sum reads the row
         return mlxs_ep_combined(h, layer, x_dev, ids_dev, weights_dev, T, shared, y_dev, st);
     }
     StageTimer tm(h, MLXS_STAGE_COMBINE, st);
@@ -719,14 +761,16 @@ extern "C" int mlxs_moe_forward_host(mlxs_moe* h, uint32_t layer, const void* x_
                                      void* y_host, void* stream) {
     int rc = check_call(h, layer, T, "forward_host");
     if (rc) return rc;
-    if (T == 0) return MLXS_OK;
-    if (!x_host || !logits_host || !y_host) return fail(MLXS_E_ARG, "forward_host: null buffer");
+    if (T == 0 && h->cfg.ep_world == 1) return MLXS_OK;  // with expert parallelism an empty rank still serves its peers
+    if (T && (!x_host || !logits_host || !y_host)) return fail(MLXS_E_ARG, "forward_host: null buffer");
     cudaStream_t st = (cudaStream_t)stream;
     const size_t xb = (size_t)T * h->cfg.hidden * 2;
-    CU(cudaMemcpyAsync(h->x_io, x_host, xb, cudaMemcpyHostToDevice, st));
-    CU(cudaMemcpyAsync(h->logits_io, logits_host, (size_t)T * h->cfg.n_experts * 4, cudaMemcpyHostToDevice, st));
+    if (T) {
+        CU(cudaMemcpyAsync(h->x_io, x_host, xb, cudaMemcpyHostToDevice, st));
+        CU(cudaMemcpyAsync(h->logits_io, logits_host, (size_t)T * h->cfg.n_experts * 4, cudaMemcpyHostToDevice, st));
+    }
     if ((rc = mlxs_moe_forward(h, layer, h->x_io, h->logits_io, T, h->y_io, stream))) return rc;
-    CU(cudaMemcpyAsync(y_host, h->y_io, xb, cudaMemcpyDeviceToHost, st));
+    if (T) CU(cudaMemcpyAsync(y_host, h->y_io, xb, cudaMemcpyDeviceToHost, st));
     return read_status(h, st);
 }
 
@@ -754,6 +798,43 @@ extern "C" int mlxs_moe_exl3_gemv(mlxs_moe* h, uint32_t layer, uint32_t expert, 
     const uint32_t tw8 = 8u * exl3_tile_words(d);   // words of one projection's eight tiles of a k-tile
     CU(launch_exl3_raw(code, in_dim, out_dim, proj == 2 ? tw8 : 2u * tw8, proj == 1 ? tw8 : 0u, (int)d.K, h->tabs, h->xa_gu, z_dev,
                        h->status, h->sm_count, st));
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_status_clear(mlxs_moe* h) {
+    if (!h) return fail(MLXS_E_ARG, "status_clear: null handle");
+    CU(cudaSetDevice(h->cfg.device));
+    CU(cudaDeviceSynchronize());
+    CU(cudaMemset(h->status, 0, 16));
+    // a call that gave up may have left arrivals of the K-split fold behind
+    if (h->ks_count) CU(cudaMemset(h->ks_count, 0, (size_t)3 * h->sm_count * 4));
+    h->stats.device_status = 0;
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_debug_wait(mlxs_moe* h, uint32_t poll_limit, uint32_t withhold_stage) {
+    if (!h) return fail(MLXS_E_ARG, "debug_wait: null handle");
+    if (withhold_stage && (poll_limit == 0 || poll_limit > 4096))
+        return fail(MLXS_E_ARG, "debug_wait: a withheld stage needs a poll limit of 1..4096 (the wait must run out quickly)");
+    h->dbg_poll_limit = poll_limit;
+    h->dbg_withhold = withhold_stage;
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_sort_rows(mlxs_moe* h, const int32_t* slot_dev, uint32_t n, uint32_t n_slots, uint32_t* order_dev,
+                                  uint32_t* offsets_dev, void* stream) {
+    if (!h || (n && (!slot_dev || !order_dev)) || !offsets_dev) return fail(MLXS_E_ARG, "sort_rows: null argument");
+    if (n_slots == 0 || n_slots > h->cfg.n_experts) return fail(MLXS_E_ARG, "sort_rows: %u slots, the handle's tables hold %u", n_slots, h->cfg.n_experts);
+    if (n > h->rows_cap) return fail(MLXS_E_TOO_MANY_TOKENS, "sort_rows: %u rows exceed the workspace's %u", n, h->rows_cap);
+    CU(cudaSetDevice(h->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    // the layer path's own dispatch: one CTA up to 2048 rows, count / scan / place over several CTAs above
+    if (n > 2048)
+        CU(launch_dispatch_large(slot_dev, n, n_slots, nullptr, h->tabs, h->chunk_rows, h->group_chunks, 0, h->blk_cnt, h->status, st));
+    else
+        CU(launch_dispatch(slot_dev, n, n_slots, nullptr, h->tabs, h->chunk_rows, h->group_chunks, 0, h->status, st));
+    if (n) CU(cudaMemcpyAsync(order_dev, h->tabs.order, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
+    CU(cudaMemcpyAsync(offsets_dev, h->tabs.offsets, ((size_t)n_slots + 1) * 4, cudaMemcpyDeviceToDevice, st));
     return MLXS_OK;
 }
 

@@ -340,6 +340,23 @@ int mlxs_ep_allreduce_u64(mlxs_moe* h, unsigned long long* buf_dev, size_t n, cu
     return MLXS_OK;
 }
 
+// The all-ranks refusal: every rank holds the same W x W count matrix after the all-gather (counts[(s * W + d) *
+// stride] = rows rank s sends to rank d) and the same row capacity, so every rank finds the same overloaded rank and
+// returns the same refusal before any send or receive is queued; nobody is left waiting for a peer that bailed out.
+extern "C" int32_t mlxs_moe_ep_overloaded_rank(const int32_t* counts, uint32_t world, uint32_t stride, uint64_t rows_cap) {
+    if (!counts || world == 0 || stride == 0) return -2;
+    for (uint32_t d = 0; d < world; ++d) {
+        uint64_t recv = 0;
+        for (uint32_t s = 0; s < world; ++s) {
+            const int32_t c = counts[((size_t)s * world + d) * stride];
+            if (c < 0) return (int32_t)d;   // a corrupt count is an overload of its destination
+            recv += (uint64_t)c;
+        }
+        if (recv > rows_cap) return (int32_t)d;
+    }
+    return -1;
+}
+
 int mlxs_ep_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, uint32_t T, void* ro,
                    int ro_bf16, cudaStream_t st) {
     EpState* ep = h->ep;
@@ -367,9 +384,12 @@ int mlxs_ep_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t
     if (W > 64) return mlxs_fail(MLXS_E_EP, "experts: ep_world %u > 64", W);
     for (uint32_t r = 0; r < W; ++r) { soff[r] = S; S += (size_t)cnt[me * W + r]; }
     for (uint32_t s = 0; s < W; ++s) { roff[s] = R; R += (size_t)cnt[s * W + me]; }
+    {
+        const int32_t over = mlxs_moe_ep_overloaded_rank(cnt, W, 1, h->rows_cap);
+        if (over >= 0)
+            return mlxs_fail(MLXS_E_EP, "experts: rank %d would receive more rows than its workspace's %u (every rank refuses this call; capacity = min(world, 4) x max_tokens x top_k)", over, h->rows_cap);
+    }
     if (S != A) return mlxs_fail(MLXS_E_EP, "experts: exchange plan counts %zu rows, the call has %u", S, A);
-    if (R > h->rows_cap)
-        return mlxs_fail(MLXS_E_EP, "experts: this rank would receive %zu rows, its workspace holds %u (load imbalance beyond the capacity)", R, h->rows_cap);
     {
         StageTimer tm(h, MLXS_STAGE_EXCHANGE, st);
         NC(api->GroupStart());
@@ -441,9 +461,12 @@ int mlxs_ep_combined(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32
         ru[r + 1] = ru[r] + (size_t)cnt[(r * W + me) * 2 + 1];
     }
     const size_t SA = sa[W], SU = su[W], RA = ra[W], RU = ru[W];
+    {
+        const int32_t over = mlxs_moe_ep_overloaded_rank(cnt, W, 2, h->rows_cap);
+        if (over >= 0)
+            return mlxs_fail(MLXS_E_EP, "experts: rank %d would receive more rows than its workspace's %u (every rank refuses this call; capacity = min(world, 4) x max_tokens x top_k)", over, h->rows_cap);
+    }
     if (SA != A) return mlxs_fail(MLXS_E_EP, "experts: exchange plan counts %zu rows, the call has %u", SA, A);
-    if (RA > h->rows_cap)
-        return mlxs_fail(MLXS_E_EP, "experts: this rank would receive %zu rows, its workspace holds %u (load imbalance beyond the capacity)", RA, h->rows_cap);
     {
         StageTimer tm(h, MLXS_STAGE_EXCHANGE, st);
         NC(api->GroupStart());

@@ -176,6 +176,10 @@ struct GemvParams {
     // item's parts over 2 or 4 CTAs: each leaves its parts here and the last to arrive folds them and runs the epilogue.
     float* ks_scratch;           // [2 x CTAs][zs words] or null (one CTA per item always)
     uint32_t* ks_count;          // [CTAs] arrivals per item, zero between launches
+    // Every wait gives up after poll_limit polls.  Self-test only (mlxs_moe_debug_wait): withhold = n makes every
+    // producer leave out the copies of its n-th ring stage, so the consumers' wait for that stage runs out, the CTA
+    // records ST_WAIT_FULL and returns with nothing in flight.
+    uint32_t poll_limit, withhold;
 };
 
 // flags: 1 = first stage of a part of the sum, 2 = last stage of a part, 4 = last stage of this CTA's share of the item;
@@ -249,6 +253,7 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
         // ---------------- producer warp: one lane issues every copy ----------------
         if (lane == 0) {
             uint32_t s = 0, ph = 0;     // ring slot and phase
+            uint32_t n_stage = 0;       // stages this producer has filled (self-test: the withheld one)
             const uint32_t np_mask = NP - 1, np_shift = NP == 4 ? 2u : (NP == 2 ? 1u : 0u);
             bool ok = true;
             while (ok) {
@@ -273,7 +278,7 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
                 // k_begin is a multiple of the part length: the place inside a part advances with the stages
                 uint32_t part = share * (LP / NP), in_part = 0;
                 for (uint32_t kt0 = k_begin; kt0 < k_end; kt0 += step, s = (s + 1 == NS) ? (ph ^= 1u, 0u) : s + 1) {
-                    if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, &s_abort, 128)) {
+                    if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, &s_abort, 128, P.poll_limit)) {
                         if (!s_abort) atomicMax(P.status, (uint32_t)ST_WAIT_EMPTY);
                         s_abort = 1; ok = false; break;
                     }
@@ -285,6 +290,7 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
                     in_part = part_ends ? 0u : in_part + step;
                     part += part_ends ? 1u : 0u;
                     if (last) { mbar_arrive(&full_bar[s]); ok = false; break; }
+                    if (P.withhold && ++n_stage == P.withhold) continue;   // self-test: this stage never arrives
                     uint8_t* dst = ring + (size_t)s * P.stage_bytes;
                     mbar_expect_tx(&full_bar[s], sub * P.w_bytes + mc * NPROJ * xa_bytes);
                     bulk_g2s(dst, wsrc + (size_t)kt0 * P.kt_stride_words, sub * P.w_bytes, &full_bar[s]);
@@ -312,14 +318,14 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
     auto epi_sync = [&]() -> bool {
         __syncwarp();
         if (lane == 0) mbar_arrive(&epi_bar);
-        const bool ok = mbar_wait_bounded(&epi_bar, epi_ph, &s_abort);
+        const bool ok = mbar_wait_bounded(&epi_bar, epi_ph, &s_abort, 0, P.poll_limit);
         epi_ph ^= 1u;
         if (!ok) { if (!s_abort) atomicMax(P.status, (uint32_t)ST_WAIT_FULL); s_abort = 1; }
         return ok;
     };
     // ring slot and its phase advance by increment-and-wrap (the ring depth is a run-time value: no division per stage)
     for (uint32_t s = 0, ph = 0;; s = (s + 1 == NS) ? (ph ^= 1u, 0u) : s + 1) {
-        if (!mbar_wait_bounded(&full_bar[s], ph, &s_abort)) {
+        if (!mbar_wait_bounded(&full_bar[s], ph, &s_abort, 0, P.poll_limit)) {
             if (!s_abort) atomicMax(P.status, (uint32_t)ST_WAIT_FULL);
             s_abort = 1;
             break;
@@ -538,6 +544,7 @@ cudaError_t launch_exl3_gate_up(const Exl3GemvArgs& a, cudaStream_t st) {
     P.scales = a.L.scales; P.scales_stride = exl3_scales_per_expert(a.d);
     P.H = a.d.H; P.I = a.d.I; P.xa_d = a.xa_d; P.out = nullptr; P.out_dim = a.d.I; P.limit = a.limit; P.status = a.status;
     P.ks_scratch = a.ks_scratch; P.ks_count = a.ks_count;
+    P.poll_limit = a.poll_limit ? a.poll_limit : (1u << 20); P.withhold = a.withhold;
     return launch_gemv(2, EPI_GATE_UP, (int)a.d.K, P, a.sm_count, st);
 }
 cudaError_t launch_exl3_down(const Exl3GemvArgs& a, cudaStream_t st) {
@@ -549,6 +556,7 @@ cudaError_t launch_exl3_down(const Exl3GemvArgs& a, cudaStream_t st) {
     P.scales = a.L.scales; P.scales_stride = exl3_scales_per_expert(a.d);
     P.H = a.d.H; P.I = a.d.I; P.xa_d = nullptr; P.out = a.ro; P.out_dim = a.d.H; P.limit = a.limit; P.status = a.status;
     P.ks_scratch = a.ks_scratch; P.ks_count = a.ks_count;
+    P.poll_limit = a.poll_limit ? a.poll_limit : (1u << 20); P.withhold = 0;
     return launch_gemv(1, EPI_DOWN, (int)a.d.K, P, a.sm_count, st);
 }
 cudaError_t launch_exl3_raw(const uint32_t* code_e, uint32_t in_dim, uint32_t out_dim, uint32_t ktile_stride_words,
@@ -559,7 +567,7 @@ cudaError_t launch_exl3_raw(const uint32_t* code_e, uint32_t in_dim, uint32_t ou
     P.n_blocks = out_dim / 128; P.nkt = in_dim / 16; P.kt_stride_words = ktile_stride_words; P.proj_off_words = proj_off_words;
     P.xa = xa; P.t = t; P.counter_idx = HDR_CTR_AUX;
     P.scales = nullptr; P.scales_stride = 0; P.H = 0; P.I = 0; P.xa_d = nullptr; P.out = z; P.out_dim = out_dim;
-    P.limit = 0.f; P.status = status;
+    P.limit = 0.f; P.status = status; P.poll_limit = 1u << 20; P.withhold = 0;
     return launch_gemv(1, EPI_RAW, kbits, P, sm_count, st);
 }
 

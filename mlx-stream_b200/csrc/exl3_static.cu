@@ -1,4 +1,5 @@
-// An allocation-free EXL3 projection: z = xh . W_hat for one code plane, with its scratch in a fixed device array.
+// An allocation-free EXL3 projection (K = 3 code planes only: 24 words per 16x16 tile): z = xh . W_hat for one code
+// plane, with its scratch in a fixed device array.
 //
 // Who needs it: a host that settles its device-memory budget when the model loads and allows no device allocation
 // afterwards, and any code that runs while a stream is being captured into a graph, where cudaMalloc is not allowed.
@@ -129,6 +130,14 @@ extern "C" int mlxs_moe_exl3_gemv_noalloc(const void* code_dev, uint32_t in_dim,
     if (in_dim == 0 || in_dim % 128 || in_dim > NA_MAX_IN)
         return mlxs_fail(MLXS_E_ARG, "exl3_gemv_noalloc: in_dim %u must be a multiple of 128 up to %u", in_dim, NA_MAX_IN);
     if (out_dim == 0 || out_dim % 16) return mlxs_fail(MLXS_E_ARG, "exl3_gemv_noalloc: out_dim %u must be a multiple of 16", out_dim);
+    // the staging kernel reads the rows as 16-byte vectors (row offsets are multiples of 512 bytes, so only the base
+    // matters); code and output are read and written as 4-byte words
+    if (reinterpret_cast<uintptr_t>(xh_dev) & 15u)
+        return mlxs_fail(MLXS_E_ARG, "exl3_gemv_noalloc: xh_dev must be 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(code_dev) & 3u)
+        return mlxs_fail(MLXS_E_ARG, "exl3_gemv_noalloc: code_dev must be 4-byte aligned");
+    if (reinterpret_cast<uintptr_t>(z_dev) & 3u)
+        return mlxs_fail(MLXS_E_ARG, "exl3_gemv_noalloc: z_dev must be 4-byte aligned");
     if (rows == 0) return MLXS_OK;
     uint32_t* scratch = nullptr;
     int rc = scratch_address(&scratch);

@@ -79,6 +79,7 @@ struct mlxs_moe {
     float* logits_io = nullptr;
     mlxs_moe_stats stats{};
     EpState* ep = nullptr;
+    uint32_t dbg_poll_limit = 0, dbg_withhold = 0;  // mlxs_moe_debug_wait (self-test of the bounded waits)
     uint32_t rows_cap = 0;  // rows the expert kernels' workspaces hold (assignments of one call, or received rows)
     // per-stage timing (off by default)
     bool prof_on = false;

@@ -88,6 +88,8 @@ struct Exl3GemvArgs {
     int sm_count;
     float* ks_scratch;      // optional K-split workspace: exl3_ksplit_scratch_bytes(sm_count) bytes
     uint32_t* ks_count;     // [3 * sm_count] zeroed once
+    uint32_t poll_limit;    // polls after which a wait gives up (0: the default, 2^20)
+    uint32_t withhold;      // self-test: the gate/up producers leave out their n-th ring stage (0: off)
 };
 static inline size_t exl3_ksplit_scratch_bytes(int sm_count) { return (size_t)2 * 3 * sm_count * 2 * 16 * 132 * 4; }
 cudaError_t launch_exl3_gate_up(const Exl3GemvArgs& a, cudaStream_t st);

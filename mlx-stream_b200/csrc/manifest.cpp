@@ -135,6 +135,7 @@ std::string gets(const JVal* o, const char* k) {
     const JVal* v = o ? o->get(k) : nullptr;
     return v && v->kind == JVal::Str ? v->str : std::string();
 }
+bool lower_hex64(const std::string& h);   // 64 lowercase hex digits (the reference decodes lowercase hex only: src/expert/bank.zig:432-466)
 bool plain_name(const std::string& s) {
     if (s.empty() || s == "." || s == "..") return false;
     for (char c : s) if (c == '/' || c == '\\' || c == 0) return false;
@@ -318,7 +319,7 @@ int parse_exl3(const JVal& m, Bank& b) {
                 so != b.layer_base[rl] + re * b.layer_stride[rl] || rb != b.layer_stride[rl] || lb != b.layer_logical[rl])
                 return mlxs_fail(MLXS_E_MANIFEST, "v2: record (%llu,%llu) offset/size differs from its layer geometry", (unsigned long long)rl, (unsigned long long)re);
             dst.sha256 = gets(&r, "sha256");
-            if (dst.sha256.size() != 64) return mlxs_fail(MLXS_E_MANIFEST, "v2: record (%llu,%llu) has no sha256", (unsigned long long)rl, (unsigned long long)re);
+            if (!lower_hex64(dst.sha256)) return mlxs_fail(MLXS_E_MANIFEST, "v2: record (%llu,%llu) has no sha256 (RecordSha256)", (unsigned long long)rl, (unsigned long long)re);
             dst.offset = so;
             dst.present = true;
         }
@@ -396,7 +397,7 @@ int parse_fp4(const JVal& m, Bank& b, bool nv) {
             rl != first + i / E || re != i % E || ro != i * stride || rlen != logical)
             return mlxs_fail(MLXS_E_MANIFEST, "%s: record %zu: its layer, expert or place (InvalidRecord)", tag, i);
         b.records[i].sha256 = gets(&r, "sha256");
-        if (b.records[i].sha256.size() != 64) return mlxs_fail(MLXS_E_MANIFEST, "%s: record %zu has no sha256 (InvalidDigest)", tag, i);
+        if (!lower_hex64(b.records[i].sha256)) return mlxs_fail(MLXS_E_MANIFEST, "%s: record %zu has no sha256 (InvalidDigest)", tag, i);
         b.records[i].offset = ro;
         b.records[i].present = true;
     }
@@ -404,7 +405,9 @@ int parse_fp4(const JVal& m, Bank& b, bool nv) {
     const JVal* eb = of ? of->get("experts.bin") : nullptr;
     uint64_t sz = 0;
     const uint64_t total = nv ? L * E * stride : L * E * logical;
-    if (!eb || !geti(eb, "size", sz) || sz != total || gets(eb, "sha256").size() != 64)
+    if (eb && !lower_hex64(gets(eb, "sha256")))
+        return mlxs_fail(MLXS_E_MANIFEST, "%s: output_files experts.bin has no sha256 (InvalidDigest)", tag);
+    if (!eb || !geti(eb, "size", sz) || sz != total)
         return mlxs_fail(MLXS_E_MANIFEST, "%s: output_files experts.bin size %llu != %llu (InvalidOutputFile)", tag, (unsigned long long)sz, (unsigned long long)total);
     b.info.bank_kind = nv ? MLXS_BANK_NVFP4 : MLXS_BANK_MXFP4;
     b.info.hidden = H; b.info.inter = I; b.info.n_experts = E; b.info.n_layers = L; b.info.first_layer = first;

@@ -2,7 +2,7 @@
 //! is the compiled, tested statement of the same ABI).  One declaration per C entry point, same order.
 const std = @import("std");
 
-pub const abi_expected: i32 = 2026112508;
+pub const abi_expected: i32 = 2026112601;
 
 pub const Moe = opaque {};
 
@@ -87,6 +87,12 @@ pub extern fn mlxs_moe_forward_host(h: *Moe, layer: u32, x_host: *const anyopaqu
 pub extern fn mlxs_moe_exl3_gemv(h: *Moe, layer: u32, expert: u32, proj: u32, xh_dev: *const anyopaque, rows: u32, z_dev: *anyopaque, stream: ?*anyopaque) c_int;
 pub extern fn mlxs_moe_exl3_gemv_noalloc(code_dev: *const anyopaque, in_dim: u32, out_dim: u32, xh_dev: *const anyopaque, rows: u32, z_dev: *anyopaque, stream: ?*anyopaque) c_int;
 pub extern fn mlxs_moe_stats_get(h: *Moe, out: *Stats) c_int;
+/// acknowledges a recorded device error (the status word is sticky)
+pub extern fn mlxs_moe_status_clear(h: *Moe) c_int;
+/// the dispatch permutation alone (src/sdk_ext/quant.zig:269-301): slot ids -> order, offsets
+pub extern fn mlxs_moe_sort_rows(h: *Moe, slot_dev: ?*const i32, n: u32, n_slots: u32, order_dev: ?*u32, offsets_dev: *u32, stream: ?*anyopaque) c_int;
+/// self-test hook of the bounded waits
+pub extern fn mlxs_moe_debug_wait(h: *Moe, poll_limit: u32, withhold_stage: u32) c_int;
 
 /// stage order of the profile arrays (include/mlxs_moe.h MLXS_STAGE_*)
 pub const Stage = enum(u32) { router, dispatch, prep, gate_up, down, shared, combine, exchange, tensor_lane };

@@ -175,6 +175,15 @@ class Nvfp4Case(Exl3Case):
         return O.nvfp4_synth_record(self.record_seed(e), self.H, self.I, 0.02)
 
 
+def zipf_bias(n_experts, layer=0, s=1.1):
+    """ln p_e with p_e ~ rank^-s over a permutation of the experts seeded by the layer: added to N(0,1) logits it gives
+    the skewed routing of the benchmark's Zipf workloads (tau = 1)."""
+    perm = np.random.default_rng(4242 + layer).permutation(n_experts)
+    p = np.arange(1, n_experts + 1, dtype=np.float64) ** -s
+    p /= p.sum()
+    return np.log(p)[np.argsort(perm)].astype(np.float32)
+
+
 def rel_l2(got, ref):
     got = np.asarray(got, np.float64)
     ref = np.asarray(ref, np.float64)

@@ -71,6 +71,11 @@ def test_v2_full_manifest_records_and_parity():
     with pytest.raises(pkg.MlxsError) as ei:
         pkg.bank_peek(text=json.dumps(bad))
     assert "plain file name" in ei.value.msg
+    # a v2 record digest must be 64 lowercase hex digits (src/expert/bank.zig:432-466 decodes nothing else)
+    bad = json.loads(json.dumps(m)); bad["records"][2]["sha256"] = "AB" * 32
+    with pytest.raises(pkg.MlxsError) as ei:
+        pkg.bank_peek(text=json.dumps(bad))
+    assert "RecordSha256" in ei.value.msg and "record (0,2)" in ei.value.msg
 
 
 def test_v2_bank_of_mixed_layer_widths():
@@ -142,6 +147,9 @@ def test_fp4_manifests(nv):
     refused(lambda d: d["records"][0].update(offset=4), "InvalidRecord")
     refused(lambda d: d["records"].pop(), "InvalidRecord")
     refused(lambda d: d["records"][0].update(sha256="12"), "InvalidDigest")
+    # 64 characters that are not lowercase hex are no digest either (the reference decodes lowercase hex only)
+    refused(lambda d: d["records"][0].update(sha256="A" * 64), "InvalidDigest")
+    refused(lambda d: d["output_files"]["experts.bin"].update(sha256="g" * 64), "InvalidDigest")
     refused(lambda d: d["source"].update(revision="z" * 40), "InvalidSource")
     refused(lambda d: d["source"].update(repository=""), "InvalidSource")
     refused(lambda d: d["output_files"]["experts.bin"].update(size=1), "InvalidOutputFile")

@@ -44,6 +44,12 @@ def test_noalloc_matches_handle_entry_twice_in_a_row():
             with pytest.raises(pkg.MlxsError) as ei:
                 pkg.exl3_gemv_noalloc(code_d.data_ptr(), a["n_in"], a["n_out"], xd.data_ptr(), a["rows"], z.data_ptr(), None)
             assert word in ei.value.msg
+        # misaligned buffers are refused before any launch (the staging kernel reads 16-byte vectors)
+        for bad, word in ((dict(x=4), "xh_dev"), (dict(code=2), "code_dev"), (dict(z=2), "z_dev")):
+            with pytest.raises(pkg.MlxsError) as ei:
+                pkg.exl3_gemv_noalloc(code_d.data_ptr() + bad.get("code", 0), H, I, xd.data_ptr() + bad.get("x", 0), 4,
+                                      z.data_ptr() + bad.get("z", 0), None)
+            assert word in ei.value.msg and ei.value.rc == pkg.E_ARG
         assert case.status() == 0
     finally:
         case.close()
