@@ -628,6 +628,7 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of a few tokens")
     ap.add_argument("--experts", type=int, default=0, help="routed experts (smaller only for profiler captures)")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--ceiling", action="store_true", help="also measure the EXL3 decode's own ceiling (operands from registers)")
     ap.add_argument("--graph", action="store_true", help="also time the steps replayed from CUDA graphs (one GPU)")
     ap.add_argument("--placement", default=None, choices=["contiguous", "usage"],
                     help="expert parallel: experts in contiguous blocks, or dealt to the ranks by a routing histogram")
@@ -709,6 +710,16 @@ def main():
                                          "oracle fast f32 form with OpenMP (the whole workload at its own token count: --impl reference)",
                                "one_thread": {"value": T1 / dt1, "unit": UNIT,
                                               "sample": f"{T1} tokens x top-{K} ({len(recs1)} distinct experts)"}}
+    if args.ceiling and rank == 0 and wl["bank"] == "exl3":
+        hbm_peak = peaks()[0]
+        ceil = {}
+        for bits in (3, 2):
+            for mma in (0, 1):
+                tps = pkg.exl3_decode_rate(local, bits, bool(mma), 1 << 15)
+                gbs = tps * 32 * bits / 1e9
+                ceil[f"k{bits}_{'decode_mma' if mma else 'decode_only'}"] = {"tiles_per_s": tps, "code_gb_s": gbs,
+                                                                             "frac_of_measured_hbm": gbs / hbm_peak}
+        out["decode_ceiling"] = ceil
     rig.close()
     del rig
     # N = 1, default workload: the 24-layer Zipf stack of the expert-parallel configuration on the one GPU, so that the

@@ -82,7 +82,7 @@ typedef struct {
     uint64_t a2a_bytes_sent, a2a_bytes_recv;
     uint64_t resident_bytes;        /* HBM held by the handle */
     uint32_t device_status;         /* sticky error word written by kernels (0 = none) */
-    uint32_t reserved;
+    uint32_t ep_transport;          /* expert parallel: 0 none, 1 NCCL send/recv, 2 stores into the peers' windows */
 } mlxs_moe_stats;
 
 /* version gate and error text (csrc/q3_lookahead4.h:91, csrc/mlx_alloc_shim.h:14-17) */
@@ -196,6 +196,13 @@ int mlxs_moe_exl3_gemv(mlxs_moe *h, uint32_t layer, uint32_t expert, uint32_t pr
 int mlxs_moe_exl3_gemv_noalloc(const void *code_dev, uint32_t in_dim, uint32_t out_dim, const float *xh_dev,
                                uint32_t rows, float *z_dev, void *stream);
 
+/* Measured ceiling of the EXL3 in-register decode on this GPU (the reference's kernel bench has the same role for its
+ * lanes, src/arch/glm5_next/exl3_kbench.zig:1-23): the streaming kernel's decode statements alone, operands from
+ * registers, no loads, with (with_mma != 0) or without the one mma per tile, at the streaming kernel's residency.
+ * tiles_per_s x 32 bits bytes per tile (96 at K = 3, 64 at K = 2) is the code rate the decode can consume whatever
+ * the memory system delivers.  Allocates 16 bytes for the duration of the call; needs no handle. */
+int mlxs_moe_exl3_decode_rate(int32_t device, uint32_t bits, int with_mma, uint32_t tiles_per_warp, double *tiles_per_s);
+
 int mlxs_moe_stats_get(mlxs_moe *h, mlxs_moe_stats *out);
 /* The device status word is sticky (a host must see a fault it did not poll for): once a kernel has recorded an error
  * every mlxs_moe_forward_host returns MLXS_E_DEVICE_STATUS until the host acknowledges it here.  Synchronises the
@@ -234,7 +241,22 @@ int mlxs_moe_profile_read(mlxs_moe *h, mlxs_moe_profile *out);
  * resident and sharded, with a dispatch and a combine all-to-all per layer) ---- */
 /* 128-byte NCCL unique id made on rank 0 and handed to every rank by the host */
 int mlxs_moe_ep_unique_id(void *id128_out);
+/* Joins the ranks: the NCCL communicator, then one window of device memory per rank that the other ranks map through
+ * CUDA IPC (mlxs_moe_ep_window_bytes says how large).  With the windows mapped a layer call exchanges rows by plain
+ * stores into the peers' windows: no host synchronisation and no collective inside the call (stats.ep_transport = 2).
+ * If any rank cannot map a window all ranks fall back to NCCL send/recv with a host-read count exchange (= 1).
+ * Capacity: a rank's workspace holds min(world, 4) x max_tokens x top_k received rows; a call that sends a rank more
+ * is not executed on that rank, which records MLXS_E_DEVICE_STATUS ("expert parallel: more rows than the workspace
+ * holds"), while every rank still completes the call: nobody is left waiting.  Every rank must make the same sequence
+ * of layer calls (a rank without tokens calls with T = 0).  Waits for a peer are bounded (MLXS_EP_WAIT_MS, 20 s by
+ * default) and report through the status word.  Expert-parallel calls cannot be captured into a CUDA graph. */
 int mlxs_moe_ep_init(mlxs_moe *h, const void *id128);
+/* bytes of the window mlxs_moe_ep_init allocates per rank (pure arithmetic) */
+uint64_t mlxs_moe_ep_window_bytes(uint32_t world, uint32_t max_tokens, uint32_t top_k, uint32_t n_experts, uint32_t hidden);
+/* The all-ranks capacity check of the NCCL transport as a pure function: counts[(s * world + d) * stride] = rows rank s
+ * sends to rank d; returns the lowest rank that would receive more than rows_cap rows, or -1.  Every rank evaluates it
+ * on the same matrix and refuses the call together, before any send or receive is queued. */
+int32_t mlxs_moe_ep_overloaded_rank(const int32_t *counts, uint32_t world, uint32_t stride, uint64_t rows_cap);
 /* Where a layer's experts live: rank_of_expert[e] in [0, ep_world), every rank exactly n_experts / ep_world of them;
  * an expert's local slot is its order among the rank's experts.  Default: contiguous blocks.  Call on every rank with
  * the same table before the layer's experts are loaded.  (The reference keeps a usage tally per expert for its

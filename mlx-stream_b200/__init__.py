@@ -31,7 +31,8 @@ EXPORTS = [
     "mlxs_moe_stats_get", "mlxs_moe_profile_enable", "mlxs_moe_profile_read", "mlxs_moe_ep_unique_id", "mlxs_moe_ep_init", "mlxs_moe_ep_plan",
     "mlxs_moe_set_placement", "mlxs_moe_set_router_weight", "mlxs_moe_logits", "mlxs_moe_forward_x",
     "mlxs_moe_set_layer_bits", "mlxs_moe_layer_record_bytes", "mlxs_moe_bank_layer_bits_text",
-    "mlxs_moe_status_clear", "mlxs_moe_sort_rows", "mlxs_moe_debug_wait",
+    "mlxs_moe_ep_window_bytes", "mlxs_moe_ep_overloaded_rank",
+    "mlxs_moe_status_clear", "mlxs_moe_sort_rows", "mlxs_moe_debug_wait", "mlxs_moe_exl3_decode_rate",
     "mlxs_moe_bank_verify", "mlxs_moe_usage_enable", "mlxs_moe_usage_add", "mlxs_moe_usage_read", "mlxs_moe_usage_reset", "mlxs_moe_plan_placement",
 ]
 
@@ -48,7 +49,7 @@ class Stats(C.Structure):
     _fields_ = [("route_calls", C.c_uint64), ("expert_calls", C.c_uint64), ("tokens", C.c_uint64),
                 ("assignments", C.c_uint64), ("distinct_experts_last", C.c_uint64), ("weight_bytes_last", C.c_uint64),
                 ("a2a_bytes_sent", C.c_uint64), ("a2a_bytes_recv", C.c_uint64), ("resident_bytes", C.c_uint64),
-                ("device_status", C.c_uint32), ("reserved", C.c_uint32)]
+                ("device_status", C.c_uint32), ("ep_transport", C.c_uint32)]
 
 
 STAGES = ["router", "dispatch", "prep", "gate_up", "down", "shared", "combine", "exchange", "tensor_lane"]
@@ -123,6 +124,11 @@ def lib():
         L.mlxs_moe_set_router_weight.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_int]
         L.mlxs_moe_logits.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
         L.mlxs_moe_forward_x.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
+        L.mlxs_moe_exl3_decode_rate.argtypes = [C.c_int32, C.c_uint32, C.c_int, C.c_uint32, C.POINTER(C.c_double)]
+        L.mlxs_moe_ep_window_bytes.restype = C.c_uint64
+        L.mlxs_moe_ep_window_bytes.argtypes = [C.c_uint32] * 5
+        L.mlxs_moe_ep_overloaded_rank.restype = C.c_int32
+        L.mlxs_moe_ep_overloaded_rank.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint64]
         L.mlxs_moe_status_clear.argtypes = [C.c_void_p]
         L.mlxs_moe_sort_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p]
         L.mlxs_moe_debug_wait.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32]
@@ -183,6 +189,13 @@ def bank_layer_bits(text):
     out = (C.c_uint32 * n.value)()
     _check(lib().mlxs_moe_bank_layer_bits_text(raw, out, n.value, C.byref(n)))
     return list(out)
+
+
+def exl3_decode_rate(device=0, bits=3, with_mma=True, tiles_per_warp=1 << 16):
+    """Tiles per second of the EXL3 in-register decode alone (operands from registers): the decode's own ceiling."""
+    out = C.c_double()
+    _check(lib().mlxs_moe_exl3_decode_rate(device, bits, int(with_mma), tiles_per_warp, C.byref(out)))
+    return out.value
 
 
 def exl3_gemv_noalloc(code, in_dim, out_dim, xh, rows, z, stream=None):

@@ -187,10 +187,8 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
     }
     if (c->shared_expert) {
         if ((rc = h->alloc(&h->sh_h, T * I * 2)) || (rc = h->alloc(&h->sh_out, T * H * 4))) return bail(rc);
-        if (T > 64) {
-            if ((rc = h->alloc(&h->sh_gu, 2 * T * I * 4))) return bail(rc);
-            if (shared_gemm_create(&h->sh_gemm)) return bail(fail(MLXS_E_CUDA, "create: cublasCreate failed"));
-        }
+        const size_t T16 = (T + 15) / 16 * 16;
+        if ((rc = h->alloc(&h->dg_hb, T16 * I * 2))) return bail(rc);
     }
     if (c->shared_expert || h->pf_tiles) {
         if (cudaStreamCreateWithFlags(&h->aux_stream, cudaStreamNonBlocking) != cudaSuccess ||
@@ -211,7 +209,6 @@ extern "C" void mlxs_moe_destroy(mlxs_moe* h) {
     cudaSetDevice(h->cfg.device);
     cudaDeviceSynchronize();
     mlxs_ep_destroy(h);
-    shared_gemm_destroy(h->sh_gemm);
     if (h->lane_fork) cudaEventDestroy(h->lane_fork);
     if (h->lane_join) cudaEventDestroy(h->lane_join);
     if (h->aux_fork) cudaEventDestroy(h->aux_fork);
@@ -357,6 +354,24 @@ extern "C" int mlxs_moe_set_router_bias(mlxs_moe* h, uint32_t layer, const float
     return MLXS_OK;
 }
 
+// batches of this many tokens or more take the tcgen05 form of the shared expert (dense_gemm.cu), smaller ones the
+// skinny streaming kernel (MLXS_SHARED_DENSE_MIN moves the limit)
+static uint32_t shared_dense_min() {
+    static const uint32_t v = getenv("MLXS_SHARED_DENSE_MIN") ? (uint32_t)atoi(getenv("MLXS_SHARED_DENSE_MIN")) : 65u;
+    return v;
+}
+// scratch of the dense tensor-core products, allocated with the first weights that need them
+static int dense_workspace(mlxs_moe* h) {
+    int rc;
+    const size_t T16 = ((size_t)h->cfg.max_tokens + 15) / 16 * 16;
+    if (!h->dg_xb && (rc = h->alloc(&h->dg_xb, T16 * h->cfg.hidden * 2))) return rc;
+    if (!h->dg_scratch) {
+        if ((rc = h->alloc(&h->dg_scratch, dense_gemm_scratch_bytes(h->sm_count))) || (rc = h->alloc(&h->dg_count, (size_t)h->sm_count * 4))) return rc;
+        CU(cudaMemset(h->dg_count, 0, (size_t)h->sm_count * 4));
+    }
+    return 0;
+}
+
 extern "C" int mlxs_moe_set_shared(mlxs_moe* h, uint32_t layer, const void* w1, const void* w3, const void* w2, int on_device) {
     if (!h || !w1 || !w3 || !w2) return fail(MLXS_E_ARG, "set_shared: null argument");
     if (layer >= h->cfg.n_layers) return fail(MLXS_E_ARG, "set_shared: layer %u of %u", layer, h->cfg.n_layers);
@@ -370,6 +385,15 @@ extern "C" int mlxs_moe_set_shared(mlxs_moe* h, uint32_t layer, const void* w1, 
     CU(cudaMemcpy(L.sh_w1, w1, n, k));
     CU(cudaMemcpy(L.sh_w3, w3, n, k));
     CU(cudaMemcpy(L.sh_w2, w2, n, k));
+    // the tensor-core form of the same weights, when the handle can see batches that take it
+    if (h->cfg.max_tokens < shared_dense_min() || !dense_gemm_supported(h->cfg.inter, h->cfg.hidden, 0) ||
+        !dense_gemm_supported(h->cfg.hidden, h->cfg.inter, 1))
+        return MLXS_OK;
+    if ((rc = dense_workspace(h))) return rc;
+    if (!L.sh_gu_t && ((rc = h->alloc(&L.sh_gu_t, 2 * n)) || (rc = h->alloc(&L.sh_d_t, n)))) return rc;
+    CU(launch_dense_retile(L.sh_w1, L.sh_w3, h->cfg.inter, h->cfg.hidden, L.sh_gu_t, 0));
+    CU(launch_dense_retile(L.sh_w2, nullptr, h->cfg.hidden, h->cfg.inter, L.sh_d_t, 0));
+    CU(cudaStreamSynchronize(0));
     return MLXS_OK;
 }
 
@@ -509,8 +533,13 @@ extern "C" int mlxs_moe_set_router_weight(mlxs_moe* h, uint32_t layer, const voi
     int rc;
     if (!L.router_w && (rc = h->alloc(&L.router_w, n))) return rc;
     if (!h->logits_ws && (rc = h->alloc(&h->logits_ws, (size_t)h->cfg.max_tokens * h->cfg.n_experts * 4))) return rc;
-    if (!h->sh_gemm && h->cfg.max_tokens > 64 && shared_gemm_create(&h->sh_gemm)) return fail(MLXS_E_CUDA, "set_router_weight: cublasCreate failed");
     CU(cudaMemcpy(L.router_w, w_gate_bf16, n, on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice));
+    if (h->cfg.max_tokens > 64 && dense_gemm_supported(h->cfg.n_experts, h->cfg.hidden, 1)) {
+        if ((rc = dense_workspace(h))) return rc;
+        if (!L.router_w_t && (rc = h->alloc(&L.router_w_t, n))) return rc;
+        CU(launch_dense_retile(L.router_w, nullptr, h->cfg.n_experts, h->cfg.hidden, L.router_w_t, 0));
+        CU(cudaStreamSynchronize(0));
+    }
     return MLXS_OK;
 }
 
@@ -524,10 +553,9 @@ extern "C" int mlxs_moe_logits(mlxs_moe* h, uint32_t layer, const void* x_dev, u
     if (!L.router_w) return fail(MLXS_E_NOT_LOADED, "logits: layer %u has no router weight (mlxs_moe_set_router_weight)", layer);
     cudaStream_t st = (cudaStream_t)stream;
     StageTimer tm(h, MLXS_STAGE_ROUTER, st);
-    if (T > 64 && h->sh_gemm) {
-        if (launch_router_logits_gemm(h->sh_gemm, static_cast<const __nv_bfloat16*>(x_dev), L.router_w, T, c.n_experts, c.hidden,
-                                      logits_dev, st))
-            return fail(MLXS_E_CUDA, "logits: the library GEMM failed");
+    if (T > 64 && L.router_w_t) {
+        CU(launch_dense_logits(static_cast<const __nv_bfloat16*>(x_dev), L.router_w_t, T, c.n_experts, c.hidden, h->dg_xb, logits_dev,
+                               h->dg_scratch, h->dg_count, h->status, h->sm_count, st));
     } else {
         CU(launch_router_logits(static_cast<const __nv_bfloat16*>(x_dev), L.router_w, T, c.n_experts, c.hidden, logits_dev, st));
     }
@@ -544,7 +572,7 @@ extern "C" int mlxs_moe_forward_x(mlxs_moe* h, uint32_t layer, const void* x_dev
 
 // dispatch + the bank's expert kernels -> ro (unweighted rows in assignment order)
 int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, uint32_t T, uint32_t top_k,
-                    uint32_t n_exp, uint32_t first, void* ro, int ro_bf16, cudaStream_t st) {
+                    uint32_t n_exp, uint32_t first, void* ro, int ro_bf16, cudaStream_t st, const uint32_t* n_rows_dev) {
     const mlxs_moe_config& c = h->cfg;
     LayerBank& L = h->layers[layer];
     const uint32_t A = T * top_k;
@@ -560,10 +588,10 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
         StageTimer tm(h, MLXS_STAGE_DISPATCH, st);
         if (A > 2048)
             CU(launch_dispatch_large(ids_dev, A, n_exp, L.loaded_dev + first, h->tabs, h->chunk_rows, h->group_chunks, heavy,
-                                     h->blk_cnt, h->status, st));
+                                     h->blk_cnt, h->status, st, n_rows_dev));
         else
             CU(launch_dispatch(ids_dev, A, n_exp, L.loaded_dev + first, h->tabs, h->chunk_rows, h->group_chunks, heavy,
-                               h->status, st));
+                               h->status, st, n_rows_dev));
     }
     // The two lanes serve disjoint experts from separate staging buffers: the tensor-core lane (tile plan, row prep and
     // its two kernels) is queued on a stream of its own beside the streaming lane, forked after the dispatch
@@ -700,10 +728,12 @@ extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, 
     const float* shared = nullptr;
     auto run_shared = [&](cudaStream_t s) -> int {
         const float lim = c.act == MLXS_ACT_SWIGLU_CLAMPED ? c.act_limit : 0.f;
-        if (T > 64 && h->sh_gemm) {
-            if (launch_shared_expert_gemm(h->sh_gemm, static_cast<const __nv_bfloat16*>(x_dev), L.sh_w1, L.sh_w3, L.sh_w2, T,
-                                          c.hidden, c.inter, lim, h->sh_gu, h->sh_h, h->sh_out, s))
-                return fail(MLXS_E_CUDA, "experts: the shared expert's GEMMs failed");
+        if (T >= shared_dense_min() && L.sh_gu_t) {
+            DenseSharedArgs da{};
+            da.x = static_cast<const __nv_bfloat16*>(x_dev); da.w_gu = L.sh_gu_t; da.w_d = L.sh_d_t;
+            da.T = T; da.H = c.hidden; da.I = c.inter; da.limit = lim; da.xb = h->dg_xb; da.hb = h->dg_hb; da.out = h->sh_out;
+            da.part_scratch = h->dg_scratch; da.part_count = h->dg_count; da.status = h->status; da.sm_count = h->sm_count;
+            CU(launch_dense_shared_expert(da, s));
         } else {
             CU(launch_shared_expert(static_cast<const __nv_bfloat16*>(x_dev), L.sh_w1, L.sh_w3, L.sh_w2, T, c.hidden, c.inter,
                                     lim, h->sh_h, h->sh_out, s));
@@ -753,7 +783,10 @@ static int read_status(mlxs_moe* h, cudaStream_t st) {
     h->stats.device_status = s;
     if (s) return fail(MLXS_E_DEVICE_STATUS, "device status %u (%s)", s,
                        s == ST_BAD_EXPERT_ID ? "expert id out of range" : s == ST_NOT_LOADED ? "a routed expert is not resident"
-                       : s == ST_WORKLIST_OVERFLOW ? "work list overflow" : "a bounded wait ran out");
+                       : s == ST_WORKLIST_OVERFLOW ? "work list overflow"
+                       : s == ST_EP_OVERFLOW ? "expert parallel: a rank received more rows than the workspace holds"
+                       : s == ST_EP_TIMEOUT ? "expert parallel: a peer's signal did not arrive within the bound"
+                                            : "a bounded wait ran out");
     return MLXS_OK;
 }
 
@@ -849,6 +882,8 @@ extern "C" int mlxs_moe_stats_get(mlxs_moe* h, mlxs_moe_stats* out) {
     h->stats.distinct_experts_last = hdr[HDR_DISTINCT];
     h->stats.weight_bytes_last = (uint64_t)hdr[HDR_DISTINCT] * (h->last_logical ? h->last_logical : h->logical_bytes);
     h->stats.resident_bytes = h->resident;
+    h->stats.ep_transport = (uint32_t)mlxs_ep_transport(h);
+    mlxs_ep_bytes(h, &h->stats.a2a_bytes_sent, &h->stats.a2a_bytes_recv);
     *out = h->stats;
     return MLXS_OK;
 }

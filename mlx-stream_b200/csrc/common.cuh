@@ -14,7 +14,9 @@ enum : uint32_t {
     ST_WAIT_FULL = 2,        // a consumer's bounded wait for a staged copy ran out
     ST_WAIT_EMPTY = 3,       // the producer's bounded wait for a free stage ran out
     ST_WORKLIST_OVERFLOW = 4,
-    ST_NOT_LOADED = 5        // a routed expert has no resident record
+    ST_NOT_LOADED = 5,       // a routed expert has no resident record
+    ST_EP_OVERFLOW = 6,      // expert parallel: a rank received more rows than its workspace holds
+    ST_EP_TIMEOUT = 7        // expert parallel: a peer's epoch word did not arrive within the bound
 };
 
 constexpr uint32_t SCALE_BITS = 0x3DB504F3u;  // 128^-0.5 (src/arch/deepseek_v41/experts.zig:428-429)

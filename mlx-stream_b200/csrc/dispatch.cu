@@ -107,11 +107,13 @@ __device__ __forceinline__ void place_block(uint32_t id, bool valid, uint32_t a,
     }
 }
 
+// A_dev: when given, the row count is read on the device (it may not exceed A, the bound the launch was sized for)
 __global__ void __launch_bounds__(DTHREADS) dispatch_kernel(const int32_t* __restrict__ ids, uint32_t A, uint32_t E,
                                                             const uint8_t* __restrict__ loaded, DispatchTables t,
                                                             uint32_t CHUNK_ROWS, uint32_t GROUP_CHUNKS, uint32_t HEAVY,
-                                                            uint32_t* status) {
+                                                            uint32_t* status, const uint32_t* __restrict__ A_dev) {
     extern __shared__ uint32_t dsm[];
+    if (A_dev) A = min(A, *A_dev);
     uint32_t* cnt = dsm;                // [E] counts, then running write positions
     uint32_t* ws = dsm + E;             // [99] scan scratch
     const uint32_t tid = threadIdx.x;
@@ -143,8 +145,10 @@ __global__ void __launch_bounds__(DTHREADS) dispatch_kernel(const int32_t* __res
 // 1: per-block histograms; 2: one CTA turns them into per-block bases and builds the tables; 3: per-block stable placement
 __global__ void __launch_bounds__(DTHREADS) dispatch_count_kernel(const int32_t* __restrict__ ids, uint32_t A, uint32_t E,
                                                                   const uint8_t* __restrict__ loaded,
-                                                                  uint32_t* __restrict__ blk_cnt, uint32_t* status) {
+                                                                  uint32_t* __restrict__ blk_cnt, uint32_t* status,
+                                                                  const uint32_t* __restrict__ A_dev) {
     extern __shared__ uint32_t dsm[];
+    if (A_dev) A = min(A, *A_dev);
     for (uint32_t e = threadIdx.x; e < E; e += DTHREADS) dsm[e] = 0;
     __syncthreads();
     const uint32_t a = blockIdx.x * DTHREADS + threadIdx.x;
@@ -177,8 +181,11 @@ __global__ void __launch_bounds__(DTHREADS) dispatch_scan_kernel(uint32_t nblk, 
     build_tables(cnt, E, loaded, t, CHUNK_ROWS, GROUP_CHUNKS, HEAVY, ws, status);
 }
 __global__ void __launch_bounds__(DTHREADS) dispatch_place_kernel(const int32_t* __restrict__ ids, uint32_t A, uint32_t E,
-                                                                  const uint32_t* __restrict__ blk_base, DispatchTables t) {
+                                                                  const uint32_t* __restrict__ blk_base, DispatchTables t,
+                                                                  const uint32_t* __restrict__ A_dev) {
     extern __shared__ uint32_t dsm[];   // [E] running positions of this block
+    if (A_dev) A = min(A, *A_dev);
+    if (blockIdx.x * DTHREADS >= A) return;   // a block beyond the device-side count
     const uint32_t tid = threadIdx.x, a0 = blockIdx.x * DTHREADS, a = a0 + tid, left = A - a0;
     for (uint32_t e = tid; e < E; e += DTHREADS) dsm[e] = t.offsets[e] + blk_base[(size_t)blockIdx.x * E + e];
     __syncthreads();
@@ -192,19 +199,20 @@ __global__ void __launch_bounds__(DTHREADS) dispatch_place_kernel(const int32_t*
 
 cudaError_t launch_dispatch_large(const int32_t* ids, uint32_t A, uint32_t E, const uint8_t* loaded, DispatchTables t,
                                   uint32_t chunk_rows, uint32_t group_chunks, uint32_t heavy, uint32_t* blk_cnt,
-                                  uint32_t* status, cudaStream_t st) {
+                                  uint32_t* status, cudaStream_t st, const uint32_t* A_dev) {
     if (E > (uint32_t)DTHREADS) return cudaErrorInvalidValue;
     const uint32_t nblk = (A + DTHREADS - 1) / DTHREADS;
-    dispatch_count_kernel<<<nblk, DTHREADS, E * sizeof(uint32_t), st>>>(ids, A, E, loaded, blk_cnt, status);
+    dispatch_count_kernel<<<nblk, DTHREADS, E * sizeof(uint32_t), st>>>(ids, A, E, loaded, blk_cnt, status, A_dev);
     dispatch_scan_kernel<<<1, DTHREADS, (E + 99) * sizeof(uint32_t), st>>>(nblk, E, blk_cnt, t, chunk_rows, group_chunks, heavy, loaded, status);
-    dispatch_place_kernel<<<nblk, DTHREADS, E * sizeof(uint32_t), st>>>(ids, A, E, blk_cnt, t);
+    dispatch_place_kernel<<<nblk, DTHREADS, E * sizeof(uint32_t), st>>>(ids, A, E, blk_cnt, t, A_dev);
     return cudaGetLastError();
 }
 
 cudaError_t launch_dispatch(const int32_t* ids, uint32_t A, uint32_t E, const uint8_t* loaded, DispatchTables t,
-                            uint32_t chunk_rows, uint32_t group_chunks, uint32_t heavy, uint32_t* status, cudaStream_t st) {
+                            uint32_t chunk_rows, uint32_t group_chunks, uint32_t heavy, uint32_t* status, cudaStream_t st,
+                            const uint32_t* A_dev) {
     if (E > (uint32_t)DTHREADS) return cudaErrorInvalidValue;
-    dispatch_kernel<<<1, DTHREADS, (E + 99) * sizeof(uint32_t), st>>>(ids, A, E, loaded, t, chunk_rows, group_chunks, heavy, status);
+    dispatch_kernel<<<1, DTHREADS, (E + 99) * sizeof(uint32_t), st>>>(ids, A, E, loaded, t, chunk_rows, group_chunks, heavy, status, A_dev);
     return cudaGetLastError();
 }
 

@@ -12,13 +12,25 @@
 // partial row per (token, rank) comes back; the source adds the partials in k order of their first expert, then the
 // shared expert's row.
 //
-// NCCL point-to-point (grouped ncclSend / ncclRecv with exact counts).  The counts are exchanged with one small
-// all-gather and read by the host, which is the only host synchronisation of the layer.  NCCL is loaded at run time
+// Transport of the layer form: stores into the peers' memory.  At init every rank allocates one window (rows, per-row
+// records, returned partial rows, flag words), the ranks exchange CUDA IPC handles of their windows (one NCCL
+// all-gather) and map each other's.  A call then needs no host round trip and no library collective: the gather kernel
+// writes each row and its records straight into the destination rank's window over NVLink, the last block to finish
+// publishes the counts and an epoch word to every peer (release at system scope); the receiver's unpack kernel waits for
+// the epoch words of all sources with a bounded poll, builds the local call from the counts it finds there (the row
+// count stays on the device, the launches are sized for the capacity), and after the expert kernels the partial rows go
+// back the same way.  Every rank signals every rank in both phases of every call, which is also what makes one buffer
+// per direction enough: a peer cannot start writing call n + 1 into a window before its owner has finished reading
+// call n.  Ordinary stores and loads only: no bulk-tensor copy ever touches peer memory.
+// The per-assignment form (mlxs_ep_routed) and ranks whose windows could not be mapped use NCCL point-to-point (grouped
+// ncclSend / ncclRecv with exact counts after a count all-gather that the host reads).  NCCL is loaded at run time
 // (dlopen), so a single-GPU process needs no NCCL at all.
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <cstdlib>
 #include <cstring>
+#include <vector>
 
 #include "common.cuh"
 #include "handle.h"
@@ -80,6 +92,14 @@ struct EpState {
     uint32_t *urow = nullptr, *ustart = nullptr, *a_urow = nullptr, *a_first = nullptr, *xrow = nullptr;
     int32_t *send_urow = nullptr, *recv_urow = nullptr;
     float *send_w = nullptr, *recv_w = nullptr;
+    // peer-store transport
+    bool p2p = false;
+    uint8_t* win = nullptr;              // this rank's window
+    void* peer_base[64] = {nullptr};     // every rank's window as mapped here (own: win)
+    uint32_t epoch = 0;                  // call counter, the same on every rank
+    uint32_t* ctl = nullptr;             // device words: [0] push blocks done, [1] partial blocks done, [2] received rows, [3..] a0[W + 1]
+    unsigned long long* bytes_dev = nullptr;   // [2] bytes stored into / returned from peers' windows
+    uint32_t wait_polls = 0;             // bound of a wait for the peers' epoch words
 };
 
 #define CU(call)                                                                                            \
@@ -269,6 +289,239 @@ __global__ void ep_reduce_kernel(const float* __restrict__ ret, const uint32_t* 
 
 }  // namespace mlxs
 
+
+// ---- peer-store transport ----
+// One rank's window, the same layout on every rank (offsets in bytes):
+//   disp [W] x 128 B : {assignments, unique rows, epoch} written by source rank s at slot s
+//   retf [W] x 128 B : {epoch} written by rank r when its partial rows for this rank are in place
+//   rx_x [W][Tm][H] bf16 : rows from source s (a token's row once per pair of ranks)
+//   rx_meta [W][Tm * Kc] x 16 B : {local expert slot, row inside the source's block, weight bits, 0} per assignment
+//   ret  [W][Tm][H] f32 : partial rows coming back from rank r, by the row's index inside what this rank sent to r
+struct EpWin {
+    uint8_t* peer[64];
+    uint32_t W, me, Tm, Kc, H;
+    size_t off_disp, off_retf, off_rx_x, off_rx_meta, off_ret, bytes;
+};
+static EpWin ep_win_layout(uint32_t W, uint32_t me, uint32_t Tm, uint32_t Kc, uint32_t H) {
+    EpWin w{};
+    w.W = W; w.me = me; w.Tm = Tm; w.Kc = Kc; w.H = H;
+    size_t o = 0;
+    auto take = [&](size_t n) { const size_t at = o; o += (n + 255) / 256 * 256; return at; };
+    w.off_disp = take((size_t)W * 128);
+    w.off_retf = take((size_t)W * 128);
+    w.off_rx_x = take((size_t)W * Tm * H * 2);
+    w.off_rx_meta = take((size_t)W * Tm * Kc * 16);
+    w.off_ret = take((size_t)W * Tm * H * 4);
+    w.bytes = o;
+    return w;
+}
+extern "C" uint64_t mlxs_moe_ep_window_bytes(uint32_t world, uint32_t max_tokens, uint32_t top_k, uint32_t n_experts, uint32_t hidden) {
+    if (world == 0 || n_experts % world) return 0;
+    const uint32_t e_local = n_experts / world;
+    return ep_win_layout(world, 0, max_tokens, top_k < e_local ? top_k : e_local, hidden).bytes;
+}
+
+namespace mlxs {
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// bounded wait for a peer's epoch word in this rank's own window; false when it ran out
+__device__ __forceinline__ bool ep_wait_epoch(const uint32_t* word, uint32_t epoch, uint32_t polls) {
+    for (uint32_t i = 0; i < polls; ++i) {
+        if ((int32_t)(ld_acquire_sys(word) - epoch) >= 0) return true;
+        __nanosleep(i < 64 ? 100 : 1000);
+    }
+    return false;
+}
+
+// Sorted position i (assignments sorted by destination rank): the pair's first position stores the token's row into
+// the destination's window, every position its record; the last block to finish publishes counts and epoch to all.
+__global__ void __launch_bounds__(128) ep_push_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ meta,
+                                                      const int32_t* __restrict__ dest, const float* __restrict__ weights,
+                                                      const uint32_t* __restrict__ order, const uint32_t* __restrict__ offsets,
+                                                      const uint32_t* __restrict__ urow, const uint32_t* __restrict__ ustart,
+                                                      const int32_t* __restrict__ counts, uint32_t A, uint32_t k, EpWin w,
+                                                      uint32_t epoch, uint32_t* __restrict__ a_urow, uint32_t* __restrict__ a_first,
+                                                      uint32_t* ctl, unsigned long long* bytes) {
+    const uint32_t i = blockIdx.x;
+    if (i < A) {
+        const uint32_t a = order[i], u = urow[i];
+        const uint32_t d = (uint32_t)dest[a];
+        const bool first = i == 0 || urow[i - 1] != u;
+        const uint32_t ul = u - ustart[d], il = i - offsets[d];
+        uint8_t* pw = w.peer[d];
+        if (first) {
+            const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(a / k) * w.H);
+            uint4* dst = reinterpret_cast<uint4*>(pw + w.off_rx_x + ((size_t)w.me * w.Tm + ul) * w.H * 2);
+            for (uint32_t j = threadIdx.x; j < w.H / 8; j += blockDim.x) dst[j] = src[j];
+        }
+        if (threadIdx.x == 0) {
+            uint4* rec = reinterpret_cast<uint4*>(pw + w.off_rx_meta + ((size_t)w.me * w.Tm * w.Kc + il) * 16);
+            *rec = make_uint4((uint32_t)meta[a], ul, __float_as_uint(weights[a]), 0u);
+            a_urow[a] = d * w.Tm + ul;      // where this pair's partial row will land in this rank's `ret`
+            a_first[a] = first ? 1u : 0u;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t prev = atomicAdd(&ctl[0], 1u);
+        if (prev == gridDim.x - 1) {
+            ctl[0] = 0;
+            __threadfence_system();
+            unsigned long long sent = 0, back = 0;
+            for (uint32_t r = 0; r < w.W; ++r) {
+                uint32_t* slot = reinterpret_cast<uint32_t*>(w.peer[r] + w.off_disp + (size_t)w.me * 128);
+                const uint32_t na = A ? (uint32_t)counts[2 * r] : 0u, nu = A ? (uint32_t)counts[2 * r + 1] : 0u;
+                slot[0] = na;
+                slot[1] = nu;
+                st_release_sys(slot + 2, epoch);
+                if (r != w.me) { sent += (unsigned long long)nu * w.H * 2 + (unsigned long long)na * 16; back += (unsigned long long)nu * w.H * 4; }
+            }
+            atomicAdd(&bytes[0], sent);   // rows and records stored into peers' windows
+            atomicAdd(&bytes[3], back);   // partial rows the peers will store into this rank's window
+        }
+    }
+}
+
+// Receiver: wait for every source's epoch word, lay the received assignments out as one local call (ids, the row of
+// rx_x each reads, weights) and leave the row count on the device.  Every block waits by itself (the words are in
+// this GPU's memory); block 0 writes the counts.
+__global__ void __launch_bounds__(256) ep_unpack_kernel(EpWin w, uint32_t epoch, uint32_t polls, uint32_t rows_cap,
+                                                        int32_t* __restrict__ ids, uint32_t* __restrict__ xrow,
+                                                        float* __restrict__ wts, uint32_t* ctl, unsigned long long* bytes,
+                                                        uint32_t* status) {
+    __shared__ uint32_t a0[65];
+    __shared__ int s_ok;
+    const uint8_t* own = w.peer[w.me];
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < w.W) {
+        const uint32_t* slot = reinterpret_cast<const uint32_t*>(own + w.off_disp + (size_t)threadIdx.x * 128);
+        if (!ep_wait_epoch(slot + 2, epoch, polls)) s_ok = 0;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t run = 0;
+        for (uint32_t s = 0; s < w.W; ++s) {
+            a0[s] = run;
+            const uint32_t na = s_ok ? reinterpret_cast<const uint32_t*>(own + w.off_disp + (size_t)s * 128)[0] : 0u;
+            run += na <= w.Tm * w.Kc ? na : 0u;
+        }
+        if (!s_ok) { atomicMax(status, (uint32_t)ST_EP_TIMEOUT); run = 0; }
+        else if (run > rows_cap) { atomicMax(status, (uint32_t)ST_EP_OVERFLOW); run = 0; }
+        if (run == 0) for (uint32_t s = 0; s < w.W; ++s) a0[s] = 0;
+        a0[w.W] = run;
+        if (blockIdx.x == 0) {
+            ctl[2] = run;
+            for (uint32_t s = 0; s <= w.W; ++s) ctl[3 + s] = a0[s];
+            unsigned long long got = 0;
+            if (run)
+                for (uint32_t s = 0; s < w.W; ++s)
+                    if (s != w.me) {
+                        const uint32_t* slot = reinterpret_cast<const uint32_t*>(own + w.off_disp + (size_t)s * 128);
+                        got += (unsigned long long)slot[1] * w.H * 2 + (unsigned long long)slot[0] * 16;
+                    }
+            atomicAdd(&bytes[2], got);
+        }
+    }
+    __syncthreads();
+    const uint32_t RA = a0[w.W];
+    for (uint32_t a = blockIdx.x * blockDim.x + threadIdx.x; a < RA; a += gridDim.x * blockDim.x) {
+        uint32_t s = 0;
+        while (s + 1 < w.W && a >= a0[s + 1]) ++s;
+        const uint4 rec = *reinterpret_cast<const uint4*>(own + w.off_rx_meta + ((size_t)s * w.Tm * w.Kc + (a - a0[s])) * 16);
+        ids[a] = (int32_t)rec.x;
+        xrow[a] = s * w.Tm + (rec.y < w.Tm ? rec.y : 0u);
+        wts[a] = __uint_as_float(rec.z);
+    }
+}
+
+// partial[(s, ul)] = sum over the received assignments of that row of w x ro (each product rounded, folded in order, as
+// the single-GPU combine does; a row's assignments are consecutive), stored straight into source s's window; the last
+// block to finish tells every source that its partial rows are in place.
+__global__ void __launch_bounds__(256) ep_partial_push_kernel(const float* __restrict__ ro, const float* __restrict__ wts,
+                                                              const uint32_t* __restrict__ xrow, EpWin w, uint32_t epoch,
+                                                              uint32_t* ctl, unsigned long long* bytes) {
+    const uint32_t RA = ctl[2], H = w.H;
+    unsigned long long rows_out = 0;
+    for (uint32_t a = blockIdx.x; a < RA; a += gridDim.x) {
+        const uint32_t u = xrow[a];
+        if (a > 0 && xrow[a - 1] == u) continue;
+        const uint32_t s = u / w.Tm, ul = u % w.Tm;
+        float* dst = reinterpret_cast<float*>(w.peer[s] + w.off_ret + ((size_t)w.me * w.Tm + ul) * H * 4);
+        for (uint32_t col = threadIdx.x * 4; col < H; col += blockDim.x * 4) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            for (uint32_t b = a; b < RA && xrow[b] == u; ++b) {
+                const float wb = wts[b];
+                const float4 v = *reinterpret_cast<const float4*>(ro + (size_t)b * H + col);
+                const float r4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float p = __fadd_rn(__fmul_rn(r4[q], wb), 0.0f);
+                    acc[q] = b == a ? p : __fadd_rn(p, acc[q]);
+                }
+            }
+            *reinterpret_cast<float4*>(dst + col) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        }
+        if (s != w.me) rows_out += 1;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (rows_out) atomicAdd(&bytes[1], rows_out * H * 4);
+        const uint32_t prev = atomicAdd(&ctl[1], 1u);
+        if (prev == gridDim.x - 1) {
+            ctl[1] = 0;
+            __threadfence_system();
+            for (uint32_t r = 0; r < w.W; ++r)
+                st_release_sys(reinterpret_cast<uint32_t*>(w.peer[r] + w.off_retf + (size_t)w.me * 128), epoch);
+        }
+    }
+}
+
+// y[t] = bf16(sum of the token's partial rows, in k order of each pair's first assignment, + shared row); every block
+// first waits for the peers' "partial rows in place" words
+__global__ void __launch_bounds__(256) ep_reduce_p2p_kernel(EpWin w, uint32_t epoch, uint32_t polls,
+                                                            const uint32_t* __restrict__ a_urow, const uint32_t* __restrict__ a_first,
+                                                            const float* __restrict__ shared, uint32_t T, uint32_t k,
+                                                            __nv_bfloat16* __restrict__ y, uint32_t* status) {
+    __shared__ int s_ok;
+    const uint8_t* own = w.peer[w.me];
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < w.W) {
+        if (!ep_wait_epoch(reinterpret_cast<const uint32_t*>(own + w.off_retf + (size_t)threadIdx.x * 128), epoch, polls)) s_ok = 0;
+    }
+    __syncthreads();
+    if (!s_ok) { if (threadIdx.x == 0) atomicMax(status, (uint32_t)ST_EP_TIMEOUT); return; }
+    const uint32_t H = w.H, col = (blockIdx.x * blockDim.x + threadIdx.x) * 4, t = blockIdx.y;
+    if (col >= H || t >= T) return;
+    const float* ret = reinterpret_cast<const float*>(own + w.off_ret);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    bool any = false;
+    for (uint32_t j = 0; j < k; ++j) {
+        const uint32_t a = t * k + j;
+        if (!a_first[a]) continue;
+        const float4 v = *reinterpret_cast<const float4*>(ret + (size_t)a_urow[a] * H + col);
+        if (!any) { acc[0] = v.x; acc[1] = v.y; acc[2] = v.z; acc[3] = v.w; any = true; }
+        else { acc[0] = __fadd_rn(v.x, acc[0]); acc[1] = __fadd_rn(v.y, acc[1]); acc[2] = __fadd_rn(v.z, acc[2]); acc[3] = __fadd_rn(v.w, acc[3]); }
+    }
+    float o[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) o[q] = shared ? __fadd_rn(acc[q], shared[(size_t)t * H + col + q]) : acc[q];
+    __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+    *reinterpret_cast<uint2*>(y + (size_t)t * H + col) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+}
+
+}  // namespace mlxs
+
 extern "C" int mlxs_moe_ep_unique_id(void* id128_out) {
     if (!id128_out) return mlxs_fail(MLXS_E_ARG, "ep_unique_id: null argument");
     NcclApi* api = nccl_api();
@@ -320,11 +573,72 @@ extern "C" int mlxs_moe_ep_init(mlxs_moe* h, const void* id128) {
         return mlxs_fail(MLXS_E_CUDA, "cudaMallocHost: %s", cudaGetErrorString(e));
     }
     h->ep = ep;
+    // the peer-store transport; every rank must end up with the same answer, so the outcome is agreed with one all-reduce
+    {
+        int ok = getenv("MLXS_EP_NCCL_ONLY") ? 0 : 1;
+        const uint32_t Kc = c.top_k < h->e_local ? c.top_k : h->e_local;
+        EpWin wl = ep_win_layout((uint32_t)W, c.ep_rank, c.max_tokens, Kc, c.hidden);
+        cudaIpcMemHandle_t mine;
+        unsigned char* hbuf = nullptr;
+        std::vector<cudaIpcMemHandle_t> all(W);
+        if (W > 64) ok = 0;
+        if (ok && (h->alloc(&ep->win, wl.bytes) || h->alloc(&ep->ctl, 128 * 4) || h->alloc(&ep->bytes_dev, 4 * 8) ||
+                   h->alloc(&hbuf, W * sizeof(cudaIpcMemHandle_t))))
+            ok = 0;
+        if (ok && (cudaMemset(ep->win, 0, wl.off_rx_x) != cudaSuccess || cudaMemset(ep->ctl, 0, 128 * 4) != cudaSuccess ||
+                   cudaMemset(ep->bytes_dev, 0, 32) != cudaSuccess || cudaIpcGetMemHandle(&mine, ep->win) != cudaSuccess))
+            ok = 0;
+        if (hbuf) {
+            // the handles travel through the communicator that exists already; a rank that could not make one sends zeros
+            if (!ok) memset(&mine, 0, sizeof mine);
+            cudaMemcpy(hbuf + c.ep_rank * sizeof mine, &mine, sizeof mine, cudaMemcpyHostToDevice);
+            ncclResult_t nr = api->AllGather(hbuf + c.ep_rank * sizeof mine, hbuf, sizeof mine, ncclUint8, ep->comm, 0);
+            if (nr != ncclSuccess || cudaStreamSynchronize(0) != cudaSuccess ||
+                cudaMemcpy(all.data(), hbuf, W * sizeof mine, cudaMemcpyDeviceToHost) != cudaSuccess)
+                ok = 0;
+        }
+        if (ok) {
+            for (uint32_t r = 0; r < W && ok; ++r) {
+                if (r == c.ep_rank) { ep->peer_base[r] = ep->win; continue; }
+                if (cudaIpcOpenMemHandle(&ep->peer_base[r], all[r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+                    cudaGetLastError();
+                    ep->peer_base[r] = nullptr;
+                    ok = 0;
+                }
+            }
+        }
+        // agree: the transport is on only if every rank mapped every window (the flag rides in the first word of ctl)
+        int agreed = 0;
+        if (ep->ctl) {
+            const uint32_t flag = ok ? 1u : 0u;
+            cudaMemcpy(ep->ctl + 100, &flag, 4, cudaMemcpyHostToDevice);
+            uint32_t res = 0;
+            if (api->AllReduce(ep->ctl + 100, ep->ctl + 100, 1, ncclUint32, ncclMin, ep->comm, 0) == ncclSuccess &&
+                cudaStreamSynchronize(0) == cudaSuccess && cudaMemcpy(&res, ep->ctl + 100, 4, cudaMemcpyDeviceToHost) == cudaSuccess)
+                agreed = res == 1u;
+        }
+        ep->p2p = agreed != 0;
+        const char* ms = getenv("MLXS_EP_WAIT_MS");
+        const double wait_ms = ms ? atof(ms) : 20000.0;      // a wait polls about once a microsecond
+        ep->wait_polls = (uint32_t)(wait_ms * 1000.0 < 64.0 ? 64.0 : (wait_ms * 1000.0 > 4.0e9 ? 4.0e9 : wait_ms * 1000.0));
+    }
     return MLXS_OK;
+}
+
+int mlxs_ep_transport(const mlxs_moe* h) { return !h->ep ? 0 : (h->ep->p2p ? 2 : 1); }
+void mlxs_ep_bytes(mlxs_moe* h, uint64_t* sent, uint64_t* recv) {
+    if (!h->ep || !h->ep->p2p || !h->ep->bytes_dev) return;
+    unsigned long long b[4] = {0, 0, 0, 0};
+    if (cudaMemcpy(b, h->ep->bytes_dev, sizeof b, cudaMemcpyDeviceToHost) != cudaSuccess) return;
+    *sent += b[0] + b[1];
+    *recv += b[2] + b[3];
+    cudaMemset(h->ep->bytes_dev, 0, sizeof b);
 }
 
 void mlxs_ep_destroy(mlxs_moe* h) {
     if (!h->ep) return;
+    for (uint32_t r = 0; r < h->cfg.ep_world && r < 64; ++r)
+        if (r != h->cfg.ep_rank && h->ep->peer_base[r]) cudaIpcCloseMemHandle(h->ep->peer_base[r]);
     NcclApi* api = nccl_api();
     if (api && h->ep->comm) api->CommDestroy(h->ep->comm);
     if (h->ep->all_counts_host) cudaFreeHost(h->ep->all_counts_host);
@@ -427,11 +741,60 @@ int mlxs_ep_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t
     return MLXS_OK;
 }
 
+// the layer form over peer stores: no host round trip, no library collective
+static int ep_combined_p2p(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, const float* weights_dev,
+                           uint32_t T, const float* shared, void* y_dev, cudaStream_t st) {
+    EpState* ep = h->ep;
+    const mlxs_moe_config& c = h->cfg;
+    const uint32_t A = T * c.top_k, W = c.ep_world, H = c.hidden;
+    const uint32_t Kc = c.top_k < h->e_local ? c.top_k : h->e_local;
+    EpWin w = ep_win_layout(W, c.ep_rank, c.max_tokens, Kc, H);
+    for (uint32_t r = 0; r < W; ++r) w.peer[r] = static_cast<uint8_t*>(ep->peer_base[r]);
+    const uint32_t epoch = ++ep->epoch;
+    {
+        StageTimer tm(h, MLXS_STAGE_EXCHANGE, st);
+        if (A) mlxs::ep_dest_kernel<<<(A + 255) / 256, 256, 0, st>>>(ids_dev, A, c.n_experts, h->layers[layer].place_dev, ep->dest, ep->meta, h->status);
+        CU(launch_dispatch(ep->dest, A, W, nullptr, ep->rtab, h->chunk_rows, h->group_chunks, 0, h->status, st));
+        mlxs::ep_dedup_kernel<<<1, 1024, 0, st>>>(ep->rtab.order, ep->rtab.offsets, ep->dest, A, W, c.top_k, ep->urow, ep->ustart,
+                                                 ep->counts_dev);
+        mlxs::ep_push_kernel<<<A ? A : 1, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x_dev), ep->meta, ep->dest, weights_dev,
+                                                        ep->rtab.order, ep->rtab.offsets, ep->urow, ep->ustart, ep->counts_dev, A,
+                                                        c.top_k, w, epoch, ep->a_urow, ep->a_first, ep->ctl, ep->bytes_dev);
+        const uint32_t ub = (h->rows_cap + 255) / 256, ucap = 4u * (uint32_t)h->sm_count;
+        mlxs::ep_unpack_kernel<<<ub < ucap ? (ub ? ub : 1) : ucap, 256, 0, st>>>(w, epoch, ep->wait_polls, h->rows_cap, ep->recv_meta,
+                                                                            ep->xrow, ep->recv_w, ep->ctl, ep->bytes_dev, h->status);
+        CU(cudaGetLastError());
+    }
+    // the single-GPU kernels over the received assignments: each is its own "token" with one expert, its row of x in
+    // this rank's window through the table; the row count stays on the device
+    h->tabs.xrow = ep->xrow;
+    int rc = mlxs_run_routed(h, layer, ep->win + w.off_rx_x, ep->recv_meta, h->rows_cap, 1, h->e_local, 0, ep->recv_ro, 0, st,
+                             ep->ctl + 2);
+    h->tabs.xrow = nullptr;
+    if (rc) return rc;   // a refused launch: the peers' next wait runs out and reports, nobody hangs
+    {
+        StageTimer tm(h, MLXS_STAGE_EXCHANGE, st);
+        const uint32_t pcap = 8u * (uint32_t)h->sm_count;
+        mlxs::ep_partial_push_kernel<<<h->rows_cap < pcap ? (h->rows_cap ? h->rows_cap : 1) : pcap, 256, 0, st>>>(
+            static_cast<const float*>(ep->recv_ro), ep->recv_w, ep->xrow, w, epoch, ep->ctl, ep->bytes_dev);
+        CU(cudaGetLastError());
+    }
+    {
+        StageTimer tm(h, MLXS_STAGE_COMBINE, st);
+        dim3 grid((H / 4 + 255) / 256, T ? T : 1);
+        mlxs::ep_reduce_p2p_kernel<<<grid, 256, 0, st>>>(w, epoch, ep->wait_polls, ep->a_urow, ep->a_first, shared, T, c.top_k,
+                                                        static_cast<__nv_bfloat16*>(y_dev), h->status);
+        CU(cudaGetLastError());
+    }
+    return MLXS_OK;
+}
+
 int mlxs_ep_combined(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, const float* weights_dev,
                      uint32_t T, const float* shared, void* y_dev, cudaStream_t st) {
     EpState* ep = h->ep;
     NcclApi* api = nccl_api();
     if (!ep || !api) return mlxs_fail(MLXS_E_EP, "experts: expert-parallel exchange is not initialised (mlxs_moe_ep_init)");
+    if (ep->p2p) return ep_combined_p2p(h, layer, x_dev, ids_dev, weights_dev, T, shared, y_dev, st);
     const mlxs_moe_config& c = h->cfg;
     const uint32_t A = T * c.top_k, W = c.ep_world, H = c.hidden, me = c.ep_rank;
     if (W > 64) return mlxs_fail(MLXS_E_EP, "experts: ep_world %u > 64", W);

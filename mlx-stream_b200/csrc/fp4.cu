@@ -5,13 +5,12 @@
 // scale per projection, w = (e4m3 * g/2688) * e2m1 (src/arch/glm5_next/decode_kernels_ref.zig:13-65).
 //
 // Same streaming structure as the EXL3 kernels: a CTA owns 128 output rows of one expert for up to 16 token rows,
-// a producer warp streams the block's bytes through a bulk-copy ring, a consumer warp owns 16 output rows and decodes
-// two codes per integer op (the reference's decode8, src/arch/mimo_v2/kernels/header_mimo_moe_k1.metal:7-12) straight
-// into the mma A fragment.  The k order inside a 32-wide block is a fixed permutation applied to both operands.
-// MXFP4: the two mma of a 32-block accumulate into a fresh fragment that is folded with the block's power-of-two scale
-// in f32 (exact).  NVFP4: the decoded halves (e2m1 x 2^-14) are multiplied by the block's E4M3 scale in f16, which is
-// exact (a 2-bit by 4-bit significand product, every value a multiple of 2^-24); the global g/2688 x 2^14 is applied
-// once per output in f32.
+// a producer warp streams the block's bytes through a bulk-copy ring, a consumer warp owns 16 output rows and turns
+// its codes into f16 with the e2m1x2 conversion instruction (two codes per instruction, exact values; the reference
+// places the code bits with integer ops, src/arch/mimo_v2/kernels/header_mimo_moe_k1.metal:7-12) straight into the mma
+// A fragment.  MXFP4: the two mma of a 32-block accumulate into a fresh fragment that is folded with the block's
+// power-of-two scale in f32 (exact).  NVFP4: the decoded halves are multiplied by the block's E4M3 scale in f16, which
+// is exact (a 2-bit by 4-bit significand product of at most 6 x 448); the global g/2688 is applied once per output in f32.
 #include <cstdlib>
 
 #include "common.cuh"
@@ -85,8 +84,9 @@ cudaError_t launch_fp4_repack(const uint8_t* record_dev, uint32_t H, uint32_t I,
 // ------------------------------------------------------------------------------------------------------------
 // activation staging: bf16 rows -> f16 in the kernels' B-fragment order
 // ------------------------------------------------------------------------------------------------------------
-// per (chunk of 8 rows, 32-block): lane (g = row slot, c) holds 4 u32: {x[8c+0],x[8c+4]}, {x[8c+1],x[8c+5]},
-// {x[8c+2],x[8c+6]}, {x[8c+3],x[8c+7]} (the first two feed the block's first mma, the others the second)
+// per (chunk of 8 rows, 32-block): lane (g = row slot, c) holds 4 u32: {x[8c+0],x[8c+1]}, {x[8c+2],x[8c+3]},
+// {x[8c+4],x[8c+5]}, {x[8c+6],x[8c+7]} (the first two feed the block's first mma, the others the second): the order in
+// which the conversion instruction hands out a word's eight codes
 __global__ void __launch_bounds__(256) fp4_prep_kernel(const __nv_bfloat16* __restrict__ x, uint32_t top_k, uint32_t H,
                                                        DispatchTables t, uint32_t* __restrict__ xa) {
     const uint32_t chunk = blockIdx.x;
@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(256) fp4_prep_kernel(const __nv_bfloat16* __re
             h[2 * i + 1] = __float2half_rn(__uint_as_float(wds[i] & 0xFFFF0000u));
         }
         const uint32_t sb = idx / 4, c = idx % 4;
-        uint4 o = make_uint4(pack_h2(h[0], h[4]), pack_h2(h[1], h[5]), pack_h2(h[2], h[6]), pack_h2(h[3], h[7]));
+        uint4 o = make_uint4(pack_h2(h[0], h[1]), pack_h2(h[2], h[3]), pack_h2(h[4], h[5]), pack_h2(h[6], h[7]));
         *reinterpret_cast<uint4*>(xa + ((size_t)chunk * (H / 32) + sb) * F4_XA_SB_WORDS + (warp * 4 + c) * 4) = o;
     }
 }
@@ -148,11 +148,18 @@ struct Fp4Params {
 // Only `item` and `flags` (with the chunk count in bits 8..) are read every stage, the rest at the end of a part.
 struct F4Meta { int32_t item; uint32_t flags, mc, ks, chunk0, expert, nb, part; };
 
+// Eight e2m1 codes of a word -> four f16x2 through sm_100a's e2m1x2 conversion (one instruction per two codes, exact
+// values): h[i] = codes (2i, 2i + 1).  Measured against placing the code bits with shifts and masks (two logic ops per
+// weight on the half-rate pipe): the gate/up stream went from 0.57 to 0.77 of the measured HBM rate.
 __device__ __forceinline__ void fp4_decode8(uint32_t w, uint32_t (&h)[4]) {
-    h[0] = ((w << 9) & 0x0E000E00u) | ((w << 12) & 0x80008000u);
-    h[1] = ((w << 5) & 0x0E000E00u) | ((w << 8) & 0x80008000u);
-    h[2] = ((w << 1) & 0x0E000E00u) | ((w << 4) & 0x80008000u);
-    h[3] = ((w >> 3) & 0x0E000E00u) | (w & 0x80008000u);
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+        : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+        : "r"(w));
 }
 // E4M3 byte -> half2 (both halves) of its value (glm5n_e4m3: bits << 7 is the value x 2^-8 as f16; x 256 is exact)
 __device__ __forceinline__ __half2 e4m3_half2(uint32_t b) {
@@ -192,8 +199,10 @@ __device__ __forceinline__ void fp4_stage(const uint8_t* __restrict__ st, const 
             for (int i = 0; i < 4; ++i) { hx[i] = hmul2_u32(hx[i], sg); hy[i] = hmul2_u32(hy[i], sg8); }
         } else {
             const uint32_t bb = *reinterpret_cast<const uint16_t*>(sc + ((j * 4 + sb) * 8 + g) * 2);
-            s_lo = __uint_as_float(((bb & 0xFFu) + 14u) << 23);  // 2^(b - 127) x 2^14 (the halves carry 2^-14)
-            s_hi = __uint_as_float(((bb >> 8) + 14u) << 23);
+            // 2^(b - 127); b = 0 is the subnormal 2^-127 (src/arch/mimo_v2/moe.zig:410-413)
+            const uint32_t b0 = bb & 0xFFu, b1 = bb >> 8;
+            s_lo = __uint_as_float(b0 ? b0 << 23 : 0x00400000u);
+            s_hi = __uint_as_float(b1 ? b1 << 23 : 0x00400000u);
         }
         const uint32_t a1[4] = {hx[0], hy[0], hx[1], hy[1]}, a2[4] = {hx[2], hy[2], hx[3], hy[3]};
 #pragma unroll
@@ -357,7 +366,7 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
         // One CTA per item: the parts are folded left in the staging array.  Several CTAs: every part goes to its slot.
         const uint32_t g = lane >> 2, c = lane & 3u;
         float gs = 1.f;
-        if (NV) gs = (P.gscale[m.expert * 3 + (NPROJ == 2 ? p : 2)] / 2688.0f) * 16384.0f;
+        if (NV) gs = P.gscale[m.expert * 3 + (NPROJ == 2 ? p : 2)] / 2688.0f;
         const bool fold = NP == 1 && m.part != 0;
 #pragma unroll
         for (int mt = 0; mt < F4_GROUP; ++mt) {
@@ -431,11 +440,11 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
                     }
                 }
                 // the down kernel's B-fragment order: 32-block lane/8 of this 128 block, word c = (lane % 8) / 2,
-                // inputs 4 (lane % 2) + q -> register q, half lane % 2
+                // inputs 4 (lane % 2) + q in natural order
                 __half* dsth = reinterpret_cast<__half*>(
                     P.xa_d + ((size_t)chunk * (P.I / 32) + m.nb * 4 + (lane >> 3)) * F4_XA_SB_WORDS + (row * 4 + ((lane & 7u) >> 1)) * 4);
 #pragma unroll
-                for (int q = 0; q < 4; ++q) dsth[q * 2 + (lane & 1u)] = hv[q];
+                for (int q = 0; q < 4; ++q) dsth[4 * (lane & 1u) + q] = hv[q];
             } else if (valid) {
                 const float4 z4 = *reinterpret_cast<const float4*>(zs + ((size_t)mt * F4_CHUNK + row) * F4_ZS_STRIDE + lane * 4);
                 const uint32_t assign = P.t.order[P.t.chunk_row0[chunk] + row];

@@ -34,6 +34,9 @@ struct LayerBank {
     float* bias = nullptr;          // [E] or null
     __nv_bfloat16* router_w = nullptr;  // [E, H] bf16 or null (logits supplied by the caller)
     __nv_bfloat16 *sh_w1 = nullptr, *sh_w3 = nullptr, *sh_w2 = nullptr;
+    // the same weights re-tiled for the tensor-core products (dense_gemm.cu): gate + up interleaved, down
+    void *sh_gu_t = nullptr, *sh_d_t = nullptr;
+    void* router_w_t = nullptr;         // router weight re-tiled (n_experts a multiple of 256), or null
 };
 
 struct mlxs_moe {
@@ -61,8 +64,11 @@ struct mlxs_moe {
     uint32_t pf_min_rows = 0;   // experts with at least this many rows of a call take the tensor-core lane (0: lane off)
     uint32_t chunk_rows = CHUNK_ROWS, group_chunks = GROUP_CHUNKS;
     __nv_bfloat16* sh_h = nullptr;
-    float* sh_gu = nullptr;   // f32 [2][T, I] for the GEMM form of the shared expert
-    void* sh_gemm = nullptr;  // cuBLAS handle (plain dense GEMMs only)
+    // dense tensor-core products (shared expert, router logits): rows / h in the MMA's B-operand order, the scratch of
+    // the split reduction
+    uint16_t *dg_xb = nullptr, *dg_hb = nullptr;
+    float* dg_scratch = nullptr;
+    uint32_t* dg_count = nullptr;
     // small batches: the shared expert runs beside the routed kernels on a second stream (they leave SMs free)
     float* logits_ws = nullptr;       // [max_tokens, E] logits of mlxs_moe_forward_x
     float* ks_scratch = nullptr;      // K-split workspace of the streaming kernels (exl3.cu)
@@ -130,8 +136,10 @@ struct StageTimer {
 
 // dispatch + the bank's expert kernels over `rows` = n_tok * top_k assignment rows with ids in [0, n_exp) indexing this
 // rank's resident experts from `first`: unweighted rows in assignment order into ro (api.cu)
+// n_rows_dev (optional): the row count lives on the device; n_tok * top_k is then the bound the launches are sized for
 int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, uint32_t n_tok,
-                    uint32_t top_k, uint32_t n_exp, uint32_t first, void* ro, int ro_bf16, cudaStream_t st);
+                    uint32_t top_k, uint32_t n_exp, uint32_t first, void* ro, int ro_bf16, cudaStream_t st,
+                    const uint32_t* n_rows_dev = nullptr);
 // the expert-parallel form of the same (ep.cu): dispatch all-to-all, local experts, combine all-to-all
 int mlxs_ep_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, uint32_t T, void* ro,
                    int ro_bf16, cudaStream_t st);
@@ -140,5 +148,7 @@ int mlxs_ep_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t
 int mlxs_ep_combined(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, const float* weights_dev,
                      uint32_t T, const float* shared, void* y_dev, cudaStream_t st);
 void mlxs_ep_destroy(mlxs_moe* h);
+int mlxs_ep_transport(const mlxs_moe* h);                         // 0 none, 1 NCCL send/recv, 2 stores into peers' windows
+void mlxs_ep_bytes(mlxs_moe* h, uint64_t* sent, uint64_t* recv);  // adds the peer-store transport's device-side byte counts
 // sum of a u64 array over the ranks, in place (expert-parallel handles)
 int mlxs_ep_allreduce_u64(mlxs_moe* h, unsigned long long* buf_dev, size_t n, cudaStream_t st);

@@ -30,11 +30,9 @@ __host__ __device__ inline uint32_t x_row_of(const DispatchTables& t, uint32_t a
 }
 enum { HDR_NCHUNKS = 0, HDR_NGROUPS = 1, HDR_CTR_GU = 2, HDR_CTR_DOWN = 3, HDR_DISTINCT = 4, HDR_CTR_AUX = 5 };
 
-// logits[T, E] = f32(x) . f32(W)^T for decode-sized batches (own kernel), and the same through one library GEMM
+// logits[T, E] = f32(x) . f32(W)^T for decode-sized batches (larger ones: launch_dense_logits)
 cudaError_t launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* w, uint32_t T, uint32_t E, uint32_t H,
                                  float* logits, cudaStream_t st);
-int launch_router_logits_gemm(void* cublas, const __nv_bfloat16* x, const __nv_bfloat16* w, uint32_t T, uint32_t E, uint32_t H,
-                              float* logits, cudaStream_t st);
 cudaError_t launch_router(const float* logits, const float* bias, int T, int E, int K, int scoring, int norm,
                           float scale, int32_t* ids, float* weights, cudaStream_t st);
 
@@ -42,13 +40,15 @@ cudaError_t launch_router(const float* logits, const float* bias, int T, int E, 
 // loaded: optional [E] bytes, 0 = expert not resident -> *status = ST_NOT_LOADED.
 // chunk_rows / group_chunks: rows per chunk and chunks per work item of the bank's kernels (EXL3 4 x 4, FP4 8 x 2).
 // heavy > 0: experts with that many rows or more get no chunks (the tensor-core lane serves them from `offsets`).
+// A_dev (optional): the row count lives on the device (at most A, the bound the launch is sized for)
 cudaError_t launch_dispatch(const int32_t* ids, uint32_t A, uint32_t E, const uint8_t* loaded, DispatchTables t,
-                            uint32_t chunk_rows, uint32_t group_chunks, uint32_t heavy, uint32_t* status, cudaStream_t st);
+                            uint32_t chunk_rows, uint32_t group_chunks, uint32_t heavy, uint32_t* status, cudaStream_t st,
+                            const uint32_t* A_dev = nullptr);
 
 // the same over several CTAs for prefill-sized calls; blk_cnt: scratch [ceil(A/1024)][E]
 cudaError_t launch_dispatch_large(const int32_t* ids, uint32_t A, uint32_t E, const uint8_t* loaded, DispatchTables t,
                                   uint32_t chunk_rows, uint32_t group_chunks, uint32_t heavy, uint32_t* blk_cnt,
-                                  uint32_t* status, cudaStream_t st);
+                                  uint32_t* status, cudaStream_t st, const uint32_t* A_dev = nullptr);
 
 // usage tally: usage[e] += number of ids equal to e
 cudaError_t launch_usage_count(const int32_t* ids, uint64_t n, uint32_t E, unsigned long long* usage, cudaStream_t st);
@@ -211,12 +211,32 @@ bool fp4_prefill_supported(uint32_t H, uint32_t I);
 cudaError_t launch_shared_expert(const __nv_bfloat16* x, const __nv_bfloat16* w1, const __nv_bfloat16* w3,
                                  const __nv_bfloat16* w2, uint32_t T, uint32_t H, uint32_t I, float limit,
                                  __nv_bfloat16* h_ws, float* out, cudaStream_t st);
-// the same at prefill widths: the three plain GEMMs through cuBLAS, our activation kernel between them
-int shared_gemm_create(void** handle);
-void shared_gemm_destroy(void* handle);
-int launch_shared_expert_gemm(void* handle, const __nv_bfloat16* x, const __nv_bfloat16* w1, const __nv_bfloat16* w3,
-                              const __nv_bfloat16* w2, uint32_t T, uint32_t H, uint32_t I, float limit, float* gu_ws,
-                              __nv_bfloat16* h_ws, float* out, cudaStream_t st);
+// ---- dense bf16 products on tcgen05 (dense_gemm.cu): the shared expert at every batch size, the router's logits ----
+// weights re-tiled at load: w_gu = [I/128][H/64] stages of gate and up interleaved, w_d = [H/128][I/64]; see the file
+struct DenseSharedArgs {
+    const __nv_bfloat16* x;  // [T, H]
+    const void* w_gu;        // re-tiled gate + up, 2 * H * I bf16
+    const void* w_d;         // re-tiled down, H * I bf16
+    uint32_t T, H, I;
+    float limit;
+    uint16_t* xb;            // [T rounded to 16, H] rows in the MMA's B-operand order (scratch)
+    uint16_t* hb;            // [T rounded to 16, I] h in the same order (scratch)
+    float* out;              // [T, H] f32
+    float* part_scratch;     // dense_gemm_scratch_bytes(sm_count), or null: never split the reduction
+    uint32_t* part_count;    // [sm_count] zeroed once
+    uint32_t* status;
+    int sm_count;
+};
+size_t dense_gemm_scratch_bytes(int sm_count);
+bool dense_gemm_supported(uint32_t n_out, uint32_t K, int two_blocks);
+// W[n_out, K] row-major bf16 (w1 = a second matrix interleaved per 8-row group, or null) -> the tiled order
+cudaError_t launch_dense_retile(const __nv_bfloat16* w0, const __nv_bfloat16* w1, uint32_t n_out, uint32_t K, void* dst,
+                                cudaStream_t st);
+cudaError_t launch_dense_shared_expert(const DenseSharedArgs& a, cudaStream_t st);
+// logits[T, E] f32 = x . W_g^T with W_g re-tiled (single projection); E a multiple of 256
+cudaError_t launch_dense_logits(const __nv_bfloat16* x, const void* w_tiled, uint32_t T, uint32_t E, uint32_t H, uint16_t* xb,
+                                float* logits, float* part_scratch, uint32_t* part_count, uint32_t* status, int sm_count,
+                                cudaStream_t st);
 // y[t] = sum_k ro[t,k] w[t,k] (+ shared[t]) -> bf16
 cudaError_t launch_combine(const void* ro, int ro_bf16, const float* weights, const float* shared, uint32_t T,
                            uint32_t K, uint32_t H, int chain, __nv_bfloat16* y, cudaStream_t st);

@@ -1,4 +1,4 @@
-// The bf16 dense shared expert at decode widths, and the weighted combine.
+// The bf16 dense shared expert at decode widths (larger batches: dense_gemm.cu), and the weighted combine.
 //
 // Shared expert (src/arch/deepseek_v41/graph.zig:2162-2172): h = silu(min(w1 x, lim)) * clip(w3 x, +-lim) in f32,
 // rounded to the activation dtype, then w2 h.  Memory-bound on the 3 H I bf16 weights: a CTA owns 16 output features,
@@ -7,8 +7,6 @@
 //
 // Combine (src/arch/deepseek_v41/graph.zig:2182-2184; src/arch/mimo_v2/kernels/mimo_moe_combine.metal;
 // src/arch/glm5_next/kernels/glm5n_moe_combine.metal): fixed fold order k = 0..top_k-1, one bf16 rounding.
-#include <cublas_v2.h>
-
 #include "common.cuh"
 #include "kernels.h"
 
@@ -150,62 +148,6 @@ cudaError_t launch_shared_expert(const __nv_bfloat16* x, const __nv_bfloat16* w1
     if (e != cudaSuccess) return e;
     shared_kernel<1><<<H / 16, sh_warps(1) * 32, smem1, st>>>(h_ws, T, I, H, w2, nullptr, 0.f, nullptr, out);
     return cudaGetLastError();
-}
-
-// ---- prefill widths: the shared expert is a plain dense bf16 MLP, so its three GEMMs are the library's (cuBLAS);
-// the activation between them is ours ----
-__global__ void shared_act_kernel(const float* __restrict__ g, const float* __restrict__ u, size_t n, float limit,
-                                  __nv_bfloat16* __restrict__ h) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    float gate = g[i], up = u[i];
-    if (limit > 0.f) {
-        gate = (gate != gate) ? gate : (gate < limit ? gate : limit);
-        up = (up != up) ? up : (up > limit ? limit : (up < -limit ? -limit : up));
-    }
-    const float yv = 1.0f / (1.0f + expf(fabsf(gate)));
-    const float sg = gate < 0.f ? yv : 1.0f - yv;
-    h[i] = __float2bfloat16_rn((gate * sg) * up);
-}
-
-int shared_gemm_create(void** handle) {
-    cublasHandle_t h = nullptr;
-    if (cublasCreate(&h) != CUBLAS_STATUS_SUCCESS) return -1;
-    *handle = h;
-    return 0;
-}
-void shared_gemm_destroy(void* handle) {
-    if (handle) cublasDestroy(static_cast<cublasHandle_t>(handle));
-}
-// router logits at prefill widths: one plain library GEMM, logits[T, E] = X[T, H] . W[E, H]^T, f32 out
-int launch_router_logits_gemm(void* handle, const __nv_bfloat16* x, const __nv_bfloat16* w, uint32_t T, uint32_t E, uint32_t H,
-                              float* logits, cudaStream_t st) {
-    cublasHandle_t cb = static_cast<cublasHandle_t>(handle);
-    if (cublasSetStream(cb, st) != CUBLAS_STATUS_SUCCESS) return -1;
-    const float one = 1.f, zero = 0.f;
-    if (cublasGemmEx(cb, CUBLAS_OP_T, CUBLAS_OP_N, (int)E, (int)T, (int)H, &one, w, CUDA_R_16BF, (int)H, x, CUDA_R_16BF, (int)H,
-                     &zero, logits, CUDA_R_32F, (int)E, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT) != CUBLAS_STATUS_SUCCESS) return -2;
-    return 0;
-}
-// gu_ws: f32 [2][T, I]
-int launch_shared_expert_gemm(void* handle, const __nv_bfloat16* x, const __nv_bfloat16* w1, const __nv_bfloat16* w3,
-                              const __nv_bfloat16* w2, uint32_t T, uint32_t H, uint32_t I, float limit, float* gu_ws,
-                              __nv_bfloat16* h_ws, float* out, cudaStream_t st) {
-    cublasHandle_t cb = static_cast<cublasHandle_t>(handle);
-    if (cublasSetStream(cb, st) != CUBLAS_STATUS_SUCCESS) return -1;
-    const float one = 1.f, zero = 0.f;
-    float* g = gu_ws;
-    float* u = gu_ws + (size_t)T * I;
-    // row-major C[T, N] = X[T, K] . W[N, K]^T  ==  column-major C^T[N, T] = W^T-as-stored (op T) . X-as-stored
-    if (cublasGemmEx(cb, CUBLAS_OP_T, CUBLAS_OP_N, (int)I, (int)T, (int)H, &one, w1, CUDA_R_16BF, (int)H, x, CUDA_R_16BF, (int)H,
-                     &zero, g, CUDA_R_32F, (int)I, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT) != CUBLAS_STATUS_SUCCESS) return -2;
-    if (cublasGemmEx(cb, CUBLAS_OP_T, CUBLAS_OP_N, (int)I, (int)T, (int)H, &one, w3, CUDA_R_16BF, (int)H, x, CUDA_R_16BF, (int)H,
-                     &zero, u, CUDA_R_32F, (int)I, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT) != CUBLAS_STATUS_SUCCESS) return -2;
-    const size_t n = (size_t)T * I;
-    shared_act_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(g, u, n, limit, h_ws);
-    if (cublasGemmEx(cb, CUBLAS_OP_T, CUBLAS_OP_N, (int)H, (int)T, (int)I, &one, w2, CUDA_R_16BF, (int)I, h_ws, CUDA_R_16BF, (int)I,
-                     &zero, out, CUDA_R_32F, (int)H, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT) != CUBLAS_STATUS_SUCCESS) return -2;
-    return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
 // thread = 4 columns of one token

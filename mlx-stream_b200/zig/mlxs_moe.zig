@@ -43,7 +43,7 @@ pub const Stats = extern struct {
     a2a_bytes_recv: u64,
     resident_bytes: u64,
     device_status: u32,
-    reserved: u32,
+    ep_transport: u32,
 };
 
 pub extern fn mlxs_moe_abi() i32;
@@ -87,10 +87,16 @@ pub extern fn mlxs_moe_forward_host(h: *Moe, layer: u32, x_host: *const anyopaqu
 pub extern fn mlxs_moe_exl3_gemv(h: *Moe, layer: u32, expert: u32, proj: u32, xh_dev: *const anyopaque, rows: u32, z_dev: *anyopaque, stream: ?*anyopaque) c_int;
 pub extern fn mlxs_moe_exl3_gemv_noalloc(code_dev: *const anyopaque, in_dim: u32, out_dim: u32, xh_dev: *const anyopaque, rows: u32, z_dev: *anyopaque, stream: ?*anyopaque) c_int;
 pub extern fn mlxs_moe_stats_get(h: *Moe, out: *Stats) c_int;
+/// bytes of the per-rank window of the peer-store transport
+pub extern fn mlxs_moe_ep_window_bytes(world: u32, max_tokens: u32, top_k: u32, n_experts: u32, hidden: u32) u64;
+/// all-ranks capacity check of the NCCL transport (pure): lowest overloaded rank or -1
+pub extern fn mlxs_moe_ep_overloaded_rank(counts: [*]const i32, world: u32, stride: u32, rows_cap: u64) i32;
 /// acknowledges a recorded device error (the status word is sticky)
 pub extern fn mlxs_moe_status_clear(h: *Moe) c_int;
 /// the dispatch permutation alone (src/sdk_ext/quant.zig:269-301): slot ids -> order, offsets
 pub extern fn mlxs_moe_sort_rows(h: *Moe, slot_dev: ?*const i32, n: u32, n_slots: u32, order_dev: ?*u32, offsets_dev: *u32, stream: ?*anyopaque) c_int;
+/// measured ceiling of the in-register EXL3 decode (tiles per second, operands from registers)
+pub extern fn mlxs_moe_exl3_decode_rate(device: i32, bits: u32, with_mma: c_int, tiles_per_warp: u32, tiles_per_s: *f64) c_int;
 /// self-test hook of the bounded waits
 pub extern fn mlxs_moe_debug_wait(h: *Moe, poll_limit: u32, withhold_stage: u32) c_int;
 

@@ -110,8 +110,10 @@ def main():
         print(f"rank {rank} iter {it} rel-L2 layer {err:.3e} rows {err_ro:.3e}", flush=True)
         ok = ok and err < 1e-2 and err_ro < 1e-3
     st = moe.stats()
-    print(f"rank {rank} status {st.device_status} a2a sent {st.a2a_bytes_sent} recv {st.a2a_bytes_recv}", flush=True)
-    ok = ok and st.device_status == 0 and st.a2a_bytes_sent > 0
+    print(f"rank {rank} status {st.device_status} transport {st.ep_transport} a2a sent {st.a2a_bytes_sent} recv {st.a2a_bytes_recv}", flush=True)
+    # 2 = rows stored straight into the peers' windows, 1 = NCCL send/recv (forced with MLXS_EP_NCCL_ONLY)
+    want_transport = 1 if os.environ.get("MLXS_EP_NCCL_ONLY") else 2
+    ok = ok and st.device_status == 0 and st.a2a_bytes_sent > 0 and st.ep_transport == want_transport
     moe.close()
     print(f"rank {rank} {'OK' if ok else 'FAIL'}", flush=True)
     sys.exit(0 if ok else 1)

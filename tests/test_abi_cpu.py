@@ -76,6 +76,32 @@ def test_ep_plan_counts():
     assert "outside" in pkg.last_error()
 
 
+def test_ep_capacity_refusal_is_the_same_on_every_rank():
+    """The NCCL transport's capacity check is a pure function of the gathered count matrix, so every rank reaches the
+    same verdict before any send or receive is queued; the peer-store transport's window size is pure arithmetic."""
+    pkg = load_package()
+    L = pkg.lib()
+    W = 4
+    counts = np.zeros((W, W), np.int32)
+    counts[:, 2] = [300, 200, 100, 500]          # everyone sends most rows to rank 2
+    counts[:, 0] = 10
+    flat = np.ascontiguousarray(counts)
+    assert L.mlxs_moe_ep_overloaded_rank(flat.ctypes.data, W, 1, 1100) == -1
+    assert L.mlxs_moe_ep_overloaded_rank(flat.ctypes.data, W, 1, 1099) == 2
+    assert L.mlxs_moe_ep_overloaded_rank(flat.ctypes.data, W, 1, 39) == 0     # the lowest overloaded rank
+    # the deduplicated form carries two counts per pair: stride 2 reads the assignments
+    two = np.zeros((W, W, 2), np.int32)
+    two[..., 0] = counts
+    two[..., 1] = 1
+    assert L.mlxs_moe_ep_overloaded_rank(two.ctypes.data, W, 2, 1099) == 2
+    neg = flat.copy(); neg[1, 3] = -5
+    assert L.mlxs_moe_ep_overloaded_rank(neg.ctypes.data, W, 1, 10**9) == 3   # a corrupt count overloads its destination
+    # every rank evaluates the same matrix: the verdict does not depend on who asks (no rank argument at all)
+    b = L.mlxs_moe_ep_window_bytes(8, 64, 8, 256, 5120)
+    assert b >= 8 * 64 * 5120 * 6 and b < 8 * 64 * 5120 * 6 + 2 * 1024 * 1024
+    assert L.mlxs_moe_ep_window_bytes(3, 64, 8, 256, 5120) == 0              # 256 experts do not shard over 3 ranks
+
+
 def test_plan_placement_deals_by_use():
     """Most used first (ties to the lower id, as Profile.order, src/sdk_ext/expert/usage.zig:352-366), dealt to the
     ranks in snake order: every rank gets n_experts / world experts and the ranks' loads come out close."""

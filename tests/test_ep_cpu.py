@@ -266,3 +266,93 @@ def test_usage_placement_world2_gloo():
         assert sent == (300 + 50 * rank) * 4 and total == (300 + 350) * 4
         assert max(by_use) - min(by_use) < max(blocks) - min(blocks), (by_use, blocks)
     assert res[0][2] == res[1][2]
+
+
+def test_peer_store_protocol_model():
+    """The peer-store exchange restated in numpy over W in-process "ranks" with one window each: the same indices the
+    kernels use (a token's row once per destination rank at its index inside the pair's block, one 16-byte record per
+    assignment, partial rows back at d * Tm + ul, sums in k order of each pair's first assignment).  The result must
+    equal the single-rank weighted combine, for skewed and empty ranks, and a window is never larger than its layout."""
+    rng = np.random.default_rng(3)
+    W, E, k, H, Tm = 4, 16, 4, 8, 12
+    e_local = E // W
+    Kc = min(k, e_local)
+    place_rank = rng.permutation(E) % W                      # a scattered placement
+    place_slot = np.zeros(E, np.int64)
+    for r in range(W):
+        place_slot[place_rank == r] = np.arange(e_local)
+    expert_fn = lambda e, rows: rows * (1.0 + e) + 0.25 * e   # any per-expert map of a row
+    Ts = [12, 0, 5, 9]                                       # rank 1 has no tokens and still takes part
+    xs = [rng.standard_normal((T, H)) for T in Ts]
+    ids = [np.stack([rng.permutation(E)[:k] for _ in range(T)]).reshape(T, k) if T else np.zeros((0, k), np.int64) for T in Ts]
+    ws = [rng.random((T, k)) for T in Ts]
+    # windows
+    rx_x = np.full((W, W, Tm, H), np.nan)
+    rx_meta = np.full((W, W, Tm * Kc, 3), np.nan)
+    disp = np.zeros((W, W, 2), np.int64)
+    ret = np.full((W, W, Tm, H), np.nan)
+    a_urow, a_first = [], []
+    for me in range(W):                                      # push
+        A = Ts[me] * k
+        flat = ids[me].reshape(-1)
+        dest = place_rank[flat]
+        order = np.argsort(dest, kind="stable")
+        offsets = np.concatenate([[0], np.cumsum(np.bincount(dest, minlength=W))])
+        au, af = np.zeros(A, np.int64), np.zeros(A, np.int64)
+        u = -1
+        ustart = np.zeros(W + 1, np.int64)
+        urow = np.zeros(A, np.int64)
+        for i in range(A):
+            a = order[i]
+            first = i == 0 or order[i - 1] // k != a // k or dest[order[i - 1]] != dest[a]
+            u += int(first)
+            urow[i] = u
+        for r in range(W + 1):
+            ustart[r] = urow[offsets[r]] if r < W and offsets[r] < A else u + 1
+        for i in range(A):
+            a, d = order[i], dest[order[i]]
+            ul, il = urow[i] - ustart[d], i - offsets[d]
+            first = i == 0 or urow[i - 1] != urow[i]
+            assert ul < Tm and il < Tm * Kc
+            if first:
+                rx_x[d, me, ul] = xs[me][a // k]
+            rx_meta[d, me, il] = (place_slot[flat[a]], ul, ws[me].reshape(-1)[a])
+            au[a], af[a] = d * Tm + ul, int(first)
+        for r in range(W):
+            disp[r, me] = (offsets[r + 1] - offsets[r], ustart[r + 1] - ustart[r])
+        a_urow.append(au); a_first.append(af)
+    for me in range(W):                                      # unpack, local experts, partial rows back
+        a0 = np.concatenate([[0], np.cumsum(disp[me, :, 0])])
+        RA = a0[W]
+        slots = np.zeros(RA, np.int64); xrow = np.zeros(RA, np.int64); wt = np.zeros(RA)
+        for a in range(RA):
+            s = np.searchsorted(a0, a, side="right") - 1
+            rec = rx_meta[me, s, a - a0[s]]
+            slots[a], xrow[a], wt[a] = int(rec[0]), s * Tm + int(rec[1]), rec[2]
+        my_experts = {place_slot[e]: e for e in range(E) if place_rank[e] == me}
+        flat_x = rx_x[me].reshape(W * Tm, H)
+        ro = np.stack([expert_fn(my_experts[slots[a]], flat_x[xrow[a]]) for a in range(RA)]) if RA else np.zeros((0, H))
+        a = 0
+        while a < RA:
+            b, acc = a, None
+            while b < RA and xrow[b] == xrow[a]:
+                p = ro[b] * wt[b]
+                acc = p if acc is None else p + acc
+                b += 1
+            s, ul = divmod(xrow[a], Tm)
+            ret[s, me, ul] = acc
+            a = b
+    for me in range(W):                                      # final sums against the single-rank combine
+        flat_ret = ret[me].reshape(W * Tm, H)
+        for t in range(Ts[me]):
+            acc = None
+            for j in range(k):
+                a = t * k + j
+                if a_first[me][a]:
+                    v = flat_ret[a_urow[me][a]]
+                    acc = v if acc is None else v + acc
+            want = sum(expert_fn(ids[me][t, j], xs[me][t]) * ws[me][t, j] for j in range(k))
+            assert np.allclose(acc, want, rtol=1e-12), (me, t)
+    from __graft_entry__ import load_package
+    L = load_package().lib()
+    assert L.mlxs_moe_ep_window_bytes(W, Tm, k, E, H) >= W * Tm * H * 6 + W * Tm * Kc * 16 + 2 * W * 128

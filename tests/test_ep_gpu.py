@@ -12,12 +12,15 @@ pytestmark = pytest.mark.gpu
 HERE = Path(__file__).resolve().parent
 
 
+@pytest.mark.parametrize("transport", ["peer-stores", "nccl"])
 @pytest.mark.parametrize("placement", ["contiguous", "interleaved", "usage"])
-def test_two_rank_exchange_matches_oracle(placement):
+def test_two_rank_exchange_matches_oracle(placement, transport):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    if transport == "nccl":
+        env["MLXS_EP_NCCL_ONLY"] = "1"
     with tempfile.TemporaryDirectory() as rdv:
         procs = [subprocess.Popen([sys.executable, str(HERE / "ep_worker.py"), str(r), "2", rdv, placement], env=env,
                                   stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]

@@ -177,6 +177,69 @@ def test_nvfp4_tensor_lane_at_real_dims():
         case.close()
 
 
+# ---- the dense bf16 products (shared expert, router logits) on the tensor cores ----
+def _shared_ref(x, ws, limit):
+    """f64 shared expert (src/arch/deepseek_v41/graph.zig:2162-2172): clamped SwiGLU, h rounded to bf16, down."""
+    w1, w3, w2 = [O.bf16_bits_to_f32(w).astype(np.float64) for w in ws]
+    g = x.astype(np.float64) @ w1.T
+    u = x.astype(np.float64) @ w3.T
+    if limit > 0:
+        g = np.minimum(g, limit)
+        u = np.clip(u, -limit, limit)
+    h = g / (1.0 + np.exp(-g)) * u
+    h = O.bf16_bits_to_f32(O.f32_to_bf16_bits(h.astype(np.float32))).astype(np.float64)
+    return h @ w2.T
+
+
+@pytest.mark.parametrize("H,I", [(5120, 2304), (6144, 2048)])
+def test_shared_expert_alone_at_every_batch_size(H, I):
+    """Routed weights of zero leave y = bf16(shared expert): the skinny streaming kernel up to 64 tokens, the tcgen05
+    products above (one and several token tiles, a ragged last tile), all against the f64 product."""
+    case = Exl3Case(H, I, 2, 1, seed=11, shared=True, max_tokens=600)
+    try:
+        for T in (1, 8, 64, 65, 256, 300, 600):
+            x, _ = case.inputs(T, seed=900 + T)
+            ids = np.zeros((T, 1), np.int32)
+            w = np.zeros((T, 1), np.float32)
+            y = case.gpu_experts(x, ids, w)
+            ref = _shared_ref(x, case.shared, case.limit)
+            assert case.status() == 0
+            assert rel_l2(y, ref) < 4e-3, (T, rel_l2(y, ref))       # one bf16 rounding of the output: 2^-9 relative
+            assert (case.gpu_experts(x, ids, w) == y).all()
+            if T == 300:   # a row does not depend on the batch around it while the tile count stays the same
+                part = case.gpu_experts(x[256:300], ids[256:300], w[256:300])
+                assert np.allclose(part, y[256:300], rtol=2e-2, atol=1e-3)
+    finally:
+        case.close()
+
+
+def test_router_logits_on_the_tensor_cores():
+    """logits = f32(x) . W_g^T (src/arch/deepseek_v41/graph.zig:2033) for 256 experts above 64 tokens: the tcgen05
+    product against the f64 product, and the layer from x equal to the layer from those logits."""
+    import torch
+    case = Exl3Case(5120, 2304, 256, 8, seed=2, shared=False, max_tokens=600, experts_to_load=[])
+    try:
+        rng = np.random.default_rng(5)
+        wg = O.f32_to_bf16_bits((rng.standard_normal((256, 5120)) * 0.05).astype(np.float32))
+        case.moe.set_router_weight(0, wg.ctypes.data)
+        wf = O.bf16_bits_to_f32(wg).astype(np.float64)
+        for T in (64, 65, 300, 600):
+            x, _ = case.inputs(T, seed=70 + T)
+            ref = x.astype(np.float64) @ wf.T
+            xd = case.to_dev_bf16(x)
+            lg = torch.full((T, 256), float("nan"), dtype=torch.float32, device=case.dev)
+            case.moe.logits(0, xd.data_ptr(), T, lg.data_ptr(), None)
+            torch.cuda.synchronize()
+            got = lg.cpu().numpy()
+            assert np.allclose(got, ref, rtol=2e-5, atol=1e-4), (T, np.abs(got - ref).max())
+            ids, w = case.gpu_route(got)
+            rid, rw = case.cpu_route(got)
+            assert (ids == rid).all()
+        assert case.status() == 0
+    finally:
+        case.close()
+
+
 # ---- the reference's own fixture, no oracle in between ----
 def test_reference_expert_forward_fixture_on_the_gpu():
     """src/arch/glm5_next/exl3_forms_ref.zig:365-450: the fixture expert (seed 0x676C6D35, hidden 4096, inter 2048,
