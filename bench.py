@@ -178,12 +178,12 @@ def own_launches_per_layer(wl, T, world):
     # the tensor-core lane's kernels launch when the local call has enough "tokens" for an expert to reach the threshold
     # (with expert parallelism every received assignment is a token of the local call)
     if (T if world == 1 else A) >= LANE_MIN_ROWS:
-        n += 4 if wl["bank"] == "exl3" else 6   # plan, prep, gate/up, down (FP4: two tile shapes of each)
+        n += 6                              # tile plan, row prep, gate/up and down in two tile shapes each
     if wl["shared"]:
-        n += 2                              # gate/up + activation, down
+        n += 2 if T <= 64 else 3            # skinny gate/up + down, or row staging + the two tcgen05 products
     n += 1                                  # combine
     if world > 1:
-        n += 6                              # destination ranks, rank sort, dedup, gather, rebase / partial, final sum
+        n += 7                              # destination ranks, rank sort, dedup, push, unpack, partial push, final sum
     return n
 
 

@@ -178,8 +178,8 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
             h->pf_min_rows = (uint32_t)min_rows;
             const size_t heavy_max = A / (size_t)min_rows < h->e_local ? A / (size_t)min_rows : h->e_local;
             h->pf_max_tiles = (uint32_t)(A / PREFILL_TILE_ROWS + heavy_max + 1);
-            const size_t xa_bytes = exl3 ? exl3_prefill_xa_bytes(d, h->pf_max_tiles) : fp4_prefill_xa_bytes(c->hidden, A, h->pf_max_tiles);
-            const size_t xd_bytes = exl3 ? exl3_prefill_xd_bytes(d, h->pf_max_tiles) : fp4_prefill_xa_bytes(c->inter, A, h->pf_max_tiles);
+            const size_t xa_bytes = exl3 ? exl3_prefill_xa_bytes(d, A, h->pf_max_tiles) : fp4_prefill_xa_bytes(c->hidden, A, h->pf_max_tiles);
+            const size_t xd_bytes = exl3 ? exl3_prefill_xd_bytes(d, A, h->pf_max_tiles) : fp4_prefill_xa_bytes(c->inter, A, h->pf_max_tiles);
             if ((rc = h->alloc(&h->pf_tiles, prefill_tile_words(h->pf_max_tiles) * 4)) || (rc = h->alloc(&h->pf_xa, xa_bytes)) ||
                 (rc = h->alloc(&h->pf_xd, xd_bytes)))
                 return bail(rc);
@@ -616,7 +616,7 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
             Exl3PrefillArgs pa{};
             pa.L = EL; pa.d = d; pa.t = h->tabs; pa.n_experts = n_exp; pa.min_rows = heavy;
             pa.x = static_cast<const __nv_bfloat16*>(x_dev); pa.top_k = top_k; pa.tiles = h->pf_tiles; pa.max_tiles = h->pf_max_tiles;
-            pa.xa = h->pf_xa; pa.xd = h->pf_xd; pa.ro = static_cast<float*>(ro);
+            pa.xa = h->pf_xa; pa.xd = h->pf_xd; pa.rows_cap = h->rows_cap; pa.ro = static_cast<float*>(ro);
             pa.limit = limit; pa.status = h->status; pa.sm_count = h->sm_count;
             StageTimer tm(h, MLXS_STAGE_TENSOR_LANE, tl);
             CU(launch_exl3_prefill(pa, tl));

@@ -1,18 +1,27 @@
-// EXL3 expert kernels for prefill-sized batches: tcgen05 tensor cores with the trellis decoded into shared memory.
+// EXL3 expert kernels for experts with many rows: tcgen05 tensor cores, the trellis decoded straight into tensor memory.
 //
 // The reference's prefill lane (src/exl3/quant.zig:1040-1271; texts dsv41_prefill_dig_gemm_*_m128*.metal) decodes
 // trellis tiles to f16 in threadgroup memory per K stage and feeds its MMA units with f16 rotated activations and an
-// f32 accumulator.  Here the same roles map to Blackwell: a CTA owns (expert, 256 output columns of gate and up | 512
-// of down, up to 128 of the expert's rows).  W^T is the MMA's A operand (M = 128 output columns per accumulator
-// group) and the rows are the B operand (N = rows rounded to 16), so a ragged expert pads to 16 rows, not 128, and the
-// four accumulator groups D[128 columns x rows] fill the SM's tensor memory (512 columns).  One staged copy of the rows
-// serves all four groups: the rows, not the weights, are what travels most through L2 in this lane.
-//   * a producer warp streams the raw code (bulk copies) and the rows' rotated f16 activations, which a prep kernel
-//     laid out in global memory in the K-major core-matrix order the MMA reads, so a stage is one contiguous copy;
-//   * decode warps (one per 16-column tile and projection) turn each 16x16 tile into f16 with the same in-register
-//     decode as the decode-batch kernel and store it as K-major core matrices (no swizzle: a lane's four half2 land at
-//     row*16 + 4c bytes of a 128-byte core matrix, conflict free), then fence to the async proxy;
-//   * one thread issues tcgen05.mma.kind::f16 (K = 16 per instruction) and commits to mbarriers;
+// f32 accumulator.  Here a CTA owns (expert, a tile of its rows, a group of 128-column blocks).  W^T is the MMA's A
+// operand (M = 128 output columns per accumulator group) and lives in tensor memory; the rows are the B operand in
+// shared memory (N = rows rounded to 16), so a ragged expert pads to 16 rows.
+//   * the in-register decode of a 16x16 tile leaves a lane (g, c) with W[k 2c,2c+1 | 2c+8,2c+9][column g | g+8]: that
+//     is one tcgen05.st.16x256b fragment (thread (g, c): lanes g and g + 8, two adjacent 32-bit columns) once the K
+//     order inside a 16-block is taken as k' = 4c + 2 (k / 8) + k % 2, c = (k % 8) / 2; the rows are staged in the same
+//     order, which a dot product does not see.  One tile costs its decode plus one tensor-memory store: no shared-memory
+//     stores, no address arithmetic, no proxy fence;
+//   * tensor memory (512 columns) holds the f32 accumulators and a ring of two decoded stages of 64 inputs (32 columns
+//     per group and stage).  Two shapes: 4 groups x 64 rows (experts with up to 64 rows: gate and up of two column
+//     blocks, or four blocks of down) and 2 groups x 192 rows (the others: gate and up of one block, or two blocks of
+//     down), where one decode serves three times the rows;
+//   * a producer thread streams the raw code (bulk copies, one stage = 4 k-tiles of the group's blocks) and the rows'
+//     rotated f16 activations, which a prep kernel laid out as K-major core matrices;
+//   * 16 decode warps in two teams that take the stages alternately (team = stage parity = slot of the operand ring):
+//     a warp's chain per stage is barrier wait, decode, tensor-memory store latency, arrive, and with one team that
+//     chain, not the decode's instructions, set the stage time; two teams overlap each other's latencies.  A warp
+//     = (lane quarter q, team, half of the groups) decodes the tiles 2q and 2q + 1 of its groups for all 4 k-tiles;
+//   * one thread issues tcgen05.mma.kind::f16 (K = 16, A from tensor memory) and commits to mbarriers; it waits on one
+//     barrier per stage (decode warp 0 arrives only after it has seen the stage's rows land);
 //   * the decode warps run the epilogue: tcgen05.ld, transpose through shared memory, then the same row-wise math as
 //     the decode-batch kernel (Hadamard-128, svh, clamped SwiGLU, suh_d, Hadamard for gate/up; Hadamard, svh_d for down).
 // Every wait is bounded; on a give-up the CTA sets the status word, skips work and still frees its tensor memory.
@@ -24,18 +33,13 @@
 
 namespace mlxs {
 
-constexpr int PF_NT = 128;        // rows per tile (MMA N, rounded up to 16 per item)
-constexpr int PF_KS = 32;         // inputs per pipeline stage (2 k-tiles)
-constexpr int PF_KT = PF_KS / 16; // k-tiles per stage
-constexpr int PF_RAW_STAGES = 4;  // raw code ring
-constexpr int PF_A_STAGES = 2;    // decoded-A ring (decode -> MMA is a short hop)
-constexpr int PF_B_STAGES = 4;    // B-operand ring: deep, the rows come through L2 with a long latency
-constexpr int PF_A_BYTES = 128 * PF_KS * 2;     // decoded W^T (128 columns x 32 inputs f16) per projection per stage: 8 KB
-constexpr int PF_B_BYTES = PF_NT * PF_KS * 2;   // rows (128 x 32 f16) per projection per stage: 8 KB
-constexpr int PF_LBO_A = (128 / 8) * 128;       // byte distance of two core matrices along K, A operand
-constexpr int PF_LBO_B = (PF_NT / 8) * 128;     // the same, B operand
-constexpr int PF_SBO = 128;                     // byte distance of two core matrices along M / N
-constexpr int PF_EPI_ROWS = 32;                 // rows per epilogue batch
+constexpr int PF_KST = 64;          // inputs per operand stage (4 k-tiles)
+constexpr int PF_KT = PF_KST / 16;
+constexpr int PF_A_COLS = PF_KST / 2;   // tensor-memory columns of one group's decoded stage
+constexpr int PF_CAP0 = 64, PF_CAP1 = 192;   // rows per tile of the two shapes
+constexpr int PF_RAW_STAGES = 4, PF_B_MAX = 8;  // stages of the code ring; most stages of the row ring
+constexpr int PF_SBO = 128;                  // byte distance of two core matrices along N
+constexpr int PF_EPI_ROWS = 32;              // rows per epilogue batch
 constexpr int PF_ZS_STRIDE = 132;
 
 // ------------------------------------------------------------------------------------------------------------
@@ -94,21 +98,35 @@ __global__ void pf_plan_kernel(DispatchTables t, uint32_t E, const uint8_t* __re
 // ------------------------------------------------------------------------------------------------------------
 // prep: rows -> rotated f16 activations in the MMA's B-operand order
 // ------------------------------------------------------------------------------------------------------------
-// xa[tile][proj][stage = k/32][kc = (k%32)/8][rc = row/8][row%8][k%8] f16
-__device__ __forceinline__ size_t pf_xa_off(uint32_t nstage, uint32_t tile, uint32_t np, uint32_t p, uint32_t row, uint32_t k) {
-    return ((((size_t)tile * np + p) * nstage + k / PF_KS) * (PF_KS / 8) + (k % PF_KS) / 8) * (PF_NT * 8) + (row / 8) * 64 + (row % 8) * 8 + k % 8;
+// position of input k % 16 inside its 16-block: the order in which the decode's registers fill a tensor-memory fragment
+__host__ __device__ inline uint32_t pf_pos16(uint32_t k16) { return 4u * ((k16 & 7u) >> 1) + 2u * (k16 >> 3) + (k16 & 1u); }
+// Staged rows of a tile with rows16 rows over `width` inputs, as K-major core matrices:
+// [k / 64][kc = position / 8 of the stage][row / 8][row % 8][position % 8], so a stage of 64 inputs is rows16 x 128
+// contiguous bytes and the K-direction distance of two core matrices is rows16 x 16 bytes.  Element offset of (row, k):
+__device__ __forceinline__ size_t pf_b_off(uint32_t rows16, uint32_t row, uint32_t k) {
+    const uint32_t pos = (k % PF_KST) / 16 * 16 + pf_pos16(k % 16);   // position inside the stage
+    return (size_t)(k / PF_KST) * (rows16 * PF_KST) + (pos / 8) * (rows16 * 8) + (row / 8) * 64 + (row % 8) * 8 + pos % 8;
 }
+// a lane that holds the four consecutive inputs 4 (lane % 4) + q of a 16-block stores them as two half2: positions
+// p0, p0 + 1 and p0 + 4, p0 + 5 with p0 = {0, 8, 2, 10}[lane % 4]
+__device__ __forceinline__ void pf_store4(__half* tile_base, uint32_t rows16, uint32_t row, uint32_t k0, float v0, float v1, float v2, float v3) {
+    const __half2 h01 = __floats2half2_rn(v0, v1), h23 = __floats2half2_rn(v2, v3);
+    *reinterpret_cast<__half2*>(tile_base + pf_b_off(rows16, row, k0)) = h01;
+    *reinterpret_cast<__half2*>(tile_base + pf_b_off(rows16, row, k0 + 2)) = h23;
+}
+
+// xa: [projection][staging rows][H] (a tile's rows start at its first staging row, padded to 16)
 __global__ void __launch_bounds__(256) pf_prep_kernel(const __nv_bfloat16* __restrict__ x, uint32_t top_k, uint32_t H,
                                                       const __half* __restrict__ scales, size_t scales_stride,
-                                                      DispatchTables t, const uint32_t* __restrict__ tiles,
-                                                      __half* __restrict__ xa) {
-    const uint32_t tile = blockIdx.x;
-    if (tile >= tiles[0]) return;
-    const uint32_t* te = prefill_tile(tiles, 0, 0, tile);
+                                                      DispatchTables t, const uint32_t* __restrict__ tiles, uint32_t max_tiles,
+                                                      size_t proj_stride, __half* __restrict__ xa) {
+    const int list = blockIdx.x >= max_tiles;
+    const uint32_t tile = blockIdx.x - (list ? max_tiles : 0u);
+    if (tile >= tiles[list]) return;
+    const uint32_t* te = prefill_tile(tiles, list, max_tiles, tile);
     const uint32_t e = te[0], row0 = te[1], rows = te[2];
     const uint32_t rows16 = (rows + 15) / 16 * 16, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, b = blockIdx.y;
     const float S = __uint_as_float(SCALE_BITS);
-    const uint32_t nstage = H / PF_KS;
     for (uint32_t r = warp; r < rows16; r += 8) {
         const bool valid = r < rows;
         const uint32_t tok = valid ? x_row_of(t, t.order[row0 + r], top_k) : 0u;
@@ -127,9 +145,7 @@ __global__ void __launch_bounds__(256) pf_prep_kernel(const __nv_bfloat16* __res
                 hadamard128_warp(v, lane);
             }
             // src/kernels/exl3/dsv41_prefill_dig_take2v_5120.metal:57-58: the rotated input is rounded to f16
-            const __half2 h01 = __floats2half2_rn(v[0] * S, v[1] * S), h23 = __floats2half2_rn(v[2] * S, v[3] * S);
-            *reinterpret_cast<uint2*>(xa + pf_xa_off(nstage, tile, 2, p, r, b * 128 + lane * 4)) =
-                make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+            pf_store4(xa + p * proj_stride + (size_t)te[3] * H, rows16, r, b * 128 + lane * 4, v[0] * S, v[1] * S, v[2] * S, v[3] * S);
         }
     }
 }
@@ -141,118 +157,135 @@ struct PfParams {
     const uint32_t* code;        // layer base of the block stream (8 tiles of 8 K words per k-tile and projection)
     size_t expert_stride_words;
     uint32_t n_blocks, nkt;      // out / 128, in / 16
-    const __half* xa;            // B operand, layout of pf_xa_off
+    const __half* xa;            // B operand: [projection][staging rows][in]
+    size_t xa_proj_stride;       // elements between the projections' staged rows
     const uint32_t* tiles;
+    uint32_t max_tiles;
     DispatchTables t;
     const __half* scales;
     size_t scales_stride;
     uint32_t H, I;
-    __half* xd;                  // gate/up output = down's B operand
+    __half* xd;                  // gate/up output = down's B operand, [staging rows][I]
     float* ro;                   // down output [A, H]
     float limit;
     uint32_t* status;
+    uint32_t b_stages;
 };
 
-// NPROJ projections x CB adjacent 128-column blocks = 4 accumulator groups of 128 TMEM columns each
-template <int NPROJ, int CB, int KB>
+__device__ __forceinline__ void tmem_st_16x256(uint32_t taddr, const uint32_t (&v)[4]) {
+    asm volatile("tcgen05.st.sync.aligned.16x256b.x1.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// NPROJ projections x CB adjacent 128-column blocks = NG accumulator groups of NT tensor-memory columns each
+template <int NPROJ, int CB, int NT, int KB>
 __global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParams P) {
-    static_assert(NPROJ * CB == 4, "four accumulator groups fill the 512 tensor-memory columns at 128 rows");
+    constexpr int NG = NPROJ * CB;
+    constexpr int A_STAGES = 2;                        // one per decode team
+    static_assert((NG == 2 || NG == 4) && NG * NT + A_STAGES * NG * PF_A_COLS <= 512, "shape");
     extern __shared__ __align__(128) uint8_t smem_raw[];
+    constexpr int LIST = NG == 4 ? 0 : 1;
     constexpr int NCW = 16;                            // decode warps
-    constexpr int NG = NPROJ * CB;                     // accumulator groups
+    constexpr int TEAM = NCW / 2;                      // warps of a team
     constexpr int TW = 8 * KB;                         // words per 16x16 tile (KB bits per weight)
     constexpr int KSTRIDE = NPROJ * 8 * TW;            // words per k-tile in one block's code stream
     constexpr int RAW_BLK = PF_KT * KSTRIDE * 4;       // bytes of one block's k-tiles of a stage
     constexpr int RAW_BYTES = CB * RAW_BLK;
-    constexpr int TMEM_COLS = NG * PF_NT;
+    constexpr int B_TILE = NT * PF_KST * 2;            // one projection's rows of a stage (at the shape's row cap)
+    constexpr int B_SLOT = NPROJ * B_TILE;
     __shared__ __align__(8) uint64_t raw_full[PF_RAW_STAGES], raw_empty[PF_RAW_STAGES];
-    __shared__ __align__(8) uint64_t b_full[PF_B_STAGES], b_empty[PF_B_STAGES], a_full[PF_A_STAGES], a_empty[PF_A_STAGES];
+    __shared__ __align__(8) uint64_t b_full[PF_B_MAX], b_empty[PF_B_MAX], a_full[A_STAGES], a_empty[A_STAGES];
     __shared__ __align__(8) uint64_t acc_full, acc_empty, epi_bar;
     __shared__ uint32_t s_tmem;
     __shared__ volatile int s_abort;
-    // carve: [A ring: NG groups per stage][B ring: NPROJ operands per stage][raw ring][epilogue staging zs]
-    uint8_t* a_ring = smem_raw;
-    uint8_t* b_ring = a_ring + PF_A_STAGES * NG * PF_A_BYTES;
-    uint8_t* raw_ring = b_ring + PF_B_STAGES * NPROJ * PF_B_BYTES;
-    float* zs = reinterpret_cast<float*>(raw_ring + PF_RAW_STAGES * RAW_BYTES);
+    const uint32_t B_STAGES = P.b_stages;
+    constexpr uint32_t RAW_STAGES = PF_RAW_STAGES;
+    // carve: [B ring][raw ring][epilogue staging zs]
+    uint8_t* b_ring = smem_raw;
+    uint8_t* raw_ring = b_ring + B_STAGES * B_SLOT;
+    float* zs = reinterpret_cast<float*>(raw_ring + RAW_STAGES * RAW_BYTES);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t nbg = P.n_blocks / CB;              // column-block groups per row tile
+    const uint32_t n_items = P.tiles[LIST] * nbg;
     // a CTA without work leaves before it takes tensor memory (the whole CTA reads the same count)
-    if (blockIdx.x >= P.tiles[0] * (P.n_blocks / CB)) return;
+    if (blockIdx.x >= n_items) return;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < PF_RAW_STAGES; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], NCW); }
-        for (int s = 0; s < PF_A_STAGES; ++s) { mbar_init(&a_full[s], NCW); mbar_init(&a_empty[s], 1); }
-        for (int s = 0; s < PF_B_STAGES; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
+        // a code slot and an operand slot belong to one team: the stage count of an item is even, so stage parity = team
+        for (uint32_t s = 0; s < RAW_STAGES; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], TEAM); }
+        for (int s = 0; s < A_STAGES; ++s) { mbar_init(&a_full[s], TEAM); mbar_init(&a_empty[s], 1); }
+        for (uint32_t s = 0; s < B_STAGES; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
         mbar_init(&acc_full, 1);
         mbar_init(&acc_empty, NCW);
         mbar_init(&epi_bar, NCW);
         s_abort = 0;
         mbar_fence_init();
     }
-    if (warp == 0) tmem_alloc(&s_tmem, TMEM_COLS);  // tensor memory for the accumulators (one warp allocates and frees)
+    if (warp == 0) tmem_alloc(&s_tmem, 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = s_tmem;
-    const uint32_t n_tiles = P.tiles[0];
-    const uint32_t nbg = P.n_blocks / CB;              // column-block groups per row tile
-    const uint32_t n_items = n_tiles * nbg;
-    const uint32_t nstage = P.nkt / PF_KT;
+    const uint32_t tmem = s_tmem, tmem_a = tmem + NG * NT;
+    const uint32_t nstage = P.nkt / PF_KT, width = P.nkt * 16;
     auto give_up = [&](uint32_t code) { if (!s_abort) atomicMax(P.status, code); s_abort = 1; };
 
     if (warp == NCW) {
-        // ---------------- producer: raw code + B operand ----------------
+        // ---------------- producer: raw code + rows ----------------
         if (lane == 0) {
-            uint32_t rit = 0, bit = 0;
+            uint32_t rs = 0, rph = 0, bs = 0, bph = 0;
             for (uint32_t item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
-                const uint32_t tile = item / nbg, nb0 = (item % nbg) * CB, expert = prefill_tile(P.tiles, 0, 0, tile)[0];
+                const uint32_t nb0 = (item % nbg) * CB;
+                const uint32_t* te = prefill_tile(P.tiles, LIST, P.max_tiles, item / nbg);
+                const uint32_t expert = te[0], rows16 = (te[2] + 15) / 16 * 16, b_bytes = rows16 * PF_KST * 2;
                 const uint32_t* wsrc = P.code + (size_t)expert * P.expert_stride_words + (size_t)nb0 * P.nkt * KSTRIDE;
-                for (uint32_t ks = 0; ks < nstage; ++ks, ++rit, ++bit) {
-                    const uint32_t rs = rit % PF_RAW_STAGES, rph = (rit / PF_RAW_STAGES) & 1u;
-                    if (!mbar_wait_bounded(&raw_empty[rs], rph ^ 1u, &s_abort, 128)) { give_up(ST_WAIT_EMPTY); break; }
+                const __half* xsrc = P.xa + (size_t)te[3] * width;
+                bool ok = true;
+                for (uint32_t ks = 0; ks < nstage; ++ks) {
+                    if (!mbar_wait_bounded(&raw_empty[rs], rph ^ 1u, &s_abort, 64)) { give_up(ST_WAIT_EMPTY); ok = false; break; }
                     mbar_expect_tx(&raw_full[rs], RAW_BYTES);
                     for (int cb = 0; cb < CB; ++cb)
                         bulk_g2s(raw_ring + rs * RAW_BYTES + cb * RAW_BLK,
                                  wsrc + (size_t)cb * P.nkt * KSTRIDE + (size_t)ks * PF_KT * KSTRIDE, RAW_BLK, &raw_full[rs]);
-                    const uint32_t bs = bit % PF_B_STAGES, bph = (bit / PF_B_STAGES) & 1u;
-                    if (!mbar_wait_bounded(&b_empty[bs], bph ^ 1u, &s_abort, 128)) { give_up(ST_WAIT_EMPTY); break; }
-                    mbar_expect_tx(&b_full[bs], NPROJ * PF_B_BYTES);
+                    if (++rs == RAW_STAGES) { rs = 0; rph ^= 1u; }
+                    if (!mbar_wait_bounded(&b_empty[bs], bph ^ 1u, &s_abort, 64)) { give_up(ST_WAIT_EMPTY); ok = false; break; }
+                    mbar_expect_tx(&b_full[bs], NPROJ * b_bytes);
                     for (int p = 0; p < NPROJ; ++p)
-                        bulk_g2s(b_ring + (bs * NPROJ + p) * PF_B_BYTES,
-                                 P.xa + (((size_t)tile * NPROJ + p) * nstage + ks) * (PF_B_BYTES / 2), PF_B_BYTES, &b_full[bs]);
+                        bulk_g2s(b_ring + bs * B_SLOT + p * B_TILE, xsrc + p * P.xa_proj_stride + (size_t)ks * (rows16 * PF_KST), b_bytes, &b_full[bs]);
+                    if (++bs == B_STAGES) { bs = 0; bph ^= 1u; }
                 }
+                if (!ok) break;
             }
             if (s_abort) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
         }
     } else if (warp == NCW + 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            uint32_t bit = 0, nitem = 0;
+            uint32_t as = 0, aph = 0, bs = 0, nitem = 0;
+            const uint32_t b_ring_s = smem_u32(b_ring);
             for (uint32_t item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++nitem) {
-                const uint32_t tile = item / nbg, rows = prefill_tile(P.tiles, 0, 0, tile)[2];
-                const uint32_t idesc = umma_idesc(UMMA_F16, (rows + 15) / 16 * 16);
+                const uint32_t rows16 = (prefill_tile(P.tiles, LIST, P.max_tiles, item / nbg)[2] + 15) / 16 * 16;
+                const uint32_t idesc = umma_idesc(UMMA_F16, rows16), lbo_b = rows16 * 16;
+                const uint64_t bdesc0 = umma_smem_desc(b_ring_s, lbo_b, PF_SBO);   // + byte offset >> 4 in the low word
                 if (!mbar_wait_bounded(&acc_empty, (nitem & 1u) ^ 1u, &s_abort, 64)) { give_up(ST_WAIT_EMPTY); break; }
                 tc_fence_after();
                 bool ok = true;
-                for (uint32_t ks = 0; ks < nstage; ++ks, ++bit) {
-                    const uint32_t as = bit % PF_A_STAGES, aph = (bit / PF_A_STAGES) & 1u;
-                    const uint32_t bs = bit % PF_B_STAGES, bph = (bit / PF_B_STAGES) & 1u;
-                    if (!mbar_wait_bounded(&a_full[as], aph, &s_abort, 32) || !mbar_wait_bounded(&b_full[bs], bph, &s_abort, 32)) {
-                        give_up(ST_WAIT_FULL); ok = false; break;
-                    }
+                for (uint32_t kk = 0; kk < nstage; ++kk) {
+                    if (!mbar_wait_bounded(&a_full[as], aph, &s_abort)) { give_up(ST_WAIT_FULL); ok = false; break; }
                     tc_fence_after();
+                    const uint32_t ta = tmem_a + as * (NG * PF_A_COLS);
 #pragma unroll
                     for (int gq = 0; gq < NG; ++gq) {
-                        const int p = gq / CB;  // group = (projection, column block)
-                        const uint32_t a0 = smem_u32(a_ring + (as * NG + gq) * PF_A_BYTES);
-                        const uint32_t b0 = smem_u32(b_ring + (bs * NPROJ + p) * PF_B_BYTES);
+                        const int p = gq / CB;
+                        const uint64_t bd = bdesc0 + ((bs * B_SLOT + p * B_TILE) >> 4);
 #pragma unroll
-                        for (int i = 0; i < PF_KS / 16; ++i)
-                            umma_f16(tmem + gq * PF_NT, umma_smem_desc(a0 + i * 2 * PF_LBO_A, PF_LBO_A, PF_SBO),
-                                     umma_smem_desc(b0 + i * 2 * PF_LBO_B, PF_LBO_B, PF_SBO), idesc, (ks | (uint32_t)i) ? 1u : 0u);
+                        for (int i = 0; i < PF_KT; ++i)
+                            umma_f16_ts(tmem + gq * NT, ta + gq * PF_A_COLS + i * 8, bd + ((i * 2 * lbo_b) >> 4), idesc,
+                                        (kk | (uint32_t)i) ? 1u : 0u);
                     }
-                    umma_commit(&a_empty[as]);  // the stage's operands are free once these MMAs have read them
+                    umma_commit(&a_empty[as]);
                     umma_commit(&b_empty[bs]);
+                    if (++as == A_STAGES) { as = 0; aph ^= 1u; }
+                    if (++bs == B_STAGES) bs = 0;
                 }
                 if (!ok) break;
                 umma_commit(&acc_full);
@@ -260,14 +293,14 @@ __global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParam
         }
     } else {
         // ---------------- decode warps + epilogue ----------------
-        // a warp owns 16-column tile j of two accumulator groups: gate/up: projection hi, both column blocks;
-        // down: column blocks 2 hi and 2 hi + 1.  Group index = NPROJ == 2 ? hi * CB + cb : 2 hi + cb.
-        const uint32_t hi = warp >> 3, j = warp & 7u;
+        // warp = (lane quarter q, team, sub): its tensor-memory lanes hold the 16-column tiles 2q and 2q + 1 of every
+        // group; it decodes them for half of the groups (sub) in the stages of its team.
+        const uint32_t q = warp & 3u, slot = warp >> 2, team = slot >> 1, sub2 = slot & 1u;
+        constexpr int GPW = NG / 2;                     // groups per warp
         uint32_t wi, wj, lp;
         exl3_lane_plan_kb<KB>(lane, wi, wj, lp);
-        const uint32_t g = lane >> 2, c = lane & 3u;
         const float S = __uint_as_float(SCALE_BITS);
-        uint32_t rit = 0, bit = 0, nitem = 0, epi_ph = 0;
+        uint32_t gs0 = 0, nitem = 0, epi_ph = 0;        // gs0: stages of the items before this one
         auto epi_sync = [&]() -> bool {
             __syncwarp();
             if (lane == 0) mbar_arrive(&epi_bar);
@@ -276,61 +309,69 @@ __global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParam
             if (!ok) give_up(ST_WAIT_FULL);
             return ok;
         };
-        for (uint32_t item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++nitem) {
-            const uint32_t tile = item / nbg, nb0 = (item % nbg) * CB;
-            const uint32_t* te = prefill_tile(P.tiles, 0, 0, tile);
-            const uint32_t expert = te[0], row0 = te[1], rows = te[2];
+        for (uint32_t item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++nitem, gs0 += nstage) {
+            const uint32_t nb0 = (item % nbg) * CB;
+            const uint32_t* te = prefill_tile(P.tiles, LIST, P.max_tiles, item / nbg);
+            const uint32_t expert = te[0], row0 = te[1], rows = te[2], srow0 = te[3];
             bool ok = true;
-            for (uint32_t ks = 0; ks < nstage; ++ks, ++rit, ++bit) {
-                const uint32_t rs = rit % PF_RAW_STAGES, rph = (rit / PF_RAW_STAGES) & 1u;
-                const uint32_t as = bit % PF_A_STAGES, aph = (bit / PF_A_STAGES) & 1u;
-                if (!mbar_wait_bounded(&raw_full[rs], rph, &s_abort) || !mbar_wait_bounded(&a_empty[as], aph ^ 1u, &s_abort)) {
+            for (uint32_t ks = team; ks < nstage; ks += 2) {
+                const uint32_t gs = gs0 + ks;           // stage number since the kernel started (gs0 is even)
+                const uint32_t rs = gs % RAW_STAGES, rph = (gs / RAW_STAGES) & 1u, aph = (gs >> 1) & 1u;
+                if (!mbar_wait_bounded(&raw_full[rs], rph, &s_abort) || !mbar_wait_bounded(&a_empty[team], aph ^ 1u, &s_abort)) {
                     give_up(ST_WAIT_FULL); ok = false; break;
                 }
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    const uint32_t cb = NPROJ == 2 ? (uint32_t)u : 2u * hi + u, p = NPROJ == 2 ? hi : 0u;
-                    const uint32_t gq = NPROJ == 2 ? hi * CB + u : cb;
-                    const uint32_t* wt = reinterpret_cast<const uint32_t*>(raw_ring + rs * RAW_BYTES + cb * RAW_BLK) + p * (8u * TW) + j * TW;
-                    // the warp's 16 columns are core-matrix rows 2j and 2j+1; a lane's half2 pairs sit at g*16 + 4c bytes
-                    uint8_t* ad = a_ring + (as * NG + gq) * PF_A_BYTES + (2 * j) * PF_SBO + g * 16 + c * 4;
+                for (int gi = 0; gi < GPW; ++gi) {
+                    const uint32_t gq = sub2 * GPW + gi;
+                    const uint32_t p = NPROJ == 2 ? gq / CB : 0u, cb = NPROJ == 2 ? gq % CB : gq;
+                    // the group's code of this stage: [k-tile][projection][tile j][TW words]
+                    const uint32_t* wt = reinterpret_cast<const uint32_t*>(raw_ring + rs * RAW_BYTES + cb * RAW_BLK) + p * (8u * TW) + (2u * q) * TW;
+                    const uint32_t ta = tmem_a + ((q * 32u) << 16) + (team * NG + gq) * PF_A_COLS;
 #pragma unroll
                     for (int kt = 0; kt < PF_KT; ++kt) {
-                        uint32_t bq[4];
-                        exl3_decode_lane_kb<KB>(wt[kt * KSTRIDE + wi], wt[kt * KSTRIDE + wj], lp, bq);
-                        uint8_t* d = ad + (2 * kt) * PF_LBO_A;
-                        *reinterpret_cast<uint32_t*>(d) = bq[0];                        // k 2c,2c+1      column g
-                        *reinterpret_cast<uint32_t*>(d + PF_LBO_A) = bq[1];             // k 2c+8,2c+9    column g
-                        *reinterpret_cast<uint32_t*>(d + PF_SBO) = bq[2];               // k 2c,2c+1      column g+8
-                        *reinterpret_cast<uint32_t*>(d + PF_SBO + PF_LBO_A) = bq[3];    // k 2c+8,2c+9    column g+8
+#pragma unroll
+                        for (int jj = 0; jj < 2; ++jj) {
+                            const uint32_t* tw = wt + kt * KSTRIDE + jj * TW;
+                            uint32_t bq[4];
+                            exl3_decode_lane_kb<KB>(tw[wi], tw[wj], lp, bq);
+                            // thread (g, c): lanes g / g + 8 of the tile's 16, columns 2c, 2c + 1 of the k-tile's 8
+                            tmem_st_16x256(ta + ((jj * 16u) << 16) + kt * 8, bq);
+                        }
                     }
                 }
-                fence_async_smem();
+                tmem_wait_st();
+                tc_fence_before();
+                if (q == 0 && sub2 == 0) {  // the stage's rows have landed too: the issuer then waits on one barrier only
+                    const uint32_t bsl = gs % B_STAGES, bph = (gs / B_STAGES) & 1u;
+                    if (!mbar_wait_bounded(&b_full[bsl], bph, &s_abort)) { give_up(ST_WAIT_FULL); ok = false; break; }
+                }
                 __syncwarp();
-                if (lane == 0) { mbar_arrive(&a_full[as]); mbar_arrive(&raw_empty[rs]); }
+                if (lane == 0) { mbar_arrive(&a_full[team]); mbar_arrive(&raw_empty[rs]); }
             }
             if (!ok) break;
             // ---- epilogue: per column block, 32 rows at a time ----
             if (!mbar_wait_bounded(&acc_full, nitem & 1u, &s_abort)) { give_up(ST_WAIT_FULL); break; }
             tc_fence_after();
-            const uint32_t q = warp & 3u, sub = warp >> 2;
+            const uint32_t sub = warp >> 2;
             const uint32_t rows16 = (rows + 15) / 16 * 16;
-            for (uint32_t cb = 0; cb < (uint32_t)CB && ok; ++cb) {
+            for (uint32_t ecb = 0; ecb < (uint32_t)CB && ok; ++ecb) {
                 for (uint32_t rb = 0; rb < rows16 && ok; rb += PF_EPI_ROWS) {
                     // 16 warps: lane quarter q, then (projection, 16-row half) for gate/up; down uses warps 0..7
                     if (sub < 2u * NPROJ) {
                         const uint32_t ep = sub % NPROJ, half = sub / NPROJ;
-                        uint32_t v[16];
-                        tmem_ld16(tmem + ((q * 32u) << 16) + (ep * CB + cb) * PF_NT + rb + half * 16, v);
+                        if (rb + half * 16 < rows16) {
+                            uint32_t v[16];
+                            tmem_ld16(tmem + ((q * 32u) << 16) + (ep * CB + ecb) * NT + rb + half * 16, v);
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) zs[(ep * PF_EPI_ROWS + half * 16 + i) * PF_ZS_STRIDE + q * 32 + lane] = __uint_as_float(v[i]);
+                            for (int i = 0; i < 16; ++i) zs[(ep * PF_EPI_ROWS + half * 16 + i) * PF_ZS_STRIDE + q * 32 + lane] = __uint_as_float(v[i]);
+                        }
                     }
                     if (!epi_sync()) { ok = false; break; }
                     for (uint32_t rr = warp; rr < PF_EPI_ROWS; rr += NCW) {
                         const uint32_t r = rb + rr;
                         if (r >= rows16) continue;
                         const bool valid = r < rows;
-                        const uint32_t col = (nb0 + cb) * 128 + lane * 4;
+                        const uint32_t col = (nb0 + ecb) * 128 + lane * 4;
                         if (NPROJ == 2) {
                             float vv[4] = {0.f, 0.f, 0.f, 0.f};
                             if (valid) {
@@ -367,9 +408,7 @@ __global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParam
                                 hadamard128_warp(vv, lane);
                             }
                             // src/kernels/exl3/header_dig2_x.metal:104: the down input is rounded to f16
-                            const __half2 h01 = __floats2half2_rn(vv[0] * S, vv[1] * S), h23 = __floats2half2_rn(vv[2] * S, vv[3] * S);
-                            *reinterpret_cast<uint2*>(P.xd + pf_xa_off(P.I / PF_KS, tile, 1, 0, r, col)) =
-                                make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+                            pf_store4(P.xd + (size_t)srow0 * P.I, rows16, r, col, vv[0] * S, vv[1] * S, vv[2] * S, vv[3] * S);
                         } else if (valid) {
                             const float4 z4 = *reinterpret_cast<const float4*>(zs + rr * PF_ZS_STRIDE + lane * 4);
                             float vv[4] = {z4.x, z4.y, z4.z, z4.w};
@@ -396,15 +435,10 @@ __global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParam
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp == 0) tmem_free(tmem, TMEM_COLS);
+    if (warp == 0) tmem_free(tmem, 512);
 }
 
-static size_t pf_smem_bytes(int nproj) {
-    return (size_t)PF_A_STAGES * 4 * PF_A_BYTES + (size_t)PF_B_STAGES * nproj * PF_B_BYTES +
-           (size_t)PF_RAW_STAGES * PF_KT * 4 * 192 * 4 + (size_t)nproj * PF_EPI_ROWS * PF_ZS_STRIDE * sizeof(float);
-}
-
-bool exl3_prefill_supported(Exl3Dims d) { return (d.I / 128) % 2 == 0 && (d.H / 128) % 4 == 0; }
+bool exl3_prefill_supported(Exl3Dims d) { return (d.I / 128) % 2 == 0 && (d.H / 128) % 4 == 0 && d.H % PF_KST == 0 && d.I % PF_KST == 0; }
 
 cudaError_t launch_prefill_plan(DispatchTables t, uint32_t n_experts, const uint8_t* lane_flags, uint32_t min_rows,
                                 uint32_t cap0, uint32_t cap1, uint32_t max_tiles, uint32_t* tiles, uint32_t* status,
@@ -413,39 +447,48 @@ cudaError_t launch_prefill_plan(DispatchTables t, uint32_t n_experts, const uint
     return cudaGetLastError();
 }
 
-cudaError_t launch_exl3_prefill(const Exl3PrefillArgs& a, cudaStream_t st) {
-    cudaError_t e = launch_prefill_plan(a.t, a.n_experts, nullptr, a.min_rows, PF_NT, 0, a.max_tiles, a.tiles, a.status, st);
+template <int NPROJ, int CB, int NT, int KB>
+static cudaError_t pf_launch(PfParams P, int sm_count, cudaStream_t st) {
+    // ring depths: the code ring first (HBM latency), the rest of the budget to the rows
+    const size_t raw_bytes = (size_t)CB * PF_KT * NPROJ * 8 * 8 * KB * 4, b_slot = (size_t)NPROJ * NT * PF_KST * 2;
+    const size_t zs_bytes = (size_t)NPROJ * PF_EPI_ROWS * PF_ZS_STRIDE * sizeof(float);
+    const size_t budget = 222 * 1024 - zs_bytes;
+    if (PF_RAW_STAGES * raw_bytes + 2 * b_slot > budget) return cudaErrorInvalidValue;
+    size_t nb = (budget - PF_RAW_STAGES * raw_bytes) / b_slot;
+    P.b_stages = (uint32_t)(nb > (size_t)PF_B_MAX ? (size_t)PF_B_MAX : nb);
+    const size_t smem = P.b_stages * b_slot + PF_RAW_STAGES * raw_bytes + zs_bytes;
+    cudaError_t e = cudaFuncSetAttribute(exl3_prefill_kernel<NPROJ, CB, NT, KB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    pf_prep_kernel<<<dim3(a.max_tiles, a.d.H / 128), 256, 0, st>>>(a.x, a.top_k, a.d.H, a.L.scales, exl3_scales_per_expert(a.d),
-                                                                  a.t, a.tiles, a.xa);
-    if ((e = cudaGetLastError()) != cudaSuccess) return e;
-    PfParams P{};
-    P.tiles = a.tiles; P.t = a.t; P.scales = a.L.scales; P.scales_stride = exl3_scales_per_expert(a.d);
-    P.H = a.d.H; P.I = a.d.I; P.limit = a.limit; P.status = a.status;
-    // gate / up: two projections x two adjacent column blocks per CTA
-    P.code = a.L.gu_code; P.expert_stride_words = 2 * exl3_code_words(a.d); P.n_blocks = a.d.I / 128; P.nkt = a.d.H / 16;
-    P.xa = a.xa; P.xd = a.xd; P.ro = nullptr;
-    size_t smem = pf_smem_bytes(2);
-    if (a.d.K == 3) {
-        if ((e = cudaFuncSetAttribute(exl3_prefill_kernel<2, 2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
-        exl3_prefill_kernel<2, 2, 3><<<a.sm_count, 512 + 64, smem, st>>>(P);
-    } else {
-        if ((e = cudaFuncSetAttribute(exl3_prefill_kernel<2, 2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
-        exl3_prefill_kernel<2, 2, 2><<<a.sm_count, 512 + 64, smem, st>>>(P);
-    }
-    if ((e = cudaGetLastError()) != cudaSuccess) return e;
-    // down: four adjacent column blocks per CTA
-    P.code = a.L.d_code; P.expert_stride_words = exl3_code_words(a.d); P.n_blocks = a.d.H / 128; P.nkt = a.d.I / 16;
-    P.xa = a.xd; P.xd = nullptr; P.ro = a.ro;
-    smem = pf_smem_bytes(1);
-    if (a.d.K == 3) {
-        if ((e = cudaFuncSetAttribute(exl3_prefill_kernel<1, 4, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
-        exl3_prefill_kernel<1, 4, 3><<<a.sm_count, 512 + 64, smem, st>>>(P);
-    } else {
-        if ((e = cudaFuncSetAttribute(exl3_prefill_kernel<1, 4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
-        exl3_prefill_kernel<1, 4, 2><<<a.sm_count, 512 + 64, smem, st>>>(P);
-    }
+    exl3_prefill_kernel<NPROJ, CB, NT, KB><<<sm_count, 512 + 64, smem, st>>>(P);
     return cudaGetLastError();
+}
+
+template <int KB>
+static cudaError_t pf_launch_all(const Exl3PrefillArgs& a, cudaStream_t st) {
+    PfParams P{};
+    P.tiles = a.tiles; P.max_tiles = a.max_tiles; P.t = a.t; P.scales = a.L.scales; P.scales_stride = exl3_scales_per_expert(a.d);
+    P.H = a.d.H; P.I = a.d.I; P.limit = a.limit; P.status = a.status;
+    // gate / up: both projections of two adjacent column blocks (tiles up to 64 rows) or of one (up to 192 rows)
+    P.code = a.L.gu_code; P.expert_stride_words = 2 * exl3_code_words(a.d); P.n_blocks = a.d.I / 128; P.nkt = a.d.H / 16;
+    P.xa = a.xa; P.xa_proj_stride = exl3_prefill_staging_rows(a.rows_cap, a.max_tiles) * a.d.H; P.xd = a.xd; P.ro = nullptr;
+    cudaError_t e = pf_launch<2, 2, PF_CAP0, KB>(P, a.sm_count, st);
+    if (e != cudaSuccess) return e;
+    if ((e = pf_launch<2, 1, PF_CAP1, KB>(P, a.sm_count, st)) != cudaSuccess) return e;
+    // down: four adjacent column blocks per CTA, or two
+    P.code = a.L.d_code; P.expert_stride_words = exl3_code_words(a.d); P.n_blocks = a.d.H / 128; P.nkt = a.d.I / 16;
+    P.xa = a.xd; P.xa_proj_stride = 0; P.xd = nullptr; P.ro = a.ro;
+    if ((e = pf_launch<1, 4, PF_CAP0, KB>(P, a.sm_count, st)) != cudaSuccess) return e;
+    return pf_launch<1, 2, PF_CAP1, KB>(P, a.sm_count, st);
+}
+
+cudaError_t launch_exl3_prefill(const Exl3PrefillArgs& a, cudaStream_t st) {
+    cudaError_t e = launch_prefill_plan(a.t, a.n_experts, nullptr, a.min_rows, PF_CAP0, PF_CAP1, a.max_tiles, a.tiles, a.status, st);
+    if (e != cudaSuccess) return e;
+    pf_prep_kernel<<<dim3(2 * a.max_tiles, a.d.H / 128), 256, 0, st>>>(a.x, a.top_k, a.d.H, a.L.scales, exl3_scales_per_expert(a.d), a.t,
+                                                                      a.tiles, a.max_tiles,
+                                                                      exl3_prefill_staging_rows(a.rows_cap, a.max_tiles) * a.d.H, a.xa);
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    return a.d.K == 3 ? pf_launch_all<3>(a, st) : pf_launch_all<2>(a, st);
 }
 
 }  // namespace mlxs

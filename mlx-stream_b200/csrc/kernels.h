@@ -132,15 +132,18 @@ struct Exl3PrefillArgs {
     uint32_t top_k;
     uint32_t* tiles;         // [prefill_tile_words(max_tiles)] row-tile table (device scratch)
     uint32_t max_tiles;
-    __half* xa;              // [max_tiles][2][H/32][128 x 32] f16: rotated rows in the MMA's B-operand order
-    __half* xd;              // [max_tiles][I/32][128 x 32] f16
+    __half* xa;              // [2 projections][staging rows][H] f16: rotated rows in the MMA's B-operand order
+    __half* xd;              // [staging rows][I] f16
+    uint32_t rows_cap;       // assignment rows the staging was sized for
     float* ro;               // [A, H]
     float limit;
     uint32_t* status;
     int sm_count;
 };
-static inline size_t exl3_prefill_xa_bytes(Exl3Dims d, uint32_t max_tiles) { return (size_t)max_tiles * 2 * d.H * PREFILL_TILE_ROWS * 2; }
-static inline size_t exl3_prefill_xd_bytes(Exl3Dims d, uint32_t max_tiles) { return (size_t)max_tiles * d.I * PREFILL_TILE_ROWS * 2; }
+// staging rows: every tile's rows padded to 16, tiles in sorted order
+static inline size_t exl3_prefill_staging_rows(size_t rows_cap, uint32_t max_tiles) { return rows_cap + 16 * (size_t)(2 * max_tiles + 1); }
+static inline size_t exl3_prefill_xa_bytes(Exl3Dims d, size_t rows_cap, uint32_t max_tiles) { return 2 * exl3_prefill_staging_rows(rows_cap, max_tiles) * d.H * 2; }
+static inline size_t exl3_prefill_xd_bytes(Exl3Dims d, size_t rows_cap, uint32_t max_tiles) { return exl3_prefill_staging_rows(rows_cap, max_tiles) * d.I * 2; }
 cudaError_t launch_exl3_prefill(const Exl3PrefillArgs& a, cudaStream_t st);
 bool exl3_prefill_supported(Exl3Dims d);  // the lane groups 2 (gate/up) and 4 (down) column blocks per CTA
 

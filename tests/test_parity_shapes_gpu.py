@@ -206,9 +206,11 @@ def test_shared_expert_alone_at_every_batch_size(H, I):
             assert case.status() == 0
             assert rel_l2(y, ref) < 4e-3, (T, rel_l2(y, ref))       # one bf16 rounding of the output: 2^-9 relative
             assert (case.gpu_experts(x, ids, w) == y).all()
-            if T == 300:   # a row does not depend on the batch around it while the tile count stays the same
+            if T == 300:
+                # the ragged last tile (44 rows) against the same rows through the skinny kernel: two f32 sum orders, so
+                # an intermediate h may round to the neighbouring bf16 and move its row by a few 1e-4
                 part = case.gpu_experts(x[256:300], ids[256:300], w[256:300])
-                assert np.allclose(part, y[256:300], rtol=2e-2, atol=1e-3)
+                assert rel_l2(part, y[256:300]) < 2e-3, rel_l2(part, y[256:300])
     finally:
         case.close()
 
