@@ -144,12 +144,14 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
         (rc = h->alloc(&h->tabs.chunk_expert, max_chunks * 4)) || (rc = h->alloc(&h->tabs.chunk_row0, max_chunks * 4)) ||
         (rc = h->alloc(&h->tabs.chunk_rows, max_chunks * 4)) || (rc = h->alloc(&h->tabs.group_chunk0, max_chunks * 4)) ||
         (rc = h->alloc(&h->tabs.group_mc, max_chunks * 4)) || (rc = h->alloc(&h->status, 16)) ||
+        (rc = h->alloc(&h->front_bar, 16)) ||
         (rc = h->alloc(&h->blk_cnt, (A / 1024 + 1) * (size_t)c->n_experts * 4)) ||
         (rc = h->alloc(&h->staging, is_exl3(c->bank_kind) ? exl3_logical(H, I, 3) : h->logical_bytes)) ||
         (rc = h->alloc(&h->x_io, T * H * 2)) ||
         (rc = h->alloc(&h->y_io, T * H * 2)) || (rc = h->alloc(&h->logits_io, T * c->n_experts * 4)))
         return bail(rc);
-    if (cudaMemset(h->status, 0, 16) != cudaSuccess || cudaMemset(h->tabs.header, 0, 64) != cudaSuccess)
+    if (cudaMemset(h->status, 0, 16) != cudaSuccess || cudaMemset(h->tabs.header, 0, 64) != cudaSuccess ||
+        cudaMemset(h->front_bar, 0, 16) != cudaSuccess)
         return bail(fail(MLXS_E_CUDA, "create: cudaMemset failed"));
     if (is_exl3(c->bank_kind)) {
         const size_t kmax = (H > I ? H : I) / 16;
@@ -299,6 +301,24 @@ extern "C" int mlxs_moe_load_expert(mlxs_moe* h, uint32_t layer, uint32_t expert
     L.loaded[expert] = 1;
     return MLXS_OK;
 }
+
+// what a fused front launch needs beyond the experts call's own arguments (null: ids and weights are given)
+struct FrontCall {
+    const float* logits;   // the router's logits, or null when the layer starts from x (the layer's router weight)
+};
+
+// Can this call take the fused front kernel (front.cu)?  One rank, a decode-sized batch whose experts all stream, no
+// route tally to feed.  MLXS_FRONT_MAX moves the batch limit (0: never).
+static bool front_applies(const mlxs_moe* h, uint32_t T) {
+    static const uint32_t front_max = getenv("MLXS_FRONT_MAX") ? (uint32_t)atoi(getenv("MLXS_FRONT_MAX")) : 16u;
+    if (T == 0 || T > front_max || h->cfg.ep_world != 1 || h->usage_on || h->front_off) return false;
+    if (T * h->cfg.top_k > 2048) return false;
+    if (h->pf_tiles && T >= h->pf_min_rows) return false;   // some expert could take the tensor-core lane
+    return true;
+}
+
+static int experts_impl(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, const float* weights_dev,
+                        uint32_t T, void* y_dev, void* stream, const FrontCall* front);
 
 int mlxs_bank_for_each_record(const char* dir, uint32_t bank_kind, uint64_t H, uint64_t I, uint64_t E, uint64_t n_layers,
                               uint32_t e_first, uint32_t e_count, int (*layer_begin)(void* ctx, uint32_t layer, uint32_t bits),
@@ -565,6 +585,12 @@ extern "C" int mlxs_moe_logits(mlxs_moe* h, uint32_t layer, const void* x_dev, u
 extern "C" int mlxs_moe_forward_x(mlxs_moe* h, uint32_t layer, const void* x_dev, uint32_t T, void* y_dev, void* stream) {
     if (!h) return fail(MLXS_E_ARG, "forward_x: null handle");
     if (!h->logits_ws) return fail(MLXS_E_NOT_LOADED, "forward_x: no router weight was set (mlxs_moe_set_router_weight)");
+    if (layer < h->cfg.n_layers && front_applies(h, T)) {
+        // decode-sized: the logits product is the first phase of the fused front kernel (no [T, E] round trip, no launch)
+        if (!h->layers[layer].router_w) return fail(MLXS_E_NOT_LOADED, "forward_x: layer %u has no router weight (mlxs_moe_set_router_weight)", layer);
+        const FrontCall fc{nullptr};
+        return experts_impl(h, layer, x_dev, h->ids_ws, h->w_ws, T, y_dev, stream, &fc);
+    }
     int rc = mlxs_moe_logits(h, layer, x_dev, T, h->logits_ws, stream);
     if (rc) return rc;
     return mlxs_moe_forward(h, layer, x_dev, h->logits_ws, T, y_dev, stream);
@@ -584,7 +610,9 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
     const bool two_lanes = h->pf_tiles && T >= h->pf_min_rows;
     const uint32_t heavy = two_lanes ? h->pf_min_rows : 0u;
     h->last_logical = L.logical_bytes;
-    {
+    const bool front_done = h->front_done;   // the fused front kernel has sorted the rows and staged them already
+    h->front_done = false;
+    if (!front_done) {
         StageTimer tm(h, MLXS_STAGE_DISPATCH, st);
         if (A > 2048)
             CU(launch_dispatch_large(ids_dev, A, n_exp, L.loaded_dev + first, h->tabs, h->chunk_rows, h->group_chunks, heavy,
@@ -621,7 +649,7 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
             StageTimer tm(h, MLXS_STAGE_TENSOR_LANE, tl);
             CU(launch_exl3_prefill(pa, tl));
         }
-        {
+        if (!front_done) {
             StageTimer tm(h, MLXS_STAGE_PREP, st);
             CU(launch_exl3_prep_in(static_cast<const __nv_bfloat16*>(x_dev), top_k, EL, d, h->tabs, h->xa_gu, st));
         }
@@ -650,7 +678,7 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
             StageTimer tm(h, MLXS_STAGE_TENSOR_LANE, tl);
             CU(launch_fp4_prefill(pa, tl));
         }
-        {
+        if (!front_done) {
             StageTimer tm(h, MLXS_STAGE_PREP, st);
             CU(launch_fp4_prep(static_cast<const __nv_bfloat16*>(x_dev), top_k, c.hidden, h->tabs, h->xa_gu, st));
         }
@@ -698,8 +726,8 @@ extern "C" int mlxs_moe_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, c
     return run_routed(h, layer, x_dev, ids_dev, T, out_dev, 0, (cudaStream_t)stream);
 }
 
-extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev,
-                                const float* weights_dev, uint32_t T, void* y_dev, void* stream) {
+static int experts_impl(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev, const float* weights_dev,
+                        uint32_t T, void* y_dev, void* stream, const FrontCall* front) {
     int rc = check_call(h, layer, T, "experts");
     if (rc) return rc;
     if (T == 0 && h->cfg.ep_world == 1) return MLXS_OK;  // with expert parallelism an empty rank still serves its peers
@@ -752,7 +780,37 @@ extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, 
         CU(aux_guard.record());
         shared = h->sh_out;
     }
-    if (!ep_fused && (rc = run_routed(h, layer, x_dev, ids_dev, T, h->ro, ro_bf16, st))) return rc;
+    if (front) {
+        // route (from the logits, or from x through the layer's router weight), sort and stage in one launch; the
+        // shared expert is already running beside it
+        FrontArgs fa{};
+        fa.w_router = front->logits ? nullptr : L.router_w; fa.logits_out = h->logits_ws; fa.logits = front->logits; fa.bias = L.bias;
+        fa.E = (int)c.n_experts; fa.K = (int)c.top_k; fa.scoring = (int)c.scoring; fa.norm = (int)c.norm_topk; fa.scale = c.routed_scale;
+        fa.ids = h->ids_ws; fa.weights = h->w_ws; fa.T = T; fa.loaded = L.loaded_dev; fa.t = h->tabs;
+        fa.chunk_rows = h->chunk_rows; fa.group_chunks = h->group_chunks; fa.status = h->status;
+        fa.x = static_cast<const __nv_bfloat16*>(x_dev); fa.H = c.hidden; fa.bank_exl3 = is_exl3(c.bank_kind) ? 1 : 0;
+        fa.scales = L.scales; fa.scales_stride = is_exl3(c.bank_kind) ? exl3_scales_per_expert(Exl3Dims{c.hidden, c.inter, L.kbits}) : 0;
+        fa.xa = h->xa_gu; fa.bar = h->front_bar;
+        StageTimer tm(h, MLXS_STAGE_ROUTER, st);
+        const cudaError_t fe = launch_front(fa, st);
+        h->stats.route_calls += 1;
+        if (fe == cudaSuccess) {
+            h->front_done = true;
+        } else {
+            // the cooperative launch was refused (no room for all of its CTAs at once): the same work as separate
+            // kernels, now and from here on
+            cudaGetLastError();
+            h->front_off = true;
+            const float* lg = front->logits;
+            if (!lg) {
+                CU(launch_router_logits(fa.x, L.router_w, T, c.n_experts, c.hidden, h->logits_ws, st));
+                lg = h->logits_ws;
+            }
+            CU(launch_router(lg, L.bias, (int)T, (int)c.n_experts, (int)c.top_k, (int)c.scoring, (int)c.norm_topk, c.routed_scale,
+                             h->ids_ws, h->w_ws, st));
+        }
+    }
+    if (!ep_fused && (rc = run_routed(h, layer, x_dev, ids_dev, T, h->ro, ro_bf16, st))) { h->front_done = false; return rc; }
     if (c.shared_expert && !shared_aside) {
         StageTimer tm(h, MLXS_STAGE_SHARED, st);
         if ((rc = run_shared(st))) return rc;
@@ -769,8 +827,20 @@ extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, 
     return MLXS_OK;
 }
 
+extern "C" int mlxs_moe_experts(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_t* ids_dev,
+                                const float* weights_dev, uint32_t T, void* y_dev, void* stream) {
+    return experts_impl(h, layer, x_dev, ids_dev, weights_dev, T, y_dev, stream, nullptr);
+}
+
 extern "C" int mlxs_moe_forward(mlxs_moe* h, uint32_t layer, const void* x_dev, const float* logits_dev, uint32_t T,
                                 void* y_dev, void* stream) {
+    if (h && layer < h->cfg.n_layers && front_applies(h, T)) {
+        if (!logits_dev) return fail(MLXS_E_ARG, "forward: null buffer");
+        int rc = check_aligned(logits_dev, 4, "forward", "logits_dev");
+        if (rc) return rc;
+        const FrontCall fc{logits_dev};
+        return experts_impl(h, layer, x_dev, h->ids_ws, h->w_ws, T, y_dev, stream, &fc);
+    }
     int rc = mlxs_moe_route(h, layer, logits_dev, T, h ? h->ids_ws : nullptr, h ? h->w_ws : nullptr, stream);
     if (rc) return rc;
     return mlxs_moe_experts(h, layer, x_dev, h->ids_ws, h->w_ws, T, y_dev, stream);
@@ -841,6 +911,8 @@ extern "C" int mlxs_moe_status_clear(mlxs_moe* h) {
     CU(cudaMemset(h->status, 0, 16));
     // a call that gave up may have left arrivals of the K-split fold behind
     if (h->ks_count) CU(cudaMemset(h->ks_count, 0, (size_t)3 * h->sm_count * 4));
+    if (h->dg_count) CU(cudaMemset(h->dg_count, 0, (size_t)h->sm_count * 4));
+    CU(cudaMemset(h->front_bar, 0, 16));
     h->stats.device_status = 0;
     return MLXS_OK;
 }

@@ -15,6 +15,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "fp4_prep_body.cuh"
 
 namespace mlxs {
 
@@ -22,7 +23,6 @@ constexpr int F4_KS = 128;           // inputs per pipeline stage (4 sub-blocks 
 constexpr int F4_CHUNK = 8;          // token rows per mma n-tile
 constexpr int F4_GROUP = 2;          // chunks per work item
 constexpr int F4_W_STAGE = 8192;     // bytes of codes per projection per stage: 128 rows x 128 inputs / 2
-constexpr int F4_XA_SB_WORDS = 128;  // one chunk x one 32-block of activations: 32 lanes x 4 u32
 constexpr int F4_ZS_STRIDE = 132;
 
 __host__ __device__ inline uint32_t f4_scale_stage_bytes(bool nv) { return nv ? 1024u : 512u; }
@@ -94,21 +94,7 @@ __global__ void __launch_bounds__(256) fp4_prep_kernel(const __nv_bfloat16* __re
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;  // warp = row slot
     const bool valid = warp < t.chunk_rows[chunk];
     const uint32_t tok = valid ? x_row_of(t, t.order[t.chunk_row0[chunk] + warp], top_k) : 0u;
-    // a lane converts 8 consecutive inputs: block sb = idx / 4, word c = idx % 4
-    for (uint32_t idx = blockIdx.y * 32 + lane; idx < H / 8; idx += gridDim.y * 32) {
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if (valid) raw = *reinterpret_cast<const uint4*>(x + (size_t)tok * H + (size_t)idx * 8);
-        const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
-        __half h[8];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            h[2 * i] = __float2half_rn(__uint_as_float(wds[i] << 16));
-            h[2 * i + 1] = __float2half_rn(__uint_as_float(wds[i] & 0xFFFF0000u));
-        }
-        const uint32_t sb = idx / 4, c = idx % 4;
-        uint4 o = make_uint4(pack_h2(h[0], h[1]), pack_h2(h[2], h[3]), pack_h2(h[4], h[5]), pack_h2(h[6], h[7]));
-        *reinterpret_cast<uint4*>(xa + ((size_t)chunk * (H / 32) + sb) * F4_XA_SB_WORDS + (warp * 4 + c) * 4) = o;
-    }
+    fp4_prep_row(x, tok, valid, H, chunk, warp, blockIdx.y * 32 + lane, gridDim.y * 32, xa);
 }
 
 cudaError_t launch_fp4_prep(const __nv_bfloat16* x, uint32_t top_k, uint32_t H, DispatchTables t, uint32_t* xa,

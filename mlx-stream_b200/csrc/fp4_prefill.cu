@@ -22,8 +22,9 @@
 //     code is a bf16 subnormal); one bf16x2 multiply by 2^(b-1) gives e2m1 x 2^(b-127) exactly, and the rows stay the
 //     bf16 they arrived as, so every product is exact.  This needs 2^(b-1) to be a bf16, b <= 128 (block scale <= 2):
 //     an expert with a larger scale byte is marked at load and always takes the streaming lane;
-//   * NVFP4: operands are f16, weights e2m1 x 2^-14 times the block's E4M3 scale (exact in f16, as in the streaming
-//     lane), rows rounded bf16 -> f16, the global g/2688 x 2^14 applied in the epilogue (decode_kernels_ref.zig:13-65);
+//   * NVFP4: operands are f16, weights the exact e2m1 values (one e2m1x2 conversion per two codes) times the block's
+//     E4M3 scale (exact in f16, as in the streaming lane), rows rounded bf16 -> f16, the global g/2688 applied in the
+//     epilogue (decode_kernels_ref.zig:13-65);
 //   * one thread issues tcgen05.mma.kind::f16 (K = 16, A from tensor memory) and commits to mbarriers.  The tensor
 //     pipe queues only about two MMAs behind the running one, so this thread's time between two stages shows: a
 //     stage therefore carries 64 inputs (8 or 16 MMAs), and the thread waits on one barrier per stage (decode warp 0
@@ -51,13 +52,14 @@ constexpr int Q_CAP0 = 64, Q_CAP1 = 192;      // rows per tile of the two shapes
 constexpr int Q_W_STAGE = 8192;               // code bytes per projection per raw stage (fp4.cu F4_W_STAGE)
 
 __host__ __device__ inline uint32_t q_scale_stage_bytes(bool nv) { return nv ? 1024u : 512u; }
-// position of input k % 8 inside its 16-byte group: the order the two-codes-per-op decode produces
-__host__ __device__ inline uint32_t q_pos8(uint32_t j) { return (j & 3u) * 2u + (j >> 2); }
+// position of input k % 8 inside its 16-byte group: the order the decode produces.  MXFP4 (two codes per integer op into
+// bf16): 0,4,1,5,2,6,3,7; NVFP4 (the e2m1x2 -> f16x2 conversion instruction): natural order
+__host__ __device__ inline uint32_t q_pos8(uint32_t j, bool nv) { return nv ? j : (j & 3u) * 2u + (j >> 2); }
 // Staged rows of a tile with rows16 rows (its rows padded to 16) over `width` inputs, as K-major core matrices:
 // [k/32][(k%32)/8][row/8][row%8][pos], so a block of 32 inputs is rows16 x 64 contiguous bytes, consecutive blocks
 // follow each other, and the K-direction distance of two core matrices is rows16 x 16 bytes throughout.  Element offset of (row, k):
-__device__ __forceinline__ size_t q_b_off(uint32_t rows16, uint32_t row, uint32_t k) {
-    return (size_t)(k / Q_SB) * (rows16 * Q_SB) + ((k % Q_SB) / 8) * (rows16 * 8) + (row / 8) * 64 + (row % 8) * 8 + q_pos8(k % 8);
+__device__ __forceinline__ size_t q_b_off(uint32_t rows16, uint32_t row, uint32_t k, bool nv) {
+    return (size_t)(k / Q_SB) * (rows16 * Q_SB) + ((k % Q_SB) / 8) * (rows16 * 8) + (row / 8) * 64 + (row % 8) * 8 + q_pos8(k % 8, nv);
 }
 
 // ------------------------------------------------------------------------------------------------------------
@@ -90,10 +92,12 @@ __global__ void __launch_bounds__(256) q_prep_kernel(const __nv_bfloat16* __rest
                 e[2 * q + 1] = (uint16_t)(wds[q] >> 16);
             }
         }
-        // stored order 0,4,1,5,2,6,3,7
-        const uint4 o = make_uint4(e[0] | ((uint32_t)e[4] << 16), e[1] | ((uint32_t)e[5] << 16), e[2] | ((uint32_t)e[6] << 16),
-                                   e[3] | ((uint32_t)e[7] << 16));
-        *reinterpret_cast<uint4*>(dst + q_b_off(rows16, r, kg * 8)) = o;
+        // stored order 0,4,1,5,2,6,3,7 (MXFP4) or natural (NVFP4): q_pos8
+        const uint4 o = nv ? make_uint4(e[0] | ((uint32_t)e[1] << 16), e[2] | ((uint32_t)e[3] << 16), e[4] | ((uint32_t)e[5] << 16),
+                                        e[6] | ((uint32_t)e[7] << 16))
+                           : make_uint4(e[0] | ((uint32_t)e[4] << 16), e[1] | ((uint32_t)e[5] << 16), e[2] | ((uint32_t)e[6] << 16),
+                                        e[3] | ((uint32_t)e[7] << 16));
+        *reinterpret_cast<uint4*>(dst + q_b_off(rows16, r, kg * 8, nv != 0)) = o;
     }
 }
 
@@ -126,12 +130,17 @@ __device__ __forceinline__ void q_decode8_bf16(uint32_t w, uint32_t (&h)[4]) {
     h[2] = ((w >> 2) & 0x01C001C0u) | ((w << 4) & 0x80008000u);
     h[3] = ((w >> 6) & 0x01C001C0u) | (w & 0x80008000u);
 }
-// NVFP4: the same to f16x2 of e2m1 x 2^-14
+// NVFP4: 8 codes of a word -> 4 f16x2 of the exact e2m1 values through the conversion instruction (pairs (0,1), (2,3),
+// (4,5), (6,7))
 __device__ __forceinline__ void q_decode8_f16(uint32_t w, uint32_t (&h)[4]) {
-    h[0] = ((w << 9) & 0x0E000E00u) | ((w << 12) & 0x80008000u);
-    h[1] = ((w << 5) & 0x0E000E00u) | ((w << 8) & 0x80008000u);
-    h[2] = ((w << 1) & 0x0E000E00u) | ((w << 4) & 0x80008000u);
-    h[3] = ((w >> 3) & 0x0E000E00u) | (w & 0x80008000u);
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+        : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+        : "r"(w));
 }
 __device__ __forceinline__ uint32_t q_mul_bf16x2(uint32_t a, uint32_t b) {
     uint32_t d;
@@ -347,8 +356,8 @@ __global__ void __launch_bounds__(512 + 64, 1) fp4_prefill_kernel(const QParams 
             if (NPROJ == 2) {
                 float gs_g = 1.f, gs_u = 1.f;
                 if (NV) {
-                    gs_g = (P.gscale[expert * 3 + 0] / 2688.0f) * 16384.0f;
-                    gs_u = (P.gscale[expert * 3 + 1] / 2688.0f) * 16384.0f;
+                    gs_g = P.gscale[expert * 3 + 0] / 2688.0f;
+                    gs_u = P.gscale[expert * 3 + 1] / 2688.0f;
                 }
                 uint16_t* xd_tile = P.xd + (size_t)srow0 * P.I;
                 for (uint32_t unit = slot; unit < CB * nrb; unit += 4) {
@@ -369,12 +378,12 @@ __global__ void __launch_bounds__(512 + 64, 1) fp4_prefill_kernel(const QParams 
                         const uint32_t rr = rb + i;
                         uint16_t bits = 0;
                         if (rr < rows) bits = NV ? __half_as_ushort(__float2half_rn(hq)) : (uint16_t)(__float_as_uint(hq) >> 16);
-                        xd_tile[q_b_off(rows16, rr, col)] = bits;
+                        xd_tile[q_b_off(rows16, rr, col, NV)] = bits;
                     }
                 }
             } else {
                 float gs = 1.f;
-                if (NV) gs = (P.gscale[expert * 3 + 2] / 2688.0f) * 16384.0f;
+                if (NV) gs = P.gscale[expert * 3 + 2] / 2688.0f;
                 for (uint32_t unit = slot; unit < CB * nrb; unit += 4) {
                     const uint32_t ecb = unit / nrb, rb = (unit % nrb) * 16;
                     uint32_t v[16];

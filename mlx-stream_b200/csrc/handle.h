@@ -85,6 +85,9 @@ struct mlxs_moe {
     float* logits_io = nullptr;
     mlxs_moe_stats stats{};
     EpState* ep = nullptr;
+    uint32_t* front_bar = nullptr;    // grid barrier of the fused front kernel (two words)
+    bool front_done = false;          // the fused front kernel of this call has built the tables and staged the rows
+    bool front_off = false;           // a cooperative launch was refused once: separate kernels from then on
     uint32_t dbg_poll_limit = 0, dbg_withhold = 0;  // mlxs_moe_debug_wait (self-test of the bounded waits)
     uint32_t rows_cap = 0;  // rows the expert kernels' workspaces hold (assignments of one call, or received rows)
     // per-stage timing (off by default)

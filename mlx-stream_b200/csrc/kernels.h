@@ -36,6 +36,32 @@ cudaError_t launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* w,
 cudaError_t launch_router(const float* logits, const float* bias, int T, int E, int K, int scoring, int norm,
                           float scale, int32_t* ids, float* weights, cudaStream_t st);
 
+// The front of a decode-sized call in one cooperative launch (front.cu): [logits from x] -> route -> dispatch -> row
+// staging for the streaming lane.  bar: two zeroed words (the grid barrier).
+struct FrontArgs {
+    const __nv_bfloat16* w_router;  // [E, H] bf16: phase 0 computes the logits into logits_out; null: `logits` is given
+    float* logits_out;
+    const float* logits;
+    const float* bias;
+    int E, K, scoring, norm;
+    float scale;
+    int32_t* ids;
+    float* weights;
+    uint32_t T;
+    const uint8_t* loaded;
+    DispatchTables t;
+    uint32_t chunk_rows, group_chunks;
+    uint32_t* status;
+    const __nv_bfloat16* x;
+    uint32_t H;
+    int bank_exl3;
+    const __half* scales;           // EXL3: the layer's sign / scale vectors
+    size_t scales_stride;
+    uint32_t* xa;
+    uint32_t* bar;
+};
+cudaError_t launch_front(const FrontArgs& a, cudaStream_t st);
+
 // ids [A] (A = T*k) -> tables; expert ids outside [0, E) set *status and are treated as expert 0.
 // loaded: optional [E] bytes, 0 = expert not resident -> *status = ST_NOT_LOADED.
 // chunk_rows / group_chunks: rows per chunk and chunks per work item of the bank's kernels (EXL3 4 x 4, FP4 8 x 2).
