@@ -203,6 +203,19 @@ int mlxs_moe_exl3_gemv_noalloc(const void *code_dev, uint32_t in_dim, uint32_t o
  * the memory system delivers.  Allocates 16 bytes for the duration of the call; needs no handle. */
 int mlxs_moe_exl3_decode_rate(int32_t device, uint32_t bits, int with_mma, uint32_t tiles_per_warp, double *tiles_per_s);
 
+/* The native block-scaled FP4 tensor-core instruction, measured (no counterpart in the reference, whose FP4 prefill is a
+ * sorted quantised GEMM of its array library, src/arch/mimo_v2/math.zig:426-447): tcgen05.mma.kind::mxf8f6f4.block_scale
+ * with A = MXFP4 codes and E8M0 block scales as the bank stores them and B = bf16 rows split into an E4M3 high and low
+ * part with UE8M0 block scales.  rel_l2_*: the product over one 128 x 64 x 128 tile against the exact product of the
+ * bf16 rows (hi + lo, and hi alone); tflops_*: issue rates of the two instruction streams on shared-memory operands
+ * (M 128, N 256, rate_mmas instructions per SM; 0 skips the timing); the hi / lo pair needs two 8-bit-rate MMAs per 32
+ * inputs, so its useful rate is tflops_mxf8f6f4 / 2. */
+typedef struct {
+    double rel_l2_hi_lo, rel_l2_hi_only;
+    double tflops_f16, tflops_mxf8f6f4, tflops_hi_lo_effective;
+} mlxs_fp4_native_result;
+int mlxs_moe_fp4_native_probe(int32_t device, uint32_t rate_mmas, mlxs_fp4_native_result *out);
+
 int mlxs_moe_stats_get(mlxs_moe *h, mlxs_moe_stats *out);
 /* The device status word is sticky (a host must see a fault it did not poll for): once a kernel has recorded an error
  * every mlxs_moe_forward_host returns MLXS_E_DEVICE_STATUS until the host acknowledges it here.  Synchronises the

@@ -32,7 +32,7 @@ EXPORTS = [
     "mlxs_moe_set_placement", "mlxs_moe_set_router_weight", "mlxs_moe_logits", "mlxs_moe_forward_x",
     "mlxs_moe_set_layer_bits", "mlxs_moe_layer_record_bytes", "mlxs_moe_bank_layer_bits_text",
     "mlxs_moe_ep_window_bytes", "mlxs_moe_ep_overloaded_rank",
-    "mlxs_moe_status_clear", "mlxs_moe_sort_rows", "mlxs_moe_debug_wait", "mlxs_moe_exl3_decode_rate",
+    "mlxs_moe_status_clear", "mlxs_moe_sort_rows", "mlxs_moe_debug_wait", "mlxs_moe_exl3_decode_rate", "mlxs_moe_fp4_native_probe",
     "mlxs_moe_bank_verify", "mlxs_moe_usage_enable", "mlxs_moe_usage_add", "mlxs_moe_usage_read", "mlxs_moe_usage_reset", "mlxs_moe_plan_placement",
 ]
 
@@ -64,6 +64,11 @@ class BankInfo(C.Structure):
                 ("n_experts", C.c_uint64), ("n_layers", C.c_uint64), ("first_layer", C.c_uint64),
                 ("logical_bytes", C.c_uint64), ("record_stride", C.c_uint64), ("data_bytes", C.c_uint64),
                 ("data_file", C.c_char * 64), ("bits_min", C.c_uint32), ("bits_max", C.c_uint32)]
+
+
+class Fp4NativeResult(C.Structure):
+    _fields_ = [("rel_l2_hi_lo", C.c_double), ("rel_l2_hi_only", C.c_double), ("tflops_f16", C.c_double),
+                ("tflops_mxf8f6f4", C.c_double), ("tflops_hi_lo_effective", C.c_double)]
 
 
 class MlxsError(RuntimeError):
@@ -124,6 +129,7 @@ def lib():
         L.mlxs_moe_set_router_weight.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_int]
         L.mlxs_moe_logits.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
         L.mlxs_moe_forward_x.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
+        L.mlxs_moe_fp4_native_probe.argtypes = [C.c_int32, C.c_uint32, C.POINTER(Fp4NativeResult)]
         L.mlxs_moe_exl3_decode_rate.argtypes = [C.c_int32, C.c_uint32, C.c_int, C.c_uint32, C.POINTER(C.c_double)]
         L.mlxs_moe_ep_window_bytes.restype = C.c_uint64
         L.mlxs_moe_ep_window_bytes.argtypes = [C.c_uint32] * 5
@@ -196,6 +202,13 @@ def exl3_decode_rate(device=0, bits=3, with_mma=True, tiles_per_warp=1 << 16):
     out = C.c_double()
     _check(lib().mlxs_moe_exl3_decode_rate(device, bits, int(with_mma), tiles_per_warp, C.byref(out)))
     return out.value
+
+
+def fp4_native_probe(device=0, rate_mmas=20000):
+    """The native block-scaled FP4 MMA measured: numerics of the e2m1 x (e4m3 hi + lo) product and the issue rates."""
+    out = Fp4NativeResult()
+    _check(lib().mlxs_moe_fp4_native_probe(device, rate_mmas, C.byref(out)))
+    return {k: getattr(out, k) for k, _ in Fp4NativeResult._fields_}
 
 
 def exl3_gemv_noalloc(code, in_dim, out_dim, xh, rows, z, stream=None):

@@ -97,6 +97,9 @@ pub extern fn mlxs_moe_status_clear(h: *Moe) c_int;
 pub extern fn mlxs_moe_sort_rows(h: *Moe, slot_dev: ?*const i32, n: u32, n_slots: u32, order_dev: ?*u32, offsets_dev: *u32, stream: ?*anyopaque) c_int;
 /// measured ceiling of the in-register EXL3 decode (tiles per second, operands from registers)
 pub extern fn mlxs_moe_exl3_decode_rate(device: i32, bits: u32, with_mma: c_int, tiles_per_warp: u32, tiles_per_s: *f64) c_int;
+pub const Fp4NativeResult = extern struct { rel_l2_hi_lo: f64, rel_l2_hi_only: f64, tflops_f16: f64, tflops_mxf8f6f4: f64, tflops_hi_lo_effective: f64 };
+/// the native block-scaled FP4 MMA measured (numerics of the hi / lo split, issue rates)
+pub extern fn mlxs_moe_fp4_native_probe(device: i32, rate_mmas: u32, out: *Fp4NativeResult) c_int;
 /// self-test hook of the bounded waits
 pub extern fn mlxs_moe_debug_wait(h: *Moe, poll_limit: u32, withhold_stage: u32) c_int;
 

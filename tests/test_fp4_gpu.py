@@ -128,3 +128,15 @@ def test_mxfp4_wide_scale_stays_in_streaming_lane():
         assert rel_l2(y, case.cpu_layer(x, ids, w)) < TOL
     finally:
         case.close()
+
+
+def test_native_block_scaled_fp4_mma_measured():
+    """tcgen05.mma.kind::mxf8f6f4.block_scale on the bank's own bytes: with the bf16 rows split into an E4M3 high and low
+    part the product matches the bf16-row product to a few 1e-3 of its rms (the high part alone does not), and the pair
+    of 8-bit-rate MMAs it needs per 32 inputs delivers about the 16-bit rate."""
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    r = pkg.fp4_native_probe(0, 4000)
+    assert r["rel_l2_hi_lo"] < 4e-3, r
+    assert 5e-3 < r["rel_l2_hi_only"] < 0.1, r
+    assert r["tflops_f16"] > 100 and r["tflops_mxf8f6f4"] > 1.3 * r["tflops_f16"], r
