@@ -169,21 +169,28 @@ def workload_config(wl, E, T, layers, routing, gpus, placement):
             "parallelism": "single GPU" if gpus == 1 else f"ep{gpus}, experts placed: {placement}"}
 
 
+FRONT_MAX_TOKENS = int(os.environ.get("MLXS_FRONT_MAX", "16"))   # the library's own default and knob
+
+
 def own_launches_per_layer(wl, T, world):
     """Kernels of this library one layer call launches (NCCL's kernels are not counted)."""
     A = T * wl["k"]
-    n = 1                                   # router
-    n += 3 if A > 2048 else 1               # dispatch: count / scan / place above 2048 rows, one CTA below
-    n += 3                                  # streaming lane: prep, gate/up, down
+    if world == 1 and T <= FRONT_MAX_TOKENS:
+        n = 1 + 2                           # fused front (route, dispatch, row staging in one launch), gate/up, down
+    else:
+        n = 1                               # router
+        n += 3 if A > 2048 else 1           # dispatch: count / scan / place above 2048 rows, one CTA below
+        n += 3                              # streaming lane: prep, gate/up, down
     # the tensor-core lane's kernels launch when the local call has enough "tokens" for an expert to reach the threshold
     # (with expert parallelism every received assignment is a token of the local call)
     if (T if world == 1 else A) >= LANE_MIN_ROWS:
         n += 6                              # tile plan, row prep, gate/up and down in two tile shapes each
     if wl["shared"]:
         n += 2 if T <= 64 else 3            # skinny gate/up + down, or row staging + the two tcgen05 products
-    n += 1                                  # combine
     if world > 1:
         n += 7                              # destination ranks, rank sort, dedup, push, unpack, partial push, final sum
+    else:
+        n += 1                              # combine (expert parallel: the partial push and the final sum do its work)
     return n
 
 
