@@ -8,7 +8,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OUT = HERE / "libmlxs_moe.so"
-SOURCES = ["api.cu", "router.cu", "dispatch.cu", "exl3.cu", "shared_combine.cu", "exl3_static.cu", "exl3_probe.cu", "fp4_native_probe.cu", "fp4.cu", "ep.cu", "exl3_prefill.cu", "fp4_prefill.cu", "dense_gemm.cu", "front.cu", "manifest.cpp"]
+SOURCES = ["api.cu", "router.cu", "dispatch.cu", "exl3.cu", "shared_combine.cu", "exl3_static.cu", "exl3_probe.cu", "fp4_native_probe.cu", "fp4.cu", "ep.cu", "exl3_prefill.cu", "fp4_prefill.cu", "fp4_native.cu", "dense_gemm.cu", "front.cu", "manifest.cpp"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "-Xptxas", "-v", "--expt-relaxed-constexpr"]

@@ -173,6 +173,7 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
         // Staging for the tensor-core lane.  One decode pass of the streaming lane serves 16 rows, one of the
         // tensor-core lane up to 128 at about 1.5 times the instructions: from 17 rows on the latter is the cheaper one.
         const bool exl3 = is_exl3(c->bank_kind);
+        if (const char* nv = getenv("MLXS_MXFP4_NATIVE")) h->mxfp4_native = atoi(nv) != 0;
         const char* ev = getenv("MLXS_PREFILL_MIN_ROWS");
         const int min_rows = ev ? atoi(ev) : 17;
         const bool supported = exl3 ? exl3_prefill_supported(d) : fp4_prefill_supported(c->hidden, c->inter);
@@ -180,8 +181,12 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
             h->pf_min_rows = (uint32_t)min_rows;
             const size_t heavy_max = A / (size_t)min_rows < h->e_local ? A / (size_t)min_rows : h->e_local;
             h->pf_max_tiles = (uint32_t)(A / PREFILL_TILE_ROWS + heavy_max + 1);
-            const size_t xa_bytes = exl3 ? exl3_prefill_xa_bytes(d, A, h->pf_max_tiles) : fp4_prefill_xa_bytes(c->hidden, A, h->pf_max_tiles);
-            const size_t xd_bytes = exl3 ? exl3_prefill_xd_bytes(d, A, h->pf_max_tiles) : fp4_prefill_xa_bytes(c->inter, A, h->pf_max_tiles);
+            size_t xa_bytes = exl3 ? exl3_prefill_xa_bytes(d, A, h->pf_max_tiles) : fp4_prefill_xa_bytes(c->hidden, A, h->pf_max_tiles);
+            size_t xd_bytes = exl3 ? exl3_prefill_xd_bytes(d, A, h->pf_max_tiles) : fp4_prefill_xa_bytes(c->inter, A, h->pf_max_tiles);
+            if (c->bank_kind == MLXS_BANK_MXFP4) {   // the block-scaled lane stages 132 bytes per row per 64 inputs
+                xa_bytes = std::max(xa_bytes, mxfp4_native_xa_bytes(c->hidden, A, h->pf_max_tiles));
+                xd_bytes = std::max(xd_bytes, mxfp4_native_xa_bytes(c->inter, A, h->pf_max_tiles));
+            }
             if ((rc = h->alloc(&h->pf_tiles, prefill_tile_words(h->pf_max_tiles) * 4)) || (rc = h->alloc(&h->pf_xa, xa_bytes)) ||
                 (rc = h->alloc(&h->pf_xd, xd_bytes)))
                 return bail(rc);
@@ -676,7 +681,9 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
             pa.xa = reinterpret_cast<uint16_t*>(h->pf_xa); pa.xd = reinterpret_cast<uint16_t*>(h->pf_xd);
             pa.ro = ro; pa.ro_bf16 = ro_bf16; pa.limit = limit; pa.status = h->status; pa.sm_count = h->sm_count;
             StageTimer tm(h, MLXS_STAGE_TENSOR_LANE, tl);
-            CU(launch_fp4_prefill(pa, tl));
+            // MXFP4: the block-scaled tensor-core kind on the codes as stored when the handle was created with MLXS_MXFP4_NATIVE=1
+            if (!pa.nv && h->mxfp4_native) CU(launch_mxfp4_native(pa, tl));
+            else CU(launch_fp4_prefill(pa, tl));
         }
         if (!front_done) {
             StageTimer tm(h, MLXS_STAGE_PREP, st);

@@ -234,6 +234,12 @@ static inline size_t fp4_prefill_xa_bytes(uint32_t width, size_t rows_cap, uint3
     return (rows_cap + 16 * (size_t)(2 * max_tiles + 1)) * width * 2;
 }
 cudaError_t launch_fp4_prefill(const Fp4PrefillArgs& a, cudaStream_t st);
+// MXFP4 on the block-scaled tensor-core kind (fp4_native.cu): the same arguments; xa / xd hold the rows split into E4M3
+// high and low parts with their block scales, 132 bytes per row per 64 inputs
+static inline size_t mxfp4_native_xa_bytes(uint32_t width, size_t rows_cap, uint32_t max_tiles) {
+    return (rows_cap + 16 * (size_t)(2 * max_tiles + 1)) * (width / 64) * 132;
+}
+cudaError_t launch_mxfp4_native(const Fp4PrefillArgs& a, cudaStream_t st);
 bool fp4_prefill_supported(uint32_t H, uint32_t I);
 
 // ---- shared expert (bf16 dense) + combine ----

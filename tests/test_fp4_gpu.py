@@ -130,6 +130,35 @@ def test_mxfp4_wide_scale_stays_in_streaming_lane():
         case.close()
 
 
+@pytest.mark.parametrize("H,I,T", [(512, 256, 300), (4096, 2048, 280)])
+def test_mxfp4_block_scaled_lane_against_decoded_lane(monkeypatch, H, I, T):
+    """A handle created with MLXS_MXFP4_NATIVE=1 runs the MXFP4 tensor-core lane on tcgen05.mma.kind::mxf8f6f4.block_scale
+    (codes and E8M0 scales as stored, rows split into E4M3 high and low parts); the default lane decodes to bf16 operands.
+    Both multiply the same exact operands with f32 accumulation: the unweighted rows agree to a bf16 rounding boundary of
+    the gate/up chain, and both match the f64 oracle."""
+    outs = {}
+    for native in ("1", "0"):
+        monkeypatch.setenv("MLXS_MXFP4_NATIVE", native)
+        case = Mxfp4Case(H, I, 4, 2, seed=21, shared=False, scoring=O.SCORE_SIGMOID, max_tokens=512, routed_scale=1.0,
+                         limit=0.0, chain=True)
+        try:
+            x, ids, w = _skewed_batch(case, T, seed=5)
+            counts = np.bincount(ids.reshape(-1), minlength=4)
+            assert counts.max() > 192 and (counts >= 17).sum() >= 2       # both tile shapes, several tiles
+            ro = case.gpu_routed(x, ids)
+            assert case.status() == 0
+            assert np.isfinite(ro).all()
+            y = case.gpu_experts(x, ids, w)
+            ref = case.cpu_layer(x[:24], ids[:24], w[:24])
+            assert rel_l2(y[:24], ref) < TOL, (native, rel_l2(y[:24], ref))
+            again = case.gpu_routed(x, ids)
+            assert (again.view(np.uint32) == ro.view(np.uint32)).all()
+            outs[native] = ro
+        finally:
+            case.close()
+    assert rel_l2(outs["1"], outs["0"]) < 2e-3, rel_l2(outs["1"], outs["0"])
+
+
 def test_native_block_scaled_fp4_mma_measured():
     """tcgen05.mma.kind::mxf8f6f4.block_scale on the bank's own bytes: with the bf16 rows split into an E4M3 high and low
     part the product matches the bf16-row product to a few 1e-3 of its rms (the high part alone does not), and the pair
