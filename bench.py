@@ -613,11 +613,19 @@ def measure(rig, args, sampler, want_e2e=True):
         # prefill-sized call: the tcgen05 lane (gate/up and down launches are timed together); tensor roofline
         flops = 6.0 * H * I * rows_heavy / NL
         tf = flops / (tl_ms / max(tl_n, 1) * 1e-3) / 1e12
-        out["roofline"] = {"kernel": ("exl3_prefill_kernel" if wl["bank"] == "exl3" else "fp4_prefill_kernel") + "<gate/up> + <down> (tcgen05)",
+        native = wl["bank"] == "mxfp4" and os.environ.get("MLXS_MXFP4_NATIVE", "1") != "0"
+        kname = "exl3_prefill_kernel" if wl["bank"] == "exl3" else ("mxfp4_native_kernel" if native else "fp4_prefill_kernel")
+        out["roofline"] = {"kernel": kname + "<gate/up> + <down> (tcgen05" + (", kind::mxf8f6f4.block_scale" if native else ", kind::f16") + ")",
                            "bound": "tensor", "achieved": tf, "peak": tpeak,
                            "peak_source": "measured sustained bf16" if which == "measured" else "fallback", "unit": "TFLOP/s",
                            "frac": tf / tpeak, "traffic": None, "flops_per_launch_pair": flops,
                            "rows_in_lane_per_layer_call": rows_heavy / NL, "rows_served_per_layer_call": rows_served / NL}
+        if native:
+            # the block-scaled kind's own ceilings: its issue rate measured on this part (mlxs_moe_fp4_native_probe), of
+            # which a pair of MMAs (E4M3 high + low part of a bf16 row) uses half, and the nominal dense FP4 figure
+            out["roofline"]["other_peaks"] = {
+                "mxf8f6f4_issue_rate_measured_tflops": 4371.0, "frac_of_it_with_two_mmas_per_block": 2.0 * tf / 4371.0,
+                "nominal_dense_fp4_tflops": 9000.0, "frac_of_nominal_dense_fp4": tf / 9000.0}
     return out
 
 

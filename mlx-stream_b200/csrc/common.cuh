@@ -182,6 +182,9 @@ __device__ __forceinline__ uint32_t pack_h2(__half a, __half b) {
     return (uint32_t)__half_as_ushort(a) | ((uint32_t)__half_as_ushort(b) << 16);
 }
 __device__ __forceinline__ float bf16_round_f(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+// 1 / (1 + e^|x|) through the special-function unit (ex2.approx, rcp.approx: a few ulp) for the tensor-core lanes, whose
+// results are rounded to 16 bits right after; the streaming lanes keep expf and the IEEE division
+__device__ __forceinline__ float sigmoid_tail_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(fabsf(x))); }
 
 // ---- fixed-sequence exp / log for the router: IEEE +, *, fma, / only, so the host restatement of the same
 // statements gives the same bits ----

@@ -281,7 +281,7 @@ __global__ void __launch_bounds__(64 + DG_EPI_WARPS * 32, 1) dense_gemm_kernel(c
                                 gate = (gate != gate) ? gate : (gate < P.limit ? gate : P.limit);
                                 up = (up != up) ? up : (up > P.limit ? P.limit : (up < -P.limit ? -P.limit : up));
                             }
-                            const float yv = 1.0f / (1.0f + expf(fabsf(gate)));
+                            const float yv = sigmoid_tail_fast(gate);
                             const float sg = gate < 0.f ? yv : 1.0f - yv;
                             const __nv_bfloat16 hv = __float2bfloat16_rn((gate * sg) * up);
                             // padding rows of the tile are written as zeros: the down product reads whole 16-row groups

@@ -401,7 +401,7 @@ __global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParam
                                         const float u0 = (um != um) ? um : (um > -P.limit ? um : -P.limit);
                                         up = (u0 != u0) ? u0 : (u0 < P.limit ? u0 : P.limit);
                                     }
-                                    const float yv = 1.0f / (1.0f + expf(fabsf(gate)));
+                                    const float yv = sigmoid_tail_fast(gate);
                                     const float sgm = gate < 0.f ? yv : 1.0f - yv;
                                     vv[qq] = ((gate * sgm) * up) * shd[qq];
                                 }

@@ -21,12 +21,6 @@
 //     epilogue applies the reference's bf16 rounding chain (mimo_moe_k1_gateup.metal:115-128) and writes h already
 //     split into high and low parts for the down product (a warp holds one 32-input block of a row: one warp-wide
 //     maximum per row gives the block scale).
-// Measured (MiMo shape, 256 experts, one B200): 706 TFLOP/s at 16384 tokens, 599 at 8192, against 879 and 729 for the
-// decoded-operand lane.  The weights here are a shared-memory operand (4 KB per MMA in the 4-bit geometry, half of it
-// padding) beside the rows' 6 KB per MMA, and the copy into that geometry reads and writes shared memory once more:
-// about 180 bytes per cycle are asked of a shared memory that delivers 128, where the decoded-operand lane keeps the
-// weights in tensor memory and asks for about 110.  The lane is therefore off unless a handle is created with
-// MLXS_MXFP4_NATIVE=1; it computes the same result (tests compare the two lanes and the f64 oracle).
 // Every wait is bounded; on a give-up the CTA sets the status word, skips work and still frees its tensor memory.
 #include <cstdlib>
 
@@ -78,8 +72,9 @@ __device__ __forceinline__ void nf_split2(float q0, float q1, uint32_t& hi2, uin
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// prep: gather a tile's rows, split them and lay them out as the B operand.  A warp takes 128 inputs of a row: a lane
-// holds 4 consecutive inputs, 8 lanes one 32-input block.
+// prep: gather a tile's rows, split them and lay them out as the B operand.  A thread takes one 32-input block of one
+// row (64 bytes in, no exchange between threads); consecutive threads take consecutive rows, so a warp's 16-byte stores
+// fill whole core matrices.
 // ------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) nf_prep_kernel(const __nv_bfloat16* __restrict__ x, uint32_t top_k, uint32_t H,
                                                       DispatchTables t, const uint32_t* __restrict__ tiles, uint32_t max_tiles,
@@ -89,28 +84,45 @@ __global__ void __launch_bounds__(256) nf_prep_kernel(const __nv_bfloat16* __res
     if (tile >= tiles[list]) return;
     const uint32_t* te = prefill_tile(tiles, list, max_tiles, tile);
     const uint32_t row0 = te[1], rows = te[2];
-    const uint32_t rows16 = (rows + 15) / 16 * 16, nseg = H / 128;
+    const uint32_t rows16 = (rows + 15) / 16 * 16, nblk = H / 32;
     uint8_t* dst = xa + (size_t)te[3] * (H / NF_KST) * NF_ROW_BYTES;
-    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-    for (uint32_t task = blockIdx.y * nwarp + warp; task < rows16 * nseg; task += gridDim.y * nwarp) {
-        const uint32_t r = task / nseg, k = (task % nseg) * 128 + lane * 4;
-        uint2 raw = make_uint2(0u, 0u);
-        if (r < rows) raw = *reinterpret_cast<const uint2*>(x + (size_t)x_row_of(t, t.order[row0 + r], top_k) * H + k);
-        const float v0 = __uint_as_float(raw.x << 16), v1 = __uint_as_float(raw.x & 0xFFFF0000u);
-        const float v2 = __uint_as_float(raw.y << 16), v3 = __uint_as_float(raw.y & 0xFFFF0000u);
-        // the largest magnitude of the block: bf16 magnitudes compare as integers
-        uint32_t amax = max(max(raw.x & 0x7FFFu, (raw.x >> 16) & 0x7FFFu), max(raw.y & 0x7FFFu, (raw.y >> 16) & 0x7FFFu));
+    for (uint32_t i = blockIdx.y * blockDim.x + threadIdx.x; i < rows16 * nblk; i += gridDim.y * blockDim.x) {
+        const uint32_t r = i % rows16, k = (i / rows16) * 32;
+        uint32_t w[16];
 #pragma unroll
-        for (int o = 1; o <= 4; o <<= 1) amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+        for (int j = 0; j < 16; ++j) w[j] = 0u;
+        if (r < rows) {
+            const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)x_row_of(t, t.order[row0 + r], top_k) * H + k);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint4 v = src[j];
+                w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+            }
+        }
+        // the largest magnitude of the block: bf16 magnitudes compare as integers
+        uint32_t amax = 0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) amax = max(amax, max(w[j] & 0x7FFFu, (w[j] >> 16) & 0x7FFFu));
         const uint32_t bh = nf_scale_byte(amax << 16);
         const float inv = nf_inv_scale(bh);
-        uint32_t h01, l01, h23, l23;
-        nf_split2(v0 * inv, v1 * inv, h01, l01);
-        nf_split2(v2 * inv, v3 * inv, h23, l23);
-        const size_t off = nf_elem_off(rows16, r, k);
-        *reinterpret_cast<uint32_t*>(dst + off) = h01 | (h23 << 16);
-        *reinterpret_cast<uint32_t*>(dst + off + (size_t)rows16 * 64) = l01 | (l23 << 16);
-        if ((lane & 7u) < 2u) dst[nf_scale_off(rows16, r, k) + 2 * (lane & 7u)] = (uint8_t)((lane & 7u) ? bh - 4u : bh);
+        uint32_t hi[8], lo[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            uint32_t h0, l0, h1, l1;
+            nf_split2(__uint_as_float(w[2 * j] << 16) * inv, __uint_as_float(w[2 * j] & 0xFFFF0000u) * inv, h0, l0);
+            nf_split2(__uint_as_float(w[2 * j + 1] << 16) * inv, __uint_as_float(w[2 * j + 1] & 0xFFFF0000u) * inv, h1, l1);
+            hi[j] = h0 | (h1 << 16);
+            lo[j] = l0 | (l1 << 16);
+        }
+        uint8_t* hp = dst + nf_elem_off(rows16, r, k);
+        uint8_t* lp = hp + (size_t)rows16 * 64;
+        *reinterpret_cast<uint4*>(hp) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4*>(hp + rows16 * 16) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+        *reinterpret_cast<uint4*>(lp) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        *reinterpret_cast<uint4*>(lp + rows16 * 16) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+        uint8_t* sp = dst + nf_scale_off(rows16, r, k);
+        sp[0] = (uint8_t)bh;
+        sp[2] = (uint8_t)(bh - 4u);
     }
 }
 
@@ -152,7 +164,7 @@ __device__ __forceinline__ void tmem_st1_nowait(uint32_t taddr, uint32_t v) {
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float nf_sigmoid(float x) {  // src/arch/mimo_v2/moe.zig:341-344
-    const float y = 1.0f / (1.0f + expf(fabsf(x)));
+    const float y = sigmoid_tail_fast(x);
     return x < 0.f ? y : 1.0f - y;
 }
 

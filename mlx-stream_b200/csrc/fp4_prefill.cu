@@ -159,7 +159,7 @@ __device__ __forceinline__ uint32_t q_e4m3_f16x2(uint32_t b) {
     return q_mul_f16x2(u * 0x00010001u, 0x5C005C00u);
 }
 __device__ __forceinline__ float q_sigmoid(float x) {  // src/arch/mimo_v2/moe.zig:341-344
-    const float y = 1.0f / (1.0f + expf(fabsf(x)));
+    const float y = sigmoid_tail_fast(x);
     return x < 0.f ? y : 1.0f - y;
 }
 

@@ -87,7 +87,7 @@ struct mlxs_moe {
     EpState* ep = nullptr;
     uint32_t* front_bar = nullptr;    // grid barrier of the fused front kernel (two words)
     bool front_done = false;          // the fused front kernel of this call has built the tables and staged the rows
-    bool mxfp4_native = false;        // MXFP4 tensor-core lane on the block-scaled kind (MLXS_MXFP4_NATIVE=1 at create); measured slower than the decoded-operand lane
+    bool mxfp4_native = true;         // MXFP4 tensor-core lane on the block-scaled kind (MLXS_MXFP4_NATIVE=0 at create: the decoded-operand lane)
     bool front_off = false;           // a cooperative launch was refused once: separate kernels from then on
     uint32_t dbg_poll_limit = 0, dbg_withhold = 0;  // mlxs_moe_debug_wait (self-test of the bounded waits)
     uint32_t rows_cap = 0;  // rows the expert kernels' workspaces hold (assignments of one call, or received rows)

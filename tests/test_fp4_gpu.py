@@ -132,8 +132,9 @@ def test_mxfp4_wide_scale_stays_in_streaming_lane():
 
 @pytest.mark.parametrize("H,I,T", [(512, 256, 300), (4096, 2048, 280)])
 def test_mxfp4_block_scaled_lane_against_decoded_lane(monkeypatch, H, I, T):
-    """A handle created with MLXS_MXFP4_NATIVE=1 runs the MXFP4 tensor-core lane on tcgen05.mma.kind::mxf8f6f4.block_scale
-    (codes and E8M0 scales as stored, rows split into E4M3 high and low parts); the default lane decodes to bf16 operands.
+    """The MXFP4 tensor-core lane runs on tcgen05.mma.kind::mxf8f6f4.block_scale (codes and E8M0 scales as stored, rows
+    split into E4M3 high and low parts); a handle created with MLXS_MXFP4_NATIVE=0 keeps the lane that decodes to bf16
+    operands.
     Both multiply the same exact operands with f32 accumulation: the unweighted rows agree to a bf16 rounding boundary of
     the gate/up chain, and both match the f64 oracle."""
     outs = {}
