@@ -158,16 +158,16 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
         if ((rc = h->alloc(&h->xa_gu, (size_t)max_chunks * 2 * kmax * 256)) ||
             (rc = h->alloc(&h->xa_d, (size_t)max_chunks * kmax * 256)) || (rc = h->alloc(&h->ro, A * (H > I ? H : I) * 4)))
             return bail(rc);
-        if ((rc = h->alloc(&h->ks_scratch, exl3_ksplit_scratch_bytes(h->sm_count))) || (rc = h->alloc(&h->ks_count, (size_t)3 * h->sm_count * 4)))
+        if ((rc = h->alloc(&h->ks_scratch, exl3_ksplit_scratch_bytes(h->sm_count))) || (rc = h->alloc(&h->ks_count, ksplit_count_words(h->sm_count) * 4)))
             return bail(rc);
-        if (cudaMemset(h->ks_count, 0, (size_t)3 * h->sm_count * 4) != cudaSuccess) return bail(fail(MLXS_E_CUDA, "create: cudaMemset failed"));
+        if (cudaMemset(h->ks_count, 0, ksplit_count_words(h->sm_count) * 4) != cudaSuccess) return bail(fail(MLXS_E_CUDA, "create: cudaMemset failed"));
     } else {
         if ((rc = h->alloc(&h->xa_gu, (size_t)max_chunks * (H / 32) * 512)) ||
             (rc = h->alloc(&h->xa_d, (size_t)max_chunks * (I / 32) * 512)) || (rc = h->alloc(&h->ro, A * H * 4)))
             return bail(rc);
-        if ((rc = h->alloc(&h->ks_scratch, exl3_ksplit_scratch_bytes(h->sm_count))) || (rc = h->alloc(&h->ks_count, (size_t)3 * h->sm_count * 4)))
+        if ((rc = h->alloc(&h->ks_scratch, exl3_ksplit_scratch_bytes(h->sm_count))) || (rc = h->alloc(&h->ks_count, ksplit_count_words(h->sm_count) * 4)))
             return bail(rc);
-        if (cudaMemset(h->ks_count, 0, (size_t)3 * h->sm_count * 4) != cudaSuccess) return bail(fail(MLXS_E_CUDA, "create: cudaMemset failed"));
+        if (cudaMemset(h->ks_count, 0, ksplit_count_words(h->sm_count) * 4) != cudaSuccess) return bail(fail(MLXS_E_CUDA, "create: cudaMemset failed"));
     }
     {
         // Staging for the tensor-core lane.  One decode pass of the streaming lane serves 16 rows, one of the
@@ -917,7 +917,7 @@ extern "C" int mlxs_moe_status_clear(mlxs_moe* h) {
     CU(cudaDeviceSynchronize());
     CU(cudaMemset(h->status, 0, 16));
     // a call that gave up may have left arrivals of the K-split fold behind
-    if (h->ks_count) CU(cudaMemset(h->ks_count, 0, (size_t)3 * h->sm_count * 4));
+    if (h->ks_count) CU(cudaMemset(h->ks_count, 0, ksplit_count_words(h->sm_count) * 4));
     if (h->dg_count) CU(cudaMemset(h->dg_count, 0, (size_t)h->sm_count * 4));
     CU(cudaMemset(h->front_bar, 0, 16));
     h->stats.device_status = 0;

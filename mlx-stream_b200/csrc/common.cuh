@@ -186,6 +186,17 @@ __device__ __forceinline__ float bf16_round_f(float x) { return __bfloat162float
 // results are rounded to 16 bits right after; the streaming lanes keep expf and the IEEE division
 __device__ __forceinline__ float sigmoid_tail_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(fabsf(x))); }
 
+// Over how many CTAs (1, 2 or 4, at most lp) the parts of an item's sum are spread in one call of a streaming kernel:
+// as many as still give every unit a CTA of its own.  (Splitting further to even out the SMs' shares was measured: the
+// extra folds cost more than the balance gains, 0.165 against 0.156 ms at one token.)  cap_items: the items the fold's
+// workspace holds.
+__device__ __forceinline__ uint32_t ksplit_ctas(uint32_t n_items, uint32_t lp, uint32_t grid, uint32_t cap_items) {
+    if (!n_items || n_items > cap_items) return 1u;
+    uint32_t np = 1;
+    while (np < lp && n_items * (np * 2) <= grid) np *= 2;
+    return np;
+}
+
 // ---- fixed-sequence exp / log for the router: IEEE +, *, fma, / only, so the host restatement of the same
 // statements gives the same bits ----
 __device__ __forceinline__ float det_expf(float x) {

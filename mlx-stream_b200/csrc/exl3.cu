@@ -131,8 +131,9 @@ struct GemvParams {
     // The sum over the inputs is always taken in `parts` equal parts, folded left in part order: a fixed function of the
     // shape, so a row's bits do not depend on the batch around it.  Calls with fewer work items than CTAs spread an
     // item's parts over 2 or 4 CTAs: each leaves its parts here and the last to arrive folds them and runs the epilogue.
-    float* ks_scratch;           // [2 x CTAs][zs words] or null (one CTA per item always)
-    uint32_t* ks_count;          // [CTAs] arrivals per item, zero between launches
+    float* ks_scratch;           // [items][parts][zs words] or null (one CTA per item always)
+    uint32_t* ks_count;          // [ks_cap_items] arrivals per item, zero between launches
+    uint32_t n_sm, ks_cap_items; // SMs of the device; items the workspace and the counters hold
     // Every wait gives up after poll_limit polls.  Self-test only (mlxs_moe_debug_wait): withhold = n makes every
     // producer leave out the copies of its n-th ring stage, so the consumers' wait for that stage runs out, the CTA
     // records ST_WAIT_FULL and returns with nothing in flight.
@@ -201,9 +202,7 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
     uint32_t LP = P.nkt % (4 * KT) == 0 ? 4u : (P.nkt % (2 * KT) == 0 ? 2u : 1u);
     LP = LP < P.max_parts ? LP : P.max_parts;
     const uint32_t part_kt = P.nkt / LP;
-    uint32_t NP = 1;
-    if (P.ks_scratch && n_items)
-        while (NP < LP && n_items * (NP * 2) <= gridDim.x) NP *= 2;
+    const uint32_t NP = P.ks_scratch ? ksplit_ctas(n_items, LP, gridDim.x, P.ks_cap_items) : 1u;
     const uint32_t share_kt = P.nkt / NP;
 
     if (warp == NCW) {
@@ -327,6 +326,9 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
         // One CTA per item: the parts are folded left in the staging array.  Several CTAs: every part goes to its slot.
         const uint32_t g = lane >> 2, c = lane & 3u;
         const bool fold = NP == 1 && m.part != 0;
+        constexpr uint32_t ZS_VEC = NPROJ * GROUP_CHUNKS * CHUNK_ROWS * ZS_STRIDE / 4;
+        // several CTAs per item: a part goes from the registers straight to its slot of the workspace
+        float* zdst = NP > 1 ? P.ks_scratch + ((size_t)m.item * LP + m.part) * (ZS_VEC * 4) : zs;
 #pragma unroll
         for (int mt = 0; mt < GROUP_CHUNKS; ++mt) {
             if (mt < (int)m.mc) {
@@ -334,26 +336,20 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
 #pragma unroll
                 for (int q = 0; q < 4; ++q) v[q] = acc[mt][q] + __shfl_xor_sync(0xFFFFFFFFu, acc[mt][q], 2);
                 if (c < 2) {
-                    float* zr = zs + ((p * GROUP_CHUNKS + mt) * CHUNK_ROWS + 2 * c) * ZS_STRIDE + j * 16 + g;
+                    float* zr = zdst + ((p * GROUP_CHUNKS + mt) * CHUNK_ROWS + 2 * c) * ZS_STRIDE + j * 16 + g;
                     if (fold) { zr[0] += v[0]; zr[ZS_STRIDE] += v[1]; zr[8] += v[2]; zr[ZS_STRIDE + 8] += v[3]; }
                     else { zr[0] = v[0]; zr[ZS_STRIDE] = v[1]; zr[8] = v[2]; zr[ZS_STRIDE + 8] = v[3]; }
                 }
             }
         }
-        constexpr uint32_t ZS_VEC = NPROJ * GROUP_CHUNKS * CHUNK_ROWS * ZS_STRIDE / 4;
-        if (NP > 1) {
-            if (!epi_sync()) break;
-            float4* slot = reinterpret_cast<float4*>(P.ks_scratch) + ((size_t)m.item * LP + m.part) * ZS_VEC;
-            for (uint32_t i = threadIdx.x; i < ZS_VEC; i += NCW * 32) slot[i] = reinterpret_cast<const float4*>(zs)[i];
-            __threadfence();
-            if (!epi_sync()) break;
-        }
         if (!(flags & 4u)) continue;
         if (NP == 1) {
             if (!epi_sync()) break;
         } else {
-            // the last CTA of the item to arrive folds the parts in part order (whoever it is) and goes on to the
-            // epilogue; the others take the next unit
+            // every thread's parts are out before thread 0 counts this CTA in; the last CTA of the item to arrive folds
+            // the parts in part order (whoever it is) and goes on to the epilogue; the others take the next unit
+            __threadfence();
+            if (!epi_sync()) break;
             if (threadIdx.x == 0) {
                 const uint32_t seen = atomicAdd(&P.ks_count[m.item], 1u);
                 s_last_part = seen == NP - 1 ? 1 : 0;
@@ -362,8 +358,11 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) exl3_gem
             if (!epi_sync()) break;
             if (!s_last_part) continue;
             __threadfence();
+            // only the chunks that hold rows: [projection][chunk < mc][row][stride]
             const float4* base = reinterpret_cast<const float4*>(P.ks_scratch) + (size_t)m.item * LP * ZS_VEC;
-            for (uint32_t i = threadIdx.x; i < ZS_VEC; i += NCW * 32) {
+            const uint32_t per_p = m.mc * (CHUNK_ROWS * ZS_STRIDE / 4);
+            for (uint32_t i0 = threadIdx.x; i0 < NPROJ * per_p; i0 += NCW * 32) {
+                const uint32_t i = (i0 / per_p) * (GROUP_CHUNKS * CHUNK_ROWS * ZS_STRIDE / 4) + i0 % per_p;
                 float4 a = __ldcg(base + i);
                 for (uint32_t q = 1; q < LP; ++q) {
                     const float4 b = __ldcg(base + (size_t)q * ZS_VEC + i);
@@ -500,7 +499,8 @@ cudaError_t launch_exl3_gate_up(const Exl3GemvArgs& a, cudaStream_t st) {
     P.xa = a.xa_gu; P.t = a.t; P.counter_idx = HDR_CTR_GU;
     P.scales = a.L.scales; P.scales_stride = exl3_scales_per_expert(a.d);
     P.H = a.d.H; P.I = a.d.I; P.xa_d = a.xa_d; P.out = nullptr; P.out_dim = a.d.I; P.limit = a.limit; P.status = a.status;
-    P.ks_scratch = a.ks_scratch; P.ks_count = a.ks_count;
+    P.ks_scratch = a.ks_scratch; P.ks_count = a.ks_count; P.n_sm = (uint32_t)a.sm_count;
+    P.ks_cap_items = ksplit_cap_items(a.sm_count, (size_t)2 * GROUP_CHUNKS * CHUNK_ROWS * ZS_STRIDE * sizeof(float));
     P.poll_limit = a.poll_limit ? a.poll_limit : (1u << 20); P.withhold = a.withhold;
     return launch_gemv(2, EPI_GATE_UP, (int)a.d.K, P, a.sm_count, st);
 }
@@ -512,7 +512,8 @@ cudaError_t launch_exl3_down(const Exl3GemvArgs& a, cudaStream_t st) {
     P.xa = a.xa_d; P.t = a.t; P.counter_idx = HDR_CTR_DOWN;
     P.scales = a.L.scales; P.scales_stride = exl3_scales_per_expert(a.d);
     P.H = a.d.H; P.I = a.d.I; P.xa_d = nullptr; P.out = a.ro; P.out_dim = a.d.H; P.limit = a.limit; P.status = a.status;
-    P.ks_scratch = a.ks_scratch; P.ks_count = a.ks_count;
+    P.ks_scratch = a.ks_scratch; P.ks_count = a.ks_count; P.n_sm = (uint32_t)a.sm_count;
+    P.ks_cap_items = ksplit_cap_items(a.sm_count, (size_t)GROUP_CHUNKS * CHUNK_ROWS * ZS_STRIDE * sizeof(float));
     P.poll_limit = a.poll_limit ? a.poll_limit : (1u << 20); P.withhold = 0;
     return launch_gemv(1, EPI_DOWN, (int)a.d.K, P, a.sm_count, st);
 }

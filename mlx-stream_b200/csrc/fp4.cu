@@ -126,8 +126,9 @@ struct Fp4Params {
     // The sum over the inputs is taken in `parts` equal parts folded left in part order (a function of the shape only, so
     // a row's bits do not depend on the batch); calls with fewer items than CTAs spread an item's parts over 2 or 4
     // CTAs, as the EXL3 streaming kernel does
-    float* ks_scratch;           // [2 x CTAs][zs words] or null
-    uint32_t* ks_count;          // [CTAs], zero between launches
+    float* ks_scratch;           // [items][parts][zs words] or null
+    uint32_t* ks_count;          // [ks_cap_items or more], zero between launches
+    uint32_t n_sm, ks_cap_items; // SMs of the device; items the workspace and the counters hold
 };
 
 // flags: 1 = first stage of a part of the sum, 2 = last stage of a part, 4 = last stage of this CTA's share of the item
@@ -253,9 +254,8 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
     uint32_t LP = P.n_stages_k % 4 == 0 ? 4u : (P.n_stages_k % 2 == 0 ? 2u : 1u);   // parts of the sum (shape only)
     LP = LP < P.max_parts ? LP : P.max_parts;
     const uint32_t part_stages = P.n_stages_k / LP;
-    uint32_t NP = 1;   // CTAs an item's parts are spread over (this call's item count)
-    if (P.ks_scratch && n_items)
-        while (NP < LP && n_items * (NP * 2) <= gridDim.x) NP *= 2;
+    // CTAs an item's parts are spread over (this call's item count)
+    const uint32_t NP = P.ks_scratch ? ksplit_ctas(n_items, LP, gridDim.x, P.ks_cap_items) : 1u;
     const uint32_t share_stages = P.n_stages_k / NP;
 
     if (warp == NCW) {
@@ -354,10 +354,13 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
         float gs = 1.f;
         if (NV) gs = P.gscale[m.expert * 3 + (NPROJ == 2 ? p : 2)] / 2688.0f;
         const bool fold = NP == 1 && m.part != 0;
+        constexpr uint32_t ZS_VEC = NPROJ * F4_GROUP * F4_CHUNK * F4_ZS_STRIDE / 4;
+        // several CTAs per item: a part goes from the registers straight to its slot of the workspace
+        float* zdst = NP > 1 ? P.ks_scratch + ((size_t)m.item * LP + m.part) * (ZS_VEC * 4) : zs;
 #pragma unroll
         for (int mt = 0; mt < F4_GROUP; ++mt) {
             if (mt < (int)m.mc) {
-                float* zr = zs + ((p * F4_GROUP + mt) * F4_CHUNK + 2 * c) * F4_ZS_STRIDE + j * 16 + g;
+                float* zr = zdst + ((p * F4_GROUP + mt) * F4_CHUNK + 2 * c) * F4_ZS_STRIDE + j * 16 + g;
                 if (fold) {
                     zr[0] += acc[mt][0] * gs; zr[F4_ZS_STRIDE] += acc[mt][1] * gs;
                     zr[8] += acc[mt][2] * gs; zr[F4_ZS_STRIDE + 8] += acc[mt][3] * gs;
@@ -367,18 +370,13 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
                 }
             }
         }
-        constexpr uint32_t ZS_VEC = NPROJ * F4_GROUP * F4_CHUNK * F4_ZS_STRIDE / 4;
-        if (NP > 1) {
-            if (!epi_sync()) break;
-            float4* slot = reinterpret_cast<float4*>(P.ks_scratch) + ((size_t)m.item * LP + m.part) * ZS_VEC;
-            for (uint32_t i = threadIdx.x; i < ZS_VEC; i += NCW * 32) slot[i] = reinterpret_cast<const float4*>(zs)[i];
-            __threadfence();
-            if (!epi_sync()) break;
-        }
         if (!(flags & 4u)) continue;
         if (NP == 1) {
             if (!epi_sync()) break;
         } else {
+            // every thread's parts are out before thread 0 counts this CTA in
+            __threadfence();
+            if (!epi_sync()) break;
             if (threadIdx.x == 0) {
                 const uint32_t seen = atomicAdd(&P.ks_count[m.item], 1u);
                 s_last_part = seen == NP - 1 ? 1 : 0;
@@ -387,8 +385,11 @@ __global__ void __launch_bounds__(NPROJ * 256 + 32, NPROJ == 1 ? 3 : 2) fp4_gemv
             if (!epi_sync()) break;
             if (!s_last_part) continue;
             __threadfence();
+            // only the chunks that hold rows: [projection][chunk < mc][row][stride]
             const float4* base = reinterpret_cast<const float4*>(P.ks_scratch) + (size_t)m.item * LP * ZS_VEC;
-            for (uint32_t i = threadIdx.x; i < ZS_VEC; i += NCW * 32) {
+            const uint32_t per_p = m.mc * (F4_CHUNK * F4_ZS_STRIDE / 4);
+            for (uint32_t i0 = threadIdx.x; i0 < NPROJ * per_p; i0 += NCW * 32) {
+                const uint32_t i = (i0 / per_p) * (F4_GROUP * F4_CHUNK * F4_ZS_STRIDE / 4) + i0 % per_p;
                 float4 a = __ldcg(base + i);
                 for (uint32_t q = 1; q < LP; ++q) {
                     const float4 b = __ldcg(base + (size_t)q * ZS_VEC + i);
@@ -474,6 +475,7 @@ cudaError_t launch_fp4_gemv(const Fp4GemvArgs& a, int down, cudaStream_t st) {
     static const int gu_ctas = f4_tune_env("MLXS_F4_GU_CTAS", 2, 1, 2), dn_ctas = f4_tune_env("MLXS_F4_DN_CTAS", 3, 1, 3);
     const int per_sm = down ? dn_ctas : gu_ctas;
     const uint32_t zs_bytes = (uint32_t)(nproj * F4_GROUP * F4_CHUNK * F4_ZS_STRIDE * sizeof(float));
+    P.n_sm = (uint32_t)a.sm_count; P.ks_cap_items = ksplit_cap_items(a.sm_count, zs_bytes);
     const uint32_t budget = (uint32_t)(225 * 1024 / per_sm) - 2048u;
     // One barrier round trip of the ring serves `sub` 128-input sub-stages: the largest of 4, 2, 1 that divides a part
     // of the sum and still leaves a ring of two slots.

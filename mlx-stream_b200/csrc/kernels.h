@@ -113,11 +113,18 @@ struct Exl3GemvArgs {
     uint32_t* status;
     int sm_count;
     float* ks_scratch;      // optional K-split workspace: exl3_ksplit_scratch_bytes(sm_count) bytes
-    uint32_t* ks_count;     // [3 * sm_count] zeroed once
+    uint32_t* ks_count;     // [ksplit_count_words(sm_count)] zeroed once
     uint32_t poll_limit;    // polls after which a wait gives up (0: the default, 2^20)
     uint32_t withhold;      // self-test: the gate/up producers leave out their n-th ring stage (0: off)
 };
-static inline size_t exl3_ksplit_scratch_bytes(int sm_count) { return (size_t)2 * 3 * sm_count * 2 * 16 * 132 * 4; }
+// The fold's workspace: 12 slots per SM of the largest staging array (2 projections x 16 rows x 132 floats), and as many
+// arrival counters.  A kernel whose staging array is zs_bytes and whose sums have up to 4 parts can split this many items:
+static inline size_t exl3_ksplit_scratch_bytes(int sm_count) { return (size_t)12 * sm_count * 2 * 16 * 132 * 4; }
+static inline size_t ksplit_count_words(int sm_count) { return (size_t)12 * sm_count; }
+static inline uint32_t ksplit_cap_items(int sm_count, size_t zs_bytes) {
+    const size_t by_slots = exl3_ksplit_scratch_bytes(sm_count) / zs_bytes / 4, by_count = ksplit_count_words(sm_count);
+    return (uint32_t)(by_slots < by_count ? by_slots : by_count);
+}
 cudaError_t launch_exl3_gate_up(const Exl3GemvArgs& a, cudaStream_t st);
 cudaError_t launch_exl3_down(const Exl3GemvArgs& a, cudaStream_t st);
 // raw projection: z [rows, out] = xa . W_hat(code); `code` in the single-projection block layout with a k-tile
@@ -202,7 +209,7 @@ struct Fp4GemvArgs {
     uint32_t* status;
     int sm_count;
     float* ks_scratch;      // optional K-split workspace, exl3_ksplit_scratch_bytes(sm_count) bytes
-    uint32_t* ks_count;     // [3 * sm_count] zeroed once
+    uint32_t* ks_count;     // [ksplit_count_words(sm_count)] zeroed once
 };
 cudaError_t launch_fp4_gemv(const Fp4GemvArgs& a, int down, cudaStream_t st);
 // experts with many rows: tcgen05 MMA over codes decoded to 16-bit operands in shared memory (fp4_prefill.cu)
