@@ -560,11 +560,11 @@ def measure(rig, args, sampler, want_e2e=True):
         code_bytes = (H // 16) * (I // 16) * 96
         gu_bytes = 2 * code_bytes + 2 * (2 * I + 2 * H)  # one expert's gate + up code and sign/scale vectors
         kname = "exl3_gemv_kernel<2,gate_up>"
-        traffic_ratio = 1.014  # dram read+write / algorithmic bytes of the ncu capture on the small case (profiles/)
+        traffic_ratio = 1.016  # dram read+write / algorithmic bytes of the ncu capture on the small case (profiles/)
     else:
         gu_bytes = 2 * (H * I // 2 + H * I // (16 if wl["bank"] == "nvfp4" else 32))  # gate + up codes and block scales
         kname = "fp4_gemv_kernel<2>"
-        traffic_ratio = 1.003
+        traffic_ratio = 1.015
     hbm_peak, tpeak, which = peaks()
     gu_ms, gu_n = prof["gate_up"]
     per_launch_s = gu_ms / max(gu_n, 1) * 1e-3
