@@ -535,6 +535,17 @@ def measure(rig, args, sampler, want_e2e=True):
         for i in range(args.warmup):
             graphs[i % N_BATCHES].replay()
         graph_ms, _ = rig.timed(lambda i: graphs[i % N_BATCHES].replay(), args.steps)
+    from_x_ms = None
+    if world == 1 and NL == 1 and not args.no_from_x:
+        # the layer from x: the router's logits product x . W_g^T inside the call (mlxs_moe_forward_x); W_g ~ N(0, 1/H)
+        # so that the logits of N(0,1) rows are N(0,1) like the given ones
+        gen = torch.Generator(device=env["dev"]).manual_seed(4321)
+        wg = (torch.randn(E, H, generator=gen, device=env["dev"], dtype=torch.float32) * (H ** -0.5)).to(torch.bfloat16).contiguous()
+        moe.set_router_weight(0, wg.data_ptr(), on_device=True)
+        fx = lambda i: moe.forward_x(0, rig.xs[i % N_BATCHES].data_ptr(), T, rig.y.data_ptr(), rig.sp)
+        for i in range(args.warmup):
+            fx(i)
+        from_x_ms, _ = rig.timed(fx, args.steps)
     ms_host = None
     if want_e2e:
         for i in range(args.warmup):
@@ -597,6 +608,8 @@ def measure(rig, args, sampler, want_e2e=True):
         "stage_ms_per_step": {k: v[0] / max(args.steps, 1) for k, v in prof.items()
                               if v[1] and not (k == "tensor_lane" and rows_heavy == 0)},
         "gpu_launches": NL * own_launches_per_layer(wl, T, world) * args.steps,
+        "from_x": None if from_x_ms is None else {"ms_per_step": from_x_ms / args.steps, "value": T * args.steps / (from_x_ms * 1e-3),
+                                                   "unit": UNIT, "note": "the same layer call with the router's logits product inside it (mlxs_moe_forward_x)"},
         "graph_replay": None if graph_ms is None else {"ms_per_step": graph_ms / args.steps,
                                                         "value": T * args.steps / (graph_ms * 1e-3), "unit": UNIT},
         "exchange": None if world == 1 else {
@@ -641,6 +654,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--no-stack", action="store_true", help="N = 1: skip the 24-layer stack measured beside the layer")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of a few tokens")
+    ap.add_argument("--no-from-x", action="store_true", help="N = 1, one layer: skip the measurement of the layer from x (router logits inside)")
     ap.add_argument("--experts", type=int, default=0, help="routed experts (smaller only for profiler captures)")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--ceiling", action="store_true", help="also measure the EXL3 decode's own ceiling (operands from registers)")
