@@ -2,8 +2,8 @@
 // staging.  Four dependent kernels of a few microseconds each cost a decode step more in launch gaps than in work
 // (at one token: 37 us of a 175 us call); here they are phases of one cooperative kernel separated by grid barriers,
 // and the [T, E] logits, the ids and the tables never leave the L2 between them.
-//   phase 0 (only when the layer starts from x): logits = f32(x) . f32(W_g)^T, a warp per expert, 8 token rows staged
-//            in shared memory at a time (src/arch/deepseek_v41/graph.zig:2033; mimo_glue_router_rows.metal);
+//   phase 0 (only when the layer starts from x): logits = f32(x) . f32(W_g)^T, four warps per expert row, 8 token rows
+//            staged in shared memory at a time (src/arch/deepseek_v41/graph.zig:2033; mimo_glue_router_rows.metal);
 //   phase 1: CTA t routes token t (the router kernel's code: scoring, bias, top-k, weights);
 //   phase 2: CTA 0 sorts the assignment rows by expert and builds the work tables (the dispatch kernel's code);
 //   phase 3: all warps stage the rows for the streaming lane (the prep kernels' code).
@@ -15,11 +15,10 @@
 #include "dispatch_body.cuh"
 #include "exl3_prep_body.cuh"
 #include "fp4_prep_body.cuh"
+#include "logits_body.cuh"
 #include "router_body.cuh"
 
 namespace mlxs {
-
-constexpr int FRONT_TOK = 8;   // token rows staged per pass of phase 0
 
 struct FrontParams {
     // phase 0 (w_router == null: the caller supplies logits)
@@ -94,47 +93,9 @@ __global__ void __launch_bounds__(1024, 1) front_kernel(const FrontParams P) {
     uint32_t gen = s_gen;
     const uint32_t T = P.T;
 
-    // ---- phase 0: logits from x ----
+    // ---- phase 0: logits from x (the logits kernel's code: four warps per expert row) ----
     if (P.w_router) {
-        uint4* xs = reinterpret_cast<uint4*>(fsm);            // [FRONT_TOK][H / 8] vectors of 8 bf16
-        const uint32_t nv = P.H / 8;
-        for (uint32_t t0 = 0; t0 < T; t0 += FRONT_TOK) {
-            const uint32_t nt = T - t0 < (uint32_t)FRONT_TOK ? T - t0 : (uint32_t)FRONT_TOK;
-            __syncthreads();
-            for (uint32_t v = threadIdx.x; v < nt * nv; v += blockDim.x) xs[v] = reinterpret_cast<const uint4*>(P.x + (size_t)t0 * P.H)[v];
-            __syncthreads();
-            for (uint32_t e = blockIdx.x * nwarp + warp; e < (uint32_t)P.E; e += gridDim.x * nwarp) {
-                const uint4* wrow = reinterpret_cast<const uint4*>(P.w_router + (size_t)e * P.H);
-                float acc[FRONT_TOK];
-#pragma unroll
-                for (int tt = 0; tt < FRONT_TOK; ++tt) acc[tt] = 0.f;
-                // the same sum order as the stand-alone logits kernel: a lane adds its strided products in k order,
-                // then an xor butterfly
-                for (uint32_t v = lane; v < nv; v += 32) {
-                    const uint4 wv = wrow[v];
-                    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-                    for (int tt = 0; tt < FRONT_TOK; ++tt) {
-                        if ((uint32_t)tt < nt) {
-                            const uint4 xv = xs[tt * nv + v];
-                            const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                acc[tt] = __fmaf_rn(__uint_as_float(xw[q] << 16), __uint_as_float(ww[q] << 16), acc[tt]);
-                                acc[tt] = __fmaf_rn(__uint_as_float(xw[q] & 0xFFFF0000u), __uint_as_float(ww[q] & 0xFFFF0000u), acc[tt]);
-                            }
-                        }
-                    }
-                }
-#pragma unroll
-                for (int tt = 0; tt < FRONT_TOK; ++tt) {
-                    float a = acc[tt];
-#pragma unroll
-                    for (int o = 16; o >= 1; o >>= 1) a = __fadd_rn(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
-                    if (lane == 0 && (uint32_t)tt < nt) P.logits_out[(size_t)(t0 + tt) * P.E + e] = a;
-                }
-            }
-        }
+        logits_rows(P.x, P.w_router, T, (uint32_t)P.E, P.H, P.logits_out, fsm, blockIdx.x, gridDim.x);
         front_grid_sync(P.bar, gen, P.poll_limit, P.status);
     }
 
@@ -178,7 +139,7 @@ static size_t front_smem_bytes(const FrontArgs& a, int rthreads) {
     size_t s = router_smem_floats(a.E, a.K, rthreads) * sizeof(float);
     const size_t d = ((size_t)a.E + 99) * sizeof(uint32_t);
     if (d > s) s = d;
-    if (a.w_router) { const size_t l = (size_t)FRONT_TOK * a.H * 2; if (l > s) s = l; }
+    if (a.w_router) { const size_t l = logits_smem_bytes(a.H, 32); if (l > s) s = l; }
     return s;
 }
 
