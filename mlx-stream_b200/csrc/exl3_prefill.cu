@@ -177,14 +177,16 @@ __device__ __forceinline__ void tmem_st_16x256(uint32_t taddr, const uint32_t (&
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// NPROJ projections x CB adjacent 128-column blocks = NG accumulator groups of NT tensor-memory columns each
-template <int NPROJ, int CB, int NT, int KB>
-__global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParams P) {
+// NPROJ projections x CB adjacent 128-column blocks = NG accumulator groups of NT tensor-memory columns each; PER_SM
+// CTAs share an SM (and its 512 tensor-memory columns)
+template <int NPROJ, int CB, int NT, int KB, int PER_SM>
+__global__ void __launch_bounds__(512 + 64, PER_SM) exl3_prefill_kernel(const PfParams P) {
     constexpr int NG = NPROJ * CB;
     constexpr int A_STAGES = 2;                        // one per decode team
-    static_assert((NG == 2 || NG == 4) && NG * NT + A_STAGES * NG * PF_A_COLS <= 512, "shape");
+    constexpr int TCOLS = 512 / PER_SM;                // tensor-memory columns of this CTA
+    static_assert((NG == 2 || NG == 4) && NG * NT + A_STAGES * NG * PF_A_COLS <= TCOLS, "shape");
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    constexpr int LIST = NG == 4 ? 0 : 1;
+    constexpr int LIST = NT == PF_CAP0 ? 0 : 1;      // which tile list this shape serves
     constexpr int NCW = 16;                            // decode warps
     constexpr int TEAM = NCW / 2;                      // warps of a team
     constexpr int TW = 8 * KB;                         // words per 16x16 tile (KB bits per weight)
@@ -221,7 +223,7 @@ __global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParam
         s_abort = 0;
         mbar_fence_init();
     }
-    if (warp == 0) tmem_alloc(&s_tmem, 512);
+    if (warp == 0) tmem_alloc(&s_tmem, TCOLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -435,7 +437,7 @@ __global__ void __launch_bounds__(512 + 64, 1) exl3_prefill_kernel(const PfParam
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp == 0) tmem_free(tmem, 512);
+    if (warp == 0) tmem_free(tmem, TCOLS);
 }
 
 bool exl3_prefill_supported(Exl3Dims d) { return (d.I / 128) % 2 == 0 && (d.H / 128) % 4 == 0 && d.H % PF_KST == 0 && d.I % PF_KST == 0; }
@@ -447,19 +449,19 @@ cudaError_t launch_prefill_plan(DispatchTables t, uint32_t n_experts, const uint
     return cudaGetLastError();
 }
 
-template <int NPROJ, int CB, int NT, int KB>
+template <int NPROJ, int CB, int NT, int KB, int PER_SM>
 static cudaError_t pf_launch(PfParams P, int sm_count, cudaStream_t st) {
     // ring depths: the code ring first (HBM latency), the rest of the budget to the rows
     const size_t raw_bytes = (size_t)CB * PF_KT * NPROJ * 8 * 8 * KB * 4, b_slot = (size_t)NPROJ * NT * PF_KST * 2;
     const size_t zs_bytes = (size_t)NPROJ * PF_EPI_ROWS * PF_ZS_STRIDE * sizeof(float);
-    const size_t budget = 222 * 1024 - zs_bytes;
+    const size_t budget = (PER_SM == 1 ? 222 * 1024 : 110 * 1024) - zs_bytes;
     if (PF_RAW_STAGES * raw_bytes + 2 * b_slot > budget) return cudaErrorInvalidValue;
     size_t nb = (budget - PF_RAW_STAGES * raw_bytes) / b_slot;
     P.b_stages = (uint32_t)(nb > (size_t)PF_B_MAX ? (size_t)PF_B_MAX : nb);
     const size_t smem = P.b_stages * b_slot + PF_RAW_STAGES * raw_bytes + zs_bytes;
-    cudaError_t e = cudaFuncSetAttribute(exl3_prefill_kernel<NPROJ, CB, NT, KB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(exl3_prefill_kernel<NPROJ, CB, NT, KB, PER_SM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    exl3_prefill_kernel<NPROJ, CB, NT, KB><<<sm_count, 512 + 64, smem, st>>>(P);
+    exl3_prefill_kernel<NPROJ, CB, NT, KB, PER_SM><<<PER_SM * sm_count, 512 + 64, smem, st>>>(P);
     return cudaGetLastError();
 }
 
@@ -471,14 +473,14 @@ static cudaError_t pf_launch_all(const Exl3PrefillArgs& a, cudaStream_t st) {
     // gate / up: both projections of two adjacent column blocks (tiles up to 64 rows) or of one (up to 192 rows)
     P.code = a.L.gu_code; P.expert_stride_words = 2 * exl3_code_words(a.d); P.n_blocks = a.d.I / 128; P.nkt = a.d.H / 16;
     P.xa = a.xa; P.xa_proj_stride = exl3_prefill_staging_rows(a.rows_cap, a.max_tiles) * a.d.H; P.xd = a.xd; P.ro = nullptr;
-    cudaError_t e = pf_launch<2, 2, PF_CAP0, KB>(P, a.sm_count, st);
+    cudaError_t e = pf_launch<2, 1, PF_CAP0, KB, 2>(P, a.sm_count, st);
     if (e != cudaSuccess) return e;
-    if ((e = pf_launch<2, 1, PF_CAP1, KB>(P, a.sm_count, st)) != cudaSuccess) return e;
+    if ((e = pf_launch<2, 1, PF_CAP1, KB, 1>(P, a.sm_count, st)) != cudaSuccess) return e;
     // down: four adjacent column blocks per CTA, or two
     P.code = a.L.d_code; P.expert_stride_words = exl3_code_words(a.d); P.n_blocks = a.d.H / 128; P.nkt = a.d.I / 16;
     P.xa = a.xd; P.xa_proj_stride = 0; P.xd = nullptr; P.ro = a.ro;
-    if ((e = pf_launch<1, 4, PF_CAP0, KB>(P, a.sm_count, st)) != cudaSuccess) return e;
-    return pf_launch<1, 2, PF_CAP1, KB>(P, a.sm_count, st);
+    if ((e = pf_launch<1, 2, PF_CAP0, KB, 2>(P, a.sm_count, st)) != cudaSuccess) return e;
+    return pf_launch<1, 2, PF_CAP1, KB, 1>(P, a.sm_count, st);
 }
 
 cudaError_t launch_exl3_prefill(const Exl3PrefillArgs& a, cudaStream_t st) {
