@@ -171,17 +171,18 @@ __device__ __forceinline__ float nf_sigmoid(float x) {  // src/arch/mimo_v2/moe.
 // NPROJ projections x CB adjacent 128-column blocks = NG accumulator groups of NT tensor-memory columns each.  Tensor
 // memory after the accumulators: per operand stage NG x 8 columns of weight scales (4 used: column + lane quarter) and 8
 // columns of row scales (row n: lane n % 32 of every quarter, column + n / 32; bytes 0, 1 high part, 2, 3 low part).
-template <int NPROJ, int CB, int NT>
-__global__ void __launch_bounds__(512 + 64, 1) mxfp4_native_kernel(const NfParams P) {
+template <int NPROJ, int CB, int NT, int PER_SM>
+__global__ void __launch_bounds__(512 + 64, PER_SM) mxfp4_native_kernel(const NfParams P) {
     constexpr int NG = NPROJ * CB;
     constexpr int SFC = NG * 8 + 8;
-    constexpr int LIST = NG == 4 ? 0 : 1;
+    constexpr int TCOLS = 512 / PER_SM;                               // tensor-memory columns of this CTA (PER_SM CTAs share an SM)
+    constexpr int LIST = NT == NF_CAP0 ? 0 : 1;
     constexpr int NCW = 16;
     constexpr uint32_t B_SLOT = NT * NF_ROW_BYTES;
     constexpr uint32_t A_SLOT = NG * 8192;                            // an operand stage of codes in operand geometry
     constexpr uint32_t W_BYTES = NPROJ * (NF_W_STAGE + NF_S_STAGE);   // one block's stage of the stream
     constexpr uint32_t RAW_BYTES = CB * W_BYTES;
-    static_assert((NG == 2 || NG == 4) && NG * NT + 2 * SFC <= 512, "shape");
+    static_assert((NG == 2 || NG == 4) && NG * NT + 2 * SFC <= TCOLS, "shape");
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t raw_full[NF_RAW_MAX], raw_empty[NF_RAW_MAX];
     __shared__ __align__(8) uint64_t b_full[NF_B_MAX], b_empty[NF_B_MAX], a_full[NF_A_MAX], a_empty[NF_A_MAX];
@@ -208,7 +209,7 @@ __global__ void __launch_bounds__(512 + 64, 1) mxfp4_native_kernel(const NfParam
     }
     // the unused high halves of the operand rows stay zero for the whole kernel
     for (uint32_t i = threadIdx.x; i < A_STAGES * A_SLOT / 16; i += blockDim.x) reinterpret_cast<uint4*>(a_ring)[i] = make_uint4(0, 0, 0, 0);
-    if (warp == 0) tmem_alloc(&s_tmem, 512);
+    if (warp == 0) tmem_alloc(&s_tmem, TCOLS);
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -419,15 +420,15 @@ __global__ void __launch_bounds__(512 + 64, 1) mxfp4_native_kernel(const NfParam
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp == 0) tmem_free(tmem, 512);
+    if (warp == 0) tmem_free(tmem, TCOLS);
 }
 
-template <int NPROJ, int CB, int NT>
+template <int NPROJ, int CB, int NT, int PER_SM>
 static cudaError_t nf_launch(NfParams P, int sm_count, cudaStream_t st) {
     constexpr int NG = NPROJ * CB;
     const size_t raw_bytes = (size_t)CB * NPROJ * (NF_W_STAGE + NF_S_STAGE), b_slot = (size_t)NT * NF_ROW_BYTES, a_slot = (size_t)NG * 8192;
-    const size_t budget = 222 * 1024;
-    const uint32_t a_max = (512 - NG * NT) / (NG * 8 + 8);
+    const size_t budget = PER_SM == 1 ? 222 * 1024 : 110 * 1024;
+    const uint32_t a_max = (512 / PER_SM - NG * NT) / (NG * 8 + 8);
     P.a_stages = a_max < 3 ? a_max : 3;
     P.raw_stages = 3;
     while (P.raw_stages > 2 && P.a_stages * a_slot + P.raw_stages * raw_bytes + 3 * b_slot > budget) --P.raw_stages;
@@ -436,9 +437,9 @@ static cudaError_t nf_launch(NfParams P, int sm_count, cudaStream_t st) {
     P.b_stages = (uint32_t)(nb > (size_t)NF_B_MAX ? (size_t)NF_B_MAX : nb);
     if (P.b_stages < 2) return cudaErrorInvalidConfiguration;
     const size_t smem = P.a_stages * a_slot + P.b_stages * b_slot + P.raw_stages * raw_bytes;
-    cudaError_t e = cudaFuncSetAttribute(mxfp4_native_kernel<NPROJ, CB, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(mxfp4_native_kernel<NPROJ, CB, NT, PER_SM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    mxfp4_native_kernel<NPROJ, CB, NT><<<sm_count, 512 + 64, smem, st>>>(P);
+    mxfp4_native_kernel<NPROJ, CB, NT, PER_SM><<<PER_SM * sm_count, 512 + 64, smem, st>>>(P);
     return cudaGetLastError();
 }
 
@@ -454,13 +455,13 @@ cudaError_t launch_mxfp4_native(const Fp4PrefillArgs& a, cudaStream_t st) {
     P.w = a.gu; P.n_blocks = a.I / 128; P.n_stages_k = a.H / NF_KS;
     P.expert_stride = (size_t)P.n_blocks * P.n_stages_k * 2 * (NF_W_STAGE + NF_S_STAGE);
     P.xa = xa; P.xd = xd; P.out = nullptr; P.out_bf16 = 0;
-    if ((e = nf_launch<2, 2, NF_CAP0>(P, a.sm_count, st)) != cudaSuccess) return e;
-    if ((e = nf_launch<2, 1, NF_CAP1>(P, a.sm_count, st)) != cudaSuccess) return e;
+    if ((e = nf_launch<2, 1, NF_CAP0, 2>(P, a.sm_count, st)) != cudaSuccess) return e;
+    if ((e = nf_launch<2, 1, NF_CAP1, 1>(P, a.sm_count, st)) != cudaSuccess) return e;
     P.w = a.dn; P.n_blocks = a.H / 128; P.n_stages_k = a.I / NF_KS;
     P.expert_stride = (size_t)P.n_blocks * P.n_stages_k * (NF_W_STAGE + NF_S_STAGE);
     P.xa = xd; P.xd = nullptr; P.out = a.ro; P.out_bf16 = a.ro_bf16;
-    if ((e = nf_launch<1, 4, NF_CAP0>(P, a.sm_count, st)) != cudaSuccess) return e;
-    return nf_launch<1, 2, NF_CAP1>(P, a.sm_count, st);
+    if ((e = nf_launch<1, 2, NF_CAP0, 2>(P, a.sm_count, st)) != cudaSuccess) return e;
+    return nf_launch<1, 2, NF_CAP1, 1>(P, a.sm_count, st);
 }
 
 }  // namespace mlxs

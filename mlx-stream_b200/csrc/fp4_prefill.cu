@@ -166,16 +166,17 @@ __device__ __forceinline__ float q_sigmoid(float x) {  // src/arch/mimo_v2/moe.z
 // NPROJ projections x CB adjacent 128-column blocks = NG accumulator groups of NT tensor-memory columns each; an
 // operand stage holds KST inputs (KST / 2 tensor-memory columns per group).  One synchronisation round trip (decode ->
 // MMA -> stage free) costs several hundred cycles whatever the stage holds, so a stage carries NG x KST / 16 MMAs.
-template <int NPROJ, int CB, int NT, int KST, bool NV>
-__global__ void __launch_bounds__(512 + 64, 1) fp4_prefill_kernel(const QParams P) {
+template <int NPROJ, int CB, int NT, int KST, bool NV, int PER_SM>
+__global__ void __launch_bounds__(512 + 64, PER_SM) fp4_prefill_kernel(const QParams P) {
     constexpr int NG = NPROJ * CB;
     constexpr int KB = KST / Q_SB;                                   // 32-input blocks per operand stage
     constexpr int A_COLS = KST / 2;                                  // tensor-memory columns of one group's stage
-    constexpr int A_STAGES = (512 - NG * NT) / (NG * A_COLS);
+    constexpr int TCOLS = 512 / PER_SM;                              // tensor-memory columns of this CTA (PER_SM CTAs share an SM)
+    constexpr int A_STAGES = (TCOLS - NG * NT) / (NG * A_COLS);
     constexpr int TASKS = NG * KB / 4;                               // (group, block) tasks of a warp per stage
     static_assert((NG == 2 || NG == 4) && A_STAGES >= 2 && TASKS >= 1 && Q_KS % KST == 0, "shape");
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    constexpr int LIST = NG == 4 ? 0 : 1;
+    constexpr int LIST = NT == Q_CAP0 ? 0 : 1;
     constexpr int NCW = 16;
     constexpr int B_SLOT = NT * KST * 2;
     constexpr uint32_t SSTAGE = NV ? 1024u : 512u;
@@ -206,7 +207,7 @@ __global__ void __launch_bounds__(512 + 64, 1) fp4_prefill_kernel(const QParams 
         mbar_fence_init();
     }
     if (NV && threadIdx.x < 256) s_lut[threadIdx.x] = q_e4m3_f16x2(threadIdx.x);
-    if (warp == 0) tmem_alloc(&s_tmem, 512);
+    if (warp == 0) tmem_alloc(&s_tmem, TCOLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -409,7 +410,7 @@ __global__ void __launch_bounds__(512 + 64, 1) fp4_prefill_kernel(const QParams 
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp == 0) tmem_free(tmem, 512);
+    if (warp == 0) tmem_free(tmem, TCOLS);
 }
 
 static int q_env(const char* name, int dflt, int lo, int hi) {
@@ -420,20 +421,20 @@ static int q_env(const char* name, int dflt, int lo, int hi) {
 
 bool fp4_prefill_supported(uint32_t H, uint32_t I) { return H % 128 == 0 && I % 128 == 0 && (I / 128) % 2 == 0 && (H / 128) % 4 == 0; }
 
-template <int NPROJ, int CB, int NT, int KST, bool NV>
+template <int NPROJ, int CB, int NT, int KST, bool NV, int PER_SM>
 static cudaError_t q_launch(QParams P, int sm_count, cudaStream_t st) {
     // ring depths: the code ring first (HBM latency), the rest of the budget to the rows
     const size_t raw_bytes = (size_t)CB * NPROJ * (Q_W_STAGE + q_scale_stage_bytes(NV)), b_slot = (size_t)NT * KST * 2;
-    const size_t budget = 224 * 1024;
+    const size_t budget = PER_SM == 1 ? 224 * 1024 : 110 * 1024;
     static const int raw_want = q_env("MLXS_Q_RAW_STAGES", 4, 2, Q_RAW_MAX), b_want = q_env("MLXS_Q_B_STAGES", Q_B_MAX, 2, Q_B_MAX);
     P.raw_stages = (uint32_t)raw_want;
     while (P.raw_stages > 2 && P.raw_stages * raw_bytes + 3 * b_slot > budget) --P.raw_stages;
     size_t nb = (budget - P.raw_stages * raw_bytes) / b_slot;
     P.b_stages = (uint32_t)(nb > (size_t)b_want ? (size_t)b_want : nb);
     const size_t smem = P.b_stages * b_slot + P.raw_stages * raw_bytes;
-    cudaError_t e = cudaFuncSetAttribute(fp4_prefill_kernel<NPROJ, CB, NT, KST, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(fp4_prefill_kernel<NPROJ, CB, NT, KST, NV, PER_SM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    fp4_prefill_kernel<NPROJ, CB, NT, KST, NV><<<sm_count, 512 + 64, smem, st>>>(P);
+    fp4_prefill_kernel<NPROJ, CB, NT, KST, NV, PER_SM><<<PER_SM * sm_count, 512 + 64, smem, st>>>(P);
     return cudaGetLastError();
 }
 
@@ -451,17 +452,17 @@ cudaError_t launch_fp4_prefill(const Fp4PrefillArgs& a, cudaStream_t st) {
     P.w = a.gu; P.w_bytes = 2 * (Q_W_STAGE + sstage); P.n_blocks = a.I / 128; P.n_stages_k = a.H / Q_KS;
     P.expert_stride = (size_t)P.n_blocks * P.n_stages_k * P.w_bytes;
     P.xa = a.xa; P.xd = a.xd; P.out = nullptr; P.out_bf16 = 0;
-    e = a.nv ? q_launch<2, 2, Q_CAP0, Q_KST, true>(P, a.sm_count, st) : q_launch<2, 2, Q_CAP0, Q_KST, false>(P, a.sm_count, st);
+    e = a.nv ? q_launch<2, 1, Q_CAP0, Q_KST, true, 2>(P, a.sm_count, st) : q_launch<2, 1, Q_CAP0, Q_KST, false, 2>(P, a.sm_count, st);
     if (e != cudaSuccess) return e;
-    e = a.nv ? q_launch<2, 1, Q_CAP1, Q_KST, true>(P, a.sm_count, st) : q_launch<2, 1, Q_CAP1, Q_KST, false>(P, a.sm_count, st);
+    e = a.nv ? q_launch<2, 1, Q_CAP1, Q_KST, true, 1>(P, a.sm_count, st) : q_launch<2, 1, Q_CAP1, Q_KST, false, 1>(P, a.sm_count, st);
     if (e != cudaSuccess) return e;
     // down: four adjacent column blocks per CTA, or two
     P.w = a.dn; P.w_bytes = Q_W_STAGE + sstage; P.n_blocks = a.H / 128; P.n_stages_k = a.I / Q_KS;
     P.expert_stride = (size_t)P.n_blocks * P.n_stages_k * P.w_bytes;
     P.xa = a.xd; P.xd = nullptr; P.out = a.ro; P.out_bf16 = a.ro_bf16;
-    e = a.nv ? q_launch<1, 4, Q_CAP0, Q_KST, true>(P, a.sm_count, st) : q_launch<1, 4, Q_CAP0, Q_KST, false>(P, a.sm_count, st);
+    e = a.nv ? q_launch<1, 2, Q_CAP0, Q_KST, true, 2>(P, a.sm_count, st) : q_launch<1, 2, Q_CAP0, Q_KST, false, 2>(P, a.sm_count, st);
     if (e != cudaSuccess) return e;
-    return a.nv ? q_launch<1, 2, Q_CAP1, Q_KST, true>(P, a.sm_count, st) : q_launch<1, 2, Q_CAP1, Q_KST, false>(P, a.sm_count, st);
+    return a.nv ? q_launch<1, 2, Q_CAP1, Q_KST, true, 1>(P, a.sm_count, st) : q_launch<1, 2, Q_CAP1, Q_KST, false, 1>(P, a.sm_count, st);
 }
 
 }  // namespace mlxs
