@@ -10,10 +10,10 @@
 //     order inside a 16-block is taken as k' = 4c + 2 (k / 8) + k % 2, c = (k % 8) / 2; the rows are staged in the same
 //     order, which a dot product does not see.  One tile costs its decode plus one tensor-memory store: no shared-memory
 //     stores, no address arithmetic, no proxy fence;
-//   * tensor memory (512 columns) holds the f32 accumulators and a ring of two decoded stages of 64 inputs (32 columns
-//     per group and stage).  Two shapes: 4 groups x 64 rows (experts with up to 64 rows: gate and up of two column
-//     blocks, or four blocks of down) and 2 groups x 192 rows (the others: gate and up of one block, or two blocks of
-//     down), where one decode serves three times the rows;
+//   * tensor memory holds the f32 accumulators and a ring of two decoded stages of 64 inputs (32 columns per group
+//     and stage).  Two shapes, each 2 groups (gate and up of one column block, or two column blocks of down): 64 rows
+//     (experts with up to 64 rows) in 256 columns, two CTAs per SM, so that one CTA's barrier waits and epilogue run
+//     under the other's decode; and 192 rows (the others) in 512 columns, where one decode serves three times the rows;
 //   * a producer thread streams the raw code (bulk copies, one stage = 4 k-tiles of the group's blocks) and the rows'
 //     rotated f16 activations, which a prep kernel laid out as K-major core matrices;
 //   * 16 decode warps in two teams that take the stages alternately (team = stage parity = slot of the operand ring):
@@ -470,13 +470,13 @@ static cudaError_t pf_launch_all(const Exl3PrefillArgs& a, cudaStream_t st) {
     PfParams P{};
     P.tiles = a.tiles; P.max_tiles = a.max_tiles; P.t = a.t; P.scales = a.L.scales; P.scales_stride = exl3_scales_per_expert(a.d);
     P.H = a.d.H; P.I = a.d.I; P.limit = a.limit; P.status = a.status;
-    // gate / up: both projections of two adjacent column blocks (tiles up to 64 rows) or of one (up to 192 rows)
+    // gate / up: both projections of one column block, tiles up to 64 rows (two CTAs per SM) or up to 192 rows
     P.code = a.L.gu_code; P.expert_stride_words = 2 * exl3_code_words(a.d); P.n_blocks = a.d.I / 128; P.nkt = a.d.H / 16;
     P.xa = a.xa; P.xa_proj_stride = exl3_prefill_staging_rows(a.rows_cap, a.max_tiles) * a.d.H; P.xd = a.xd; P.ro = nullptr;
     cudaError_t e = pf_launch<2, 1, PF_CAP0, KB, 2>(P, a.sm_count, st);
     if (e != cudaSuccess) return e;
     if ((e = pf_launch<2, 1, PF_CAP1, KB, 1>(P, a.sm_count, st)) != cudaSuccess) return e;
-    // down: four adjacent column blocks per CTA, or two
+    // down: two adjacent column blocks per CTA
     P.code = a.L.d_code; P.expert_stride_words = exl3_code_words(a.d); P.n_blocks = a.d.H / 128; P.nkt = a.d.I / 16;
     P.xa = a.xd; P.xa_proj_stride = 0; P.xd = nullptr; P.ro = a.ro;
     if ((e = pf_launch<1, 2, PF_CAP0, KB, 2>(P, a.sm_count, st)) != cudaSuccess) return e;

@@ -7,10 +7,10 @@
 // rows are the B operand in shared memory (N = rows rounded to 16).  Shared memory carries only the packed codes and
 // the rows, which is what bounds a one-SM MMA fed from decoded operands: a decoded A tile in shared memory would be
 // written once and read once per use, as many bytes as the rows themselves.
-//   * tensor memory (512 columns) holds the f32 accumulators and a ring of two decoded A stages of 64 inputs.  Two
-//     shapes: 4 groups x 64 rows (experts with up to 64 rows; gate and up of two column blocks, or four column blocks
-//     of down; 256 + 256 columns) and 2 groups x 192 rows (the others: gate and up of one block, or two blocks of
-//     down; 384 + 128 columns), where a decoded operand serves three times the rows;
+//   * tensor memory holds the f32 accumulators and a ring of two decoded A stages of 64 inputs.  Two shapes, each 2
+//     groups (gate and up of one column block, or two column blocks of down): 64 rows (experts with up to 64 rows;
+//     128 + 128 columns, two CTAs per SM: one CTA's waits and epilogue run under the other's work) and 192 rows (the
+//     others; 384 + 128 columns), where a decoded operand serves three times the rows;
 //   * a producer thread streams the same repacked code/scale stream the decode-batch kernel reads (bulk copies, one
 //     stage = 128 inputs of a 128-column block) and the rows, which a prep kernel laid out in core-matrix order;
 //   * 16 decode warps: a thread owns one output column of one group, loads 32 of its codes as one 16-byte word, turns
@@ -47,7 +47,7 @@ constexpr int Q_SB = 32;                      // inputs per block of the staged 
 constexpr int Q_B_MAX = 12, Q_RAW_MAX = 6;   // most stages of the row ring and of the code ring
 constexpr int Q_SBO = 128;
 constexpr int Q_KST = 64;                     // inputs per operand stage
-constexpr int Q_CAP0 = 64, Q_CAP1 = 192;      // rows per tile of the two shapes: 4 groups x 64 rows, 2 groups x 192 rows
+constexpr int Q_CAP0 = 64, Q_CAP1 = 192;      // rows per tile of the two shapes (64: two CTAs per SM)
                                               // (256 / 384 accumulator columns; the other columns hold decoded A stages)
 constexpr int Q_W_STAGE = 8192;               // code bytes per projection per raw stage (fp4.cu F4_W_STAGE)
 
@@ -447,8 +447,7 @@ cudaError_t launch_fp4_prefill(const Fp4PrefillArgs& a, cudaStream_t st) {
     QParams P{};
     P.gscale = a.gscale; P.tiles = a.tiles; P.max_tiles = a.max_tiles; P.t = a.t; P.H = a.H; P.I = a.I; P.limit = a.limit;
     P.status = a.status;
-    // gate / up: both projections of two adjacent column blocks (tiles up to 96 rows) or of one (up to 192 rows), one
-    // copy of the rows
+    // gate / up: both projections of one column block, tiles up to 64 rows (two CTAs per SM) or up to 192 rows
     P.w = a.gu; P.w_bytes = 2 * (Q_W_STAGE + sstage); P.n_blocks = a.I / 128; P.n_stages_k = a.H / Q_KS;
     P.expert_stride = (size_t)P.n_blocks * P.n_stages_k * P.w_bytes;
     P.xa = a.xa; P.xd = a.xd; P.out = nullptr; P.out_bf16 = 0;
@@ -456,7 +455,7 @@ cudaError_t launch_fp4_prefill(const Fp4PrefillArgs& a, cudaStream_t st) {
     if (e != cudaSuccess) return e;
     e = a.nv ? q_launch<2, 1, Q_CAP1, Q_KST, true, 1>(P, a.sm_count, st) : q_launch<2, 1, Q_CAP1, Q_KST, false, 1>(P, a.sm_count, st);
     if (e != cudaSuccess) return e;
-    // down: four adjacent column blocks per CTA, or two
+    // down: two adjacent column blocks per CTA
     P.w = a.dn; P.w_bytes = Q_W_STAGE + sstage; P.n_blocks = a.H / 128; P.n_stages_k = a.I / Q_KS;
     P.expert_stride = (size_t)P.n_blocks * P.n_stages_k * P.w_bytes;
     P.xa = a.xd; P.xd = nullptr; P.out = a.ro; P.out_bf16 = a.ro_bf16;
