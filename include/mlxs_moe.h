@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define MLXS_MOE_ABI 2026112601
+#define MLXS_MOE_ABI 2026112602
 
 /* refusals (the names mirror the reference's refusal sets: src/sdk_ext/quant.zig:94-111, src/expert/bank.zig:79-101) */
 enum {
@@ -215,6 +215,12 @@ typedef struct {
     double tflops_f16, tflops_mxf8f6f4, tflops_hi_lo_effective;
 } mlxs_fp4_native_result;
 int mlxs_moe_fp4_native_probe(int32_t device, uint32_t rate_mmas, mlxs_fp4_native_result *out);
+
+/* Time of one tcgen05.mma.kind::f16 (M 128 x N x K 16, bf16) issued back to back by one thread per SM on all SMs, with the
+ * A operand in shared memory (a_from_tmem = 0) or in tensor memory: what the tensor-core lanes' tile shapes are chosen
+ * by (no counterpart in the reference).  n: 16 .. 256, a multiple of 16; mmas instructions per SM.  ns_per_mma: the
+ * measured time; the rate is 2 x 128 x n x 16 / ns_per_mma per SM.  Needs no handle. */
+int mlxs_moe_mma_rate(int32_t device, uint32_t n, int a_from_tmem, uint32_t mmas, double *ns_per_mma);
 
 int mlxs_moe_stats_get(mlxs_moe *h, mlxs_moe_stats *out);
 /* The device status word is sticky (a host must see a fault it did not poll for): once a kernel has recorded an error

@@ -14,7 +14,7 @@ from pathlib import Path  # noqa: E402
 
 HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "libmlxs_moe.so"
-ABI = 2026112601
+ABI = 2026112602
 
 BANK_EXL3_K3_MUL1, BANK_MXFP4, BANK_NVFP4, BANK_EXL3_K2_MUL1 = 0, 1, 2, 3
 SCORE_SQRTSOFTPLUS, SCORE_SIGMOID, SCORE_SOFTMAX = 0, 1, 2
@@ -32,7 +32,7 @@ EXPORTS = [
     "mlxs_moe_set_placement", "mlxs_moe_set_router_weight", "mlxs_moe_logits", "mlxs_moe_forward_x",
     "mlxs_moe_set_layer_bits", "mlxs_moe_layer_record_bytes", "mlxs_moe_bank_layer_bits_text",
     "mlxs_moe_ep_window_bytes", "mlxs_moe_ep_overloaded_rank",
-    "mlxs_moe_status_clear", "mlxs_moe_sort_rows", "mlxs_moe_debug_wait", "mlxs_moe_exl3_decode_rate", "mlxs_moe_fp4_native_probe",
+    "mlxs_moe_status_clear", "mlxs_moe_sort_rows", "mlxs_moe_debug_wait", "mlxs_moe_exl3_decode_rate", "mlxs_moe_fp4_native_probe", "mlxs_moe_mma_rate",
     "mlxs_moe_bank_verify", "mlxs_moe_usage_enable", "mlxs_moe_usage_add", "mlxs_moe_usage_read", "mlxs_moe_usage_reset", "mlxs_moe_plan_placement",
 ]
 
@@ -130,6 +130,7 @@ def lib():
         L.mlxs_moe_logits.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
         L.mlxs_moe_forward_x.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
         L.mlxs_moe_fp4_native_probe.argtypes = [C.c_int32, C.c_uint32, C.POINTER(Fp4NativeResult)]
+        L.mlxs_moe_mma_rate.argtypes = [C.c_int32, C.c_uint32, C.c_int, C.c_uint32, C.POINTER(C.c_double)]
         L.mlxs_moe_exl3_decode_rate.argtypes = [C.c_int32, C.c_uint32, C.c_int, C.c_uint32, C.POINTER(C.c_double)]
         L.mlxs_moe_ep_window_bytes.restype = C.c_uint64
         L.mlxs_moe_ep_window_bytes.argtypes = [C.c_uint32] * 5
@@ -201,6 +202,13 @@ def exl3_decode_rate(device=0, bits=3, with_mma=True, tiles_per_warp=1 << 16):
     """Tiles per second of the EXL3 in-register decode alone (operands from registers): the decode's own ceiling."""
     out = C.c_double()
     _check(lib().mlxs_moe_exl3_decode_rate(device, bits, int(with_mma), tiles_per_warp, C.byref(out)))
+    return out.value
+
+
+def mma_rate(device=0, n=256, a_from_tmem=False, mmas=20000):
+    """Nanoseconds per tcgen05.mma (M 128 x n x K 16, bf16) issued back to back on every SM."""
+    out = C.c_double()
+    _check(lib().mlxs_moe_mma_rate(device, n, int(a_from_tmem), mmas, C.byref(out)))
     return out.value
 
 

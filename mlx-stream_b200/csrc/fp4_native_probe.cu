@@ -114,8 +114,9 @@ __global__ void __launch_bounds__(128) mxf8_numerics_kernel(const uint32_t* __re
 }
 
 // Issue-rate loop on operands that stay in shared memory (contents irrelevant): mode 0 = kind::f16 (bf16, K = 16 per MMA),
-// mode 1 = kind::mxf8f6f4.block_scale (K = 32 per MMA).  N = 256, M = 128, `mmas` instructions per CTA, one CTA per SM.
-__global__ void __launch_bounds__(128) mxf8_rate_kernel(int mode, uint32_t mmas, uint32_t* status) {
+// mode 1 = kind::mxf8f6f4.block_scale (K = 32 per MMA), mode 2 = kind::f16 with the A operand in tensor memory.  M = 128,
+// N = nn, `mmas` instructions per CTA, one CTA per SM.
+__global__ void __launch_bounds__(128) mxf8_rate_kernel(int mode, uint32_t mmas, uint32_t* status, uint32_t nn) {
     extern __shared__ __align__(128) uint8_t smem_raw[];   // A 128 x 64 B, B 256 x 64 B
     __shared__ __align__(8) uint64_t bar;
     __shared__ uint32_t s_tmem;
@@ -136,14 +137,15 @@ __global__ void __launch_bounds__(128) mxf8_rate_kernel(int mode, uint32_t mmas,
     tc_fence_after();
     if (tid == 0) {
         const uint32_t a_s = smem_u32(smem_raw), b_s = a_s + 128 * 64;
-        if (mode == 0) {
+        if (mode == 0 || mode == 2) {
             // 16-bit elements: a core matrix is 8 rows x 8 elements; K = 16 is two of them
             const uint64_t da = umma_smem_desc(a_s, 16 * 128, 128), db = umma_smem_desc(b_s, 32 * 128, 128);
-            const uint32_t id = umma_idesc(UMMA_BF16, 256);
-            for (uint32_t i = 0; i < mmas; ++i) umma_f16(tmem, da, db, id, i ? 1u : 0u);
+            const uint32_t id = umma_idesc(UMMA_BF16, nn);
+            if (mode == 0) for (uint32_t i = 0; i < mmas; ++i) umma_f16(tmem, da, db, id, i ? 1u : 0u);
+            else for (uint32_t i = 0; i < mmas; ++i) umma_f16_ts(tmem, tmem + 300, db, id, i ? 1u : 0u);
         } else {
             const uint64_t da = umma_smem_desc(a_s, 16 * 128, 128), db = umma_smem_desc(b_s, 32 * 128, 128);
-            const uint32_t id = mxf8_idesc(256, 0, 0);
+            const uint32_t id = mxf8_idesc(nn, 0, 0);
             for (uint32_t i = 0; i < mmas; ++i) umma_mxf8(tmem, da, db, id, tmem + 256, tmem + 264, i ? 1u : 0u);
         }
         umma_commit(&bar);
@@ -279,9 +281,9 @@ extern "C" int mlxs_moe_fp4_native_probe(int32_t device, uint32_t rate_mmas, mlx
         cudaEventCreate(&a);
         cudaEventCreate(&b);
         for (int mode = 0; mode < 2 && e == cudaSuccess; ++mode) {
-            mxf8_rate_kernel<<<prop.multiProcessorCount, 128, smem>>>(mode, rate_mmas / 8 + 1, d_status);   // warm-up
+            mxf8_rate_kernel<<<prop.multiProcessorCount, 128, smem>>>(mode, rate_mmas / 8 + 1, d_status, 256u);   // warm-up
             cudaEventRecord(a, 0);
-            mxf8_rate_kernel<<<prop.multiProcessorCount, 128, smem>>>(mode, rate_mmas, d_status);
+            mxf8_rate_kernel<<<prop.multiProcessorCount, 128, smem>>>(mode, rate_mmas, d_status, 256u);
             cudaEventRecord(b, 0);
             if ((e = cudaEventSynchronize(b)) != cudaSuccess) break;
             float ms = 0.f;
@@ -302,5 +304,40 @@ extern "C" int mlxs_moe_fp4_native_probe(int32_t device, uint32_t rate_mmas, mlx
     out->tflops_f16 = tf[0];
     out->tflops_mxf8f6f4 = tf[1];
     out->tflops_hi_lo_effective = tf[1] / 2.0;
+    return MLXS_OK;
+}
+
+extern "C" int mlxs_moe_mma_rate(int32_t device, uint32_t n, int a_from_tmem, uint32_t mmas, double* ns_per_mma) {
+    using namespace mlxs;
+    if (!ns_per_mma || !mmas) return mlxs_fail(MLXS_E_ARG, "mma_rate: null or zero argument");
+    if (n < 16 || n > 256 || n % 16) return mlxs_fail(MLXS_E_ARG, "mma_rate: n = %u is not a multiple of 16 in 16 .. 256", n);
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return mlxs_fail(MLXS_E_CUDA, "mma_rate: cudaSetDevice: %s", cudaGetErrorString(e));
+    cudaDeviceProp prop;
+    if ((e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess || prop.major != 10)
+        return mlxs_fail(MLXS_E_CUDA, "mma_rate: needs an sm_100 device");
+    uint32_t* d_status = nullptr;
+    if ((e = cudaMalloc(&d_status, 16)) != cudaSuccess) return mlxs_fail(MLXS_E_CUDA, "mma_rate: cudaMalloc: %s", cudaGetErrorString(e));
+    cudaMemset(d_status, 0, 16);
+    const size_t smem = (128 + 256) * 64;
+    const int mode = a_from_tmem ? 2 : 0;
+    cudaEvent_t a, b;
+    cudaEventCreate(&a);
+    cudaEventCreate(&b);
+    mxf8_rate_kernel<<<prop.multiProcessorCount, 128, smem>>>(mode, mmas / 8 + 1, d_status, n);   // warm-up
+    cudaEventRecord(a, 0);
+    mxf8_rate_kernel<<<prop.multiProcessorCount, 128, smem>>>(mode, mmas, d_status, n);
+    cudaEventRecord(b, 0);
+    e = cudaEventSynchronize(b);
+    float ms = 0.f;
+    if (e == cudaSuccess) cudaEventElapsedTime(&ms, a, b);
+    uint32_t st = 0;
+    if (e == cudaSuccess) cudaMemcpy(&st, d_status, 4, cudaMemcpyDeviceToHost);
+    cudaEventDestroy(a);
+    cudaEventDestroy(b);
+    cudaFree(d_status);
+    if (e != cudaSuccess) return mlxs_fail(MLXS_E_CUDA, "mma_rate: %s", cudaGetErrorString(e));
+    if (st) return mlxs_fail(MLXS_E_DEVICE_STATUS, "mma_rate: a bounded wait ran out (status %u)", st);
+    *ns_per_mma = (double)ms * 1e6 / (double)mmas;
     return MLXS_OK;
 }

@@ -2,7 +2,7 @@
 //! is the compiled, tested statement of the same ABI).  One declaration per C entry point, same order.
 const std = @import("std");
 
-pub const abi_expected: i32 = 2026112601;
+pub const abi_expected: i32 = 2026112602;
 
 pub const Moe = opaque {};
 
@@ -100,6 +100,8 @@ pub extern fn mlxs_moe_exl3_decode_rate(device: i32, bits: u32, with_mma: c_int,
 pub const Fp4NativeResult = extern struct { rel_l2_hi_lo: f64, rel_l2_hi_only: f64, tflops_f16: f64, tflops_mxf8f6f4: f64, tflops_hi_lo_effective: f64 };
 /// the native block-scaled FP4 MMA measured (numerics of the hi / lo split, issue rates)
 pub extern fn mlxs_moe_fp4_native_probe(device: i32, rate_mmas: u32, out: *Fp4NativeResult) c_int;
+/// nanoseconds per tcgen05.mma (M 128 x n x K 16) issued back to back on every SM, A in shared or tensor memory
+pub extern fn mlxs_moe_mma_rate(device: i32, n: u32, a_from_tmem: c_int, mmas: u32, ns_per_mma: *f64) c_int;
 /// self-test hook of the bounded waits
 pub extern fn mlxs_moe_debug_wait(h: *Moe, poll_limit: u32, withhold_stage: u32) c_int;
 

@@ -170,3 +170,18 @@ def test_native_block_scaled_fp4_mma_measured():
     assert r["rel_l2_hi_lo"] < 4e-3, r
     assert 5e-3 < r["rel_l2_hi_only"] < 0.1, r
     assert r["tflops_f16"] > 100 and r["tflops_mxf8f6f4"] > 1.3 * r["tflops_f16"], r
+
+
+def test_mma_time_against_the_row_count_of_a_tile():
+    """One tcgen05.mma of M 128 x N x K 16 costs the same whether its A operand sits in shared or in tensor memory, takes
+    time in proportion to N from 128 rows on and has a floor below that: what the lanes' tile shapes (192-row tiles, A in
+    tensor memory) rest on."""
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    t = {(n, a): pkg.mma_rate(0, n, a, 8000) for n in (64, 128, 256) for a in (False, True)}
+    for n in (64, 128, 256):
+        assert abs(t[(n, True)] - t[(n, False)]) < 0.15 * t[(n, False)], t
+    assert 1.6 < t[(256, False)] / t[(128, False)] < 2.4, t          # in proportion from 128 rows on
+    assert t[(64, False)] > 0.6 * t[(128, False)], t                  # a floor below
+    with pytest.raises(Exception):
+        pkg.mma_rate(0, 100, False, 10)
