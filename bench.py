@@ -188,7 +188,9 @@ def own_launches_per_layer(wl, T, world):
     if wl["shared"]:
         n += 2 if T <= 64 else 3            # skinny gate/up + down, or row staging + the two tcgen05 products
     if world > 1:
-        n += 7                              # destination ranks, rank sort, dedup, push, unpack, partial push, final sum
+        # the exchange: its plan (destination ranks, rank sort, dedup: one launch up to 2048 assignments, three above),
+        # push, unpack, partial push, final sum
+        n += 5 if A <= 2048 else 7
     else:
         n += 1                              # combine (expert parallel: the partial push and the final sum do its work)
     return n

@@ -33,6 +33,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "dispatch_body.cuh"
 #include "handle.h"
 
 namespace {
@@ -157,10 +158,10 @@ __global__ void ep_scatter_kernel(const uint4* __restrict__ ret, const uint32_t*
 // (token, rank) pair, and which unique row (numbered over all ranks in sorted order) does it read.  One CTA of 1024
 // threads walks the positions in blocks with a running total.  ustart[r] = first unique row of rank r's segment;
 // counts[2r] = assignments, counts[2r + 1] = unique rows going to rank r.
-__global__ void __launch_bounds__(1024) ep_dedup_kernel(const uint32_t* __restrict__ order, const uint32_t* __restrict__ offsets,
-                                                        const int32_t* __restrict__ dest, uint32_t A, uint32_t W, uint32_t k,
-                                                        uint32_t* __restrict__ urow, uint32_t* __restrict__ ustart,
-                                                        int32_t* __restrict__ counts) {
+__device__ __forceinline__ void ep_dedup_body(const uint32_t* __restrict__ order, const uint32_t* __restrict__ offsets,
+                                              const int32_t* __restrict__ dest, uint32_t A, uint32_t W, uint32_t k,
+                                              uint32_t* __restrict__ urow, uint32_t* __restrict__ ustart,
+                                              int32_t* __restrict__ counts) {
     __shared__ uint32_t wsum[33];
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     uint32_t carry = 0;
@@ -206,6 +207,33 @@ __global__ void __launch_bounds__(1024) ep_dedup_kernel(const uint32_t* __restri
         counts[2 * r] = (int32_t)(offsets[r + 1] - offsets[r]);
         counts[2 * r + 1] = (int32_t)(ustart[r + 1] - ustart[r]);
     }
+}
+__global__ void __launch_bounds__(1024) ep_dedup_kernel(const uint32_t* __restrict__ order, const uint32_t* __restrict__ offsets,
+                                                        const int32_t* __restrict__ dest, uint32_t A, uint32_t W, uint32_t k,
+                                                        uint32_t* __restrict__ urow, uint32_t* __restrict__ ustart,
+                                                        int32_t* __restrict__ counts) {
+    ep_dedup_body(order, offsets, dest, A, W, k, urow, ustart, counts);
+}
+// The plan of one exchange for decode-sized calls in one launch: destination rank and local slot of every assignment,
+// the stable sort by rank (the dispatch kernel's code), the first assignment of every (token, rank) pair.  One CTA; the
+// three steps read what the one before wrote to global memory after a CTA barrier.  dsm: W + 99 words.
+__global__ void __launch_bounds__(DTHREADS) ep_plan_kernel(const int32_t* __restrict__ ids, uint32_t A, uint32_t E,
+                                                           const uint32_t* __restrict__ place, int32_t* __restrict__ dest,
+                                                           int32_t* __restrict__ meta, DispatchTables rtab, uint32_t W, uint32_t k,
+                                                           uint32_t chunk_rows, uint32_t group_chunks, uint32_t* __restrict__ urow,
+                                                           uint32_t* __restrict__ ustart, int32_t* __restrict__ counts, uint32_t* status) {
+    extern __shared__ uint32_t ep_dsm[];
+    for (uint32_t a = threadIdx.x; a < A; a += DTHREADS) {
+        int32_t id = ids[a];
+        if (id < 0 || (uint32_t)id >= E) { atomicMax(status, (uint32_t)ST_BAD_EXPERT_ID); id = 0; }
+        const uint32_t pl = place[id];   // rank << 16 | local slot
+        dest[a] = (int32_t)(pl >> 16);
+        meta[a] = (int32_t)(pl & 0xFFFFu);
+    }
+    __syncthreads();
+    dispatch_body(dest, A, W, nullptr, rtab, chunk_rows, group_chunks, 0u, status, ep_dsm);
+    __syncthreads();
+    ep_dedup_body(rtab.order, rtab.offsets, dest, A, W, k, urow, ustart, counts);
 }
 // per sorted position: the unique row's copy of x (by the pair's first assignment), the assignment's local expert,
 // its row inside what the destination rank receives from this rank, its weight; and the inverse maps for the final sum
@@ -753,10 +781,18 @@ static int ep_combined_p2p(mlxs_moe* h, uint32_t layer, const void* x_dev, const
     const uint32_t epoch = ++ep->epoch;
     {
         StageTimer tm(h, MLXS_STAGE_EXCHANGE, st);
-        if (A) mlxs::ep_dest_kernel<<<(A + 255) / 256, 256, 0, st>>>(ids_dev, A, c.n_experts, h->layers[layer].place_dev, ep->dest, ep->meta, h->status);
-        CU(launch_dispatch(ep->dest, A, W, nullptr, ep->rtab, h->chunk_rows, h->group_chunks, 0, h->status, st));
-        mlxs::ep_dedup_kernel<<<1, 1024, 0, st>>>(ep->rtab.order, ep->rtab.offsets, ep->dest, A, W, c.top_k, ep->urow, ep->ustart,
-                                                 ep->counts_dev);
+        if (A <= 2048) {
+            // decode-sized calls: destination ranks, rank sort and dedup in one launch
+            mlxs::ep_plan_kernel<<<1, mlxs::DTHREADS, (W + 99) * sizeof(uint32_t), st>>>(ids_dev, A, c.n_experts, h->layers[layer].place_dev,
+                                                                                     ep->dest, ep->meta, ep->rtab, W, c.top_k, h->chunk_rows,
+                                                                                     h->group_chunks, ep->urow, ep->ustart, ep->counts_dev,
+                                                                                     h->status);
+        } else {
+            mlxs::ep_dest_kernel<<<(A + 255) / 256, 256, 0, st>>>(ids_dev, A, c.n_experts, h->layers[layer].place_dev, ep->dest, ep->meta, h->status);
+            CU(launch_dispatch(ep->dest, A, W, nullptr, ep->rtab, h->chunk_rows, h->group_chunks, 0, h->status, st));
+            mlxs::ep_dedup_kernel<<<1, 1024, 0, st>>>(ep->rtab.order, ep->rtab.offsets, ep->dest, A, W, c.top_k, ep->urow, ep->ustart,
+                                                     ep->counts_dev);
+        }
         mlxs::ep_push_kernel<<<A ? A : 1, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x_dev), ep->meta, ep->dest, weights_dev,
                                                         ep->rtab.order, ep->rtab.offsets, ep->urow, ep->ustart, ep->counts_dev, A,
                                                         c.top_k, w, epoch, ep->a_urow, ep->a_first, ep->ctl, ep->bytes_dev);
