@@ -12,6 +12,9 @@ SOURCES = ["api.cu", "router.cu", "dispatch.cu", "exl3.cu", "shared_combine.cu",
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "-Xptxas", "-v", "--expt-relaxed-constexpr"]
+# extra compiler flags for a measurement build (e.g. MLXS_NVCC_EXTRA=-DMLXS_LANE_COUNTERS; rebuild with --force, and
+# again without the variable afterwards)
+FLAGS += os.environ.get("MLXS_NVCC_EXTRA", "").split()
 
 
 def _stale(obj: Path, src: Path) -> bool:

@@ -31,6 +31,15 @@
 #include "kernels.h"
 #include "umma.cuh"
 
+// -DMLXS_LANE_COUNTERS: cycle counters around the waits, the decode and the MMA issue of one CTA, printed once per launch
+// (how the lane's bound was found; off in the library)
+#ifdef MLXS_LANE_COUNTERS
+#include <cstdio>
+#define LC(...) __VA_ARGS__
+#else
+#define LC(...)
+#endif
+
 namespace mlxs {
 
 constexpr int PF_KST = 64;          // inputs per operand stage (4 k-tiles)
@@ -263,6 +272,7 @@ __global__ void __launch_bounds__(512 + 64, PER_SM) exl3_prefill_kernel(const Pf
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             uint32_t as = 0, aph = 0, bs = 0, nitem = 0;
+            LC(long long m_wait = 0, m_issue = 0; uint32_t m_n = 0;)
             const uint32_t b_ring_s = smem_u32(b_ring);
             for (uint32_t item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++nitem) {
                 const uint32_t rows16 = (prefill_tile(P.tiles, LIST, P.max_tiles, item / nbg)[2] + 15) / 16 * 16;
@@ -272,8 +282,10 @@ __global__ void __launch_bounds__(512 + 64, PER_SM) exl3_prefill_kernel(const Pf
                 tc_fence_after();
                 bool ok = true;
                 for (uint32_t kk = 0; kk < nstage; ++kk) {
+                    LC(const long long w0 = clock64();)
                     if (!mbar_wait_bounded(&a_full[as], aph, &s_abort)) { give_up(ST_WAIT_FULL); ok = false; break; }
                     tc_fence_after();
+                    LC(const long long w1 = clock64(); m_wait += w1 - w0; ++m_n;)
                     const uint32_t ta = tmem_a + as * (NG * PF_A_COLS);
 #pragma unroll
                     for (int gq = 0; gq < NG; ++gq) {
@@ -288,10 +300,13 @@ __global__ void __launch_bounds__(512 + 64, PER_SM) exl3_prefill_kernel(const Pf
                     umma_commit(&b_empty[bs]);
                     if (++as == A_STAGES) { as = 0; aph ^= 1u; }
                     if (++bs == B_STAGES) bs = 0;
+                    LC(m_issue += clock64() - w1;)
                 }
                 if (!ok) break;
                 umma_commit(&acc_full);
             }
+            LC(if (blockIdx.x == 3 && m_n) printf("LANE<%d,%d,%d> mma thread: items %u stages %u, cycles per stage: wait %lld issue %lld\n", NPROJ, CB,
+                                                  NT, nitem, m_n, m_wait / m_n, m_issue / m_n);)
         }
     } else {
         // ---------------- decode warps + epilogue ----------------
@@ -311,17 +326,20 @@ __global__ void __launch_bounds__(512 + 64, PER_SM) exl3_prefill_kernel(const Pf
             if (!ok) give_up(ST_WAIT_FULL);
             return ok;
         };
+        LC(long long t_wait = 0, t_dec = 0, t_arr = 0, t_epi = 0; uint32_t n_st = 0;)
         for (uint32_t item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++nitem, gs0 += nstage) {
             const uint32_t nb0 = (item % nbg) * CB;
             const uint32_t* te = prefill_tile(P.tiles, LIST, P.max_tiles, item / nbg);
             const uint32_t expert = te[0], row0 = te[1], rows = te[2], srow0 = te[3];
             bool ok = true;
             for (uint32_t ks = team; ks < nstage; ks += 2) {
+                LC(const long long c0 = clock64();)
                 const uint32_t gs = gs0 + ks;           // stage number since the kernel started (gs0 is even)
                 const uint32_t rs = gs % RAW_STAGES, rph = (gs / RAW_STAGES) & 1u, aph = (gs >> 1) & 1u;
                 if (!mbar_wait_bounded(&raw_full[rs], rph, &s_abort) || !mbar_wait_bounded(&a_empty[team], aph ^ 1u, &s_abort)) {
                     give_up(ST_WAIT_FULL); ok = false; break;
                 }
+                LC(const long long c1 = clock64(); t_wait += c1 - c0; ++n_st;)
 #pragma unroll
                 for (int gi = 0; gi < GPW; ++gi) {
                     const uint32_t gq = sub2 * GPW + gi;
@@ -343,14 +361,17 @@ __global__ void __launch_bounds__(512 + 64, PER_SM) exl3_prefill_kernel(const Pf
                 }
                 tmem_wait_st();
                 tc_fence_before();
+                LC(const long long c2 = clock64(); t_dec += c2 - c1;)
                 if (q == 0 && sub2 == 0) {  // the stage's rows have landed too: the issuer then waits on one barrier only
                     const uint32_t bsl = gs % B_STAGES, bph = (gs / B_STAGES) & 1u;
                     if (!mbar_wait_bounded(&b_full[bsl], bph, &s_abort)) { give_up(ST_WAIT_FULL); ok = false; break; }
                 }
                 __syncwarp();
                 if (lane == 0) { mbar_arrive(&a_full[team]); mbar_arrive(&raw_empty[rs]); }
+                LC(t_arr += clock64() - c2;)
             }
             if (!ok) break;
+            LC(const long long e0 = clock64();)
             // ---- epilogue: per column block, 32 rows at a time ----
             if (!mbar_wait_bounded(&acc_full, nitem & 1u, &s_abort)) { give_up(ST_WAIT_FULL); break; }
             tc_fence_after();
@@ -431,7 +452,11 @@ __global__ void __launch_bounds__(512 + 64, PER_SM) exl3_prefill_kernel(const Pf
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty);
+            LC(t_epi += clock64() - e0;)
         }
+        LC(if (blockIdx.x == 3 && lane == 0 && warp == 9 && n_st) printf(
+               "LANE<%d,%d,%d> decode warp 9: items %u of %u stages, cycles per stage of the team: wait %lld decode+store %lld arrive %lld; per item: epilogue %lld\n",
+               NPROJ, CB, NT, nitem, n_st, t_wait / n_st, t_dec / n_st, t_arr / n_st, t_epi / (nitem ? nitem : 1));)
     }
     // every thread comes here, also after a give-up: the tensor memory is always released
     tc_fence_before();

@@ -55,6 +55,18 @@ def test_create_refuses_by_name():
     assert "struct_size" in ei.value.msg
 
 
+def test_measurement_entries_refuse_bad_arguments_by_name():
+    """The probes check their arguments before they touch a device."""
+    pkg = load_package()
+    for n in (0, 8, 100, 272):
+        with pytest.raises(pkg.MlxsError) as ei:
+            pkg.mma_rate(0, n, False, 10)
+        assert ei.value.rc == -1 and "multiple of 16" in ei.value.msg, ei.value.msg   # MLXS_E_ARG
+    with pytest.raises(pkg.MlxsError) as ei:
+        pkg.mma_rate(0, 128, False, 0)
+    assert ei.value.rc == -1
+
+
 def test_no_cpu_fallback_without_a_device():
     import torch
     if torch.cuda.is_available():
