@@ -312,13 +312,11 @@ struct FrontCall {
     const float* logits;   // the router's logits, or null when the layer starts from x (the layer's router weight)
 };
 
-// Can this call take the fused front kernel (front.cu)?  One rank, a decode-sized batch whose experts all stream, no
-// route tally to feed.  MLXS_FRONT_MAX moves the batch limit (0: never).
+// Can this call take the fused front kernel (front.cu)?  One rank, a decode-sized batch, no route tally to feed.  MLXS_FRONT_MAX moves the batch limit (0: never).
 static bool front_applies(const mlxs_moe* h, uint32_t T) {
     static const uint32_t front_max = getenv("MLXS_FRONT_MAX") ? (uint32_t)atoi(getenv("MLXS_FRONT_MAX")) : 16u;
     if (T == 0 || T > front_max || h->cfg.ep_world != 1 || h->usage_on || h->front_off) return false;
     if (T * h->cfg.top_k > 2048) return false;
-    if (h->pf_tiles && T >= h->pf_min_rows) return false;   // some expert could take the tensor-core lane
     return true;
 }
 
@@ -794,7 +792,8 @@ static int experts_impl(mlxs_moe* h, uint32_t layer, const void* x_dev, const in
         fa.w_router = front->logits ? nullptr : L.router_w; fa.logits_out = h->logits_ws; fa.logits = front->logits; fa.bias = L.bias;
         fa.E = (int)c.n_experts; fa.K = (int)c.top_k; fa.scoring = (int)c.scoring; fa.norm = (int)c.norm_topk; fa.scale = c.routed_scale;
         fa.ids = h->ids_ws; fa.weights = h->w_ws; fa.T = T; fa.loaded = L.loaded_dev; fa.t = h->tabs;
-        fa.chunk_rows = h->chunk_rows; fa.group_chunks = h->group_chunks; fa.status = h->status;
+        fa.chunk_rows = h->chunk_rows; fa.group_chunks = h->group_chunks; fa.status = h->status; fa.sm_count = h->sm_count;
+        fa.heavy = (h->pf_tiles && T >= h->pf_min_rows) ? h->pf_min_rows : 0u;   // the lane choice of mlxs_run_routed
         fa.x = static_cast<const __nv_bfloat16*>(x_dev); fa.H = c.hidden; fa.bank_exl3 = is_exl3(c.bank_kind) ? 1 : 0;
         fa.scales = L.scales; fa.scales_stride = is_exl3(c.bank_kind) ? exl3_scales_per_expert(Exl3Dims{c.hidden, c.inter, L.kbits}) : 0;
         fa.xa = h->xa_gu; fa.bar = h->front_bar;

@@ -35,7 +35,7 @@ struct FrontParams {
     // phase 2
     const uint8_t* loaded;
     DispatchTables t;
-    uint32_t chunk_rows, group_chunks;
+    uint32_t chunk_rows, group_chunks, heavy;
     uint32_t* status;
     // phase 3
     const __nv_bfloat16* x;
@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(1024, 1) front_kernel(const FrontParams P) {
 
     // ---- phase 2: dispatch by CTA 0 ----
     if (blockIdx.x == 0)
-        dispatch_body(P.ids, T * (uint32_t)P.K, (uint32_t)P.E, P.loaded, P.t, P.chunk_rows, P.group_chunks, 0u, P.status,
+        dispatch_body(P.ids, T * (uint32_t)P.K, (uint32_t)P.E, P.loaded, P.t, P.chunk_rows, P.group_chunks, P.heavy, P.status,
                       reinterpret_cast<uint32_t*>(fsm));
     front_grid_sync(P.bar, gen, P.poll_limit, P.status);
 
@@ -148,7 +148,7 @@ cudaError_t launch_front(const FrontArgs& a, cudaStream_t st) {
     FrontParams P{};
     P.w_router = a.w_router; P.logits_out = a.logits_out; P.logits = a.w_router ? a.logits_out : a.logits; P.bias = a.bias;
     P.E = a.E; P.K = a.K; P.scoring = a.scoring; P.norm = a.norm; P.scale = a.scale; P.ids = a.ids; P.weights = a.weights; P.T = a.T;
-    P.loaded = a.loaded; P.t = a.t; P.chunk_rows = a.chunk_rows; P.group_chunks = a.group_chunks; P.status = a.status;
+    P.loaded = a.loaded; P.t = a.t; P.chunk_rows = a.chunk_rows; P.group_chunks = a.group_chunks; P.heavy = a.heavy; P.status = a.status;
     P.x = a.x; P.H = a.H; P.bank_exl3 = a.bank_exl3; P.scales = a.scales; P.scales_stride = a.scales_stride; P.xa = a.xa;
     P.bar = a.bar; P.poll_limit = 1u << 22;
     const int rt = ((a.E > a.K ? a.E : a.K) + 31) / 32 * 32;
@@ -157,8 +157,9 @@ cudaError_t launch_front(const FrontArgs& a, cudaStream_t st) {
     cudaError_t e = cudaFuncSetAttribute(front_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     void* args[] = {&P};
-    // enough CTAs for the staging of up to 16 tokens' rows; every CTA of a cooperative launch is resident at once
-    const unsigned grid = a.T > 4 ? 32u : (a.T > 1 ? 16u : 8u);
+    // enough CTAs for the staging of the call's rows (a CTA per SM above 16 tokens); every CTA of a cooperative launch
+    // is resident at once
+    const unsigned grid = a.T > 16 ? (unsigned)(a.sm_count > 0 ? a.sm_count : 32) : (a.T > 4 ? 32u : (a.T > 1 ? 16u : 8u));
     return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(front_kernel), dim3(grid), dim3(1024), args, smem, st);
 }
 

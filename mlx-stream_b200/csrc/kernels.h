@@ -51,6 +51,7 @@ struct FrontArgs {
     const uint8_t* loaded;
     DispatchTables t;
     uint32_t chunk_rows, group_chunks;
+    uint32_t heavy;                 // rows from which an expert leaves the streaming lane (0: never)
     uint32_t* status;
     const __nv_bfloat16* x;
     uint32_t H;
@@ -59,6 +60,7 @@ struct FrontArgs {
     size_t scales_stride;
     uint32_t* xa;
     uint32_t* bar;
+    int sm_count;
 };
 cudaError_t launch_front(const FrontArgs& a, cudaStream_t st);
 
