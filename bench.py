@@ -51,7 +51,12 @@ WORKLOADS = {
     "glm": dict(name="glm: GLM-Flash-shaped routed MoE layer, EXL3 K=3 mul1 bank", H=4096, I=2048, E=256, k=8, bank="exl3",
                 shared=True, scoring="sigmoid", scale=2.5, limit=10.0, chain=False),
 }
-LANE_MIN_ROWS = int(os.environ.get("MLXS_PREFILL_MIN_ROWS", "17"))  # the library's default lane threshold
+LANE_MIN_ROWS = int(os.environ.get("MLXS_PREFILL_MIN_ROWS", "0"))  # 0: the library's default for the bank (lane_min_rows)
+
+
+def lane_min_rows(wl):
+    """Rows from which an expert of a call takes the tensor-core lane: the library's default is 13 for EXL3 banks, 17 for FP4."""
+    return LANE_MIN_ROWS or (13 if wl["bank"] == "exl3" else 17)
 N_BATCHES = 4  # a few seeded batches in rotation, so that consecutive steps route differently
 
 
@@ -183,7 +188,7 @@ def own_launches_per_layer(wl, T, world):
         n += 3                              # streaming lane: prep, gate/up, down
     # the tensor-core lane's kernels launch when the local call has enough "tokens" for an expert to reach the threshold
     # (with expert parallelism every received assignment is a token of the local call)
-    if (T if world == 1 else A) >= LANE_MIN_ROWS:
+    if (T if world == 1 else A) >= lane_min_rows(wl):
         n += 6                              # tile plan, row prep, gate/up and down in two tile shapes each
     if wl["shared"]:
         n += 2 if T <= 64 else 3            # skinny gate/up + down, or row staging + the two tcgen05 products
@@ -566,8 +571,9 @@ def measure(rig, args, sampler, want_e2e=True):
         return tot / args.steps     # per step (summed over the stack's layers)
 
     distinct_step = mean_over_calls(lambda c: float((c > 0).sum()))
-    light_step = mean_over_calls(lambda c: float(((c > 0) & (c < LANE_MIN_ROWS)).sum()) if T >= LANE_MIN_ROWS or world > 1 else float((c > 0).sum()))
-    rows_heavy = mean_over_calls(lambda c: float(c[c >= LANE_MIN_ROWS].sum()))
+    lmr = lane_min_rows(wl)
+    light_step = mean_over_calls(lambda c: float(((c > 0) & (c < lmr)).sum()) if T >= lmr or world > 1 else float((c > 0).sum()))
+    rows_heavy = mean_over_calls(lambda c: float(c[c >= lmr].sum()))
     rows_served = mean_over_calls(lambda c: float(c.sum()))
     if wl["bank"] == "exl3":
         code_bytes = (H // 16) * (I // 16) * 96

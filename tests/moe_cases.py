@@ -7,6 +7,12 @@ f16(+-(0.5+u) 0.02) so the effective dense weight has element std ~0.02; activat
 """
 import ctypes as C
 
+# rows from which an expert of a call takes the tensor-core lane (the library's defaults; MLXS_PREFILL_MIN_ROWS moves both)
+import os as _os
+LANE_MIN_EXL3 = int(_os.environ.get("MLXS_PREFILL_MIN_ROWS", "13"))
+LANE_MIN_FP4 = int(_os.environ.get("MLXS_PREFILL_MIN_ROWS", "17"))
+
+
 import numpy as np
 
 import oracle_lib as O

@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 
 import oracle_lib as O
-from moe_cases import Exl3Case, Exl3K2Case, max_err_over_rms, rel_l2
+from moe_cases import Exl3Case, Exl3K2Case, max_err_over_rms, rel_l2, LANE_MIN_EXL3
 
 pytestmark = pytest.mark.gpu
 GOLD = Path(__file__).resolve().parent / "golden"
@@ -193,7 +193,7 @@ def test_small_shape_layer_many_seeds():
 
 
 def test_prefill_lane_tcgen05():
-    """Experts with 17 rows or more take the tensor-core lane, the others of the same call the streaming lane (the
+    """Experts with LANE_MIN_EXL3 rows or more take the tensor-core lane, the others of the same call the streaming lane (the
     reference picks the lane on logical M: src/sdk_ext/quant.zig:5-6): f16-rounded rotated activations as the
     reference's prefill chain (src/kernels/exl3/dsv41_prefill_dig_take2v_5120.metal:57-58), f32 accumulate."""
     case = Exl3Case(512, 256, 4, 2, seed=12, shared=True, max_tokens=1024)
@@ -206,7 +206,7 @@ def test_prefill_lane_tcgen05():
         logits[:, 3] -= 2.5
         ids, w = case.cpu_route(logits)
         counts = np.bincount(ids.reshape(-1), minlength=4)
-        assert counts.max() > 128 and 0 < counts.min() < 17  # both lanes in one call
+        assert counts.max() > 128 and 0 < counts.min() < LANE_MIN_EXL3  # both lanes in one call
         ref_y, ref_ro = case.cpu_layer(x, ids, w, want_ro=True)
         ro = case.gpu_routed(x, ids)
         assert case.status() == 0
@@ -220,7 +220,7 @@ def test_prefill_lane_tcgen05():
         keep = np.arange(0, T, 2)
         sub = case.gpu_routed(x[keep], ids[keep])
         sub_counts = np.bincount(ids[keep].reshape(-1), minlength=4)
-        same_lane = (counts >= 17) == (sub_counts >= 17)
+        same_lane = (counts >= LANE_MIN_EXL3) == (sub_counts >= LANE_MIN_EXL3)
         assert same_lane.sum() >= 2
         m = same_lane[ids[keep]]
         assert (sub.view(np.uint32)[m] == ro[keep].view(np.uint32)[m]).all()
@@ -400,7 +400,7 @@ def test_many_assignments_take_the_multi_cta_dispatch():
         x, logits = case.inputs(T, seed=77)
         logits[:, 5] -= 3.0          # one expert with few rows (streaming lane), the others heavy (tensor-core lane)
         ids, w = case.cpu_route(logits)
-        assert ids.size > 2048 and 0 < np.bincount(ids.reshape(-1), minlength=8)[5] < 17
+        assert ids.size > 2048 and 0 < np.bincount(ids.reshape(-1), minlength=8)[5] < LANE_MIN_EXL3
         y = case.gpu_experts(x, ids, w)
         assert case.status() == 0
         assert rel_l2(y, case.cpu_layer(x, ids, w)) < TOL_LAYER
@@ -553,7 +553,7 @@ def test_k2_layer_both_lanes():
         logits[:, 3] -= 2.5
         ids, w = case.cpu_route(logits)
         counts = np.bincount(ids.reshape(-1), minlength=4)
-        assert counts.max() > 128 and 0 < counts.min() < 17
+        assert counts.max() > 128 and 0 < counts.min() < LANE_MIN_EXL3
         ref_y, ref_ro = case.cpu_layer(x, ids, w, want_ro=True)
         ro = case.gpu_routed(x, ids)
         assert rel_l2(ro, ref_ro) < 1e-3

@@ -18,7 +18,7 @@ import numpy as np
 import pytest
 
 import oracle_lib as O
-from moe_cases import Exl3Case, Mxfp4Case, Nvfp4Case, max_err_over_rms, rel_l2, zipf_bias
+from moe_cases import Exl3Case, Mxfp4Case, Nvfp4Case, max_err_over_rms, rel_l2, zipf_bias, LANE_MIN_EXL3
 
 pytestmark = pytest.mark.gpu
 GOLD = Path(__file__).resolve().parent / "golden"
@@ -108,10 +108,10 @@ def test_exl3_tensor_lane_at_real_dims():
     case = _Exl3Shared(5120, 2304, 16, 4, seed=3, shared=True, max_tokens=320)
     try:
         T = 300
-        x, logits = _lane_mix(case, T, 41, [([0, 1], 6.0), ([2], 2.2), ([3], 0.9), ([4], 0.5)])
+        x, logits = _lane_mix(case, T, 41, [([0, 1], 6.0), ([2], 2.2), ([3], 0.9), ([4], 0.5), ([10, 13], -1.2)])
         ids, w = case.cpu_route(logits)
         counts = np.bincount(ids.reshape(-1), minlength=case.E)
-        assert counts.max() > 256 and ((counts >= 17) & (counts <= 128)).any() and ((counts > 0) & (counts < 17)).any(), counts
+        assert counts.max() > 256 and ((counts >= LANE_MIN_EXL3) & (counts <= 128)).any() and ((counts > 0) & (counts < LANE_MIN_EXL3)).any(), counts
         gid, gw = case.gpu_route(logits)
         assert (gid == ids).all()
         ro = case.gpu_routed(x, ids)
