@@ -136,7 +136,7 @@ cudaError_t launch_exl3_raw(const uint32_t* code_e, uint32_t in_dim, uint32_t ou
                             uint32_t proj_off_words, int kbits, DispatchTables t, const uint32_t* xa, float* z,
                             uint32_t* status, int sm_count, cudaStream_t st);
 
-// prefill-sized batches: tcgen05 MMA over trellis tiles decoded to f16 in shared memory (exl3_prefill.cu)
+// prefill-sized batches: tcgen05 MMA over trellis tiles decoded to f16 in tensor memory (exl3_prefill.cu)
 constexpr int PREFILL_TILE_ROWS = 128;
 // An expert's lane in a call: the tensor-core lane when it has `min_rows` rows or more, unless its entry of the
 // per-expert table (1 = resident, bit 1 = its weights are outside that lane's exact range) says otherwise.
@@ -214,7 +214,7 @@ struct Fp4GemvArgs {
     uint32_t* ks_count;     // [ksplit_count_words(sm_count)] zeroed once
 };
 cudaError_t launch_fp4_gemv(const Fp4GemvArgs& a, int down, cudaStream_t st);
-// experts with many rows: tcgen05 MMA over codes decoded to 16-bit operands in shared memory (fp4_prefill.cu)
+// experts with many rows: tcgen05 MMA over codes decoded to 16-bit operands in tensor memory (fp4_prefill.cu)
 struct Fp4PrefillArgs {
     const uint8_t* gu;       // the streams of Fp4GemvArgs
     const uint8_t* dn;
@@ -229,8 +229,9 @@ struct Fp4PrefillArgs {
     uint32_t top_k;
     uint32_t* tiles;         // [prefill_tile_words(max_tiles)]
     uint32_t max_tiles;
-    uint16_t* xa;            // [staging rows][H] rows in the MMA's B-operand order (bf16 MXFP4, f16 NVFP4)
-    uint16_t* xd;            // [staging rows][I]
+    uint16_t* xa;            // [staging rows][H] rows in the MMA's B-operand order (bf16 MXFP4, f16 NVFP4; the block-scaled
+                             // MXFP4 lane keeps E4M3 high / low parts and scale bytes here, mxfp4_native_xa_bytes)
+    uint16_t* xd;            // [staging rows][I], the same for the down product
     uint32_t rows_cap;       // assignment rows the staging was sized for
     void* ro;                // [A, H] bf16 (chain combine) or f32
     int ro_bf16;
