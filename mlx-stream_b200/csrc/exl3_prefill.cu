@@ -296,8 +296,8 @@ __global__ void __launch_bounds__(512 + 64, PER_SM) exl3_prefill_kernel(const Pf
                             umma_f16_ts(tmem + gq * NT, ta + gq * PF_A_COLS + i * 8, bd + ((i * 2 * lbo_b) >> 4), idesc,
                                         (kk | (uint32_t)i) ? 1u : 0u);
                     }
+                    // one commit per stage: it frees the operand slot, and the decode team that sees it frees the rows' slot
                     umma_commit(&a_empty[as]);
-                    umma_commit(&b_empty[bs]);
                     if (++as == A_STAGES) { as = 0; aph ^= 1u; }
                     if (++bs == B_STAGES) bs = 0;
                     LC(m_issue += clock64() - w1;)
@@ -339,6 +339,8 @@ __global__ void __launch_bounds__(512 + 64, PER_SM) exl3_prefill_kernel(const Pf
                 if (!mbar_wait_bounded(&raw_full[rs], rph, &s_abort) || !mbar_wait_bounded(&a_empty[team], aph ^ 1u, &s_abort)) {
                     give_up(ST_WAIT_FULL); ok = false; break;
                 }
+                // the operand slot is free: the MMAs of this team's last stage (two stages back) are done with their rows too
+                if (q == 0 && sub2 == 0 && lane == 0 && gs >= 2) mbar_arrive(&b_empty[(gs - 2) % B_STAGES]);
                 LC(const long long c1 = clock64(); t_wait += c1 - c0; ++n_st;)
 #pragma unroll
                 for (int gi = 0; gi < GPW; ++gi) {

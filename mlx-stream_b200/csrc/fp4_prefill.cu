@@ -274,8 +274,9 @@ __global__ void __launch_bounds__(512 + 64, PER_SM) fp4_prefill_kernel(const QPa
                             umma_f16_ts(tmem + gq * NT, ta + gq * A_COLS + i * 8, bd + ((i * 2 * lbo_b) >> 4), idesc,
                                         (kk | (uint32_t)i) ? 1u : 0u);
                     }
+                    // one commit per stage (a commit costs the issuing thread about as much as an MMA): it frees the
+                    // operand slot, and decode warp 0, when it sees that, frees the rows' slot of the same stage
                     umma_commit(&a_empty[as]);
-                    umma_commit(&b_empty[bs]);
                     if (++as == A_STAGES) { as = 0; aph ^= 1u; }
                     if (++bs == B_STAGES) bs = 0;
                 }
@@ -292,6 +293,7 @@ __global__ void __launch_bounds__(512 + 64, PER_SM) fp4_prefill_kernel(const QPa
         const uint32_t p = NPROJ == 2 ? gq / CB : 0u, cb = NPROJ == 2 ? gq % CB : gq;
         const uint32_t m = q * 32u + lane, wr = m >> 4, r = (m >> 3) & 1u, g = m & 7u;
         uint32_t rs = 0, rph = 0, as = 0, aph = 0, bs = 0, bph = 0, nitem = 0;
+        uint32_t n_stage = 0, rel_bs = 0;   // operand stages so far; the rows' slot to free next (A_STAGES stages behind)
         for (uint32_t item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++nitem) {
             const uint32_t nb0 = (item % nbg) * CB;
             const uint32_t* te = prefill_tile(P.tiles, LIST, P.max_tiles, item / nbg);
@@ -304,7 +306,14 @@ __global__ void __launch_bounds__(512 + 64, PER_SM) fp4_prefill_kernel(const QPa
 #pragma unroll
                 for (int os = 0; os < Q_KS / KST; ++os) {
                     if (!mbar_wait_bounded(&a_empty[as], aph ^ 1u, &s_abort)) { give_up(ST_WAIT_FULL); ok = false; break; }
-
+                    // the slot is free: the MMAs of the stage that used it (A_STAGES stages back) are done with their rows too
+                    if (warp == 0) {
+                        if (n_stage >= (uint32_t)A_STAGES) {
+                            if (lane == 0) mbar_arrive(&b_empty[rel_bs]);
+                            if (++rel_bs == B_STAGES) rel_bs = 0;
+                        }
+                        ++n_stage;
+                    }
 #pragma unroll
                     for (int n = 0; n < TASKS; ++n) {
                         const uint32_t kb = kb0 + n * (4 / NG), sb = os * KB + kb;   // block of the stage, of the raw stage
