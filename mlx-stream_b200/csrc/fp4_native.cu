@@ -276,8 +276,11 @@ __global__ void __launch_bounds__(512 + 64, PER_SM) mxfp4_native_kernel(const Nf
                             umma_mxf8(tmem + gq * NT, da, dl, nf_idesc(rows16, os * 2 + j, 2 + j), sf + gq * 8, sfb, 1u);
                         }
                     }
+                    // A commit costs the issuing thread about as much as an MMA.  The large shape commits once per
+                    // stage (the operand slot; operand warp 0, when it sees that slot free, frees the rows' slot of the
+                    // same stage); the two-CTA shape, whose rows' ring is short, commits both
                     umma_commit(&a_empty[as]);
-                    umma_commit(&b_empty[bs]);
+                    if (PER_SM != 1) umma_commit(&b_empty[bs]);
                     if (++as == A_STAGES) { as = 0; aph ^= 1u; }
                     if (++bs == B_STAGES) bs = 0;
                 }
@@ -295,6 +298,7 @@ __global__ void __launch_bounds__(512 + 64, PER_SM) mxfp4_native_kernel(const Nf
         const bool sf_warp = slot < (uint32_t)NG, b_warp = slot == 3u;
         const uint32_t sgq = sf_warp ? slot : 0u, sp = NPROJ == 2 ? sgq / CB : 0u, scb = NPROJ == 2 ? sgq % CB : sgq;
         uint32_t rs = 0, rph = 0, as = 0, aph = 0, bs = 0, bph = 0, nitem = 0;
+        uint32_t n_stage = 0, rel_bs = 0;   // operand stages so far; the rows' slot to free next (A_STAGES stages behind)
         for (uint32_t item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x, ++nitem) {
             const uint32_t nb0 = (item % nbg) * CB;
             const uint32_t* te = prefill_tile(P.tiles, LIST, P.max_tiles, item / nbg);
@@ -315,6 +319,14 @@ __global__ void __launch_bounds__(512 + 64, PER_SM) mxfp4_native_kernel(const Nf
                 for (int os = 0; os < NF_KS / NF_KST; ++os) {
                     if (!mbar_wait_bounded(&a_empty[as], aph ^ 1u, &s_abort)) { give_up(ST_WAIT_FULL); ok = false; break; }
                     tc_fence_after();
+                    // the slot is free: the MMAs of the stage that used it (A_STAGES stages back) are done with their rows too
+                    if (PER_SM == 1 && warp == 0) {
+                        if (n_stage >= A_STAGES) {
+                            if (lane == 0) mbar_arrive(&b_empty[rel_bs]);
+                            if (++rel_bs == B_STAGES) rel_bs = 0;
+                        }
+                        ++n_stage;
+                    }
                     // codes: chunk c of group gq = (wr, block of the stage, r, g): 32 codes of one column and block ->
                     // the low halves of two operand rows, 2048 bytes apart along K
                     uint8_t* a_slot = a_ring + as * A_SLOT;
@@ -428,14 +440,18 @@ static cudaError_t nf_launch(NfParams P, int sm_count, cudaStream_t st) {
     constexpr int NG = NPROJ * CB;
     const size_t raw_bytes = (size_t)CB * NPROJ * (NF_W_STAGE + NF_S_STAGE), b_slot = (size_t)NT * NF_ROW_BYTES, a_slot = (size_t)NG * 8192;
     const size_t budget = PER_SM == 1 ? 222 * 1024 : 110 * 1024;
+    // the large shape has two operand slots: a rows' slot is freed two stages after its use, and the rows' ring wants to
+    // be deeper than that
     const uint32_t a_max = (512 / PER_SM - NG * NT) / (NG * 8 + 8);
-    P.a_stages = a_max < 3 ? a_max : 3;
+    const uint32_t a_want = PER_SM == 1 ? 2u : 3u;
+    P.a_stages = a_max < a_want ? a_max : a_want;
     P.raw_stages = 3;
     while (P.raw_stages > 2 && P.a_stages * a_slot + P.raw_stages * raw_bytes + 3 * b_slot > budget) --P.raw_stages;
     while (P.a_stages > 2 && P.a_stages * a_slot + P.raw_stages * raw_bytes + 3 * b_slot > budget) --P.a_stages;
     size_t nb = (budget - P.a_stages * a_slot - P.raw_stages * raw_bytes) / b_slot;
     P.b_stages = (uint32_t)(nb > (size_t)NF_B_MAX ? (size_t)NF_B_MAX : nb);
     if (P.b_stages < 2) return cudaErrorInvalidConfiguration;
+    if (P.a_stages > P.b_stages) P.a_stages = P.b_stages;
     const size_t smem = P.a_stages * a_slot + P.b_stages * b_slot + P.raw_stages * raw_bytes;
     cudaError_t e = cudaFuncSetAttribute(mxfp4_native_kernel<NPROJ, CB, NT, PER_SM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
