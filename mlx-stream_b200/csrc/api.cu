@@ -206,7 +206,10 @@ extern "C" int mlxs_moe_create(const mlxs_moe_config* c, mlxs_moe** out) {
             cudaEventCreateWithFlags(&h->aux_join, cudaEventDisableTiming) != cudaSuccess ||
             cudaStreamCreateWithFlags(&h->lane_stream, cudaStreamNonBlocking) != cudaSuccess ||
             cudaEventCreateWithFlags(&h->lane_fork, cudaEventDisableTiming) != cudaSuccess ||
-            cudaEventCreateWithFlags(&h->lane_join, cudaEventDisableTiming) != cudaSuccess)
+            cudaEventCreateWithFlags(&h->lane_join, cudaEventDisableTiming) != cudaSuccess ||
+            cudaStreamCreateWithFlags(&h->lane2_stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&h->lane2_fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&h->lane2_join, cudaEventDisableTiming) != cudaSuccess)
             return bail(fail(MLXS_E_CUDA, "create: second stream"));
     }
     if (cudaDeviceSynchronize() != cudaSuccess) return bail(fail(MLXS_E_CUDA, "create: device synchronize failed"));
@@ -221,6 +224,9 @@ extern "C" void mlxs_moe_destroy(mlxs_moe* h) {
     mlxs_ep_destroy(h);
     if (h->lane_fork) cudaEventDestroy(h->lane_fork);
     if (h->lane_join) cudaEventDestroy(h->lane_join);
+    if (h->lane2_fork) cudaEventDestroy(h->lane2_fork);
+    if (h->lane2_join) cudaEventDestroy(h->lane2_join);
+    if (h->lane2_stream) cudaStreamDestroy(h->lane2_stream);
     if (h->aux_fork) cudaEventDestroy(h->aux_fork);
     if (h->aux_join) cudaEventDestroy(h->aux_join);
     if (h->aux_stream) cudaStreamDestroy(h->aux_stream);
@@ -652,6 +658,8 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
             pa.x = static_cast<const __nv_bfloat16*>(x_dev); pa.top_k = top_k; pa.tiles = h->pf_tiles; pa.max_tiles = h->pf_max_tiles;
             pa.xa = h->pf_xa; pa.xd = h->pf_xd; pa.rows_cap = h->rows_cap; pa.ro = static_cast<float*>(ro);
             pa.limit = limit; pa.status = h->status; pa.sm_count = h->sm_count;
+            // side by side with the streaming lane: the large-tile kernels also beside the small-tile ones
+            if (lane_aside) { pa.side = h->lane2_stream; pa.side_fork = h->lane2_fork; pa.side_join = h->lane2_join; }
             StageTimer tm(h, MLXS_STAGE_TENSOR_LANE, tl);
             CU(launch_exl3_prefill(pa, tl));
         }

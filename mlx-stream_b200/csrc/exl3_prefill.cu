@@ -500,14 +500,29 @@ static cudaError_t pf_launch_all(const Exl3PrefillArgs& a, cudaStream_t st) {
     // gate / up: both projections of one column block, tiles up to 64 rows (two CTAs per SM) or up to 192 rows
     P.code = a.L.gu_code; P.expert_stride_words = 2 * exl3_code_words(a.d); P.n_blocks = a.d.I / 128; P.nkt = a.d.H / 16;
     P.xa = a.xa; P.xa_proj_stride = exl3_prefill_staging_rows(a.rows_cap, a.max_tiles) * a.d.H; P.xd = a.xd; P.ro = nullptr;
-    cudaError_t e = pf_launch<2, 1, PF_CAP0, KB, 2>(P, a.sm_count, st);
-    if (e != cudaSuccess) return e;
-    if ((e = pf_launch<2, 1, PF_CAP1, KB, 1>(P, a.sm_count, st)) != cudaSuccess) return e;
+    PfParams D = P;
     // down: two adjacent column blocks per CTA
-    P.code = a.L.d_code; P.expert_stride_words = exl3_code_words(a.d); P.n_blocks = a.d.H / 128; P.nkt = a.d.I / 16;
-    P.xa = a.xd; P.xa_proj_stride = 0; P.xd = nullptr; P.ro = a.ro;
-    if ((e = pf_launch<1, 2, PF_CAP0, KB, 2>(P, a.sm_count, st)) != cudaSuccess) return e;
-    return pf_launch<1, 2, PF_CAP1, KB, 1>(P, a.sm_count, st);
+    D.code = a.L.d_code; D.expert_stride_words = exl3_code_words(a.d); D.n_blocks = a.d.H / 128; D.nkt = a.d.I / 16;
+    D.xa = a.xd; D.xa_proj_stride = 0; D.xd = nullptr; D.ro = a.ro;
+    // The two tile lists hold different experts and rows: with a side stream the large tiles' gate/up and down run
+    // beside the small tiles' (a few hot experts keep few CTAs busy for long; the other list fills the SMs meanwhile)
+    cudaError_t e;
+    const cudaStream_t s1 = a.side ? a.side : st;
+    if (a.side) {
+        if ((e = cudaEventRecord(a.side_fork, st)) != cudaSuccess || (e = cudaStreamWaitEvent(a.side, a.side_fork, 0)) != cudaSuccess) return e;
+    }
+    // (a refused launch does not skip the join: the side stream is always waited for before this returns)
+    e = pf_launch<2, 1, PF_CAP1, KB, 1>(P, a.sm_count, s1);
+    if (e == cudaSuccess && a.side) e = pf_launch<1, 2, PF_CAP1, KB, 1>(D, a.sm_count, s1);
+    if (e == cudaSuccess) e = pf_launch<2, 1, PF_CAP0, KB, 2>(P, a.sm_count, st);
+    if (e == cudaSuccess) e = pf_launch<1, 2, PF_CAP0, KB, 2>(D, a.sm_count, st);
+    if (e == cudaSuccess && !a.side) e = pf_launch<1, 2, PF_CAP1, KB, 1>(D, a.sm_count, st);
+    if (a.side) {
+        const cudaError_t j1 = cudaEventRecord(a.side_join, a.side);
+        const cudaError_t j2 = j1 == cudaSuccess ? cudaStreamWaitEvent(st, a.side_join, 0) : j1;
+        if (e == cudaSuccess) e = j2;
+    }
+    return e;
 }
 
 cudaError_t launch_exl3_prefill(const Exl3PrefillArgs& a, cudaStream_t st) {

@@ -78,6 +78,8 @@ struct mlxs_moe {
     // the tensor-core lane runs on a stream of its own beside the streaming lane
     cudaStream_t lane_stream = nullptr;
     cudaEvent_t lane_fork = nullptr, lane_join = nullptr;
+    cudaStream_t lane2_stream = nullptr;   // the tensor-core lane's large-tile kernels beside its small-tile kernels
+    cudaEvent_t lane2_fork = nullptr, lane2_join = nullptr;
     float* sh_out = nullptr;
     uint32_t* status = nullptr;
     uint8_t* staging = nullptr;

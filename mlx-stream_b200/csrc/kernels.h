@@ -174,6 +174,10 @@ struct Exl3PrefillArgs {
     float limit;
     uint32_t* status;
     int sm_count;
+    // optional: a stream for the kernels of the large tiles (they touch other experts than the small-tile kernels), with
+    // the two events that fork it from and join it into the call's stream; null: one stream
+    cudaStream_t side = nullptr;
+    cudaEvent_t side_fork = nullptr, side_join = nullptr;
 };
 // staging rows: every tile's rows padded to 16, tiles in sorted order
 static inline size_t exl3_prefill_staging_rows(size_t rows_cap, uint32_t max_tiles) { return rows_cap + 16 * (size_t)(2 * max_tiles + 1); }
