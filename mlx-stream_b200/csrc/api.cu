@@ -689,6 +689,7 @@ int mlxs_run_routed(mlxs_moe* h, uint32_t layer, const void* x_dev, const int32_
             pa.x = static_cast<const __nv_bfloat16*>(x_dev); pa.top_k = top_k; pa.tiles = h->pf_tiles; pa.max_tiles = h->pf_max_tiles;
             pa.xa = reinterpret_cast<uint16_t*>(h->pf_xa); pa.xd = reinterpret_cast<uint16_t*>(h->pf_xd);
             pa.ro = ro; pa.ro_bf16 = ro_bf16; pa.limit = limit; pa.status = h->status; pa.sm_count = h->sm_count;
+            if (lane_aside) { pa.side = h->lane2_stream; pa.side_fork = h->lane2_fork; pa.side_join = h->lane2_join; }
             StageTimer tm(h, MLXS_STAGE_TENSOR_LANE, tl);
             // MXFP4: the block-scaled tensor-core kind on the codes as stored, unless the handle was created with MLXS_MXFP4_NATIVE=0
             if (!pa.nv && h->mxfp4_native) CU(launch_mxfp4_native(pa, tl));

@@ -506,23 +506,14 @@ static cudaError_t pf_launch_all(const Exl3PrefillArgs& a, cudaStream_t st) {
     D.xa = a.xd; D.xa_proj_stride = 0; D.xd = nullptr; D.ro = a.ro;
     // The two tile lists hold different experts and rows: with a side stream the large tiles' gate/up and down run
     // beside the small tiles' (a few hot experts keep few CTAs busy for long; the other list fills the SMs meanwhile)
-    cudaError_t e;
-    const cudaStream_t s1 = a.side ? a.side : st;
-    if (a.side) {
-        if ((e = cudaEventRecord(a.side_fork, st)) != cudaSuccess || (e = cudaStreamWaitEvent(a.side, a.side_fork, 0)) != cudaSuccess) return e;
-    }
-    // (a refused launch does not skip the join: the side stream is always waited for before this returns)
-    e = pf_launch<2, 1, PF_CAP1, KB, 1>(P, a.sm_count, s1);
-    if (e == cudaSuccess && a.side) e = pf_launch<1, 2, PF_CAP1, KB, 1>(D, a.sm_count, s1);
-    if (e == cudaSuccess) e = pf_launch<2, 1, PF_CAP0, KB, 2>(P, a.sm_count, st);
-    if (e == cudaSuccess) e = pf_launch<1, 2, PF_CAP0, KB, 2>(D, a.sm_count, st);
-    if (e == cudaSuccess && !a.side) e = pf_launch<1, 2, PF_CAP1, KB, 1>(D, a.sm_count, st);
-    if (a.side) {
-        const cudaError_t j1 = cudaEventRecord(a.side_join, a.side);
-        const cudaError_t j2 = j1 == cudaSuccess ? cudaStreamWaitEvent(st, a.side_join, 0) : j1;
-        if (e == cudaSuccess) e = j2;
-    }
-    return e;
+    return prefill_lists_side_by_side(st, a.side, a.side_fork, a.side_join, [&](cudaStream_t s1) {
+        cudaError_t r = pf_launch<2, 1, PF_CAP1, KB, 1>(P, a.sm_count, s1);
+        if (r == cudaSuccess && a.side) r = pf_launch<1, 2, PF_CAP1, KB, 1>(D, a.sm_count, s1);
+        if (r == cudaSuccess) r = pf_launch<2, 1, PF_CAP0, KB, 2>(P, a.sm_count, st);
+        if (r == cudaSuccess) r = pf_launch<1, 2, PF_CAP0, KB, 2>(D, a.sm_count, st);
+        if (r == cudaSuccess && !a.side) r = pf_launch<1, 2, PF_CAP1, KB, 1>(D, a.sm_count, st);
+        return r;
+    });
 }
 
 cudaError_t launch_exl3_prefill(const Exl3PrefillArgs& a, cudaStream_t st) {

@@ -471,13 +471,20 @@ cudaError_t launch_mxfp4_native(const Fp4PrefillArgs& a, cudaStream_t st) {
     P.w = a.gu; P.n_blocks = a.I / 128; P.n_stages_k = a.H / NF_KS;
     P.expert_stride = (size_t)P.n_blocks * P.n_stages_k * 2 * (NF_W_STAGE + NF_S_STAGE);
     P.xa = xa; P.xd = xd; P.out = nullptr; P.out_bf16 = 0;
-    if ((e = nf_launch<2, 1, NF_CAP0, 2>(P, a.sm_count, st)) != cudaSuccess) return e;
-    if ((e = nf_launch<2, 1, NF_CAP1, 1>(P, a.sm_count, st)) != cudaSuccess) return e;
-    P.w = a.dn; P.n_blocks = a.H / 128; P.n_stages_k = a.I / NF_KS;
-    P.expert_stride = (size_t)P.n_blocks * P.n_stages_k * (NF_W_STAGE + NF_S_STAGE);
-    P.xa = xd; P.xd = nullptr; P.out = a.ro; P.out_bf16 = a.ro_bf16;
-    if ((e = nf_launch<1, 2, NF_CAP0, 2>(P, a.sm_count, st)) != cudaSuccess) return e;
-    return nf_launch<1, 2, NF_CAP1, 1>(P, a.sm_count, st);
+    NfParams D = P;
+    D.w = a.dn; D.n_blocks = a.H / 128; D.n_stages_k = a.I / NF_KS;
+    D.expert_stride = (size_t)D.n_blocks * D.n_stages_k * (NF_W_STAGE + NF_S_STAGE);
+    D.xa = xd; D.xd = nullptr; D.out = a.ro; D.out_bf16 = a.ro_bf16;
+    // the two tile lists hold different experts and rows: the large tiles' kernels run beside the small tiles' when the
+    // call has a side stream for them
+    return prefill_lists_side_by_side(st, a.side, a.side_fork, a.side_join, [&](cudaStream_t s1) {
+        cudaError_t r = nf_launch<2, 1, NF_CAP1, 1>(P, a.sm_count, s1);
+        if (r == cudaSuccess && a.side) r = nf_launch<1, 2, NF_CAP1, 1>(D, a.sm_count, s1);
+        if (r == cudaSuccess) r = nf_launch<2, 1, NF_CAP0, 2>(P, a.sm_count, st);
+        if (r == cudaSuccess) r = nf_launch<1, 2, NF_CAP0, 2>(D, a.sm_count, st);
+        if (r == cudaSuccess && !a.side) r = nf_launch<1, 2, NF_CAP1, 1>(D, a.sm_count, st);
+        return r;
+    });
 }
 
 }  // namespace mlxs

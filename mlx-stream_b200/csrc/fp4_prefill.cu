@@ -460,17 +460,21 @@ cudaError_t launch_fp4_prefill(const Fp4PrefillArgs& a, cudaStream_t st) {
     P.w = a.gu; P.w_bytes = 2 * (Q_W_STAGE + sstage); P.n_blocks = a.I / 128; P.n_stages_k = a.H / Q_KS;
     P.expert_stride = (size_t)P.n_blocks * P.n_stages_k * P.w_bytes;
     P.xa = a.xa; P.xd = a.xd; P.out = nullptr; P.out_bf16 = 0;
-    e = a.nv ? q_launch<2, 1, Q_CAP0, Q_KST, true, 2>(P, a.sm_count, st) : q_launch<2, 1, Q_CAP0, Q_KST, false, 2>(P, a.sm_count, st);
-    if (e != cudaSuccess) return e;
-    e = a.nv ? q_launch<2, 1, Q_CAP1, Q_KST, true, 1>(P, a.sm_count, st) : q_launch<2, 1, Q_CAP1, Q_KST, false, 1>(P, a.sm_count, st);
-    if (e != cudaSuccess) return e;
+    QParams D = P;
     // down: two adjacent column blocks per CTA
-    P.w = a.dn; P.w_bytes = Q_W_STAGE + sstage; P.n_blocks = a.H / 128; P.n_stages_k = a.I / Q_KS;
-    P.expert_stride = (size_t)P.n_blocks * P.n_stages_k * P.w_bytes;
-    P.xa = a.xd; P.xd = nullptr; P.out = a.ro; P.out_bf16 = a.ro_bf16;
-    e = a.nv ? q_launch<1, 2, Q_CAP0, Q_KST, true, 2>(P, a.sm_count, st) : q_launch<1, 2, Q_CAP0, Q_KST, false, 2>(P, a.sm_count, st);
-    if (e != cudaSuccess) return e;
-    return a.nv ? q_launch<1, 2, Q_CAP1, Q_KST, true, 1>(P, a.sm_count, st) : q_launch<1, 2, Q_CAP1, Q_KST, false, 1>(P, a.sm_count, st);
+    D.w = a.dn; D.w_bytes = Q_W_STAGE + sstage; D.n_blocks = a.H / 128; D.n_stages_k = a.I / Q_KS;
+    D.expert_stride = (size_t)D.n_blocks * D.n_stages_k * D.w_bytes;
+    D.xa = a.xd; D.xd = nullptr; D.out = a.ro; D.out_bf16 = a.ro_bf16;
+    // the two tile lists hold different experts and rows: the large tiles' kernels run beside the small tiles' when the
+    // call has a side stream for them
+    return prefill_lists_side_by_side(st, a.side, a.side_fork, a.side_join, [&](cudaStream_t s1) {
+        cudaError_t r = a.nv ? q_launch<2, 1, Q_CAP1, Q_KST, true, 1>(P, a.sm_count, s1) : q_launch<2, 1, Q_CAP1, Q_KST, false, 1>(P, a.sm_count, s1);
+        if (r == cudaSuccess && a.side) r = a.nv ? q_launch<1, 2, Q_CAP1, Q_KST, true, 1>(D, a.sm_count, s1) : q_launch<1, 2, Q_CAP1, Q_KST, false, 1>(D, a.sm_count, s1);
+        if (r == cudaSuccess) r = a.nv ? q_launch<2, 1, Q_CAP0, Q_KST, true, 2>(P, a.sm_count, st) : q_launch<2, 1, Q_CAP0, Q_KST, false, 2>(P, a.sm_count, st);
+        if (r == cudaSuccess) r = a.nv ? q_launch<1, 2, Q_CAP0, Q_KST, true, 2>(D, a.sm_count, st) : q_launch<1, 2, Q_CAP0, Q_KST, false, 2>(D, a.sm_count, st);
+        if (r == cudaSuccess && !a.side) r = a.nv ? q_launch<1, 2, Q_CAP1, Q_KST, true, 1>(D, a.sm_count, st) : q_launch<1, 2, Q_CAP1, Q_KST, false, 1>(D, a.sm_count, st);
+        return r;
+    });
 }
 
 }  // namespace mlxs

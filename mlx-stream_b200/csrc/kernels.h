@@ -242,7 +242,24 @@ struct Fp4PrefillArgs {
     float limit;
     uint32_t* status;
     int sm_count;
+    // optional: a stream for the kernels of the large tiles, with the events that fork it from and join it into the
+    // call's stream (as in Exl3PrefillArgs); null: one stream
+    cudaStream_t side = nullptr;
+    cudaEvent_t side_fork = nullptr, side_join = nullptr;
 };
+// the large-tile kernels beside the small-tile ones: fork before, join after (always, also after a refused launch)
+template <class F>
+static inline cudaError_t prefill_lists_side_by_side(cudaStream_t st, cudaStream_t side, cudaEvent_t fork_ev, cudaEvent_t join_ev, F&& launches) {
+    cudaError_t e = cudaSuccess;
+    if (side && ((e = cudaEventRecord(fork_ev, st)) != cudaSuccess || (e = cudaStreamWaitEvent(side, fork_ev, 0)) != cudaSuccess)) return e;
+    e = launches(side ? side : st);
+    if (side) {
+        const cudaError_t j1 = cudaEventRecord(join_ev, side);
+        const cudaError_t j2 = j1 == cudaSuccess ? cudaStreamWaitEvent(st, join_ev, 0) : j1;
+        if (e == cudaSuccess) e = j2;
+    }
+    return e;
+}
 // staging rows: every tile's rows padded to 16
 static inline size_t fp4_prefill_xa_bytes(uint32_t width, size_t rows_cap, uint32_t max_tiles) {
     return (rows_cap + 16 * (size_t)(2 * max_tiles + 1)) * width * 2;
