@@ -20,8 +20,10 @@
 //     a warp's chain per stage is barrier wait, decode, tensor-memory store latency, arrive, and with one team that
 //     chain, not the decode's instructions, set the stage time; two teams overlap each other's latencies.  A warp
 //     = (lane quarter q, team, half of the groups) decodes the tiles 2q and 2q + 1 of its groups for all 4 k-tiles;
-//   * one thread issues tcgen05.mma.kind::f16 (K = 16, A from tensor memory) and commits to mbarriers; it waits on one
-//     barrier per stage (decode warp 0 arrives only after it has seen the stage's rows land);
+//   * one thread issues tcgen05.mma.kind::f16 (K = 16, A from tensor memory) and commits once per stage (a commit costs
+//     it about as much as an MMA): the commit frees the operand slot, and the decode team that sees the slot free
+//     arrives on the rows' slot of the same stage on the MMAs' behalf; the thread waits on one barrier per stage (decode
+//     warp 0 arrives only after it has seen the stage's rows land);
 //   * the decode warps run the epilogue: tcgen05.ld, transpose through shared memory, then the same row-wise math as
 //     the decode-batch kernel (Hadamard-128, svh, clamped SwiGLU, suh_d, Hadamard for gate/up; Hadamard, svh_d for down).
 // Every wait is bounded; on a give-up the CTA sets the status word, skips work and still frees its tensor memory.
