@@ -376,6 +376,41 @@ def test_forward_is_capturable_in_a_cuda_graph():
         case.close()
 
 
+def test_call_with_both_lanes_is_capturable_in_a_cuda_graph():
+    """A call whose experts use the streaming lane and both tile lists of the tensor-core lane forks three side streams
+    (shared expert, tensor-core lane, the lane's large tiles) and joins them again: the capture stays valid and a replay
+    gives the eager call's bits."""
+    import torch
+    case = Exl3Case(512, 256, 4, 2, seed=12, shared=True, max_tokens=512)
+    try:
+        T = 300
+        x, logits = case.inputs(T, seed=31)
+        logits[:, 0] += 3.0          # every token: several large tiles
+        logits[:, 3] -= 2.5          # a handful of rows: streaming lane
+        ids, _ = case.cpu_route(logits)
+        counts = np.bincount(ids.reshape(-1), minlength=4)
+        assert counts.max() > 192 and ((counts > 0) & (counts < LANE_MIN_EXL3)).any(), counts   # large tiles and streaming rows
+        ref = case.gpu_forward(x, logits)
+        xd = case.to_dev_bf16(x)
+        lg = torch.from_numpy(logits).to(case.dev)
+        y = torch.zeros((T, case.H), dtype=torch.bfloat16, device=case.dev)
+        side = torch.cuda.Stream(device=case.dev)
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                case.moe.forward(0, xd.data_ptr(), lg.data_ptr(), T, y.data_ptr(), side.cuda_stream)
+        torch.cuda.synchronize()
+        for _ in range(2):
+            y.zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            assert (y.float().cpu().numpy() == ref).all()
+        assert case.status() == 0
+    finally:
+        case.close()
+
+
 def test_placement_refusals():
     case = Exl3Case(512, 256, 4, 2, seed=1, shared=False, max_tokens=8, experts_to_load=[])
     try:
