@@ -382,6 +382,21 @@ __global__ void __launch_bounds__(512 + 64, PER_SM) exl3_prefill_kernel(const Pf
             const uint32_t sub = warp >> 2;
             const uint32_t rows16 = (rows + 15) / 16 * 16;
             for (uint32_t ecb = 0; ecb < (uint32_t)CB && ok; ++ecb) {
+                // this lane's four columns of the block and their sign / scale vectors: the same for every row
+                const uint32_t col = (nb0 + ecb) * 128 + lane * 4;
+                float svg[4], svu[4], shd[4];
+                {
+                    const __half* sc = P.scales + (size_t)expert * P.scales_stride + 2 * (size_t)P.H;
+                    const uint2 s0 = *reinterpret_cast<const uint2*>(NPROJ == 2 ? sc + col : sc + 3 * (size_t)P.I + col);
+                    const uint2 s1 = *reinterpret_cast<const uint2*>(NPROJ == 2 ? sc + P.I + col : sc + 3 * (size_t)P.I + col);
+                    const uint2 s2 = *reinterpret_cast<const uint2*>(NPROJ == 2 ? sc + 2 * (size_t)P.I + col : sc + 3 * (size_t)P.I + col);
+                    const float2 a01 = __half22float2(*reinterpret_cast<const __half2*>(&s0.x)), a23 = __half22float2(*reinterpret_cast<const __half2*>(&s0.y));
+                    const float2 b01 = __half22float2(*reinterpret_cast<const __half2*>(&s1.x)), b23 = __half22float2(*reinterpret_cast<const __half2*>(&s1.y));
+                    const float2 c01 = __half22float2(*reinterpret_cast<const __half2*>(&s2.x)), c23 = __half22float2(*reinterpret_cast<const __half2*>(&s2.y));
+                    svg[0] = a01.x; svg[1] = a01.y; svg[2] = a23.x; svg[3] = a23.y;     // gate's svh, or down's svh_d
+                    svu[0] = b01.x; svu[1] = b01.y; svu[2] = b23.x; svu[3] = b23.y;     // up's svh
+                    shd[0] = c01.x; shd[1] = c01.y; shd[2] = c23.x; shd[3] = c23.y;     // down's suh
+                }
                 for (uint32_t rb = 0; rb < rows16 && ok; rb += PF_EPI_ROWS) {
                     // 16 warps: lane quarter q, then (projection, 16-row half) for gate/up; down uses warps 0..7
                     if (sub < 2u * NPROJ) {
@@ -398,7 +413,6 @@ __global__ void __launch_bounds__(512 + 64, PER_SM) exl3_prefill_kernel(const Pf
                         const uint32_t r = rb + rr;
                         if (r >= rows16) continue;
                         const bool valid = r < rows;
-                        const uint32_t col = (nb0 + ecb) * 128 + lane * 4;
                         if (NPROJ == 2) {
                             float vv[4] = {0.f, 0.f, 0.f, 0.f};
                             if (valid) {
@@ -407,18 +421,6 @@ __global__ void __launch_bounds__(512 + 64, PER_SM) exl3_prefill_kernel(const Pf
                                 float gq4[4] = {zg.x, zg.y, zg.z, zg.w}, uq4[4] = {zu.x, zu.y, zu.z, zu.w};
                                 hadamard128_warp(gq4, lane);
                                 hadamard128_warp(uq4, lane);
-                                const __half* sc = P.scales + (size_t)expert * P.scales_stride;
-                                const uint2 sg = *reinterpret_cast<const uint2*>(sc + 2 * (size_t)P.H + col);
-                                const uint2 su = *reinterpret_cast<const uint2*>(sc + 2 * (size_t)P.H + P.I + col);
-                                const uint2 sd = *reinterpret_cast<const uint2*>(sc + 2 * (size_t)P.H + 2 * (size_t)P.I + col);
-                                const float2 sg01 = __half22float2(*reinterpret_cast<const __half2*>(&sg.x));
-                                const float2 sg23 = __half22float2(*reinterpret_cast<const __half2*>(&sg.y));
-                                const float2 su01 = __half22float2(*reinterpret_cast<const __half2*>(&su.x));
-                                const float2 su23 = __half22float2(*reinterpret_cast<const __half2*>(&su.y));
-                                const float2 sd01 = __half22float2(*reinterpret_cast<const __half2*>(&sd.x));
-                                const float2 sd23 = __half22float2(*reinterpret_cast<const __half2*>(&sd.y));
-                                const float svg[4] = {sg01.x, sg01.y, sg23.x, sg23.y}, svu[4] = {su01.x, su01.y, su23.x, su23.y};
-                                const float shd[4] = {sd01.x, sd01.y, sd23.x, sd23.y};
 #pragma unroll
                                 for (int qq = 0; qq < 4; ++qq) {
                                     const float gm = (gq4[qq] * S) * svg[qq], um = (uq4[qq] * S) * svu[qq];
@@ -440,13 +442,9 @@ __global__ void __launch_bounds__(512 + 64, PER_SM) exl3_prefill_kernel(const Pf
                             const float4 z4 = *reinterpret_cast<const float4*>(zs + rr * PF_ZS_STRIDE + lane * 4);
                             float vv[4] = {z4.x, z4.y, z4.z, z4.w};
                             hadamard128_warp(vv, lane);
-                            const __half* sc = P.scales + (size_t)expert * P.scales_stride + 2 * (size_t)P.H + 3 * (size_t)P.I;
-                            const uint2 so = *reinterpret_cast<const uint2*>(sc + col);
-                            const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&so.x));
-                            const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&so.y));
                             const uint32_t assign = P.t.order[row0 + r];
                             *reinterpret_cast<float4*>(P.ro + (size_t)assign * P.H + col) =
-                                make_float4((vv[0] * S) * s01.x, (vv[1] * S) * s01.y, (vv[2] * S) * s23.x, (vv[3] * S) * s23.y);
+                                make_float4((vv[0] * S) * svg[0], (vv[1] * S) * svg[1], (vv[2] * S) * svg[2], (vv[3] * S) * svg[3]);
                         }
                     }
                     if (!epi_sync()) { ok = false; break; }
